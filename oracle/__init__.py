@@ -1,0 +1,208 @@
+"""ctypes binding of the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Only tests/, the smoke check and bench.py's CPU-baseline legs may import this module; the
+shipped package never does.  The oracle restates catena-lang's generated code on the host
+(see catena_oracle.cpp for the per-function reference citations).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libcatena_oracle.so")
+
+UNARY_OPS = ["math.sin-approx", "math.cos-approx", "math.sin-approx-full-nonneg",
+             "math.sin-approx-full", "math.log-approx", "math.exp-approx-nonneg",
+             "math.exp-approx", "math.exp2-approx", "math.log2-approx", None, "math.sqrt",
+             "nn.sigmoid", "nn.silu", "nn.tanh", "nn.gelu-approx"]
+
+
+def build(force=False):
+    src = os.path.join(_HERE, "catena_oracle.cpp")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "libcatena_oracle.so"],
+                              stdout=subprocess.DEVNULL)
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        L = C.CDLL(_SO)
+        f32, u64, i32, vp = C.c_float, C.c_uint64, C.c_int, C.c_void_p
+        for name in ["sin_approx", "cos_approx", "sin_approx_full_nonneg", "sin_approx_full",
+                     "log_approx", "exp_approx_nonneg", "exp_approx", "exp2_approx",
+                     "log2_approx", "sqrt"]:
+            fn = getattr(L, "orc_math_" + name)
+            fn.restype, fn.argtypes = f32, [f32]
+        for name in ["sigmoid", "silu", "tanh", "gelu_approx"]:
+            fn = getattr(L, "orc_nn_" + name)
+            fn.restype, fn.argtypes = f32, [f32]
+        L.orc_math_powf.restype, L.orc_math_powf.argtypes = f32, [f32, f32]
+        L.orc_f32_fma.restype, L.orc_f32_fma.argtypes = f32, [f32, f32, f32]
+        L.orc_f32_mul_add.restype, L.orc_f32_mul_add.argtypes = f32, [f32, f32, f32]
+        L.orc_map_unary.restype, L.orc_map_unary.argtypes = None, [i32, vp, vp, u64, i32]
+        L.orc_sum_f32.restype, L.orc_sum_f32.argtypes = f32, [vp, u64]
+        L.orc_mean_f32.restype, L.orc_mean_f32.argtypes = f32, [vp, u64]
+        L.orc_max_f32.restype, L.orc_max_f32.argtypes = f32, [vp, u64]
+        L.orc_sum_u64.restype, L.orc_sum_u64.argtypes = u64, [vp, u64]
+        L.orc_dot_u64.restype, L.orc_dot_u64.argtypes = u64, [vp, vp, u64]
+        L.orc_tensor_argmax_f32.restype, L.orc_tensor_argmax_f32.argtypes = u64, [vp, u64]
+        L.orc_nn_softmax.restype, L.orc_nn_softmax.argtypes = None, [vp, vp, u64, i32]
+        L.orc_nn_rmsnorm.restype, L.orc_nn_rmsnorm.argtypes = None, [vp, vp, u64, i32]
+        L.orc_tensor_broadcast_f32.restype, L.orc_tensor_broadcast_f32.argtypes = None, [f32, u64, vp]
+        L.orc_tensor_arange_f32.restype, L.orc_tensor_arange_f32.argtypes = None, [u64, vp]
+        L.orc_tensor_slice_f32.restype, L.orc_tensor_slice_f32.argtypes = i32, [vp, u64, u64, u64, vp]
+        L.orc_tensor_concat_f32.restype, L.orc_tensor_concat_f32.argtypes = None, [vp, u64, vp, u64, vp]
+        L.orc_matmul_f32.restype = i32
+        L.orc_matmul_f32.argtypes = [vp, u64, vp, u64, u64, u64, u64, u64, u64, u64, vp, i32]
+        L.orc_matmul_f32_rows.restype = None
+        L.orc_matmul_f32_rows.argtypes = [vp, vp, u64, u64, u64, u64, vp, i32]
+        L.orc_gemm_bf16_rows.restype = None
+        L.orc_gemm_bf16_rows.argtypes = [vp, vp, u64, u64, u64, u64, vp, vp, i32]
+        L.orc_gemm_i8_rows.restype = None
+        L.orc_gemm_i8_rows.argtypes = [vp, vp, u64, u64, u64, u64, vp, i32]
+        L.orc_attn_decode_bf16.restype = None
+        L.orc_attn_decode_bf16.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, f32, u64, u64, vp, vp, i32]
+        L.orc_max_threads.restype = i32
+        L.orc_f32_to_bf16.restype, L.orc_f32_to_bf16.argtypes = C.c_uint16, [f32]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def max_threads():
+    return int(lib().orc_max_threads())
+
+
+def scalar(name, *args):
+    """Evaluate a scalar stdlib program, e.g. scalar('math.exp-approx', 0.5)."""
+    sym = "orc_" + name.replace(".", "_").replace("-", "_")
+    return float(getattr(lib(), sym)(*[C.c_float(a) for a in args]))
+
+
+def map_unary(name, x, threads=1):
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().orc_map_unary(UNARY_OPS.index(name), _p(x), _p(y), x.size, threads)
+    return y
+
+
+def sum_f32(x):
+    x = _f32(x); return np.float32(lib().orc_sum_f32(_p(x), x.size))
+
+
+def mean_f32(x):
+    x = _f32(x); return np.float32(lib().orc_mean_f32(_p(x), x.size))
+
+
+def max_f32(x):
+    x = _f32(x); return np.float32(lib().orc_max_f32(_p(x), x.size))
+
+
+def sum_u64(x):
+    x = np.ascontiguousarray(x, dtype=np.uint64); return int(lib().orc_sum_u64(_p(x), x.size))
+
+
+def dot_u64(x, y):
+    x = np.ascontiguousarray(x, dtype=np.uint64); y = np.ascontiguousarray(y, dtype=np.uint64)
+    return int(lib().orc_dot_u64(_p(x), _p(y), x.size))
+
+
+def argmax_f32(x):
+    x = _f32(x); return int(lib().orc_tensor_argmax_f32(_p(x), x.size))
+
+
+def softmax(x, threads=1):
+    x = _f32(x); y = np.empty_like(x); lib().orc_nn_softmax(_p(x), _p(y), x.size, threads); return y
+
+
+def rmsnorm(x, threads=1):
+    x = _f32(x); y = np.empty_like(x); lib().orc_nn_rmsnorm(_p(x), _p(y), x.size, threads); return y
+
+
+def broadcast_f32(v, n):
+    y = np.empty(n, np.float32); lib().orc_tensor_broadcast_f32(C.c_float(v), n, _p(y)); return y
+
+
+def arange_f32(n):
+    y = np.empty(n, np.float32); lib().orc_tensor_arange_f32(n, _p(y)); return y
+
+
+def slice_f32(x, start, length):
+    x = _f32(x); y = np.empty(length, np.float32)
+    rc = lib().orc_tensor_slice_f32(_p(x), x.size, start, length, _p(y))
+    if rc:
+        raise IndexError("tensor.slice-f32: bounds assert (the reference traps here)")
+    return y
+
+
+def concat_f32(l, r):
+    l = _f32(l); r = _f32(r); y = np.empty(l.size + r.size, np.float32)
+    lib().orc_tensor_concat_f32(_p(l), l.size, _p(r), r.size, _p(y)); return y
+
+
+def matmul_f32(a, b, n, m, k, threads=1):
+    a = _f32(a).ravel(); b = _f32(b).ravel(); out = np.empty(n * m, np.float32)
+    rc = lib().orc_matmul_f32(_p(a), a.size, _p(b), b.size, n, m, k, n * k, k * m, n * m, _p(out), threads)
+    if rc:
+        raise ValueError("matmul: length assert (the reference traps here)")
+    return out
+
+
+def matmul_f32_rows(a, b, m, k, row0, row1, threads=1):
+    a = _f32(a).ravel(); b = _f32(b).ravel(); out = np.empty((row1 - row0) * m, np.float32)
+    lib().orc_matmul_f32_rows(_p(a), _p(b), m, k, row0, row1, _p(out), threads); return out
+
+
+def gemm_bf16_rows(a_bits, bt_bits, N, K, row0, row1, threads=1, want_f32=False):
+    """a_bits [M,K] uint16 (bf16 bits), bt_bits [N,K] uint16 -> bf16 bits [(row1-row0), N]."""
+    a = np.ascontiguousarray(a_bits, dtype=np.uint16); bt = np.ascontiguousarray(bt_bits, dtype=np.uint16)
+    c = np.empty(((row1 - row0), N), np.uint16)
+    cf = np.empty(((row1 - row0), N), np.float32) if want_f32 else None
+    lib().orc_gemm_bf16_rows(_p(a), _p(bt), N, K, row0, row1, _p(c), _p(cf), threads)
+    return (c, cf) if want_f32 else c
+
+
+def gemm_i8_rows(a, bt, N, K, row0, row1, threads=1):
+    a = np.ascontiguousarray(a, dtype=np.int8); bt = np.ascontiguousarray(bt, dtype=np.int8)
+    c = np.empty(((row1 - row0), N), np.int32)
+    lib().orc_gemm_i8_rows(_p(a), _p(bt), N, K, row0, row1, _p(c), threads); return c
+
+
+def attn_decode_bf16(q, k, v, B, Hq, Hkv, D, L, scale, unit0=0, unit1=None, threads=1, want_f32=False):
+    """q [B,Hq,D], k/v [B,Hkv,L,D] as bf16 bit patterns (uint16) -> o bits [B,Hq,D]."""
+    q = np.ascontiguousarray(q, dtype=np.uint16); k = np.ascontiguousarray(k, dtype=np.uint16)
+    v = np.ascontiguousarray(v, dtype=np.uint16)
+    if unit1 is None:
+        unit1 = B * Hq
+    o = np.zeros((B, Hq, D), np.uint16)
+    of = np.zeros((B, Hq, D), np.float32) if want_f32 else None
+    lib().orc_attn_decode_bf16(_p(q), _p(k), _p(v), B, Hq, Hkv, D, L, C.c_float(scale), unit0, unit1,
+                               _p(o), _p(of), threads)
+    return (o, of) if want_f32 else o
+
+
+def f32_to_bf16_bits(x):
+    """Round-to-nearest-even f32 -> bf16 bit patterns (numpy, same rule as the oracle)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return r
+
+
+def bf16_bits_to_f32(b):
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
