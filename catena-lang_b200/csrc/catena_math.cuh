@@ -1,0 +1,156 @@
+// Scalar arithmetic of the catena stdlib as `__host__ __device__` functions whose results are
+// bit-identical on host and device and independent of compiler flags: every f32 operation is an
+// explicitly rounded intrinsic on the device (`__fmul_rn`, `__fadd_rn`, ... are never contracted
+// into FMAs, whatever -fmad says) and a plain operator on the host (the host objects are built
+// with -ffp-contract=off).  This is the determinism contract the reference gets from
+// `--fmad=false` (catena-lang/src/runtime/artifact.rs:59-80) and from `f32.mul`/`f32.add` being
+// separate C expressions (catena-lang/src/codegen/gpu.rs:322-447).
+//
+// Formulas and constants: catena-lang/stdlib/math.hex and catena-lang/stdlib/nn.hex (cited per
+// function).  The polynomials are the reference's own low-order approximations — they are part
+// of the semantics (math.exp-approx(0) is 0x3F7FF8FC, not 1).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#define CM_HD __host__ __device__ __forceinline__
+
+namespace cmath {
+
+#ifdef __CUDA_ARCH__
+CM_HD float mul(float a, float b) { return __fmul_rn(a, b); }
+CM_HD float add(float a, float b) { return __fadd_rn(a, b); }
+CM_HD float sub(float a, float b) { return __fsub_rn(a, b); }
+CM_HD float div(float a, float b) { return __fdiv_rn(a, b); }
+CM_HD float from_bits(uint32_t u) { return __uint_as_float(u); }
+CM_HD uint32_t to_bits(float f) { return __float_as_uint(f); }
+CM_HD uint32_t round_to_u32(float x) { return __float2uint_rn(x); }   // (uint32_t)nearbyintf(x), gpu.rs:642-655
+CM_HD float u32_to_f32(uint32_t x) { return __uint2float_rn(x); }
+CM_HD float u64_to_f32(uint64_t x) { return __ull2float_rn(x); }
+#else
+CM_HD float mul(float a, float b) { return a * b; }
+CM_HD float add(float a, float b) { return a + b; }
+CM_HD float sub(float a, float b) { return a - b; }
+CM_HD float div(float a, float b) { return a / b; }
+CM_HD float from_bits(uint32_t u) { union { uint32_t u; float f; } v; v.u = u; return v.f; }
+CM_HD uint32_t to_bits(float f) { union { uint32_t u; float f; } v; v.f = f; return v.u; }
+CM_HD uint32_t round_to_u32(float x) { return (uint32_t)nearbyintf(x); }
+CM_HD float u32_to_f32(uint32_t x) { return (float)x; }
+CM_HD float u64_to_f32(uint64_t x) { return (float)x; }
+#endif
+
+// math.hex:3-23
+CM_HD float sin_approx(float x) {
+    float x2 = mul(x, x), x3 = mul(x2, x), x5 = mul(x3, x2), x7 = mul(x5, x2);
+    float p1 = sub(x, div(x3, 6.0f));
+    float p2 = add(p1, div(x5, 120.0f));
+    return sub(p2, div(x7, 5040.0f));
+}
+
+// math.hex:27-47
+CM_HD float cos_approx(float x) {
+    float x2 = mul(x, x), x4 = mul(x2, x2), x6 = mul(x4, x2);
+    float p1 = sub(1.0f, div(x2, 2.0f));
+    float p2 = add(p1, div(x4, 24.0f));
+    return sub(p2, div(x6, 720.0f));
+}
+
+// math.hex:52-87 (Cody-Waite reduction by pi/2, quadrant select)
+CM_HD float sin_full_nonneg(float x) {
+    uint32_t n = round_to_u32(mul(x, from_bits(0x3F22F983u)));
+    float nf = u32_to_f32(n);
+    float r = sub(sub(x, mul(nf, from_bits(0x3FC90FDAu))), mul(nf, from_bits(0x33A22168u)));
+    float s = sin_approx(r), c = cos_approx(r);
+    uint32_t q = n & 3u;
+    float q23 = (q == 2u) ? -s : -c;
+    float q123 = (q == 1u) ? c : q23;
+    return (q == 0u) ? s : q123;
+}
+
+// math.hex:91-103
+CM_HD float sin_full(float x) {
+    bool neg = x < 0.0f;
+    float base = sin_full_nonneg(neg ? -x : x);
+    return neg ? -base : base;
+}
+
+// math.hex:110-144
+CM_HD float log_approx(float x) {
+    uint32_t xb = to_bits(x);
+    float m = from_bits((xb & 0x007FFFFFu) + 0x3F000000u);
+    float e = sub(u32_to_f32(xb >> 23), 126.0f);
+    float p2 = add(from_bits(0xC03AA687u), mul(m, from_bits(0x3F60A4E1u)));
+    float p1 = add(from_bits(0x4087355Au), mul(m, p2));
+    float poly = add(from_bits(0xC00BE629u), mul(m, p1));
+    return add(poly, mul(e, from_bits(0x3F317218u)));
+}
+
+// math.hex:148-183
+CM_HD float exp_nonneg(float x) {
+    uint32_t k = round_to_u32(mul(x, from_bits(0x3FB8AA3Bu)));
+    float kf = u32_to_f32(k);
+    float xr = sub(sub(x, mul(kf, from_bits(0x3F317200u))), mul(kf, from_bits(0x35BFBE8Eu)));
+    float p2 = add(from_bits(0x3EEF1187u), mul(xr, from_bits(0x3E738A8Bu)));
+    float p1 = add(from_bits(0x3F809C7Eu), mul(xr, p2));
+    float poly = add(from_bits(0x3F7FF8FCu), mul(xr, p1));
+    uint32_t pow2_bits = (k + 0x7Fu) * 0x00800000u;  // wraps in u32, as in the reference
+    return mul(poly, from_bits(pow2_bits));
+}
+
+// math.hex:185-199
+CM_HD float exp_approx(float x) {
+    bool neg = x < 0.0f;
+    float base = exp_nonneg(neg ? -x : x);
+    return neg ? div(1.0f, base) : base;
+}
+
+// math.hex:202-231
+CM_HD float exp2_approx(float x) { return exp_approx(mul(x, from_bits(0x3F317218u))); }
+CM_HD float log2_approx(float x) { return mul(log_approx(x), from_bits(0x3FB8AA3Bu)); }
+CM_HD float powf_approx(float x, float y) { return exp2_approx(mul(y, log2_approx(x))); }
+
+// math.hex:235-272 (six Newton steps from max(1, x); 0 for x <= 0)
+CM_HD float sqrt_newton(float x) {
+    float g = (x < 1.0f) ? 1.0f : x;
+#pragma unroll
+    for (int it = 0; it < 6; ++it) g = mul(add(g, div(x, g)), 0.5f);
+    return (x <= 0.0f) ? 0.0f : g;
+}
+
+// nn.hex:2-56
+CM_HD float sigmoid(float x) { return div(1.0f, add(1.0f, exp_approx(-x))); }
+CM_HD float silu(float x) { return mul(x, sigmoid(x)); }
+CM_HD float tanh_approx(float x) { return sub(mul(sigmoid(mul(x, 2.0f)), 2.0f), 1.0f); }
+CM_HD float gelu_approx(float x) {
+    float x3 = mul(mul(x, x), x);
+    float inner = add(x, mul(x3, from_bits(0x3D372713u)));
+    float shaped = tanh_approx(mul(inner, from_bits(0x3F4C422Au)));
+    return mul(mul(x, add(1.0f, shaped)), 0.5f);
+}
+
+enum MapOp {
+    OP_SIN_APPROX = 0, OP_COS_APPROX, OP_SIN_FULL_NONNEG, OP_SIN_FULL, OP_LOG, OP_EXP_NONNEG, OP_EXP,
+    OP_EXP2, OP_LOG2, OP_SQRT, OP_SIGMOID, OP_SILU, OP_TANH, OP_GELU, OP_COUNT
+};
+
+template <int OP>
+CM_HD float apply(float x) {
+    if (OP == OP_SIN_APPROX) return sin_approx(x);
+    if (OP == OP_COS_APPROX) return cos_approx(x);
+    if (OP == OP_SIN_FULL_NONNEG) return sin_full_nonneg(x);
+    if (OP == OP_SIN_FULL) return sin_full(x);
+    if (OP == OP_LOG) return log_approx(x);
+    if (OP == OP_EXP_NONNEG) return exp_nonneg(x);
+    if (OP == OP_EXP) return exp_approx(x);
+    if (OP == OP_EXP2) return exp2_approx(x);
+    if (OP == OP_LOG2) return log2_approx(x);
+    if (OP == OP_SQRT) return sqrt_newton(x);
+    if (OP == OP_SIGMOID) return sigmoid(x);
+    if (OP == OP_SILU) return silu(x);
+    if (OP == OP_TANH) return tanh_approx(x);
+    return gelu_approx(x);
+}
+
+}  // namespace cmath

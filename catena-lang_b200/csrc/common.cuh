@@ -1,0 +1,85 @@
+// Shared declarations of the kernel library: status handling, per-thread runtime state,
+// launch bookkeeping.  Internal — the public surface is include/catena_b200.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/catena_b200.h"
+
+namespace catena {
+
+// Per-host-thread library state.  The generated code of the reference uses the process-global
+// current device and the default stream (catena-lang/doc/CODEGEN.md:164-166); here both are
+// explicit so one process per GPU (or one thread per GPU) can drive the library.
+struct ThreadState {
+    int device = -1;           // -1: not initialised
+    cudaStream_t stream = 0;   // legacy default stream unless set
+    int blocking = 1;          // synchronise after each entry point
+    catena_status_t last = CATENA_OK;
+    int sm_count = 0;
+    int cc_major = 0;
+};
+
+ThreadState& tls();
+
+// Makes sure a device is bound (lazy init on device 0).  Returns CATENA_OK or an error.
+catena_status_t ensure_device();
+
+// Records a failure: remembers it for catena_b200_last_status and prints one line.
+catena_status_t fail(catena_status_t s, const char* what);
+catena_status_t fail_cuda(cudaError_t e, const char* what);
+
+void count_launch(uint64_t n = 1);
+
+// Pool allocator (mem.cu).
+catena_status_t pool_alloc(uint64_t bytes, void** out);
+catena_status_t pool_free(void* p);
+
+// After enqueuing: check launch error, optionally synchronise.
+catena_status_t finish(const char* what);
+
+#define CATENA_CUDA(expr)                                                   \
+    do {                                                                    \
+        cudaError_t _e = (expr);                                            \
+        if (_e != cudaSuccess) return ::catena::fail_cuda(_e, #expr);       \
+    } while (0)
+
+#define CATENA_TRY(expr)                                                    \
+    do {                                                                    \
+        catena_status_t _s = (expr);                                        \
+        if (_s != CATENA_OK) return _s;                                     \
+    } while (0)
+
+static inline uint64_t ceil_div_u64(uint64_t a, uint64_t b) { return (a + b - 1) / b; }
+
+// ---- launchers implemented by the kernel files (all enqueue on tls().stream) ------------
+// gemm_f32.cu
+catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint64_t n, uint64_t m,
+                                  uint64_t k);
+catena_status_t launch_identity_matmul_f32(const float* a, float* c, uint64_t n, int identity_on_left);
+// gemm_tc.cu
+catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
+                               uint64_t ldc, int is_i8);
+catena_status_t gemm_tc_check_errors();
+void gemm_tc_set_cta_limit(int limit);
+// attn_decode.cu
+catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
+                                   uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t unit0,
+                                   uint64_t unit1);
+catena_status_t attn_check_errors();
+// map_reduce.cu
+enum ReduceKind { RED_SUM = 0, RED_MAX = 1, RED_SUMSQ = 2 };
+int map_op_from_name(const char* name);  // -1 if unknown
+catena_status_t launch_map_unary(int op, const float* in, float* out, uint64_t n);
+catena_status_t reduce_f32(int kind, const float* in, uint64_t n, float* host_out);
+catena_status_t argmax_f32(const float* in, uint64_t n, uint64_t* host_out);
+catena_status_t launch_softmax(const float* in, float* out, uint64_t n);
+catena_status_t launch_rmsnorm(const float* in, float* out, uint64_t n);
+catena_status_t launch_broadcast(float v, float* out, uint64_t n);
+catena_status_t launch_arange(float* out, uint64_t n);
+catena_status_t launch_slice(const float* in, uint64_t start, float* out, uint64_t n);
+catena_status_t launch_concat(const float* l, uint64_t nl, const float* r, uint64_t nr, float* out);
+
+}  // namespace catena

@@ -1,0 +1,129 @@
+// f32 matrix product with the reference's exact semantics
+// (catena-lang/stdlib/matrix.hex:210-327, entry catena-lang/tests/cases/matrix/matmul.hex:2-63):
+//
+//     C[i,j] = (((+0 + a_i0*b_0j) + a_i1*b_1j) + ... + a_i,K-1*b_K-1,j)
+//
+// with `*` and `+` rounded separately (never an FMA) and k strictly ascending.  The reference
+// runs one thread per output with an untiled K loop; here A and B are staged through shared
+// memory in k-slabs and every thread keeps a TM x TN register tile, but each output element
+// still owns its own accumulation chain in the same order, so results are bit-identical for
+// every tile shape.  The K loop never pads: a trailing partial slab stops at exactly K (adding
+// `+0` terms could flip a `-0` accumulator to `+0`).  tcgen05 has no fp32 input mode and tensor
+// cores do not accumulate as a sequential IEEE chain, so this kernel is CUDA-core work by design.
+#include "common.cuh"
+
+namespace catena {
+
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int n, int m,
+                  int k) {
+    constexpr int THREADS = (BM / TM) * (BN / TN);
+    __shared__ float As[BK][BM + 4];  // transposed: As[kk][row]
+    __shared__ float Bs[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN);   // column group
+    const int ty = tid / (BN / TN);   // row group
+    const int row0 = blockIdx.y * BM;
+    const int col0 = blockIdx.x * BN;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;  // bit pattern 0x00000000 (matrix.hex:249)
+
+    for (int k0 = 0; k0 < k; k0 += BK) {
+        const int kb = min(BK, k - k0);
+        // stage A[row0.., k0..] transposed and B[k0.., col0..]
+        for (int idx = tid; idx < BM * BK; idx += THREADS) {
+            int r = idx / BK, kk = idx % BK;
+            int gr = row0 + r, gk = k0 + kk;
+            As[kk][r] = (gr < n && gk < k) ? A[(size_t)gr * k + gk] : 0.0f;
+        }
+        for (int idx = tid; idx < BK * BN; idx += THREADS) {
+            int kk = idx / BN, c = idx % BN;
+            int gk = k0 + kk, gc = col0 + c;
+            Bs[kk][c] = (gk < k && gc < m) ? B[(size_t)gk * m + gc] : 0.0f;
+        }
+        __syncthreads();
+        if (kb == BK) {
+#pragma unroll
+            for (int kk = 0; kk < BK; ++kk) {
+                float a[TM], b[TN];
+#pragma unroll
+                for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+                for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+                for (int i = 0; i < TM; ++i)
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));
+            }
+        } else {
+            for (int kk = 0; kk < kb; ++kk) {
+#pragma unroll
+                for (int i = 0; i < TM; ++i)
+#pragma unroll
+                    for (int j = 0; j < TN; ++j)
+                        acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(As[kk][ty * TM + i], Bs[kk][tx * TN + j]));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        int gr = row0 + ty * TM + i;
+        if (gr >= n) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            int gc = col0 + tx * TN + j;
+            if (gc < m) C[(size_t)gr * m + gc] = acc[i][j];
+        }
+    }
+}
+
+// A * I or I * A with the identity generated on the fly (catena-lang/stdlib/matrix.hex:129-159):
+// every output is the same left fold, whose terms are a*1 and a*0.
+__global__ void identity_matmul_kernel(const float* __restrict__ A, float* __restrict__ C, int n, int left) {
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n * n) return;
+    int i = idx / n, j = idx % n;
+    float acc = 0.0f;
+    for (int kk = 0; kk < n; ++kk) {
+        float a = left ? (i == kk ? 1.0f : 0.0f) : A[(size_t)i * n + kk];
+        float b = left ? A[(size_t)kk * n + j] : (kk == j ? 1.0f : 0.0f);
+        acc = __fadd_rn(acc, __fmul_rn(a, b));
+    }
+    C[idx] = acc;
+}
+
+catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint64_t n, uint64_t m, uint64_t k) {
+    if (n == 0 || m == 0) return CATENA_OK;
+    if (n > 0x7FFFFFFFull || m > 0x7FFFFFFFull || k > 0x7FFFFFFFull)
+        return fail(CATENA_E_TOO_LARGE, "matmul f32: dimension beyond 2^31-1");
+    cudaStream_t st = tls().stream;
+    int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+    uint64_t big_tiles = ceil_div_u64(n, 64) * ceil_div_u64(m, 64);
+    if (big_tiles >= (uint64_t)sms) {
+        dim3 grid((unsigned)ceil_div_u64(m, 64), (unsigned)ceil_div_u64(n, 64));
+        matmul_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+    } else {
+        // small products are latency bound: more, smaller tiles to cover the SMs
+        dim3 grid((unsigned)ceil_div_u64(m, 16), (unsigned)ceil_div_u64(n, 16));
+        matmul_f32_kernel<16, 16, 32, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+    }
+    count_launch();
+    return CATENA_OK;
+}
+
+catena_status_t launch_identity_matmul_f32(const float* a, float* c, uint64_t n, int identity_on_left) {
+    if (n == 0) return CATENA_OK;
+    if (n > 46340) return fail(CATENA_E_TOO_LARGE, "identity matmul: n*n beyond 2^31-1");
+    unsigned total = (unsigned)(n * n);
+    identity_matmul_kernel<<<(total + 255) / 256, 256, 0, tls().stream>>>(a, c, (int)n, identity_on_left);
+    count_launch();
+    return CATENA_OK;
+}
+
+}  // namespace catena

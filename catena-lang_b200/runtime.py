@@ -1,0 +1,262 @@
+"""Host-side mirror of the reference's runtime surface over the prebuilt kernel library.
+
+Names, argument meaning and error behaviour follow catena-lang/src/runtime:
+  Runtime.from_sources / Runtime.new / exec / mem_f32 / mem_u64   runtime.rs:104-236
+  Value, ValueKind                                                value.rs:5-73
+  Mem.to_f32_vec / to_u64_vec                                     mem.rs:43-70
+  ExecError variants                                              runtime.rs:80-102
+  GpuDialect {Hip, Cuda}                                          codegen/mod.rs:50-54
+
+What differs, by design of a native lowering that SELECTS prebuilt sm_100a kernels instead of
+generating and compiling C++ per Runtime (runtime.rs:123-164, artifact.rs:56-103):
+  * `from_sources` does not run the catena compiler (its front end, the third-party `metacat`
+    crate, is Rust and not part of this build).  It scans the sources for `(def program <name>`
+    and builds the signature table (signature.rs:18-61) from the catalogue of programs the library
+    ships; a program it has no kernel for stays out of the table, so `exec` reports
+    UnknownSourceFunction for it.  The stdlib entry points are always present.
+  * `GpuDialect.Hip` is refused with InitError (no multi-backend dispatch).
+  * `Mem` owns device memory (cudaMalloc pool) and copies on `to_*_vec`, instead of dereferencing
+    managed memory.  Like the Rust API, `exec` consumes its `Mem` arguments: they are freed when
+    the call returns (runtime.rs:175-179, mem.rs:119-125).
+"""
+import ctypes as C
+import enum
+import re
+
+import numpy as np
+
+
+class GpuDialect(enum.Enum):
+    Hip = "hip"
+    Cuda = "cuda"
+
+
+class ValueKind(enum.Enum):
+    Bool = "Bool"
+    U32 = "U32"
+    U64 = "U64"
+    F32 = "F32"
+    Mem = "Mem"
+
+
+class InitError(RuntimeError):
+    pass
+
+
+class ExecError(RuntimeError):
+    """kind is one of UnknownSourceFunction, TypeMismatch, InputArityMismatch, OutputArityMismatch
+    (runtime.rs:80-102) or Device (a status from the library; the reference would have trapped)."""
+
+    def __init__(self, kind, message, status=None):
+        super().__init__(message)
+        self.kind = kind
+        self.status = status
+
+
+class Mem:
+    """Owned device buffer: fat pointer {data, len_bytes} (mem.rs:38-41)."""
+
+    def __init__(self, raw=None):
+        from . import CatenaMem
+        self.raw = raw if raw is not None else CatenaMem()
+
+    @property
+    def len_bytes(self):
+        return int(self.raw.len)
+
+    def is_null(self):
+        return not self.raw.data
+
+    def to_f32_vec(self):
+        from . import download
+        return download(self.raw, np.float32)
+
+    def to_u64_vec(self):
+        from . import download
+        return download(self.raw, np.uint64)
+
+    def to_array(self, dtype, out=None):
+        from . import download
+        return download(self.raw, dtype, out=out)
+
+    def free(self):
+        from . import CatenaMem, free
+        if self.raw.data:
+            free(self.raw)
+            self.raw = CatenaMem()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Value:
+    """Tagged runtime value accepted at program boundaries (value.rs:5-11)."""
+
+    __slots__ = ("kind", "v")
+
+    def __init__(self, kind, v):
+        self.kind = kind
+        self.v = v
+
+    @staticmethod
+    def bool(v):
+        return Value(ValueKind.Bool, 1 if v else 0)
+
+    @staticmethod
+    def u32(v):
+        return Value(ValueKind.U32, int(v) & 0xFFFFFFFF)
+
+    @staticmethod
+    def u64(v):
+        return Value(ValueKind.U64, int(v) & 0xFFFFFFFFFFFFFFFF)
+
+    @staticmethod
+    def f32(v):
+        return Value(ValueKind.F32, float(np.float32(v)))
+
+    @staticmethod
+    def mem(m):
+        return Value(ValueKind.Mem, m)
+
+    @staticmethod
+    def of(x):
+        """`.into()` of the Rust API: bool -> Bool, int -> U64, float -> F32, Mem -> Mem."""
+        if isinstance(x, Value):
+            return x
+        if isinstance(x, Mem):
+            return Value.mem(x)
+        if isinstance(x, (bool, np.bool_)):
+            return Value.bool(x)
+        if isinstance(x, np.uint32):
+            return Value.u32(x)
+        if isinstance(x, (int, np.integer)):
+            return Value.u64(x)
+        if isinstance(x, (float, np.floating)):
+            return Value.f32(x)
+        raise TypeError(f"cannot convert {type(x).__name__} into a catena Value")
+
+    def __repr__(self):
+        return f"Value.{self.kind.value}({self.v!r})"
+
+
+K = ValueKind
+# Catalogue: hexpr source name -> (inputs, outputs).  Symbols follow codegen/mod.rs:379-388.
+# The first block is the stdlib (always registered, stdlib.rs:47-66); the second block is programs a
+# user source must define for them to be callable (the reference's test program and the
+# beyond-reference tensor-core / attention programs).
+_SCALAR = ([K.F32], [K.F32])
+STDLIB = {name: _SCALAR for name in [
+    "math.sin-approx", "math.cos-approx", "math.sin-approx-full-nonneg", "math.sin-approx-full",
+    "math.log-approx", "math.exp-approx-nonneg", "math.exp-approx", "math.exp2-approx", "math.log2-approx",
+    "math.sqrt", "nn.sigmoid", "nn.silu", "nn.tanh", "nn.gelu-approx"]}
+STDLIB.update({
+    "math.powf": ([K.F32, K.F32], [K.F32]),
+    "nn.softmax": ([K.Mem], [K.Mem]),
+    "nn.rmsnorm": ([K.Mem], [K.Mem]),
+    "sum-f32": ([K.Mem], [K.F32]),
+    "mean-f32": ([K.Mem], [K.F32]),
+    "max-f32": ([K.Mem], [K.F32]),
+    "tensor.broadcast-f32": ([K.F32, K.U64], [K.Mem]),
+    "tensor.arange-f32": ([K.U64], [K.Mem]),
+    "tensor.slice-f32": ([K.Mem, K.U64, K.U64], [K.Mem]),
+    "tensor.concat-f32": ([K.Mem, K.Mem], [K.Mem]),
+    "tensor.argmax-f32": ([K.Mem], [K.U64]),
+})
+USER_PROGRAMS = {
+    "matmul-2x2-via-mem": ([K.Mem, K.Mem, K.U64, K.U64, K.U64, K.U64, K.U64, K.U64], [K.Mem]),
+    "matmul-right-identity-2x2-via-mem": ([K.Mem, K.U64, K.U64], [K.Mem]),
+    "matmul-left-identity-2x2-via-mem": ([K.Mem, K.U64, K.U64], [K.Mem]),
+    "gemm-bf16-rc": ([K.Mem, K.Mem, K.U64, K.U64, K.U64], [K.Mem]),
+    "gemm-i8-rc": ([K.Mem, K.Mem, K.U64, K.U64, K.U64], [K.Mem]),
+    "attn-decode-bf16": ([K.Mem, K.Mem, K.Mem, K.U64, K.U64, K.U64, K.U64, K.U64], [K.Mem]),
+}
+
+_DEF_RE = re.compile(r"\(\s*def\s+program\s+([^\s:()]+)")
+
+_CTYPE = {K.Bool: C.c_uint8, K.U32: C.c_uint32, K.U64: C.c_uint64, K.F32: C.c_float}
+
+
+class Runtime:
+    def __init__(self, signatures):
+        from . import lib
+        self._lib = lib()
+        self.signatures = signatures
+
+    @classmethod
+    def new(cls, paths, dialect=GpuDialect.Cuda):
+        texts = []
+        for p in paths:
+            with open(p, "r", encoding="utf-8") as fh:
+                texts.append(fh.read())
+        return cls.from_sources(texts, dialect)
+
+    @classmethod
+    def from_sources(cls, sources, dialect=GpuDialect.Cuda):
+        if dialect is not GpuDialect.Cuda:
+            raise InitError("GpuDialect.Hip is not supported: this backend only selects prebuilt sm_100a CUDA kernels")
+        from . import symbol_for
+        table = {name: (symbol_for(name), ins, outs) for name, (ins, outs) in STDLIB.items()}
+        for text in sources:
+            for name in _DEF_RE.findall(text):
+                if name in USER_PROGRAMS:
+                    ins, outs = USER_PROGRAMS[name]
+                    table[name] = (symbol_for(name), ins, outs)
+        return cls(table)
+
+    # -- memory constructors (runtime.rs:166-172; mem_bytes is additive: Mem is untyped bytes) --
+    def mem_f32(self, values):
+        return self.mem_bytes(np.ascontiguousarray(values, dtype=np.float32))
+
+    def mem_u64(self, values):
+        return self.mem_bytes(np.ascontiguousarray(values, dtype=np.uint64))
+
+    def mem_bytes(self, array):
+        from . import upload
+        return Value.mem(Mem(upload(array)))
+
+    def exec(self, name, args, n_outputs=None):
+        """Runs a source-level `program` definition (runtime.rs:175-236) and returns the list of its
+        outputs.  `n_outputs` plays the role of the Rust const generic N."""
+        sig = self.signatures.get(name)
+        if sig is None:
+            raise ExecError("UnknownSourceFunction", f"Unknown source function '{name}'")
+        symbol, ins, outs = sig
+        args = [Value.of(a) for a in args]
+        if len(args) != len(ins):
+            raise ExecError("InputArityMismatch", f"Function '{name}' expected {len(ins)} inputs, got {len(args)}")
+        if n_outputs is not None and n_outputs != len(outs):
+            raise ExecError("OutputArityMismatch", f"Function '{name}' expected {len(outs)} outputs, got {n_outputs}")
+        for index, (value, expected) in enumerate(zip(args, ins)):
+            if value.kind is not expected:
+                raise ExecError("TypeMismatch", f"Argument {index} expected {expected.value}, got {value.kind.value}")
+        from . import CatenaMem
+        cargs = []
+        for value in args:
+            if value.kind is K.Mem:
+                cargs.append(value.v.raw)
+            else:
+                cargs.append(_CTYPE[value.kind](value.v))
+        couts = [CatenaMem() if kind is K.Mem else _CTYPE[kind](0) for kind in outs]
+        fn = getattr(self._lib, symbol)
+        self._lib.catena_b200_clear_status()
+        fn(*cargs, *[C.byref(o) for o in couts])
+        status = self._lib.catena_b200_last_status()
+        # inputs are moved into exec and dropped on return (runtime.rs:175-179)
+        for value in args:
+            if value.kind is K.Mem:
+                value.v.free()
+        if status != 0:
+            from . import status_string
+            raise ExecError("Device", f"program '{name}' failed: {status_string(status)}", status)
+        results = []
+        for kind, o in zip(outs, couts):
+            if kind is K.Mem:
+                results.append(Value.mem(Mem(o)))
+            elif kind is K.F32:
+                results.append(Value.f32(o.value))
+            else:
+                results.append(Value(kind, int(o.value)))
+        return results

@@ -1,0 +1,83 @@
+"""Host-side sharding plans for one 8xB200 box: one process per GPU.
+
+GEMMs shard by output-column blocks (every output element is independent in the reference's
+`materializec`, catena-lang/src/codegen/ops/materializec.rs:36-82) and decode attention by
+(batch, kv-head) units.  The plans are pure functions of the problem and the world size; tile
+shape, k order and KV split count never depend on them, which is what keeps results bitwise
+identical across 1/2/4/8 GPUs.  The only collective is the final gather of the output.
+"""
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class ColumnBlock:
+    rank: int
+    n0: int      # first output column (= first row of column-major B)
+    n1: int      # one past the last
+
+
+def column_blocks(n, world, align=256):
+    """Splits N output columns into `world` contiguous blocks whose boundaries are multiples of the
+    GEMM tile width (so a rank's tiles are exactly tiles of the unsharded problem)."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    tiles = (n + align - 1) // align
+    out = []
+    for r in range(world):
+        t0 = tiles * r // world
+        t1 = tiles * (r + 1) // world
+        out.append(ColumnBlock(r, min(n, t0 * align), min(n, t1 * align)))
+    return out
+
+
+@dataclass(frozen=True)
+class UnitRange:
+    rank: int
+    u0: int
+    u1: int
+
+
+def unit_ranges(units, world):
+    """Contiguous ranges of (batch, kv-head) units per rank."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    return [UnitRange(r, units * r // world, units * (r + 1) // world) for r in range(world)]
+
+
+def gather_columns(local_block, blocks, rows, dist=None, group=None):
+    """All-gathers row-major column blocks [rows, n1-n0] into the full [rows, N] matrix.
+    `local_block` is a torch tensor on this rank's device; returns the assembled tensor on every rank."""
+    import torch
+    if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local_block
+    widths = [b.n1 - b.n0 for b in blocks]
+    wmax = max(widths)
+    pad = torch.zeros((rows, wmax), dtype=local_block.dtype, device=local_block.device)
+    pad[:, : local_block.shape[1]] = local_block
+    parts = [torch.empty_like(pad) for _ in blocks]
+    dist.all_gather(parts, pad, group=group)
+    return torch.cat([p[:, :w] for p, w in zip(parts, widths)], dim=1)
+
+
+def gather_units(local_rows, ranges, row_width, dist=None, group=None):
+    """All-gathers per-unit output rows (attention O) in unit order."""
+    import torch
+    if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local_rows
+    counts = [r.u1 - r.u0 for r in ranges]
+    cmax = max(counts)
+    pad = torch.zeros((cmax, row_width), dtype=local_rows.dtype, device=local_rows.device)
+    pad[: local_rows.shape[0]] = local_rows
+    parts = [torch.empty_like(pad) for _ in ranges]
+    dist.all_gather(parts, pad, group=group)
+    return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
+
+
+def max_over_ranks(ms, dist=None, device="cpu"):
+    """Device-timed milliseconds -> max over ranks (the number every multi-GPU figure is quoted on)."""
+    import torch
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return float(ms)
+    t = torch.tensor([float(ms)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())

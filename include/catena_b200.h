@@ -1,0 +1,202 @@
+/* catena_b200.h — C ABI of libcatena_b200.so
+ *
+ * A prebuilt sm_100a kernel library behind the calling convention that catena-lang's code
+ * generator gives every entry point (catena-lang/src/codegen/gpu.rs:235-261,
+ * catena-lang/src/runtime/executor.rs:65-106):
+ *
+ *     extern "C" void program_<name>(<inputs by value, source order>..., <T>* out...)
+ *
+ * with `bool -> uint8_t`, `u32 -> uint32_t`, `u64 -> uint64_t`, `f32 -> float` and
+ * `mem -> catena_mem_t` passed BY VALUE (catena-lang/src/codegen/lower_types.rs:84-137,
+ * catena-lang/src/codegen/prelude.rs:28-31).  Symbol names follow
+ * catena-lang/src/codegen/mod.rs:379-388 (`program_` + name, non-alphanumerics -> `_`).
+ *
+ * Differences from the generated code, all additive:
+ *   - `catena_mem_t.data` is DEVICE memory from catena_b200_mem_alloc (cudaMalloc behind a
+ *     size-class pool), not cudaMallocManaged (catena-lang/src/runtime/mem.rs:152-171); hosts
+ *     read results with catena_b200_mem_download.  Managed pointers are accepted as inputs.
+ *   - a failed assertion never traps the device (catena-lang/src/codegen/prelude.rs:38-55
+ *     calls __builtin_trap): the `void` entry point records a status readable with
+ *     catena_b200_last_status(), prints one line on stderr and returns `{NULL,0}` / zero
+ *     outputs; every entry point also has a `_s` twin returning the status.
+ *   - there is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     CATENA_E_NO_DEVICE.
+ */
+#ifndef CATENA_B200_H
+#define CATENA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* catena-lang/src/codegen/prelude.rs:28-31, catena-lang/src/runtime/executor.rs:14-19 */
+typedef struct {
+    void* data;   /* device pointer (NULL when len == 0) */
+    uint64_t len; /* BYTES */
+} catena_mem_t;
+
+typedef int32_t catena_status_t;
+enum {
+    CATENA_OK = 0,
+    CATENA_E_ASSERT = 1,      /* a `catena_assert` of the program would have trapped        */
+    CATENA_E_CUDA = 2,        /* a CUDA runtime/driver call failed (`catena_host_gpu_check`) */
+    CATENA_E_NO_DEVICE = 3,   /* no CUDA device / not an sm_100 part                         */
+    CATENA_E_BAD_ARG = 4,     /* null pointer, misaligned buffer, unsupported shape          */
+    CATENA_E_TIMEOUT = 5,     /* a bounded device-side wait gave up                          */
+    CATENA_E_TOO_LARGE = 6,   /* size beyond a stated maximum                                */
+    CATENA_E_UNSUPPORTED = 7  /* e.g. GpuDialect::Hip                                        */
+};
+
+/* ---- runtime: device, stream, status ------------------------------------------------ */
+/* Replaces the implicit "globally set device" of the generated code
+ * (catena-lang/doc/CODEGEN.md:164-166): binds the calling thread's library state to `device`. */
+catena_status_t catena_b200_init(int device);
+int catena_b200_device_count(void);
+/* Entry points launch on this stream (default: the legacy default stream, as the generated
+ * code does).  `stream` is a cudaStream_t. */
+catena_status_t catena_b200_set_stream(void* stream);
+void* catena_b200_get_stream(void);
+/* 1 (default): every entry point synchronises before returning, as the generated code's
+ * cudaDeviceSynchronize does (catena-lang/src/codegen/ops/materializec.rs:138-141).
+ * 0: entry points only enqueue; call catena_b200_sync() before reading results. */
+void catena_b200_set_blocking(int blocking);
+catena_status_t catena_b200_sync(void);
+catena_status_t catena_b200_last_status(void);
+void catena_b200_clear_status(void);
+const char* catena_b200_status_string(catena_status_t s);
+const char* catena_b200_version(void);
+/* number of kernels this library launched since load (all threads) */
+uint64_t catena_b200_launch_count(void);
+
+/* ---- allocator (replaces GpuRuntime::{alloc,free}, catena-lang/src/runtime/mem.rs:152-190) */
+catena_status_t catena_b200_mem_alloc(uint64_t bytes, catena_mem_t* out);
+catena_status_t catena_b200_mem_free(catena_mem_t mem);
+/* Mem::from_slice (catena-lang/src/runtime/mem.rs:72-106): allocate + copy host bytes in */
+catena_status_t catena_b200_mem_upload(const void* host, uint64_t bytes, catena_mem_t* out);
+/* Mem::to_f32_vec / to_u64_vec (catena-lang/src/runtime/mem.rs:43-70): copy bytes out */
+catena_status_t catena_b200_mem_download(catena_mem_t mem, void* host, uint64_t bytes);
+/* copy host bytes into an existing allocation (no reallocation) */
+catena_status_t catena_b200_mem_write(catena_mem_t mem, const void* host, uint64_t bytes);
+/* return pooled blocks to the driver */
+catena_status_t catena_b200_mem_trim(void);
+/* CUDA-IPC export/import so another process (one per GPU) can map an allocation as peer
+ * memory over NVLink.  `handle64` is a 64-byte cudaIpcMemHandle_t; `offset` is the byte
+ * offset of `mem.data` inside the exported allocation.  No counterpart in the reference
+ * (single device, catena-lang/doc/CODEGEN.md:164-166). */
+catena_status_t catena_b200_ipc_export(catena_mem_t mem, void* handle64, uint64_t* offset);
+catena_status_t catena_b200_ipc_import(const void* handle64, uint64_t offset, uint64_t bytes,
+                                       catena_mem_t* out);
+catena_status_t catena_b200_ipc_close(catena_mem_t mem, uint64_t offset);
+
+/* ---- scalar stdlib programs (run on the host, like the reference's non-materialize code)
+ * catena-lang/stdlib/math.hex:3,27,52,91,110,148,185,202,213,224,235; stdlib/nn.hex:2,15,24,38 */
+void program_math_sin_approx(float x, float* out);
+void program_math_cos_approx(float x, float* out);
+void program_math_sin_approx_full_nonneg(float x, float* out);
+void program_math_sin_approx_full(float x, float* out);
+void program_math_log_approx(float x, float* out);
+void program_math_exp_approx_nonneg(float x, float* out);
+void program_math_exp_approx(float x, float* out);
+void program_math_exp2_approx(float x, float* out);
+void program_math_log2_approx(float x, float* out);
+void program_math_powf(float x, float y, float* out);
+void program_math_sqrt(float x, float* out);
+void program_nn_sigmoid(float x, float* out);
+void program_nn_silu(float x, float* out);
+void program_nn_tanh(float x, float* out);
+void program_nn_gelu_approx(float x, float* out);
+
+/* ---- buffer programs ------------------------------------------------------------------ */
+/* catena-lang/stdlib/nn.hex:93-122 and :154-182 */
+void program_nn_softmax(catena_mem_t in, catena_mem_t* out);
+void program_nn_rmsnorm(catena_mem_t in, catena_mem_t* out);
+catena_status_t program_nn_softmax_s(catena_mem_t in, catena_mem_t* out);
+catena_status_t program_nn_rmsnorm_s(catena_mem_t in, catena_mem_t* out);
+/* catena-lang/stdlib/sum.hex:29-44, :47-67, :86-101 */
+void program_sum_f32(catena_mem_t in, float* out);
+void program_mean_f32(catena_mem_t in, float* out);
+void program_max_f32(catena_mem_t in, float* out);
+catena_status_t program_sum_f32_s(catena_mem_t in, float* out);
+catena_status_t program_mean_f32_s(catena_mem_t in, float* out);
+catena_status_t program_max_f32_s(catena_mem_t in, float* out);
+/* catena-lang/stdlib/tensor.hex:10-21, :35-46, :70-82, :141-168, :204-227 */
+void program_tensor_broadcast_f32(float v, uint64_t n, catena_mem_t* out);
+void program_tensor_arange_f32(uint64_t n, catena_mem_t* out);
+void program_tensor_slice_f32(catena_mem_t in, uint64_t start, uint64_t len, catena_mem_t* out);
+void program_tensor_concat_f32(catena_mem_t l, catena_mem_t r, catena_mem_t* out);
+void program_tensor_argmax_f32(catena_mem_t in, uint64_t* out);
+catena_status_t program_tensor_broadcast_f32_s(float v, uint64_t n, catena_mem_t* out);
+catena_status_t program_tensor_arange_f32_s(uint64_t n, catena_mem_t* out);
+catena_status_t program_tensor_slice_f32_s(catena_mem_t in, uint64_t start, uint64_t len,
+                                           catena_mem_t* out);
+catena_status_t program_tensor_concat_f32_s(catena_mem_t l, catena_mem_t r, catena_mem_t* out);
+catena_status_t program_tensor_argmax_f32_s(catena_mem_t in, uint64_t* out);
+/* catena-lang/tests/cases/matrix/matmul.hex:2-63 (entry program of the f32 matmul chain,
+ * catena-lang/stdlib/matrix.hex:210-327): row-major f32, bit-exact ascending-k left fold with
+ * separately rounded mul/add.  Asserts a.len/4 == nk and b.len/4 == km. */
+void program_matmul_2x2_via_mem(catena_mem_t a, catena_mem_t b, uint64_t n, uint64_t m, uint64_t k,
+                                uint64_t nk, uint64_t km, uint64_t nm, catena_mem_t* out);
+catena_status_t program_matmul_2x2_via_mem_s(catena_mem_t a, catena_mem_t b, uint64_t n, uint64_t m,
+                                             uint64_t k, uint64_t nk, uint64_t km, uint64_t nm,
+                                             catena_mem_t* out);
+/* catena-lang/tests/cases/matrix/matmul.hex:66-149 (identity views, stdlib/matrix.hex:129-159) */
+void program_matmul_right_identity_2x2_via_mem(catena_mem_t a, uint64_t n, uint64_t nn, catena_mem_t* out);
+void program_matmul_left_identity_2x2_via_mem(catena_mem_t a, uint64_t n, uint64_t nn, catena_mem_t* out);
+
+/* elementwise application of a scalar stdlib program over an f32 buffer: the map kernel a
+ * `materializec` with that producer lowers to (catena-lang/src/codegen/ops/materializec.rs:36-145).
+ * `op` is the hexpr name, e.g. "nn.silu", "math.exp-approx". */
+catena_status_t catena_b200_map_f32_s(const char* op, catena_mem_t in, catena_mem_t* out);
+
+/* ---- programs with no counterpart in the reference (it has no bf16, int8 or attention);
+ *      same calling convention; semantics composed from the reference's rules -------------- */
+/* C[M,N] = A[M,K] * B, A row-major bf16, B column-major bf16 (stored [N,K]); fp32 accumulation in
+ * ascending k (tcgen05 tiles, fixed order, no split-K), bf16 round-to-nearest-even output. */
+void program_gemm_bf16_rc(catena_mem_t a, catena_mem_t b_colmajor, uint64_t m, uint64_t n, uint64_t k,
+                          catena_mem_t* c);
+catena_status_t program_gemm_bf16_rc_s(catena_mem_t a, catena_mem_t b_colmajor, uint64_t m, uint64_t n,
+                                       uint64_t k, catena_mem_t* c);
+/* int8 x int8 -> int32, same layouts, exact. */
+void program_gemm_i8_rc(catena_mem_t a, catena_mem_t b_colmajor, uint64_t m, uint64_t n, uint64_t k,
+                        catena_mem_t* c_i32);
+catena_status_t program_gemm_i8_rc_s(catena_mem_t a, catena_mem_t b_colmajor, uint64_t m, uint64_t n,
+                                     uint64_t k, catena_mem_t* c_i32);
+/* Cached-attention decode, one new token: q [B,Hq,D] bf16, k/v cache [B,Hkv,L,D] bf16,
+ * o [B,Hq,D] bf16; scale = 1/sqrt(D); softmax per catena-lang/stdlib/nn.hex:93-122 (global max,
+ * math.exp-approx, fp32).  D must be 128; Hq a multiple of Hkv with Hq/Hkv <= 8. */
+void program_attn_decode_bf16(catena_mem_t q, catena_mem_t k_cache, catena_mem_t v_cache, uint64_t batch,
+                              uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, catena_mem_t* o);
+catena_status_t program_attn_decode_bf16_s(catena_mem_t q, catena_mem_t k_cache, catena_mem_t v_cache,
+                                           uint64_t batch, uint64_t hq, uint64_t hkv, uint64_t d,
+                                           uint64_t kv_len, catena_mem_t* o);
+
+/* ---- launch-level API: caller-owned outputs, used for sharded (multi-GPU) execution ------ */
+/* Same kernels as the programs above writing into caller memory; `ldc` is the row pitch of C in
+ * elements so a rank can write its column block straight into a full-width matrix. */
+catena_status_t catena_b200_gemm_bf16_into(const void* a, const void* b_colmajor, void* c, uint64_t m,
+                                           uint64_t n, uint64_t k, uint64_t ldc);
+catena_status_t catena_b200_gemm_i8_into(const void* a, const void* b_colmajor, void* c_i32, uint64_t m,
+                                         uint64_t n, uint64_t k, uint64_t ldc);
+catena_status_t catena_b200_matmul_f32_into(const void* a, const void* b, void* c, uint64_t n, uint64_t m,
+                                            uint64_t k);
+/* units [unit0, unit1) of the B*Hkv (batch, kv-head) pairs only; q/o are indexed by absolute
+ * position, so disjoint unit ranges can be run by different launches (or GPUs) into one output. */
+catena_status_t catena_b200_attn_decode_bf16_into(const void* q, const void* k_cache, const void* v_cache,
+                                                  void* o, uint64_t batch, uint64_t hq, uint64_t hkv,
+                                                  uint64_t d, uint64_t kv_len, uint64_t unit0, uint64_t unit1);
+/* elementwise / fold kernels into caller memory (device pointers; `n` in elements) */
+catena_status_t catena_b200_map_f32_into(const char* op, const void* in, void* out, uint64_t n);
+catena_status_t catena_b200_softmax_f32_into(const void* in, void* out, uint64_t n);
+catena_status_t catena_b200_rmsnorm_f32_into(const void* in, void* out, uint64_t n);
+/* test hook: cap the persistent grid of the tensor-core GEMM (0 = one CTA per SM); results must not
+ * change with it.  No counterpart in the reference. */
+void catena_b200_debug_set_cta_limit(int limit);
+/* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry */
+catena_status_t catena_b200_check_device_errors(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CATENA_B200_H */

@@ -1,0 +1,358 @@
+"""Parity tests proper: the CUDA path, called through the C ABI (`program_*` symbols via the
+reference-shaped Runtime mirror), against the CPU oracle on the same seeded inputs.
+
+Bar: bit-exact for integer / index results, for every elementwise program, for the f32 matmul
+(any shape) and for folds of up to 65536 elements; stated tolerances elsewhere (written next to
+each assert).  Vectors marked with a file:line come from the reference's own tests."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+import catena_lang_b200 as cb
+
+pytestmark = pytest.mark.gpu
+
+MATMUL_SRC = """
+(def program matmul-2x2-via-mem : x -> y = ())
+(def program matmul-right-identity-2x2-via-mem : x -> y = ())
+(def program matmul-left-identity-2x2-via-mem : x -> y = ())
+(def program gemm-bf16-rc : x -> y = ())
+(def program gemm-i8-rc : x -> y = ())
+(def program attn-decode-bf16 : x -> y = ())
+"""
+
+
+@pytest.fixture(scope="module")
+def rt():
+    assert cb.lib().catena_b200_device_count() > 0, "GPU tests need a CUDA device"
+    cb.check(cb.lib().catena_b200_init(0))
+    return cb.Runtime.from_sources([MATMUL_SRC], cb.GpuDialect.Cuda)
+
+
+def u32(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def matmul(rt, a, b, n, m, k):
+    [r] = rt.exec("matmul-2x2-via-mem", [rt.mem_f32(a), rt.mem_f32(b), n, m, k, n * k, k * m, n * m])
+    return r.v.to_f32_vec()
+
+
+# ---------------------------------------------------------------- f32 matmul (bit-exact)
+def test_matmul_reference_vectors(rt):
+    # tests/cases/matrix.rs:6-82
+    out = matmul(rt, [1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12], 2, 2, 3)
+    assert out.tolist() == [58.0, 64.0, 139.0, 154.0]
+    a = [1.0, 2.0, 3.0, 4.0]
+    [r] = rt.exec("matmul-right-identity-2x2-via-mem", [rt.mem_f32(a), 2, 4])
+    assert r.v.to_f32_vec().tolist() == a
+    [r] = rt.exec("matmul-left-identity-2x2-via-mem", [rt.mem_f32(a), 2, 4])
+    assert r.v.to_f32_vec().tolist() == a
+
+
+@pytest.mark.parametrize("n,m,k", [(256, 256, 256), (1, 1, 1), (37, 53, 29), (130, 70, 257), (64, 64, 1),
+                                   (640, 1280, 96), (1000, 900, 515)])
+def test_matmul_bit_exact(rt, orc, n, m, k):
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, m)).astype(np.float32)
+    got = matmul(rt, a, b, n, m, k)
+    want = orc.matmul_f32(a, b, n, m, k, threads=orc.max_threads())
+    assert np.array_equal(u32(got), u32(want))
+
+
+def test_matmul_signed_zero_and_specials(rt, orc):
+    a = np.array([[-0.0, 0.0, -1.0], [np.inf, 1.0, -0.0]], np.float32)
+    b = np.array([[0.0, 1.0], [-0.0, 2.0], [0.0, -3.0]], np.float32)
+    got = matmul(rt, a, b, 2, 2, 3)
+    want = orc.matmul_f32(a, b, 2, 2, 3)
+    assert np.array_equal(u32(got), u32(want))
+
+
+def test_matmul_length_assert_is_a_status_not_a_trap(rt):
+    with pytest.raises(cb.ExecError) as e:
+        rt.exec("matmul-2x2-via-mem", [rt.mem_f32([1, 2, 3]), rt.mem_f32([1, 2, 3, 4]), 2, 2, 2, 4, 4, 4])
+    assert e.value.status == cb.E_ASSERT
+    # the context is still usable
+    assert matmul(rt, [2.0], [3.0], 1, 1, 1).tolist() == [6.0]
+
+
+# ---------------------------------------------------------------- elementwise programs (bit-exact)
+@pytest.mark.parametrize("name", cb.SCALAR_PROGRAMS)
+def test_map_bit_exact(rt, orc, name):
+    rng = np.random.default_rng(3)
+    x = np.concatenate([rng.uniform(-30, 30, 1 << 20), rng.normal(0, 1, 1 << 18),
+                        [0.0, -0.0, 1.0, -1.0, 80.0, -80.0, 1e-30, 3.5]]).astype(np.float32)
+    if name in ("math.log-approx", "math.log2-approx", "math.sin-approx-full-nonneg", "math.exp-approx-nonneg"):
+        x = np.abs(x) + np.float32(1e-6)
+    x = x[: x.size - 3]  # odd length: exercises the scalar tail
+    m = cb.upload(x)
+    out = cb.CatenaMem()
+    cb.check(cb.lib().catena_b200_map_f32_s(name.encode(), m, C.byref(out)))
+    got = cb.download(out, np.float32)
+    cb.free(m), cb.free(out)
+    want = orc.map_unary(name, x, threads=orc.max_threads())
+    assert np.array_equal(u32(got), u32(want))
+
+
+# ---------------------------------------------------------------- folds
+def test_fold_reference_vectors(rt):
+    # tests/cases/reducec.rs:50-90
+    x = [1.5, -0.5, 2.0, 4.0]
+    assert rt.exec("sum-f32", [rt.mem_f32(x)])[0].v == 7.0
+    assert rt.exec("mean-f32", [rt.mem_f32(x)])[0].v == 1.75
+    assert rt.exec("max-f32", [rt.mem_f32(x)])[0].v == 4.0
+    assert u32(rt.exec("sum-f32", [rt.mem_f32([])])[0].v) == 0
+    assert u32(rt.exec("max-f32", [rt.mem_f32([])])[0].v) == 0xFF800000
+
+
+@pytest.mark.parametrize("n", [1, 7, 2048, 2049, 65536])
+def test_fold_bit_exact_up_to_65536(rt, orc, n):
+    x = np.random.default_rng(n).normal(0, 3, n).astype(np.float32)
+    assert u32(rt.exec("sum-f32", [rt.mem_f32(x)])[0].v) == u32(orc.sum_f32(x))
+    assert u32(rt.exec("mean-f32", [rt.mem_f32(x)])[0].v) == u32(orc.mean_f32(x))
+    assert u32(rt.exec("max-f32", [rt.mem_f32(x)])[0].v) == u32(orc.max_f32(x))
+
+
+@pytest.mark.parametrize("n", [65537, 1 << 20, (1 << 22) + 12345])
+def test_fold_tree_tolerance_and_determinism(rt, orc, n):
+    x = np.random.default_rng(n).normal(0, 3, n).astype(np.float32)
+    s1 = rt.exec("sum-f32", [rt.mem_f32(x)])[0].v
+    s2 = rt.exec("sum-f32", [rt.mem_f32(x)])[0].v
+    assert u32(s1) == u32(s2)                                  # bitwise identical across runs
+    exact = float(np.sum(x.astype(np.float64)))
+    bound = 4e-7 * float(np.sum(np.abs(x.astype(np.float64))))   # ~ log2(n) * eps * sum|x|, far below the
+    assert abs(s1 - exact) <= bound                             # sequential fold's own n * eps * sum|x|
+    assert abs(s1 - float(orc.sum_f32(x))) <= 64 * bound
+    assert u32(rt.exec("max-f32", [rt.mem_f32(x)])[0].v) == u32(orc.max_f32(x))   # order-free: exact
+
+
+def test_argmax(rt, orc):
+    # tests/runtime.rs:1170-1197 (ties keep the first index)
+    for xs, want in [([5.0], 0), ([1, 2, 4], 2), ([4, 2, 1], 0), ([1, 7, 3, 2], 1), ([1, 7, 7, 2], 1), ([3, 3, 3], 0)]:
+        assert rt.exec("tensor.argmax-f32", [rt.mem_f32(xs)])[0].v == want
+    rng = np.random.default_rng(5)
+    for n in [4097, 65536, 65537, 3_000_001]:
+        x = rng.integers(0, 1000, n).astype(np.float32)        # many exact ties
+        assert rt.exec("tensor.argmax-f32", [rt.mem_f32(x)])[0].v == orc.argmax_f32(x)
+    with pytest.raises(cb.ExecError) as e:
+        rt.exec("tensor.argmax-f32", [rt.mem_f32([])])
+    assert e.value.status == cb.E_ASSERT
+
+
+# ---------------------------------------------------------------- softmax / rmsnorm
+def test_softmax_rmsnorm_reference_vectors(rt):
+    # tests/runtime.rs:971-1044
+    x = np.array([1.0, 2.0, 4.0], np.float32)
+    y = rt.exec("nn.softmax", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    want = np.exp(x - x.max()) / np.exp(x - x.max()).sum()
+    assert np.all(np.abs(y - want) < 6e-3) and abs(y.sum() - 1) < 6e-3
+    x = np.array([1.0, 2.0, 4.0, -1.0, -9.0, 13.29], np.float32)
+    y = rt.exec("nn.rmsnorm", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    rms = math.sqrt(float((x.astype(np.float64) ** 2).mean()) + 1e-5)
+    assert np.all(np.abs(y - x / rms) < 3e-3)
+
+
+@pytest.mark.parametrize("n", [1, 3, 128, 4096, 5000, 65536])
+def test_softmax_rmsnorm_bit_exact_up_to_65536(rt, orc, n):
+    x = np.random.default_rng(n).normal(0, 2, n).astype(np.float32)
+    y = rt.exec("nn.softmax", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    assert np.array_equal(u32(y), u32(orc.softmax(x)))
+    y = rt.exec("nn.rmsnorm", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    assert np.array_equal(u32(y), u32(orc.rmsnorm(x)))
+
+
+def test_softmax_rmsnorm_long_rows(rt, orc):
+    n = (1 << 21) + 77
+    x = np.random.default_rng(1).normal(0, 2, n).astype(np.float32)
+    y = rt.exec("nn.softmax", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    want = orc.softmax(x, threads=orc.max_threads())
+    # the only difference is the rounding of the tree-summed denominator: relative 1e-6
+    assert np.all(np.abs(y - want) <= 2e-6 * want + 1e-30)
+    y2 = rt.exec("nn.softmax", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    assert np.array_equal(u32(y), u32(y2))
+    y = rt.exec("nn.rmsnorm", [rt.mem_f32(x)])[0].v.to_f32_vec()
+    want = orc.rmsnorm(x, threads=orc.max_threads())
+    assert np.all(np.abs(y - want) <= 2e-6 * np.abs(want))
+
+
+# ---------------------------------------------------------------- tensor programs (exact)
+def test_tensor_programs(rt):
+    # tests/runtime.rs:1046-1168
+    assert rt.exec("tensor.broadcast-f32", [3.5, 0])[0].v.to_f32_vec().tolist() == []
+    assert rt.exec("tensor.broadcast-f32", [3.5, 4])[0].v.to_f32_vec().tolist() == [3.5] * 4
+    assert rt.exec("tensor.arange-f32", [0])[0].v.to_f32_vec().tolist() == []
+    assert rt.exec("tensor.arange-f32", [5])[0].v.to_f32_vec().tolist() == [0, 1, 2, 3, 4]
+    src = [10.0, 20.0, 30.0, 40.0]
+    for start, ln, want in [(0, 2, [10, 20]), (1, 2, [20, 30]), (2, 0, []), (0, 4, src)]:
+        assert rt.exec("tensor.slice-f32", [rt.mem_f32(src), start, ln])[0].v.to_f32_vec().tolist() == want
+    with pytest.raises(cb.ExecError) as e:
+        rt.exec("tensor.slice-f32", [rt.mem_f32(src), 3, 2])
+    assert e.value.status == cb.E_ASSERT
+    for l, r in [([1, 2], [3, 4]), ([1], [2, 3, 4]), ([], [3, 4]), ([1, 2], []), ([], [])]:
+        got = rt.exec("tensor.concat-f32", [rt.mem_f32(l), rt.mem_f32(r)])[0].v.to_f32_vec().tolist()
+        assert got == [float(v) for v in l + r]
+
+
+def test_tensor_programs_large(rt):
+    n = 3_000_003
+    got = rt.exec("tensor.arange-f32", [n])[0].v.to_f32_vec()
+    assert np.array_equal(got, np.arange(n, dtype=np.uint64).astype(np.float32))
+    x = np.random.default_rng(2).normal(size=n).astype(np.float32)
+    got = rt.exec("tensor.slice-f32", [rt.mem_f32(x), 1001, n - 2002])[0].v.to_f32_vec()
+    assert np.array_equal(u32(got), u32(x[1001:n - 1001]))
+    got = rt.exec("tensor.concat-f32", [rt.mem_f32(x[:12345]), rt.mem_f32(x[12345:])])[0].v.to_f32_vec()
+    assert np.array_equal(u32(got), u32(x))
+
+
+# ---------------------------------------------------------------- tensor-core GEMMs
+def bf16_inputs(seed, m, n, k):
+    import oracle
+    rng = np.random.default_rng(seed)
+    a = oracle.f32_to_bf16_bits((rng.standard_normal((m, k)) / math.sqrt(k)).astype(np.float32))
+    bt = oracle.f32_to_bf16_bits((rng.standard_normal((n, k)) / math.sqrt(k)).astype(np.float32))
+    return a, bt
+
+
+def bf16_ulp_diff(got_bits, want_bits):
+    """distance in bf16 units of last place between two bf16 bit arrays (monotone integer mapping)"""
+    def key(b):
+        b = b.astype(np.int32)
+        return np.where(b & 0x8000, 0x8000 - b, b)
+    return np.abs(key(got_bits) - key(want_bits))
+
+
+def run_gemm_bf16(rt, a, bt, m, n, k):
+    [r] = rt.exec("gemm-bf16-rc", [rt.mem_bytes(a), rt.mem_bytes(bt), m, n, k])
+    return r.v.to_array(np.uint16).reshape(m, n)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 128), (200, 264, 72), (1, 8, 8),
+                                   (1024, 1024, 1024), (333, 1000, 200)])
+def test_gemm_bf16_vs_oracle(rt, orc, m, n, k):
+    a, bt = bf16_inputs(1, m, n, k)
+    got = run_gemm_bf16(rt, a, bt, m, n, k)
+    want = orc.gemm_bf16_rows(a, bt, n, k, 0, m, threads=orc.max_threads())
+    d = bf16_ulp_diff(got, want)
+    # fp32 accumulation in tensor-core order vs the sequential fp32 fold: the two fp32 sums differ by
+    # rounding only, so after rounding to bf16 they agree except where the sum sits on a rounding
+    # boundary: at most 1 bf16 ulp, on well under 1 % of the outputs
+    assert d.max() <= 1
+    assert (d != 0).mean() < 0.01
+
+
+def test_gemm_bf16_4096_rows_determinism_and_grid_independence(rt, orc):
+    m = n = k = 4096
+    a, bt = bf16_inputs(1, m, n, k)
+    got = run_gemm_bf16(rt, a, bt, m, n, k)
+    again = run_gemm_bf16(rt, a, bt, m, n, k)
+    assert np.array_equal(got, again)                         # bitwise identical across runs
+    cb.lib().catena_b200_debug_set_cta_limit(37)
+    try:
+        small_grid = run_gemm_bf16(rt, a, bt, m, n, k)
+    finally:
+        cb.lib().catena_b200_debug_set_cta_limit(0)
+    assert np.array_equal(got, small_grid)                    # the grid size never enters the arithmetic
+    for row0 in (0, 2048 + 64, 4096 - 32):                    # oracle slabs (the full product takes minutes on a CPU)
+        want = orc.gemm_bf16_rows(a, bt, n, k, row0, row0 + 32, threads=orc.max_threads())
+        d = bf16_ulp_diff(got[row0:row0 + 32], want)
+        assert d.max() <= 1 and (d != 0).mean() < 0.01
+    # column-block partitioning (how the GEMM shards across GPUs) gives the same bits
+    am, btm = cb.upload(a), cb.upload(bt)
+    cm = cb.CatenaMem()
+    cb.check(cb.lib().catena_b200_mem_alloc(m * n * 2, C.byref(cm)))
+    parts = 4
+    for p in range(parts):
+        n0 = p * (n // parts)
+        cb.check(cb.lib().catena_b200_gemm_bf16_into(am.data, btm.data + n0 * k * 2, cm.data + n0 * 2, m, n // parts, k, n))
+    sharded = cb.download(cm, np.uint16).reshape(m, n)
+    for x in (am, btm, cm):
+        cb.free(x)
+    assert np.array_equal(got, sharded)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 256), (200, 264, 80), (1, 4, 16), (1024, 1024, 2048),
+                                   (333, 1000, 208)])
+def test_gemm_i8_bit_exact(rt, orc, m, n, k):
+    rng = np.random.default_rng(4)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    bt = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    [r] = rt.exec("gemm-i8-rc", [rt.mem_bytes(a), rt.mem_bytes(bt), m, n, k])
+    got = r.v.to_array(np.int32).reshape(m, n)
+    want = orc.gemm_i8_rows(a, bt, n, k, 0, m, threads=orc.max_threads())
+    assert np.array_equal(got, want)
+
+
+def test_gemm_i8_extremes(rt):
+    m, n, k = 128, 256, 8192
+    a = np.full((m, k), -128, np.int8)
+    bt = np.full((n, k), -128, np.int8)
+    [r] = rt.exec("gemm-i8-rc", [rt.mem_bytes(a), rt.mem_bytes(bt), m, n, k])
+    assert np.all(r.v.to_array(np.int32) == 128 * 128 * k)   # 134 217 728 < 2^31
+
+
+def test_gemm_rejects_bad_shapes(rt):
+    a, bt = bf16_inputs(1, 16, 16, 12)
+    with pytest.raises(cb.ExecError) as e:
+        rt.exec("gemm-bf16-rc", [rt.mem_bytes(a), rt.mem_bytes(bt), 16, 16, 12])    # K*2 not a multiple of 16 B
+    assert e.value.status == cb.E_BAD_ARG
+
+
+# ---------------------------------------------------------------- cached-attention decode
+def attn_inputs(B, Hq, Hkv, L, D=128, seeds=(2, 3, 4)):
+    import oracle
+    q = oracle.f32_to_bf16_bits(np.random.default_rng(seeds[0]).standard_normal((B, Hq, D)).astype(np.float32))
+    k = oracle.f32_to_bf16_bits(np.random.default_rng(seeds[1]).standard_normal((B, Hkv, L, D)).astype(np.float32))
+    v = oracle.f32_to_bf16_bits(np.random.default_rng(seeds[2]).standard_normal((B, Hkv, L, D)).astype(np.float32))
+    return q, k, v
+
+
+def run_attn(rt, q, k, v, B, Hq, Hkv, L, D=128):
+    [r] = rt.exec("attn-decode-bf16", [rt.mem_bytes(q), rt.mem_bytes(k), rt.mem_bytes(v), B, Hq, Hkv, D, L])
+    return r.v.to_array(np.uint16).reshape(B, Hq, D)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,L", [(2, 8, 2, 256), (1, 4, 1, 64), (3, 8, 8, 333), (2, 16, 2, 77), (1, 2, 1, 1),
+                                        (2, 8, 4, 1000), (1, 32, 8, 4096)])
+def test_attn_decode_vs_oracle(rt, orc, B, Hq, Hkv, L):
+    q, k, v = attn_inputs(B, Hq, Hkv, L)
+    got = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    want = orc.attn_decode_bf16(q, k, v, B, Hq, Hkv, 128, L, np.float32(1.0 / math.sqrt(128.0)), threads=orc.max_threads())
+    d = bf16_ulp_diff(got, want)
+    # same probabilities (global max, the reference's exp polynomial); only fp32 summation order
+    # differs from the sequential folds, so the bf16 outputs agree to 1 ulp, nearly always exactly
+    assert d.max() <= 1
+    assert (d != 0).mean() < 0.02
+
+
+def test_attn_decode_c3_partition_and_determinism(rt, orc):
+    B, Hq, Hkv, L = 32, 32, 8, 4096
+    q, k, v = attn_inputs(B, Hq, Hkv, L)
+    got = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    again = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    assert np.array_equal(got, again)
+    units = list(range(0, B * Hq, 97))[:12]                   # oracle on a sample of (batch, head) rows
+    for u in units:
+        want = orc.attn_decode_bf16(q, k, v, B, Hq, Hkv, 128, L, np.float32(1.0 / math.sqrt(128.0)), unit0=u, unit1=u + 1)
+        d = bf16_ulp_diff(got.reshape(-1, 128)[u], want.reshape(-1, 128)[u])
+        assert d.max() <= 1
+    # sharding by (batch, kv-head) ranges, as across GPUs, gives the same bits
+    qm, km, vm = cb.upload(q), cb.upload(k), cb.upload(v)
+    om = cb.CatenaMem()
+    cb.check(cb.lib().catena_b200_mem_alloc(B * Hq * 128 * 2, C.byref(om)))
+    total = B * Hkv
+    for lo, hi in [(0, 100), (100, 101), (101, total)]:
+        cb.check(cb.lib().catena_b200_attn_decode_bf16_into(qm.data, km.data, vm.data, om.data, B, Hq, Hkv, 128, L, lo, hi))
+    sharded = cb.download(om, np.uint16).reshape(B, Hq, 128)
+    for x in (qm, km, vm, om):
+        cb.free(x)
+    assert np.array_equal(got, sharded)
+
+
+def test_attn_rejects_unsupported(rt):
+    q, k, v = attn_inputs(1, 4, 1, 16)
+    with pytest.raises(cb.ExecError) as e:
+        rt.exec("attn-decode-bf16", [rt.mem_bytes(q), rt.mem_bytes(k), rt.mem_bytes(v), 1, 4, 1, 64, 32])
+    assert e.value.status in (cb.E_UNSUPPORTED, cb.E_ASSERT)
