@@ -117,7 +117,7 @@ def run_reference(args, rank):
     oracle.build()
     threads = oracle.max_threads()
     a, bt = gemm_operands(1)
-    rows = 32
+    rows = 256
     def step():
         t0 = time.perf_counter()
         oracle.gemm_bf16_rows(a, bt, GEMM_N, GEMM_K, 0, rows, threads=threads)
@@ -259,6 +259,12 @@ def run_gpu(args, rank, world, local_rank):
         t0 = time.perf_counter()
         want = oracle.gemm_bf16_rows(a_np, bt_np, GEMM_N, GEMM_K, 0, rows, threads=threads)
         sec = time.perf_counter() - t0
+        more = min(GEMM_M, int(rows * 12.0 / max(sec, 1e-3)) // 64 * 64)   # about 12 s of CPU work
+        if more > 2 * rows:
+            rows = more
+            t0 = time.perf_counter()
+            want = oracle.gemm_bf16_rows(a_np, bt_np, GEMM_N, GEMM_K, 0, rows, threads=threads)
+            sec = time.perf_counter() - t0
         got = c_host.reshape(GEMM_M, GEMM_N)[:rows]
         agree = float((got == want).mean())
         cpu_baseline = {"value": 2.0 * rows * GEMM_N * GEMM_K / sec / 1e12, "unit": "TFLOP/s", "cores": threads,
@@ -296,10 +302,112 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_single(args):
+    """`--only <kernel>`: a few launches of one kernel on the bench workload (or a smaller case with
+    `--small`), for profiler captures and quick timing.  Prints a short JSON line."""
+    import torch
+    import catena_lang_b200 as cb
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = cb.lib()
+    cb.check(L.catena_b200_init(0))
+    stream = torch.cuda.Stream(device=dev)
+    L.catena_b200_set_stream(C.c_void_p(stream.cuda_stream))
+    L.catena_b200_set_blocking(0)
+    which = args.only
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    if which in ("gemm", "gemm_i8"):
+        m = n = k = 2048 if args.small else 4096
+        if args.shape:
+            m, n, k = [int(v) for v in args.shape.split("x")]
+        eb = 1 if which == "gemm_i8" else 2
+        sets = []
+        for _ in range(4):
+            if eb == 1:
+                a = torch.randint(-128, 128, (m, k), generator=g, device=dev, dtype=torch.int8)
+                b = torch.randint(-128, 128, (n, k), generator=g, device=dev, dtype=torch.int8)
+                c = torch.empty((m, n), dtype=torch.int32, device=dev)
+            else:
+                a = (torch.randn((m, k), generator=g, device=dev) / math.sqrt(k)).to(torch.bfloat16)
+                b = (torch.randn((n, k), generator=g, device=dev) / math.sqrt(k)).to(torch.bfloat16)
+                c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            sets.append((a, b, c))
+        fn = L.catena_b200_gemm_i8_into if eb == 1 else L.catena_b200_gemm_bf16_into
+
+        def step(i):
+            a, b, c = sets[i % 4]
+            cb.check(fn(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, n))
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+        desc = f"{which} {m}x{n}x{k}"
+    elif which == "attn":
+        B, Hq, Hkv, D, Lk = (8, 32, 8, 128, 4096) if args.small else (32, 32, 8, 128, 4096)
+        sets = []
+        for _ in range(2):
+            q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
+            kk = torch.randn((B, Hkv, Lk, D), generator=g, device=dev).to(torch.bfloat16)
+            vv = torch.randn((B, Hkv, Lk, D), generator=g, device=dev).to(torch.bfloat16)
+            o = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=dev)
+            sets.append((q, kk, vv, o))
+
+        def step(i):
+            q, kk, vv, o = sets[i % 2]
+            cb.check(L.catena_b200_attn_decode_bf16_into(q.data_ptr(), kk.data_ptr(), vv.data_ptr(), o.data_ptr(), B, Hq,
+                                                         Hkv, D, Lk, 0, B * Hkv))
+        work, unit = (2 * B * Hkv * Lk * D * 2 + 2 * B * Hq * D * 2) / 1e9, "GB/s"
+        desc = f"attn decode B={B} Hq={Hq} Hkv={Hkv} D={D} L={Lk}"
+    elif which == "matmul_f32":
+        n = 256 if args.small else 4096
+        a = torch.rand((n, n), generator=g, device=dev) * 2 - 1
+        b = torch.rand((n, n), generator=g, device=dev) * 2 - 1
+        c = torch.empty((n, n), device=dev)
+
+        def step(i):
+            cb.check(L.catena_b200_matmul_f32_into(a.data_ptr(), b.data_ptr(), c.data_ptr(), n, n, n))
+        work, unit = 2.0 * n ** 3 / 1e12, "TFLOP/s"
+        desc = f"f32 matmul {n}^3 (bit-exact sequential-k)"
+    else:  # map / softmax / rmsnorm over 64 Mi f32 (256 MiB in, 256 MiB out)
+        n = (1 << 24) if args.small else (1 << 26)
+        x = torch.randn((2, n), generator=g, device=dev)
+        y = torch.empty((2, n), device=dev)
+
+        def step(i):
+            s = i % 2
+            if which == "softmax":
+                cb.check(L.catena_b200_softmax_f32_into(x[s].data_ptr(), y[s].data_ptr(), n))
+            elif which == "rmsnorm":
+                cb.check(L.catena_b200_rmsnorm_f32_into(x[s].data_ptr(), y[s].data_ptr(), n))
+            else:
+                cb.check(L.catena_b200_map_f32_into(b"nn.silu", x[s].data_ptr(), y[s].data_ptr(), n))
+        passes = {"softmax": 4, "rmsnorm": 3}.get(which, 2)     # algorithmic reads + writes of the buffer
+        work, unit = passes * n * 4 / 1e9, "GB/s"
+        desc = f"{which} over {n} f32"
+    torch.cuda.synchronize(dev)
+    with torch.cuda.stream(stream):
+        for i in range(args.warmup):
+            step(i)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+    cb.check(L.catena_b200_check_device_errors())
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"only": which, "case": desc, "ms_per_step": ms, "value": work / (ms * 1e-3), "unit": unit,
+                      "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None,
+                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm"])
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -309,6 +417,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.only:
+        run_single(args)
         return
     run_gpu(args, rank, world, local_rank)
 
