@@ -113,6 +113,7 @@ def lib():
     proto("catena_b200_rmsnorm_f32_into", st, [vp, vp, u64])
     proto("catena_b200_check_device_errors", st, [])
     proto("catena_b200_debug_set_cta_limit", None, [C.c_int])
+    proto("catena_b200_sum_f32_noalloc", st, [vp, u64, vp])
     _lib = L
     return L
 

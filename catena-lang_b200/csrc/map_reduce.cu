@@ -515,4 +515,68 @@ catena_status_t launch_concat(const float* l, uint64_t nl, const float* r, uint6
     return CATENA_OK;
 }
 
+// ---- sum without any allocation ------------------------------------------------------------------
+// Block partials of the tree sum live in this fixed array instead of a pool block.  It is part of the
+// module image, so every GPU that loads the library carries these 256 KiB until the process exits.
+// kNoAllocMaxPartials level-0 partials cover kNoAllocMaxElems = 2^30 elements; the few extra slots
+// hold the partials of the upper tree levels.
+static constexpr uint64_t kNoAllocMaxPartials = 65536;
+static constexpr uint64_t kNoAllocMaxElems = kNoAllocMaxPartials * kChunk;
+static __device__ __align__(256) float g_sum_scratch[kNoAllocMaxPartials + 64];
+
+// In host code `g_sum_scratch` is only a handle for the symbol, never a pointer a kernel may use: the
+// device address is looked up once per device (with that device current) and cached here.
+static float* g_sum_scratch_dev[16] = {nullptr};
+
+catena_status_t sum_f32_noalloc(const float* in, uint64_t n, float* d_out) {
+    CATENA_TRY(ensure_device());
+    if (!d_out || (n != 0 && !in)) return fail(CATENA_E_BAD_ARG, "sum_f32_noalloc: null pointer");
+    if (n > kNoAllocMaxElems)
+        return fail(CATENA_E_TOO_LARGE, "sum_f32_noalloc: more than 2^30 elements (fixed scratch array)");
+    const int dev = tls().device & 15;
+    if (!g_sum_scratch_dev[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_sum_scratch);
+        if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(g_sum_scratch)");
+        g_sum_scratch_dev[dev] = static_cast<float*>(p);
+    }
+    float* scratch = g_sum_scratch_dev[dev];
+    cudaStream_t st = tls().stream;
+    if (n <= kExactFoldMax) {
+        // short inputs (and the empty one, whose sum is +0) take the sequential fold: no scratch at all
+        fold_exact_kernel<F_SUM><<<1, kThreads, 0, st>>>(in, n, nullptr, d_out);
+        count_launch();
+        return finish("sum_f32_noalloc");
+    }
+    // Same tree as the pooled path: level 0 writes every partial it will read back, so nothing in the
+    // array needs clearing between calls.
+    uint64_t blocks = ceil_div_u64(n, kChunk);
+    float* src = scratch;
+    float* dst = scratch + kNoAllocMaxPartials;          // upper levels: at most 4, then 1 partials
+    fold_tree_kernel<F_SUM, F_SUM><<<(unsigned)blocks, kThreads, 0, st>>>(in, n, nullptr, blocks == 1 ? d_out : src);
+    count_launch();
+    uint64_t cur = blocks;
+    while (cur > 1) {
+        uint64_t nb = ceil_div_u64(cur, kChunk);
+        fold_tree_kernel<F_SUM, F_SUM><<<(unsigned)nb, kThreads, 0, st>>>(src, cur, nullptr, nb == 1 ? d_out : dst);
+        count_launch();
+        float* t = src; src = dst; dst = t;
+        cur = nb;
+    }
+    return finish("sum_f32_noalloc");
+}
+
 }  // namespace catena
+
+// Sum of `n` f32 values for callers that must not allocate: a host that gave all of HBM to its own
+// arena when it started (so a cudaMalloc inside the library would fail), or a latency-critical loop
+// that cannot take the device-wide synchronisation an allocation implies.  `in` and `out` are device
+// pointers owned by the caller (`out`: one float).  No cudaMalloc, cudaFree or pool call is made; the
+// partial sums of the reduction tree go to a fixed 256 KiB array inside the library image, which
+// bounds the input at 2^30 elements (CATENA_E_TOO_LARGE beyond).  The first call on each device looks
+// up that array's device address; make it before starting any stream capture.  All calls on a device
+// share the array, so two calls whose kernels overlap on the GPU (different streams or threads) race;
+// calls on one stream are ordered and safe.  The value is bit-identical to program_sum_f32.
+extern "C" catena_status_t catena_b200_sum_f32_noalloc(const void* in, uint64_t n, void* out) {
+    return catena::sum_f32_noalloc(static_cast<const float*>(in), n, static_cast<float*>(out));
+}

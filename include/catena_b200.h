@@ -190,6 +190,16 @@ catena_status_t catena_b200_attn_decode_bf16_into(const void* q, const void* k_c
 catena_status_t catena_b200_map_f32_into(const char* op, const void* in, void* out, uint64_t n);
 catena_status_t catena_b200_softmax_f32_into(const void* in, void* out, uint64_t n);
 catena_status_t catena_b200_rmsnorm_f32_into(const void* in, void* out, uint64_t n);
+/* Sum of n f32 values without any allocation.  No counterpart in the reference (its sum-f32 folds
+ * on the host).  For callers that cannot let the library allocate: a host that handed all of HBM to
+ * its own arena at start-up, or a latency-critical loop that cannot take the device-wide
+ * synchronisation of a cudaMalloc.  `in` (n floats) and `out` (1 float) are caller-owned DEVICE
+ * pointers.  The reduction tree's partial sums live in a fixed 256 KiB array inside the library image
+ * (resident on every GPU that loads the library), which limits n to 2^30 elements; larger inputs
+ * return CATENA_E_TOO_LARGE.  The first call on a device resolves that array's device address: make
+ * it before any stream capture begins.  Calls share the array, so calls whose kernels overlap on the
+ * GPU race; calls issued on one stream are ordered.  The result is bit-identical to program_sum_f32. */
+catena_status_t catena_b200_sum_f32_noalloc(const void* in, uint64_t n, void* out);
 /* test hook: cap the persistent grid of the tensor-core GEMM (0 = one CTA per SM); results must not
  * change with it.  No counterpart in the reference. */
 void catena_b200_debug_set_cta_limit(int limit);
