@@ -19,7 +19,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libcatena_b200.so")
+# CATENA_B200_LIB overrides the location of the kernel library (same role as in INTEGRATION.md)
+LIB_PATH = os.environ.get("CATENA_B200_LIB") or os.path.join(_HERE, "libcatena_b200.so")
 
 OK, E_ASSERT, E_CUDA, E_NO_DEVICE, E_BAD_ARG, E_TIMEOUT, E_TOO_LARGE, E_UNSUPPORTED = range(8)
 
@@ -114,6 +115,7 @@ def lib():
     proto("catena_b200_check_device_errors", st, [])
     proto("catena_b200_debug_set_cta_limit", None, [C.c_int])
     proto("catena_b200_sum_f32_noalloc", st, [vp, u64, vp])
+    proto("catena_b200_debug_set_gemm_pair", None, [C.c_int])
     _lib = L
     return L
 

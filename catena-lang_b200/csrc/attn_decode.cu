@@ -7,18 +7,21 @@
 // exp~(x-m1)*exp~(m1-m2) != exp~(x-m2), so every probability here is exp~(s_j - m) with the one
 // true row maximum m, exactly as nn.softmax computes it.
 //
-// Work decomposition (a function of the problem only, never of the GPU or SM count):
+// Work decomposition (a function of the problem only, never of the GPU, SM or cluster count):
 //   unit   = (batch, kv-head) with its G = Hq/Hkv query heads, so K and V are read once per group;
-//   split  = the KV length is cut into kSplits = 8 contiguous chunks; the 8 CTAs of one unit form a
-//            thread-block cluster.  Each CTA streams its K chunk (TMA, 128B-swizzled 64-position
-//            tiles, 4-stage mbarrier ring), keeps raw scores in shared memory, the cluster exchanges
-//            the chunk maxima over distributed shared memory, each CTA turns its scores into
-//            probabilities with the global maximum and streams its V chunk (already prefetched
-//            into the ring during the exchange), and the 8 partial (sum p*v, sum p) pairs are
-//            combined in ascending chunk order through distributed shared memory.
-// Math runs on `mma.sync.m16n8k16` bf16 (positions on the M axis, the <= 8 query heads on N);
-// probabilities enter the P*V product as a bf16 hi + bf16 lo pair so no precision is lost to the
-// operand format.  FLOPs are irrelevant here (4 FLOP per KV byte); the kernel is sized for HBM.
+//   split  = the KV length is cut into kSplits = 8 contiguous chunks, one per CTA of a thread-block
+//            cluster; partial results are combined in ascending chunk order.
+// Execution: persistent clusters, each walking units first, first + #clusters, ...  A CTA streams
+// 64-position tiles of its chunk through a 4-stage TMA / mbarrier ring (128B-swizzled, no multicast)
+// and software-pipelines consecutive units so the cluster-wide exchanges never idle the stream:
+//   iteration i:  K tiles of unit i -> raw scores, chunk maxima          | barrier.cluster.arrive
+//                 V tiles of unit i-1 -> partial sum p*v                 | barrier.cluster.wait
+//                 global max of unit i over DSMEM, p = exp~(s - max) (bf16 hi + lo), chunk denominator
+//                 combine unit i-2 over DSMEM in ascending chunk order, divide, round to bf16, store
+// Buffers that peers read are multi-buffered (maxima x2, partial outputs and denominators x3) so a
+// slot is only rewritten after a later cluster barrier has proved every reader done.
+// Math runs on `mma.sync.m16n8k16` bf16 (positions or head-dim on M, the <= 8 query heads on N);
+// FLOPs are irrelevant here (4 FLOP per KV byte); the kernel is sized for HBM.
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -34,7 +37,10 @@ namespace attn {
 
 constexpr int kD = 128;
 constexpr int kTile = 64;                    // positions per ring stage
-constexpr int kStages = 4;
+#ifndef CATENA_ATTN_STAGES
+#define CATENA_ATTN_STAGES 4
+#endif
+constexpr int kStages = CATENA_ATTN_STAGES;
 constexpr int kSplits = 8;                   // cluster size = KV chunks per unit
 constexpr int kStageBytes = kTile * kD * 2;  // 16 KiB (two 8 KiB halves of 64 d each)
 constexpr int kHalfBytes = kTile * 128;
@@ -44,8 +50,8 @@ constexpr uint64_t kWaitNs = 1000000000ull;
 
 struct __align__(16) Control {
     uint64_t full[kStages];
-    float local_max[kMaxG];
-    float denom_part[kMaxG];
+    float lmax_all[2][kSplits][kMaxG];   // chunk maxima of every rank, written by the peers (push)
+    float den_all[3][kSplits][kMaxG];    // chunk denominators of every rank, written by the peers
     float gmax[kMaxG];
     float warp_part[4][kMaxG];
     volatile uint32_t abort_flag;
@@ -105,36 +111,46 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Split cluster barrier: every thread of every CTA of the cluster executes both halves, once per
+// iteration; writes made before `arrive` are visible to peers after their `wait`.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // byte offset inside a stage of the 16-byte chunk `chunk` (0..15 over d) of position row `row`
 __device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t chunk) {
     uint32_t half = chunk >> 3, c = chunk & 7u;
     return half * kHalfBytes + row * 128u + ((c ^ (row & 7u)) << 4);
 }
 
-// grid.x = kSplits * (unit1 - unit0); cluster (kSplits,1,1); block 128 threads.
+// grid.x = kSplits * #clusters; cluster (kSplits,1,1); block 128 threads.
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ o, uint32_t L, uint32_t G,
-                   uint32_t Hq, uint32_t Hkv, uint32_t unit0, uint32_t chunk, float scale, uint32_t* err) {
+                   uint32_t Hq, uint32_t Hkv, uint32_t unit0, uint32_t unit1, uint32_t chunk, float scale,
+                   uint32_t* err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* ring = smem;
-    float* scores = reinterpret_cast<float*>(smem + kStages * kStageBytes);       // [G][chunk]
-    __nv_bfloat16* p_hi = reinterpret_cast<__nv_bfloat16*>(scores + (size_t)G * chunk);  // [G][chunk]
-    __nv_bfloat16* p_lo = p_hi + (size_t)G * chunk;
-    float* o_part = reinterpret_cast<float*>(p_lo + (size_t)G * chunk);            // [G][128]
-    Control* ctl = reinterpret_cast<Control*>(o_part + (size_t)G * kD);
+    const size_t gc = (size_t)G * chunk;
+    float* scores = reinterpret_cast<float*>(smem + kStages * kStageBytes);           // [2][G][chunk]
+    __nv_bfloat16* p_hi = reinterpret_cast<__nv_bfloat16*>(scores + 2 * gc);          // [2][G][chunk]
+    __nv_bfloat16* p_lo = p_hi + 2 * gc;                                              // [2][G][chunk]
+    // partial outputs of every rank for THIS CTA's slice of the (head, d) outputs, written by the peers
+    float* o_gather = reinterpret_cast<float*>(p_lo + 2 * gc);                        // [3][kSplits][G*16]
+    Control* ctl = reinterpret_cast<Control*>(o_gather + 3 * (size_t)G * kD);
+    const uint32_t per_rank = G * kD / kSplits;                                       // outputs combined per CTA
 
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t rank = cluster.block_rank();
-    const uint32_t unit = unit0 + blockIdx.x / kSplits;
-    const uint32_t b = unit / Hkv, kvh = unit % Hkv;
+    const uint32_t nclusters = gridDim.x / kSplits;
+    const uint32_t first = unit0 + blockIdx.x / kSplits;
+    const uint32_t n = first < unit1 ? (unit1 - first + nclusters - 1) / nclusters : 0;   // units of this cluster
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const uint32_t pos_begin = rank * chunk;
-    const uint32_t valid = pos_begin < L ? min(chunk, L - pos_begin) : 0u;   // positions of this CTA
-    const uint32_t T = (valid + kTile - 1) / kTile;                          // K tiles (= V tiles)
-    const uint32_t total = 2 * T;
+    const uint32_t valid = pos_begin < L ? min(chunk, L - pos_begin) : 0u;   // positions of this CTA per unit
+    const uint32_t T = (valid + kTile - 1) / kTile;                          // K tiles (= V tiles) per unit
+    const uint32_t total = 2 * n * T;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s)
@@ -144,17 +160,25 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     }
     __syncthreads();
 
-    // tile g of this CTA: g < T -> K tile g, else V tile g - T
+    // The tile stream of this CTA, in groups of T tiles:  K(0) | K(1) V(0) | K(2) V(1) | ... | V(n-1)
     auto issue = [&](uint32_t g) {
-        uint32_t st = g % kStages;
-        const CUtensorMap* map = g < T ? &map_k : &map_v;
-        uint32_t pos = pos_begin + (g < T ? g : g - T) * kTile;
+        const uint32_t c = g / T, t = g - c * T;
+        bool is_v;
+        uint32_t j;
+        if (c == 0) { is_v = false; j = 0; }
+        else if (c == 2 * n - 1) { is_v = true; j = n - 1; }
+        else if (c & 1u) { is_v = false; j = (c + 1) >> 1; }
+        else { is_v = true; j = (c >> 1) - 1; }
+        const uint32_t st = g % kStages;
+        const CUtensorMap* map = is_v ? &map_v : &map_k;
+        const int pos = (int)(pos_begin + t * kTile);
+        const int unit = (int)(first + j * nclusters);
         uint64_t* bar = &ctl->full[st];
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"((uint32_t)kStageBytes)
                      : "memory");
-        uint32_t dst = smem_u32(ring + st * kStageBytes);
-        tma_load_3d(dst, map, 0, (int)pos, (int)unit, bar);
-        tma_load_3d(dst + kHalfBytes, map, 64, (int)pos, (int)unit, bar);
+        const uint32_t dst = smem_u32(ring + st * kStageBytes);
+        tma_load_3d(dst, map, 0, pos, unit, bar);
+        tma_load_3d(dst + kHalfBytes, map, 64, pos, unit, bar);
     };
     if (tid == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
@@ -162,171 +186,205 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         for (uint32_t g = 0; g < total && g < (uint32_t)kStages; ++g) issue(g);
     }
 
-    // Q as B fragments of S^T = K * Q^T: lane holds Q[head = lane/4][d = 16*ks + 2*(lane%4) + {0,1}] and d + 8
-    uint32_t qb[8][2];
-    {
-        const uint32_t head = lane >> 2;
-        const __nv_bfloat16* qrow = q + ((size_t)b * Hq + (size_t)kvh * G + head) * kD;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            uint32_t d = ks * 16 + (lane & 3u) * 2;
-            qb[ks][0] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d) : 0u;
-            qb[ks][1] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d + 8) : 0u;
-        }
-    }
-
     bool aborted = false;
+    uint32_t g = 0;   // tiles consumed so far
     // Waits for tile g, makes the decision block-uniform, and refills the stage of tile g-1
     // (every warp finished reading it before reaching this barrier).
-    auto acquire = [&](uint32_t g) -> bool {
-        bool ok = mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err);
+    auto acquire = [&](uint32_t gg) -> bool {
+        bool ok = mbar_wait(&ctl->full[gg % kStages], (gg / kStages) & 1u, ctl, err);
         if (__syncthreads_or(ok ? 0 : 1)) return false;
-        if (tid == 0 && g >= 1 && g - 1 + kStages < total) issue(g - 1 + kStages);
+        if (tid == 0 && gg >= 1 && gg - 1 + kStages < total) issue(gg - 1 + kStages);
         return true;
     };
 
-    // ---------------- phase 1: scores of this chunk ----------------
-    for (uint32_t g = 0; g < T && !aborted; ++g) {
-        if (!acquire(g)) { aborted = true; break; }
-        const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t row = warp * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8;
+    // Q of unit j as B fragments of S^T = K * Q^T: lane holds Q[head = lane/4][d = 16*ks + 2*(lane%4) + {0,1}], d + 8
+    auto load_q = [&](uint32_t j, uint32_t (&dst)[8][2]) {
+        const uint32_t unit = first + j * nclusters;
+        const uint32_t head = lane >> 2;
+        const __nv_bfloat16* qrow = q + ((size_t)unit * G + head) * kD;   // (b*Hq + kvh*G + head) = unit*G + head
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-            uint32_t a[4];
-            ldsm_x4(base + tile_off(row, ks * 2 + (lane >> 4)), a);
-            mma_bf16(c, a, qb[ks][0], qb[ks][1]);
+            uint32_t d = ks * 16 + (lane & 3u) * 2;
+            dst[ks][0] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d) : 0u;
+            dst[ks][1] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d + 8) : 0u;
         }
-        // C fragment: rows (lane/4, lane/4+8) of this warp's 16 positions, heads 2*(lane%4)+{0,1}
-        const uint32_t p0 = g * kTile + warp * 16 + (lane >> 2);
-        const uint32_t h0 = (lane & 3u) * 2;
-        if (h0 < G) {
-            scores[(size_t)h0 * chunk + p0] = cmath::mul(c[0], scale);
-            scores[(size_t)h0 * chunk + p0 + 8] = cmath::mul(c[2], scale);
-        }
-        if (h0 + 1 < G) {
-            scores[(size_t)(h0 + 1) * chunk + p0] = cmath::mul(c[1], scale);
-            scores[(size_t)(h0 + 1) * chunk + p0 + 8] = cmath::mul(c[3], scale);
-        }
-    }
-    __syncthreads();
+    };
+    uint32_t qb[8][2], qn[8][2];
+    if (n > 0) load_q(0, qn);
 
-    // chunk maxima (order-free on finite data)
-    for (uint32_t h = warp; h < G; h += 4) {
-        float m = __uint_as_float(0xFF800000u);
-        if (!aborted)
-            for (uint32_t p = lane; p < valid; p += 32) m = fmaxf(m, scores[(size_t)h * chunk + p]);
+    for (uint32_t i = 0; i <= n + 1; ++i) {
+        // ---------------- K tiles of unit i: raw scores ----------------
+        if (i < n) {
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-        if (lane == 0) ctl->local_max[h] = m;
-    }
-    cluster.sync();   // #1: every CTA's local_max is visible cluster-wide
-    if (tid < G) {
-        float m = __uint_as_float(0xFF800000u);
-        for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) {
-            const float* remote = cluster.map_shared_rank(ctl->local_max, r);
-            m = fmaxf(m, remote[tid]);
-        }
-        ctl->gmax[tid] = m;
-    }
-    __syncthreads();
-
-    // probabilities p = exp~(s - max) as bf16 hi + lo, and this chunk's denominator in a fixed order:
-    // thread t sums positions t, t+128, ... ascending; xor butterfly per warp; warps 0..3 ascending.
-    for (uint32_t h = 0; h < G; ++h) {
-        const float m = ctl->gmax[h];
-        float acc = 0.0f;
-        for (uint32_t p = tid; p < chunk; p += kThreads) {
-            float pv = 0.0f;
-            if (p < valid && !aborted) pv = cmath::exp_approx(cmath::sub(scores[(size_t)h * chunk + p], m));
-            __nv_bfloat16 hi = __float2bfloat16_rn(pv);
-            __nv_bfloat16 lo = __float2bfloat16_rn(cmath::sub(pv, __bfloat162float(hi)));
-            p_hi[(size_t)h * chunk + p] = hi;
-            p_lo[(size_t)h * chunk + p] = lo;
-            acc = cmath::add(acc, pv);
-        }
+            for (int ks = 0; ks < 8; ++ks) { qb[ks][0] = qn[ks][0]; qb[ks][1] = qn[ks][1]; }
+            if (i + 1 < n) load_q(i + 1, qn);     // lands while this unit streams
+            float* sc = scores + (size_t)(i & 1u) * gc;
+            for (uint32_t t = 0; t < T && !aborted; ++t, ++g) {
+                if (!acquire(g)) { aborted = true; break; }
+                const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
+                // two accumulation chains (even / odd 16-wide d slices) so consecutive MMAs do not wait on
+                // each other, joined by one fp32 add per score
+                float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t row = warp * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8;
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) acc = cmath::add(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, off));
-        if (lane == 0) ctl->warp_part[warp][h] = acc;
-    }
-    __syncthreads();
-    if (tid < G) {
-        float d = ctl->warp_part[0][tid];
-        for (int w = 1; w < 4; ++w) d = cmath::add(d, ctl->warp_part[w][tid]);
-        ctl->denom_part[tid] = d;
-    }
-
-    // ---------------- phase 2: O^T = V^T * P^T over this chunk ----------------
-    float acc[2][4];
+                for (int ks = 0; ks < 8; ks += 2) {
+                    uint32_t a[4], a2[4];
+                    ldsm_x4(base + tile_off(row, ks * 2 + (lane >> 4)), a);
+                    ldsm_x4(base + tile_off(row, (ks + 1) * 2 + (lane >> 4)), a2);
+                    mma_bf16(c, a, qb[ks][0], qb[ks][1]);
+                    mma_bf16(c2, a2, qb[ks + 1][0], qb[ks + 1][1]);
+                }
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[mt][e] = 0.0f;
-    for (uint32_t g = T; g < total && !aborted; ++g) {
-        if (!acquire(g)) { aborted = true; break; }
-        const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
-        const uint32_t tile_pos = (g - T) * kTile;
-        const uint32_t head = lane >> 2;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            uint32_t bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;
-            if (head < G) {
-                size_t off = (size_t)head * chunk + tile_pos + ks * 16 + (lane & 3u) * 2;
-                bh0 = *reinterpret_cast<const uint32_t*>(p_hi + off);
-                bh1 = *reinterpret_cast<const uint32_t*>(p_hi + off + 8);
-                bl0 = *reinterpret_cast<const uint32_t*>(p_lo + off);
-                bl1 = *reinterpret_cast<const uint32_t*>(p_lo + off + 8);
+                for (int e = 0; e < 4; ++e) c[e] = cmath::add(c[e], c2[e]);
+                // C fragment: rows (lane/4, lane/4+8) of this warp's 16 positions, heads 2*(lane%4)+{0,1}
+                const uint32_t p0 = t * kTile + warp * 16 + (lane >> 2);
+                const uint32_t h0 = (lane & 3u) * 2;
+                if (h0 < G) {
+                    sc[(size_t)h0 * chunk + p0] = cmath::mul(c[0], scale);
+                    sc[(size_t)h0 * chunk + p0 + 8] = cmath::mul(c[2], scale);
+                }
+                if (h0 + 1 < G) {
+                    sc[(size_t)(h0 + 1) * chunk + p0] = cmath::mul(c[1], scale);
+                    sc[(size_t)(h0 + 1) * chunk + p0 + 8] = cmath::mul(c[3], scale);
+                }
             }
-            const uint32_t prow = ks * 16 + (lane & 7u) + (lane >> 4) * 8;
+            __syncthreads();
+            // chunk maxima (order-free on finite data)
+            for (uint32_t h = warp; h < G; h += 4) {
+                float m = __uint_as_float(0xFF800000u);
+                if (!aborted)
+                    for (uint32_t p = lane; p < valid; p += 32) m = fmaxf(m, sc[(size_t)h * chunk + p]);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+                // push: lane r stores this chunk's maximum into rank r's table, so after the barrier every
+                // CTA finds all eight maxima in its own shared memory
+                if (lane < (uint32_t)kSplits) *cluster.map_shared_rank(&ctl->lmax_all[i & 1u][rank][h], lane) = m;
+            }
+        }
+        cluster_arrive();
+
+        // ---------------- V tiles of unit i-1: O^T = V^T * P^T over this chunk ----------------
+        if (i >= 1 && i <= n) {
+            const uint32_t j = i - 1;
+            const __nv_bfloat16* ph = p_hi + (size_t)(j & 1u) * gc;
+            const __nv_bfloat16* pl = p_lo + (size_t)(j & 1u) * gc;
+            // separate chains for the hi and lo halves of p (4 independent MMA chains per warp)
+            float acc[2][4], acc_lo[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { acc[mt][e] = 0.0f; acc_lo[mt][e] = 0.0f; }
+            for (uint32_t t = 0; t < T && !aborted; ++t, ++g) {
+                if (!acquire(g)) { aborted = true; break; }
+                const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
+                const uint32_t tile_pos = t * kTile;
+                const uint32_t head = lane >> 2;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;
+                    if (head < G) {
+                        size_t off = (size_t)head * chunk + tile_pos + ks * 16 + (lane & 3u) * 2;
+                        bh0 = *reinterpret_cast<const uint32_t*>(ph + off);
+                        bh1 = *reinterpret_cast<const uint32_t*>(ph + off + 8);
+                        bl0 = *reinterpret_cast<const uint32_t*>(pl + off);
+                        bl1 = *reinterpret_cast<const uint32_t*>(pl + off + 8);
+                    }
+                    const uint32_t prow = ks * 16 + (lane & 7u) + (lane >> 4) * 8;
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        uint32_t a[4];
+                        ldsm_x4_trans(base + tile_off(prow, (warp * 2 + mt) * 2 + ((lane >> 3) & 1u)), a);
+                        mma_bf16(acc[mt], a, bh0, bh1);
+                        mma_bf16(acc_lo[mt], a, bl0, bl1);
+                    }
+                }
+            }
+            // partial outputs: C fragment rows d = 16*mtile + lane/4 (+8), heads 2*(lane%4)+{0,1}.
+            // push: output (h, d) belongs to the slice of rank (h*128 + d) / per_rank, which will combine it
+            float* og = o_gather + ((size_t)(j % 3u) * kSplits + rank) * per_rank;
+            const uint32_t h0 = (lane & 3u) * 2;
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) {
-                uint32_t a[4];
-                ldsm_x4_trans(base + tile_off(prow, (warp * 2 + mt) * 2 + ((lane >> 3) & 1u)), a);
-                mma_bf16(acc[mt], a, bh0, bh1);
-                mma_bf16(acc[mt], a, bl0, bl1);
-            }
-        }
-    }
-    // partial outputs: C fragment rows d = 16*mtile + lane/4 (+8), heads 2*(lane%4)+{0,1}
-    {
-        const uint32_t h0 = (lane & 3u) * 2;
+                const uint32_t d0 = (warp * 2 + mt) * 16 + (lane >> 2);
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-            const uint32_t d0 = (warp * 2 + mt) * 16 + (lane >> 2);
-            if (h0 < G) {
-                o_part[h0 * kD + d0] = acc[mt][0];
-                o_part[h0 * kD + d0 + 8] = acc[mt][2];
-            }
-            if (h0 + 1 < G) {
-                o_part[(h0 + 1) * kD + d0] = acc[mt][1];
-                o_part[(h0 + 1) * kD + d0 + 8] = acc[mt][3];
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t h = h0 + (e & 1), d = d0 + (e >> 1) * 8;
+                    if (h < G) {
+                        const uint32_t idx = h * kD + d;
+                        const uint32_t dst_rank = idx / per_rank;
+                        *cluster.map_shared_rank(og + (idx - dst_rank * per_rank), dst_rank) =
+                            cmath::add(acc[mt][e], acc_lo[mt][e]);
+                    }
+                }
             }
         }
-    }
-    cluster.sync();   // #2: every CTA's o_part / denom_part is visible cluster-wide
+        cluster_wait();
 
-    // ---------------- combine: ascending chunk order, one slice of the outputs per CTA ----------------
-    {
-        const uint32_t per_rank = G * kD / kSplits;   // G*16 <= 128
-        if (tid < per_rank) {
-            const uint32_t idx = rank * per_rank + tid;
-            const uint32_t h = idx / kD, d = idx % kD;
-            float num = 0.0f, den = 0.0f;
-            for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) {
-                const float* ro = cluster.map_shared_rank(o_part, r);
-                const float* rd = cluster.map_shared_rank(ctl->denom_part, r);
-                num = cmath::add(num, ro[h * kD + d]);
-                den = cmath::add(den, rd[h]);
+        // ---------------- unit i: global max over the cluster, probabilities, chunk denominator ----------------
+        if (i < n) {
+            if (tid < G) {
+                float m = __uint_as_float(0xFF800000u);
+#pragma unroll
+                for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) m = fmaxf(m, ctl->lmax_all[i & 1u][r][tid]);
+                ctl->gmax[tid] = m;
             }
-            if (!aborted)
-                o[((size_t)b * Hq + (size_t)kvh * G + h) * kD + d] = __float2bfloat16_rn(cmath::div(num, den));
+            __syncthreads();
+            const float* sc = scores + (size_t)(i & 1u) * gc;
+            __nv_bfloat16* ph = p_hi + (size_t)(i & 1u) * gc;
+            __nv_bfloat16* pl = p_lo + (size_t)(i & 1u) * gc;
+            // fixed order: thread t sums positions t, t+128, ... ascending; xor butterfly per warp; warps 0..3 ascending
+            for (uint32_t h = 0; h < G; ++h) {
+                const float m = ctl->gmax[h];
+                float acc = 0.0f;
+                for (uint32_t p = tid; p < chunk; p += kThreads) {
+                    float pv = 0.0f;
+                    if (p < valid && !aborted) pv = cmath::exp_approx(cmath::sub(sc[(size_t)h * chunk + p], m));
+                    __nv_bfloat16 hi = __float2bfloat16_rn(pv);
+                    __nv_bfloat16 lo = __float2bfloat16_rn(cmath::sub(pv, __bfloat162float(hi)));
+                    ph[(size_t)h * chunk + p] = hi;
+                    pl[(size_t)h * chunk + p] = lo;
+                    acc = cmath::add(acc, pv);
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) acc = cmath::add(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, off));
+                if (lane == 0) ctl->warp_part[warp][h] = acc;
+            }
+            __syncthreads();
+            if (tid < G) {
+                float d = ctl->warp_part[0][tid];
+                for (int w = 1; w < 4; ++w) d = cmath::add(d, ctl->warp_part[w][tid]);
+#pragma unroll
+                for (uint32_t r = 0; r < (uint32_t)kSplits; ++r)
+                    *cluster.map_shared_rank(&ctl->den_all[i % 3u][rank][tid], r) = d;
+            }
+        }
+
+        // ---------------- unit i-2: combine in ascending chunk order, one slice of the outputs per CTA ----------------
+        if (i >= 2) {
+            const uint32_t j = i - 2;
+            if (tid < per_rank) {   // per_rank = G*16 <= 128
+                const uint32_t idx = rank * per_rank + tid;
+                const uint32_t h = idx / kD, d = idx % kD;
+                const float* og = o_gather + (size_t)(j % 3u) * kSplits * per_rank + tid;
+                float num = 0.0f, den = 0.0f;
+#pragma unroll
+                for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) {
+                    num = cmath::add(num, og[r * per_rank]);
+                    den = cmath::add(den, ctl->den_all[j % 3u][r][h]);
+                }
+                const uint32_t unit = first + j * nclusters;
+                if (!ctl->abort_flag)
+                    o[((size_t)unit * G + h) * kD + d] = __float2bfloat16_rn(cmath::div(num, den));
+            }
         }
     }
     if (ctl->abort_flag) {
         uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
-    cluster.sync();   // #3: nobody leaves while peers still read its shared memory
+    // nobody leaves while peers may still read its shared memory
+    cluster_arrive();
+    cluster_wait();
 }
 
 }  // namespace attn
@@ -364,14 +422,17 @@ static catena_status_t make_kv_map(CUtensorMap* map, const void* base, uint64_t 
 
 static thread_local uint32_t* g_attn_err_dev[16] = {nullptr};
 static thread_local uint32_t* g_attn_err_host[16] = {nullptr};
+// Test hook shared with the GEMM: caps the number of resident clusters (0 = as many as fit).
+static int g_attn_cluster_limit = 0;
+void attn_set_cluster_limit(int limit) { g_attn_cluster_limit = limit > 0 ? limit : 0; }
 
 static uint32_t chunk_for(uint64_t L) {
     uint64_t c = ceil_div_u64(ceil_div_u64(L, attn::kSplits), attn::kTile) * attn::kTile;
     return (uint32_t)(c < (uint64_t)attn::kTile ? attn::kTile : c);
 }
 static size_t attn_smem_bytes(uint32_t G, uint32_t chunk) {
-    return 1024 + (size_t)attn::kStages * attn::kStageBytes + (size_t)G * chunk * (4 + 2 + 2) + (size_t)G * attn::kD * 4 +
-           sizeof(attn::Control) + 16;
+    return 1024 + (size_t)attn::kStages * attn::kStageBytes + 2 * (size_t)G * chunk * (4 + 2 + 2) +
+           3 * (size_t)G * attn::kD * 4 + sizeof(attn::Control) + 16;
 }
 
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch, uint64_t hq,
@@ -405,7 +466,6 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     CATENA_CUDA(cudaFuncSetAttribute(attn::attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((unit1 - unit0) * attn::kSplits));
     cfg.blockDim = dim3(attn::kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = tls().stream;
@@ -416,10 +476,21 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
+    // persistent clusters: as many as can be resident at once, never more than there are units
+    cfg.gridDim = dim3((unsigned)(attn::kSplits * (unit1 - unit0)));
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, attn::attn_decode_kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+        (void)cudaGetLastError();
+        max_clusters = 16;
+    }
+    uint64_t clusters = unit1 - unit0;
+    if (clusters > (uint64_t)max_clusters) clusters = (uint64_t)max_clusters;
+    if (g_attn_cluster_limit > 0 && clusters > (uint64_t)g_attn_cluster_limit) clusters = (uint64_t)g_attn_cluster_limit;
+    cfg.gridDim = dim3((unsigned)(clusters * attn::kSplits));
     float scale = 1.0f / sqrtf((float)attn::kD);
     CATENA_CUDA(cudaLaunchKernelEx(&cfg, attn::attn_decode_kernel, map_k, map_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)o,
-                                   (uint32_t)kv_len, G, (uint32_t)hq, (uint32_t)hkv, (uint32_t)unit0, chunk, scale,
-                                   g_attn_err_dev[dev]));
+                                   (uint32_t)kv_len, G, (uint32_t)hq, (uint32_t)hkv, (uint32_t)unit0, (uint32_t)unit1, chunk,
+                                   scale, g_attn_err_dev[dev]));
     count_launch();
     if (tls().blocking) {
         cudaStream_t st = tls().stream;

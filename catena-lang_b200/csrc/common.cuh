@@ -64,6 +64,8 @@ catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m
                                uint64_t ldc, int is_i8);
 catena_status_t gemm_tc_check_errors();
 void gemm_tc_set_cta_limit(int limit);
+void gemm_tc_set_pair_mode(int on);
+void attn_set_cluster_limit(int limit);
 // attn_decode.cu
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
                                    uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t unit0,

@@ -23,6 +23,7 @@
 // returns — it never traps and never spins forever.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -155,9 +156,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 // c_format [4,6): 1 = F32, 2 = S32; a_format [7,10), b_format [10,13): 1 = BF16 (kind::f16) or
 // 1 = signed int8 (kind::i8); n_dim = N >> 3 in [17,23); m_dim = M >> 4 in [24,29).
 template <bool IS_I8>
-__host__ __device__ constexpr uint32_t make_idesc() {
-    return ((IS_I8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-           ((uint32_t)(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t n) {
+    return ((IS_I8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ void tile_coords(uint32_t t, uint32_t mb, uint32_t nb, uint32_t& m_blk, uint32_t& n_blk) {
@@ -170,10 +170,42 @@ __device__ __forceinline__ void tile_coords(uint32_t t, uint32_t mb, uint32_t nb
     n_blk = in_g / rows;
 }
 
+// One unit of work: a 128-row tile of `width` columns starting at column `col0`.
+struct Work {
+    uint32_t m_blk, col0, width;
+};
+
+// Static schedule.  Tiles are dealt round-robin to the persistent CTAs; the tiles of the last, partial
+// round are cut along N into `split` (1, 2 or 4) narrower units so that (nearly) every SM has work in
+// that round too.  An output element's k order does not depend on the width of the unit that owns it,
+// so the split changes the timing only, never a bit of the result.
+__device__ __forceinline__ bool get_work(uint32_t it, uint32_t mb, uint32_t nb, uint32_t tiles, uint32_t split, Work& w) {
+    const uint32_t full = (tiles / gridDim.x) * gridDim.x;
+    const uint32_t idx = it * gridDim.x + blockIdx.x;
+    uint32_t t, part = 0, width = BN;
+    if (idx < full) {
+        t = idx;
+    } else {
+        const uint32_t u = idx - full;
+        if (u >= (tiles - full) * split) return false;
+        t = full + u / split;
+        part = u % split;
+        width = BN / split;
+    }
+    uint32_t m_blk, n_blk;
+    tile_coords(t, mb, nb, m_blk, n_blk);
+    w.m_blk = m_blk;
+    w.col0 = n_blk * BN + part * width;
+    w.width = width;
+    return true;
+}
+
 template <bool IS_I8>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               void* __restrict__ c_out, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t* err) {
+               const __grid_constant__ CUtensorMap map_b128, const __grid_constant__ CUtensorMap map_b64,
+               void* __restrict__ c_out, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split,
+               uint32_t* err) {
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need 1024-byte alignment (descriptor base_offset = 0)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -217,15 +249,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-                uint32_t m_blk, n_blk;
-                tile_coords(t, mb, nb, m_blk, n_blk);
+            Work w;
+            for (uint32_t it = 0; ok && get_work(it, mb, nb, tiles, split, w); ++it) {
+                const CUtensorMap* mapb = w.width == (uint32_t)BN ? &map_b : (w.width == (uint32_t)BN / 2 ? &map_b128 : &map_b64);
+                const uint32_t bytes = A_BYTES + w.width * BK_BYTES;
                 for (uint32_t kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, ctl, err, 1u)) { ok = false; break; }
-                    mbar_expect_tx(&ctl->full[stage], STAGE_BYTES);
+                    mbar_expect_tx(&ctl->full[stage], bytes);
                     uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                    tma_load_2d(sa, &map_a, (int)(kb * K_ELEMS), (int)(m_blk * BM), &ctl->full[stage]);
-                    tma_load_2d(sa + A_BYTES, &map_b, (int)(kb * K_ELEMS), (int)(n_blk * BN), &ctl->full[stage]);
+                    tma_load_2d(sa, &map_a, (int)(kb * K_ELEMS), (int)(w.m_blk * BM), &ctl->full[stage]);
+                    tma_load_2d(sa + A_BYTES, mapb, (int)(kb * K_ELEMS), (int)w.col0, &ctl->full[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -233,10 +266,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
-            constexpr uint32_t idesc = make_idesc<IS_I8>();
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            Work w;
+            for (uint32_t it = 0; ok && get_work(it, mb, nb, tiles, split, w); ++it) {
+                const uint32_t idesc = make_idesc<IS_I8>(w.width);
                 if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, ctl, err, 2u)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
@@ -266,18 +300,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t row_in_tile = quad * 32 + lane;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-            uint32_t m_blk, n_blk;
-            tile_coords(t, mb, nb, m_blk, n_blk);
+        Work w;
+        for (uint32_t it = 0; ok && get_work(it, mb, nb, tiles, split, w); ++it) {
             // warp-uniform decision: the tcgen05.ld below is .sync.aligned
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(&ctl->tmem_full[acc], acc_phase, ctl, err, 4u));
             if (!ok) break;
             tc_fence_after();
-            const uint32_t row = m_blk * BM + row_in_tile;
-            const uint32_t col0 = n_blk * BN;
+            const uint32_t row = w.m_blk * BM + row_in_tile;
+            const uint32_t col0 = w.col0;
             const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN; c += 32) {
+            for (uint32_t c = 0; c < w.width; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
                 tmem_ld_wait();
@@ -376,6 +409,22 @@ static catena_status_t make_operand_map(CUtensorMap* map, const void* base, uint
 static int g_cta_limit = 0;
 void gemm_tc_set_cta_limit(int limit) { g_cta_limit = limit > 0 ? limit : 0; }
 
+// Kernel selection.  The CTA-pair kernel (gemm_tc2.cu) is the default; the single-CTA kernel serves
+// products of at most 128 rows (half of a pair tile would be idle) and stays selectable — environment
+// variable CATENA_B200_GEMM_PAIR=0 (read once) or the test hook below — because the two independent
+// implementations must agree bit for bit, which the tests check.
+static int g_pair_mode = -1;
+static bool gemm_pair_mode(uint64_t m) {
+    if (g_pair_mode < 0) {
+        const char* e = getenv("CATENA_B200_GEMM_PAIR");
+        g_pair_mode = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_pair_mode == 1 && m > 128;
+}
+void gemm_tc_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
+catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                 int is_i8, int cta_limit, uint32_t* err_dev);
+
 struct ErrWord {
     uint32_t* dev = nullptr;
     uint32_t* host = nullptr;  // pinned
@@ -406,30 +455,38 @@ catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m
     if (m > 0x7FFFFF00ull || n > 0x7FFFFF00ull || k > 0x7FFFFF00ull) return fail(CATENA_E_TOO_LARGE, "gemm: dimension too large");
     if (ldc < n) return fail(CATENA_E_BAD_ARG, "gemm: ldc < n");
 
-    CUtensorMap map_a, map_b;
-    CATENA_TRY(make_operand_map(&map_a, a, m, k, eb, tc::BM));
-    CATENA_TRY(make_operand_map(&map_b, b, n, k, eb, tc::BN));
     ErrWord* ew = nullptr;
     CATENA_TRY(err_word(&ew));
-
-    if (is_i8)
-        CATENA_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES));
-    else
-        CATENA_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES));
-    uint64_t tiles = ceil_div_u64(m, tc::BM) * ceil_div_u64(n, tc::BN);
-    int sms = tls().sm_count > 0 ? tls().sm_count : 148;
-    unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
-    if (g_cta_limit > 0 && grid > (unsigned)g_cta_limit) grid = (unsigned)g_cta_limit;
     cudaStream_t st = tls().stream;
-    if (is_i8)
-        tc::gemm_tc_kernel<true><<<grid, tc::NUM_THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, c, (uint32_t)m, (uint32_t)n,
-                                                                               (uint32_t)k, ldc, ew->dev);
-    else
-        tc::gemm_tc_kernel<false><<<grid, tc::NUM_THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, c, (uint32_t)m, (uint32_t)n,
-                                                                                (uint32_t)k, ldc, ew->dev);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail_cuda(e, "gemm_tc launch");
+    if (gemm_pair_mode(m)) {
+        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev));
+    } else {
+        CUtensorMap map_a, map_b, map_b128, map_b64;
+        CATENA_TRY(make_operand_map(&map_a, a, m, k, eb, tc::BM));
+        CATENA_TRY(make_operand_map(&map_b, b, n, k, eb, tc::BN));
+        CATENA_TRY(make_operand_map(&map_b128, b, n, k, eb, tc::BN / 2));
+        CATENA_TRY(make_operand_map(&map_b64, b, n, k, eb, tc::BN / 4));
+        if (is_i8)
+            CATENA_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES));
+        else
+            CATENA_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES));
+        uint64_t tiles = ceil_div_u64(m, tc::BM) * ceil_div_u64(n, tc::BN);
+        int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+        unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
+        if (g_cta_limit > 0 && grid > (unsigned)g_cta_limit) grid = (unsigned)g_cta_limit;
+        // tiles of the last partial round are cut along N so that round keeps (nearly) all CTAs busy
+        const uint64_t rem = tiles % grid;
+        const uint32_t split = rem == 0 ? 1u : (rem * 4 <= grid ? 4u : (rem * 2 <= grid ? 2u : 1u));
+        if (is_i8)
+            tc::gemm_tc_kernel<true><<<grid, tc::NUM_THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, map_b128, map_b64, c, (uint32_t)m,
+                                                                                   (uint32_t)n, (uint32_t)k, ldc, split, ew->dev);
+        else
+            tc::gemm_tc_kernel<false><<<grid, tc::NUM_THREADS, tc::SMEM_BYTES, st>>>(map_a, map_b, map_b128, map_b64, c, (uint32_t)m,
+                                                                                    (uint32_t)n, (uint32_t)k, ldc, split, ew->dev);
+        count_launch();
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail_cuda(e, "gemm_tc launch");
+    }
     if (tls().blocking) {
         CATENA_CUDA(cudaMemcpyAsync(ew->host, ew->dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
         CATENA_CUDA(cudaStreamSynchronize(st));

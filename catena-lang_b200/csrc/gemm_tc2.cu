@@ -1,0 +1,439 @@
+// Tensor-core GEMM for sm_100a on CTA PAIRS: C[M,N] = A[M,K] * B^T, A row-major [M,K], B stored [N,K]
+// (both K-major), bf16 -> fp32 -> bf16 or int8 -> int32 -> int32.  Same arithmetic contract as the
+// single-CTA kernel in gemm_tc.cu: one TMEM accumulator per output tile, k-blocks issued in ascending
+// order, no split-K, no atomics; tile -> CTA map and grid size never enter the arithmetic.
+//
+// Why pairs: with one CTA per 128x256 tile each SM must pull 48 KiB per 512 tensor-cycles (96 B/clk);
+// at the measured L2 latency that needs more bytes in flight than shared memory can hold, so the
+// tensor pipe waits on the ring.  `tcgen05.mma.cta_group::2` computes a 256x256 tile on two SMs with
+// each CTA loading only its own 128 rows of A and its own 128 rows (half of N) of B — 32 KiB per
+// k-block per SM (64 B/clk) — which a 6-stage ring covers.
+//
+// Structure (cluster of 2 CTAs = 2 SMs, persistent, 192 threads per CTA):
+//   warp 0      TMA producer in BOTH CTAs: `cp.async.bulk.tensor.2d.cta_group::2` (no multicast) of its
+//               A and B halves into its own 128B-swizzled ring; every load signals the LEADER CTA's
+//               full barrier, which the leader arms with the byte count of both CTAs;
+//   warp 1      both CTAs allocate TMEM together (`tcgen05.alloc.cta_group::2`); the LEADER's elected
+//               thread issues `tcgen05.mma.cta_group::2` (M=256, N<=256) and `tcgen05.commit` with a
+//               cluster multicast mask, releasing ring stages / publishing accumulators in both CTAs;
+//   warps 2-5   epilogue in both CTAs: `tcgen05.ld` of the CTA's own 128 accumulator rows, convert,
+//               store, then arrive on the leader's tmem-empty barrier (remote arrive for the peer).
+// Every mbarrier wait is bounded (about one second); the cluster barriers at start and end are
+// hardware barriers that every thread of both CTAs reaches unconditionally.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace catena {
+
+namespace tc2 {
+
+constexpr int BM = 128;            // rows per CTA (pair tile: 256)
+constexpr int BN = 256;            // pair-tile columns = TMEM columns per accumulator
+constexpr int BK_BYTES = 128;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK_BYTES;              // 16 KiB
+constexpr int B_BYTES = (BN / 2) * BK_BYTES;        // 16 KiB: this CTA's half of N
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 32 KiB
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;         // rasterisation in pair-tile rows (8 x 256 rows)
+constexpr uint64_t WAIT_NS = 1000000000ull;
+
+struct __align__(8) Control {
+    uint64_t full[STAGES];       // used in the leader CTA
+    uint64_t empty[STAGES];      // one per CTA, signalled by the leader's commit (multicast)
+    uint64_t tmem_full[2];       // one per CTA, signalled by the leader's commit (multicast)
+    uint64_t tmem_empty[2];      // used in the leader CTA: 2 x 128 epilogue threads arrive
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+};
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Control);
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// arrive on a barrier anywhere in the cluster (address from mapa)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Control* ctl, uint32_t* err, uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 255u) == 0) {
+            if (ctl->abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_NS) {
+                ctl->abort_flag = 1;
+                atomicCAS(err, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+// TMA load into this CTA's shared memory; completion bytes go to `bar_cluster_addr` (the leader's barrier)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// arrives (once the MMAs issued so far have completed) on the barrier at this shared-memory offset in
+// every CTA of `mask`
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask)
+                 : "memory");
+}
+template <bool IS_I8>
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if (IS_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0),
+              "r"(0), "r"(0), "r"(0)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0),
+              "r"(0), "r"(0), "r"(0)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// K-major, 128 B rows, 128B swizzle: start >> 4, LBO field 1 (unused), SBO = 1024 B, version 1, SWIZZLE_128B
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// dense, K-major A and B; c_format F32 / S32; a,b format BF16 / signed int8; N >> 3 at [17,23); M >> 4 at [24,29), M = 256
+template <bool IS_I8>
+__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
+    return ((IS_I8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+struct Work {
+    uint32_t m_blk;   // pair-tile row block (256 rows)
+    uint32_t col0;    // first column
+    uint32_t width;   // columns: 256, or 128 / 64 for the units of the last partial round
+};
+
+// Static schedule over CTA pairs; the tiles of the last partial round are cut along N into `split` units
+// (timing only: an element's k order does not depend on the unit width).
+__device__ __forceinline__ bool get_work(uint32_t it, uint32_t pair, uint32_t pairs, uint32_t mb, uint32_t nb, uint32_t tiles,
+                                         uint32_t split, Work& w) {
+    const uint32_t full = (tiles / pairs) * pairs;
+    const uint32_t idx = it * pairs + pair;
+    uint32_t t, part = 0, width = BN;
+    if (idx < full) {
+        t = idx;
+    } else {
+        const uint32_t u = idx - full;
+        if (u >= (tiles - full) * split) return false;
+        t = full + u / split;
+        part = u % split;
+        width = BN / split;
+    }
+    const uint32_t per_group = GROUP_M * nb;
+    const uint32_t g = t / per_group;
+    const uint32_t first_m = g * GROUP_M;
+    const uint32_t rows = min((uint32_t)GROUP_M, mb - first_m);
+    const uint32_t in_g = t - g * per_group;
+    w.m_blk = first_m + in_g % rows;
+    w.col0 = (in_g / rows) * BN + part * width;
+    w.width = width;
+    return true;
+}
+
+template <bool IS_I8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b128,
+                const __grid_constant__ CUtensorMap map_b64, const __grid_constant__ CUtensorMap map_b32,
+                void* __restrict__ c_out, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    constexpr uint32_t K_ELEMS = IS_I8 ? BK_BYTES : BK_BYTES / 2;
+    constexpr uint32_t MMA_PER_BLOCK = BK_BYTES / 32;
+    const uint32_t mb = (M + 2 * BM - 1) / (2 * BM), nb = (N + BN - 1) / BN;
+    const uint32_t tiles = mb * nb;
+    const uint32_t kblocks = (K + K_ELEMS - 1) / K_ELEMS;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->tmem_full[b], 1);
+            mbar_init(&ctl->tmem_empty[b], 2 * EPI_THREADS);
+        }
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // both CTAs' barriers exist before anything in the pair signals them
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer (both CTAs) ----------------
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b128)) : "memory");
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            Work w;
+            for (uint32_t it = 0; ok && get_work(it, pair, pairs, mb, nb, tiles, split, w); ++it) {
+                const uint32_t half = w.width / 2;     // this CTA's rows of B
+                const CUtensorMap* mapb = half == 128u ? &map_b128 : (half == 64u ? &map_b64 : &map_b32);
+                const uint32_t bytes_pair = 2u * (A_BYTES + half * BK_BYTES);
+                const int a_row = (int)(w.m_blk * 2 * BM + rank * BM);
+                const int b_row = (int)(w.col0 + rank * half);
+                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, ctl, err, 1u)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(&ctl->full[stage], bytes_pair);
+                    const uint32_t bar = mapa(smem_u32(&ctl->full[stage]), 0);
+                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                    tma_load_2d_pair(sa, &map_a, (int)(kb * K_ELEMS), a_row, bar);
+                    tma_load_2d_pair(sa + A_BYTES, mapb, (int)(kb * K_ELEMS), b_row, bar);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---------------- MMA issuer (leader CTA only) ----------------
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            Work w;
+            for (uint32_t it = 0; ok && get_work(it, pair, pairs, mb, nb, tiles, split, w); ++it) {
+                const uint32_t idesc = make_idesc<IS_I8>(w.width);
+                if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, ctl, err, 2u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(&ctl->full[stage], phase, ctl, err, 3u)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(sa);
+                    const uint64_t db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < MMA_PER_BLOCK; ++kk)
+                        tc_mma_pair<IS_I8>(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    tc_commit_pair(&ctl->empty[stage], 3);     // both CTAs may refill this stage
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit_pair(&ctl->tmem_full[acc], 3);       // accumulator complete in both CTAs
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: warps 2..5 of both CTAs ----------------
+        const uint32_t quad = warp & 3u;
+        const uint32_t row_in_cta = quad * 32 + lane;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        Work w;
+        for (uint32_t it = 0; ok && get_work(it, pair, pairs, mb, nb, tiles, split, w); ++it) {
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(&ctl->tmem_full[acc], acc_phase, ctl, err, 4u));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t row = w.m_blk * 2 * BM + rank * BM + row_in_cta;
+            const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < w.width; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c, v);
+                tmem_ld_wait();
+                if (row < M) {
+                    const uint32_t col = w.col0 + c;
+                    if (IS_I8) {
+                        int32_t* dst = reinterpret_cast<int32_t*>(c_out) + (uint64_t)row * ldc + col;
+                        if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
+                            for (int q = 0; q < 32; ++q)
+                                if (col + q < N) dst[q] = (int32_t)v[q];
+                        }
+                    } else {
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + (uint64_t)row * ldc + col;
+                        if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]),
+                                                                             __uint_as_float(v[8 * q + 2 * e + 1]));
+                                    p[e] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(p[0], p[1], p[2], p[3]);
+                            }
+                        } else {
+                            for (int q = 0; q < 32; ++q)
+                                if (col + q < N) dst[q] = __float2bfloat16_rn(__uint_as_float(v[q]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_cluster(mapa(smem_u32(&ctl->tmem_empty[acc]), 0));   // the leader's barrier counts both CTAs
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    __syncwarp();
+    if (ctl->abort_flag) {
+        uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before();
+    // neither CTA frees TMEM or leaves while its peer can still signal or read it
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+}
+
+}  // namespace tc2
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn2 encode_fn2() {
+    static EncodeTiledFn2 fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn2)p;
+    }
+    return fn;
+}
+static catena_status_t make_map2(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k_elems, int elem_bytes,
+                                 uint32_t box_rows) {
+    EncodeTiledFn2 fn = encode_fn2();
+    if (!fn) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled is unavailable");
+    cuuint64_t dims[2] = {k_elems, rows};
+    cuuint64_t strides[1] = {k_elems * (uint64_t)elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(tc2::BK_BYTES / elem_bytes), box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled failed");
+    return CATENA_OK;
+}
+
+// Enqueues the CTA-pair GEMM.  `err_dev` is the device error word shared with the single-CTA kernel.
+catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                 int is_i8, int cta_limit, uint32_t* err_dev) {
+    const int eb = is_i8 ? 1 : 2;
+    CUtensorMap map_a, map_b128, map_b64, map_b32;
+    CATENA_TRY(make_map2(&map_a, a, m, k, eb, tc2::BM));
+    CATENA_TRY(make_map2(&map_b128, b, n, k, eb, 128));
+    CATENA_TRY(make_map2(&map_b64, b, n, k, eb, 64));
+    CATENA_TRY(make_map2(&map_b32, b, n, k, eb, 32));
+    if (is_i8)
+        CATENA_CUDA(cudaFuncSetAttribute(tc2::gemm_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES));
+    else
+        CATENA_CUDA(cudaFuncSetAttribute(tc2::gemm_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES));
+    const uint64_t tiles = ceil_div_u64(m, 2 * tc2::BM) * ceil_div_u64(n, tc2::BN);
+    const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+    uint64_t pairs = (uint64_t)(sms / 2);
+    if (cta_limit > 0 && pairs > (uint64_t)(cta_limit / 2 > 0 ? cta_limit / 2 : 1)) pairs = (uint64_t)(cta_limit / 2 > 0 ? cta_limit / 2 : 1);
+    if (tiles < pairs) pairs = tiles;
+    const uint64_t rem = tiles % pairs;
+    const uint32_t split = rem == 0 ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
+    const unsigned grid = (unsigned)(pairs * 2);
+    cudaStream_t st = tls().stream;
+    if (is_i8)
+        tc2::gemm_tc2_kernel<true><<<grid, tc2::NUM_THREADS, tc2::SMEM_BYTES, st>>>(map_a, map_b128, map_b64, map_b32, c, (uint32_t)m,
+                                                                                   (uint32_t)n, (uint32_t)k, ldc, split, err_dev);
+    else
+        tc2::gemm_tc2_kernel<false><<<grid, tc2::NUM_THREADS, tc2::SMEM_BYTES, st>>>(map_a, map_b128, map_b64, map_b32, c, (uint32_t)m,
+                                                                                    (uint32_t)n, (uint32_t)k, ldc, split, err_dev);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail_cuda(e, "gemm_tc2 launch");
+    return CATENA_OK;
+}
+
+}  // namespace catena

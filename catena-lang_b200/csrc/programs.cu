@@ -268,7 +268,12 @@ catena_status_t catena_b200_attn_decode_bf16_into(const void* q, const void* kc,
     return finish("attn_decode");
 }
 
-void catena_b200_debug_set_cta_limit(int limit) { gemm_tc_set_cta_limit(limit); }
+void catena_b200_debug_set_cta_limit(int limit) {
+    gemm_tc_set_cta_limit(limit);
+    attn_set_cluster_limit(limit > 0 ? (limit >= 8 ? limit / 8 : 1) : 0);
+}
+
+void catena_b200_debug_set_gemm_pair(int on) { gemm_tc_set_pair_mode(on); }
 
 catena_status_t catena_b200_check_device_errors(void) {
     CATENA_TRY(gemm_tc_check_errors());

@@ -203,6 +203,9 @@ catena_status_t catena_b200_sum_f32_noalloc(const void* in, uint64_t n, void* ou
 /* test hook: cap the persistent grid of the tensor-core GEMM (0 = one CTA per SM); results must not
  * change with it.  No counterpart in the reference. */
 void catena_b200_debug_set_cta_limit(int limit);
+/* test hook: 1 = run tensor-core GEMMs on the CTA-pair (cta_group::2) kernel, 0 = single-CTA kernel;
+ * both give bit-identical results.  No counterpart in the reference. */
+void catena_b200_debug_set_gemm_pair(int on);
 /* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry */
 catena_status_t catena_b200_check_device_errors(void);
 

@@ -298,6 +298,29 @@ def test_gemm_i8_bit_exact(rt, orc, m, n, k):
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 256), (200, 264, 72), (333, 1000, 200), (2048, 2304, 512),
+                                   (4096, 4096, 4096)])
+def test_gemm_pair_and_single_cta_kernels_agree_bitwise(rt, m, n, k):
+    """Two independent implementations (tcgen05 cta_group::2 on CTA pairs with 256-row tiles and a
+    6-stage ring; cta_group::1 with 128-row tiles and a 4-stage ring), different tile -> SM maps and
+    different widths for the units of the last round: the output bits must not depend on any of it."""
+    a, bt = bf16_inputs(7, m, n, k)
+    rng = np.random.default_rng(8)
+    k8 = max(16, k // 16 * 16)
+    ai = rng.integers(-128, 128, (m, k8), dtype=np.int8)
+    bi = rng.integers(-128, 128, (n, k8), dtype=np.int8)
+    out = {}
+    try:
+        for pair in (1, 0):
+            cb.lib().catena_b200_debug_set_gemm_pair(pair)
+            out[pair] = (run_gemm_bf16(rt, a, bt, m, n, k),
+                         rt.exec("gemm-i8-rc", [rt.mem_bytes(ai), rt.mem_bytes(bi), m, n, k8])[0].v.to_array(np.int32))
+    finally:
+        cb.lib().catena_b200_debug_set_gemm_pair(1)
+    assert np.array_equal(out[0][0], out[1][0])
+    assert np.array_equal(out[0][1], out[1][1])
+
+
 def test_gemm_i8_extremes(rt):
     m, n, k = 128, 256, 8192
     a = np.full((m, k), -128, np.int8)
@@ -345,6 +368,12 @@ def test_attn_decode_c3_partition_and_determinism(rt, orc):
     got = run_attn(rt, q, k, v, B, Hq, Hkv, L)
     again = run_attn(rt, q, k, v, B, Hq, Hkv, L)
     assert np.array_equal(got, again)
+    cb.lib().catena_b200_debug_set_cta_limit(40)              # 5 resident clusters instead of ~33
+    try:
+        few_clusters = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    finally:
+        cb.lib().catena_b200_debug_set_cta_limit(0)
+    assert np.array_equal(got, few_clusters)                  # the cluster count never enters the arithmetic
     units = list(range(0, B * Hq, 97))[:12]                   # oracle on a sample of (batch, head) rows
     for u in units:
         want, want_f32 = orc.attn_decode_bf16(q, k, v, B, Hq, Hkv, 128, L, np.float32(1.0 / math.sqrt(128.0)),
