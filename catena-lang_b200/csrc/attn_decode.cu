@@ -11,15 +11,19 @@
 //   unit   = (batch, kv-head) with its G = Hq/Hkv query heads, so K and V are read once per group;
 //   split  = the KV length is cut into kSplits = 8 contiguous chunks, one per CTA of a thread-block
 //            cluster; partial results are combined in ascending chunk order.
-// Execution: persistent clusters, each walking units first, first + #clusters, ...  A CTA streams
-// 64-position tiles of its chunk through a 4-stage TMA / mbarrier ring (128B-swizzled, no multicast)
-// and software-pipelines consecutive units so the cluster-wide exchanges never idle the stream:
-//   iteration i:  K tiles of unit i -> raw scores, chunk maxima          | barrier.cluster.arrive
-//                 V tiles of unit i-1 -> partial sum p*v                 | barrier.cluster.wait
-//                 global max of unit i over DSMEM, p = exp~(s - max) (bf16 hi + lo), chunk denominator
-//                 combine unit i-2 over DSMEM in ascending chunk order, divide, round to bf16, store
-// Buffers that peers read are multi-buffered (maxima x2, partial outputs and denominators x3) so a
-// slot is only rewritten after a later cluster barrier has proved every reader done.
+// Execution: persistent clusters, each walking units first, first + #clusters, ...  Per CTA:
+//   warp 4      producer: one 4-D `cp.async.bulk.tensor` (128B swizzle, no multicast) per 64-position
+//               tile into a ring of mbarrier-guarded stages, running ahead of the consumers;
+//   warps 0-3   consumers; consecutive units are software-pipelined so the cluster-wide exchanges
+//               never idle the stream:
+//     iteration i:  K tiles of unit i -> raw scores, chunk maxima pushed to the peers | barrier.cluster.arrive
+//                   V tiles of unit i-1 -> partial sum p*v, pushed to the owning peer  | barrier.cluster.wait
+//                   global max of unit i, p = exp~(s - max) (bf16 hi + lo), chunk denominator pushed
+//                   combine unit i-2 in ascending chunk order, divide, round to bf16, store
+// Everything a peer needs is PUSHED into its shared memory (distributed shared memory stores) before
+// the barrier, so after the barrier all reads are local.  Pushed buffers are multi-buffered (maxima
+// x2, partial outputs and denominators x3): a slot is rewritten only after a later cluster barrier
+// has proved every reader done.
 // Math runs on `mma.sync.m16n8k16` bf16 (positions or head-dim on M, the <= 8 query heads on N);
 // FLOPs are irrelevant here (4 FLOP per KV byte); the kernel is sized for HBM.
 #include <cooperative_groups.h>
@@ -42,14 +46,16 @@ constexpr int kTile = 64;                    // positions per ring stage
 #endif
 constexpr int kStages = CATENA_ATTN_STAGES;
 constexpr int kSplits = 8;                   // cluster size = KV chunks per unit
-constexpr int kStageBytes = kTile * kD * 2;  // 16 KiB (two 8 KiB halves of 64 d each)
+constexpr int kStageBytes = kTile * kD * 2;  // 16 KiB: [d-half 2][position 64][128 B]
 constexpr int kHalfBytes = kTile * 128;
-constexpr int kThreads = 128;
+constexpr int kConsumers = 128;              // warps 0..3
+constexpr int kThreads = 160;                // + producer warp 4
 constexpr int kMaxG = 8;
 constexpr uint64_t kWaitNs = 1000000000ull;
 
 struct __align__(16) Control {
     uint64_t full[kStages];
+    uint64_t empty[kStages];
     float lmax_all[2][kSplits][kMaxG];   // chunk maxima of every rank, written by the peers (push)
     float den_all[3][kSplits][kMaxG];    // chunk denominators of every rank, written by the peers
     float gmax[kMaxG];
@@ -74,6 +80,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Bounded wait: false when it expired (about one second) or another thread already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Control* ctl, uint32_t* err) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = globaltimer_ns();
@@ -90,10 +97,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Contro
         }
     }
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -115,6 +125,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 // iteration; writes made before `arrive` are visible to peers after their `wait`.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// barrier among the four consumer warps only (the producer warp never joins it)
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // byte offset inside a stage of the 16-byte chunk `chunk` (0..15 over d) of position row `row`
 __device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t chunk) {
@@ -122,7 +134,7 @@ __device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t chunk) {
     return half * kHalfBytes + row * 128u + ((c ^ (row & 7u)) << 4);
 }
 
-// grid.x = kSplits * #clusters; cluster (kSplits,1,1); block 128 threads.
+// grid.x = kSplits * #clusters; cluster (kSplits,1,1); block 160 threads.
 __global__ void __launch_bounds__(kThreads)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ o, uint32_t L, uint32_t G,
@@ -137,7 +149,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     __nv_bfloat16* p_lo = p_hi + 2 * gc;                                              // [2][G][chunk]
     // partial outputs of every rank for THIS CTA's slice of the (head, d) outputs, written by the peers
     float* o_gather = reinterpret_cast<float*>(p_lo + 2 * gc);                        // [3][kSplits][G*16]
-    Control* ctl = reinterpret_cast<Control*>(o_gather + 3 * (size_t)G * kD);
+    float* o_stage = o_gather + 3 * (size_t)G * kD;                                  // [G][128] local staging
+    Control* ctl = reinterpret_cast<Control*>(o_stage + (size_t)G * kD);
     const uint32_t per_rank = G * kD / kSplits;                                       // outputs combined per CTA
 
     cg::cluster_group cluster = cg::this_cluster();
@@ -150,239 +163,274 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     const uint32_t pos_begin = rank * chunk;
     const uint32_t valid = pos_begin < L ? min(chunk, L - pos_begin) : 0u;   // positions of this CTA per unit
     const uint32_t T = (valid + kTile - 1) / kTile;                          // K tiles (= V tiles) per unit
-    const uint32_t total = 2 * n * T;
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s)
+        for (int s = 0; s < kStages; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&ctl->full[s])), "r"(1) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&ctl->empty[s])), "r"(4) : "memory");
+        }
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    // The tile stream of this CTA, in groups of T tiles:  K(0) | K(1) V(0) | K(2) V(1) | ... | V(n-1)
-    auto issue = [&](uint32_t g) {
-        const uint32_t c = g / T, t = g - c * T;
-        bool is_v;
-        uint32_t j;
-        if (c == 0) { is_v = false; j = 0; }
-        else if (c == 2 * n - 1) { is_v = true; j = n - 1; }
-        else if (c & 1u) { is_v = false; j = (c + 1) >> 1; }
-        else { is_v = true; j = (c >> 1) - 1; }
-        const uint32_t st = g % kStages;
-        const CUtensorMap* map = is_v ? &map_v : &map_k;
-        const int pos = (int)(pos_begin + t * kTile);
-        const int unit = (int)(first + j * nclusters);
-        uint64_t* bar = &ctl->full[st];
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"((uint32_t)kStageBytes)
-                     : "memory");
-        const uint32_t dst = smem_u32(ring + st * kStageBytes);
-        tma_load_3d(dst, map, 0, pos, unit, bar);
-        tma_load_3d(dst + kHalfBytes, map, 64, pos, unit, bar);
-    };
-    if (tid == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-        for (uint32_t g = 0; g < total && g < (uint32_t)kStages; ++g) issue(g);
-    }
-
-    bool aborted = false;
-    uint32_t g = 0;   // tiles consumed so far
-    // Waits for tile g, makes the decision block-uniform, and refills the stage of tile g-1
-    // (every warp finished reading it before reaching this barrier).
-    auto acquire = [&](uint32_t gg) -> bool {
-        bool ok = mbar_wait(&ctl->full[gg % kStages], (gg / kStages) & 1u, ctl, err);
-        if (__syncthreads_or(ok ? 0 : 1)) return false;
-        if (tid == 0 && gg >= 1 && gg - 1 + kStages < total) issue(gg - 1 + kStages);
-        return true;
-    };
-
-    // Q of unit j as B fragments of S^T = K * Q^T: lane holds Q[head = lane/4][d = 16*ks + 2*(lane%4) + {0,1}], d + 8
-    auto load_q = [&](uint32_t j, uint32_t (&dst)[8][2]) {
-        const uint32_t unit = first + j * nclusters;
-        const uint32_t head = lane >> 2;
-        const __nv_bfloat16* qrow = q + ((size_t)unit * G + head) * kD;   // (b*Hq + kvh*G + head) = unit*G + head
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            uint32_t d = ks * 16 + (lane & 3u) * 2;
-            dst[ks][0] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d) : 0u;
-            dst[ks][1] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d + 8) : 0u;
-        }
-    };
-    uint32_t qb[8][2], qn[8][2];
-    if (n > 0) load_q(0, qn);
-
-    for (uint32_t i = 0; i <= n + 1; ++i) {
-        // ---------------- K tiles of unit i: raw scores ----------------
-        if (i < n) {
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) { qb[ks][0] = qn[ks][0]; qb[ks][1] = qn[ks][1]; }
-            if (i + 1 < n) load_q(i + 1, qn);     // lands while this unit streams
-            float* sc = scores + (size_t)(i & 1u) * gc;
-            for (uint32_t t = 0; t < T && !aborted; ++t, ++g) {
-                if (!acquire(g)) { aborted = true; break; }
-                const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
-                // two accumulation chains (even / odd 16-wide d slices) so consecutive MMAs do not wait on
-                // each other, joined by one fp32 add per score
-                float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint32_t row = warp * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8;
-#pragma unroll
-                for (int ks = 0; ks < 8; ks += 2) {
-                    uint32_t a[4], a2[4];
-                    ldsm_x4(base + tile_off(row, ks * 2 + (lane >> 4)), a);
-                    ldsm_x4(base + tile_off(row, (ks + 1) * 2 + (lane >> 4)), a2);
-                    mma_bf16(c, a, qb[ks][0], qb[ks][1]);
-                    mma_bf16(c2, a2, qb[ks + 1][0], qb[ks + 1][1]);
-                }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) c[e] = cmath::add(c[e], c2[e]);
-                // C fragment: rows (lane/4, lane/4+8) of this warp's 16 positions, heads 2*(lane%4)+{0,1}
-                const uint32_t p0 = t * kTile + warp * 16 + (lane >> 2);
-                const uint32_t h0 = (lane & 3u) * 2;
-                if (h0 < G) {
-                    sc[(size_t)h0 * chunk + p0] = cmath::mul(c[0], scale);
-                    sc[(size_t)h0 * chunk + p0 + 8] = cmath::mul(c[2], scale);
-                }
-                if (h0 + 1 < G) {
-                    sc[(size_t)(h0 + 1) * chunk + p0] = cmath::mul(c[1], scale);
-                    sc[(size_t)(h0 + 1) * chunk + p0 + 8] = cmath::mul(c[3], scale);
-                }
+    if (warp == 4) {
+        // =============================== producer warp ===============================
+        // Tile stream, in groups of T tiles:  K(0) | K(1) V(0) | K(2) V(1) | ... | V(n-1)   (consumption order).
+        // Cluster-barrier schedule: arrive_i as early as possible, wait_i only after K(i+1) has been issued, so the
+        // ring keeps filling across the exchange and no consumer ever waits for an arrival the producer owes.
+        uint32_t g = 0;
+        bool ok = true;
+        auto issue_group = [&](bool is_v, uint32_t j) {
+            if (lane != 0) return;
+            const CUtensorMap* map = is_v ? &map_v : &map_k;
+            const int unit = (int)(first + j * nclusters);
+            for (uint32_t t = 0; t < T; ++t, ++g) {
+                if (!ok) continue;
+                const uint32_t st = g % kStages;
+                if (!mbar_wait(&ctl->empty[st], ((g / kStages) & 1u) ^ 1u, ctl, err)) { ok = false; continue; }
+                uint64_t* bar = &ctl->full[st];
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                             "r"((uint32_t)kStageBytes)
+                             : "memory");
+                tma_load_4d(smem_u32(ring + st * kStageBytes), map, 0, (int)(pos_begin + t * kTile), 0, unit, bar);
             }
-            __syncthreads();
-            // chunk maxima (order-free on finite data)
-            for (uint32_t h = warp; h < G; h += 4) {
-                float m = __uint_as_float(0xFF800000u);
-                if (!aborted)
-                    for (uint32_t p = lane; p < valid; p += 32) m = fmaxf(m, sc[(size_t)h * chunk + p]);
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
-                // push: lane r stores this chunk's maximum into rank r's table, so after the barrier every
-                // CTA finds all eight maxima in its own shared memory
-                if (lane < (uint32_t)kSplits) *cluster.map_shared_rank(&ctl->lmax_all[i & 1u][rank][h], lane) = m;
-            }
+        };
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
         }
-        cluster_arrive();
+        cluster_arrive();                                    // arrive_0
+        if (n > 0) issue_group(false, 0);
+        for (uint32_t i = 0; i <= n + 1; ++i) {
+            if (i >= 1 && i <= n) issue_group(true, i - 1);
+            if (i + 1 < n) issue_group(false, i + 1);
+            __syncwarp();
+            cluster_wait();                                  // wait_i
+            if (i < n + 1) cluster_arrive();                 // arrive_{i+1}
+        }
+    } else {
+        // =============================== consumer warps 0..3 ===============================
+        bool aborted = false;
+        uint32_t g = 0;   // tiles consumed so far
+        // warp-uniform: wait for tile gg to land
+        auto acquire = [&](uint32_t gg) -> bool {
+            bool ok = mbar_wait(&ctl->full[gg % kStages], (gg / kStages) & 1u, ctl, err);
+            return __all_sync(0xFFFFFFFFu, ok);
+        };
+        auto release = [&](uint32_t gg) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->empty[gg % kStages]);
+        };
 
-        // ---------------- V tiles of unit i-1: O^T = V^T * P^T over this chunk ----------------
-        if (i >= 1 && i <= n) {
-            const uint32_t j = i - 1;
-            const __nv_bfloat16* ph = p_hi + (size_t)(j & 1u) * gc;
-            const __nv_bfloat16* pl = p_lo + (size_t)(j & 1u) * gc;
-            // separate chains for the hi and lo halves of p (4 independent MMA chains per warp)
-            float acc[2][4], acc_lo[2][4];
+        // Q of unit j as B fragments of S^T = K * Q^T: lane holds Q[head = lane/4][d = 16*ks + 2*(lane%4) + {0,1}], d + 8
+        auto load_q = [&](uint32_t j, uint32_t (&dst)[8][2]) {
+            const uint32_t unit = first + j * nclusters;
+            const uint32_t head = lane >> 2;
+            const __nv_bfloat16* qrow = q + ((size_t)unit * G + head) * kD;   // (b*Hq + kvh*G + head) = unit*G + head
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t d = ks * 16 + (lane & 3u) * 2;
+                dst[ks][0] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d) : 0u;
+                dst[ks][1] = head < G ? *reinterpret_cast<const uint32_t*>(qrow + d + 8) : 0u;
+            }
+        };
+        uint32_t qb[8][2], qn[8][2];
+        if (n > 0) load_q(0, qn);
+
+        for (uint32_t i = 0; i <= n + 1; ++i) {
+            // ---------------- K tiles of unit i: raw scores ----------------
+            if (i < n) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { acc[mt][e] = 0.0f; acc_lo[mt][e] = 0.0f; }
-            for (uint32_t t = 0; t < T && !aborted; ++t, ++g) {
-                if (!acquire(g)) { aborted = true; break; }
-                const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
-                const uint32_t tile_pos = t * kTile;
-                const uint32_t head = lane >> 2;
+                for (int ks = 0; ks < 8; ++ks) { qb[ks][0] = qn[ks][0]; qb[ks][1] = qn[ks][1]; }
+                if (i + 1 < n) load_q(i + 1, qn);     // lands while this unit streams
+                float* sc = scores + (size_t)(i & 1u) * gc;
+                for (uint32_t t = 0; t < T; ++t, ++g) {
+                    if (aborted || !acquire(g)) { aborted = true; continue; }
+                    const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
+                    // The legacy MMA has a long result latency here, so the eight 16-wide d slices go to eight
+                    // independent accumulators (no MMA waits on another) and are joined by a fixed fp32 tree.
+                    float cs[8][4];
+                    const uint32_t row = warp * 16 + (lane & 7u) + ((lane >> 3) & 1u) * 8;
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    uint32_t bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;
-                    if (head < G) {
-                        size_t off = (size_t)head * chunk + tile_pos + ks * 16 + (lane & 3u) * 2;
-                        bh0 = *reinterpret_cast<const uint32_t*>(ph + off);
-                        bh1 = *reinterpret_cast<const uint32_t*>(ph + off + 8);
-                        bl0 = *reinterpret_cast<const uint32_t*>(pl + off);
-                        bl1 = *reinterpret_cast<const uint32_t*>(pl + off + 8);
-                    }
-                    const uint32_t prow = ks * 16 + (lane & 7u) + (lane >> 4) * 8;
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
+                    for (int ks = 0; ks < 8; ++ks) {
                         uint32_t a[4];
-                        ldsm_x4_trans(base + tile_off(prow, (warp * 2 + mt) * 2 + ((lane >> 3) & 1u)), a);
-                        mma_bf16(acc[mt], a, bh0, bh1);
-                        mma_bf16(acc_lo[mt], a, bl0, bl1);
+                        ldsm_x4(base + tile_off(row, ks * 2 + (lane >> 4)), a);
+                        cs[ks][0] = cs[ks][1] = cs[ks][2] = cs[ks][3] = 0.0f;
+                        mma_bf16(cs[ks], a, qb[ks][0], qb[ks][1]);
+                    }
+                    release(g);
+                    float c[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        c[e] = cmath::add(cmath::add(cmath::add(cs[0][e], cs[1][e]), cmath::add(cs[2][e], cs[3][e])),
+                                          cmath::add(cmath::add(cs[4][e], cs[5][e]), cmath::add(cs[6][e], cs[7][e])));
+                    // C fragment: rows (lane/4, lane/4+8) of this warp's 16 positions, heads 2*(lane%4)+{0,1}
+                    const uint32_t p0 = t * kTile + warp * 16 + (lane >> 2);
+                    const uint32_t h0 = (lane & 3u) * 2;
+                    if (h0 < G) {
+                        sc[(size_t)h0 * chunk + p0] = cmath::mul(c[0], scale);
+                        sc[(size_t)h0 * chunk + p0 + 8] = cmath::mul(c[2], scale);
+                    }
+                    if (h0 + 1 < G) {
+                        sc[(size_t)(h0 + 1) * chunk + p0] = cmath::mul(c[1], scale);
+                        sc[(size_t)(h0 + 1) * chunk + p0 + 8] = cmath::mul(c[3], scale);
                     }
                 }
+                consumer_sync();
+                // chunk maxima (order-free on finite data)
+                for (uint32_t h = warp; h < G; h += 4) {
+                    float m = __uint_as_float(0xFF800000u);
+                    if (!ctl->abort_flag)
+                        for (uint32_t p = lane; p < valid; p += 32) m = fmaxf(m, sc[(size_t)h * chunk + p]);
+#pragma unroll
+                    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+                    // push: lane r stores this chunk's maximum into rank r's table, so after the barrier
+                    // every CTA finds all eight maxima in its own shared memory
+                    if (lane < (uint32_t)kSplits) *cluster.map_shared_rank(&ctl->lmax_all[i & 1u][rank][h], lane) = m;
+                }
             }
-            // partial outputs: C fragment rows d = 16*mtile + lane/4 (+8), heads 2*(lane%4)+{0,1}.
-            // push: output (h, d) belongs to the slice of rank (h*128 + d) / per_rank, which will combine it
-            float* og = o_gather + ((size_t)(j % 3u) * kSplits + rank) * per_rank;
-            const uint32_t h0 = (lane & 3u) * 2;
+            __syncwarp();
+            cluster_arrive();
+
+            // ---------------- V tiles of unit i-1: O^T = V^T * P^T over this chunk ----------------
+            if (i >= 1 && i <= n) {
+                const uint32_t j = i - 1;
+                const __nv_bfloat16* ph = p_hi + (size_t)(j & 1u) * gc;
+                const __nv_bfloat16* pl = p_lo + (size_t)(j & 1u) * gc;
+                // one accumulator per (d tile, 16-position slice, hi/lo half of p): within a tile no MMA waits on
+                // another; each accumulator only chains from tile to tile.  Joined by a fixed fp32 tree at the end.
+                float acc[2][4][2][4];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                const uint32_t d0 = (warp * 2 + mt) * 16 + (lane >> 2);
+                for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t h = h0 + (e & 1), d = d0 + (e >> 1) * 8;
-                    if (h < G) {
-                        const uint32_t idx = h * kD + d;
-                        const uint32_t dst_rank = idx / per_rank;
-                        *cluster.map_shared_rank(og + (idx - dst_rank * per_rank), dst_rank) =
-                            cmath::add(acc[mt][e], acc_lo[mt][e]);
+                    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) { acc[mt][ks][0][e] = 0.0f; acc[mt][ks][1][e] = 0.0f; }
+                for (uint32_t t = 0; t < T; ++t, ++g) {
+                    if (aborted || !acquire(g)) { aborted = true; continue; }
+                    const uint32_t base = smem_u32(ring + (g % kStages) * kStageBytes);
+                    const uint32_t tile_pos = t * kTile;
+                    const uint32_t head = lane >> 2;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        uint32_t bh0 = 0, bh1 = 0, bl0 = 0, bl1 = 0;
+                        if (head < G) {
+                            size_t off = (size_t)head * chunk + tile_pos + ks * 16 + (lane & 3u) * 2;
+                            bh0 = *reinterpret_cast<const uint32_t*>(ph + off);
+                            bh1 = *reinterpret_cast<const uint32_t*>(ph + off + 8);
+                            bl0 = *reinterpret_cast<const uint32_t*>(pl + off);
+                            bl1 = *reinterpret_cast<const uint32_t*>(pl + off + 8);
+                        }
+                        const uint32_t prow = ks * 16 + (lane & 7u) + (lane >> 4) * 8;
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            uint32_t a[4];
+                            ldsm_x4_trans(base + tile_off(prow, (warp * 2 + mt) * 2 + ((lane >> 3) & 1u)), a);
+                            mma_bf16(acc[mt][ks][0], a, bh0, bh1);
+                            mma_bf16(acc[mt][ks][1], a, bl0, bl1);
+                        }
+                    }
+                    release(g);
+                }
+                // partial outputs: C fragment rows d = 16*mtile + lane/4 (+8), heads 2*(lane%4)+{0,1},
+                // staged as [head][d] in local shared memory ...
+                const uint32_t h0 = (lane & 3u) * 2;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    const uint32_t d0 = (warp * 2 + mt) * 16 + (lane >> 2);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t h = h0 + (e & 1), d = d0 + (e >> 1) * 8;
+                        if (h < G) {
+                            const float hi = cmath::add(cmath::add(acc[mt][0][0][e], acc[mt][1][0][e]),
+                                                        cmath::add(acc[mt][2][0][e], acc[mt][3][0][e]));
+                            const float lo = cmath::add(cmath::add(acc[mt][0][1][e], acc[mt][1][1][e]),
+                                                        cmath::add(acc[mt][2][1][e], acc[mt][3][1][e]));
+                            o_stage[h * kD + d] = cmath::add(hi, lo);
+                        }
                     }
                 }
-            }
-        }
-        cluster_wait();
-
-        // ---------------- unit i: global max over the cluster, probabilities, chunk denominator ----------------
-        if (i < n) {
-            if (tid < G) {
-                float m = __uint_as_float(0xFF800000u);
-#pragma unroll
-                for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) m = fmaxf(m, ctl->lmax_all[i & 1u][r][tid]);
-                ctl->gmax[tid] = m;
-            }
-            __syncthreads();
-            const float* sc = scores + (size_t)(i & 1u) * gc;
-            __nv_bfloat16* ph = p_hi + (size_t)(i & 1u) * gc;
-            __nv_bfloat16* pl = p_lo + (size_t)(i & 1u) * gc;
-            // fixed order: thread t sums positions t, t+128, ... ascending; xor butterfly per warp; warps 0..3 ascending
-            for (uint32_t h = 0; h < G; ++h) {
-                const float m = ctl->gmax[h];
-                float acc = 0.0f;
-                for (uint32_t p = tid; p < chunk; p += kThreads) {
-                    float pv = 0.0f;
-                    if (p < valid && !aborted) pv = cmath::exp_approx(cmath::sub(sc[(size_t)h * chunk + p], m));
-                    __nv_bfloat16 hi = __float2bfloat16_rn(pv);
-                    __nv_bfloat16 lo = __float2bfloat16_rn(cmath::sub(pv, __bfloat162float(hi)));
-                    ph[(size_t)h * chunk + p] = hi;
-                    pl[(size_t)h * chunk + p] = lo;
-                    acc = cmath::add(acc, pv);
+                consumer_sync();
+                // ... then pushed 16 bytes at a time: outputs [idx, idx+4) belong to the slice of rank
+                // idx / per_rank, which will combine them (per_rank is a multiple of 4)
+                for (uint32_t v4 = tid; v4 < G * (kD / 4); v4 += kConsumers) {
+                    const uint32_t idx = v4 * 4;
+                    const uint32_t dst_rank = idx / per_rank;
+                    float* og = o_gather + ((size_t)(j % 3u) * kSplits + rank) * per_rank + (idx - dst_rank * per_rank);
+                    *reinterpret_cast<float4*>(cluster.map_shared_rank(og, dst_rank)) =
+                        *reinterpret_cast<const float4*>(o_stage + idx);
                 }
-#pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) acc = cmath::add(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, off));
-                if (lane == 0) ctl->warp_part[warp][h] = acc;
             }
-            __syncthreads();
-            if (tid < G) {
-                float d = ctl->warp_part[0][tid];
-                for (int w = 1; w < 4; ++w) d = cmath::add(d, ctl->warp_part[w][tid]);
-#pragma unroll
-                for (uint32_t r = 0; r < (uint32_t)kSplits; ++r)
-                    *cluster.map_shared_rank(&ctl->den_all[i % 3u][rank][tid], r) = d;
-            }
-        }
+            __syncwarp();
+            cluster_wait();
 
-        // ---------------- unit i-2: combine in ascending chunk order, one slice of the outputs per CTA ----------------
-        if (i >= 2) {
-            const uint32_t j = i - 2;
-            if (tid < per_rank) {   // per_rank = G*16 <= 128
-                const uint32_t idx = rank * per_rank + tid;
-                const uint32_t h = idx / kD, d = idx % kD;
-                const float* og = o_gather + (size_t)(j % 3u) * kSplits * per_rank + tid;
-                float num = 0.0f, den = 0.0f;
+            // ---------------- unit i: global max over the cluster, probabilities, chunk denominator ----------------
+            if (i < n) {
+                if (tid < G) {
+                    float m = __uint_as_float(0xFF800000u);
 #pragma unroll
-                for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) {
-                    num = cmath::add(num, og[r * per_rank]);
-                    den = cmath::add(den, ctl->den_all[j % 3u][r][h]);
+                    for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) m = fmaxf(m, ctl->lmax_all[i & 1u][r][tid]);
+                    ctl->gmax[tid] = m;
                 }
-                const uint32_t unit = first + j * nclusters;
-                if (!ctl->abort_flag)
-                    o[((size_t)unit * G + h) * kD + d] = __float2bfloat16_rn(cmath::div(num, den));
+                consumer_sync();
+                const float* sc = scores + (size_t)(i & 1u) * gc;
+                __nv_bfloat16* ph = p_hi + (size_t)(i & 1u) * gc;
+                __nv_bfloat16* pl = p_lo + (size_t)(i & 1u) * gc;
+                const bool dead = ctl->abort_flag != 0;
+                // fixed order: thread t sums positions t, t+128, ... ascending; xor butterfly per warp; warps 0..3 ascending
+                for (uint32_t h = 0; h < G; ++h) {
+                    const float m = ctl->gmax[h];
+                    float acc = 0.0f;
+                    for (uint32_t p = tid; p < chunk; p += kConsumers) {
+                        float pv = 0.0f;
+                        if (p < valid && !dead) pv = cmath::exp_approx(cmath::sub(sc[(size_t)h * chunk + p], m));
+                        __nv_bfloat16 hi = __float2bfloat16_rn(pv);
+                        __nv_bfloat16 lo = __float2bfloat16_rn(cmath::sub(pv, __bfloat162float(hi)));
+                        ph[(size_t)h * chunk + p] = hi;
+                        pl[(size_t)h * chunk + p] = lo;
+                        acc = cmath::add(acc, pv);
+                    }
+#pragma unroll
+                    for (int off = 16; off >= 1; off >>= 1) acc = cmath::add(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, off));
+                    if (lane == 0) ctl->warp_part[warp][h] = acc;
+                }
+                consumer_sync();
+                if (tid < G) {
+                    float d = ctl->warp_part[0][tid];
+                    for (int w = 1; w < 4; ++w) d = cmath::add(d, ctl->warp_part[w][tid]);
+#pragma unroll
+                    for (uint32_t r = 0; r < (uint32_t)kSplits; ++r)
+                        *cluster.map_shared_rank(&ctl->den_all[i % 3u][rank][tid], r) = d;
+                }
+            }
+
+            // ---------------- unit i-2: combine in ascending chunk order, one slice of the outputs per CTA ----------------
+            if (i >= 2) {
+                const uint32_t j = i - 2;
+                if (tid < per_rank) {   // per_rank = G*16 <= 128
+                    const uint32_t idx = rank * per_rank + tid;
+                    const uint32_t h = idx / kD, d = idx % kD;
+                    const float* og = o_gather + (size_t)(j % 3u) * kSplits * per_rank + tid;
+                    float num = 0.0f, den = 0.0f;
+#pragma unroll
+                    for (uint32_t r = 0; r < (uint32_t)kSplits; ++r) {
+                        num = cmath::add(num, og[r * per_rank]);
+                        den = cmath::add(den, ctl->den_all[j % 3u][r][h]);
+                    }
+                    const uint32_t unit = first + j * nclusters;
+                    if (!ctl->abort_flag)
+                        o[((size_t)unit * G + h) * kD + d] = __float2bfloat16_rn(cmath::div(num, den));
+                }
             }
         }
     }
+    __syncwarp();
     if (ctl->abort_flag) {
         uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
-    // nobody leaves while peers may still read its shared memory
+    // nobody leaves while peers may still write into its shared memory
     cluster_arrive();
     cluster_wait();
 }
@@ -404,16 +452,17 @@ static EncodeTiledFn attn_encode_fn() {
     return fn;
 }
 
-// KV cache [units, L, 128] bf16 as a 3-D tensor: box = 64 d x 64 positions x 1 unit, 128B swizzle;
+// KV cache [units, L, 128] bf16 viewed as a 4-D tensor (64 d, L positions, 2 d-halves, units) so that one
+// copy of box 64 x 64 x 2 x 1 brings a whole 64-position tile as [d-half][position][128 B], 128B-swizzled;
 // positions past L read as zero, so a ragged last tile never touches the next unit's rows.
 static catena_status_t make_kv_map(CUtensorMap* map, const void* base, uint64_t units, uint64_t L) {
     EncodeTiledFn fn = attn_encode_fn();
     if (!fn) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled is unavailable");
-    cuuint64_t dims[3] = {(cuuint64_t)attn::kD, L, units};
-    cuuint64_t strides[2] = {(cuuint64_t)attn::kD * 2, L * (cuuint64_t)attn::kD * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)attn::kTile, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+    cuuint64_t dims[4] = {64, L, 2, units};
+    cuuint64_t strides[3] = {(cuuint64_t)attn::kD * 2, 128, L * (cuuint64_t)attn::kD * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)attn::kTile, 2, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled (kv cache) failed");
@@ -432,7 +481,7 @@ static uint32_t chunk_for(uint64_t L) {
 }
 static size_t attn_smem_bytes(uint32_t G, uint32_t chunk) {
     return 1024 + (size_t)attn::kStages * attn::kStageBytes + 2 * (size_t)G * chunk * (4 + 2 + 2) +
-           3 * (size_t)G * attn::kD * 4 + sizeof(attn::Control) + 16;
+           4 * (size_t)G * attn::kD * 4 + sizeof(attn::Control) + 16;
 }
 
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch, uint64_t hq,

@@ -24,6 +24,8 @@ CM_HD float mul(float a, float b) { return __fmul_rn(a, b); }
 CM_HD float add(float a, float b) { return __fadd_rn(a, b); }
 CM_HD float sub(float a, float b) { return __fsub_rn(a, b); }
 CM_HD float div(float a, float b) { return __fdiv_rn(a, b); }
+// 1.0f / x: the correctly rounded reciprocal IS the IEEE quotient of 1 and x, at a fraction of the cost
+CM_HD float recip(float x) { return __frcp_rn(x); }
 CM_HD float from_bits(uint32_t u) { return __uint_as_float(u); }
 CM_HD uint32_t to_bits(float f) { return __float_as_uint(f); }
 CM_HD uint32_t round_to_u32(float x) { return __float2uint_rn(x); }   // (uint32_t)nearbyintf(x), gpu.rs:642-655
@@ -34,6 +36,7 @@ CM_HD float mul(float a, float b) { return a * b; }
 CM_HD float add(float a, float b) { return a + b; }
 CM_HD float sub(float a, float b) { return a - b; }
 CM_HD float div(float a, float b) { return a / b; }
+CM_HD float recip(float x) { return 1.0f / x; }
 CM_HD float from_bits(uint32_t u) { union { uint32_t u; float f; } v; v.u = u; return v.f; }
 CM_HD uint32_t to_bits(float f) { union { uint32_t u; float f; } v; v.f = f; return v.u; }
 CM_HD uint32_t round_to_u32(float x) { return (uint32_t)nearbyintf(x); }
@@ -103,7 +106,7 @@ CM_HD float exp_nonneg(float x) {
 CM_HD float exp_approx(float x) {
     bool neg = x < 0.0f;
     float base = exp_nonneg(neg ? -x : x);
-    return neg ? div(1.0f, base) : base;
+    return neg ? recip(base) : base;
 }
 
 // math.hex:202-231
@@ -120,7 +123,7 @@ CM_HD float sqrt_newton(float x) {
 }
 
 // nn.hex:2-56
-CM_HD float sigmoid(float x) { return div(1.0f, add(1.0f, exp_approx(-x))); }
+CM_HD float sigmoid(float x) { return recip(add(1.0f, exp_approx(-x))); }
 CM_HD float silu(float x) { return mul(x, sigmoid(x)); }
 CM_HD float tanh_approx(float x) { return sub(mul(sigmoid(mul(x, 2.0f)), 2.0f), 1.0f); }
 CM_HD float gelu_approx(float x) {
