@@ -98,7 +98,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Contro
     }
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+#ifdef CATENA_ATTN_RELAXED_ARRIVE
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+#else
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+#endif
 }
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
     asm volatile(
