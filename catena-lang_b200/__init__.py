@@ -116,6 +116,8 @@ def lib():
     proto("catena_b200_debug_set_cta_limit", None, [C.c_int])
     proto("catena_b200_sum_f32_noalloc", st, [vp, u64, vp])
     proto("catena_b200_debug_set_gemm_pair", None, [C.c_int])
+    proto("catena_b200_debug_set_attn_tc", None, [C.c_int])
+    proto("catena_b200_debug_attn_last_launch", None, [C.POINTER(C.c_uint32)])
     _lib = L
     return L
 

@@ -29,6 +29,7 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "catena_math.cuh"
 #include "common.cuh"
@@ -52,6 +53,9 @@ constexpr int kConsumers = 128;              // warps 0..3
 constexpr int kThreads = 160;                // + producer warp 4
 constexpr int kMaxG = 8;
 constexpr uint64_t kWaitNs = 1000000000ull;
+// a waiting thread may be suspended by the hardware for up to this long (it is woken when the phase completes):
+// without the hint the producer / issuer threads spin and take issue slots from the warps doing the work
+constexpr uint32_t kSuspendHintNs = 20000;
 
 struct __align__(16) Control {
     uint64_t full[kStages];
@@ -73,10 +77,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
@@ -478,6 +482,43 @@ static thread_local uint32_t* g_attn_err_host[16] = {nullptr};
 // Test hook shared with the GEMM: caps the number of resident clusters (0 = as many as fit).
 static int g_attn_cluster_limit = 0;
 void attn_set_cluster_limit(int limit) { g_attn_cluster_limit = limit > 0 ? limit : 0; }
+// Geometry of this thread's last decode launch: {kernel (0 mma.sync, 1 tcgen05), clusters that fit, clusters launched,
+// dynamic shared memory per CTA}.
+thread_local uint32_t g_attn_last_launch[4] = {0, 0, 0, 0};
+void attn_last_launch(uint32_t out[4]) { for (int i = 0; i < 4; ++i) out[i] = g_attn_last_launch[i]; }
+
+// Kernel selection: the tcgen05 kernel (attn_decode_tc.cu) wherever it supports the problem, else the mma.sync
+// kernel in this file.  CATENA_B200_ATTN_TC=0 (read once) or the test hook forces the mma.sync kernel; both
+// implement the same semantics.
+static int g_attn_tc_mode = -1;
+static bool attn_tc_mode() {
+    if (g_attn_tc_mode < 0) {
+        const char* e = getenv("CATENA_B200_ATTN_TC");
+        g_attn_tc_mode = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_attn_tc_mode == 1;
+}
+void attn_set_tc_mode(int on) { g_attn_tc_mode = on ? 1 : 0; }
+bool attn_tc_supports(uint32_t G, uint64_t kv_len);
+void attn_tc_reset_exchange();
+catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
+                                       uint64_t kv_len, uint64_t unit0, uint64_t unit1, int cluster_limit, uint32_t* err_dev);
+
+// After enqueuing: in blocking mode wait and turn a device-side bounded-wait expiry into a status.
+static catena_status_t attn_finish_launch(int dev) {
+    if (tls().blocking) {
+        cudaStream_t st = tls().stream;
+        CATENA_CUDA(cudaMemcpyAsync(g_attn_err_host[dev], g_attn_err_dev[dev], sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+        CATENA_CUDA(cudaStreamSynchronize(st));
+        if (*g_attn_err_host[dev] != 0) {
+            *g_attn_err_host[dev] = 0;
+            cudaMemsetAsync(g_attn_err_dev[dev], 0, sizeof(uint32_t), st);
+            attn_tc_reset_exchange();
+            return fail(CATENA_E_TIMEOUT, "attn_decode: bounded wait expired");
+        }
+    }
+    return CATENA_OK;
+}
 
 static uint32_t chunk_for(uint64_t L) {
     uint64_t c = ceil_div_u64(ceil_div_u64(L, attn::kSplits), attn::kTile) * attn::kTile;
@@ -502,13 +543,6 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     if (((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)q & 3)) return fail(CATENA_E_BAD_ARG, "attn_decode: alignment");
     if (kv_len > 0x7FFFFFFFull || units > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "attn_decode: size");
     const uint32_t G = (uint32_t)(hq / hkv);
-    const uint32_t chunk = chunk_for(kv_len);
-    const size_t smem = attn_smem_bytes(G, chunk);
-    if (smem > 227 * 1024) return fail(CATENA_E_TOO_LARGE, "attn_decode: KV length beyond the shared-memory score buffer");
-
-    CUtensorMap map_k, map_v;
-    CATENA_TRY(make_kv_map(&map_k, kc, units, kv_len));
-    CATENA_TRY(make_kv_map(&map_v, vc, units, kv_len));
     int dev = tls().device & 15;
     if (!g_attn_err_dev[dev]) {
         CATENA_CUDA(cudaMalloc(&g_attn_err_dev[dev], sizeof(uint32_t)));
@@ -516,6 +550,17 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
         CATENA_CUDA(cudaMallocHost(&g_attn_err_host[dev], sizeof(uint32_t)));
         *g_attn_err_host[dev] = 0;
     }
+    if (attn_tc_mode() && attn_tc_supports(G, kv_len) && ((uintptr_t)q & 15) == 0) {
+        CATENA_TRY(enqueue_attn_decode_tc(q, kc, vc, o, units, G, kv_len, unit0, unit1, g_attn_cluster_limit, g_attn_err_dev[dev]));
+        return attn_finish_launch(dev);
+    }
+    const uint32_t chunk = chunk_for(kv_len);
+    const size_t smem = attn_smem_bytes(G, chunk);
+    if (smem > 227 * 1024) return fail(CATENA_E_TOO_LARGE, "attn_decode: KV length beyond the shared-memory score buffer");
+
+    CUtensorMap map_k, map_v;
+    CATENA_TRY(make_kv_map(&map_k, kc, units, kv_len));
+    CATENA_TRY(make_kv_map(&map_v, vc, units, kv_len));
     CATENA_CUDA(cudaFuncSetAttribute(attn::attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaLaunchConfig_t cfg = {};
@@ -540,22 +585,14 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     if (clusters > (uint64_t)max_clusters) clusters = (uint64_t)max_clusters;
     if (g_attn_cluster_limit > 0 && clusters > (uint64_t)g_attn_cluster_limit) clusters = (uint64_t)g_attn_cluster_limit;
     cfg.gridDim = dim3((unsigned)(clusters * attn::kSplits));
+    g_attn_last_launch[0] = 0; g_attn_last_launch[1] = (uint32_t)max_clusters;
+    g_attn_last_launch[2] = (uint32_t)clusters; g_attn_last_launch[3] = (uint32_t)smem;
     float scale = 1.0f / sqrtf((float)attn::kD);
     CATENA_CUDA(cudaLaunchKernelEx(&cfg, attn::attn_decode_kernel, map_k, map_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)o,
                                    (uint32_t)kv_len, G, (uint32_t)hq, (uint32_t)hkv, (uint32_t)unit0, (uint32_t)unit1, chunk,
                                    scale, g_attn_err_dev[dev]));
     count_launch();
-    if (tls().blocking) {
-        cudaStream_t st = tls().stream;
-        CATENA_CUDA(cudaMemcpyAsync(g_attn_err_host[dev], g_attn_err_dev[dev], sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
-        CATENA_CUDA(cudaStreamSynchronize(st));
-        if (*g_attn_err_host[dev] != 0) {
-            *g_attn_err_host[dev] = 0;
-            cudaMemsetAsync(g_attn_err_dev[dev], 0, sizeof(uint32_t), st);
-            return fail(CATENA_E_TIMEOUT, "attn_decode: bounded wait expired");
-        }
-    }
-    return CATENA_OK;
+    return attn_finish_launch(dev);
 }
 
 catena_status_t attn_check_errors() {
@@ -568,6 +605,7 @@ catena_status_t attn_check_errors() {
     if (*g_attn_err_host[dev] != 0) {
         *g_attn_err_host[dev] = 0;
         cudaMemsetAsync(g_attn_err_dev[dev], 0, sizeof(uint32_t), st);
+        attn_tc_reset_exchange();
         return fail(CATENA_E_TIMEOUT, "attn_decode: bounded wait expired");
     }
     return CATENA_OK;

@@ -66,6 +66,9 @@ catena_status_t gemm_tc_check_errors();
 void gemm_tc_set_cta_limit(int limit);
 void gemm_tc_set_pair_mode(int on);
 void attn_set_cluster_limit(int limit);
+void attn_set_tc_mode(int on);
+void attn_last_launch(uint32_t out[4]);
+extern thread_local uint32_t g_attn_last_launch[4];
 // attn_decode.cu
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
                                    uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t unit0,

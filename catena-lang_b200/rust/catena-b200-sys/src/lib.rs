@@ -1,0 +1,77 @@
+//! Raw bindings of `include/catena_b200.h`.
+//!
+//! The entry points keep the calling convention of the code catena-lang generates
+//! (`catena-lang/src/codegen/gpu.rs:235-261`): inputs by value, one trailing pointer per output,
+//! `mem` as the 16-byte `{pointer, u64 bytes}` struct of `catena-lang/src/runtime/executor.rs:14-19`.
+//! `Executor::new` can therefore keep resolving `program_<name>` with `dlsym` and calling through
+//! libffi; these declarations are for callers that prefer to link directly.
+#![allow(non_camel_case_types)]
+
+use core::ffi::{c_char, c_int, c_void};
+
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct catena_mem_t {
+    pub data: *mut c_void,
+    pub len: u64, // bytes
+}
+
+pub type catena_status_t = i32;
+pub const CATENA_OK: catena_status_t = 0;
+pub const CATENA_E_ASSERT: catena_status_t = 1;
+pub const CATENA_E_CUDA: catena_status_t = 2;
+pub const CATENA_E_NO_DEVICE: catena_status_t = 3;
+pub const CATENA_E_BAD_ARG: catena_status_t = 4;
+pub const CATENA_E_TIMEOUT: catena_status_t = 5;
+pub const CATENA_E_TOO_LARGE: catena_status_t = 6;
+pub const CATENA_E_UNSUPPORTED: catena_status_t = 7;
+
+extern "C" {
+    // runtime
+    pub fn catena_b200_init(device: c_int) -> catena_status_t;
+    pub fn catena_b200_device_count() -> c_int;
+    pub fn catena_b200_set_stream(stream: *mut c_void) -> catena_status_t;
+    pub fn catena_b200_set_blocking(blocking: c_int);
+    pub fn catena_b200_sync() -> catena_status_t;
+    pub fn catena_b200_last_status() -> catena_status_t;
+    pub fn catena_b200_clear_status();
+    pub fn catena_b200_status_string(s: catena_status_t) -> *const c_char;
+    // allocator (replaces GpuRuntime::{alloc, free}, catena-lang/src/runtime/mem.rs:152-190)
+    pub fn catena_b200_mem_alloc(bytes: u64, out: *mut catena_mem_t) -> catena_status_t;
+    pub fn catena_b200_mem_free(mem: catena_mem_t) -> catena_status_t;
+    pub fn catena_b200_mem_upload(host: *const c_void, bytes: u64, out: *mut catena_mem_t) -> catena_status_t;
+    pub fn catena_b200_mem_download(mem: catena_mem_t, host: *mut c_void, bytes: u64) -> catena_status_t;
+    pub fn catena_b200_ipc_export(mem: catena_mem_t, handle64: *mut c_void, offset: *mut u64) -> catena_status_t;
+    pub fn catena_b200_ipc_import(handle64: *const c_void, offset: u64, bytes: u64, out: *mut catena_mem_t) -> catena_status_t;
+    // stdlib programs
+    pub fn program_math_exp_approx(x: f32, out: *mut f32);
+    pub fn program_math_sqrt(x: f32, out: *mut f32);
+    pub fn program_math_powf(x: f32, y: f32, out: *mut f32);
+    pub fn program_nn_sigmoid(x: f32, out: *mut f32);
+    pub fn program_nn_silu(x: f32, out: *mut f32);
+    pub fn program_nn_softmax(input: catena_mem_t, out: *mut catena_mem_t);
+    pub fn program_nn_rmsnorm(input: catena_mem_t, out: *mut catena_mem_t);
+    pub fn program_sum_f32(input: catena_mem_t, out: *mut f32);
+    pub fn program_mean_f32(input: catena_mem_t, out: *mut f32);
+    pub fn program_max_f32(input: catena_mem_t, out: *mut f32);
+    pub fn program_tensor_broadcast_f32(v: f32, n: u64, out: *mut catena_mem_t);
+    pub fn program_tensor_arange_f32(n: u64, out: *mut catena_mem_t);
+    pub fn program_tensor_slice_f32(input: catena_mem_t, start: u64, len: u64, out: *mut catena_mem_t);
+    pub fn program_tensor_concat_f32(l: catena_mem_t, r: catena_mem_t, out: *mut catena_mem_t);
+    pub fn program_tensor_argmax_f32(input: catena_mem_t, out: *mut u64);
+    // catena-lang/tests/cases/matrix/matmul.hex:2-15
+    pub fn program_matmul_2x2_via_mem(a: catena_mem_t, b: catena_mem_t, n: u64, m: u64, k: u64, nk: u64, km: u64,
+                                      nm: u64, out: *mut catena_mem_t);
+    // programs without a counterpart in catena-lang
+    pub fn program_gemm_bf16_rc(a: catena_mem_t, b_colmajor: catena_mem_t, m: u64, n: u64, k: u64, c: *mut catena_mem_t);
+    pub fn program_gemm_i8_rc(a: catena_mem_t, b_colmajor: catena_mem_t, m: u64, n: u64, k: u64, c: *mut catena_mem_t);
+    pub fn program_attn_decode_bf16(q: catena_mem_t, k_cache: catena_mem_t, v_cache: catena_mem_t, batch: u64, hq: u64,
+                                    hkv: u64, d: u64, kv_len: u64, o: *mut catena_mem_t);
+    // sharded execution
+    pub fn catena_b200_gemm_bf16_into(a: *const c_void, b: *const c_void, c: *mut c_void, m: u64, n: u64, k: u64,
+                                      ldc: u64) -> catena_status_t;
+    pub fn catena_b200_attn_decode_bf16_into(q: *const c_void, k: *const c_void, v: *const c_void, o: *mut c_void,
+                                             batch: u64, hq: u64, hkv: u64, d: u64, kv_len: u64, unit0: u64,
+                                             unit1: u64) -> catena_status_t;
+    pub fn catena_b200_sum_f32_noalloc(input: *const c_void, n: u64, out: *mut c_void) -> catena_status_t;
+}

@@ -206,6 +206,13 @@ void catena_b200_debug_set_cta_limit(int limit);
 /* test hook: 1 = run tensor-core GEMMs on the CTA-pair (cta_group::2) kernel, 0 = single-CTA kernel;
  * both give bit-identical results.  No counterpart in the reference. */
 void catena_b200_debug_set_gemm_pair(int on);
+/* test hook: 1 = decode attention on the tcgen05 kernel, 0 = on the mma.sync kernel (same semantics).
+ * No counterpart in the reference. */
+void catena_b200_debug_set_attn_tc(int on);
+/* test hook: geometry of the calling thread's last decode-attention launch: out[0] = kernel (0 mma.sync, 1 tcgen05),
+ * out[1] = clusters of 8 CTAs that can be resident at once, out[2] = clusters launched, out[3] = dynamic shared
+ * memory per CTA in bytes.  No counterpart in the reference. */
+void catena_b200_debug_attn_last_launch(uint32_t out[4]);
 /* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry */
 catena_status_t catena_b200_check_device_errors(void);
 

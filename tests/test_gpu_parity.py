@@ -350,11 +350,28 @@ def run_attn(rt, q, k, v, B, Hq, Hkv, L, D=128):
     return r.v.to_array(np.uint16).reshape(B, Hq, D)
 
 
+def last_attn_launch():
+    """(kernel, resident CTAs or clusters, launched, shared memory) of this thread's last decode launch."""
+    g = (C.c_uint32 * 4)()
+    cb.lib().catena_b200_debug_attn_last_launch(g)
+    return list(g)
+
+
+@pytest.fixture(params=["tcgen05", "mma.sync"])
+def attn_kernel(request):
+    """Runs a test once per decode kernel: the tcgen05 kernel (the default wherever it applies) and the
+    mma.sync kernel (the fallback for long caches)."""
+    cb.lib().catena_b200_debug_set_attn_tc(1 if request.param == "tcgen05" else 0)
+    yield request.param
+    cb.lib().catena_b200_debug_set_attn_tc(1)
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,L", [(2, 8, 2, 256), (1, 4, 1, 64), (3, 8, 8, 333), (2, 16, 2, 77), (1, 2, 1, 1),
-                                        (2, 8, 4, 1000), (1, 32, 8, 4096)])
-def test_attn_decode_vs_oracle(rt, orc, B, Hq, Hkv, L):
+                                        (2, 8, 4, 1000), (1, 32, 8, 4096), (1, 8, 2, 7168)])
+def test_attn_decode_vs_oracle(rt, orc, attn_kernel, B, Hq, Hkv, L):
     q, k, v = attn_inputs(B, Hq, Hkv, L)
     got = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    assert last_attn_launch()[0] == (1 if attn_kernel == "tcgen05" else 0)
     want, want_f32 = orc.attn_decode_bf16(q, k, v, B, Hq, Hkv, 128, L, np.float32(1.0 / math.sqrt(128.0)),
                                           threads=orc.max_threads(), want_f32=True)
     # same probabilities (global max, the reference's exp polynomial); only fp32 summation order
@@ -362,18 +379,49 @@ def test_attn_decode_vs_oracle(rt, orc, B, Hq, Hkv, L):
     assert_bf16_close(got, want, want_f32, 4e-6, 0.02)
 
 
-def test_attn_decode_c3_partition_and_determinism(rt, orc):
+def test_attn_decode_long_cache_falls_back(rt, orc):
+    """More than 7 score tiles per chunk do not fit the tcgen05 kernel's TMEM sets: the mma.sync kernel takes over."""
+    B, Hq, Hkv, L = 1, 4, 1, 8192
+    q, k, v = attn_inputs(B, Hq, Hkv, L)
+    got = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    assert last_attn_launch()[0] == 0
+    want, want_f32 = orc.attn_decode_bf16(q, k, v, B, Hq, Hkv, 128, L, np.float32(1.0 / math.sqrt(128.0)),
+                                          threads=orc.max_threads(), want_f32=True)
+    assert_bf16_close(got, want, want_f32, 4e-6, 0.02)
+
+
+def test_attn_decode_kernels_agree(rt):
+    """Same semantics in both kernels: the outputs differ at most in the last bf16 bit of a few elements
+    (the tensor cores add the 16 products of a k-step in a different order)."""
+    B, Hq, Hkv, L = 4, 32, 8, 2048
+    q, k, v = attn_inputs(B, Hq, Hkv, L)
+    outs = []
+    for tc in (1, 0):
+        cb.lib().catena_b200_debug_set_attn_tc(tc)
+        try:
+            outs.append(run_attn(rt, q, k, v, B, Hq, Hkv, L))
+        finally:
+            cb.lib().catena_b200_debug_set_attn_tc(1)
+    import oracle
+    a, b = (oracle.bf16_bits_to_f32(x.ravel()) for x in outs)
+    assert np.mean(outs[0] == outs[1]) > 0.99
+    assert np.all(np.abs(a - b) <= 2.0 ** -7 * np.maximum(np.abs(a), np.abs(b)) + 4e-6)
+
+
+def test_attn_decode_c3_partition_and_determinism(rt, orc, attn_kernel):
     B, Hq, Hkv, L = 32, 32, 8, 4096
     q, k, v = attn_inputs(B, Hq, Hkv, L)
     got = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    full = last_attn_launch()
     again = run_attn(rt, q, k, v, B, Hq, Hkv, L)
     assert np.array_equal(got, again)
-    cb.lib().catena_b200_debug_set_cta_limit(40)              # 5 resident clusters instead of ~33
+    cb.lib().catena_b200_debug_set_cta_limit(40)              # a fraction of the resident CTAs / clusters
     try:
         few_clusters = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+        assert last_attn_launch()[2] < full[2]
     finally:
         cb.lib().catena_b200_debug_set_cta_limit(0)
-    assert np.array_equal(got, few_clusters)                  # the cluster count never enters the arithmetic
+    assert np.array_equal(got, few_clusters)                  # the grid never enters the arithmetic
     units = list(range(0, B * Hq, 97))[:12]                   # oracle on a sample of (batch, head) rows
     for u in units:
         want, want_f32 = orc.attn_decode_bf16(q, k, v, B, Hq, Hkv, 128, L, np.float32(1.0 / math.sqrt(128.0)),

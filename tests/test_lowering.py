@@ -1,0 +1,61 @@
+"""Native lowering selector: hand-written IR fixtures (shaped after catena-lang/src/codegen/mod.rs:107-146
+and the lowering asserted in catena-lang/tests/compile/closures/matmul.rs:45-53 and reduce.rs:30) must map
+to the prebuilt kernels; anything else must be refused, not silently run."""
+import pytest
+
+import catena_lang_b200 as cb
+from catena_lang_b200 import lowering as lo
+
+
+def mod(source_name, assigns):
+    return lo.module_from_dict({"name": cb.symbol_for(source_name), "source_name": source_name,
+                                "entry": {"name": cb.symbol_for(source_name), "sources": [], "targets": [],
+                                          "assignments": assigns}})
+
+
+def reducec(add, get):
+    return {"op": "reducec", "inputs": [{"name": "zero", "lowered": "f32"}, {"fn": add}, {"name": "buf", "lowered": "ptr<f32>"},
+                                        {"fn": get}, {"name": "len", "lowered": "u64"}], "outputs": [{"name": "acc", "lowered": "f32"}]}
+
+
+def materializec(producer):
+    return {"op": "materializec", "inputs": [{"name": "len", "lowered": "u64"}, {"name": "env", "lowered": "ptr<f32>"}, {"fn": producer}],
+            "outputs": [{"name": "out", "lowered": "ptr<f32>"}]}
+
+
+CAST = {"op": "mem.cast.f32", "inputs": [{"name": "m", "lowered": "mem"}], "outputs": [{"name": "len", "lowered": "u64"}, {"name": "buf", "lowered": "ptr<f32>"}]}
+TO_MEM = {"op": "buf.to-mem", "inputs": [{"name": "len", "lowered": "u64"}, {"name": "out", "lowered": "ptr<f32>"}], "outputs": [{"name": "r", "lowered": "mem"}]}
+
+
+def test_matmul_module_selects_the_f32_gemm():
+    m = mod("matmul-2x2-via-mem", [CAST, CAST, {"op": "u64.eq", "inputs": [], "outputs": []}, {"op": "assert", "inputs": [], "outputs": []},
+                                   materializec("closure.f32.matmul.row-major.cell-at.0"), TO_MEM])
+    plan = lo.select(m)
+    assert plan.kernel == "matmul_f32_kernel" and plan.symbol == "program_matmul_2x2_via_mem"
+
+
+def test_stdlib_folds_and_fused_programs():
+    assert lo.select(mod("sum-f32", [CAST, reducec("f32.add-env", "f32-at")])).kernel == "fold_sum"
+    assert lo.select(mod("max-f32", [CAST, reducec("f32.max-env", "f32-at")])).kernel == "fold_max"
+    assert lo.select(mod("tensor.argmax-f32", [CAST, reducec("tensor.argmax-env", "tensor.argmax-pair-at")])).kernel == "fold_argmax"
+    sm = mod("nn.softmax", [CAST, reducec("f32.max-env", "f32-at"), reducec("f32.add-env", "nn.softmax-exp-shifted-at"),
+                            materializec("nn.softmax-at"), TO_MEM])
+    assert lo.select(sm).kernel == "softmax_fused" and lo.select(sm).symbol == "program_nn_softmax"
+    rn = mod("nn.rmsnorm", [CAST, reducec("f32.add-env", "nn.squared-at"), {"op": "u64.to-f32", "inputs": [], "outputs": []},
+                            {"op": "f32.div", "inputs": [], "outputs": []}, {"op": "math.sqrt", "inputs": [], "outputs": [], "call_symbol": "program_math_sqrt"},
+                            materializec("nn.rmsnorm-at"), TO_MEM])
+    assert lo.select(rn).kernel == "rmsnorm_fused"
+    assert lo.select(mod("tensor.concat-f32", [CAST, CAST, materializec("tensor.concat-f32-at"), TO_MEM])).kernel == "copy_concat"
+
+
+def test_scalar_module_runs_on_the_host():
+    m = mod("nn.silu", [{"op": "f32.neg", "inputs": [], "outputs": []}, {"op": "math.exp-approx", "inputs": [], "outputs": [], "call_symbol": "program_math_exp_approx"},
+                        {"op": "f32.add", "inputs": [], "outputs": []}, {"op": "f32.div", "inputs": [], "outputs": []}, {"op": "f32.mul", "inputs": [], "outputs": []}])
+    assert lo.select(m).kernel == "host_scalar"
+
+
+def test_unknown_producer_is_refused():
+    with pytest.raises(lo.Unsupported):
+        lo.select(mod("my-map", [CAST, materializec("my.custom-at"), TO_MEM]))
+    with pytest.raises(lo.Unsupported):
+        lo.select(mod("odd", [CAST, reducec("f32.add-env", "my.getter")]))
