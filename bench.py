@@ -293,7 +293,7 @@ def run_gpu(args, rank, world, local_rank):
                             "config": {"workload": "decode attention B=32 Hq=32 Hkv=8 D=128 L=4096 bf16, 537395200 algorithmic bytes per launch"},
                             "roofline": {"bound": "hbm", "achieved": attn_gbs_1, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                          "frac": attn_gbs_1 / peaks["hbm_gbs"], "traffic": None,
-                                         "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "attn_decode_kernel"}},
+                                         "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "attn_decode_tc_kernel"}},
             "cpu_baseline": cpu_baseline,
             "output_checksum": f"{checksum:016x}",
         }
