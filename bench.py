@@ -287,7 +287,7 @@ def run_gpu(args, rank, world, local_rank):
             "gpu_launches": int(gemm_launches),
             "roofline": {"bound": "tensor", "achieved": gemm_tflops_1, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": gemm_tflops_1 / peaks["bf16_tflops"], "traffic": None,
-                         "peak_source": f"{peaks['source']} burst cuBLAS bf16", "kernel": "gemm_tc_kernel<bf16>"},
+                         "peak_source": f"{peaks['source']} burst cuBLAS bf16", "kernel": "gemm_tc2_kernel<bf16>"},
             "attn_decode": {"metric": "kv_attn_decode_hbm_gbs", "value": world * attn_gbs_1, "unit": "GB/s",
                             "ms_per_step": attn_per, "gpu_launches": int(attn_launches), "clocks": attn_clocks,
                             "config": {"workload": "decode attention B=32 Hq=32 Hkv=8 D=128 L=4096 bf16, 537395200 algorithmic bytes per launch"},

@@ -30,6 +30,13 @@ class CatenaMem(C.Structure):
     _fields_ = [("data", C.c_void_p), ("len", C.c_uint64)]
 
 
+class LlamaBlockStruct(C.Structure):
+    """catena_llama_block_t (include/catena_b200.h)."""
+    _fields_ = [("hidden", C.c_uint64), ("n_heads", C.c_uint64), ("n_kv_heads", C.c_uint64), ("ffn", C.c_uint64),
+                ("vocab", C.c_uint64), ("max_len", C.c_uint64), ("embedding", C.c_void_p), ("w_qkv", C.c_void_p),
+                ("w_o", C.c_void_p), ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p), ("rope_base", C.c_float)]
+
+
 class CatenaError(RuntimeError):
     def __init__(self, status, what=""):
         self.status = int(status)
@@ -113,6 +120,18 @@ def lib():
     proto("catena_b200_softmax_f32_into", st, [vp, vp, u64])
     proto("catena_b200_rmsnorm_f32_into", st, [vp, vp, u64])
     proto("catena_b200_check_device_errors", st, [])
+    pblk = C.POINTER(LlamaBlockStruct)
+    proto("catena_b200_llama_workspace_bytes", u64, [pblk, u64])
+    proto("catena_b200_llama_prefill", st, [pblk, vp, u64, u64, vp, vp, vp, vp, u64])
+    proto("catena_b200_llama_decode", st, [pblk, vp, u64, u64, vp, vp, vp, vp, u64])
+    proto("catena_b200_embed_bf16_into", st, [vp, vp, vp, u64, u64, u64])
+    proto("catena_b200_rmsnorm_rows_bf16_into", st, [vp, vp, u64, u64])
+    proto("catena_b200_rope_append_bf16_into", st, [vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, f32])
+    proto("catena_b200_attn_prefill_bf16_into", st, [vp, vp, vp, vp, u64, u64, u64, u64, u64])
+    proto("catena_b200_attn_decode_bf16_cache_into", st, [vp, vp, vp, vp, u64, u64, u64, u64, u64, u64])
+    proto("catena_b200_swiglu_bf16_into", st, [vp, vp, u64, u64])
+    proto("catena_b200_add_bf16_into", st, [vp, vp, vp, u64])
+    proto("catena_b200_linear_bf16_into", st, [vp, vp, vp, vp, u64, u64, u64])
     proto("catena_b200_debug_set_cta_limit", None, [C.c_int])
     proto("catena_b200_sum_f32_noalloc", st, [vp, u64, vp])
     proto("catena_b200_debug_set_gemm_pair", None, [C.c_int])
@@ -174,4 +193,5 @@ def free(mem):
         check(lib().catena_b200_mem_free(mem), "mem_free")
 
 
+from .llama import LlamaBlock  # noqa: E402,F401
 from .runtime import (ExecError, GpuDialect, InitError, Mem, Runtime, Value, ValueKind)  # noqa: E402,F401

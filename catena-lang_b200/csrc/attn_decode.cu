@@ -463,11 +463,11 @@ static EncodeTiledFn attn_encode_fn() {
 // KV cache [units, L, 128] bf16 viewed as a 4-D tensor (64 d, L positions, 2 d-halves, units) so that one
 // copy of box 64 x 64 x 2 x 1 brings a whole 64-position tile as [d-half][position][128 B], 128B-swizzled;
 // positions past L read as zero, so a ragged last tile never touches the next unit's rows.
-static catena_status_t make_kv_map(CUtensorMap* map, const void* base, uint64_t units, uint64_t L) {
+static catena_status_t make_kv_map(CUtensorMap* map, const void* base, uint64_t units, uint64_t L, uint64_t cap) {
     EncodeTiledFn fn = attn_encode_fn();
     if (!fn) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled is unavailable");
     cuuint64_t dims[4] = {64, L, 2, units};
-    cuuint64_t strides[3] = {(cuuint64_t)attn::kD * 2, 128, L * (cuuint64_t)attn::kD * 2};
+    cuuint64_t strides[3] = {(cuuint64_t)attn::kD * 2, 128, cap * (cuuint64_t)attn::kD * 2};   // a unit owns `cap` rows
     cuuint32_t box[4] = {64, (cuuint32_t)attn::kTile, 2, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
@@ -502,7 +502,8 @@ void attn_set_tc_mode(int on) { g_attn_tc_mode = on ? 1 : 0; }
 bool attn_tc_supports(uint32_t G, uint64_t kv_len);
 void attn_tc_reset_exchange();
 catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
-                                       uint64_t kv_len, uint64_t unit0, uint64_t unit1, int cluster_limit, uint32_t* err_dev);
+                                       uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1, int cluster_limit,
+                                       uint32_t* err_dev);
 
 // After enqueuing: in blocking mode wait and turn a device-side bounded-wait expiry into a status.
 static catena_status_t attn_finish_launch(int dev) {
@@ -530,18 +531,19 @@ static size_t attn_smem_bytes(uint32_t G, uint32_t chunk) {
 }
 
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch, uint64_t hq,
-                                   uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t unit0, uint64_t unit1) {
+                                   uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1) {
     CATENA_TRY(ensure_device());
     if (!q || !kc || !vc || !o) return fail(CATENA_E_BAD_ARG, "attn_decode: null operand");
     if (d != (uint64_t)attn::kD) return fail(CATENA_E_UNSUPPORTED, "attn_decode: head_dim must be 128");
     if (hkv == 0 || hq % hkv != 0 || hq / hkv > (uint64_t)attn::kMaxG)
         return fail(CATENA_E_UNSUPPORTED, "attn_decode: Hq must be a multiple of Hkv with Hq/Hkv <= 8");
     if (kv_len == 0 || batch == 0) return fail(CATENA_E_BAD_ARG, "attn_decode: empty cache");
+    if (kv_cap < kv_len) return fail(CATENA_E_BAD_ARG, "attn_decode: cache capacity below the visible length");
     uint64_t units = batch * hkv;
     if (unit1 > units || unit0 > unit1) return fail(CATENA_E_BAD_ARG, "attn_decode: unit range");
     if (unit0 == unit1) return CATENA_OK;
     if (((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)q & 3)) return fail(CATENA_E_BAD_ARG, "attn_decode: alignment");
-    if (kv_len > 0x7FFFFFFFull || units > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "attn_decode: size");
+    if (kv_len > 0x7FFFFFFFull || kv_cap > 0x7FFFFFFFull || units > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "attn_decode: size");
     const uint32_t G = (uint32_t)(hq / hkv);
     int dev = tls().device & 15;
     if (!g_attn_err_dev[dev]) {
@@ -551,7 +553,7 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
         *g_attn_err_host[dev] = 0;
     }
     if (attn_tc_mode() && attn_tc_supports(G, kv_len) && ((uintptr_t)q & 15) == 0) {
-        CATENA_TRY(enqueue_attn_decode_tc(q, kc, vc, o, units, G, kv_len, unit0, unit1, g_attn_cluster_limit, g_attn_err_dev[dev]));
+        CATENA_TRY(enqueue_attn_decode_tc(q, kc, vc, o, units, G, kv_len, kv_cap, unit0, unit1, g_attn_cluster_limit, g_attn_err_dev[dev]));
         return attn_finish_launch(dev);
     }
     const uint32_t chunk = chunk_for(kv_len);
@@ -559,8 +561,8 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     if (smem > 227 * 1024) return fail(CATENA_E_TOO_LARGE, "attn_decode: KV length beyond the shared-memory score buffer");
 
     CUtensorMap map_k, map_v;
-    CATENA_TRY(make_kv_map(&map_k, kc, units, kv_len));
-    CATENA_TRY(make_kv_map(&map_v, vc, units, kv_len));
+    CATENA_TRY(make_kv_map(&map_k, kc, units, kv_len, kv_cap));
+    CATENA_TRY(make_kv_map(&map_v, vc, units, kv_len, kv_cap));
     CATENA_CUDA(cudaFuncSetAttribute(attn::attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     cudaLaunchConfig_t cfg = {};

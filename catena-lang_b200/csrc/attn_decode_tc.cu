@@ -697,14 +697,14 @@ static EncodeTiledFnA2 attn2_encode_fn() {
     return fn;
 }
 
-// KV cache [units, L, 128] bf16 as a 4-D tensor (64 d, L positions, 2 d-halves, units): one copy of box
+// KV cache [units, cap, 128] bf16, L visible rows per unit, as a 4-D tensor (64 d, L positions, 2 d-halves, units): one copy of box
 // 64 x 128 x 2 x 1 brings a 128-position tile as [d-half][position][128 B], 128B-swizzled; positions past L
 // read as zero.
-static catena_status_t make_kv_map2(CUtensorMap* map, const void* base, uint64_t units, uint64_t L) {
+static catena_status_t make_kv_map2(CUtensorMap* map, const void* base, uint64_t units, uint64_t L, uint64_t cap) {
     EncodeTiledFnA2 fn = attn2_encode_fn();
     if (!fn) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled is unavailable");
     cuuint64_t dims[4] = {64, L, 2, units};
-    cuuint64_t strides[3] = {(cuuint64_t)attn2::kD * 2, 128, L * (cuuint64_t)attn2::kD * 2};
+    cuuint64_t strides[3] = {(cuuint64_t)attn2::kD * 2, 128, cap * (cuuint64_t)attn2::kD * 2};   // a unit owns `cap` rows
     cuuint32_t box[4] = {64, (cuuint32_t)attn2::kTile, 2, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
@@ -753,15 +753,16 @@ void attn_tc_reset_exchange() {
 
 // Enqueues the tcgen05 decode kernel (arguments already validated by launch_attn_decode).
 catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
-                                       uint64_t kv_len, uint64_t unit0, uint64_t unit1, int cluster_limit, uint32_t* err_dev) {
+                                       uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1, int cluster_limit,
+                                       uint32_t* err_dev) {
     const uint32_t chunk = chunk_for2(kv_len);
     const size_t smem = attn2_smem_bytes();
     const int dev = tls().device & 15;
     const uint64_t n_units = unit1 - unit0, items = n_units * attn2::kSplits;
     if (items > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "attn_decode: too many chunk items");
     CUtensorMap map_k, map_v;
-    CATENA_TRY(make_kv_map2(&map_k, kc, units, kv_len));
-    CATENA_TRY(make_kv_map2(&map_v, vc, units, kv_len));
+    CATENA_TRY(make_kv_map2(&map_k, kc, units, kv_len, kv_cap));
+    CATENA_TRY(make_kv_map2(&map_v, vc, units, kv_len, kv_cap));
 
     // resident CTAs (one per SM for a kernel that allocates TMEM), asked once per device
     if (g_attn2_max_ctas[dev] == 0) {

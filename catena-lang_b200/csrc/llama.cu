@@ -1,0 +1,665 @@
+// Llama-style transformer block (pre-norm, rotary positions, SwiGLU) wired from this library's kernels.
+// The reference has no bf16, no attention and no rotary embedding; every formula here is composed from
+// reference programs under the inherited rules:
+//   * rmsnorm      nn.rmsnorm (catena-lang/stdlib/nn.hex:125-182): y = x / sqrt~(mean(x^2) + eps), NO gain vector
+//   * projections  the matmul cell rule (catena-lang/stdlib/matrix.hex:236-256): fp32 accumulate, fixed k order
+//   * rotary       angle = position * base^(-2i/128) with base^(..) = math.powf (catena-lang/stdlib/math.hex:202-231),
+//                  sin = math.sin-approx-full (math.hex:91-103), cos(x) = sin-approx-full(x + pi/2) because the
+//                  reference has no full-range cosine (math.hex:27-47 covers small |x| only)
+//   * attention    nn.softmax semantics (nn.hex:93-122): global max, exp~, probabilities as bf16 hi + lo
+//   * SwiGLU       nn.silu (nn.hex:2-56) of the gate times the up projection
+//   * residuals    f32.add of the two bf16 values, rounded to bf16
+// Activations are bf16 in HBM; every intermediate sum is fp32 with separately rounded multiply and add.
+//
+// Kernels in this file: embedding gather, row rmsnorm, rotary + KV-cache append, causal prefill attention
+// (mma.sync, two passes over the keys: maxima, then probabilities), SwiGLU, residual add, and a skinny
+// GEMM (at most 8 rows: the decode step streams each weight matrix once, HBM-bound).  The wide
+// projections of the prefill use the tcgen05 GEMM, the decode attention the cached-attention kernel.
+#include <cuda_bf16.h>
+
+#include "catena_math.cuh"
+#include "common.cuh"
+
+namespace catena {
+
+namespace llama {
+
+constexpr int kHeadDim = 128;
+constexpr uint32_t kEpsBits = 0x3727C5ACu;      // 1e-5, nn.hex:154-182
+constexpr uint32_t kHalfPiBits = 0x3FC90FDBu;   // pi/2 rounded to f32
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16); }
+
+// ---------------------------------------------------------------- embedding gather
+// out[t, :] = table[ids[t], :]; one CTA per token, 16-byte pieces.  An id outside the table sets *bad.
+__global__ void embed_rows_kernel(const uint4* __restrict__ table, const int32_t* __restrict__ ids, uint4* __restrict__ out,
+                                  uint32_t hidden16, uint32_t vocab, uint32_t* bad) {
+    const uint32_t t = blockIdx.x;
+    const int32_t id = ids[t];
+    if (id < 0 || (uint32_t)id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(bad, 1u);
+        return;
+    }
+    const uint4* src = table + (size_t)id * hidden16;
+    uint4* dst = out + (size_t)t * hidden16;
+    for (uint32_t i = threadIdx.x; i < hidden16; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------- row rmsnorm (bf16 in / out)
+// One CTA of 256 threads per row.  Sum of squares in a fixed shape: thread t adds its elements in ascending
+// order (8 consecutive elements per 2048-element stride), xor butterfly per warp, warps added in ascending order.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, uint32_t hidden) {
+    __shared__ float warp_sum[8];
+    __shared__ float rms_s;
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint4* xr = x + (size_t)row * (hidden / 8);
+    float acc = 0.0f;
+    for (uint32_t i = tid; i < hidden / 8; i += 256) {
+        const uint4 v = xr[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float a = bf16_bits_to_f32(w[e] & 0xFFFFu), b = bf16_bits_to_f32(w[e] >> 16);
+            acc = cmath::add(acc, cmath::mul(a, a));
+            acc = cmath::add(acc, cmath::mul(b, b));
+        }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) acc = cmath::add(acc, __shfl_xor_sync(0xFFFFFFFFu, acc, off));
+    if ((tid & 31) == 0) warp_sum[tid >> 5] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        float s = warp_sum[0];
+        for (int w = 1; w < 8; ++w) s = cmath::add(s, warp_sum[w]);
+        const float mean = cmath::div(s, cmath::u64_to_f32(hidden));
+        rms_s = cmath::sqrt_newton(cmath::add(mean, cmath::from_bits(kEpsBits)));
+    }
+    __syncthreads();
+    const float rms = rms_s;
+    uint4* yr = y + (size_t)row * (hidden / 8);
+    for (uint32_t i = tid; i < hidden / 8; i += 256) {
+        const uint4 v = xr[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            r[e] = pack_bf16(cmath::div(bf16_bits_to_f32(w[e] & 0xFFFFu), rms), cmath::div(bf16_bits_to_f32(w[e] >> 16), rms));
+        yr[i] = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+}
+
+// ---------------------------------------------------------------- rotary embedding + KV-cache append
+// qkv [T, (Hq + 2 Hkv) * 128] bf16 (one row per token: query heads, key heads, value heads).
+// Token t belongs to sequence t / S at position pos0 + t % S.  Writes
+//   q_out   [T, Hq, 128]                 rotated queries
+//   k_cache [B, Hkv, cap, 128] at pos    rotated keys
+//   v_cache [B, Hkv, cap, 128] at pos    values
+// One thread per (token, head, pair i < 64): the pair is (i, i + 64) ("rotate half").
+// inv_freq[i] = base^(-2i/128), computed once on the host with the same bit-exact functions.
+__global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                   __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                   const float* __restrict__ inv_freq, uint32_t T, uint32_t S, uint32_t pos0, uint32_t Hq,
+                                   uint32_t Hkv, uint32_t cap) {
+    const uint32_t heads = Hq + 2 * Hkv;
+    const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)T * heads * 64) return;
+    const uint32_t i = (uint32_t)(idx % 64);
+    const uint32_t head = (uint32_t)((idx / 64) % heads);
+    const uint32_t t = (uint32_t)(idx / (64ull * heads));
+    const uint32_t b = t / S, pos = pos0 + t % S;
+    const __nv_bfloat16* src = qkv + ((size_t)t * heads + head) * kHeadDim;
+    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + 64]);
+    if (head >= Hq + Hkv) {   // value head: plain copy
+        __nv_bfloat16* dst = v_cache + (((size_t)b * Hkv + (head - Hq - Hkv)) * cap + pos) * kHeadDim;
+        dst[i] = src[i];
+        dst[i + 64] = src[i + 64];
+        return;
+    }
+    const float angle = cmath::mul(cmath::u32_to_f32(pos), inv_freq[i]);
+    const float sn = cmath::sin_full(angle);
+    const float cs = cmath::sin_full(cmath::add(angle, cmath::from_bits(kHalfPiBits)));
+    const float r1 = cmath::sub(cmath::mul(x1, cs), cmath::mul(x2, sn));
+    const float r2 = cmath::add(cmath::mul(x2, cs), cmath::mul(x1, sn));
+    __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)t * Hq + head) * kHeadDim
+                                   : k_cache + (((size_t)b * Hkv + (head - Hq)) * cap + pos) * kHeadDim;
+    dst[i] = __float2bfloat16_rn(r1);
+    dst[i + 64] = __float2bfloat16_rn(r2);
+}
+
+// ---------------------------------------------------------------- SwiGLU and residual add
+// gu [T, 2F] bf16 (gate columns, then up columns) -> a [T, F] = silu(gate) * up
+__global__ void swiglu_kernel(const uint4* __restrict__ gu, uint4* __restrict__ a, uint64_t T, uint32_t F8) {
+    const uint64_t n = T * F8;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t t = idx / F8, c = idx % F8;
+        const uint4 g = gu[t * 2 * F8 + c], u = gu[t * 2 * F8 + F8 + c];
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float lo = cmath::mul(cmath::silu(bf16_bits_to_f32(gw[e] & 0xFFFFu)), bf16_bits_to_f32(uw[e] & 0xFFFFu));
+            const float hi = cmath::mul(cmath::silu(bf16_bits_to_f32(gw[e] >> 16)), bf16_bits_to_f32(uw[e] >> 16));
+            r[e] = pack_bf16(lo, hi);
+        }
+        a[idx] = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+}
+
+// out = x + y (bf16, fp32 add, RNE); out may alias x or y
+__global__ void add_rows_kernel(const uint4* x, const uint4* y, uint4* out, uint64_t n8) {
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n8; idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint4 a = x[idx], b = y[idx];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            r[e] = pack_bf16(cmath::add(bf16_bits_to_f32(aw[e] & 0xFFFFu), bf16_bits_to_f32(bw[e] & 0xFFFFu)),
+                             cmath::add(bf16_bits_to_f32(aw[e] >> 16), bf16_bits_to_f32(bw[e] >> 16)));
+        out[idx] = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+}
+
+// ---------------------------------------------------------------- skinny GEMM (M <= 8 rows)
+// y[m, n] = sum_k x[m, k] * w[n, k], optionally + res[m, n]; x [M, K] bf16, w [N, K] bf16 (K contiguous), y [M, N] bf16.
+// HBM-bound on w: every weight is read exactly once.  One warp per output column at a time (persistent warps
+// stride over the columns); x sits in shared memory.  Fixed order: lane l accumulates k = 8l + 256p + e for
+// p ascending, e = 0..7 ascending; then the xor butterfly over lanes.
+template <int M>
+__global__ void __launch_bounds__(256) skinny_gemm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
+                                                         const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ y,
+                                                         uint32_t N, uint32_t K) {
+    extern __shared__ uint4 xs[];   // [M][K/8]
+    const uint32_t K8 = K / 8;
+    for (uint32_t i = threadIdx.x; i < M * K8; i += blockDim.x) xs[i] = x[i];
+    __syncthreads();
+    const uint32_t lane = threadIdx.x & 31, warps = gridDim.x * (blockDim.x >> 5);
+    for (uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += warps) {
+        const uint4* wr = w + (size_t)n * K8;
+        float acc[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+        for (uint32_t p0 = lane; p0 < K8; p0 += 128) {
+            uint4 wv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) wv[u] = p0 + 32 * u < K8 ? __ldcs(wr + p0 + 32 * u) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (p0 + 32 * u < K8) {
+                    const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const uint4 xv = xs[m * K8 + p0 + 32 * u];
+                        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc[m] = cmath::add(acc[m], cmath::mul(bf16_bits_to_f32(xw[e] & 0xFFFFu), bf16_bits_to_f32(ww[e] & 0xFFFFu)));
+                            acc[m] = cmath::add(acc[m], cmath::mul(bf16_bits_to_f32(xw[e] >> 16), bf16_bits_to_f32(ww[e] >> 16)));
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) acc[m] = cmath::add(acc[m], __shfl_xor_sync(0xFFFFFFFFu, acc[m], off));
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float v = acc[m];
+                if (res) v = cmath::add(__bfloat162float(__float2bfloat16_rn(v)), __bfloat162float(res[(size_t)m * N + n]));
+                y[(size_t)m * N + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- causal prefill attention (mma.sync)
+// q [T, Hq, 128] bf16 (rotated), k/v cache [B, Hkv, cap, 128] bf16, out [T, Hq * 128] bf16; token t = b * S + s
+// attends to cache positions 0..s of its sequence.  One CTA (4 warps) per 64 queries of one head; warp w owns
+// 16 query rows.  exp~ is not multiplicative, so there is no online rescaling: pass 1 multiplies Q K^T over all
+// visible key tiles for the row maxima only, pass 2 multiplies again, forms p = exp~(s - max) and accumulates
+// O += P V with P as a bf16 hi + lo pair.  Sums are fixed-order: a thread adds its own columns in ascending
+// key order, the four threads of a row combine by xor butterfly.
+// Shared-memory tiles are [row][128 bf16] with the 16-byte chunk index xor-ed by (row & 7).
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t chunk) { return row * 256u + ((chunk ^ (row & 7u)) << 4); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// copies rows [row0, row0 + 64) of a [rows_total, 128] bf16 matrix (row pitch `pitch` elements) into a swizzled tile;
+// rows past rows_total are filled with zeros
+__device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* base, size_t pitch, uint32_t row0, uint32_t rows_total) {
+    for (uint32_t i = threadIdx.x; i < 64 * 16; i += 128) {
+        const uint32_t r = i >> 4, c = i & 15;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row0 + r < rows_total) v = *reinterpret_cast<const uint4*>(base + (size_t)(row0 + r) * pitch + c * 8);
+        *reinterpret_cast<uint4*>(tile + tile_off(r, c)) = v;
+    }
+}
+
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                                                          const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                                                          uint32_t S, uint32_t Hq, uint32_t Hkv, uint32_t cap, float scale) {
+    extern __shared__ __align__(1024) uint8_t smem_pf[];
+    uint8_t* q_tile = smem_pf;
+    uint8_t* k_tile = smem_pf + 16384;
+    uint8_t* v_tile = smem_pf + 32768;
+    const uint32_t qt = gridDim.x - 1 - blockIdx.x;          // heavy tiles first
+    const uint32_t h = blockIdx.y, b = blockIdx.z, kvh = h / (Hq / Hkv);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const __nv_bfloat16* qb = q + ((size_t)b * S * Hq + h) * kHeadDim;               // row pitch Hq * 128
+    const __nv_bfloat16* kb = k_cache + ((size_t)b * Hkv + kvh) * cap * kHeadDim;    // row pitch 128
+    const __nv_bfloat16* vb = v_cache + ((size_t)b * Hkv + kvh) * cap * kHeadDim;
+    const float ninf = __uint_as_float(0xFF800000u);
+
+    load_tile(q_tile, qb, (size_t)Hq * kHeadDim, qt * 64, S);
+    __syncthreads();
+    uint32_t qa[8][4];   // A fragments of this warp's 16 query rows, one per 16-d step
+#pragma unroll
+    for (uint32_t ks = 0; ks < 8; ++ks)
+        ldsm_x4(smem_addr(q_tile) + tile_off(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), qa[ks]);
+    const uint32_t row_a = qt * 64 + warp * 16 + g, row_b = row_a + 8;   // the two query rows of this thread
+
+    // S tile = Q K^T for the 64 keys in k_tile: sacc[nb] covers keys 8 nb .. 8 nb + 7
+    auto scores = [&](float (&sacc)[8][4]) {
+#pragma unroll
+        for (uint32_t nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[nb][e] = 0.0f;
+#pragma unroll
+            for (uint32_t ks2 = 0; ks2 < 4; ++ks2) {   // two 16-d steps per ldmatrix.x4
+                uint32_t kf[4];
+                ldsm_x4(smem_addr(k_tile) + tile_off(nb * 8 + (lane & 7), 4 * ks2 + (lane >> 3)), kf);
+                mma_bf16(sacc[nb], qa[2 * ks2], kf[0], kf[1]);
+                mma_bf16(sacc[nb], qa[2 * ks2 + 1], kf[2], kf[3]);
+            }
+        }
+    };
+
+    // ---- pass 1: row maxima over every visible key ----
+    float ma = ninf, mb = ninf;
+    for (uint32_t kt = 0; kt <= qt; ++kt) {
+        __syncthreads();
+        load_tile(k_tile, kb, kHeadDim, kt * 64, S);
+        __syncthreads();
+        float sacc[8][4];
+        scores(sacc);
+#pragma unroll
+        for (uint32_t nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (uint32_t e = 0; e < 2; ++e) {
+                const uint32_t key = kt * 64 + nb * 8 + 2 * tq + e;
+                if (key <= row_a) ma = fmaxf(ma, cmath::mul(sacc[nb][e], scale));
+                if (key <= row_b) mb = fmaxf(mb, cmath::mul(sacc[nb][2 + e], scale));
+            }
+        }
+    }
+    ma = fmaxf(ma, __shfl_xor_sync(0xFFFFFFFFu, ma, 1));
+    ma = fmaxf(ma, __shfl_xor_sync(0xFFFFFFFFu, ma, 2));
+    mb = fmaxf(mb, __shfl_xor_sync(0xFFFFFFFFu, mb, 1));
+    mb = fmaxf(mb, __shfl_xor_sync(0xFFFFFFFFu, mb, 2));
+
+    // ---- pass 2: probabilities and O += P V ----
+    float oacc[16][4];
+#pragma unroll
+    for (int db = 0; db < 16; ++db)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[db][e] = 0.0f;
+    float la = 0.0f, lb = 0.0f;
+    for (uint32_t kt = 0; kt <= qt; ++kt) {
+        __syncthreads();
+        load_tile(k_tile, kb, kHeadDim, kt * 64, S);
+        load_tile(v_tile, vb, kHeadDim, kt * 64, S);
+        __syncthreads();
+        float sacc[8][4];
+        scores(sacc);
+        // probabilities in place (masked keys: 0), denominators in ascending key order
+#pragma unroll
+        for (uint32_t nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (uint32_t e = 0; e < 2; ++e) {
+                const uint32_t key = kt * 64 + nb * 8 + 2 * tq + e;
+                const float pa = key <= row_a ? cmath::exp_approx(cmath::sub(cmath::mul(sacc[nb][e], scale), ma)) : 0.0f;
+                const float pb = key <= row_b ? cmath::exp_approx(cmath::sub(cmath::mul(sacc[nb][2 + e], scale), mb)) : 0.0f;
+                sacc[nb][e] = pa;
+                sacc[nb][2 + e] = pb;
+                la = cmath::add(la, pa);
+                lb = cmath::add(lb, pb);
+            }
+        }
+#pragma unroll
+        for (uint32_t kk = 0; kk < 4; ++kk) {   // 16 keys per step
+            uint32_t phi[4], plo[4];
+#pragma unroll
+            for (uint32_t half = 0; half < 2; ++half) {       // n-blocks 2kk (keys 0..7) and 2kk+1 (keys 8..15)
+#pragma unroll
+                for (uint32_t rr = 0; rr < 2; ++rr) {         // row g, row g + 8
+                    const float p0 = sacc[2 * kk + half][2 * rr], p1 = sacc[2 * kk + half][2 * rr + 1];
+                    const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
+                    phi[half * 2 + rr] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+                    plo[half * 2 + rr] = pack_bf16(cmath::sub(p0, __bfloat162float(h0)), cmath::sub(p1, __bfloat162float(h1)));
+                }
+            }
+#pragma unroll
+            for (uint32_t db2 = 0; db2 < 8; ++db2) {          // two 8-d blocks per ldmatrix.x4.trans
+                uint32_t vf[4];
+                ldsm_x4_trans(smem_addr(v_tile) + tile_off(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * db2 + (lane >> 4)), vf);
+                mma_bf16(oacc[2 * db2], phi, vf[0], vf[1]);
+                mma_bf16(oacc[2 * db2], plo, vf[0], vf[1]);
+                mma_bf16(oacc[2 * db2 + 1], phi, vf[2], vf[3]);
+                mma_bf16(oacc[2 * db2 + 1], plo, vf[2], vf[3]);
+            }
+        }
+    }
+    la = cmath::add(la, __shfl_xor_sync(0xFFFFFFFFu, la, 1));
+    la = cmath::add(la, __shfl_xor_sync(0xFFFFFFFFu, la, 2));
+    lb = cmath::add(lb, __shfl_xor_sync(0xFFFFFFFFu, lb, 1));
+    lb = cmath::add(lb, __shfl_xor_sync(0xFFFFFFFFu, lb, 2));
+
+    __nv_bfloat16* ob = out + ((size_t)b * S * Hq + h) * kHeadDim;
+#pragma unroll
+    for (uint32_t db = 0; db < 16; ++db) {
+        const uint32_t d = db * 8 + 2 * tq;
+        if (row_a < S)
+            *reinterpret_cast<uint32_t*>(ob + (size_t)row_a * Hq * kHeadDim + d) = pack_bf16(cmath::div(oacc[db][0], la), cmath::div(oacc[db][1], la));
+        if (row_b < S)
+            *reinterpret_cast<uint32_t*>(ob + (size_t)row_b * Hq * kHeadDim + d) = pack_bf16(cmath::div(oacc[db][2], lb), cmath::div(oacc[db][3], lb));
+    }
+}
+
+}  // namespace llama
+
+// ================================================================ host side
+static int grid_for(uint64_t work_items, int threads) {
+    int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+    uint64_t blocks = ceil_div_u64(work_items, (uint64_t)threads);
+    uint64_t cap = (uint64_t)sms * 8;
+    return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+static catena_status_t launched(const char* what) {
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? CATENA_OK : fail_cuda(e, what);
+}
+
+// inverse frequencies base^(-2i/128), i < 64, on the device (one table per thread, device and base)
+struct RopeTable {
+    float* dev = nullptr;
+    uint32_t base_bits = 0;
+};
+static thread_local RopeTable g_rope[16];
+static thread_local uint32_t* g_embed_bad[16] = {nullptr};
+
+static catena_status_t rope_table(float base, const float** out) {
+    RopeTable& t = g_rope[tls().device & 15];
+    const uint32_t bits = cmath::to_bits(base);
+    if (!t.dev) CATENA_CUDA(cudaMalloc(&t.dev, 64 * sizeof(float)));
+    if (t.base_bits != bits) {
+        float host[64];
+        for (uint32_t i = 0; i < 64; ++i) {
+            const float e = -cmath::div(cmath::u32_to_f32(2 * i), 128.0f);
+            host[i] = cmath::powf_approx(base, e);
+        }
+        CATENA_CUDA(cudaMemcpyAsync(t.dev, host, sizeof(host), cudaMemcpyHostToDevice, tls().stream));
+        CATENA_CUDA(cudaStreamSynchronize(tls().stream));   // `host` is a stack array
+        t.base_bits = bits;
+    }
+    *out = t.dev;
+    return CATENA_OK;
+}
+
+static catena_status_t launch_embed(const void* table, const int32_t* ids, void* out, uint64_t tokens, uint64_t hidden, uint64_t vocab) {
+    if (hidden % 8) return fail(CATENA_E_BAD_ARG, "embed: hidden must be a multiple of 8");
+    if (!tokens) return CATENA_OK;
+    uint32_t*& bad = g_embed_bad[tls().device & 15];
+    if (!bad) {
+        CATENA_CUDA(cudaMalloc(&bad, sizeof(uint32_t)));
+        CATENA_CUDA(cudaMemset(bad, 0, sizeof(uint32_t)));
+    }
+    llama::embed_rows_kernel<<<(unsigned)tokens, 128, 0, tls().stream>>>((const uint4*)table, ids, (uint4*)out, (uint32_t)(hidden / 8),
+                                                                        (uint32_t)vocab, bad);
+    return launched("embed_rows_kernel");
+}
+// reports (and clears) an out-of-range token id seen by an earlier embedding launch; synchronises the stream
+static catena_status_t embed_check() {
+    uint32_t*& bad = g_embed_bad[tls().device & 15];
+    if (!bad) return CATENA_OK;
+    uint32_t h = 0;
+    CATENA_CUDA(cudaMemcpyAsync(&h, bad, sizeof(h), cudaMemcpyDeviceToHost, tls().stream));
+    CATENA_CUDA(cudaStreamSynchronize(tls().stream));
+    if (h) {
+        cudaMemsetAsync(bad, 0, sizeof(uint32_t), tls().stream);
+        return fail(CATENA_E_ASSERT, "embed: token id outside the table");
+    }
+    return CATENA_OK;
+}
+static catena_status_t launch_rmsnorm_rows(const void* x, void* y, uint64_t rows, uint64_t hidden) {
+    if (hidden % 8) return fail(CATENA_E_BAD_ARG, "rmsnorm: hidden must be a multiple of 8");
+    if (!rows) return CATENA_OK;
+    llama::rmsnorm_rows_kernel<<<(unsigned)rows, 256, 0, tls().stream>>>((const uint4*)x, (uint4*)y, (uint32_t)hidden);
+    return launched("rmsnorm_rows_kernel");
+}
+static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens, uint64_t seq,
+                                          uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, float base) {
+    if (!tokens) return CATENA_OK;
+    if (seq == 0 || tokens % seq) return fail(CATENA_E_BAD_ARG, "rope: tokens must be batch * seq");
+    if (pos0 + seq > cap) return fail(CATENA_E_BAD_ARG, "rope: positions beyond the cache capacity");
+    const float* inv = nullptr;
+    CATENA_TRY(rope_table(base, &inv));
+    const uint64_t work = tokens * (hq + 2 * hkv) * 64;
+    llama::rope_append_kernel<<<(unsigned)ceil_div_u64(work, 256), 256, 0, tls().stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv, (uint32_t)tokens,
+        (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
+    return launched("rope_append_kernel");
+}
+static catena_status_t launch_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
+                                           uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t cap) {
+    if (!batch || !seq) return CATENA_OK;
+    if (hkv == 0 || hq % hkv) return fail(CATENA_E_UNSUPPORTED, "attn_prefill: Hq must be a multiple of Hkv");
+    if (seq > cap) return fail(CATENA_E_BAD_ARG, "attn_prefill: sequence beyond the cache capacity");
+    static thread_local bool attr_set = false;
+    if (!attr_set) {
+        CATENA_CUDA(cudaFuncSetAttribute(llama::attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 49152));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)ceil_div_u64(seq, 64), (unsigned)hq, (unsigned)batch);
+    llama::attn_prefill_kernel<<<grid, 128, 49152, tls().stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                                                                  (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, (uint32_t)seq,
+                                                                  (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap, 1.0f / sqrtf(128.0f));
+    return launched("attn_prefill_kernel");
+}
+static catena_status_t launch_swiglu(const void* gu, void* a, uint64_t tokens, uint64_t ffn) {
+    if (ffn % 8) return fail(CATENA_E_BAD_ARG, "swiglu: ffn must be a multiple of 8");
+    if (!tokens) return CATENA_OK;
+    llama::swiglu_kernel<<<grid_for(tokens * (ffn / 8), 256), 256, 0, tls().stream>>>((const uint4*)gu, (uint4*)a, tokens, (uint32_t)(ffn / 8));
+    return launched("swiglu_kernel");
+}
+static catena_status_t launch_add(const void* x, const void* y, void* out, uint64_t n) {
+    if (n % 8) return fail(CATENA_E_BAD_ARG, "add: length must be a multiple of 8");
+    if (!n) return CATENA_OK;
+    llama::add_rows_kernel<<<grid_for(n / 8, 256), 256, 0, tls().stream>>>((const uint4*)x, (const uint4*)y, (uint4*)out, n / 8);
+    return launched("add_rows_kernel");
+}
+template <int M>
+static catena_status_t launch_skinny_m(const void* x, const void* w, const void* res, void* y, uint64_t n, uint64_t k) {
+    const size_t smem = (size_t)M * k * 2;
+    if (smem > 200 * 1024) return fail(CATENA_E_TOO_LARGE, "skinny gemm: M*K beyond shared memory");
+    CATENA_CUDA(cudaFuncSetAttribute(llama::skinny_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+    const uint64_t want = ceil_div_u64(n, 8);           // 8 warps per CTA, one column per warp at a time
+    const unsigned grid = (unsigned)(want < (uint64_t)sms * 2 ? want : (uint64_t)sms * 2);
+    llama::skinny_gemm_kernel<M><<<grid, 256, smem, tls().stream>>>((const uint4*)x, (const uint4*)w, (const __nv_bfloat16*)res,
+                                                                   (__nv_bfloat16*)y, (uint32_t)n, (uint32_t)k);
+    return launched("skinny_gemm_kernel");
+}
+// y[M,N] = x[M,K] w[N,K]^T (+ res): the skinny kernel for M <= 8, else the tcgen05 GEMM followed by the residual add
+static catena_status_t launch_linear(const void* x, const void* w, const void* res, void* y, uint64_t m, uint64_t n, uint64_t k) {
+    if (!m || !n) return CATENA_OK;
+    if (k % 8) return fail(CATENA_E_BAD_ARG, "linear: K must be a multiple of 8");
+    if (m <= 8 && m * k * 2 <= 200 * 1024) {
+        switch (m) {
+            case 1: return launch_skinny_m<1>(x, w, res, y, n, k);
+            case 2: return launch_skinny_m<2>(x, w, res, y, n, k);
+            case 3: return launch_skinny_m<3>(x, w, res, y, n, k);
+            case 4: return launch_skinny_m<4>(x, w, res, y, n, k);
+            case 5: return launch_skinny_m<5>(x, w, res, y, n, k);
+            case 6: return launch_skinny_m<6>(x, w, res, y, n, k);
+            case 7: return launch_skinny_m<7>(x, w, res, y, n, k);
+            default: return launch_skinny_m<8>(x, w, res, y, n, k);
+        }
+    }
+    CATENA_TRY(launch_gemm_tc(x, w, y, m, n, k, n, 0));
+    if (res) CATENA_TRY(launch_add(y, res, y, m * n));
+    return CATENA_OK;
+}
+
+// Runs `body` with per-launch synchronisation switched off, then restores the mode and (when blocking) waits
+// once and reports any device-side error of the kernels used.
+template <class F>
+static catena_status_t composite(F body) {
+    CATENA_TRY(ensure_device());
+    const int was_blocking = tls().blocking;
+    tls().blocking = 0;
+    catena_status_t s = body();
+    tls().blocking = was_blocking;
+    if (s != CATENA_OK) return s;
+    if (was_blocking) {
+        CATENA_CUDA(cudaStreamSynchronize(tls().stream));
+        CATENA_TRY(gemm_tc_check_errors());
+        CATENA_TRY(attn_check_errors());
+        CATENA_TRY(embed_check());
+    }
+    return CATENA_OK;
+}
+
+struct BlockDims {
+    uint64_t H, Hq, Hkv, F, qkv_cols;
+};
+static catena_status_t check_block(const catena_llama_block_t* blk, BlockDims* d) {
+    if (!blk || !blk->embedding || !blk->w_qkv || !blk->w_o || !blk->w_gate_up || !blk->w_down)
+        return fail(CATENA_E_BAD_ARG, "llama: null block or weights");
+    d->H = blk->hidden; d->Hq = blk->n_heads; d->Hkv = blk->n_kv_heads; d->F = blk->ffn;
+    if (d->H == 0 || d->H % 16 || d->F == 0 || d->F % 16) return fail(CATENA_E_BAD_ARG, "llama: hidden and ffn must be multiples of 16");
+    if (d->Hkv == 0 || d->Hq % d->Hkv || d->Hq / d->Hkv > 8) return fail(CATENA_E_UNSUPPORTED, "llama: heads must be a multiple (<= 8) of kv heads");
+    if (blk->max_len == 0 || blk->vocab == 0) return fail(CATENA_E_BAD_ARG, "llama: empty cache or vocabulary");
+    d->qkv_cols = (d->Hq + 2 * d->Hkv) * llama::kHeadDim;
+    return CATENA_OK;
+}
+// workspace (bf16 elements per token): x, n, q, attn, x2 [H or Hq*128 each], qkv, gu [2F], a [F]
+static uint64_t workspace_elems_per_token(const BlockDims& d) {
+    return 3 * d.H + 2 * d.Hq * llama::kHeadDim + d.qkv_cols + 3 * d.F;
+}
+
+static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t* ids, uint64_t batch, uint64_t seq, uint64_t pos0,
+                                 void* k_cache, void* v_cache, void* out, void* workspace, uint64_t workspace_bytes) {
+    BlockDims d;
+    CATENA_TRY(check_block(blk, &d));
+    if (!ids || !k_cache || !v_cache || !out || !workspace) return fail(CATENA_E_BAD_ARG, "llama: null argument");
+    const uint64_t T = batch * seq;
+    if (!T) return CATENA_OK;
+    if (pos0 + seq > blk->max_len) return fail(CATENA_E_BAD_ARG, "llama: positions beyond max_len");
+    if (workspace_bytes < T * workspace_elems_per_token(d) * 2) return fail(CATENA_E_BAD_ARG, "llama: workspace too small");
+    if ((uintptr_t)workspace & 255) return fail(CATENA_E_BAD_ARG, "llama: workspace must be 256-byte aligned");
+    __nv_bfloat16* ws = static_cast<__nv_bfloat16*>(workspace);
+    __nv_bfloat16* x = ws;                                   ws += T * d.H;
+    __nv_bfloat16* nrm = ws;                                 ws += T * d.H;
+    __nv_bfloat16* x2 = ws;                                  ws += T * d.H;
+    __nv_bfloat16* q = ws;                                   ws += T * d.Hq * llama::kHeadDim;
+    __nv_bfloat16* att = ws;                                 ws += T * d.Hq * llama::kHeadDim;
+    __nv_bfloat16* qkv = ws;                                 ws += T * d.qkv_cols;
+    __nv_bfloat16* gu = ws;                                  ws += T * 2 * d.F;
+    __nv_bfloat16* act = ws;
+    return composite([&]() -> catena_status_t {
+        CATENA_TRY(launch_embed(blk->embedding, ids, x, T, d.H, blk->vocab));
+        CATENA_TRY(launch_rmsnorm_rows(x, nrm, T, d.H));
+        CATENA_TRY(launch_linear(nrm, blk->w_qkv, nullptr, qkv, T, d.qkv_cols, d.H));
+        CATENA_TRY(launch_rope_append(qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, blk->rope_base));
+        if (seq == 1) {
+            CATENA_TRY(launch_attn_decode(q, k_cache, v_cache, att, batch, d.Hq, d.Hkv, llama::kHeadDim, pos0 + 1, blk->max_len, 0,
+                                          batch * d.Hkv));
+        } else {
+            if (pos0 != 0) return fail(CATENA_E_UNSUPPORTED, "llama: a multi-token step must start at position 0");
+            CATENA_TRY(launch_attn_prefill(q, k_cache, v_cache, att, batch, seq, d.Hq, d.Hkv, blk->max_len));
+        }
+        CATENA_TRY(launch_linear(att, blk->w_o, x, x2, T, d.H, d.Hq * llama::kHeadDim));
+        CATENA_TRY(launch_rmsnorm_rows(x2, nrm, T, d.H));
+        CATENA_TRY(launch_linear(nrm, blk->w_gate_up, nullptr, gu, T, 2 * d.F, d.H));
+        CATENA_TRY(launch_swiglu(gu, act, T, d.F));
+        CATENA_TRY(launch_linear(act, blk->w_down, x2, out, T, d.H, d.F));
+        return CATENA_OK;
+    });
+}
+
+extern "C" {
+
+uint64_t catena_b200_llama_workspace_bytes(const catena_llama_block_t* blk, uint64_t tokens) {
+    BlockDims d;
+    if (check_block(blk, &d) != CATENA_OK) return 0;
+    return tokens * workspace_elems_per_token(d) * 2;
+}
+catena_status_t catena_b200_llama_prefill(const catena_llama_block_t* blk, const int32_t* ids, uint64_t batch, uint64_t seq,
+                                          void* k_cache, void* v_cache, void* out, void* workspace, uint64_t workspace_bytes) {
+    return run_block(blk, ids, batch, seq, 0, k_cache, v_cache, out, workspace, workspace_bytes);
+}
+catena_status_t catena_b200_llama_decode(const catena_llama_block_t* blk, const int32_t* ids, uint64_t batch, uint64_t pos,
+                                         void* k_cache, void* v_cache, void* out, void* workspace, uint64_t workspace_bytes) {
+    return run_block(blk, ids, batch, 1, pos, k_cache, v_cache, out, workspace, workspace_bytes);
+}
+
+catena_status_t catena_b200_embed_bf16_into(const void* table, const int32_t* ids, void* out, uint64_t tokens, uint64_t hidden,
+                                            uint64_t vocab) {
+    if (!table || !ids || !out) return fail(CATENA_E_BAD_ARG, "embed: null argument");
+    return composite([&]() { return launch_embed(table, ids, out, tokens, hidden, vocab); });
+}
+catena_status_t catena_b200_rmsnorm_rows_bf16_into(const void* x, void* y, uint64_t rows, uint64_t hidden) {
+    if (!x || !y) return fail(CATENA_E_BAD_ARG, "rmsnorm: null argument");
+    return composite([&]() { return launch_rmsnorm_rows(x, y, rows, hidden); });
+}
+catena_status_t catena_b200_rope_append_bf16_into(const void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens,
+                                                  uint64_t seq, uint64_t pos0, uint64_t n_heads, uint64_t n_kv_heads, uint64_t cap,
+                                                  float rope_base) {
+    if (!qkv || !q_out || !k_cache || !v_cache) return fail(CATENA_E_BAD_ARG, "rope: null argument");
+    return composite([&]() { return launch_rope_append(qkv, q_out, k_cache, v_cache, tokens, seq, pos0, n_heads, n_kv_heads, cap, rope_base); });
+}
+catena_status_t catena_b200_attn_prefill_bf16_into(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
+                                                   uint64_t seq, uint64_t n_heads, uint64_t n_kv_heads, uint64_t cap) {
+    if (!q || !k_cache || !v_cache || !out) return fail(CATENA_E_BAD_ARG, "attn_prefill: null argument");
+    return composite([&]() { return launch_attn_prefill(q, k_cache, v_cache, out, batch, seq, n_heads, n_kv_heads, cap); });
+}
+catena_status_t catena_b200_attn_decode_bf16_cache_into(const void* q, const void* k_cache, const void* v_cache, void* o, uint64_t batch,
+                                                        uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap) {
+    return composite([&]() { return launch_attn_decode(q, k_cache, v_cache, o, batch, hq, hkv, d, kv_len, kv_cap, 0, batch * hkv); });
+}
+catena_status_t catena_b200_swiglu_bf16_into(const void* gate_up, void* out, uint64_t tokens, uint64_t ffn) {
+    if (!gate_up || !out) return fail(CATENA_E_BAD_ARG, "swiglu: null argument");
+    return composite([&]() { return launch_swiglu(gate_up, out, tokens, ffn); });
+}
+catena_status_t catena_b200_add_bf16_into(const void* x, const void* y, void* out, uint64_t n) {
+    if (!x || !y || !out) return fail(CATENA_E_BAD_ARG, "add: null argument");
+    return composite([&]() { return launch_add(x, y, out, n); });
+}
+catena_status_t catena_b200_linear_bf16_into(const void* x, const void* w, const void* residual, void* y, uint64_t m, uint64_t n,
+                                             uint64_t k) {
+    if (!x || !w || !y) return fail(CATENA_E_BAD_ARG, "linear: null argument");
+    return composite([&]() { return launch_linear(x, w, residual, y, m, n, k); });
+}
+
+}  // extern "C"
+
+}  // namespace catena

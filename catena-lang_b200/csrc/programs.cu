@@ -254,7 +254,7 @@ catena_status_t program_attn_decode_bf16_s(catena_mem_t q, catena_mem_t kc, cate
     if (kc.len != batch * hkv * kv_len * d * 2 || vc.len != kc.len)
         return fail(CATENA_E_ASSERT, "attn: cache length does not match batch*hkv*kv_len*d");
     return with_output(batch * hq * d * 2, o, [&](void* p) {
-        return launch_attn_decode(q.data, kc.data, vc.data, p, batch, hq, hkv, d, kv_len, 0, batch * hkv);
+        return launch_attn_decode(q.data, kc.data, vc.data, p, batch, hq, hkv, d, kv_len, kv_len, 0, batch * hkv);
     });
 }
 void program_attn_decode_bf16(catena_mem_t q, catena_mem_t kc, catena_mem_t vc, uint64_t batch, uint64_t hq, uint64_t hkv,
@@ -264,7 +264,7 @@ void program_attn_decode_bf16(catena_mem_t q, catena_mem_t kc, catena_mem_t vc, 
 catena_status_t catena_b200_attn_decode_bf16_into(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
                                                   uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t unit0,
                                                   uint64_t unit1) {
-    CATENA_TRY(launch_attn_decode(q, kc, vc, o, batch, hq, hkv, d, kv_len, unit0, unit1));
+    CATENA_TRY(launch_attn_decode(q, kc, vc, o, batch, hq, hkv, d, kv_len, kv_len, unit0, unit1));
     return finish("attn_decode");
 }
 

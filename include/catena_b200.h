@@ -200,6 +200,62 @@ catena_status_t catena_b200_rmsnorm_f32_into(const void* in, void* out, uint64_t
  * it before any stream capture begins.  Calls share the array, so calls whose kernels overlap on the
  * GPU race; calls issued on one stream are ordered.  The result is bit-identical to program_sum_f32. */
 catena_status_t catena_b200_sum_f32_noalloc(const void* in, uint64_t n, void* out);
+/* ---- Llama-style transformer block -----------------------------------------------------------
+ * No counterpart in the reference (it has no bf16, attention or rotary embedding): the block is
+ * composed from reference programs under the inherited rules — nn.rmsnorm without a gain vector
+ * (catena-lang/stdlib/nn.hex:125-182), the matmul cell rule for every projection
+ * (catena-lang/stdlib/matrix.hex:236-256), nn.softmax semantics with math.exp-approx for attention
+ * (nn.hex:93-122, math.hex:148-199), nn.silu for SwiGLU (nn.hex:2-56), rotary angles from math.powf
+ * and math.sin-approx-full (math.hex:91-103, 202-231; cos(x) = sin-approx-full(x + pi/2)).
+ * Parity unpinned.  All pointers are DEVICE pointers, all matrices bf16 and row-major with the
+ * contraction dimension contiguous ([out_features, in_features]); head_dim is 128.
+ *   x = embedding[ids];  q,k,v = rmsnorm(x) W_qkv^T;  rotate q,k;  append k,v to the cache
+ *   x2 = x + attention(q, cache) W_o^T;  out = x2 + (silu(g) * u) W_down^T with g,u = rmsnorm(x2) W_gate_up^T */
+typedef struct catena_llama_block_t {
+    uint64_t hidden, n_heads, n_kv_heads, ffn, vocab;
+    uint64_t max_len;        /* rows per (sequence, kv head) of the caches */
+    const void* embedding;   /* [vocab, hidden] */
+    const void* w_qkv;       /* [(n_heads + 2 n_kv_heads) * 128, hidden]: query heads, key heads, value heads */
+    const void* w_o;         /* [hidden, n_heads * 128] */
+    const void* w_gate_up;   /* [2 ffn, hidden]: gate rows, then up rows */
+    const void* w_down;      /* [hidden, ffn] */
+    float rope_base;         /* e.g. 10000 */
+} catena_llama_block_t;
+/* bytes of scratch the two calls below need for `tokens` tokens in flight (batch * seq, or batch) */
+uint64_t catena_b200_llama_workspace_bytes(const catena_llama_block_t* blk, uint64_t tokens);
+/* Prefill: ids [batch * seq] int32 (sequence-major), positions 0..seq-1, causal attention; fills rows 0..seq-1 of
+ * k_cache / v_cache [batch, n_kv_heads, max_len, 128] and writes out [batch * seq, hidden].  The workspace is
+ * caller-owned, 256-byte aligned.  An id outside the vocabulary gives CATENA_E_ASSERT (never a trap). */
+catena_status_t catena_b200_llama_prefill(const catena_llama_block_t* blk, const int32_t* ids, uint64_t batch, uint64_t seq,
+                                          void* k_cache, void* v_cache, void* out, void* workspace, uint64_t workspace_bytes);
+/* One decode step: ids [batch], every sequence at position `pos` (its cache rows 0..pos-1 are filled); appends
+ * row `pos` and writes out [batch, hidden].  Cache rows past the visible length are never read. */
+catena_status_t catena_b200_llama_decode(const catena_llama_block_t* blk, const int32_t* ids, uint64_t batch, uint64_t pos,
+                                         void* k_cache, void* v_cache, void* out, void* workspace, uint64_t workspace_bytes);
+/* The block's operators one by one (same kernels), for parity tests and other compositions. */
+catena_status_t catena_b200_embed_bf16_into(const void* table, const int32_t* ids, void* out, uint64_t tokens, uint64_t hidden,
+                                            uint64_t vocab);
+catena_status_t catena_b200_rmsnorm_rows_bf16_into(const void* x, void* y, uint64_t rows, uint64_t hidden);
+/* qkv [tokens, (n_heads + 2 n_kv_heads) * 128]; token t is sequence t / seq at position pos0 + t % seq; writes the rotated
+ * queries to q_out [tokens, n_heads, 128] and row `position` of the caches [batch, n_kv_heads, cap, 128] */
+catena_status_t catena_b200_rope_append_bf16_into(const void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens,
+                                                  uint64_t seq, uint64_t pos0, uint64_t n_heads, uint64_t n_kv_heads, uint64_t cap,
+                                                  float rope_base);
+/* causal attention of q [batch * seq, n_heads, 128] over cache rows 0..s of each sequence; out [batch * seq, n_heads * 128] */
+catena_status_t catena_b200_attn_prefill_bf16_into(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
+                                                   uint64_t seq, uint64_t n_heads, uint64_t n_kv_heads, uint64_t cap);
+/* catena_b200_attn_decode_bf16_into on caches whose units own kv_cap rows of which the first kv_len are visible */
+catena_status_t catena_b200_attn_decode_bf16_cache_into(const void* q, const void* k_cache, const void* v_cache, void* o, uint64_t batch,
+                                                        uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap);
+/* gate_up [tokens, 2 ffn] -> out [tokens, ffn] = silu(gate) * up */
+catena_status_t catena_b200_swiglu_bf16_into(const void* gate_up, void* out, uint64_t tokens, uint64_t ffn);
+/* out = x + y over n bf16 elements (n a multiple of 8; out may alias x or y) */
+catena_status_t catena_b200_add_bf16_into(const void* x, const void* y, void* out, uint64_t n);
+/* y [m, n] = x [m, k] w[n, k]^T (+ residual [m, n], added after the product is rounded to bf16).  m <= 8 runs a kernel
+ * that streams w once (HBM-bound), larger m the tensor-core GEMM. */
+catena_status_t catena_b200_linear_bf16_into(const void* x, const void* w, const void* residual, void* y, uint64_t m, uint64_t n,
+                                             uint64_t k);
+
 /* test hook: cap the persistent grid of the tensor-core GEMM (0 = one CTA per SM); results must not
  * change with it.  No counterpart in the reference. */
 void catena_b200_debug_set_cta_limit(int limit);

@@ -71,6 +71,17 @@ def lib():
         L.orc_gemm_i8_rows.argtypes = [vp, vp, u64, u64, u64, u64, vp, i32]
         L.orc_attn_decode_bf16.restype = None
         L.orc_attn_decode_bf16.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, f32, u64, u64, vp, vp, i32]
+        L.orc_embed_bf16.restype, L.orc_embed_bf16.argtypes = None, [vp, vp, vp, u64, u64]
+        L.orc_rmsnorm_rows_bf16.restype, L.orc_rmsnorm_rows_bf16.argtypes = None, [vp, vp, u64, u64, i32]
+        L.orc_rope_append_bf16.restype = None
+        L.orc_rope_append_bf16.argtypes = [vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, f32]
+        L.orc_attn_cached_bf16.restype = None
+        L.orc_attn_cached_bf16.argtypes = [vp, vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, f32, i32]
+        L.orc_swiglu_bf16.restype, L.orc_swiglu_bf16.argtypes = None, [vp, vp, u64, u64]
+        L.orc_add_bf16.restype, L.orc_add_bf16.argtypes = None, [vp, vp, vp, u64]
+        L.orc_linear_bf16.restype, L.orc_linear_bf16.argtypes = None, [vp, vp, vp, vp, u64, u64, u64, i32]
+        L.orc_llama_block.restype = None
+        L.orc_llama_block.argtypes = [u64, u64, u64, u64, u64, f32, vp, vp, vp, vp, vp, vp, u64, u64, u64, vp, vp, vp, i32]
         L.orc_max_threads.restype = i32
         L.orc_f32_to_bf16.restype, L.orc_f32_to_bf16.argtypes = C.c_uint16, [f32]
         _lib = L
@@ -195,6 +206,79 @@ def attn_decode_bf16(q, k, v, B, Hq, Hkv, D, L, scale, unit0=0, unit1=None, thre
     lib().orc_attn_decode_bf16(_p(q), _p(k), _p(v), B, Hq, Hkv, D, L, C.c_float(scale), unit0, unit1,
                                _p(o), _p(of), threads)
     return (o, of) if want_f32 else o
+
+
+def _u16(a):
+    return np.ascontiguousarray(a, dtype=np.uint16)
+
+
+def embed_bf16(table, ids):
+    table, ids = _u16(table), np.ascontiguousarray(ids, dtype=np.int32)
+    out = np.empty((ids.size, table.shape[1]), np.uint16)
+    lib().orc_embed_bf16(_p(table), _p(ids), _p(out), ids.size, table.shape[1])
+    return out
+
+
+def rmsnorm_rows_bf16(x, threads=1):
+    x = _u16(x)
+    y = np.empty_like(x)
+    lib().orc_rmsnorm_rows_bf16(_p(x), _p(y), x.shape[0], x.shape[1], threads)
+    return y
+
+
+def rope_append_bf16(qkv, k_cache, v_cache, seq, pos0, hq, hkv, base):
+    """qkv [tokens, (hq+2hkv)*128]; caches [batch, hkv, cap, 128] are updated in place; returns q [tokens, hq, 128]."""
+    qkv = _u16(qkv)
+    tokens, cap = qkv.shape[0], k_cache.shape[2]
+    q = np.empty((tokens, hq, 128), np.uint16)
+    lib().orc_rope_append_bf16(_p(qkv), _p(q), _p(k_cache), _p(v_cache), tokens, seq, pos0, hq, hkv, cap, C.c_float(base))
+    return q
+
+
+def attn_cached_bf16(q, k_cache, v_cache, batch, seq, pos0, hq, hkv, scale, threads=1, want_f32=False):
+    """Token (b, s) attends to cache rows 0..pos0+s; q [batch*seq, hq, 128] -> out [batch*seq, hq*128] (bits)."""
+    q = _u16(q)
+    cap = k_cache.shape[2]
+    out = np.empty((batch * seq, hq * 128), np.uint16)
+    of = np.empty((batch * seq, hq * 128), np.float32) if want_f32 else None
+    lib().orc_attn_cached_bf16(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(of), batch, seq, pos0, hq, hkv, cap,
+                               C.c_float(scale), threads)
+    return (out, of) if want_f32 else out
+
+
+def swiglu_bf16(gu):
+    gu = _u16(gu)
+    out = np.empty((gu.shape[0], gu.shape[1] // 2), np.uint16)
+    lib().orc_swiglu_bf16(_p(gu), _p(out), gu.shape[0], gu.shape[1] // 2)
+    return out
+
+
+def add_bf16(x, y):
+    x, y = _u16(x), _u16(y)
+    out = np.empty_like(x)
+    lib().orc_add_bf16(_p(x), _p(y), _p(out), x.size)
+    return out
+
+
+def linear_bf16(x, w, res=None, threads=1):
+    x, w = _u16(x), _u16(w)
+    res = _u16(res) if res is not None else None
+    y = np.empty((x.shape[0], w.shape[0]), np.uint16)
+    lib().orc_linear_bf16(_p(x), _p(w), _p(res), _p(y), x.shape[0], w.shape[0], x.shape[1], threads)
+    return y
+
+
+def llama_block(cfg, weights, ids, batch, seq, pos0, k_cache, v_cache, threads=1):
+    """cfg: dict(hidden, n_heads, n_kv_heads, ffn, max_len, rope_base); weights: dict of bf16-bit arrays
+    (embedding, w_qkv, w_o, w_gate_up, w_down); caches [batch, n_kv_heads, max_len, 128] updated in place."""
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    out = np.empty((batch * seq, cfg["hidden"]), np.uint16)
+    w = {k: _u16(v) for k, v in weights.items()}
+    lib().orc_llama_block(cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["ffn"], cfg["max_len"],
+                          C.c_float(cfg["rope_base"]), _p(w["embedding"]), _p(w["w_qkv"]), _p(w["w_o"]),
+                          _p(w["w_gate_up"]), _p(w["w_down"]), _p(ids), batch, seq, pos0, _p(k_cache), _p(v_cache),
+                          _p(out), threads)
+    return out
 
 
 def f32_to_bf16_bits(x):

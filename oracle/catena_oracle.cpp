@@ -434,6 +434,112 @@ void orc_attn_decode_bf16(const uint16_t* q, const uint16_t* kc, const uint16_t*
     });
 }
 
+// ---- Llama-style block, composed from reference programs (no counterpart in the reference) ----
+// Rules: nn.rmsnorm without gain (nn.hex:125-182) over the bf16 row; projections = orc_gemm_bf16_rows;
+// rotary angle = pos * powf~(base, -2i/128), sin = sin-approx-full, cos(x) = sin-approx-full(x + pi/2)
+// (math.hex:91-103, 202-231), pairs (i, i+64); attention = nn.softmax over the visible cache rows followed
+// by the cell-dot fold with the values; SwiGLU = nn.silu(gate) * up; residual = f32.add of two bf16 values.
+
+void orc_embed_bf16(const uint16_t* table, const int32_t* ids, uint16_t* out, uint64_t tokens, uint64_t hidden) {
+    for (uint64_t t = 0; t < tokens; ++t) std::memcpy(out + t * hidden, table + (uint64_t)ids[t] * hidden, hidden * 2);
+}
+
+void orc_rmsnorm_rows_bf16(const uint16_t* x, uint16_t* y, uint64_t rows, uint64_t hidden, int threads) {
+    parallel_for(rows, threads, [&](uint64_t r) {
+        const uint16_t* xr = x + r * hidden;
+        float s = reducec(bits_f32(0u), hidden, [&](uint64_t i) { float v = bf16_to_f32(xr[i]); return f32_mul(v, v); }, f32_add);
+        float rms = sqrt_newton(f32_add(f32_div(s, u64_to_f32(hidden)), bits_f32(0x3727C5ACu)));
+        for (uint64_t i = 0; i < hidden; ++i) y[r * hidden + i] = f32_to_bf16_rne(f32_div(bf16_to_f32(xr[i]), rms));
+    });
+}
+
+void orc_rope_append_bf16(const uint16_t* qkv, uint16_t* q_out, uint16_t* k_cache, uint16_t* v_cache, uint64_t tokens,
+                          uint64_t seq, uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, float base) {
+    const uint64_t heads = hq + 2 * hkv, D = 128;
+    float inv[64];
+    for (uint32_t i = 0; i < 64; ++i) inv[i] = powf_approx(base, f32_neg(f32_div(u32_to_f32(2 * i), 128.0f)));
+    for (uint64_t t = 0; t < tokens; ++t) {
+        const uint64_t b = t / seq, pos = pos0 + t % seq;
+        for (uint64_t h = 0; h < heads; ++h) {
+            const uint16_t* src = qkv + (t * heads + h) * D;
+            if (h >= hq + hkv) {
+                std::memcpy(v_cache + ((b * hkv + (h - hq - hkv)) * cap + pos) * D, src, D * 2);
+                continue;
+            }
+            uint16_t* dst = h < hq ? q_out + (t * hq + h) * D : k_cache + ((b * hkv + (h - hq)) * cap + pos) * D;
+            for (uint32_t i = 0; i < 64; ++i) {
+                const float x1 = bf16_to_f32(src[i]), x2 = bf16_to_f32(src[i + 64]);
+                const float angle = f32_mul(u32_to_f32((uint32_t)pos), inv[i]);
+                const float sn = sin_full(angle), cs = sin_full(f32_add(angle, bits_f32(0x3FC90FDBu)));
+                dst[i] = f32_to_bf16_rne(f32_sub(f32_mul(x1, cs), f32_mul(x2, sn)));
+                dst[i + 64] = f32_to_bf16_rne(f32_add(f32_mul(x2, cs), f32_mul(x1, sn)));
+            }
+        }
+    }
+}
+
+// Token (b, s) of q [batch*seq, hq, 128] attends to cache rows 0 .. pos0 + s of sequence b.
+void orc_attn_cached_bf16(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out, float* out_f32,
+                          uint64_t batch, uint64_t seq, uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, float scale,
+                          int threads) {
+    const uint64_t D = 128, group = hq / hkv;
+    parallel_for(batch * seq * hq, threads, [&](uint64_t u) {
+        const uint64_t t = u / hq, h = u % hq, b = t / seq, L = pos0 + t % seq + 1, kvh = h / group;
+        const uint16_t* qv = q + u * D;
+        const uint16_t* kb = k_cache + (b * hkv + kvh) * cap * D;
+        const uint16_t* vb = v_cache + (b * hkv + kvh) * cap * D;
+        std::vector<float> sc(L), w(L);
+        for (uint64_t j = 0; j < L; ++j) {
+            float dot = reducec(bits_f32(0u), D, [&](uint64_t d) { return f32_mul(bf16_to_f32(qv[d]), bf16_to_f32(kb[j * D + d])); }, f32_add);
+            sc[j] = f32_mul(dot, scale);
+        }
+        orc_nn_softmax(sc.data(), w.data(), L, 1);
+        for (uint64_t d = 0; d < D; ++d) {
+            float acc = reducec(bits_f32(0u), L, [&](uint64_t j) { return f32_mul(w[j], bf16_to_f32(vb[j * D + d])); }, f32_add);
+            if (out_f32) out_f32[u * D + d] = acc;
+            out[u * D + d] = f32_to_bf16_rne(acc);
+        }
+    });
+}
+
+void orc_swiglu_bf16(const uint16_t* gu, uint16_t* a, uint64_t tokens, uint64_t ffn) {
+    for (uint64_t t = 0; t < tokens; ++t)
+        for (uint64_t c = 0; c < ffn; ++c)
+            a[t * ffn + c] = f32_to_bf16_rne(f32_mul(silu(bf16_to_f32(gu[t * 2 * ffn + c])), bf16_to_f32(gu[t * 2 * ffn + ffn + c])));
+}
+
+void orc_add_bf16(const uint16_t* x, const uint16_t* y, uint16_t* out, uint64_t n) {
+    for (uint64_t i = 0; i < n; ++i) out[i] = f32_to_bf16_rne(f32_add(bf16_to_f32(x[i]), bf16_to_f32(y[i])));
+}
+
+// y [m, n] = x [m, k] w[n, k]^T, rounded to bf16, then + res (optional)
+void orc_linear_bf16(const uint16_t* x, const uint16_t* w, const uint16_t* res, uint16_t* y, uint64_t m, uint64_t n, uint64_t k,
+                     int threads) {
+    orc_gemm_bf16_rows(x, w, n, k, 0, m, y, nullptr, threads);
+    if (res) orc_add_bf16(y, res, y, m * n);
+}
+
+// The whole block for batch*seq tokens at positions pos0 .. pos0+seq-1 (prefill: pos0 = 0; decode: seq = 1).
+void orc_llama_block(uint64_t hidden, uint64_t hq, uint64_t hkv, uint64_t ffn, uint64_t cap, float rope_base,
+                     const uint16_t* embedding, const uint16_t* w_qkv, const uint16_t* w_o, const uint16_t* w_gate_up,
+                     const uint16_t* w_down, const int32_t* ids, uint64_t batch, uint64_t seq, uint64_t pos0,
+                     uint16_t* k_cache, uint16_t* v_cache, uint16_t* out, int threads) {
+    const uint64_t T = batch * seq, D = 128, qkv_cols = (hq + 2 * hkv) * D;
+    std::vector<uint16_t> x(T * hidden), nrm(T * hidden), qkv(T * qkv_cols), q(T * hq * D), att(T * hq * D), x2(T * hidden),
+        gu(T * 2 * ffn), act(T * ffn);
+    orc_embed_bf16(embedding, ids, x.data(), T, hidden);
+    orc_rmsnorm_rows_bf16(x.data(), nrm.data(), T, hidden, threads);
+    orc_linear_bf16(nrm.data(), w_qkv, nullptr, qkv.data(), T, qkv_cols, hidden, threads);
+    orc_rope_append_bf16(qkv.data(), q.data(), k_cache, v_cache, T, seq, pos0, hq, hkv, cap, rope_base);
+    orc_attn_cached_bf16(q.data(), k_cache, v_cache, att.data(), nullptr, batch, seq, pos0, hq, hkv, cap,
+                         0.08838834764831845f /* 1/sqrt(128) rounded to f32, as the kernels pass it */, threads);
+    orc_linear_bf16(att.data(), w_o, x.data(), x2.data(), T, hidden, hq * D, threads);
+    orc_rmsnorm_rows_bf16(x2.data(), nrm.data(), T, hidden, threads);
+    orc_linear_bf16(nrm.data(), w_gate_up, nullptr, gu.data(), T, 2 * ffn, hidden, threads);
+    orc_swiglu_bf16(gu.data(), act.data(), T, ffn);
+    orc_linear_bf16(act.data(), w_down, x2.data(), out, T, hidden, ffn, threads);
+}
+
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16_rne(f); }
 float orc_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }
 

@@ -1,0 +1,198 @@
+"""Llama-style block (rmsnorm, projections, rotary + cache append, causal / cached attention, SwiGLU,
+residuals) against the CPU oracle: operator by operator, then the whole block for a prefill and decode steps.
+The reference has no counterpart (parity unpinned); the oracle composes reference programs."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+
+import catena_lang_b200 as cb
+
+pytestmark = pytest.mark.gpu
+SCALE = np.float32(1.0 / math.sqrt(128.0))
+
+
+@pytest.fixture(scope="module")
+def orc():
+    import oracle
+    oracle.build()
+    return oracle
+
+
+@pytest.fixture(scope="module", autouse=True)
+def device():
+    cb.check(cb.lib().catena_b200_init(0))
+
+
+def bits(rng, shape, std=1.0):
+    import oracle
+    return oracle.f32_to_bf16_bits((rng.standard_normal(shape) * std).astype(np.float32)).reshape(shape)
+
+
+def close(got_bits, want_bits, rel=2.0 ** -7, floor=1e-5, frac_exact=0.0):
+    """bf16 outputs compared as f32 values: within `rel` of the oracle's value plus a floor; at least
+    `frac_exact` of them bit-identical."""
+    import oracle
+    g, w = oracle.bf16_bits_to_f32(np.asarray(got_bits).ravel()), oracle.bf16_bits_to_f32(np.asarray(want_bits).ravel())
+    assert np.all(np.isfinite(g))
+    err = np.abs(g - w)
+    bad = err > rel * np.abs(w) + floor
+    assert not bad.any(), f"{bad.sum()} of {bad.size} beyond tolerance, worst {err.max():.3e}"
+    assert np.mean(np.asarray(got_bits).ravel() == np.asarray(want_bits).ravel()) >= frac_exact
+
+
+def dev(a):
+    return cb.upload(np.ascontiguousarray(a))
+
+
+def alloc(nbytes):
+    m = cb.CatenaMem()
+    cb.check(cb.lib().catena_b200_mem_alloc(nbytes, C.byref(m)))
+    return m
+
+
+def test_embed_and_bad_id(orc):
+    rng = np.random.default_rng(0)
+    table = bits(rng, (50, 64))
+    ids = np.array([3, 49, 0, 7, 7], np.int32)
+    tm, im, om = dev(table), dev(ids), alloc(5 * 64 * 2)
+    cb.check(cb.lib().catena_b200_embed_bf16_into(tm.data, im.data, om.data, 5, 64, 50))
+    assert np.array_equal(cb.download(om, np.uint16).reshape(5, 64), orc.embed_bf16(table, ids))
+    bad = dev(np.array([1, 50], np.int32))
+    assert cb.lib().catena_b200_embed_bf16_into(tm.data, bad.data, om.data, 2, 64, 50) == cb.E_ASSERT
+    for m in (tm, im, om, bad):
+        cb.free(m)
+
+
+@pytest.mark.parametrize("rows,hidden", [(3, 256), (5, 2048), (2, 4096 + 64)])
+def test_rmsnorm_rows(orc, rows, hidden):
+    x = bits(np.random.default_rng(1), (rows, hidden), 3.0)
+    xm, ym = dev(x), alloc(x.nbytes)
+    cb.check(cb.lib().catena_b200_rmsnorm_rows_bf16_into(xm.data, ym.data, rows, hidden))
+    # the sum of squares is a fixed tree here and a sequential fold in the oracle: the quotient moves by an ulp at most
+    close(cb.download(ym, np.uint16), orc.rmsnorm_rows_bf16(x, threads=4), rel=2.0 ** -7, frac_exact=0.98)
+    cb.free(xm), cb.free(ym)
+
+
+def test_rope_append(orc):
+    B, S, hq, hkv, cap, pos0 = 2, 5, 4, 2, 16, 3
+    rng = np.random.default_rng(2)
+    qkv = bits(rng, (B * S, (hq + 2 * hkv) * 128))
+    kc = bits(rng, (B, hkv, cap, 128)); vc = bits(rng, (B, hkv, cap, 128))
+    kc_o, vc_o = kc.copy(), vc.copy()
+    q_o = orc.rope_append_bf16(qkv, kc_o, vc_o, S, pos0, hq, hkv, 10000.0)
+    qm, km, vm, xm = alloc(B * S * hq * 128 * 2), dev(kc), dev(vc), dev(qkv)
+    cb.check(cb.lib().catena_b200_rope_append_bf16_into(xm.data, qm.data, km.data, vm.data, B * S, S, pos0, hq, hkv, cap, 10000.0))
+    # identical operations in identical order: bit-exact
+    assert np.array_equal(cb.download(qm, np.uint16).reshape(q_o.shape), q_o)
+    assert np.array_equal(cb.download(km, np.uint16).reshape(kc.shape), kc_o)
+    assert np.array_equal(cb.download(vm, np.uint16).reshape(vc.shape), vc_o)
+    assert cb.lib().catena_b200_rope_append_bf16_into(xm.data, qm.data, km.data, vm.data, B * S, S, cap - 2, hq, hkv, cap, 10000.0) == cb.E_BAD_ARG
+    for m in (qm, km, vm, xm):
+        cb.free(m)
+
+
+@pytest.mark.parametrize("B,S,hq,hkv", [(1, 64, 2, 2), (2, 100, 4, 2), (1, 200, 8, 1), (1, 1, 1, 1)])
+def test_attn_prefill(orc, B, S, hq, hkv):
+    cap = S + 7
+    rng = np.random.default_rng(3)
+    q = bits(rng, (B * S, hq, 128)); kc = bits(rng, (B, hkv, cap, 128)); vc = bits(rng, (B, hkv, cap, 128))
+    want, want_f32 = orc.attn_cached_bf16(q, kc, vc, B, S, 0, hq, hkv, SCALE, threads=orc.max_threads(), want_f32=True)
+    qm, km, vm, om = dev(q), dev(kc), dev(vc), alloc(B * S * hq * 128 * 2)
+    cb.check(cb.lib().catena_b200_attn_prefill_bf16_into(qm.data, km.data, vm.data, om.data, B, S, hq, hkv, cap))
+    got = cb.download(om, np.uint16)
+    close(got, want, rel=2.0 ** -7, floor=4e-6, frac_exact=0.97)
+    cb.check(cb.lib().catena_b200_attn_prefill_bf16_into(qm.data, km.data, vm.data, om.data, B, S, hq, hkv, cap))
+    assert np.array_equal(got, cb.download(om, np.uint16))                 # run-to-run determinism
+    for m in (qm, km, vm, om):
+        cb.free(m)
+
+
+@pytest.mark.parametrize("B,hq,hkv,L,cap", [(2, 4, 2, 37, 64), (4, 16, 16, 300, 512), (1, 8, 2, 129, 129)])
+def test_attn_decode_with_capacity(orc, B, hq, hkv, L, cap):
+    """Cached attention on caches that own `cap` rows per unit of which `L` are visible; the rest is never read."""
+    rng = np.random.default_rng(4)
+    q = bits(rng, (B, hq, 128)); kc = bits(rng, (B, hkv, cap, 128)); vc = bits(rng, (B, hkv, cap, 128))
+    kc[:, :, L:, :] = 0x7FC0                                               # NaN beyond the visible length
+    vc[:, :, L:, :] = 0x7FC0
+    want = orc.attn_cached_bf16(q, kc, vc, B, 1, L - 1, hq, hkv, SCALE, threads=orc.max_threads())
+    qm, km, vm, om = dev(q), dev(kc), dev(vc), alloc(B * hq * 128 * 2)
+    for tc in (1, 0):
+        cb.lib().catena_b200_debug_set_attn_tc(tc)
+        try:
+            cb.check(cb.lib().catena_b200_attn_decode_bf16_cache_into(qm.data, km.data, vm.data, om.data, B, hq, hkv, 128, L, cap))
+        finally:
+            cb.lib().catena_b200_debug_set_attn_tc(1)
+        close(cb.download(om, np.uint16), want, rel=2.0 ** -7, floor=4e-6, frac_exact=0.97)
+    for m in (qm, km, vm, om):
+        cb.free(m)
+
+
+def test_swiglu_and_add(orc):
+    rng = np.random.default_rng(5)
+    gu = bits(rng, (7, 2 * 264), 2.0)
+    gm, am = dev(gu), alloc(7 * 264 * 2)
+    cb.check(cb.lib().catena_b200_swiglu_bf16_into(gm.data, am.data, 7, 264))
+    assert np.array_equal(cb.download(am, np.uint16).reshape(7, 264), orc.swiglu_bf16(gu))   # bit-exact
+    x, y = bits(rng, (1000 * 8,)), bits(rng, (1000 * 8,))
+    xm, ym = dev(x), dev(y)
+    cb.check(cb.lib().catena_b200_add_bf16_into(xm.data, ym.data, xm.data, x.size))
+    assert np.array_equal(cb.download(xm, np.uint16), orc.add_bf16(x, y))
+    for m in (gm, am, xm, ym):
+        cb.free(m)
+
+
+@pytest.mark.parametrize("m,n,k,res", [(1, 40, 256, False), (4, 300, 2048, True), (8, 64, 8192, True), (16, 256, 512, True)])
+def test_linear(orc, m, n, k, res):
+    rng = np.random.default_rng(6)
+    x, w = bits(rng, (m, k)), bits(rng, (n, k), 1.0 / math.sqrt(k))
+    r = bits(rng, (m, n)) if res else None
+    want = orc.linear_bf16(x, w, r, threads=orc.max_threads())
+    xm, wm, ym = dev(x), dev(w), alloc(m * n * 2)
+    rm = dev(r) if res else None
+    cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, rm.data if res else None, ym.data, m, n, k))
+    got = cb.download(ym, np.uint16)
+    # with a residual, a one-ulp difference of the rounded product survives the addition whatever the size of the sum
+    close(got, want, rel=2.0 ** -7, floor=3e-2 if res else 2e-5, frac_exact=0.9)
+    cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, rm.data if res else None, ym.data, m, n, k))
+    assert np.array_equal(got, cb.download(ym, np.uint16))
+    for mm in (xm, wm, ym) + ((rm,) if res else ()):
+        cb.free(mm)
+
+
+def make_block(rng, hidden, n_heads, n_kv_heads, ffn, vocab):
+    return {"embedding": bits(rng, (vocab, hidden)),
+            "w_qkv": bits(rng, ((n_heads + 2 * n_kv_heads) * 128, hidden), 1.0 / math.sqrt(hidden)),
+            "w_o": bits(rng, (hidden, n_heads * 128), 1.0 / math.sqrt(n_heads * 128)),
+            "w_gate_up": bits(rng, (2 * ffn, hidden), 1.0 / math.sqrt(hidden)),
+            "w_down": bits(rng, (hidden, ffn), 1.0 / math.sqrt(ffn))}
+
+
+@pytest.mark.parametrize("n_heads,n_kv_heads", [(2, 2), (4, 2)])
+def test_block_prefill_then_decode(orc, n_heads, n_kv_heads):
+    hidden, ffn, vocab, max_len, B, S = 256, 512, 300, 160, 2, 100
+    rng = np.random.default_rng(7)
+    weights = make_block(rng, hidden, n_heads, n_kv_heads, ffn, vocab)
+    cfg = dict(hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads, ffn=ffn, max_len=max_len, rope_base=10000.0)
+    blk = cb.LlamaBlock(hidden, n_heads, n_kv_heads, ffn, vocab, max_len, weights, B)
+    kc = np.zeros((B, n_kv_heads, max_len, 128), np.uint16); vc = np.zeros_like(kc)
+    ids = rng.integers(0, vocab, B * S).astype(np.int32)
+    try:
+        got = blk.prefill(ids, S)
+        want = orc.llama_block(cfg, weights, ids, B, S, 0, kc, vc, threads=orc.max_threads())
+        # a chain of nine rounded stages: a few bf16 ulps against the sequential-fold oracle
+        close(got, want, rel=2.0 ** -5, floor=2e-2)
+        gk, gv = blk.caches()
+        close(gk[:, :, :S], kc[:, :, :S], rel=2.0 ** -6, floor=1e-2)
+        close(gv[:, :, :S], vc[:, :, :S], rel=2.0 ** -6, floor=1e-2)
+        for step in range(3):
+            nxt = rng.integers(0, vocab, B).astype(np.int32)
+            # the oracle continues from the GPU's own caches so that one step is compared, not the accumulated drift
+            kc, vc = blk.caches()
+            want = orc.llama_block(cfg, weights, nxt, B, 1, S + step, kc, vc, threads=orc.max_threads())
+            got = blk.decode(nxt)
+            close(got, want, rel=2.0 ** -5, floor=2e-2)
+        assert blk.pos == S + 3
+    finally:
+        blk.close()
