@@ -302,6 +302,76 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+LLAMA = dict(hidden=2048, n_heads=16, n_kv_heads=16, ffn=8192, vocab=32000, batch=4, seq=2048, decode_steps=128)
+LLAMA_SMALL = dict(hidden=1024, n_heads=8, n_kv_heads=8, ffn=2048, vocab=4000, batch=2, seq=512, decode_steps=16)
+
+
+def llama_bench(cb, L, torch, dev, stream, peaks, cfg, reps=2):
+    """Llama-style block: prefill of batch x seq tokens, then decode_steps single-token steps, device-timed.
+    Weights N(0, 0.02) bf16, token ids uniform, seed 5 (synthetic).  Returns times and roofline fractions:
+    prefill against the tensor peak (projection + causal attention FLOP), decode against the copy bandwidth
+    (weights + visible KV rows read once per step)."""
+    H, Hq, Hkv, F, V = cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["ffn"], cfg["vocab"]
+    B, S, steps = cfg["batch"], cfg["seq"], cfg["decode_steps"]
+    max_len = S + steps
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    def w(rows, cols):
+        return (torch.randn((rows, cols), generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    emb, wqkv, wo, wgu, wd = w(V, H), w((Hq + 2 * Hkv) * 128, H), w(H, Hq * 128), w(2 * F, H), w(H, F)
+    blk = cb.LlamaBlockStruct(H, Hq, Hkv, F, V, max_len, emb.data_ptr(), wqkv.data_ptr(), wo.data_ptr(), wgu.data_ptr(),
+                              wd.data_ptr(), 10000.0)
+    ids = torch.randint(0, V, (B * S,), generator=g, device=dev, dtype=torch.int32)
+    step_ids = torch.randint(0, V, (steps, B), generator=g, device=dev, dtype=torch.int32)
+    kc = torch.zeros((B, Hkv, max_len, 128), dtype=torch.bfloat16, device=dev)
+    vc = torch.zeros_like(kc)
+    ws_bytes = L.catena_b200_llama_workspace_bytes(C.byref(blk), B * S)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    out = torch.empty((B * S, H), dtype=torch.bfloat16, device=dev)
+    torch.cuda.synchronize(dev)
+
+    def prefill():
+        cb.check(L.catena_b200_llama_prefill(C.byref(blk), ids.data_ptr(), B, S, kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                                             ws.data_ptr(), ws_bytes))
+
+    def decode_all():
+        for t in range(steps):
+            cb.check(L.catena_b200_llama_decode(C.byref(blk), step_ids[t].data_ptr(), B, S + t, kc.data_ptr(), vc.data_ptr(),
+                                                out.data_ptr(), ws.data_ptr(), ws_bytes))
+
+    times = {}
+    with torch.cuda.stream(stream):
+        for name, fn in (("prefill", prefill), ("decode", decode_all)):
+            fn()                                             # warm-up (also fills the caches for the decode steps)
+            torch.cuda.synchronize(dev)
+            launches0 = L.catena_b200_launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize(dev)
+            times[name] = e0.elapsed_time(e1) / reps
+            times[name + "_launches"] = (L.catena_b200_launch_count() - launches0) // reps
+    cb.check(L.catena_b200_check_device_errors())
+    params = H * (Hq + 2 * Hkv) * 128 + H * Hq * 128 + 3 * F * H
+    prefill_flop = 2.0 * B * S * params + 4.0 * B * Hq * 128 * S * (S + 1) / 2
+    decode_bytes = sum(params * 2 + 2 * B * Hkv * (S + t + 1) * 128 * 2 for t in range(steps)) / steps
+    pre_tf = prefill_flop / (times["prefill"] * 1e-3) / 1e12
+    dec_ms = times["decode"] / steps
+    dec_gbs = decode_bytes / (dec_ms * 1e-3) / 1e9
+    checksum = int(out[:B].view(torch.int16).to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF
+    return {"config": {"workload": f"Llama-style block hidden {H}, {Hq}x128 heads ({Hkv} kv), ffn {F}: prefill {B}x{S} tokens, "
+                                   f"then {steps} decode steps of {B} tokens; bf16, fp32 accumulate"},
+            "prefill_ms": times["prefill"], "prefill_tflops": pre_tf, "prefill_launches": times["prefill_launches"],
+            "prefill_roofline": {"bound": "tensor", "achieved": pre_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                 "frac": pre_tf / peaks["bf16_tflops"]},
+            "decode_ms_per_step": dec_ms, "decode_gbs": dec_gbs, "decode_launches_per_step": times["decode_launches"] // steps,
+            "decode_roofline": {"bound": "hbm", "achieved": dec_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": dec_gbs / peaks["hbm_gbs"]},
+            "end_to_end_ms": times["prefill"] + times["decode"], "output_checksum": f"{checksum:012x}"}
+
+
 def run_single(args):
     """`--only <kernel>`: a few launches of one kernel on the bench workload (or a smaller case with
     `--small`), for profiler captures and quick timing.  Prints a short JSON line."""
@@ -318,6 +388,10 @@ def run_single(args):
     which = args.only
     g = torch.Generator(device=dev)
     g.manual_seed(1)
+    if which == "llama":
+        res = llama_bench(cb, L, torch, dev, stream, measured_peaks(), LLAMA_SMALL if args.small else LLAMA, reps=max(1, min(args.steps, 3)))
+        print(json.dumps({"only": "llama", **res}), flush=True)
+        return
     if which in ("gemm", "gemm_i8"):
         m = n = k = 2048 if args.small else 4096
         if args.shape:
@@ -403,7 +477,7 @@ def run_single(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None,
-                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm"])
+                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm", "llama"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
     ap.add_argument("--gpus", type=int, default=1)

@@ -93,41 +93,64 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const uint4* __restri
 }
 
 // ---------------------------------------------------------------- rotary embedding + KV-cache append
+// cos / sin of angle = position * inv_freq[i] for positions pos0 .. pos0 + seq - 1, i < 64: the angle depends on
+// neither head nor sequence, so it is evaluated once per (position, i) instead of once per (token, head, i).
+__device__ __forceinline__ float2 rope_cos_sin(uint32_t pos, float inv_freq) {
+    const float angle = cmath::mul(cmath::u32_to_f32(pos), inv_freq);
+    return make_float2(cmath::sin_full(cmath::add(angle, cmath::from_bits(kHalfPiBits))), cmath::sin_full(angle));
+}
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __restrict__ table, uint32_t pos0, uint32_t seq) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < seq * 64) table[idx] = rope_cos_sin(pos0 + idx / 64, inv_freq[idx % 64]);
+}
+
 // qkv [T, (Hq + 2 Hkv) * 128] bf16 (one row per token: query heads, key heads, value heads).
 // Token t belongs to sequence t / S at position pos0 + t % S.  Writes
 //   q_out   [T, Hq, 128]                 rotated queries
 //   k_cache [B, Hkv, cap, 128] at pos    rotated keys
 //   v_cache [B, Hkv, cap, 128] at pos    values
-// One thread per (token, head, pair i < 64): the pair is (i, i + 64) ("rotate half").
+// One thread per (token, head, 8 pairs): pair i is (i, i + 64) ("rotate half").  `table` [S][64] holds (cos, sin)
+// per position; without it (few tokens) they are evaluated in place — the same function, the same bits.
 // inv_freq[i] = base^(-2i/128), computed once on the host with the same bit-exact functions.
 __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                   const float* __restrict__ inv_freq, uint32_t T, uint32_t S, uint32_t pos0, uint32_t Hq,
-                                   uint32_t Hkv, uint32_t cap) {
+                                   const float* __restrict__ inv_freq, const float2* __restrict__ table, uint32_t T, uint32_t S,
+                                   uint32_t pos0, uint32_t Hq, uint32_t Hkv, uint32_t cap) {
     const uint32_t heads = Hq + 2 * Hkv;
     const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (uint64_t)T * heads * 64) return;
-    const uint32_t i = (uint32_t)(idx % 64);
-    const uint32_t head = (uint32_t)((idx / 64) % heads);
-    const uint32_t t = (uint32_t)(idx / (64ull * heads));
-    const uint32_t b = t / S, pos = pos0 + t % S;
+    if (idx >= (uint64_t)T * heads * 8) return;
+    const uint32_t i0 = (uint32_t)(idx % 8) * 8;
+    const uint32_t head = (uint32_t)((idx / 8) % heads);
+    const uint32_t t = (uint32_t)(idx / (8ull * heads));
+    const uint32_t b = t / S, s = t % S, pos = pos0 + s;
     const __nv_bfloat16* src = qkv + ((size_t)t * heads + head) * kHeadDim;
-    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + 64]);
+    const uint4 lo = *reinterpret_cast<const uint4*>(src + i0), hi = *reinterpret_cast<const uint4*>(src + 64 + i0);
     if (head >= Hq + Hkv) {   // value head: plain copy
         __nv_bfloat16* dst = v_cache + (((size_t)b * Hkv + (head - Hq - Hkv)) * cap + pos) * kHeadDim;
-        dst[i] = src[i];
-        dst[i + 64] = src[i + 64];
+        *reinterpret_cast<uint4*>(dst + i0) = lo;
+        *reinterpret_cast<uint4*>(dst + 64 + i0) = hi;
         return;
     }
-    const float angle = cmath::mul(cmath::u32_to_f32(pos), inv_freq[i]);
-    const float sn = cmath::sin_full(angle);
-    const float cs = cmath::sin_full(cmath::add(angle, cmath::from_bits(kHalfPiBits)));
-    const float r1 = cmath::sub(cmath::mul(x1, cs), cmath::mul(x2, sn));
-    const float r2 = cmath::add(cmath::mul(x2, cs), cmath::mul(x1, sn));
+    const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+    uint32_t r1[4], r2[4];
+#pragma unroll
+    for (uint32_t e = 0; e < 4; ++e) {
+        float o1[2], o2[2];
+#pragma unroll
+        for (uint32_t u = 0; u < 2; ++u) {
+            const uint32_t i = i0 + 2 * e + u;
+            const float x1 = bf16_bits_to_f32(u ? lw[e] >> 16 : lw[e] & 0xFFFFu), x2 = bf16_bits_to_f32(u ? hw[e] >> 16 : hw[e] & 0xFFFFu);
+            const float2 cs = table ? table[(size_t)s * 64 + i] : rope_cos_sin(pos, inv_freq[i]);
+            o1[u] = cmath::sub(cmath::mul(x1, cs.x), cmath::mul(x2, cs.y));
+            o2[u] = cmath::add(cmath::mul(x2, cs.x), cmath::mul(x1, cs.y));
+        }
+        r1[e] = pack_bf16(o1[0], o1[1]);
+        r2[e] = pack_bf16(o2[0], o2[1]);
+    }
     __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)t * Hq + head) * kHeadDim
                                    : k_cache + (((size_t)b * Hkv + (head - Hq)) * cap + pos) * kHeadDim;
-    dst[i] = __float2bfloat16_rn(r1);
-    dst[i + 64] = __float2bfloat16_rn(r2);
+    *reinterpret_cast<uint4*>(dst + i0) = make_uint4(r1[0], r1[1], r1[2], r1[3]);
+    *reinterpret_cast<uint4*>(dst + 64 + i0) = make_uint4(r2[0], r2[1], r2[2], r2[3]);
 }
 
 // ---------------------------------------------------------------- SwiGLU and residual add
@@ -163,59 +186,90 @@ __global__ void add_rows_kernel(const uint4* x, const uint4* y, uint4* out, uint
     }
 }
 
-// ---------------------------------------------------------------- skinny GEMM (M <= 8 rows)
+// ---------------------------------------------------------------- skinny GEMM (M <= 16 rows)
 // y[m, n] = sum_k x[m, k] * w[n, k], optionally + res[m, n]; x [M, K] bf16, w [N, K] bf16 (K contiguous), y [M, N] bf16.
-// HBM-bound on w: every weight is read exactly once.  One warp per output column at a time (persistent warps
-// stride over the columns); x sits in shared memory.  Fixed order: lane l accumulates k = 8l + 256p + e for
-// p ascending, e = 0..7 ascending; then the xor butterfly over lanes.
-template <int M>
-__global__ void __launch_bounds__(256) skinny_gemm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w,
+// HBM-bound on w: every weight is read exactly once, 16 bytes per lane, and the few rows of x ride along as the other
+// operand of mma.sync m16n8k16 (tokens = the 16 rows of A, 8 weight rows = the columns of B).  On CUDA cores the
+// unfused multiply-adds of even 4 tokens would cost as many issue slots as the weights cost bandwidth.
+// A CTA owns 8 weight rows; its 8 warps take the 32-wide k blocks round-robin (warp v: blocks v, v+8, ...) and their
+// partial sums are added in ascending warp order.  Inside a k block lane (g, t) holds k = 8t..8t+7 of weight row g
+// and of tokens g, g+8: the MMA's k index is a permutation of the true one, the same for both operands.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+constexpr int kSkinnyUnroll = 8;
+// CTAs are persistent and software-pipelined: the weight loads of the next batch of k blocks (of this or the next
+// group of rows) are issued before the current batch is multiplied and reduced, so the stream never drains.
+__global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ y,
-                                                         uint32_t N, uint32_t K) {
-    extern __shared__ uint4 xs[];   // [M][K/8]
-    const uint32_t K8 = K / 8;
-    for (uint32_t i = threadIdx.x; i < M * K8; i += blockDim.x) xs[i] = x[i];
-    __syncthreads();
-    const uint32_t lane = threadIdx.x & 31, warps = gridDim.x * (blockDim.x >> 5);
-    for (uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); n < N; n += warps) {
-        const uint4* wr = w + (size_t)n * K8;
-        float acc[M];
+                                                         uint32_t M, uint32_t N, uint32_t K) {
+    __shared__ float part[8][16][8];    // [warp][token][weight row]
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t kblocks = (K + 31) / 32;
+    const uint32_t batches = (kblocks + 8 * kSkinnyUnroll - 1) / (8 * kSkinnyUnroll);   // per group and warp
+    const uint32_t groups = (N + 7) / 8;
+    const uint32_t my_groups = blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t steps = my_groups * batches;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const __nv_bfloat16* xa = x + (size_t)g * K + 8 * t;
+    const __nv_bfloat16* xb = x + (size_t)(g + 8) * K + 8 * t;
+
+    // weights of step s: group blockIdx.x + (s / batches) * gridDim.x, k blocks warp + 8 (u + kSkinnyUnroll (s % batches))
+    auto load_w = [&](uint32_t s, uint4 (&wv)[kSkinnyUnroll]) {
+        const uint32_t n0 = (blockIdx.x + (s / batches) * gridDim.x) * 8;
+        const uint32_t kb0 = warp + 8 * kSkinnyUnroll * (s % batches);
+        const __nv_bfloat16* wr = w + (size_t)(n0 + g) * K + 8 * t;
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[m] = 0.0f;
-        for (uint32_t p0 = lane; p0 < K8; p0 += 128) {
-            uint4 wv[4];
+        for (int u = 0; u < kSkinnyUnroll; ++u) {
+            const uint32_t k = (kb0 + 8 * u) * 32;
+            wv[u] = zero;
+            if (n0 + g < N && k + 8 * t < K)   // volatile: the whole batch is issued here, ahead of the (volatile) MMAs
+                asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(wv[u].x), "=r"(wv[u].y), "=r"(wv[u].z), "=r"(wv[u].w)
+                             : "l"(wr + k));
+        }
+    };
+
+    uint4 cur[kSkinnyUnroll], nxt[kSkinnyUnroll];
+    if (steps > 0) load_w(0, cur);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (uint32_t s = 0; s < steps; ++s) {
+        if (s + 1 < steps) load_w(s + 1, nxt);
+        const uint32_t kb0 = warp + 8 * kSkinnyUnroll * (s % batches);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) wv[u] = p0 + 32 * u < K8 ? __ldcs(wr + p0 + 32 * u) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < kSkinnyUnroll; ++u) {
+            const uint32_t k = (kb0 + 8 * u) * 32;
+            const bool ok = k + 8 * t < K;
+            const uint4 av = ok && g < M ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero;
+            const uint4 bv = ok && g + 8 < M ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero;
+            mma_bf16_16816(acc, av.x, bv.x, av.y, bv.y, cur[u].x, cur[u].y);
+            mma_bf16_16816(acc, av.z, bv.z, av.w, bv.w, cur[u].z, cur[u].w);
+        }
+        if (s % batches == batches - 1) {    // the group is complete: add the warps' partial sums in ascending order
+            const uint32_t n0 = (blockIdx.x + (s / batches) * gridDim.x) * 8;
+            __syncthreads();                 // the previous group's partials have been read
+            part[warp][g][2 * t] = acc[0];
+            part[warp][g][2 * t + 1] = acc[1];
+            part[warp][g + 8][2 * t] = acc[2];
+            part[warp][g + 8][2 * t + 1] = acc[3];
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+            __syncthreads();
+            if (threadIdx.x < 128) {
+                const uint32_t m = threadIdx.x >> 3, r = threadIdx.x & 7;
+                if (m < M && n0 + r < N) {
+                    float v = part[0][m][r];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (p0 + 32 * u < K8) {
-                    const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        const uint4 xv = xs[m * K8 + p0 + 32 * u];
-                        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            acc[m] = cmath::add(acc[m], cmath::mul(bf16_bits_to_f32(xw[e] & 0xFFFFu), bf16_bits_to_f32(ww[e] & 0xFFFFu)));
-                            acc[m] = cmath::add(acc[m], cmath::mul(bf16_bits_to_f32(xw[e] >> 16), bf16_bits_to_f32(ww[e] >> 16)));
-                        }
-                    }
+                    for (int wv2 = 1; wv2 < 8; ++wv2) v = cmath::add(v, part[wv2][m][r]);
+                    if (res) v = cmath::add(__bfloat162float(__float2bfloat16_rn(v)), __bfloat162float(res[(size_t)m * N + n0 + r]));
+                    y[(size_t)m * N + n0 + r] = __float2bfloat16_rn(v);
                 }
             }
         }
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) acc[m] = cmath::add(acc[m], __shfl_xor_sync(0xFFFFFFFFu, acc[m], off));
-        }
-        if (lane == 0) {
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-                float v = acc[m];
-                if (res) v = cmath::add(__bfloat162float(__float2bfloat16_rn(v)), __bfloat162float(res[(size_t)m * N + n]));
-                y[(size_t)m * N + n] = __float2bfloat16_rn(v);
-            }
-        }
+        for (int u = 0; u < kSkinnyUnroll; ++u) cur[u] = nxt[u];
     }
 }
 
@@ -253,7 +307,10 @@ __device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* ba
     }
 }
 
-__global__ void __launch_bounds__(128) attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+#ifndef CATENA_PF_MINB
+#define CATENA_PF_MINB 3
+#endif
+__global__ void __launch_bounds__(128, CATENA_PF_MINB) attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                                                           const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                                                           uint32_t S, uint32_t Hq, uint32_t Hkv, uint32_t cap, float scale) {
     extern __shared__ __align__(1024) uint8_t smem_pf[];
@@ -296,6 +353,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __nv_bfloat16* 
     float ma = ninf, mb = ninf;
     for (uint32_t kt = 0; kt <= qt; ++kt) {
         __syncthreads();
+#ifdef CATENA_PF_NOLOAD
+        if (kt == 0)
+#endif
         load_tile(k_tile, kb, kHeadDim, kt * 64, S);
         __syncthreads();
         float sacc[8][4];
@@ -324,8 +384,13 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __nv_bfloat16* 
     float la = 0.0f, lb = 0.0f;
     for (uint32_t kt = 0; kt <= qt; ++kt) {
         __syncthreads();
-        load_tile(k_tile, kb, kHeadDim, kt * 64, S);
-        load_tile(v_tile, vb, kHeadDim, kt * 64, S);
+#ifdef CATENA_PF_NOLOAD
+        if (kt == 0)
+#endif
+        {
+            load_tile(k_tile, kb, kHeadDim, kt * 64, S);
+            load_tile(v_tile, vb, kHeadDim, kt * 64, S);
+        }
         __syncthreads();
         float sacc[8][4];
         scores(sacc);
@@ -335,8 +400,13 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __nv_bfloat16* 
 #pragma unroll
             for (uint32_t e = 0; e < 2; ++e) {
                 const uint32_t key = kt * 64 + nb * 8 + 2 * tq + e;
+#ifdef CATENA_PF_NOEXP
+                const float pa = key <= row_a ? cmath::sub(cmath::mul(sacc[nb][e], scale), ma) : 0.0f;
+                const float pb = key <= row_b ? cmath::sub(cmath::mul(sacc[nb][2 + e], scale), mb) : 0.0f;
+#else
                 const float pa = key <= row_a ? cmath::exp_approx(cmath::sub(cmath::mul(sacc[nb][e], scale), ma)) : 0.0f;
                 const float pb = key <= row_b ? cmath::exp_approx(cmath::sub(cmath::mul(sacc[nb][2 + e], scale), mb)) : 0.0f;
+#endif
                 sacc[nb][e] = pa;
                 sacc[nb][2 + e] = pb;
                 la = cmath::add(la, pa);
@@ -455,6 +525,13 @@ static catena_status_t launch_rmsnorm_rows(const void* x, void* y, uint64_t rows
     llama::rmsnorm_rows_kernel<<<(unsigned)rows, 256, 0, tls().stream>>>((const uint4*)x, (uint4*)y, (uint32_t)hidden);
     return launched("rmsnorm_rows_kernel");
 }
+// (cos, sin) table of one call, [seq][64], in a per-thread buffer that only grows
+struct RopeAngles {
+    float2* dev = nullptr;
+    uint64_t positions = 0;
+};
+static thread_local RopeAngles g_rope_angles[16];
+
 static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens, uint64_t seq,
                                           uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, float base) {
     if (!tokens) return CATENA_OK;
@@ -462,10 +539,26 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
     if (pos0 + seq > cap) return fail(CATENA_E_BAD_ARG, "rope: positions beyond the cache capacity");
     const float* inv = nullptr;
     CATENA_TRY(rope_table(base, &inv));
-    const uint64_t work = tokens * (hq + 2 * hkv) * 64;
+    const float2* table = nullptr;
+    if (seq >= 16 && tokens / seq * (hq + hkv) >= 8) {   // many (sequence, head) pairs per position: evaluate each angle once
+        RopeAngles& ra = g_rope_angles[tls().device & 15];
+        if (ra.positions < seq) {
+            if (ra.dev) {
+                CATENA_CUDA(cudaStreamSynchronize(tls().stream));
+                CATENA_CUDA(cudaFree(ra.dev));
+                ra.dev = nullptr;
+            }
+            CATENA_CUDA(cudaMalloc(&ra.dev, seq * 64 * sizeof(float2)));
+            ra.positions = seq;
+        }
+        llama::rope_table_kernel<<<(unsigned)ceil_div_u64(seq * 64, 256), 256, 0, tls().stream>>>(inv, ra.dev, (uint32_t)pos0, (uint32_t)seq);
+        CATENA_TRY(launched("rope_table_kernel"));
+        table = ra.dev;
+    }
+    const uint64_t work = tokens * (hq + 2 * hkv) * 8;
     llama::rope_append_kernel<<<(unsigned)ceil_div_u64(work, 256), 256, 0, tls().stream>>>(
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv, (uint32_t)tokens,
-        (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv, table,
+        (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
     return launched("rope_append_kernel");
 }
 static catena_status_t launch_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
@@ -496,33 +589,21 @@ static catena_status_t launch_add(const void* x, const void* y, void* out, uint6
     llama::add_rows_kernel<<<grid_for(n / 8, 256), 256, 0, tls().stream>>>((const uint4*)x, (const uint4*)y, (uint4*)out, n / 8);
     return launched("add_rows_kernel");
 }
-template <int M>
-static catena_status_t launch_skinny_m(const void* x, const void* w, const void* res, void* y, uint64_t n, uint64_t k) {
-    const size_t smem = (size_t)M * k * 2;
-    if (smem > 200 * 1024) return fail(CATENA_E_TOO_LARGE, "skinny gemm: M*K beyond shared memory");
-    CATENA_CUDA(cudaFuncSetAttribute(llama::skinny_gemm_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int sms = tls().sm_count > 0 ? tls().sm_count : 148;
-    const uint64_t want = ceil_div_u64(n, 8);           // 8 warps per CTA, one column per warp at a time
-    const unsigned grid = (unsigned)(want < (uint64_t)sms * 2 ? want : (uint64_t)sms * 2);
-    llama::skinny_gemm_kernel<M><<<grid, 256, smem, tls().stream>>>((const uint4*)x, (const uint4*)w, (const __nv_bfloat16*)res,
-                                                                   (__nv_bfloat16*)y, (uint32_t)n, (uint32_t)k);
-    return launched("skinny_gemm_kernel");
-}
-// y[M,N] = x[M,K] w[N,K]^T (+ res): the skinny kernel for M <= 8, else the tcgen05 GEMM followed by the residual add
+// y[M,N] = x[M,K] w[N,K]^T (+ res): the skinny kernel for M <= 16, else the tcgen05 GEMM followed by the residual add
 static catena_status_t launch_linear(const void* x, const void* w, const void* res, void* y, uint64_t m, uint64_t n, uint64_t k) {
     if (!m || !n) return CATENA_OK;
-    if (k % 8) return fail(CATENA_E_BAD_ARG, "linear: K must be a multiple of 8");
-    if (m <= 8 && m * k * 2 <= 200 * 1024) {
-        switch (m) {
-            case 1: return launch_skinny_m<1>(x, w, res, y, n, k);
-            case 2: return launch_skinny_m<2>(x, w, res, y, n, k);
-            case 3: return launch_skinny_m<3>(x, w, res, y, n, k);
-            case 4: return launch_skinny_m<4>(x, w, res, y, n, k);
-            case 5: return launch_skinny_m<5>(x, w, res, y, n, k);
-            case 6: return launch_skinny_m<6>(x, w, res, y, n, k);
-            case 7: return launch_skinny_m<7>(x, w, res, y, n, k);
-            default: return launch_skinny_m<8>(x, w, res, y, n, k);
-        }
+    if (k == 0 || k % 8) return fail(CATENA_E_BAD_ARG, "linear: K must be a positive multiple of 8");
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail(CATENA_E_BAD_ARG, "linear: operands must be 16-byte aligned");
+    if (m <= 16) {
+        if (n > 0x7FFFFFFFull || k > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "linear: dimension too large");
+        int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+        // persistent CTAs (two per SM), the same number of row groups for each of them where possible
+        const uint64_t groups = ceil_div_u64(n, 8), slots = (uint64_t)sms * 2;
+        const uint64_t rounds = ceil_div_u64(groups, slots);
+        const unsigned grid = (unsigned)ceil_div_u64(groups, rounds);
+        llama::skinny_gemm_kernel<<<grid, 256, 0, tls().stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)res,
+                                                                 (__nv_bfloat16*)y, (uint32_t)m, (uint32_t)n, (uint32_t)k);
+        return launched("skinny_gemm_kernel");
     }
     CATENA_TRY(launch_gemm_tc(x, w, y, m, n, k, n, 0));
     if (res) CATENA_TRY(launch_add(y, res, y, m * n));

@@ -251,8 +251,8 @@ catena_status_t catena_b200_attn_decode_bf16_cache_into(const void* q, const voi
 catena_status_t catena_b200_swiglu_bf16_into(const void* gate_up, void* out, uint64_t tokens, uint64_t ffn);
 /* out = x + y over n bf16 elements (n a multiple of 8; out may alias x or y) */
 catena_status_t catena_b200_add_bf16_into(const void* x, const void* y, void* out, uint64_t n);
-/* y [m, n] = x [m, k] w[n, k]^T (+ residual [m, n], added after the product is rounded to bf16).  m <= 8 runs a kernel
- * that streams w once (HBM-bound), larger m the tensor-core GEMM. */
+/* y [m, n] = x [m, k] w[n, k]^T (+ residual [m, n], added after the product is rounded to bf16).  m <= 16 runs a kernel
+ * that streams w once (HBM-bound), larger m the tcgen05 GEMM. */
 catena_status_t catena_b200_linear_bf16_into(const void* x, const void* w, const void* residual, void* y, uint64_t m, uint64_t n,
                                              uint64_t k);
 

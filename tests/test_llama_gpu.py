@@ -75,8 +75,9 @@ def test_rmsnorm_rows(orc, rows, hidden):
     cb.free(xm), cb.free(ym)
 
 
-def test_rope_append(orc):
-    B, S, hq, hkv, cap, pos0 = 2, 5, 4, 2, 16, 3
+@pytest.mark.parametrize("B,S,hq,hkv", [(2, 5, 4, 2), (1, 3, 2, 1)])      # angles from a table / evaluated in place
+def test_rope_append(orc, B, S, hq, hkv):
+    cap, pos0 = 16, 3
     rng = np.random.default_rng(2)
     qkv = bits(rng, (B * S, (hq + 2 * hkv) * 128))
     kc = bits(rng, (B, hkv, cap, 128)); vc = bits(rng, (B, hkv, cap, 128))
