@@ -28,6 +28,13 @@ constexpr int kHeadDim = 128;
 constexpr uint32_t kEpsBits = 0x3727C5ACu;      // 1e-5, nn.hex:154-182
 constexpr uint32_t kHalfPiBits = 0x3FC90FDBu;   // pi/2 rounded to f32
 
+// Programmatic dependent launch: every kernel of this file lets the next launch in the stream begin at once
+// (pdl_trigger) and itself waits for the complete results of everything launched before it (pdl_wait) only when it
+// first touches data another kernel may have written — launch latency and, in the skinny GEMM, the first batch of
+// weight loads overlap the predecessor's tail.  Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
 __device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
     return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
@@ -38,6 +45,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return f32_t
 // out[t, :] = table[ids[t], :]; one CTA per token, 16-byte pieces.  An id outside the table sets *bad.
 __global__ void embed_rows_kernel(const uint4* __restrict__ table, const int32_t* __restrict__ ids, uint4* __restrict__ out,
                                   uint32_t hidden16, uint32_t vocab, uint32_t* bad) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t t = blockIdx.x;
     const int32_t id = ids[t];
     if (id < 0 || (uint32_t)id >= vocab) {
@@ -52,14 +61,29 @@ __global__ void embed_rows_kernel(const uint4* __restrict__ table, const int32_t
 // ---------------------------------------------------------------- row rmsnorm (bf16 in / out)
 // One CTA of 256 threads per row.  Sum of squares in a fixed shape: thread t adds its elements in ascending
 // order (8 consecutive elements per 2048-element stride), xor butterfly per warp, warps added in ascending order.
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, uint32_t hidden) {
+// With `ids` the row is gathered from the embedding table `x` first (and copied to x_out): embedding + first norm
+// of the block in one launch.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ ids, uint32_t vocab,
+                                                          uint32_t* bad, uint4* __restrict__ x_out, uint4* __restrict__ y, uint32_t hidden) {
     __shared__ float warp_sum[8];
     __shared__ float rms_s;
+    pdl_trigger();
+    pdl_wait();
     const uint32_t row = blockIdx.x, tid = threadIdx.x;
-    const uint4* xr = x + (size_t)row * (hidden / 8);
+    size_t src_row = row;
+    if (ids) {
+        const int32_t id = ids[row];
+        if (id < 0 || (uint32_t)id >= vocab) {
+            if (tid == 0) atomicExch(bad, 1u);
+            return;
+        }
+        src_row = (size_t)id;
+    }
+    const uint4* xr = x + src_row * (hidden / 8);
     float acc = 0.0f;
     for (uint32_t i = tid; i < hidden / 8; i += 256) {
         const uint4 v = xr[i];
+        if (x_out) x_out[(size_t)row * (hidden / 8) + i] = v;
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -100,6 +124,8 @@ __device__ __forceinline__ float2 rope_cos_sin(uint32_t pos, float inv_freq) {
     return make_float2(cmath::sin_full(cmath::add(angle, cmath::from_bits(kHalfPiBits))), cmath::sin_full(angle));
 }
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __restrict__ table, uint32_t pos0, uint32_t seq) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < seq * 64) table[idx] = rope_cos_sin(pos0 + idx / 64, inv_freq[idx % 64]);
 }
@@ -116,6 +142,8 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_b
                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                    const float* __restrict__ inv_freq, const float2* __restrict__ table, uint32_t T, uint32_t S,
                                    uint32_t pos0, uint32_t Hq, uint32_t Hkv, uint32_t cap) {
+    pdl_trigger();
+    pdl_wait();
     const uint32_t heads = Hq + 2 * Hkv;
     const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (uint64_t)T * heads * 8) return;
@@ -156,6 +184,8 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_b
 // ---------------------------------------------------------------- SwiGLU and residual add
 // gu [T, 2F] bf16 (gate columns, then up columns) -> a [T, F] = silu(gate) * up
 __global__ void swiglu_kernel(const uint4* __restrict__ gu, uint4* __restrict__ a, uint64_t T, uint32_t F8) {
+    pdl_trigger();
+    pdl_wait();
     const uint64_t n = T * F8;
     for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t t = idx / F8, c = idx % F8;
@@ -174,6 +204,8 @@ __global__ void swiglu_kernel(const uint4* __restrict__ gu, uint4* __restrict__ 
 
 // out = x + y (bf16, fp32 add, RNE); out may alias x or y
 __global__ void add_rows_kernel(const uint4* x, const uint4* y, uint4* out, uint64_t n8) {
+    pdl_trigger();
+    pdl_wait();
     for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n8; idx += (uint64_t)gridDim.x * blockDim.x) {
         const uint4 a = x[idx], b = y[idx];
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
@@ -234,7 +266,9 @@ __global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16
     };
 
     uint4 cur[kSkinnyUnroll], nxt[kSkinnyUnroll];
-    if (steps > 0) load_w(0, cur);
+    pdl_trigger();
+    if (steps > 0) load_w(0, cur);      // weights are never written by a kernel: they may be fetched before the wait
+    pdl_wait();
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (uint32_t s = 0; s < steps; ++s) {
         if (s + 1 < steps) load_w(s + 1, nxt);
@@ -296,26 +330,55 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// copies rows [row0, row0 + 64) of a [rows_total, 128] bf16 matrix (row pitch `pitch` elements) into a swizzled tile;
-// rows past rows_total are filled with zeros
-__device__ __forceinline__ void load_tile(uint8_t* tile, const __nv_bfloat16* base, size_t pitch, uint32_t row0, uint32_t rows_total) {
+// copies rows [row0, row0 + 64) of a [rows_total, 128] bf16 matrix (row pitch `pitch` elements) into a swizzled tile
+// with cp.async (one commit group per call); rows past rows_total are filled with zeros
+__device__ __forceinline__ void load_tile_async(uint8_t* tile, const __nv_bfloat16* base, size_t pitch, uint32_t row0, uint32_t rows_total) {
     for (uint32_t i = threadIdx.x; i < 64 * 16; i += 128) {
         const uint32_t r = i >> 4, c = i & 15;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row0 + r < rows_total) v = *reinterpret_cast<const uint4*>(base + (size_t)(row0 + r) * pitch + c * 8);
-        *reinterpret_cast<uint4*>(tile + tile_off(r, c)) = v;
+        const bool ok = row0 + r < rows_total;
+        const __nv_bfloat16* src = base + (size_t)(ok ? row0 + r : 0) * pitch + c * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(tile + tile_off(r, c))), "l"(src), "r"(ok ? 16u : 0u)
+                     : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// math.exp-approx (catena-lang/stdlib/math.hex:148-199) for x <= 0, bit-identical to cmath::exp_approx there, with the
+// conversions taken off the slow pipe: round-to-nearest-even of t in [0, 2^22) through the 1.5 * 2^23 constant
+// (the same integer and the same float as (uint32_t)nearbyintf(t) and its conversion back).
+__device__ __forceinline__ float exp_approx_nonpos(float x) {
+    const float mag = -x;
+    const float t = cmath::mul(mag, cmath::from_bits(0x3FB8AA3Bu));
+    const float shifted = cmath::add(t, 12582912.0f);
+    const float kf = cmath::sub(shifted, 12582912.0f);
+    const uint32_t k = __float_as_uint(shifted) - 0x4B400000u;
+    float xr = cmath::sub(mag, cmath::mul(kf, cmath::from_bits(0x3F317200u)));
+    xr = cmath::sub(xr, cmath::mul(kf, cmath::from_bits(0x35BFBE8Eu)));
+    float p = cmath::add(cmath::from_bits(0x3EEF1187u), cmath::mul(xr, cmath::from_bits(0x3E738A8Bu)));
+    p = cmath::add(cmath::from_bits(0x3F809C7Eu), cmath::mul(xr, p));
+    p = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr, p));
+    p = cmath::mul(p, cmath::from_bits((k + 0x7Fu) * 0x00800000u));
+    return x < 0.0f ? cmath::recip(p) : p;
+}
+// two probabilities -> packed bf16 hi parts and packed bf16 lo parts (p - hi), one conversion instruction each
+__device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    const float r0 = cmath::sub(p0, __uint_as_float(hi << 16)), r1 = cmath::sub(p1, __uint_as_float(hi & 0xFFFF0000u));
+    const __nv_bfloat162 l = __floats2bfloat162_rn(r0, r1);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-#ifndef CATENA_PF_MINB
-#define CATENA_PF_MINB 3
-#endif
-__global__ void __launch_bounds__(128, CATENA_PF_MINB) attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
-                                                          const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
-                                                          uint32_t S, uint32_t Hq, uint32_t Hkv, uint32_t cap, float scale) {
+// Tiles stream through three 16 KiB buffers with cp.async: the K tile of step kt+1 is in flight while step kt is
+// multiplied (two K buffers, one of them the Q tile's once the query fragments sit in registers), the V tile of
+// step kt is in flight during Q K^T and exp~ of step kt.
+__global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                                                             const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                                                             uint32_t S, uint32_t Hq, uint32_t Hkv, uint32_t cap, float scale) {
     extern __shared__ __align__(1024) uint8_t smem_pf[];
-    uint8_t* q_tile = smem_pf;
-    uint8_t* k_tile = smem_pf + 16384;
+    uint8_t* kbuf[2] = {smem_pf, smem_pf + 16384};           // kbuf[0] first holds the Q tile
     uint8_t* v_tile = smem_pf + 32768;
     const uint32_t qt = gridDim.x - 1 - blockIdx.x;          // heavy tiles first
     const uint32_t h = blockIdx.y, b = blockIdx.z, kvh = h / (Hq / Hkv);
@@ -324,17 +387,22 @@ __global__ void __launch_bounds__(128, CATENA_PF_MINB) attn_prefill_kernel(const
     const __nv_bfloat16* kb = k_cache + ((size_t)b * Hkv + kvh) * cap * kHeadDim;    // row pitch 128
     const __nv_bfloat16* vb = v_cache + ((size_t)b * Hkv + kvh) * cap * kHeadDim;
     const float ninf = __uint_as_float(0xFF800000u);
+    pdl_trigger();
+    pdl_wait();
 
-    load_tile(q_tile, qb, (size_t)Hq * kHeadDim, qt * 64, S);
+    load_tile_async(kbuf[0], qb, (size_t)Hq * kHeadDim, qt * 64, S);
+    load_tile_async(kbuf[1], kb, kHeadDim, 0, S);            // K tile 0 of pass 1 (step parity is shifted by one in pass 1)
+    cp_async_wait<1>();
     __syncthreads();
     uint32_t qa[8][4];   // A fragments of this warp's 16 query rows, one per 16-d step
 #pragma unroll
     for (uint32_t ks = 0; ks < 8; ++ks)
-        ldsm_x4(smem_addr(q_tile) + tile_off(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), qa[ks]);
+        ldsm_x4(smem_addr(kbuf[0]) + tile_off(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), qa[ks]);
     const uint32_t row_a = qt * 64 + warp * 16 + g, row_b = row_a + 8;   // the two query rows of this thread
+    __syncthreads();     // every warp holds its fragments: kbuf[0] may be overwritten
 
-    // S tile = Q K^T for the 64 keys in k_tile: sacc[nb] covers keys 8 nb .. 8 nb + 7
-    auto scores = [&](float (&sacc)[8][4]) {
+    // S tile = Q K^T for the 64 keys in `tile`: sacc[nb] covers keys 8 nb .. 8 nb + 7
+    auto scores = [&](const uint8_t* tile, float (&sacc)[8][4]) {
 #pragma unroll
         for (uint32_t nb = 0; nb < 8; ++nb) {
 #pragma unroll
@@ -342,24 +410,25 @@ __global__ void __launch_bounds__(128, CATENA_PF_MINB) attn_prefill_kernel(const
 #pragma unroll
             for (uint32_t ks2 = 0; ks2 < 4; ++ks2) {   // two 16-d steps per ldmatrix.x4
                 uint32_t kf[4];
-                ldsm_x4(smem_addr(k_tile) + tile_off(nb * 8 + (lane & 7), 4 * ks2 + (lane >> 3)), kf);
+                ldsm_x4(smem_addr(tile) + tile_off(nb * 8 + (lane & 7), 4 * ks2 + (lane >> 3)), kf);
                 mma_bf16(sacc[nb], qa[2 * ks2], kf[0], kf[1]);
                 mma_bf16(sacc[nb], qa[2 * ks2 + 1], kf[2], kf[3]);
             }
         }
     };
 
-    // ---- pass 1: row maxima over every visible key ----
+    // ---- pass 1: row maxima over every visible key; K tile kt sits in kbuf[(kt + 1) & 1] ----
     float ma = ninf, mb = ninf;
     for (uint32_t kt = 0; kt <= qt; ++kt) {
-        __syncthreads();
-#ifdef CATENA_PF_NOLOAD
-        if (kt == 0)
-#endif
-        load_tile(k_tile, kb, kHeadDim, kt * 64, S);
+        if (kt < qt) {
+            load_tile_async(kbuf[kt & 1], kb, kHeadDim, (kt + 1) * 64, S);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
         __syncthreads();
         float sacc[8][4];
-        scores(sacc);
+        scores(kbuf[(kt + 1) & 1], sacc);
 #pragma unroll
         for (uint32_t nb = 0; nb < 8; ++nb) {
 #pragma unroll
@@ -369,63 +438,57 @@ __global__ void __launch_bounds__(128, CATENA_PF_MINB) attn_prefill_kernel(const
                 if (key <= row_b) mb = fmaxf(mb, cmath::mul(sacc[nb][2 + e], scale));
             }
         }
+        __syncthreads();     // the buffer read here is the target of the load issued at the top of the next step
     }
     ma = fmaxf(ma, __shfl_xor_sync(0xFFFFFFFFu, ma, 1));
     ma = fmaxf(ma, __shfl_xor_sync(0xFFFFFFFFu, ma, 2));
     mb = fmaxf(mb, __shfl_xor_sync(0xFFFFFFFFu, mb, 1));
     mb = fmaxf(mb, __shfl_xor_sync(0xFFFFFFFFu, mb, 2));
 
-    // ---- pass 2: probabilities and O += P V ----
+    // ---- pass 2: probabilities and O += P V; K tile kt sits in kbuf[kt & 1], V tile kt in v_tile ----
     float oacc[16][4];
 #pragma unroll
     for (int db = 0; db < 16; ++db)
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[db][e] = 0.0f;
     float la = 0.0f, lb = 0.0f;
+    load_tile_async(kbuf[0], kb, kHeadDim, 0, S);
+    load_tile_async(v_tile, vb, kHeadDim, 0, S);
     for (uint32_t kt = 0; kt <= qt; ++kt) {
-        __syncthreads();
-#ifdef CATENA_PF_NOLOAD
-        if (kt == 0)
-#endif
-        {
-            load_tile(k_tile, kb, kHeadDim, kt * 64, S);
-            load_tile(v_tile, vb, kHeadDim, kt * 64, S);
+        // groups in flight, oldest first: K(kt), V(kt) [, K(kt+1)]
+        if (kt < qt) {
+            load_tile_async(kbuf[(kt + 1) & 1], kb, kHeadDim, (kt + 1) * 64, S);
+            cp_async_wait<2>();
+        } else {
+            cp_async_wait<1>();
         }
         __syncthreads();
         float sacc[8][4];
-        scores(sacc);
+        scores(kbuf[kt & 1], sacc);
         // probabilities in place (masked keys: 0), denominators in ascending key order
 #pragma unroll
         for (uint32_t nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (uint32_t e = 0; e < 2; ++e) {
                 const uint32_t key = kt * 64 + nb * 8 + 2 * tq + e;
-#ifdef CATENA_PF_NOEXP
-                const float pa = key <= row_a ? cmath::sub(cmath::mul(sacc[nb][e], scale), ma) : 0.0f;
-                const float pb = key <= row_b ? cmath::sub(cmath::mul(sacc[nb][2 + e], scale), mb) : 0.0f;
-#else
-                const float pa = key <= row_a ? cmath::exp_approx(cmath::sub(cmath::mul(sacc[nb][e], scale), ma)) : 0.0f;
-                const float pb = key <= row_b ? cmath::exp_approx(cmath::sub(cmath::mul(sacc[nb][2 + e], scale), mb)) : 0.0f;
-#endif
+                const float pa = key <= row_a ? exp_approx_nonpos(cmath::sub(cmath::mul(sacc[nb][e], scale), ma)) : 0.0f;
+                const float pb = key <= row_b ? exp_approx_nonpos(cmath::sub(cmath::mul(sacc[nb][2 + e], scale), mb)) : 0.0f;
                 sacc[nb][e] = pa;
                 sacc[nb][2 + e] = pb;
                 la = cmath::add(la, pa);
                 lb = cmath::add(lb, pb);
             }
         }
+        if (kt < qt) cp_async_wait<1>(); else cp_async_wait<0>();     // V(kt) has landed (K(kt+1) may still fly)
+        __syncthreads();
 #pragma unroll
         for (uint32_t kk = 0; kk < 4; ++kk) {   // 16 keys per step
             uint32_t phi[4], plo[4];
 #pragma unroll
-            for (uint32_t half = 0; half < 2; ++half) {       // n-blocks 2kk (keys 0..7) and 2kk+1 (keys 8..15)
+            for (uint32_t half = 0; half < 2; ++half)         // n-blocks 2kk (keys 0..7) and 2kk+1 (keys 8..15)
 #pragma unroll
-                for (uint32_t rr = 0; rr < 2; ++rr) {         // row g, row g + 8
-                    const float p0 = sacc[2 * kk + half][2 * rr], p1 = sacc[2 * kk + half][2 * rr + 1];
-                    const __nv_bfloat16 h0 = __float2bfloat16_rn(p0), h1 = __float2bfloat16_rn(p1);
-                    phi[half * 2 + rr] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
-                    plo[half * 2 + rr] = pack_bf16(cmath::sub(p0, __bfloat162float(h0)), cmath::sub(p1, __bfloat162float(h1)));
-                }
-            }
+                for (uint32_t rr = 0; rr < 2; ++rr)           // row g, row g + 8
+                    split_hi_lo(sacc[2 * kk + half][2 * rr], sacc[2 * kk + half][2 * rr + 1], phi[half * 2 + rr], plo[half * 2 + rr]);
 #pragma unroll
             for (uint32_t db2 = 0; db2 < 8; ++db2) {          // two 8-d blocks per ldmatrix.x4.trans
                 uint32_t vf[4];
@@ -436,6 +499,8 @@ __global__ void __launch_bounds__(128, CATENA_PF_MINB) attn_prefill_kernel(const
                 mma_bf16(oacc[2 * db2 + 1], plo, vf[2], vf[3]);
             }
         }
+        __syncthreads();     // v_tile and kbuf[kt & 1] are free again
+        if (kt < qt) load_tile_async(v_tile, vb, kHeadDim, (kt + 1) * 64, S);
     }
     la = cmath::add(la, __shfl_xor_sync(0xFFFFFFFFu, la, 1));
     la = cmath::add(la, __shfl_xor_sync(0xFFFFFFFFu, la, 2));
@@ -461,6 +526,24 @@ static int grid_for(uint64_t work_items, int threads) {
     uint64_t blocks = ceil_div_u64(work_items, (uint64_t)threads);
     uint64_t cap = (uint64_t)sms * 8;
     return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+// Launch on the thread's stream with programmatic stream serialisation allowed (see pdl_trigger / pdl_wait).
+template <class... KArgs, class... Args>
+static catena_status_t launch_pdl(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = tls().stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return fail_cuda(e, what);
+    count_launch();
+    return CATENA_OK;
 }
 static catena_status_t launched(const char* what) {
     count_launch();
@@ -502,9 +585,8 @@ static catena_status_t launch_embed(const void* table, const int32_t* ids, void*
         CATENA_CUDA(cudaMalloc(&bad, sizeof(uint32_t)));
         CATENA_CUDA(cudaMemset(bad, 0, sizeof(uint32_t)));
     }
-    llama::embed_rows_kernel<<<(unsigned)tokens, 128, 0, tls().stream>>>((const uint4*)table, ids, (uint4*)out, (uint32_t)(hidden / 8),
-                                                                        (uint32_t)vocab, bad);
-    return launched("embed_rows_kernel");
+    return launch_pdl("embed_rows_kernel", llama::embed_rows_kernel, dim3((unsigned)tokens), dim3(128), 0, (const uint4*)table, ids,
+                      (uint4*)out, (uint32_t)(hidden / 8), (uint32_t)vocab, bad);
 }
 // reports (and clears) an out-of-range token id seen by an earlier embedding launch; synchronises the stream
 static catena_status_t embed_check() {
@@ -522,8 +604,8 @@ static catena_status_t embed_check() {
 static catena_status_t launch_rmsnorm_rows(const void* x, void* y, uint64_t rows, uint64_t hidden) {
     if (hidden % 8) return fail(CATENA_E_BAD_ARG, "rmsnorm: hidden must be a multiple of 8");
     if (!rows) return CATENA_OK;
-    llama::rmsnorm_rows_kernel<<<(unsigned)rows, 256, 0, tls().stream>>>((const uint4*)x, (uint4*)y, (uint32_t)hidden);
-    return launched("rmsnorm_rows_kernel");
+    return launch_pdl("rmsnorm_rows_kernel", llama::rmsnorm_rows_kernel, dim3((unsigned)rows), dim3(256), 0, (const uint4*)x,
+                      (const int32_t*)nullptr, 0u, (uint32_t*)nullptr, (uint4*)nullptr, (uint4*)y, (uint32_t)hidden);
 }
 // (cos, sin) table of one call, [seq][64], in a per-thread buffer that only grows
 struct RopeAngles {
@@ -532,6 +614,19 @@ struct RopeAngles {
 };
 static thread_local RopeAngles g_rope_angles[16];
 
+// x = table[ids], y = rmsnorm(x) in one launch
+static catena_status_t launch_embed_rmsnorm(const void* table, const int32_t* ids, void* x, void* y, uint64_t tokens, uint64_t hidden,
+                                            uint64_t vocab) {
+    if (hidden % 8) return fail(CATENA_E_BAD_ARG, "embed: hidden must be a multiple of 8");
+    if (!tokens) return CATENA_OK;
+    uint32_t*& bad = g_embed_bad[tls().device & 15];
+    if (!bad) {
+        CATENA_CUDA(cudaMalloc(&bad, sizeof(uint32_t)));
+        CATENA_CUDA(cudaMemset(bad, 0, sizeof(uint32_t)));
+    }
+    return launch_pdl("rmsnorm_rows_kernel", llama::rmsnorm_rows_kernel, dim3((unsigned)tokens), dim3(256), 0, (const uint4*)table, ids,
+                      (uint32_t)vocab, bad, (uint4*)x, (uint4*)y, (uint32_t)hidden);
+}
 static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens, uint64_t seq,
                                           uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, float base) {
     if (!tokens) return CATENA_OK;
@@ -551,15 +646,14 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
             CATENA_CUDA(cudaMalloc(&ra.dev, seq * 64 * sizeof(float2)));
             ra.positions = seq;
         }
-        llama::rope_table_kernel<<<(unsigned)ceil_div_u64(seq * 64, 256), 256, 0, tls().stream>>>(inv, ra.dev, (uint32_t)pos0, (uint32_t)seq);
-        CATENA_TRY(launched("rope_table_kernel"));
+        CATENA_TRY(launch_pdl("rope_table_kernel", llama::rope_table_kernel, dim3((unsigned)ceil_div_u64(seq * 64, 256)), dim3(256), 0, inv,
+                              ra.dev, (uint32_t)pos0, (uint32_t)seq));
         table = ra.dev;
     }
     const uint64_t work = tokens * (hq + 2 * hkv) * 8;
-    llama::rope_append_kernel<<<(unsigned)ceil_div_u64(work, 256), 256, 0, tls().stream>>>(
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv, table,
-        (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
-    return launched("rope_append_kernel");
+    return launch_pdl("rope_append_kernel", llama::rope_append_kernel, dim3((unsigned)ceil_div_u64(work, 256)), dim3(256), 0,
+                      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv, table,
+                      (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
 }
 static catena_status_t launch_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
                                            uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t cap) {
@@ -572,22 +666,21 @@ static catena_status_t launch_attn_prefill(const void* q, const void* k_cache, c
         attr_set = true;
     }
     dim3 grid((unsigned)ceil_div_u64(seq, 64), (unsigned)hq, (unsigned)batch);
-    llama::attn_prefill_kernel<<<grid, 128, 49152, tls().stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
-                                                                  (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, (uint32_t)seq,
-                                                                  (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap, 1.0f / sqrtf(128.0f));
-    return launched("attn_prefill_kernel");
+    return launch_pdl("attn_prefill_kernel", llama::attn_prefill_kernel, grid, dim3(128), 49152, (const __nv_bfloat16*)q,
+                      (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out, (uint32_t)seq, (uint32_t)hq,
+                      (uint32_t)hkv, (uint32_t)cap, 1.0f / sqrtf(128.0f));
 }
 static catena_status_t launch_swiglu(const void* gu, void* a, uint64_t tokens, uint64_t ffn) {
     if (ffn % 8) return fail(CATENA_E_BAD_ARG, "swiglu: ffn must be a multiple of 8");
     if (!tokens) return CATENA_OK;
-    llama::swiglu_kernel<<<grid_for(tokens * (ffn / 8), 256), 256, 0, tls().stream>>>((const uint4*)gu, (uint4*)a, tokens, (uint32_t)(ffn / 8));
-    return launched("swiglu_kernel");
+    return launch_pdl("swiglu_kernel", llama::swiglu_kernel, dim3(grid_for(tokens * (ffn / 8), 256)), dim3(256), 0, (const uint4*)gu,
+                      (uint4*)a, tokens, (uint32_t)(ffn / 8));
 }
 static catena_status_t launch_add(const void* x, const void* y, void* out, uint64_t n) {
     if (n % 8) return fail(CATENA_E_BAD_ARG, "add: length must be a multiple of 8");
     if (!n) return CATENA_OK;
-    llama::add_rows_kernel<<<grid_for(n / 8, 256), 256, 0, tls().stream>>>((const uint4*)x, (const uint4*)y, (uint4*)out, n / 8);
-    return launched("add_rows_kernel");
+    return launch_pdl("add_rows_kernel", llama::add_rows_kernel, dim3(grid_for(n / 8, 256)), dim3(256), 0, (const uint4*)x, (const uint4*)y,
+                      (uint4*)out, n / 8);
 }
 // y[M,N] = x[M,K] w[N,K]^T (+ res): the skinny kernel for M <= 16, else the tcgen05 GEMM followed by the residual add
 static catena_status_t launch_linear(const void* x, const void* w, const void* res, void* y, uint64_t m, uint64_t n, uint64_t k) {
@@ -601,9 +694,8 @@ static catena_status_t launch_linear(const void* x, const void* w, const void* r
         const uint64_t groups = ceil_div_u64(n, 8), slots = (uint64_t)sms * 2;
         const uint64_t rounds = ceil_div_u64(groups, slots);
         const unsigned grid = (unsigned)ceil_div_u64(groups, rounds);
-        llama::skinny_gemm_kernel<<<grid, 256, 0, tls().stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)res,
-                                                                 (__nv_bfloat16*)y, (uint32_t)m, (uint32_t)n, (uint32_t)k);
-        return launched("skinny_gemm_kernel");
+        return launch_pdl("skinny_gemm_kernel", llama::skinny_gemm_kernel, dim3(grid), dim3(256), 0, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)w, (const __nv_bfloat16*)res, (__nv_bfloat16*)y, (uint32_t)m, (uint32_t)n, (uint32_t)k);
     }
     CATENA_TRY(launch_gemm_tc(x, w, y, m, n, k, n, 0));
     if (res) CATENA_TRY(launch_add(y, res, y, m * n));
@@ -667,8 +759,7 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
     __nv_bfloat16* gu = ws;                                  ws += T * 2 * d.F;
     __nv_bfloat16* act = ws;
     return composite([&]() -> catena_status_t {
-        CATENA_TRY(launch_embed(blk->embedding, ids, x, T, d.H, blk->vocab));
-        CATENA_TRY(launch_rmsnorm_rows(x, nrm, T, d.H));
+        CATENA_TRY(launch_embed_rmsnorm(blk->embedding, ids, x, nrm, T, d.H, blk->vocab));
         CATENA_TRY(launch_linear(nrm, blk->w_qkv, nullptr, qkv, T, d.qkv_cols, d.H));
         CATENA_TRY(launch_rope_append(qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, blk->rope_base));
         if (seq == 1) {
