@@ -131,6 +131,7 @@ def lib():
     proto("catena_b200_attn_decode_bf16_cache_into", st, [vp, vp, vp, vp, u64, u64, u64, u64, u64, u64])
     proto("catena_b200_swiglu_bf16_into", st, [vp, vp, u64, u64])
     proto("catena_b200_add_bf16_into", st, [vp, vp, vp, u64])
+    proto("catena_b200_linear_swiglu_bf16_into", st, [vp, vp, vp, vp, u64, u64, u64])
     proto("catena_b200_linear_bf16_into", st, [vp, vp, vp, vp, u64, u64, u64])
     proto("catena_b200_debug_set_cta_limit", None, [C.c_int])
     proto("catena_b200_sum_f32_noalloc", st, [vp, u64, vp])

@@ -136,12 +136,40 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, float2* __
 //   k_cache [B, Hkv, cap, 128] at pos    rotated keys
 //   v_cache [B, Hkv, cap, 128] at pos    values
 // One thread per (token, head, 8 pairs): pair i is (i, i + 64) ("rotate half").  `table` [S][64] holds (cos, sin)
-// per position; without it (few tokens) they are evaluated in place — the same function, the same bits.
+// per position; without it (few tokens) they are evaluated in place — the same function, the same bits — by
+// rope_append_small_kernel below, one pair per thread (the evaluation is a long dependent chain).
 // inv_freq[i] = base^(-2i/128), computed once on the host with the same bit-exact functions.
+__global__ void rope_append_small_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                         __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                         const float* __restrict__ inv_freq, uint32_t T, uint32_t S, uint32_t pos0, uint32_t Hq,
+                                         uint32_t Hkv, uint32_t cap) {
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t heads = Hq + 2 * Hkv;
+    const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)T * heads * 64) return;
+    const uint32_t i = (uint32_t)(idx % 64);
+    const uint32_t head = (uint32_t)((idx / 64) % heads);
+    const uint32_t t = (uint32_t)(idx / (64ull * heads));
+    const uint32_t b = t / S, pos = pos0 + t % S;
+    const __nv_bfloat16* src = qkv + ((size_t)t * heads + head) * kHeadDim;
+    if (head >= Hq + Hkv) {   // value head: plain copy
+        __nv_bfloat16* dst = v_cache + (((size_t)b * Hkv + (head - Hq - Hkv)) * cap + pos) * kHeadDim;
+        dst[i] = src[i];
+        dst[i + 64] = src[i + 64];
+        return;
+    }
+    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + 64]);
+    const float2 cs = rope_cos_sin(pos, inv_freq[i]);
+    __nv_bfloat16* dst = head < Hq ? q_out + ((size_t)t * Hq + head) * kHeadDim
+                                   : k_cache + (((size_t)b * Hkv + (head - Hq)) * cap + pos) * kHeadDim;
+    dst[i] = __float2bfloat16_rn(cmath::sub(cmath::mul(x1, cs.x), cmath::mul(x2, cs.y)));
+    dst[i + 64] = __float2bfloat16_rn(cmath::add(cmath::mul(x2, cs.x), cmath::mul(x1, cs.y)));
+}
 __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                   const float* __restrict__ inv_freq, const float2* __restrict__ table, uint32_t T, uint32_t S,
-                                   uint32_t pos0, uint32_t Hq, uint32_t Hkv, uint32_t cap) {
+                                   const float2* __restrict__ table, uint32_t T, uint32_t S, uint32_t pos0, uint32_t Hq, uint32_t Hkv,
+                                   uint32_t cap) {
     pdl_trigger();
     pdl_wait();
     const uint32_t heads = Hq + 2 * Hkv;
@@ -168,7 +196,7 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_b
         for (uint32_t u = 0; u < 2; ++u) {
             const uint32_t i = i0 + 2 * e + u;
             const float x1 = bf16_bits_to_f32(u ? lw[e] >> 16 : lw[e] & 0xFFFFu), x2 = bf16_bits_to_f32(u ? hw[e] >> 16 : hw[e] & 0xFFFFu);
-            const float2 cs = table ? table[(size_t)s * 64 + i] : rope_cos_sin(pos, inv_freq[i]);
+            const float2 cs = table[(size_t)s * 64 + i];
             o1[u] = cmath::sub(cmath::mul(x1, cs.x), cmath::mul(x2, cs.y));
             o2[u] = cmath::add(cmath::mul(x2, cs.x), cmath::mul(x1, cs.y));
         }
@@ -235,23 +263,32 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 constexpr int kSkinnyUnroll = 8;
 // CTAs are persistent and software-pipelined: the weight loads of the next batch of k blocks (of this or the next
 // group of rows) are issued before the current batch is multiplied and reduced, so the stream never drains.
+// With swiglu_f = F > 0 the weights are the [2F, K] gate / up matrix and y [M, F] = silu(gate) * up: a CTA multiplies the 8
+// gate rows of a group, then the matching 8 up rows, and combines them in the epilogue (both products rounded to bf16
+// first, exactly what the separate SwiGLU kernel reads back from memory).
 __global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ y,
-                                                         uint32_t M, uint32_t N, uint32_t K) {
+                                                         uint32_t M, uint32_t N, uint32_t K, uint32_t swiglu_f) {
     __shared__ float part[8][16][8];    // [warp][token][weight row]
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t kblocks = (K + 31) / 32;
     const uint32_t batches = (kblocks + 8 * kSkinnyUnroll - 1) / (8 * kSkinnyUnroll);   // per group and warp
-    const uint32_t groups = (N + 7) / 8;
+    const uint32_t halves = swiglu_f ? 2u : 1u;             // row groups multiplied per output group
+    const uint32_t groups = swiglu_f ? swiglu_f / 8 : (N + 7) / 8;
     const uint32_t my_groups = blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t steps = my_groups * batches;
+    const uint32_t steps = my_groups * halves * batches;
+    // first weight row of step s
+    auto row0_of = [&](uint32_t s) {
+        const uint32_t grp = blockIdx.x + (s / (halves * batches)) * gridDim.x;
+        return ((s / batches) % halves) * swiglu_f + grp * 8;
+    };
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const __nv_bfloat16* xa = x + (size_t)g * K + 8 * t;
     const __nv_bfloat16* xb = x + (size_t)(g + 8) * K + 8 * t;
 
-    // weights of step s: group blockIdx.x + (s / batches) * gridDim.x, k blocks warp + 8 (u + kSkinnyUnroll (s % batches))
+    // weights of step s: rows row0_of(s) .. +7, k blocks warp + 8 (u + kSkinnyUnroll (s % batches))
     auto load_w = [&](uint32_t s, uint4 (&wv)[kSkinnyUnroll]) {
-        const uint32_t n0 = (blockIdx.x + (s / batches) * gridDim.x) * 8;
+        const uint32_t n0 = row0_of(s);
         const uint32_t kb0 = warp + 8 * kSkinnyUnroll * (s % batches);
         const __nv_bfloat16* wr = w + (size_t)(n0 + g) * K + 8 * t;
 #pragma unroll
@@ -270,6 +307,7 @@ __global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16
     if (steps > 0) load_w(0, cur);      // weights are never written by a kernel: they may be fetched before the wait
     pdl_wait();
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float gate = 0.0f;                   // SwiGLU: the gate value of this thread's (token, row) until the up rows are done
     for (uint32_t s = 0; s < steps; ++s) {
         if (s + 1 < steps) load_w(s + 1, nxt);
         const uint32_t kb0 = warp + 8 * kSkinnyUnroll * (s % batches);
@@ -283,7 +321,7 @@ __global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16
             mma_bf16_16816(acc, av.z, bv.z, av.w, bv.w, cur[u].z, cur[u].w);
         }
         if (s % batches == batches - 1) {    // the group is complete: add the warps' partial sums in ascending order
-            const uint32_t n0 = (blockIdx.x + (s / batches) * gridDim.x) * 8;
+            const uint32_t n0 = row0_of(s);
             __syncthreads();                 // the previous group's partials have been read
             part[warp][g][2 * t] = acc[0];
             part[warp][g][2 * t + 1] = acc[1];
@@ -297,8 +335,14 @@ __global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16
                     float v = part[0][m][r];
 #pragma unroll
                     for (int wv2 = 1; wv2 < 8; ++wv2) v = cmath::add(v, part[wv2][m][r]);
-                    if (res) v = cmath::add(__bfloat162float(__float2bfloat16_rn(v)), __bfloat162float(res[(size_t)m * N + n0 + r]));
-                    y[(size_t)m * N + n0 + r] = __float2bfloat16_rn(v);
+                    if (swiglu_f) {
+                        const float rounded = __bfloat162float(__float2bfloat16_rn(v));
+                        if (n0 < swiglu_f) gate = rounded;
+                        else y[(size_t)m * swiglu_f + (n0 - swiglu_f) + r] = __float2bfloat16_rn(cmath::mul(cmath::silu(gate), rounded));
+                    } else {
+                        if (res) v = cmath::add(__bfloat162float(__float2bfloat16_rn(v)), __bfloat162float(res[(size_t)m * N + n0 + r]));
+                        y[(size_t)m * N + n0 + r] = __float2bfloat16_rn(v);
+                    }
                 }
             }
         }
@@ -634,7 +678,6 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
     if (pos0 + seq > cap) return fail(CATENA_E_BAD_ARG, "rope: positions beyond the cache capacity");
     const float* inv = nullptr;
     CATENA_TRY(rope_table(base, &inv));
-    const float2* table = nullptr;
     if (seq >= 16 && tokens / seq * (hq + hkv) >= 8) {   // many (sequence, head) pairs per position: evaluate each angle once
         RopeAngles& ra = g_rope_angles[tls().device & 15];
         if (ra.positions < seq) {
@@ -648,11 +691,14 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
         }
         CATENA_TRY(launch_pdl("rope_table_kernel", llama::rope_table_kernel, dim3((unsigned)ceil_div_u64(seq * 64, 256)), dim3(256), 0, inv,
                               ra.dev, (uint32_t)pos0, (uint32_t)seq));
-        table = ra.dev;
+        const uint64_t work = tokens * (hq + 2 * hkv) * 8;
+        return launch_pdl("rope_append_kernel", llama::rope_append_kernel, dim3((unsigned)ceil_div_u64(work, 256)), dim3(256), 0,
+                          (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                          (const float2*)ra.dev, (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
     }
-    const uint64_t work = tokens * (hq + 2 * hkv) * 8;
-    return launch_pdl("rope_append_kernel", llama::rope_append_kernel, dim3((unsigned)ceil_div_u64(work, 256)), dim3(256), 0,
-                      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv, table,
+    const uint64_t work = tokens * (hq + 2 * hkv) * 64;
+    return launch_pdl("rope_append_small_kernel", llama::rope_append_small_kernel, dim3((unsigned)ceil_div_u64(work, 128)), dim3(128), 0,
+                      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv,
                       (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
 }
 static catena_status_t launch_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
@@ -695,11 +741,29 @@ static catena_status_t launch_linear(const void* x, const void* w, const void* r
         const uint64_t rounds = ceil_div_u64(groups, slots);
         const unsigned grid = (unsigned)ceil_div_u64(groups, rounds);
         return launch_pdl("skinny_gemm_kernel", llama::skinny_gemm_kernel, dim3(grid), dim3(256), 0, (const __nv_bfloat16*)x,
-                          (const __nv_bfloat16*)w, (const __nv_bfloat16*)res, (__nv_bfloat16*)y, (uint32_t)m, (uint32_t)n, (uint32_t)k);
+                          (const __nv_bfloat16*)w, (const __nv_bfloat16*)res, (__nv_bfloat16*)y, (uint32_t)m, (uint32_t)n, (uint32_t)k, 0u);
     }
     CATENA_TRY(launch_gemm_tc(x, w, y, m, n, k, n, 0));
     if (res) CATENA_TRY(launch_add(y, res, y, m * n));
     return CATENA_OK;
+}
+
+// act [m, ffn] = silu(x w_gate^T) * (x w_up^T) with w = [2 ffn, k] (gate rows, then up rows): one launch for m <= 16,
+// else the GEMM into `gu` [m, 2 ffn] followed by the SwiGLU kernel
+static catena_status_t launch_linear_swiglu(const void* x, const void* w, void* gu, void* act, uint64_t m, uint64_t ffn, uint64_t k) {
+    if (!m || !ffn) return CATENA_OK;
+    if (ffn % 8) return fail(CATENA_E_BAD_ARG, "swiglu: ffn must be a multiple of 8");
+    if (m <= 16 && k % 8 == 0 && k > 0 && ffn <= 0x3FFFFFFFull && k <= 0x7FFFFFFFull && !(((uintptr_t)x | (uintptr_t)w) & 15)) {
+        int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+        const uint64_t groups = ffn / 8, slots = (uint64_t)sms * 2;
+        const uint64_t rounds = ceil_div_u64(groups, slots);
+        const unsigned grid = (unsigned)ceil_div_u64(groups, rounds);
+        return launch_pdl("skinny_gemm_kernel", llama::skinny_gemm_kernel, dim3(grid), dim3(256), 0, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)w, (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)act, (uint32_t)m, (uint32_t)(2 * ffn),
+                          (uint32_t)k, (uint32_t)ffn);
+    }
+    CATENA_TRY(launch_linear(x, w, nullptr, gu, m, 2 * ffn, k));
+    return launch_swiglu(gu, act, m, ffn);
 }
 
 // Runs `body` with per-launch synchronisation switched off, then restores the mode and (when blocking) waits
@@ -771,8 +835,7 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
         }
         CATENA_TRY(launch_linear(att, blk->w_o, x, x2, T, d.H, d.Hq * llama::kHeadDim));
         CATENA_TRY(launch_rmsnorm_rows(x2, nrm, T, d.H));
-        CATENA_TRY(launch_linear(nrm, blk->w_gate_up, nullptr, gu, T, 2 * d.F, d.H));
-        CATENA_TRY(launch_swiglu(gu, act, T, d.F));
+        CATENA_TRY(launch_linear_swiglu(nrm, blk->w_gate_up, gu, act, T, d.F, d.H));
         CATENA_TRY(launch_linear(act, blk->w_down, x2, out, T, d.H, d.F));
         return CATENA_OK;
     });
@@ -821,6 +884,11 @@ catena_status_t catena_b200_attn_decode_bf16_cache_into(const void* q, const voi
 catena_status_t catena_b200_swiglu_bf16_into(const void* gate_up, void* out, uint64_t tokens, uint64_t ffn) {
     if (!gate_up || !out) return fail(CATENA_E_BAD_ARG, "swiglu: null argument");
     return composite([&]() { return launch_swiglu(gate_up, out, tokens, ffn); });
+}
+catena_status_t catena_b200_linear_swiglu_bf16_into(const void* x, const void* w_gate_up, void* scratch, void* out, uint64_t m,
+                                                    uint64_t ffn, uint64_t k) {
+    if (!x || !w_gate_up || !out || (m > 16 && !scratch)) return fail(CATENA_E_BAD_ARG, "linear_swiglu: null argument");
+    return composite([&]() { return launch_linear_swiglu(x, w_gate_up, scratch, out, m, ffn, k); });
 }
 catena_status_t catena_b200_add_bf16_into(const void* x, const void* y, void* out, uint64_t n) {
     if (!x || !y || !out) return fail(CATENA_E_BAD_ARG, "add: null argument");

@@ -249,6 +249,11 @@ catena_status_t catena_b200_attn_decode_bf16_cache_into(const void* q, const voi
                                                         uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap);
 /* gate_up [tokens, 2 ffn] -> out [tokens, ffn] = silu(gate) * up */
 catena_status_t catena_b200_swiglu_bf16_into(const void* gate_up, void* out, uint64_t tokens, uint64_t ffn);
+/* out [m, ffn] = silu(x w_gate^T) * (x w_up^T), w_gate_up [2 ffn, k] (gate rows, then up rows); bit-identical to
+ * catena_b200_linear_bf16_into followed by catena_b200_swiglu_bf16_into.  m <= 16 is one launch and `scratch` is
+ * unused; larger m needs scratch [m, 2 ffn] bf16 for the projection. */
+catena_status_t catena_b200_linear_swiglu_bf16_into(const void* x, const void* w_gate_up, void* scratch, void* out, uint64_t m,
+                                                    uint64_t ffn, uint64_t k);
 /* out = x + y over n bf16 elements (n a multiple of 8; out may alias x or y) */
 catena_status_t catena_b200_add_bf16_into(const void* x, const void* y, void* out, uint64_t n);
 /* y [m, n] = x [m, k] w[n, k]^T (+ residual [m, n], added after the product is rounded to bf16).  m <= 16 runs a kernel

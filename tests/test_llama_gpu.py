@@ -162,6 +162,22 @@ def test_linear(orc, m, n, k, res):
         cb.free(mm)
 
 
+@pytest.mark.parametrize("m,ffn,k", [(4, 264, 512), (16, 512, 2048), (20, 256, 512)])
+def test_linear_swiglu_equals_two_steps(orc, m, ffn, k):
+    """The fused gate/up projection + SwiGLU (one launch for m <= 16) gives the bits of the two separate operators."""
+    rng = np.random.default_rng(8)
+    x, w = bits(rng, (m, k)), bits(rng, (2 * ffn, k), 1.0 / math.sqrt(k))
+    xm, wm, gm, am, bm = dev(x), dev(w), alloc(m * 2 * ffn * 2), alloc(m * ffn * 2), alloc(m * ffn * 2)
+    cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, None, gm.data, m, 2 * ffn, k))
+    cb.check(cb.lib().catena_b200_swiglu_bf16_into(gm.data, am.data, m, ffn))
+    cb.check(cb.lib().catena_b200_linear_swiglu_bf16_into(xm.data, wm.data, gm.data, bm.data, m, ffn, k))
+    two, fused = cb.download(am, np.uint16), cb.download(bm, np.uint16)
+    assert np.array_equal(two, fused)
+    close(fused, orc.swiglu_bf16(orc.linear_bf16(x, w, threads=orc.max_threads())), rel=2.0 ** -6, floor=2e-3)
+    for mm in (xm, wm, gm, am, bm):
+        cb.free(mm)
+
+
 def make_block(rng, hidden, n_heads, n_kv_heads, ffn, vocab):
     return {"embedding": bits(rng, (vocab, hidden)),
             "w_qkv": bits(rng, ((n_heads + 2 * n_kv_heads) * 128, hidden), 1.0 / math.sqrt(hidden)),
