@@ -250,6 +250,12 @@ def run_gpu(args, rank, world, local_rank):
     e2e_tflops = world * GEMM_FLOP / (e2e_ms * 1e-3) / 1e12
     checksum = int(np.bitwise_xor.reduce(c_host.astype(np.uint64) * (np.arange(c_host.size, dtype=np.uint64) | 1)))
 
+    # ---- Llama-style block (prefill 4 x 2048, then 128 decode steps), one replica per GPU; rank 0's figures are reported
+    L.catena_b200_set_blocking(0)
+    llama = llama_bench(cb, L, torch, dev, stream, peaks, LLAMA, reps=2)
+    L.catena_b200_set_blocking(1)
+    barrier()
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
@@ -294,6 +300,7 @@ def run_gpu(args, rank, world, local_rank):
                             "roofline": {"bound": "hbm", "achieved": attn_gbs_1, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                          "frac": attn_gbs_1 / peaks["hbm_gbs"], "traffic": None,
                                          "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "attn_decode_tc_kernel"}},
+            "llama_block": llama,
             "cpu_baseline": cpu_baseline,
             "output_checksum": f"{checksum:016x}",
         }
@@ -346,10 +353,12 @@ def llama_bench(cb, L, torch, dev, stream, peaks, cfg, reps=2):
             torch.cuda.synchronize(dev)
             launches0 = L.catena_b200_launch_count()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            h0 = time.perf_counter()
             e0.record(stream)
             for _ in range(reps):
                 fn()
             e1.record(stream)
+            times[name + "_host"] = (time.perf_counter() - h0) / reps * 1e3      # ms the host spent enqueuing
             torch.cuda.synchronize(dev)
             times[name] = e0.elapsed_time(e1) / reps
             times[name + "_launches"] = (L.catena_b200_launch_count() - launches0) // reps
@@ -366,7 +375,7 @@ def llama_bench(cb, L, torch, dev, stream, peaks, cfg, reps=2):
             "prefill_ms": times["prefill"], "prefill_tflops": pre_tf, "prefill_launches": times["prefill_launches"],
             "prefill_roofline": {"bound": "tensor", "achieved": pre_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                  "frac": pre_tf / peaks["bf16_tflops"]},
-            "decode_ms_per_step": dec_ms, "decode_gbs": dec_gbs, "decode_launches_per_step": times["decode_launches"] // steps,
+            "decode_ms_per_step": dec_ms, "decode_host_ms_per_step": times["decode_host"] / steps, "decode_gbs": dec_gbs, "decode_launches_per_step": times["decode_launches"] // steps,
             "decode_roofline": {"bound": "hbm", "achieved": dec_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                 "frac": dec_gbs / peaks["hbm_gbs"]},
             "end_to_end_ms": times["prefill"] + times["decode"], "output_checksum": f"{checksum:012x}"}
