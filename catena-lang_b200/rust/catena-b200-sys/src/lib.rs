@@ -74,4 +74,32 @@ extern "C" {
                                              batch: u64, hq: u64, hkv: u64, d: u64, kv_len: u64, unit0: u64,
                                              unit1: u64) -> catena_status_t;
     pub fn catena_b200_sum_f32_noalloc(input: *const c_void, n: u64, out: *mut c_void) -> catena_status_t;
+    // Llama-style block (device pointers throughout)
+    pub fn catena_b200_llama_workspace_bytes(blk: *const catena_llama_block_t, tokens: u64) -> u64;
+    pub fn catena_b200_llama_prefill(blk: *const catena_llama_block_t, ids: *const i32, batch: u64, seq: u64,
+                                     k_cache: *mut c_void, v_cache: *mut c_void, out: *mut c_void, workspace: *mut c_void,
+                                     workspace_bytes: u64) -> catena_status_t;
+    pub fn catena_b200_llama_decode(blk: *const catena_llama_block_t, ids: *const i32, batch: u64, pos: u64,
+                                    k_cache: *mut c_void, v_cache: *mut c_void, out: *mut c_void, workspace: *mut c_void,
+                                    workspace_bytes: u64) -> catena_status_t;
+    pub fn catena_b200_linear_bf16_into(x: *const c_void, w: *const c_void, residual: *const c_void, y: *mut c_void, m: u64,
+                                        n: u64, k: u64) -> catena_status_t;
+}
+
+/// catena_llama_block_t of include/catena_b200.h.
+#[repr(C)]
+#[allow(non_camel_case_types)]
+pub struct catena_llama_block_t {
+    pub hidden: u64,
+    pub n_heads: u64,
+    pub n_kv_heads: u64,
+    pub ffn: u64,
+    pub vocab: u64,
+    pub max_len: u64,
+    pub embedding: *const c_void,
+    pub w_qkv: *const c_void,
+    pub w_o: *const c_void,
+    pub w_gate_up: *const c_void,
+    pub w_down: *const c_void,
+    pub rope_base: f32,
 }

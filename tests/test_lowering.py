@@ -59,3 +59,16 @@ def test_unknown_producer_is_refused():
         lo.select(mod("my-map", [CAST, materializec("my.custom-at"), TO_MEM]))
     with pytest.raises(lo.Unsupported):
         lo.select(mod("odd", [CAST, reducec("f32.add-env", "my.getter")]))
+
+
+def test_stdlib_extension_registers_the_added_programs():
+    """The hexpr extension file declares the programs this backend adds; the host mirror finds them by name
+    (the file itself cannot be type-checked here: the checker is not part of this build)."""
+    import os
+    import catena_lang_b200 as cb
+    path = os.path.join(os.path.dirname(cb.__file__), "stdlib_ext", "b200.hex")
+    rt = cb.Runtime.new([path])
+    for name in ("gemm-bf16-rc", "gemm-i8-rc", "attn-decode-bf16"):
+        assert name in rt.signatures and rt.signatures[name][0] == cb.symbol_for(name)
+    text = open(path).read()
+    assert text.count("(") == text.count(")") and text.count("{") == text.count("}") and text.count("[") == text.count("]")
