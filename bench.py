@@ -256,6 +256,12 @@ def run_gpu(args, rank, world, local_rank):
     L.catena_b200_set_blocking(1)
     barrier()
 
+    # ---- strong scaling of one problem with the final gather (its checksums are the same for every --gpus N)
+    L.catena_b200_set_blocking(0)
+    sharded = sharded_bench(cb, L, torch, dist if world > 1 else None, shard, dev, stream, rank, world)
+    L.catena_b200_set_blocking(1)
+    barrier()
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle
@@ -301,12 +307,124 @@ def run_gpu(args, rank, world, local_rank):
                                          "frac": attn_gbs_1 / peaks["hbm_gbs"], "traffic": None,
                                          "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "attn_decode_tc_kernel"}},
             "llama_block": llama,
+            "sharded": {"scaling": "strong", "n_gpus": world, **sharded},
             "cpu_baseline": cpu_baseline,
             "output_checksum": f"{checksum:016x}",
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def sharded_bench(cb, L, torch, dist, shard, dev, stream, rank, world, reps=3):
+    """Strong scaling of ONE problem over the ranks, gather included: the int8 GEMM 16384 x 16384 x 8192 sharded by
+    row blocks of A / C (all-gather of the int32 C over NCCL) and the decode attention of the bench sharded by
+    (batch, kv-head) ranges (all-gather of O).  Every rank ends with the full result; its checksum must be the same
+    for every world size (tile shape, k order and KV split count never depend on the sharding)."""
+    M = N = 16384
+    K = 8192
+    g = torch.Generator(device=dev)
+    g.manual_seed(4)                                          # the same operands on every rank
+    a = torch.randint(-128, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+    b = torch.randint(-128, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    blocks = shard.row_blocks(M, world)
+    mine = blocks[rank]
+    c_block = torch.empty((mine.m1 - mine.m0, N), dtype=torch.int32, device=dev)
+    q = torch.randn((ATT["B"], ATT["Hq"], ATT["D"]), generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn((ATT["B"], ATT["Hkv"], ATT["L"], ATT["D"]), generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn((ATT["B"], ATT["Hkv"], ATT["L"], ATT["D"]), generator=g, device=dev).to(torch.bfloat16)
+    o = torch.zeros((ATT["B"], ATT["Hq"], ATT["D"]), dtype=torch.bfloat16, device=dev)
+    units = ATT["B"] * ATT["Hkv"]
+    ranges = shard.unit_ranges(units, world)
+    G = ATT["Hq"] // ATT["Hkv"]
+    res = {}
+
+    def gemm_compute():
+        cb.check(L.catena_b200_gemm_i8_into(a[mine.m0:mine.m1].data_ptr(), b.data_ptr(), c_block.data_ptr(), mine.m1 - mine.m0, N, K, N))
+
+    def attn_compute():
+        cb.check(L.catena_b200_attn_decode_bf16_into(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), ATT["B"], ATT["Hq"],
+                                                     ATT["Hkv"], ATT["D"], ATT["L"], ranges[rank].u0, ranges[rank].u1))
+
+    def attn_gather():
+        rows = o.view(units, G * ATT["D"])[ranges[rank].u0:ranges[rank].u1]
+        return shard.gather_units(rows, ranges, G * ATT["D"], dist if world > 1 else None)
+
+    for name, compute, gather, work, unit in (
+            ("gemm_i8_16384x16384x8192", gemm_compute, lambda: shard.gather_rows(c_block, blocks, dist if world > 1 else None),
+             2.0 * M * N * K / 1e12, "TOP/s"),
+            ("attn_decode_c3", attn_compute, attn_gather, ATT_BYTES / 1e9, "GB/s")):
+        with torch.cuda.stream(stream):
+            compute(); full = gather()                        # warm-up (NCCL communicator set-up included)
+            torch.cuda.synchronize(dev)
+            if world > 1:
+                dist.barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            t_compute = t_gather = 0.0
+            for _ in range(reps):
+                ev[0].record(stream); compute(); ev[1].record(stream); full = gather(); ev[2].record(stream)
+                torch.cuda.synchronize(dev)
+                t_compute += ev[0].elapsed_time(ev[1]) / reps
+                t_gather += ev[1].elapsed_time(ev[2]) / reps
+        total = shard.max_over_ranks(t_compute + t_gather, dist if world > 1 else None, dev)
+        checksum = int(full.view(torch.int16 if full.dtype == torch.bfloat16 else torch.int32).to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF
+        res[name] = {"ms_total": total, "ms_compute": shard.max_over_ranks(t_compute, dist if world > 1 else None, dev),
+                     "ms_gather": shard.max_over_ranks(t_gather, dist if world > 1 else None, dev),
+                     "value_incl_gather": work / (total * 1e-3), "unit": unit, "checksum": f"{checksum:012x}"}
+        del full
+    # ---- the same GEMM with the gather fused into its epilogue: every rank stores its row block into every rank's
+    # copy of C (peer-mapped through CUDA IPC) while it computes; one barrier afterwards replaces the all-gather
+    if world > 1:
+        class _DevArray:                                       # lets torch view the library's allocation (checksum only)
+            def __init__(self, ptr, shape):
+                self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i4", "data": (ptr, False), "version": 3}
+        c_full = cb.CatenaMem()
+        cb.check(L.catena_b200_mem_alloc(M * N * 4, C.byref(c_full)))
+        handle = (C.c_ubyte * 64)()
+        off = C.c_uint64()
+        cb.check(L.catena_b200_ipc_export(c_full, handle, C.byref(off)))
+        handles = [None] * world
+        dist.all_gather_object(handles, (bytes(handle), int(off.value)))
+        imported, ptrs = [], []
+        for r in range(world):
+            if r == rank:
+                continue
+            m_ = cb.CatenaMem()
+            hb = (C.c_ubyte * 64).from_buffer_copy(handles[r][0])
+            cb.check(L.catena_b200_ipc_import(hb, handles[r][1], M * N * 4, C.byref(m_)))
+            imported.append((m_, handles[r][1]))
+            ptrs.append(m_.data + mine.m0 * N * 4)
+        peer_arr = (C.c_void_p * len(ptrs))(*ptrs)
+        local_rows = c_full.data + mine.m0 * N * 4
+
+        def fused():
+            cb.check(L.catena_b200_gemm_i8_into_peers(a[mine.m0:mine.m1].data_ptr(), b.data_ptr(), local_rows, mine.m1 - mine.m0, N, K, N,
+                                                      peer_arr, len(ptrs)))
+        with torch.cuda.stream(stream):
+            fused()
+            torch.cuda.synchronize(dev)
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t = 0.0
+            for _ in range(reps):
+                e0.record(stream); fused(); e1.record(stream)
+                torch.cuda.synchronize(dev)
+                dist.barrier()                                 # every rank's stores have landed
+                t += e0.elapsed_time(e1) / reps
+        total = shard.max_over_ranks(t, dist, dev)
+        full = torch.as_tensor(_DevArray(c_full.data, (M, N)), device=dev)
+        checksum = int(full.to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF
+        res["gemm_i8_16384x16384x8192_fused_gather"] = {
+            "ms_total": total, "value_incl_gather": 2.0 * M * N * K / 1e12 / (total * 1e-3), "unit": "TOP/s",
+            "checksum": f"{checksum:012x}", "note": "epilogue stores every tile to all ranks' C over NVLink; timed on the device, max over ranks"}
+        del full
+        dist.barrier()
+        for m_, o_ in imported:
+            cb.check(L.catena_b200_ipc_close(m_, o_))
+        dist.barrier()
+        cb.free(c_full)
+    cb.check(L.catena_b200_check_device_errors())
+    return res
 
 
 LLAMA = dict(hidden=2048, n_heads=16, n_kv_heads=16, ffn=8192, vocab=32000, batch=4, seq=2048, decode_steps=128)

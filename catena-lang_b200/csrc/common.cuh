@@ -62,6 +62,8 @@ catena_status_t launch_identity_matmul_f32(const float* a, float* c, uint64_t n,
 // gemm_tc.cu
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8);
+catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                     int is_i8, void* const* peer_c, uint32_t n_peers);
 catena_status_t gemm_tc_check_errors();
 void gemm_tc_set_cta_limit(int limit);
 void gemm_tc_set_pair_mode(int on);

@@ -41,6 +41,14 @@ constexpr int EPI_THREADS = 128;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;         // rasterisation in pair-tile rows (8 x 256 rows)
 constexpr uint64_t WAIT_NS = 1000000000ull;
+constexpr int kMaxPeers = 7;       // other GPUs of an 8-GPU box
+
+// Where the epilogue stores each output tile besides this GPU's C: peer-mapped pointers (CUDA IPC / P2P) to the same
+// rows of the other GPUs' copies of C.  The gather of a row-sharded GEMM then rides on the epilogue's stores.
+struct PeerOut {
+    void* ptr[kMaxPeers];
+    uint32_t n;
+};
 
 struct __align__(8) Control {
     uint64_t full[STAGES];       // used in the leader CTA
@@ -50,7 +58,8 @@ struct __align__(8) Control {
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Control);
+constexpr int PEER_STAGE_BYTES = 32 * 128;           // per epilogue warp: 32 rows x 32 int32 (or bf16) columns, for peer stores
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + (int)((sizeof(Control) + 15) / 16 * 16) + 4 * PEER_STAGE_BYTES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -198,14 +207,16 @@ __device__ __forceinline__ bool get_work(uint32_t it, uint32_t pair, uint32_t pa
     return true;
 }
 
-template <bool IS_I8>
+// HAS_PEERS = the gather-fused variant (the plain one carries none of its code or registers)
+template <bool IS_I8, bool HAS_PEERS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b128,
                 const __grid_constant__ CUtensorMap map_b64, const __grid_constant__ CUtensorMap map_b32,
-                void* __restrict__ c_out, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err) {
+                void* __restrict__ c_out, PeerOut peers, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+    uint8_t* peer_stage = smem + STAGES * STAGE_BYTES + (sizeof(Control) + 15) / 16 * 16;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -317,12 +328,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tmem_ld_wait();
                 if (row < M) {
                     const uint32_t col = w.col0 + c;
+                    uint4 out[8];
+                    if (IS_I8) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) out[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t p[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]),
+                                                                         __uint_as_float(v[8 * q + 2 * e + 1]));
+                                p[e] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            out[q] = make_uint4(p[0], p[1], p[2], p[3]);
+                        }
+                    }
+                    // this GPU's C: each thread stores its own row (L2 merges the partial lines)
                     if (IS_I8) {
                         int32_t* dst = reinterpret_cast<int32_t*>(c_out) + (uint64_t)row * ldc + col;
                         if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                            for (int q = 0; q < 8; ++q) reinterpret_cast<uint4*>(dst)[q] = out[q];
                         } else {
                             for (int q = 0; q < 32; ++q)
                                 if (col + q < N) dst[q] = (int32_t)v[q];
@@ -330,6 +358,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     } else {
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + (uint64_t)row * ldc + col;
                         if (col + 32 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = out[q];
+                        } else {
+                            for (int q = 0; q < 32; ++q)
+                                if (col + q < N) dst[q] = __float2bfloat16_rn(__uint_as_float(v[q]));
+                        }
+                    }
+                }
+                // peer copies: NVLink wants whole lines, so the warp's 32 x 32 block is transposed through shared memory
+                // (16-byte chunk index xor-ed with the row) and written with lanes along the columns
+                if (HAS_PEERS && peers.n > 0) {
+                    constexpr uint32_t CH = IS_I8 ? 8u : 4u;              // 16-byte chunks per row of the block
+                    const uint32_t col = w.col0 + c;
+                    uint8_t* stage = peer_stage + quad * PEER_STAGE_BYTES;
+                    const bool whole = col + 32 <= N && ((ldc * (IS_I8 ? 4u : 2u)) & 15u) == 0 && ((col * (IS_I8 ? 4u : 2u)) & 15u) == 0;
+                    if (whole) {
+                        uint4 out[8];
+                        if (IS_I8) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) out[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 uint32_t p[4];
@@ -339,11 +388,35 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                                                              __uint_as_float(v[8 * q + 2 * e + 1]));
                                     p[e] = *reinterpret_cast<uint32_t*>(&h);
                                 }
-                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(p[0], p[1], p[2], p[3]);
+                                out[q] = make_uint4(p[0], p[1], p[2], p[3]);
                             }
-                        } else {
-                            for (int q = 0; q < 32; ++q)
-                                if (col + q < N) dst[q] = __float2bfloat16_rn(__uint_as_float(v[q]));
+                        }
+#pragma unroll
+                        for (uint32_t q = 0; q < CH; ++q)
+                            *reinterpret_cast<uint4*>(stage + lane * (CH * 16) + ((q ^ (lane & (CH - 1))) << 4)) = out[q];
+                        __syncwarp();
+                        const uint32_t row_base = w.m_blk * 2 * BM + rank * BM + quad * 32;
+#pragma unroll
+                        for (uint32_t j = 0; j < CH; ++j) {              // 32 / CH rows per instruction
+                            const uint32_t r = j * (32 / CH) + lane / CH, q = lane % CH;
+                            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (CH * 16) + ((q ^ (r & (CH - 1))) << 4));
+                            if (row_base + r < M) {
+                                const uint64_t off = ((uint64_t)(row_base + r) * ldc + col) * (IS_I8 ? 4u : 2u) + q * 16;
+#pragma unroll
+                                for (uint32_t pi = 0; pi < (uint32_t)kMaxPeers; ++pi)
+                                    if (pi < peers.n) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(peers.ptr[pi]) + off) = val;
+                            }
+                        }
+                        __syncwarp();
+                    } else if (row < M) {
+#pragma unroll
+                        for (uint32_t pi = 0; pi < (uint32_t)kMaxPeers; ++pi) {
+                            if (pi >= peers.n) break;
+                            for (int q = 0; q < 32; ++q) {
+                                if (col + q >= N) break;
+                                if (IS_I8) (reinterpret_cast<int32_t*>(peers.ptr[pi]) + (uint64_t)row * ldc + col)[q] = (int32_t)v[q];
+                                else (reinterpret_cast<__nv_bfloat16*>(peers.ptr[pi]) + (uint64_t)row * ldc + col)[q] = __float2bfloat16_rn(__uint_as_float(v[q]));
+                            }
                         }
                     }
                 }
@@ -404,17 +477,25 @@ static catena_status_t make_map2(CUtensorMap* map, const void* base, uint64_t ro
 
 // Enqueues the CTA-pair GEMM.  `err_dev` is the device error word shared with the single-CTA kernel.
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                 int is_i8, int cta_limit, uint32_t* err_dev) {
+                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers) {
+    if (n_peers > (uint32_t)tc2::kMaxPeers) return fail(CATENA_E_BAD_ARG, "gemm: more than 7 peer outputs");
+    tc2::PeerOut peers = {};
+    peers.n = n_peers;
+    for (uint32_t i = 0; i < n_peers; ++i) {
+        if (!peer_c || !peer_c[i] || ((uintptr_t)peer_c[i] & 15)) return fail(CATENA_E_BAD_ARG, "gemm: null or unaligned peer output");
+        peers.ptr[i] = peer_c[i];
+    }
     const int eb = is_i8 ? 1 : 2;
     CUtensorMap map_a, map_b128, map_b64, map_b32;
     CATENA_TRY(make_map2(&map_a, a, m, k, eb, tc2::BM));
     CATENA_TRY(make_map2(&map_b128, b, n, k, eb, 128));
     CATENA_TRY(make_map2(&map_b64, b, n, k, eb, 64));
     CATENA_TRY(make_map2(&map_b32, b, n, k, eb, 32));
-    if (is_i8)
-        CATENA_CUDA(cudaFuncSetAttribute(tc2::gemm_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES));
-    else
-        CATENA_CUDA(cudaFuncSetAttribute(tc2::gemm_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES));
+    typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, void*, tc2::PeerOut, uint32_t,
+                             uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*);
+    KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, true> : tc2::gemm_tc2_kernel<true, false>)
+                            : (n_peers ? tc2::gemm_tc2_kernel<false, true> : tc2::gemm_tc2_kernel<false, false>);
+    CATENA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES));
     const uint64_t tiles = ceil_div_u64(m, 2 * tc2::BM) * ceil_div_u64(n, tc2::BN);
     const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
     uint64_t pairs = (uint64_t)(sms / 2);
@@ -424,12 +505,8 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     const uint32_t split = rem == 0 ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
     const unsigned grid = (unsigned)(pairs * 2);
     cudaStream_t st = tls().stream;
-    if (is_i8)
-        tc2::gemm_tc2_kernel<true><<<grid, tc2::NUM_THREADS, tc2::SMEM_BYTES, st>>>(map_a, map_b128, map_b64, map_b32, c, (uint32_t)m,
-                                                                                   (uint32_t)n, (uint32_t)k, ldc, split, err_dev);
-    else
-        tc2::gemm_tc2_kernel<false><<<grid, tc2::NUM_THREADS, tc2::SMEM_BYTES, st>>>(map_a, map_b128, map_b64, map_b32, c, (uint32_t)m,
-                                                                                    (uint32_t)n, (uint32_t)k, ldc, split, err_dev);
+    kernel<<<grid, tc2::NUM_THREADS, tc2::SMEM_BYTES, st>>>(map_a, map_b128, map_b64, map_b32, c, peers, (uint32_t)m, (uint32_t)n, (uint32_t)k,
+                                                           ldc, split, err_dev);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "gemm_tc2 launch");

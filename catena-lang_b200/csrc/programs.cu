@@ -238,6 +238,16 @@ catena_status_t catena_b200_gemm_i8_into(const void* a, const void* b, void* c, 
     CATENA_TRY(launch_gemm_tc(a, b, c, m, n, k, ldc, 1));
     return finish("gemm_i8");
 }
+catena_status_t catena_b200_gemm_bf16_into_peers(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
+                                                 uint64_t ldc, void* const* peer_c, uint32_t n_peers) {
+    CATENA_TRY(launch_gemm_tc_peers(a, b, c, m, n, k, ldc, 0, peer_c, n_peers));
+    return finish("gemm_bf16_peers");
+}
+catena_status_t catena_b200_gemm_i8_into_peers(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
+                                               uint64_t ldc, void* const* peer_c, uint32_t n_peers) {
+    CATENA_TRY(launch_gemm_tc_peers(a, b, c, m, n, k, ldc, 1, peer_c, n_peers));
+    return finish("gemm_i8_peers");
+}
 catena_status_t catena_b200_matmul_f32_into(const void* a, const void* b, void* c, uint64_t n, uint64_t m, uint64_t k) {
     CATENA_TRY(ensure_device());
     if (!a || !b || !c) return fail(CATENA_E_BAD_ARG, "matmul_f32_into: null operand");

@@ -31,6 +31,41 @@ def column_blocks(n, world, align=256):
 
 
 @dataclass(frozen=True)
+class RowBlock:
+    rank: int
+    m0: int      # first output row (= first row of A)
+    m1: int      # one past the last
+
+
+def row_blocks(m, world, align=256):
+    """Splits M output rows into `world` contiguous blocks on tile boundaries.  Row blocks of a row-major C are
+    contiguous in memory, so the final gather needs no repacking (column blocks do)."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    tiles = (m + align - 1) // align
+    return [RowBlock(r, min(m, tiles * r // world * align), min(m, tiles * (r + 1) // world * align)) for r in range(world)]
+
+
+def gather_rows(local_block, blocks, dist=None, group=None):
+    """All-gathers contiguous row blocks [m1-m0, N] into the full [M, N] matrix on every rank (one collective when
+    the blocks are equal, padded otherwise)."""
+    import torch
+    if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local_block
+    heights = [b.m1 - b.m0 for b in blocks]
+    if len(set(heights)) == 1:
+        full = torch.empty((sum(heights),) + tuple(local_block.shape[1:]), dtype=local_block.dtype, device=local_block.device)
+        dist.all_gather_into_tensor(full, local_block.contiguous(), group=group)
+        return full
+    hmax = max(heights)
+    pad = torch.zeros((hmax,) + tuple(local_block.shape[1:]), dtype=local_block.dtype, device=local_block.device)
+    pad[: local_block.shape[0]] = local_block
+    parts = [torch.empty_like(pad) for _ in blocks]
+    dist.all_gather(parts, pad, group=group)
+    return torch.cat([p[:h] for p, h in zip(parts, heights)], dim=0)
+
+
+@dataclass(frozen=True)
 class UnitRange:
     rank: int
     u0: int
@@ -65,6 +100,10 @@ def gather_units(local_rows, ranges, row_width, dist=None, group=None):
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_rows
     counts = [r.u1 - r.u0 for r in ranges]
+    if len(set(counts)) == 1:                                  # equal ranges: one collective straight into place
+        full = torch.empty((sum(counts), row_width), dtype=local_rows.dtype, device=local_rows.device)
+        dist.all_gather_into_tensor(full, local_rows.contiguous(), group=group)
+        return full
     cmax = max(counts)
     pad = torch.zeros((cmax, row_width), dtype=local_rows.dtype, device=local_rows.device)
     pad[: local_rows.shape[0]] = local_rows

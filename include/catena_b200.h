@@ -179,6 +179,15 @@ catena_status_t catena_b200_gemm_bf16_into(const void* a, const void* b_colmajor
                                            uint64_t n, uint64_t k, uint64_t ldc);
 catena_status_t catena_b200_gemm_i8_into(const void* a, const void* b_colmajor, void* c_i32, uint64_t m,
                                          uint64_t n, uint64_t k, uint64_t ldc);
+/* GEMM fused with the gather of a row-sharded product: the epilogue stores every output tile to `c` and, with plain
+ * stores over NVLink, to the same rows of up to 7 other GPUs' copies of C.  peer_c[i] are peer-mapped DEVICE pointers
+ * (catena_b200_ipc_import of the peer's allocation, plus this rank's row offset), 16-byte aligned, same `ldc`.  The
+ * stores are complete when the stream has drained; ranks then need one barrier before they read each other's rows.
+ * Needs more than 128 rows (the CTA-pair kernel).  No counterpart in the reference. */
+catena_status_t catena_b200_gemm_bf16_into_peers(const void* a, const void* b_colmajor, void* c, uint64_t m, uint64_t n,
+                                                 uint64_t k, uint64_t ldc, void* const* peer_c, uint32_t n_peers);
+catena_status_t catena_b200_gemm_i8_into_peers(const void* a, const void* b_colmajor, void* c_i32, uint64_t m, uint64_t n,
+                                               uint64_t k, uint64_t ldc, void* const* peer_c, uint32_t n_peers);
 catena_status_t catena_b200_matmul_f32_into(const void* a, const void* b, void* c, uint64_t n, uint64_t m,
                                             uint64_t k);
 /* units [unit0, unit1) of the B*Hkv (batch, kv-head) pairs only; q/o are indexed by absolute

@@ -336,6 +336,34 @@ def test_gemm_rejects_bad_shapes(rt):
     assert e.value.status == cb.E_BAD_ARG
 
 
+def test_gemm_peer_stores_write_every_copy(rt):
+    """The gather-fused GEMM stores each output tile to C and to the peer copies: here the "peers" are two more
+    buffers of the same GPU, which must end up with the bits of the plain GEMM in their rows and nothing elsewhere."""
+    import oracle
+    m, n, k, rows_total, row0 = 384, 320, 256, 640, 128
+    rng = np.random.default_rng(11)
+    a = oracle.f32_to_bf16_bits(rng.standard_normal((m, k)).astype(np.float32) / 16)
+    b = oracle.f32_to_bf16_bits(rng.standard_normal((n, k)).astype(np.float32) / 16)
+    am, bm = cb.upload(a), cb.upload(b)
+    cm = cb.CatenaMem(); cb.check(cb.lib().catena_b200_mem_alloc(m * n * 2, C.byref(cm)))
+    cb.check(cb.lib().catena_b200_gemm_bf16_into(am.data, bm.data, cm.data, m, n, k, n))
+    want = cb.download(cm, np.uint16).reshape(m, n)
+    fill = np.full((rows_total, n), 0x7FC0, np.uint16)
+    peers = [cb.upload(fill), cb.upload(fill)]
+    ptrs = (C.c_void_p * 2)(*[p.data + row0 * n * 2 for p in peers])
+    cb.check(cb.lib().catena_b200_mem_write(cm, np.zeros(m * n, np.uint16).ctypes.data_as(C.c_void_p), m * n * 2))
+    cb.check(cb.lib().catena_b200_gemm_bf16_into_peers(am.data, bm.data, cm.data, m, n, k, n, ptrs, 2))
+    assert np.array_equal(cb.download(cm, np.uint16).reshape(m, n), want)
+    for p in peers:
+        got = cb.download(p, np.uint16).reshape(rows_total, n)
+        assert np.array_equal(got[row0:row0 + m], want)
+        assert (got[:row0] == 0x7FC0).all() and (got[row0 + m:] == 0x7FC0).all()
+    # needs the CTA-pair kernel
+    assert cb.lib().catena_b200_gemm_bf16_into_peers(am.data, bm.data, cm.data, 64, n, k, n, ptrs, 2) == cb.E_UNSUPPORTED
+    for x in [am, bm, cm] + peers:
+        cb.free(x)
+
+
 # ---------------------------------------------------------------- cached-attention decode
 def attn_inputs(B, Hq, Hkv, L, D=128, seeds=(2, 3, 4)):
     import oracle

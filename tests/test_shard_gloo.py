@@ -38,6 +38,13 @@ def _worker(rank, world, port, out_dir):
     local = torch.from_numpy(a @ bt[mine.n0:mine.n1].T)
     full = shard.gather_columns(local, blocks, m, dist)
     assert torch.equal(full, torch.from_numpy(a @ bt.T))
+    for mm in (1024, 700):                                  # equal blocks (one collective) and ragged blocks
+        a2 = rng.integers(-128, 128, (mm, k)).astype(np.int64)
+        rblocks = shard.row_blocks(mm, world, align=256)
+        mine_r = rblocks[rank]
+        local_r = torch.from_numpy(a2[mine_r.m0:mine_r.m1] @ bt.T)
+        full_r = shard.gather_rows(local_r, rblocks, dist)
+        assert torch.equal(full_r, torch.from_numpy(a2 @ bt.T))
     units, width = 37, 16
     rows = torch.arange(units * width, dtype=torch.float32).reshape(units, width)
     ranges = shard.unit_ranges(units, world)
@@ -59,6 +66,9 @@ def test_plans_are_tile_aligned_and_cover():
             assert blocks[0].n0 == 0 and blocks[-1].n1 == n
             for x, y in zip(blocks, blocks[1:]):
                 assert x.n1 == y.n0 and x.n1 % 256 == 0 or x.n1 == n
+            rows = shard.row_blocks(n, world)
+            assert rows[0].m0 == 0 and rows[-1].m1 == n
+            assert all(x.m1 == y.m0 and (x.m1 % 256 == 0 or x.m1 == n) for x, y in zip(rows, rows[1:]))
             ranges = shard.unit_ranges(256, world)
             assert ranges[0].u0 == 0 and ranges[-1].u1 == 256
             assert all(x.u1 == y.u0 for x, y in zip(ranges, ranges[1:]))
