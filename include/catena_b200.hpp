@@ -1,0 +1,365 @@
+// C++ host-side mirror of catena-lang's runtime surface over libcatena_b200.so (header-only, C++17).
+//
+// Names, argument meaning and error behaviour follow the reference's Rust API:
+//   Runtime::from_sources / Runtime::from_paths (`new`) / exec / mem_f32 / mem_u64   catena-lang/src/runtime/runtime.rs:104-236
+//   Value, ValueKind                                                                 catena-lang/src/runtime/value.rs:5-73
+//   Mem::to_f32_vec / to_u64_vec                                                     catena-lang/src/runtime/mem.rs:43-70
+//   ExecError variants                                                               catena-lang/src/runtime/runtime.rs:80-102
+//   GpuDialect {Hip, Cuda}                                                           catena-lang/src/codegen/mod.rs:50-54
+//
+// What differs, by design of a backend that SELECTS prebuilt sm_100a kernels instead of generating and compiling
+// C++ per Runtime (runtime.rs:123-164, artifact.rs:56-103):
+//   * from_sources does not run the catena compiler (its front end is Rust and not part of this build): it scans the
+//     sources for `(def program <name>` and registers the programs the library ships a kernel for.  A program without
+//     a kernel stays out of the table, so exec reports UnknownSourceFunction for it.  The stdlib is always present.
+//   * GpuDialect::Hip is refused with InitError.
+//   * Mem owns DEVICE memory and copies on to_*_vec.  Like the Rust API, exec consumes its Mem arguments: they are
+//     freed when the call returns (runtime.rs:175-179, mem.rs:119-125).
+//   * a failed device-side assertion or launch is ExecError::Device carrying the library status (the generated code
+//     of the reference would have trapped).
+// There is no CPU path: without a B200 every call that touches data fails with the library's status.
+#ifndef CATENA_B200_HPP
+#define CATENA_B200_HPP
+
+#include <cstdint>
+#include <cstring>
+#include <fstream>
+#include <functional>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "catena_b200.h"
+
+namespace catena_b200 {
+
+enum class GpuDialect { Hip, Cuda };
+enum class ValueKind { Bool, U32, U64, F32, Mem };
+
+inline const char* kind_name(ValueKind k) {
+    switch (k) {
+        case ValueKind::Bool: return "Bool";
+        case ValueKind::U32: return "U32";
+        case ValueKind::U64: return "U64";
+        case ValueKind::F32: return "F32";
+        default: return "Mem";
+    }
+}
+
+struct InitError : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+struct ExecError : std::runtime_error {
+    enum class Kind { UnknownSourceFunction, InputArityMismatch, OutputArityMismatch, TypeMismatch, Device };
+    Kind kind;
+    catena_status_t status;
+    ExecError(Kind k, const std::string& what, catena_status_t s = CATENA_OK) : std::runtime_error(what), kind(k), status(s) {}
+};
+
+// Owned device buffer: fat pointer {data, len_bytes} (mem.rs:38-41).  Move-only; freed on destruction.
+class Mem {
+public:
+    Mem() : raw_{nullptr, 0} {}
+    explicit Mem(catena_mem_t raw) : raw_(raw) {}
+    Mem(const Mem&) = delete;
+    Mem& operator=(const Mem&) = delete;
+    Mem(Mem&& o) noexcept : raw_(o.raw_) { o.raw_ = {nullptr, 0}; }
+    Mem& operator=(Mem&& o) noexcept {
+        if (this != &o) {
+            release();
+            raw_ = o.raw_;
+            o.raw_ = {nullptr, 0};
+        }
+        return *this;
+    }
+    ~Mem() { release(); }
+
+    uint64_t len_bytes() const { return raw_.len; }
+    bool is_null() const { return raw_.data == nullptr; }
+    catena_mem_t raw() const { return raw_; }
+
+    template <class T>
+    std::vector<T> to_vec() const {
+        std::vector<T> out(raw_.len / sizeof(T));
+        if (!out.empty()) {
+            catena_status_t s = catena_b200_mem_download(raw_, out.data(), out.size() * sizeof(T));
+            if (s != CATENA_OK) throw ExecError(ExecError::Kind::Device, std::string("mem download: ") + catena_b200_status_string(s), s);
+        }
+        return out;
+    }
+    std::vector<float> to_f32_vec() const { return to_vec<float>(); }        // mem.rs:43-56
+    std::vector<uint64_t> to_u64_vec() const { return to_vec<uint64_t>(); }  // mem.rs:58-70
+
+    static Mem from_bytes(const void* host, uint64_t bytes) {                // mem.rs:72-106
+        catena_mem_t raw{nullptr, 0};
+        catena_status_t s = catena_b200_mem_upload(host, bytes, &raw);
+        if (s != CATENA_OK) throw ExecError(ExecError::Kind::Device, std::string("mem upload: ") + catena_b200_status_string(s), s);
+        return Mem(raw);
+    }
+
+private:
+    void release() {
+        if (raw_.data) catena_b200_mem_free(raw_);
+        raw_ = {nullptr, 0};
+    }
+    catena_mem_t raw_;
+};
+
+// Tagged scalar or Mem (value.rs:5-21).
+class Value {
+public:
+    static Value boolean(bool v) { Value x(ValueKind::Bool); x.u_ = v ? 1 : 0; return x; }
+    static Value u32(uint32_t v) { Value x(ValueKind::U32); x.u_ = v; return x; }
+    static Value u64(uint64_t v) { Value x(ValueKind::U64); x.u_ = v; return x; }
+    static Value f32(float v) { Value x(ValueKind::F32); x.f_ = v; return x; }
+    static Value mem(Mem&& m) { Value x(ValueKind::Mem); x.m_ = std::move(m); return x; }
+
+    ValueKind kind() const { return kind_; }
+    bool as_bool() const { expect(ValueKind::Bool); return u_ != 0; }
+    uint32_t as_u32() const { expect(ValueKind::U32); return (uint32_t)u_; }
+    uint64_t as_u64() const { expect(ValueKind::U64); return u_; }
+    float as_f32() const { expect(ValueKind::F32); return f_; }
+    const Mem& as_mem() const { expect(ValueKind::Mem); return m_; }
+    Mem take_mem() { expect(ValueKind::Mem); return std::move(m_); }
+
+private:
+    explicit Value(ValueKind k) : kind_(k), u_(0), f_(0.0f) {}
+    void expect(ValueKind k) const {
+        if (kind_ != k) throw std::logic_error(std::string("Value holds ") + kind_name(kind_) + ", not " + kind_name(k));
+    }
+    ValueKind kind_;
+    uint64_t u_;
+    float f_;
+    Mem m_;
+};
+
+// C symbol of a source name (codegen/mod.rs:379-388): `program_` + name, every non-alphanumeric character replaced by `_`.
+inline std::string symbol_for(const std::string& name) {
+    std::string out;
+    for (char ch : name) out += ((ch >= '0' && ch <= '9') || (ch >= 'a' && ch <= 'z') || (ch >= 'A' && ch <= 'Z')) ? ch : '_';
+    if (!out.empty() && out[0] >= '0' && out[0] <= '9') out = "_" + out;
+    return "program_" + out;
+}
+
+class Runtime {
+public:
+    struct Signature {
+        std::string symbol;
+        std::vector<ValueKind> inputs, outputs;
+        // runs the program on already validated arguments; appends the outputs; returns the library status
+        std::function<catena_status_t(std::vector<Value>&, std::vector<Value>&)> call;
+    };
+
+    static Runtime from_sources(const std::vector<std::string>& sources, GpuDialect dialect = GpuDialect::Cuda) {
+        if (dialect != GpuDialect::Cuda)
+            throw InitError("GpuDialect::Hip is not supported: this backend only selects prebuilt sm_100a CUDA kernels");
+        Runtime rt;
+        for (auto& kv : stdlib()) rt.table_[kv.first] = kv.second;
+        const auto& user = user_programs();
+        for (const std::string& text : sources) {
+            size_t pos = 0;
+            while ((pos = text.find("(def", pos)) != std::string::npos) {
+                size_t p = pos + 4;
+                auto skip_ws = [&]() { while (p < text.size() && (text[p] == ' ' || text[p] == '\t' || text[p] == '\n' || text[p] == '\r')) ++p; };
+                skip_ws();
+                if (text.compare(p, 7, "program") == 0) {
+                    p += 7;
+                    skip_ws();
+                    size_t e = p;
+                    while (e < text.size() && !strchr(" \t\r\n:()", text[e])) ++e;
+                    auto it = user.find(text.substr(p, e - p));
+                    if (it != user.end()) rt.table_[it->first] = it->second;
+                }
+                pos += 4;
+            }
+        }
+        return rt;
+    }
+    // Runtime::new of the reference: the sources are files
+    static Runtime from_paths(const std::vector<std::string>& paths, GpuDialect dialect = GpuDialect::Cuda) {
+        std::vector<std::string> texts;
+        for (const std::string& path : paths) {
+            std::ifstream in(path);
+            if (!in) throw InitError("cannot read " + path);
+            std::stringstream ss;
+            ss << in.rdbuf();
+            texts.push_back(ss.str());
+        }
+        return from_sources(texts, dialect);
+    }
+
+    // memory constructors (runtime.rs:166-172; mem_bytes is additive: Mem is untyped bytes)
+    Mem mem_f32(const std::vector<float>& v) const { return Mem::from_bytes(v.data(), v.size() * sizeof(float)); }
+    Mem mem_u64(const std::vector<uint64_t>& v) const { return Mem::from_bytes(v.data(), v.size() * sizeof(uint64_t)); }
+    Mem mem_bytes(const void* host, uint64_t bytes) const { return Mem::from_bytes(host, bytes); }
+
+    bool has(const std::string& name) const { return table_.count(name) != 0; }
+    const Signature& signature(const std::string& name) const { return table_.at(name); }
+
+    // Runs a source-level `program` definition (runtime.rs:175-236).  `n_outputs` plays the role of the Rust const
+    // generic N (pass -1 not to check it).  The Mem arguments are consumed.
+    std::vector<Value> exec(const std::string& name, std::vector<Value> args, int n_outputs = -1) const {
+        auto it = table_.find(name);
+        if (it == table_.end()) throw ExecError(ExecError::Kind::UnknownSourceFunction, "Unknown source function '" + name + "'");
+        const Signature& sig = it->second;
+        if (args.size() != sig.inputs.size())
+            throw ExecError(ExecError::Kind::InputArityMismatch, "Function '" + name + "' expected " + std::to_string(sig.inputs.size()) +
+                                                                     " inputs, got " + std::to_string(args.size()));
+        if (n_outputs >= 0 && (size_t)n_outputs != sig.outputs.size())
+            throw ExecError(ExecError::Kind::OutputArityMismatch, "Function '" + name + "' expected " + std::to_string(sig.outputs.size()) +
+                                                                      " outputs, got " + std::to_string(n_outputs));
+        for (size_t i = 0; i < args.size(); ++i)
+            if (args[i].kind() != sig.inputs[i])
+                throw ExecError(ExecError::Kind::TypeMismatch, "Argument " + std::to_string(i) + " expected " + kind_name(sig.inputs[i]) +
+                                                                   ", got " + kind_name(args[i].kind()));
+        std::vector<Value> outs;
+        catena_status_t s = sig.call(args, outs);
+        args.clear();                       // inputs are moved into exec and dropped on return
+        if (s != CATENA_OK)
+            throw ExecError(ExecError::Kind::Device, "program '" + name + "' failed: " + catena_b200_status_string(s), s);
+        return outs;
+    }
+
+private:
+    using K = ValueKind;
+    using Table = std::map<std::string, Signature>;
+    Table table_;
+
+    static Signature make(const std::string& name, std::vector<K> ins, std::vector<K> outs,
+                          std::function<catena_status_t(std::vector<Value>&, std::vector<Value>&)> call) {
+        return Signature{symbol_for(name), std::move(ins), std::move(outs), std::move(call)};
+    }
+    // scalar f32 -> f32 programs have no status twin: they run on the host inside the library and cannot fail
+    static Signature scalar(const std::string& name, void (*fn)(float, float*)) {
+        return make(name, {K::F32}, {K::F32}, [fn](std::vector<Value>& a, std::vector<Value>& o) {
+            float r = 0.0f;
+            fn(a[0].as_f32(), &r);
+            o.push_back(Value::f32(r));
+            return CATENA_OK;
+        });
+    }
+    static Signature mem_to_mem(const std::string& name, catena_status_t (*fn)(catena_mem_t, catena_mem_t*)) {
+        return make(name, {K::Mem}, {K::Mem}, [fn](std::vector<Value>& a, std::vector<Value>& o) {
+            catena_mem_t r{nullptr, 0};
+            catena_status_t s = fn(a[0].as_mem().raw(), &r);
+            if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+            return s;
+        });
+    }
+    static Signature mem_to_f32(const std::string& name, catena_status_t (*fn)(catena_mem_t, float*)) {
+        return make(name, {K::Mem}, {K::F32}, [fn](std::vector<Value>& a, std::vector<Value>& o) {
+            float r = 0.0f;
+            catena_status_t s = fn(a[0].as_mem().raw(), &r);
+            if (s == CATENA_OK) o.push_back(Value::f32(r));
+            return s;
+        });
+    }
+
+    static const Table& stdlib() {
+        static const Table t = [] {
+            Table m;
+            m["math.sin-approx"] = scalar("math.sin-approx", program_math_sin_approx);
+            m["math.cos-approx"] = scalar("math.cos-approx", program_math_cos_approx);
+            m["math.sin-approx-full-nonneg"] = scalar("math.sin-approx-full-nonneg", program_math_sin_approx_full_nonneg);
+            m["math.sin-approx-full"] = scalar("math.sin-approx-full", program_math_sin_approx_full);
+            m["math.log-approx"] = scalar("math.log-approx", program_math_log_approx);
+            m["math.exp-approx-nonneg"] = scalar("math.exp-approx-nonneg", program_math_exp_approx_nonneg);
+            m["math.exp-approx"] = scalar("math.exp-approx", program_math_exp_approx);
+            m["math.exp2-approx"] = scalar("math.exp2-approx", program_math_exp2_approx);
+            m["math.log2-approx"] = scalar("math.log2-approx", program_math_log2_approx);
+            m["math.sqrt"] = scalar("math.sqrt", program_math_sqrt);
+            m["nn.sigmoid"] = scalar("nn.sigmoid", program_nn_sigmoid);
+            m["nn.silu"] = scalar("nn.silu", program_nn_silu);
+            m["nn.tanh"] = scalar("nn.tanh", program_nn_tanh);
+            m["nn.gelu-approx"] = scalar("nn.gelu-approx", program_nn_gelu_approx);
+            m["math.powf"] = make("math.powf", {K::F32, K::F32}, {K::F32}, [](std::vector<Value>& a, std::vector<Value>& o) {
+                float r = 0.0f;
+                program_math_powf(a[0].as_f32(), a[1].as_f32(), &r);
+                o.push_back(Value::f32(r));
+                return CATENA_OK;
+            });
+            m["nn.softmax"] = mem_to_mem("nn.softmax", program_nn_softmax_s);
+            m["nn.rmsnorm"] = mem_to_mem("nn.rmsnorm", program_nn_rmsnorm_s);
+            m["sum-f32"] = mem_to_f32("sum-f32", program_sum_f32_s);
+            m["mean-f32"] = mem_to_f32("mean-f32", program_mean_f32_s);
+            m["max-f32"] = mem_to_f32("max-f32", program_max_f32_s);
+            m["tensor.broadcast-f32"] = make("tensor.broadcast-f32", {K::F32, K::U64}, {K::Mem}, [](std::vector<Value>& a, std::vector<Value>& o) {
+                catena_mem_t r{nullptr, 0};
+                catena_status_t s = program_tensor_broadcast_f32_s(a[0].as_f32(), a[1].as_u64(), &r);
+                if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                return s;
+            });
+            m["tensor.arange-f32"] = make("tensor.arange-f32", {K::U64}, {K::Mem}, [](std::vector<Value>& a, std::vector<Value>& o) {
+                catena_mem_t r{nullptr, 0};
+                catena_status_t s = program_tensor_arange_f32_s(a[0].as_u64(), &r);
+                if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                return s;
+            });
+            m["tensor.slice-f32"] = make("tensor.slice-f32", {K::Mem, K::U64, K::U64}, {K::Mem}, [](std::vector<Value>& a, std::vector<Value>& o) {
+                catena_mem_t r{nullptr, 0};
+                catena_status_t s = program_tensor_slice_f32_s(a[0].as_mem().raw(), a[1].as_u64(), a[2].as_u64(), &r);
+                if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                return s;
+            });
+            m["tensor.concat-f32"] = make("tensor.concat-f32", {K::Mem, K::Mem}, {K::Mem}, [](std::vector<Value>& a, std::vector<Value>& o) {
+                catena_mem_t r{nullptr, 0};
+                catena_status_t s = program_tensor_concat_f32_s(a[0].as_mem().raw(), a[1].as_mem().raw(), &r);
+                if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                return s;
+            });
+            m["tensor.argmax-f32"] = make("tensor.argmax-f32", {K::Mem}, {K::U64}, [](std::vector<Value>& a, std::vector<Value>& o) {
+                uint64_t r = 0;
+                catena_status_t s = program_tensor_argmax_f32_s(a[0].as_mem().raw(), &r);
+                if (s == CATENA_OK) o.push_back(Value::u64(r));
+                return s;
+            });
+            return m;
+        }();
+        return t;
+    }
+
+    // programs a source file has to define to be callable (the reference's tests define them in .hex files)
+    static const Table& user_programs() {
+        static const Table t = [] {
+            Table m;
+            m["matmul-2x2-via-mem"] = make("matmul-2x2-via-mem", {K::Mem, K::Mem, K::U64, K::U64, K::U64, K::U64, K::U64, K::U64}, {K::Mem},
+                                           [](std::vector<Value>& a, std::vector<Value>& o) {
+                                               catena_mem_t r{nullptr, 0};
+                                               catena_status_t s = program_matmul_2x2_via_mem_s(a[0].as_mem().raw(), a[1].as_mem().raw(), a[2].as_u64(),
+                                                                                                a[3].as_u64(), a[4].as_u64(), a[5].as_u64(),
+                                                                                                a[6].as_u64(), a[7].as_u64(), &r);
+                                               if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                                               return s;
+                                           });
+            auto gemm = [](catena_status_t (*fn)(catena_mem_t, catena_mem_t, uint64_t, uint64_t, uint64_t, catena_mem_t*)) {
+                return [fn](std::vector<Value>& a, std::vector<Value>& o) {
+                    catena_mem_t r{nullptr, 0};
+                    catena_status_t s = fn(a[0].as_mem().raw(), a[1].as_mem().raw(), a[2].as_u64(), a[3].as_u64(), a[4].as_u64(), &r);
+                    if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                    return s;
+                };
+            };
+            m["gemm-bf16-rc"] = make("gemm-bf16-rc", {K::Mem, K::Mem, K::U64, K::U64, K::U64}, {K::Mem}, gemm(program_gemm_bf16_rc_s));
+            m["gemm-i8-rc"] = make("gemm-i8-rc", {K::Mem, K::Mem, K::U64, K::U64, K::U64}, {K::Mem}, gemm(program_gemm_i8_rc_s));
+            m["attn-decode-bf16"] = make("attn-decode-bf16", {K::Mem, K::Mem, K::Mem, K::U64, K::U64, K::U64, K::U64, K::U64}, {K::Mem},
+                                         [](std::vector<Value>& a, std::vector<Value>& o) {
+                                             catena_mem_t r{nullptr, 0};
+                                             catena_status_t s = program_attn_decode_bf16_s(a[0].as_mem().raw(), a[1].as_mem().raw(),
+                                                                                            a[2].as_mem().raw(), a[3].as_u64(), a[4].as_u64(),
+                                                                                            a[5].as_u64(), a[6].as_u64(), a[7].as_u64(), &r);
+                                             if (s == CATENA_OK) o.push_back(Value::mem(Mem(r)));
+                                             return s;
+                                         });
+            return m;
+        }();
+        return t;
+    }
+};
+
+}  // namespace catena_b200
+
+#endif  // CATENA_B200_HPP

@@ -1,0 +1,157 @@
+// Exercises the C++ host mirror (include/catena_b200.hpp) the way catena-lang/tests/runtime.rs and
+// catena-lang/tests/cases/{matrix,reducec}.rs exercise the Rust runtime.
+//   host_mirror_test cpu   pre-call checks only (no device needed): registration, arity and type errors, Hip refusal
+//   host_mirror_test gpu   the reference's known-answer vectors on the GPU
+// Prints "ok <n> checks" and exits 0, or the failed check and exits 1.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "catena_b200.hpp"
+
+using namespace catena_b200;
+
+static int g_checks = 0;
+#define CHECK(cond)                                                         \
+    do {                                                                    \
+        ++g_checks;                                                         \
+        if (!(cond)) {                                                      \
+            std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond);   \
+            return 1;                                                       \
+        }                                                                   \
+    } while (0)
+
+template <class F>
+static bool throws_kind(ExecError::Kind kind, F f) {
+    try {
+        f();
+    } catch (const ExecError& e) {
+        return e.kind == kind;
+    }
+    return false;
+}
+
+static const char* kMatmulSource = "(def program matmul-2x2-via-mem : x -> y = ())";
+
+static int run_cpu() {
+    Runtime rt = Runtime::from_sources({kMatmulSource});
+    CHECK(rt.has("nn.softmax") && rt.has("sum-f32") && rt.has("math.exp-approx"));      // the stdlib is always there
+    CHECK(rt.has("matmul-2x2-via-mem") && !rt.has("gemm-bf16-rc"));                      // only what the sources define
+    CHECK(rt.signature("matmul-2x2-via-mem").symbol == "program_matmul_2x2_via_mem");   // codegen/mod.rs:379-388
+    CHECK(symbol_for("tensor.argmax-f32") == "program_tensor_argmax_f32" && symbol_for("2x") == "program__2x");
+    // tests/runtime.rs:128-168: errors raised before the call
+    CHECK(throws_kind(ExecError::Kind::UnknownSourceFunction, [&] { rt.exec("no-such-program", {}); }));
+    CHECK(throws_kind(ExecError::Kind::InputArityMismatch, [&] {
+        std::vector<Value> a;
+        a.push_back(Value::f32(1.0f));
+        a.push_back(Value::f32(2.0f));
+        rt.exec("nn.silu", std::move(a));
+    }));
+    CHECK(throws_kind(ExecError::Kind::TypeMismatch, [&] {
+        std::vector<Value> a;
+        a.push_back(Value::u64(1));
+        rt.exec("nn.silu", std::move(a));
+    }));
+    CHECK(throws_kind(ExecError::Kind::OutputArityMismatch, [&] {
+        std::vector<Value> a;
+        a.push_back(Value::f32(1.0f));
+        rt.exec("nn.silu", std::move(a), 2);
+    }));
+    bool hip_refused = false;
+    try {
+        Runtime::from_sources({}, GpuDialect::Hip);
+    } catch (const InitError&) {
+        hip_refused = true;
+    }
+    CHECK(hip_refused);
+    Value v = Value::u32(7);
+    CHECK(v.kind() == ValueKind::U32 && v.as_u32() == 7);
+    Mem empty;
+    CHECK(empty.is_null() && empty.len_bytes() == 0 && empty.to_f32_vec().empty());
+    return 0;
+}
+
+static int run_gpu() {
+    if (catena_b200_init(0) != CATENA_OK) {
+        std::printf("FAILED: no device\n");
+        return 1;
+    }
+    Runtime rt = Runtime::from_sources({kMatmulSource, "(def program gemm-bf16-rc : x -> y = ())"});
+    // tests/cases/matrix.rs:6-46: [[1,2,3],[4,5,6]] . [[7,8],[9,10],[11,12]] = [58,64,139,154]
+    {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_f32({1, 2, 3, 4, 5, 6})));
+        a.push_back(Value::mem(rt.mem_f32({7, 8, 9, 10, 11, 12})));
+        for (uint64_t x : {2ull, 2ull, 3ull, 6ull, 6ull, 4ull}) a.push_back(Value::u64(x));
+        std::vector<Value> out = rt.exec("matmul-2x2-via-mem", std::move(a), 1);
+        std::vector<float> c = out[0].as_mem().to_f32_vec();
+        CHECK(c.size() == 4 && c[0] == 58.0f && c[1] == 64.0f && c[2] == 139.0f && c[3] == 154.0f);
+    }
+    // a length that does not match n*k is the program's runtime assert (tests/cases/matrix/matmul.hex:18-27): a status here
+    CHECK(throws_kind(ExecError::Kind::Device, [&] {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_f32({1, 2, 3, 4, 5})));
+        a.push_back(Value::mem(rt.mem_f32({7, 8, 9, 10, 11, 12})));
+        for (uint64_t x : {2ull, 2ull, 3ull, 6ull, 6ull, 4ull}) a.push_back(Value::u64(x));
+        rt.exec("matmul-2x2-via-mem", std::move(a));
+    }));
+    // tests/cases/reducec.rs:50-90
+    auto fold = [&](const char* name) {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_f32({1.5f, -0.5f, 2.0f, 4.0f})));
+        return rt.exec(name, std::move(a))[0].as_f32();
+    };
+    CHECK(fold("sum-f32") == 7.0f && fold("mean-f32") == 1.75f && fold("max-f32") == 4.0f);
+    // tests/runtime.rs:1046-1197: argmax keeps the first index on ties; concat with an empty side
+    {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_f32({1.0f, 5.0f, 5.0f, 2.0f})));
+        CHECK(rt.exec("tensor.argmax-f32", std::move(a))[0].as_u64() == 1);
+        std::vector<Value> b;
+        b.push_back(Value::mem(rt.mem_f32({})));
+        b.push_back(Value::mem(rt.mem_f32({3.0f, 4.0f})));
+        std::vector<float> c = rt.exec("tensor.concat-f32", std::move(b))[0].as_mem().to_f32_vec();
+        CHECK(c.size() == 2 && c[0] == 3.0f && c[1] == 4.0f);
+    }
+    // tests/runtime.rs:971-1009: softmax [1,2,4] within 6e-3 of libm, sums to 1
+    {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_f32({1.0f, 2.0f, 4.0f})));
+        std::vector<float> y = rt.exec("nn.softmax", std::move(a))[0].as_mem().to_f32_vec();
+        const double e[3] = {std::exp(-3.0), std::exp(-2.0), 1.0}, d = e[0] + e[1] + e[2];
+        CHECK(y.size() == 3 && std::fabs(y[0] - e[0] / d) < 6e-3 && std::fabs(y[1] - e[1] / d) < 6e-3 && std::fabs(y[2] - e[2] / d) < 6e-3);
+        CHECK(std::fabs(y[0] + y[1] + y[2] - 1.0f) < 1e-5);
+    }
+    // the polynomial is part of the semantics: math.exp-approx(0) is 0x3F7FF8FC, not 1 (stdlib/math.hex:148-199)
+    {
+        std::vector<Value> a;
+        a.push_back(Value::f32(0.0f));
+        float r = rt.exec("math.exp-approx", std::move(a))[0].as_f32();
+        uint32_t bits;
+        std::memcpy(&bits, &r, 4);
+        CHECK(bits == 0x3F7FF8FCu);
+    }
+    // bf16 GEMM through Runtime::exec: 256 x 256 x 64 of ones and twos -> every element 128 (exact in bf16)
+    {
+        const uint64_t m = 256, n = 256, k = 64;
+        std::vector<uint16_t> a(m * k, 0x3F80), b(n * k, 0x4000);   // 1.0, 2.0
+        std::vector<Value> args;
+        args.push_back(Value::mem(rt.mem_bytes(a.data(), a.size() * 2)));
+        args.push_back(Value::mem(rt.mem_bytes(b.data(), b.size() * 2)));
+        for (uint64_t x : {m, n, k}) args.push_back(Value::u64(x));
+        std::vector<uint16_t> c = rt.exec("gemm-bf16-rc", std::move(args))[0].as_mem().to_vec<uint16_t>();
+        bool all = c.size() == m * n;
+        for (uint16_t x : c) all = all && x == 0x4300;               // 128.0
+        CHECK(all);
+    }
+    return 0;
+}
+
+int main(int argc, char** argv) {
+    const std::string mode = argc > 1 ? argv[1] : "cpu";
+    int rc = mode == "gpu" ? run_gpu() : run_cpu();
+    if (rc == 0) std::printf("ok %d checks\n", g_checks);
+    return rc;
+}

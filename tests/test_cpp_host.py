@@ -1,0 +1,37 @@
+"""Builds the C++ host mirror's test program (include/catena_b200.hpp + tests/cpp/host_mirror_test.cpp) with g++
+against libcatena_b200.so and runs it: pre-call checks on CPU, the reference's known-answer vectors on the GPU."""
+import os
+import subprocess
+
+import pytest
+
+import catena_lang_b200 as cb
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIBDIR = os.path.dirname(cb.LIB_PATH)
+
+
+@pytest.fixture(scope="module")
+def binary(tmp_path_factory):
+    out = str(tmp_path_factory.mktemp("cpp") / "host_mirror_test")
+    gxx = os.environ.get("CXX", "g++")
+    cmd = [gxx, "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include",
+           os.path.join(ROOT, "tests", "cpp", "host_mirror_test.cpp"), "-o", out, "-L", LIBDIR, "-lcatena_b200",
+           "-Wl,-rpath," + LIBDIR, "-L/usr/local/cuda/lib64", "-Wl,-rpath,/usr/local/cuda/lib64"]
+    subprocess.check_call(cmd)
+    return out
+
+
+def run(binary, mode):
+    p = subprocess.run([binary, mode], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert p.stdout.strip().splitlines()[-1].startswith("ok ")
+
+
+def test_cpp_host_mirror_pre_call_checks(binary):
+    run(binary, "cpu")
+
+
+@pytest.mark.gpu
+def test_cpp_host_mirror_known_answers(binary):
+    run(binary, "gpu")
