@@ -516,7 +516,10 @@ def run_single(args):
     g = torch.Generator(device=dev)
     g.manual_seed(1)
     if which == "llama":
-        res = llama_bench(cb, L, torch, dev, stream, measured_peaks(), LLAMA_SMALL if args.small else LLAMA, reps=max(1, min(args.steps, 3)))
+        cfg = dict(LLAMA_SMALL if args.small else LLAMA)
+        if args.decode_steps:
+            cfg["decode_steps"] = args.decode_steps
+        res = llama_bench(cb, L, torch, dev, stream, measured_peaks(), cfg, reps=max(1, min(args.steps, 3)))
         print(json.dumps({"only": "llama", **res}), flush=True)
         return
     if which in ("gemm", "gemm_i8"):
@@ -607,6 +610,7 @@ def main():
                     choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm", "llama"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
+    ap.add_argument("--decode-steps", type=int, default=0, help="decode steps for --only llama (default: the workload's 128)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
