@@ -39,7 +39,10 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 32 KiB
 constexpr int NUM_THREADS = 192;
 constexpr int EPI_THREADS = 128;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 8;         // rasterisation in pair-tile rows (8 x 256 rows)
+#ifndef CATENA_GEMM_GROUP_M
+#define CATENA_GEMM_GROUP_M 8
+#endif
+constexpr int GROUP_M = CATENA_GEMM_GROUP_M;   // rasterisation in pair-tile rows (8 x 256 rows)
 constexpr uint64_t WAIT_NS = 1000000000ull;
 constexpr int kMaxPeers = 7;       // other GPUs of an 8-GPU box
 
