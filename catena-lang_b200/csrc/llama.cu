@@ -367,8 +367,9 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+// not volatile: the instruction is a pure function of its operands, so the compiler may interleave independent ones
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -446,17 +447,25 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const __nv_bfloat1
     __syncthreads();     // every warp holds its fragments: kbuf[0] may be overwritten
 
     // S tile = Q K^T for the 64 keys in `tile`: sacc[nb] covers keys 8 nb .. 8 nb + 7
+    // Consecutive MMAs go to different accumulators (four key blocks side by side): a chain of dependent mma.sync
+    // would wait out the result latency after every instruction.
     auto scores = [&](const uint8_t* tile, float (&sacc)[8][4]) {
 #pragma unroll
-        for (uint32_t nb = 0; nb < 8; ++nb) {
+        for (uint32_t nb = 0; nb < 8; ++nb)
 #pragma unroll
             for (int e = 0; e < 4; ++e) sacc[nb][e] = 0.0f;
 #pragma unroll
+        for (uint32_t nb0 = 0; nb0 < 8; nb0 += 4) {
+#pragma unroll
             for (uint32_t ks2 = 0; ks2 < 4; ++ks2) {   // two 16-d steps per ldmatrix.x4
-                uint32_t kf[4];
-                ldsm_x4(smem_addr(tile) + tile_off(nb * 8 + (lane & 7), 4 * ks2 + (lane >> 3)), kf);
-                mma_bf16(sacc[nb], qa[2 * ks2], kf[0], kf[1]);
-                mma_bf16(sacc[nb], qa[2 * ks2 + 1], kf[2], kf[3]);
+                uint32_t kf[4][4];
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j)
+                    ldsm_x4(smem_addr(tile) + tile_off((nb0 + j) * 8 + (lane & 7), 4 * ks2 + (lane >> 3)), kf[j]);
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) mma_bf16(sacc[nb0 + j], qa[2 * ks2], kf[j][0], kf[j][1]);
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) mma_bf16(sacc[nb0 + j], qa[2 * ks2 + 1], kf[j][2], kf[j][3]);
             }
         }
     };
@@ -534,13 +543,21 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const __nv_bfloat1
                 for (uint32_t rr = 0; rr < 2; ++rr)           // row g, row g + 8
                     split_hi_lo(sacc[2 * kk + half][2 * rr], sacc[2 * kk + half][2 * rr + 1], phi[half * 2 + rr], plo[half * 2 + rr]);
 #pragma unroll
-            for (uint32_t db2 = 0; db2 < 8; ++db2) {          // two 8-d blocks per ldmatrix.x4.trans
-                uint32_t vf[4];
-                ldsm_x4_trans(smem_addr(v_tile) + tile_off(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * db2 + (lane >> 4)), vf);
-                mma_bf16(oacc[2 * db2], phi, vf[0], vf[1]);
-                mma_bf16(oacc[2 * db2], plo, vf[0], vf[1]);
-                mma_bf16(oacc[2 * db2 + 1], phi, vf[2], vf[3]);
-                mma_bf16(oacc[2 * db2 + 1], plo, vf[2], vf[3]);
+            for (uint32_t db0 = 0; db0 < 8; db0 += 4) {       // eight 8-d blocks at a time: hi parts into all, then lo parts
+                uint32_t vf[4][4];
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j)              // two 8-d blocks per ldmatrix.x4.trans
+                    ldsm_x4_trans(smem_addr(v_tile) + tile_off(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * (db0 + j) + (lane >> 4)), vf[j]);
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    mma_bf16(oacc[2 * (db0 + j)], phi, vf[j][0], vf[j][1]);
+                    mma_bf16(oacc[2 * (db0 + j) + 1], phi, vf[j][2], vf[j][3]);
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    mma_bf16(oacc[2 * (db0 + j)], plo, vf[j][0], vf[j][1]);
+                    mma_bf16(oacc[2 * (db0 + j) + 1], plo, vf[j][2], vf[j][3]);
+                }
             }
         }
         __syncthreads();     // v_tile and kbuf[kt & 1] are free again
