@@ -213,3 +213,36 @@ def test_block_prefill_then_decode(orc, n_heads, n_kv_heads):
         assert blk.pos == S + 3
     finally:
         blk.close()
+
+
+def test_block_argument_errors():
+    """Bad arguments come back as statuses before anything is launched (the generated code of the reference would
+    have trapped on the device)."""
+    hidden, heads, kv_heads, ffn, vocab, max_len, B = 256, 2, 1, 512, 50, 8, 1
+    rng = np.random.default_rng(10)
+    blk = cb.LlamaBlock(hidden, heads, kv_heads, ffn, vocab, max_len, make_block(rng, hidden, heads, kv_heads, ffn, vocab), B)
+    L = cb.lib()
+    try:
+        ids = dev(np.zeros(max_len + 1, np.int32))
+        out = alloc((max_len + 1) * hidden * 2)
+        need = L.catena_b200_llama_workspace_bytes(C.byref(blk.struct), max_len + 1)
+        ws = alloc(need)
+        args = (blk.k_cache.data, blk.v_cache.data, out.data, ws.data)
+        assert L.catena_b200_llama_prefill(C.byref(blk.struct), ids.data, B, max_len + 1, *args, need) == cb.E_BAD_ARG      # beyond max_len
+        assert L.catena_b200_llama_prefill(C.byref(blk.struct), ids.data, B, 4, *args, 16) == cb.E_BAD_ARG                 # workspace too small
+        assert L.catena_b200_llama_prefill(C.byref(blk.struct), None, B, 4, *args, need) == cb.E_BAD_ARG                    # null ids
+        assert L.catena_b200_llama_decode(C.byref(blk.struct), ids.data, B, max_len, *args, need) == cb.E_BAD_ARG          # position == capacity
+        assert L.catena_b200_llama_prefill(None, ids.data, B, 4, *args, need) == cb.E_BAD_ARG
+        bad = cb.LlamaBlockStruct(hidden, 3, 2, ffn, vocab, max_len, *[blk._mems[n].data for n in ("embedding", "w_qkv", "w_o", "w_gate_up", "w_down")], 10000.0)
+        assert L.catena_b200_llama_workspace_bytes(C.byref(bad), 4) == 0                                                  # 3 heads over 2 kv heads
+        assert L.catena_b200_llama_prefill(C.byref(bad), ids.data, B, 4, *args, need) == cb.E_UNSUPPORTED
+        # an id outside the vocabulary is an assertion status, and the library stays usable afterwards
+        bad_ids = dev(np.array([vocab], np.int32))
+        assert L.catena_b200_llama_decode(C.byref(blk.struct), bad_ids.data, B, 0, *args, need) == cb.E_ASSERT
+        assert L.catena_b200_llama_decode(C.byref(blk.struct), ids.data, B, 0, *args, need) == cb.OK
+        # the last row of the cache can still be written
+        assert L.catena_b200_llama_prefill(C.byref(blk.struct), ids.data, B, max_len, *args, need) == cb.OK
+        for m in (ids, out, ws, bad_ids):
+            cb.free(m)
+    finally:
+        blk.close()
