@@ -1,0 +1,551 @@
+// Causal prefill attention on tcgen05 — the semantics of llama::attn_prefill_kernel (global row maximum first, then
+// p = exp~(s - max) with the reference's polynomial, probabilities as a bf16 hi + lo pair, fp32 sums), with both
+// contractions on the 5th-generation tensor cores:
+//   S[128 queries x 128 keys] = Q_tile[128 x 128 d] * K_tile^T      A = Q in shared memory, B = K tile (both K-major,
+//                                                                   128B swizzle, as TMA wrote them), D in TMEM
+//   O[128 queries x 128 d]   += P[128 x 128 keys] * V_tile           A = P in TENSOR MEMORY (written by the consumer
+//                                                                   threads with tcgen05.st), B = the V tile read as an
+//                                                                   MN-major operand (no transpose), hi then lo
+// One CTA per 128 queries of one head; a consumer thread owns one query row = one TMEM lane, so row maxima and row sums
+// need no cross-thread reduction.  exp~ admits no online rescaling, hence two passes over the key tiles: pass 1
+// multiplies Q K^T for the row maxima only, pass 2 multiplies again and accumulates P V.  A kernel that allocates TMEM
+// gets one CTA per SM, and the polynomial is the bulk of the instructions, so there are TWO consumer warpgroups: group g
+// takes the key tiles kt = g, g+2, ... (score buffer g); the two halves of a row's maximum and of its sum meet in shared
+// memory (sum = even tiles + odd tiles, a fixed order).
+//   warps 0-3 / 4-7  consumer groups 0 / 1 (warp w reads TMEM lanes 32 (w % 4) ..)
+//   warp 8     TMA producer (Q once, then K tiles / K and V tiles through a 5-stage ring)
+//   warp 9     MMA issuer; allocates the CTA's 512 TMEM columns:
+//              S buffer b at [128 b, 128 b + 128); its hi probabilities overwrite its first 64 columns in place (a chunk's
+//              packed result lands behind the columns already read); lo probabilities of buffer b at [256 + 64 b, ..);
+//              outputs at [384, 512)
+// Score tile kt+1 is multiplied while the consumers turn tile kt into probabilities.  All waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <type_traits>
+
+#include "catena_math.cuh"
+#include "common.cuh"
+
+namespace catena {
+
+namespace attn3 {
+
+constexpr int kD = 128;
+constexpr int kTile = 128;                   // queries per CTA, keys per ring stage
+constexpr int kStages = 5;
+constexpr int kHalfBytes = kTile * 128;      // 16 KiB: 128 rows x 64 d
+constexpr int kStageBytes = 2 * kHalfBytes;  // [d-half 2][row 128][128 B]
+constexpr int kConsumers = 128;              // per group
+constexpr int kThreads = 2 * kConsumers + 64;
+constexpr int kTmemCols = 512;
+constexpr int kLoCol = 256;                  // lo probabilities of buffer b at kLoCol + 64 b
+constexpr int kOCol = 384;
+constexpr uint64_t kWaitNs = 1000000000ull;
+constexpr uint32_t kSuspendHintNs = 20000;
+
+struct __align__(16) Control {
+    uint64_t q_full;
+    uint64_t full[kStages], empty[kStages];
+    uint64_t s_full[2], s_free[2];   // score buffers
+    uint64_t p_ready[2];             // probabilities of the buffer written to TMEM
+    uint64_t o_full;
+    float xch[2][kTile];             // per-row partial maxima / sums of the two consumer groups
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when it expired (about one second) or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Control* ctl, uint32_t* err) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 255u) == 0) {
+            if (ctl->abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitNs) {
+                ctl->abort_flag = 1;
+                atomicCAS(err, 0u, 5u);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (128B swizzle, descriptor version 1): K-major for Q and K tiles, MN-major for the
+// V tile (rows of 128 B along N = 64 d; consecutive K = keys are consecutive rows; 8-key groups 1024 B apart = SBO;
+// the second 64-d block `lbo` bytes away = LBO).
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// instruction descriptors: fp32 accumulate, bf16 operands, M = 128, N = 128; bit 16 = B is MN-major
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
+
+// math.exp-approx (catena-lang/stdlib/math.hex:148-199) for x <= 0, bit-identical to cmath::exp_approx there; the
+// round-to-nearest-even of t in [0, 2^22) goes through the 1.5 * 2^23 constant (same integer, same float).
+__device__ __forceinline__ float exp_approx_nonpos(float x) {
+    const float mag = -x;
+    const float t = cmath::mul(mag, cmath::from_bits(0x3FB8AA3Bu));
+    const float shifted = cmath::add(t, 12582912.0f);
+    const float kf = cmath::sub(shifted, 12582912.0f);
+    const uint32_t k = __float_as_uint(shifted) - 0x4B400000u;
+    float xr = cmath::sub(mag, cmath::mul(kf, cmath::from_bits(0x3F317200u)));
+    xr = cmath::sub(xr, cmath::mul(kf, cmath::from_bits(0x35BFBE8Eu)));
+    float p = cmath::add(cmath::from_bits(0x3EEF1187u), cmath::mul(xr, cmath::from_bits(0x3E738A8Bu)));
+    p = cmath::add(cmath::from_bits(0x3F809C7Eu), cmath::mul(xr, p));
+    p = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr, p));
+    p = cmath::mul(p, cmath::from_bits((k + 0x7Fu) * 0x00800000u));
+    return x < 0.0f ? cmath::recip(p) : p;
+}
+// The same function for eight arguments, written stage by stage across them: eight independent dependency chains are in
+// flight, so an instruction rarely waits for the result of the one before it (two warps share a scheduler here).
+// Arguments of masked keys must still be <= 0 (the caller passes 0 and discards the result).
+__device__ __forceinline__ void exp_approx_nonpos8(const float (&x)[8], float (&out)[8]) {
+    float mag[8], sh[8], kf[8], xr[8], p[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) mag[u] = -x[u];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) sh[u] = cmath::add(cmath::mul(mag[u], cmath::from_bits(0x3FB8AA3Bu)), 12582912.0f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) kf[u] = cmath::sub(sh[u], 12582912.0f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) xr[u] = cmath::sub(mag[u], cmath::mul(kf[u], cmath::from_bits(0x3F317200u)));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) xr[u] = cmath::sub(xr[u], cmath::mul(kf[u], cmath::from_bits(0x35BFBE8Eu)));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3EEF1187u), cmath::mul(xr[u], cmath::from_bits(0x3E738A8Bu)));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3F809C7Eu), cmath::mul(xr[u], p[u]));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr[u], p[u]));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) p[u] = cmath::mul(p[u], cmath::from_bits((__float_as_uint(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) out[u] = x[u] < 0.0f ? cmath::recip(p[u]) : p[u];
+}
+// two probabilities -> packed bf16 hi parts and packed bf16 lo parts (p - hi)
+__device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    const float r0 = cmath::sub(p0, __uint_as_float(hi << 16)), r1 = cmath::sub(p1, __uint_as_float(hi & 0xFFFF0000u));
+    const __nv_bfloat162 l = __floats2bfloat162_rn(r0, r1);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// grid (ceil(S / 128), Hq, B), 320 threads, one CTA per SM.
+__global__ void __launch_bounds__(kThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, uint32_t S, uint32_t Hq,
+                       uint32_t Hkv, float scale, uint32_t* err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_tile = smem;                                   // 32 KiB
+    uint8_t* ring = smem + kStageBytes;                       // kStages x 32 KiB
+    Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t qt = gridDim.x - 1 - blockIdx.x;           // heavy tiles first
+    const uint32_t h = blockIdx.y, b = blockIdx.z, kvh = h / (Hq / Hkv);
+    const uint32_t n = qt + 1;                                // visible key tiles
+    const int kv_unit = (int)(b * Hkv + kvh);
+
+    if (tid == 0) {
+        mbar_init(&ctl->q_full, 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&ctl->s_full[i], 1);
+            mbar_init(&ctl->s_free[i], kConsumers);
+            mbar_init(&ctl->p_ready[i], kConsumers);
+        }
+        mbar_init(&ctl->o_full, 1);
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctl->tmem_base;
+
+    if (warp == 8) {
+        // =============================== TMA producer ===============================
+        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) K(1) V(0) K(2) V(1) .. V(n-1)
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+            mbar_expect_tx(&ctl->q_full, kStageBytes);
+            tma_load_5d(smem_u32(q_tile), &map_q, 0, (int)(qt * kTile), 0, (int)h, (int)b, &ctl->q_full);
+            uint32_t g = 0;
+            bool ok = true;
+            auto issue = [&](const CUtensorMap* map, uint32_t kt) {
+                if (!ok) return;
+                const uint32_t st = g % kStages;
+                if (!mbar_wait(&ctl->empty[st], ((g / kStages) & 1u) ^ 1u, ctl, err)) { ok = false; return; }
+                mbar_expect_tx(&ctl->full[st], kStageBytes);
+                tma_load_4d(smem_u32(ring + st * kStageBytes), map, 0, (int)(kt * kTile), 0, kv_unit, &ctl->full[st]);
+                ++g;
+            };
+            for (uint32_t kt = 0; kt < n; ++kt) issue(&map_k, kt);
+            issue(&map_k, 0);
+            for (uint32_t kt = 0; kt < n; ++kt) {
+                if (kt + 1 < n) issue(&map_k, kt + 1);
+                issue(&map_v, kt);
+            }
+        }
+    } else if (warp == 9) {
+        // =============================== MMA issuer ===============================
+        if (lane == 0) {
+            uint32_t g = 0, uses[2] = {0, 0};
+            bool ok = mbar_wait(&ctl->q_full, 0, ctl, err);
+            const uint32_t qa = smem_u32(q_tile);
+            // S[buffer] = Q K^T with the K tile at the head of the ring
+            auto score_tile = [&](uint32_t buf) {
+                if (!ok) return;
+                if (!mbar_wait(&ctl->s_free[buf], (uses[buf] & 1u) ^ 1u, ctl, err)) { ok = false; return; }
+                if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; return; }
+                tc_fence_after();
+                const uint32_t ka = smem_u32(ring + (g % kStages) * kStageBytes);
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ++ks) {   // 16 d per MMA: d-half ks/4, 32 B steps inside the row
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3u) * 32;
+                    tc_mma_ss(tmem + buf * 128, desc_kmajor(qa + off), desc_kmajor(ka + off), kIdescQK, ks != 0 ? 1u : 0u);
+                }
+                tc_commit(&ctl->empty[g % kStages]);
+                tc_commit(&ctl->s_full[buf]);
+                ++g;
+                ++uses[buf];
+            };
+            // pass 1
+            for (uint32_t kt = 0; kt < n; ++kt) score_tile(kt & 1u);
+            // pass 2
+            score_tile(0);
+            for (uint32_t kt = 0; kt < n && ok; ++kt) {
+                const uint32_t buf = kt & 1u;
+                if (kt + 1 < n) score_tile(buf ^ 1u);
+                if (!ok) break;
+                if (!mbar_wait(&ctl->p_ready[buf], (kt >> 1) & 1u, ctl, err)) { ok = false; break; }
+                if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t va = smem_u32(ring + (g % kStages) * kStageBytes);
+#pragma unroll
+                for (uint32_t part = 0; part < 2; ++part) {          // hi probabilities, then lo
+                    const uint32_t pa = part == 0 ? tmem + buf * 128 : tmem + kLoCol + buf * 64;
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 8; ++kk)              // 16 keys per MMA = 8 TMEM columns of packed bf16
+                        tc_mma_ts(tmem + kOCol, pa + kk * 8, desc_mnmajor(va + kk * 2048, kHalfBytes), kIdescPV,
+                                  (kt | part | kk) != 0 ? 1u : 0u);
+                }
+                tc_commit(&ctl->empty[g % kStages]);
+                ++g;
+            }
+            if (ok) tc_commit(&ctl->o_full);
+        }
+    } else {
+        // =============================== consumers: group wg, thread r = query row r ===============================
+        const uint32_t wg = warp >> 2, r = tid & 127u, buf = wg;
+        const uint32_t row = qt * kTile + r;                         // position of this query in its sequence
+        const uint32_t lane_addr = tmem + (((warp & 3u) * 32u) << 16);
+        const float ninf = __uint_as_float(0xFF800000u);
+        bool aborted = false;
+        uint32_t uses = 0;                                           // score tiles of this group's buffer consumed
+        // ---- pass 1: row maximum over this group's tiles (of the raw scores: scaling by a positive constant is
+        // monotonic, so max_i fl(s_i * scale) = fl((max_i s_i) * scale); only the diagonal tile has masked keys) ----
+        float m_raw = ninf;
+        for (uint32_t kt = wg; kt < n; kt += 2) {
+            if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], uses & 1u, ctl, err))) {
+                aborted = true;
+                continue;
+            }
+            ++uses;
+            tc_fence_after();
+            const bool diag = kt == qt;
+            uint32_t va[32], vb[32];
+            tmem_ld32(lane_addr + buf * 128, va);
+            tmem_ld_wait();
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {                       // the next 32 columns are in flight while these are scanned
+                uint32_t (&cur)[32] = (c & 1u) ? vb : va;
+                uint32_t (&nxt)[32] = (c & 1u) ? va : vb;
+                if (c < 3) tmem_ld32(lane_addr + buf * 128 + (c + 1) * 32, nxt);
+                if (diag) {
+#pragma unroll
+                    for (uint32_t e = 0; e < 32; ++e)
+                        if (c * 32 + e <= r) m_raw = fmaxf(m_raw, __uint_as_float(cur[e]));
+                } else {
+#pragma unroll
+                    for (uint32_t e = 0; e < 32; ++e) m_raw = fmaxf(m_raw, __uint_as_float(cur[e]));
+                }
+                if (c < 3) tmem_ld_wait();
+            }
+            tc_fence_before();
+            mbar_arrive(&ctl->s_free[buf]);
+        }
+        ctl->xch[wg][r] = m_raw;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float m = cmath::mul(fmaxf(ctl->xch[0][r], ctl->xch[1][r]), scale);
+        asm volatile("bar.sync 1, 256;" ::: "memory");               // both halves read before xch is reused for the sums
+        // ---- pass 2: probabilities into TMEM, row sum ----
+        float l = 0.0f;
+        for (uint32_t kt = wg; kt < n; kt += 2) {
+            if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], uses & 1u, ctl, err))) {
+                aborted = true;
+                continue;
+            }
+            ++uses;
+            tc_fence_after();
+            // one chunk of 32 keys, ascending; MASKED only on the diagonal tile (keys past the query's own position)
+            auto chunk = [&](uint32_t c, auto masked_tag) {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+                uint32_t v[32], hi[16], lo[16];
+                tmem_ld32(lane_addr + buf * 128 + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (uint32_t e = 0; e < 32; e += 8) {               // eight keys side by side
+                    float xs[8], ps[8];
+#pragma unroll
+                    for (uint32_t u = 0; u < 8; ++u) {               // masked keys: argument 0, result discarded
+                        xs[u] = cmath::sub(cmath::mul(__uint_as_float(v[e + u]), scale), m);
+                        if (MASKED && c * 32 + e + u > r) xs[u] = 0.0f;
+                    }
+                    exp_approx_nonpos8(xs, ps);
+#pragma unroll
+                    for (uint32_t u = 0; u < 8; ++u) {
+                        if (MASKED && c * 32 + e + u > r) ps[u] = 0.0f;
+                        l = cmath::add(l, ps[u]);                    // ascending key order
+                    }
+#pragma unroll
+                    for (uint32_t u = 0; u < 8; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
+                }
+                // hi parts overwrite columns 16c .. 16c+15 of the score buffer (all of them already read), lo parts go beside
+                tmem_st16(lane_addr + buf * 128 + c * 16, hi);
+                tmem_st16(lane_addr + kLoCol + buf * 64 + c * 16, lo);
+            };
+            if (kt == qt) {
+#pragma unroll 1
+                for (uint32_t c = 0; c < 4; ++c) chunk(c, std::true_type{});
+            } else {
+#pragma unroll 1
+                for (uint32_t c = 0; c < 4; ++c) chunk(c, std::false_type{});
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&ctl->p_ready[buf]);
+            mbar_arrive(&ctl->s_free[buf]);
+        }
+        ctl->xch[wg][r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        l = cmath::add(ctl->xch[0][r], ctl->xch[1][r]);
+        // ---- outputs: O / l, group g takes d columns 64 g .. 64 g + 63 ----
+        if (!aborted && __all_sync(0xFFFFFFFFu, mbar_wait(&ctl->o_full, 0, ctl, err))) {
+            tc_fence_after();
+            __nv_bfloat16* orow = out + (((size_t)b * S + row) * Hq + h) * kD;
+#pragma unroll 1
+            for (uint32_t c = 2 * wg; c < 2 * wg + 2; ++c) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + kOCol + c * 32, v);
+                tmem_ld_wait();
+                if (row < S && !ctl->abort_flag) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (uint32_t e = 0; e < 32; e += 2) {
+                        const __nv_bfloat162 hv = __floats2bfloat162_rn(cmath::div(__uint_as_float(v[e]), l), cmath::div(__uint_as_float(v[e + 1]), l));
+                        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
+                    }
+#pragma unroll
+                    for (uint32_t qd = 0; qd < 4; ++qd)
+                        reinterpret_cast<uint4*>(orow + c * 32)[qd] = make_uint4(pk[4 * qd], pk[4 * qd + 1], pk[4 * qd + 2], pk[4 * qd + 3]);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
+}  // namespace attn3
+
+typedef CUresult (*EncodeTiledFnA3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFnA3 attn3_encode_fn() {
+    static EncodeTiledFnA3 fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFnA3)p;
+    }
+    return fn;
+}
+
+static thread_local uint32_t* g_attn3_err_dev[16] = {nullptr};
+
+// True when the tcgen05 prefill kernel takes the problem (it needs TMA-aligned operands).
+bool attn_prefill_tc_supports(const void* q, const void* k_cache, const void* v_cache, uint64_t hq, uint64_t hkv) {
+    return hkv != 0 && hq % hkv == 0 && !(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15);
+}
+
+// Reports (and clears) an expired wait of an earlier launch; synchronises the stream.
+catena_status_t attn_prefill_tc_check_errors() {
+    const int dev = tls().device & 15;
+    if (!g_attn3_err_dev[dev]) return CATENA_OK;
+    uint32_t h = 0;
+    CATENA_CUDA(cudaMemcpyAsync(&h, g_attn3_err_dev[dev], sizeof(h), cudaMemcpyDeviceToHost, tls().stream));
+    CATENA_CUDA(cudaStreamSynchronize(tls().stream));
+    if (h) {
+        cudaMemsetAsync(g_attn3_err_dev[dev], 0, sizeof(uint32_t), tls().stream);
+        return fail(CATENA_E_TIMEOUT, "attn_prefill: bounded wait expired");
+    }
+    return CATENA_OK;
+}
+
+// q [batch * seq, hq, 128] bf16, caches [batch, hkv, cap, 128] bf16, out [batch * seq, hq * 128] bf16.
+catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
+                                        uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t cap) {
+    EncodeTiledFnA3 fn = attn3_encode_fn();
+    if (!fn) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled is unavailable");
+    const int dev = tls().device & 15;
+    if (!g_attn3_err_dev[dev]) {
+        CATENA_CUDA(cudaMalloc(&g_attn3_err_dev[dev], sizeof(uint32_t)));
+        CATENA_CUDA(cudaMemset(g_attn3_err_dev[dev], 0, sizeof(uint32_t)));
+    }
+    CUtensorMap map_q, map_k, map_v;
+    {
+        // q as (64 d, seq tokens, 2 d-halves, hq heads, batch): one copy of box 64 x 128 x 2 x 1 x 1 brings 128 query rows of
+        // one head as [d-half][row][128 B], 128B-swizzled; rows past seq read as zero
+        cuuint64_t dims[5] = {64, seq, 2, hq, batch};
+        cuuint64_t strides[4] = {hq * 256, 128, 256, seq * hq * 256};
+        cuuint32_t box[5] = {64, (cuuint32_t)attn3::kTile, 2, 1, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUresult r = fn(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(q), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled (queries) failed");
+    }
+    for (int which = 0; which < 2; ++which) {
+        // cache as (64 d, seq visible rows, 2 d-halves, batch * hkv units owning `cap` rows each)
+        cuuint64_t dims[4] = {64, seq, 2, batch * hkv};
+        cuuint64_t strides[3] = {256, 128, cap * 256};
+        cuuint32_t box[4] = {64, (cuuint32_t)attn3::kTile, 2, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult r = fn(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_cache : k_cache), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled (kv cache) failed");
+    }
+    const size_t smem = 1024 + (size_t)(1 + attn3::kStages) * attn3::kStageBytes + sizeof(attn3::Control) + 16;
+    static thread_local bool attr_done[16] = {false};
+    if (!attr_done[dev]) {
+        CATENA_CUDA(cudaFuncSetAttribute(attn3::attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_done[dev] = true;
+    }
+    dim3 grid((unsigned)ceil_div_u64(seq, attn3::kTile), (unsigned)hq, (unsigned)batch);
+    attn3::attn_prefill_tc_kernel<<<grid, attn3::kThreads, smem, tls().stream>>>(map_q, map_k, map_v, (__nv_bfloat16*)out, (uint32_t)seq,
+                                                                                (uint32_t)hq, (uint32_t)hkv, 1.0f / sqrtf(128.0f),
+                                                                                g_attn3_err_dev[dev]);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail_cuda(e, "attn_prefill_tc launch");
+    return CATENA_OK;
+}
+
+}  // namespace catena

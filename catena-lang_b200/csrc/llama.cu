@@ -718,11 +718,29 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
                       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv,
                       (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
 }
+// Kernel selection for the prefill attention: the tcgen05 kernel (attn_prefill_tc.cu) unless CATENA_B200_PREFILL_TC=0
+// (read once) or the test hook asks for the mma.sync kernel of this file; both implement the same semantics.
+bool attn_prefill_tc_supports(const void* q, const void* k_cache, const void* v_cache, uint64_t hq, uint64_t hkv);
+catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
+                                        uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t cap);
+catena_status_t attn_prefill_tc_check_errors();
+static int g_prefill_tc_mode = -1;
+static bool prefill_tc_mode() {
+    if (g_prefill_tc_mode < 0) {
+        const char* e = getenv("CATENA_B200_PREFILL_TC");
+        g_prefill_tc_mode = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_prefill_tc_mode == 1;
+}
+void attn_prefill_set_tc_mode(int on) { g_prefill_tc_mode = on ? 1 : 0; }
+
 static catena_status_t launch_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, uint64_t batch,
                                            uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t cap) {
     if (!batch || !seq) return CATENA_OK;
     if (hkv == 0 || hq % hkv) return fail(CATENA_E_UNSUPPORTED, "attn_prefill: Hq must be a multiple of Hkv");
     if (seq > cap) return fail(CATENA_E_BAD_ARG, "attn_prefill: sequence beyond the cache capacity");
+    if (prefill_tc_mode() && attn_prefill_tc_supports(q, k_cache, v_cache, hq, hkv))
+        return enqueue_attn_prefill_tc(q, k_cache, v_cache, out, batch, seq, hq, hkv, cap);
     static thread_local bool attr_set = false;
     if (!attr_set) {
         CATENA_CUDA(cudaFuncSetAttribute(llama::attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 49152));
@@ -797,6 +815,7 @@ static catena_status_t composite(F body) {
         CATENA_CUDA(cudaStreamSynchronize(tls().stream));
         CATENA_TRY(gemm_tc_check_errors());
         CATENA_TRY(attn_check_errors());
+        CATENA_TRY(attn_prefill_tc_check_errors());
         CATENA_TRY(embed_check());
     }
     return CATENA_OK;
@@ -898,6 +917,7 @@ catena_status_t catena_b200_attn_decode_bf16_cache_into(const void* q, const voi
                                                         uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap) {
     return composite([&]() { return launch_attn_decode(q, k_cache, v_cache, o, batch, hq, hkv, d, kv_len, kv_cap, 0, batch * hkv); });
 }
+void catena_b200_debug_set_prefill_tc(int on) { attn_prefill_set_tc_mode(on); }
 catena_status_t catena_b200_swiglu_bf16_into(const void* gate_up, void* out, uint64_t tokens, uint64_t ffn) {
     if (!gate_up || !out) return fail(CATENA_E_BAD_ARG, "swiglu: null argument");
     return composite([&]() { return launch_swiglu(gate_up, out, tokens, ffn); });

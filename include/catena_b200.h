@@ -279,6 +279,9 @@ void catena_b200_debug_set_gemm_pair(int on);
 /* test hook: 1 = decode attention on the tcgen05 kernel, 0 = on the mma.sync kernel (same semantics).
  * No counterpart in the reference. */
 void catena_b200_debug_set_attn_tc(int on);
+/* test hook: 1 = prefill attention on the tcgen05 kernel (the default), 0 = on the mma.sync kernel (same semantics).
+ * No counterpart in the reference. */
+void catena_b200_debug_set_prefill_tc(int on);
 /* test hook: geometry of the calling thread's last decode-attention launch: out[0] = kernel (0 mma.sync, 1 tcgen05),
  * out[1] = clusters of 8 CTAs that can be resident at once, out[2] = clusters launched, out[3] = dynamic shared
  * memory per CTA in bytes.  No counterpart in the reference. */

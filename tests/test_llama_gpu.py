@@ -94,8 +94,16 @@ def test_rope_append(orc, B, S, hq, hkv):
         cb.free(m)
 
 
-@pytest.mark.parametrize("B,S,hq,hkv", [(1, 64, 2, 2), (2, 100, 4, 2), (1, 200, 8, 1), (1, 1, 1, 1)])
-def test_attn_prefill(orc, B, S, hq, hkv):
+@pytest.fixture(params=["tcgen05", "mma.sync"])
+def prefill_kernel(request):
+    """Runs a test once per prefill-attention kernel."""
+    cb.lib().catena_b200_debug_set_prefill_tc(1 if request.param == "tcgen05" else 0)
+    yield request.param
+    cb.lib().catena_b200_debug_set_prefill_tc(1)
+
+
+@pytest.mark.parametrize("B,S,hq,hkv", [(1, 64, 2, 2), (2, 100, 4, 2), (1, 200, 8, 1), (1, 1, 1, 1), (1, 384, 2, 1)])
+def test_attn_prefill(orc, prefill_kernel, B, S, hq, hkv):
     cap = S + 7
     rng = np.random.default_rng(3)
     q = bits(rng, (B * S, hq, 128)); kc = bits(rng, (B, hkv, cap, 128)); vc = bits(rng, (B, hkv, cap, 128))
