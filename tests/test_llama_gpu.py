@@ -118,6 +118,30 @@ def test_attn_prefill(orc, prefill_kernel, B, S, hq, hkv):
         cb.free(m)
 
 
+def test_attn_prefill_kernels_agree_long(orc):
+    """Nine key tiles per query tile (the ring wraps, both consumer groups take several tiles): the tcgen05 kernel and
+    the mma.sync kernel agree within one bf16 ulp, nearly everywhere exactly, and a sample of rows matches the oracle."""
+    B, S, hq, hkv = 2, 1100, 4, 2
+    cap = S
+    rng = np.random.default_rng(12)
+    q = bits(rng, (B * S, hq, 128)); kc = bits(rng, (B, hkv, cap, 128)); vc = bits(rng, (B, hkv, cap, 128))
+    qm, km, vm, om = dev(q), dev(kc), dev(vc), alloc(B * S * hq * 128 * 2)
+    outs = []
+    for tc in (1, 0):
+        cb.lib().catena_b200_debug_set_prefill_tc(tc)
+        try:
+            cb.check(cb.lib().catena_b200_attn_prefill_bf16_into(qm.data, km.data, vm.data, om.data, B, S, hq, hkv, cap))
+        finally:
+            cb.lib().catena_b200_debug_set_prefill_tc(1)
+        outs.append(cb.download(om, np.uint16).reshape(B * S, hq * 128))
+    close(outs[0], outs[1], rel=2.0 ** -7, floor=4e-6, frac_exact=0.97)
+    rows = [0, 127, 128, 700, S - 1, S + 5, 2 * S - 1]                    # tokens across tile boundaries of both sequences
+    want = orc.attn_cached_bf16(q, kc, vc, B, S, 0, hq, hkv, SCALE, threads=orc.max_threads())
+    close(outs[0][rows], want[rows], rel=2.0 ** -7, floor=4e-6, frac_exact=0.95)
+    for m in (qm, km, vm, om):
+        cb.free(m)
+
+
 @pytest.mark.parametrize("B,hq,hkv,L,cap", [(2, 4, 2, 37, 64), (4, 16, 16, 300, 512), (1, 8, 2, 129, 129)])
 def test_attn_decode_with_capacity(orc, B, hq, hkv, L, cap):
     """Cached attention on caches that own `cap` rows per unit of which `L` are visible; the rest is never read."""
