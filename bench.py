@@ -34,6 +34,12 @@ GEMM_FLOP = 2.0 * GEMM_M * GEMM_N * GEMM_K
 ATT_BYTES = 2 * ATT["B"] * ATT["Hkv"] * ATT["L"] * ATT["D"] * 2 + 2 * ATT["B"] * ATT["Hq"] * ATT["D"] * 2
 
 
+# DRAM traffic per launch from the ncu captures summarised under profiles/ (bytes): the GEMM capture is the bench launch
+# itself; the attention capture is the same kernel on a quarter of the batch (B=8), scaled by 4 (traffic grows with the batch)
+GEMM_NCU_TRAFFIC_BYTES = 85719808 + 15269120
+ATTN_NCU_TRAFFIC_BYTES = 4 * (134397696 + 4114176)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -298,13 +304,16 @@ def run_gpu(args, rank, world, local_rank):
                     "api": "Runtime.exec('gemm-bf16-rc') with pinned host operands, result copied back"},
             "gpu_launches": int(gemm_launches),
             "roofline": {"bound": "tensor", "achieved": gemm_tflops_1, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": gemm_tflops_1 / peaks["bf16_tflops"], "traffic": None,
+                         "frac": gemm_tflops_1 / peaks["bf16_tflops"], "traffic": GEMM_NCU_TRAFFIC_BYTES,
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch "
+                                           "(profiles/gemm_tc_bf16_4096.md); algorithmic bytes 100663296",
                          "peak_source": f"{peaks['source']} burst cuBLAS bf16", "kernel": "gemm_tc2_kernel<bf16>"},
             "attn_decode": {"metric": "kv_attn_decode_hbm_gbs", "value": world * attn_gbs_1, "unit": "GB/s",
                             "ms_per_step": attn_per, "gpu_launches": int(attn_launches), "clocks": attn_clocks,
                             "config": {"workload": "decode attention B=32 Hq=32 Hkv=8 D=128 L=4096 bf16, 537395200 algorithmic bytes per launch"},
                             "roofline": {"bound": "hbm", "achieved": attn_gbs_1, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                         "frac": attn_gbs_1 / peaks["hbm_gbs"], "traffic": None,
+                                         "frac": attn_gbs_1 / peaks["hbm_gbs"], "traffic": ATTN_NCU_TRAFFIC_BYTES,
+                                         "traffic_source": "4 x the ncu capture of the B=8 case (profiles/attn_decode_tc_small_B8.md)",
                                          "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "attn_decode_tc_kernel"}},
             "llama_block": llama,
             "sharded": {"scaling": "strong", "n_gpus": world, **sharded},
