@@ -45,8 +45,9 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as fh:
             p = json.load(fh)
-        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -304,7 +305,9 @@ def run_gpu(args, rank, world, local_rank):
                     "api": "Runtime.exec('gemm-bf16-rc') with pinned host operands, result copied back"},
             "gpu_launches": int(gemm_launches),
             "roofline": {"bound": "tensor", "achieved": gemm_tflops_1, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": gemm_tflops_1 / peaks["bf16_tflops"], "traffic": GEMM_NCU_TRAFFIC_BYTES,
+                         "frac": gemm_tflops_1 / peaks["bf16_tflops"],
+                         "frac_of_sustained_peak": (gemm_tflops_1 / peaks["bf16_tflops_sustained"]) if peaks.get("bf16_tflops_sustained") else None,
+                         "traffic": GEMM_NCU_TRAFFIC_BYTES,
                          "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch "
                                            "(profiles/gemm_tc_bf16_4096.md); algorithmic bytes 100663296",
                          "peak_source": f"{peaks['source']} burst cuBLAS bf16", "kernel": "gemm_tc2_kernel<bf16>"},
