@@ -1,0 +1,143 @@
+// Native-CUDA lowering (header-only, C++17): selects a prebuilt sm_100a kernel for a lowered catena module instead of
+// rendering C++ source for it.
+//
+// Input is the reference's semantic IR after `codegen::codegen` — GpuModule { name, source_name, entry: GpuFunction {
+// sources, targets, assignments: [GpuAssign { op, inputs, outputs }] } } (catena-lang/src/codegen/mod.rs:107-146).
+// Where the reference calls `render_modules` (catena-lang/src/codegen/gpu.rs:111-143) this backend calls `select`, which
+// recognises the shapes the stdlib lowers to:
+//   * one `materializec` whose producer is the matmul cell chain (`f32.matmul.row-major.cell-at`,
+//     catena-lang/stdlib/matrix.hex:261-327; the lowering leaves exactly one materializec,
+//     catena-lang/tests/compile/closures/matmul.rs:45-53)                     -> f32 GEMM kernel
+//   * `reducec` with `f32.add-env` / `f32.max-env` / `tensor.argmax-env` and an element getter
+//     (catena-lang/stdlib/sum.hex, tensor.hex:171-227)                         -> fold kernels
+//   * max fold + exp-shifted sum fold + `nn.softmax-at` map (nn.hex:93-122)    -> fused softmax
+//   * squared-sum fold + `nn.rmsnorm-at` map (nn.hex:154-182)                  -> fused rmsnorm
+//   * `materializec` over tensor.broadcast-at / arange-at / slice-at / concat-f32-at (tensor.hex) -> fill / copy kernels
+//   * a module of scalar primitives only                                       -> host execution
+// Anything else is reported as unsupported (the reference would render a generic one-thread-per-element kernel for it;
+// this backend ships no source generator).  The Rust front end that produces the IR is not part of this build, so the
+// fixtures of the tests are written by hand from the lowering rules cited above.
+#ifndef CATENA_B200_LOWERING_HPP
+#define CATENA_B200_LOWERING_HPP
+
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace catena_b200 {
+namespace lowering {
+
+// An input or output of an assignment: a lowered variable, or the symbol of the function a closure points at.
+struct Operand {
+    std::string name;
+    std::string lowered;      // "f32", "u64", "ptr<f32>", "mem", "erased", ...; empty for a function symbol
+    bool is_fn = false;
+    static Operand var(std::string n, std::string l) { return Operand{std::move(n), std::move(l), false}; }
+    static Operand fn(std::string n) { return Operand{std::move(n), std::string(), true}; }
+};
+struct GpuAssign {
+    std::string op;
+    std::vector<Operand> inputs, outputs;
+    std::string call_symbol;  // non-empty for a call of another program
+};
+struct GpuFunction {
+    std::string name;
+    std::vector<Operand> sources, targets;
+    std::vector<GpuAssign> assignments;
+};
+struct GpuModule {
+    std::string name, source_name;
+    GpuFunction entry;
+};
+struct KernelPlan {
+    std::string kernel;       // name of the prebuilt kernel family
+    std::string symbol;       // C symbol of the entry point that runs it
+    std::string note;
+};
+struct Unsupported : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+// C symbol of a source name (catena-lang/src/codegen/mod.rs:379-388)
+inline std::string symbol_for(const std::string& name) {
+    std::string out;
+    for (char ch : name) out += ((ch >= '0' && ch <= '9') || (ch >= 'a' && ch <= 'z') || (ch >= 'A' && ch <= 'Z')) ? ch : '_';
+    if (!out.empty() && out[0] >= '0' && out[0] <= '9') out = "_" + out;
+    return "program_" + out;
+}
+
+namespace detail {
+inline bool has_fn(const GpuAssign& a, const std::string& name) {
+    for (const Operand& o : a.inputs)
+        if (o.is_fn && o.name == name) return true;
+    return false;
+}
+inline bool starts_with(const std::string& s, const char* prefix) { return s.rfind(prefix, 0) == 0; }
+}  // namespace detail
+
+// One assignment -> kernel family, "scalar", or "" when nothing matches.
+inline std::string classify(const GpuAssign& a) {
+    using detail::has_fn;
+    if (a.op == "reducec") {
+        static const char* folds[][3] = {{"f32.add-env", "f32-at", "fold_sum"},
+                                         {"f32.max-env", "f32-at", "fold_max"},
+                                         {"f32.add-env", "nn.squared-at", "fold_sumsq"},
+                                         {"f32.add-env", "nn.softmax-exp-shifted-at", "fold_expsum"},
+                                         {"tensor.argmax-env", "tensor.argmax-pair-at", "fold_argmax"}};
+        for (auto& f : folds)
+            if (has_fn(a, f[0]) && has_fn(a, f[1])) return f[2];
+        return "";
+    }
+    if (a.op == "materializec" || a.op == "gpu.materialize") {
+        for (const Operand& o : a.inputs)
+            if (o.is_fn && (o.name.find("f32.matmul.row-major.cell-at") != std::string::npos || detail::starts_with(o.name, "closure.f32.matmul")))
+                return "gemm_f32";
+        static const char* maps[][2] = {{"tensor.broadcast-at", "fill_broadcast"}, {"tensor.arange-at", "fill_arange"},
+                                        {"tensor.slice-at", "copy_slice"},         {"tensor.concat-f32-at", "copy_concat"},
+                                        {"nn.softmax-at", "softmax_map"},          {"nn.rmsnorm-at", "rmsnorm_map"}};
+        for (const Operand& o : a.inputs)
+            if (o.is_fn)
+                for (auto& m : maps)
+                    if (o.name == m[0]) return m[1];
+        return "";
+    }
+    // scalar primitives the renderer prints as single C expressions (catena-lang/src/codegen/gpu.rs:322-447)
+    static const char* scalar_prefixes[] = {"f32.", "u32.", "u64.", "bool.", "const.", "ix", "unit.", ":.", "ax-mp", "assert", "mem.cast",
+                                            "buf.", "row-major-", "math.", "nn.sigmoid", "nn.silu", "nn.tanh", "nn.gelu"};
+    for (const char* p : scalar_prefixes)
+        if (detail::starts_with(a.op, p)) return "scalar";
+    return a.call_symbol.empty() ? "" : "scalar";
+}
+
+// GpuModule -> KernelPlan, or throws Unsupported.
+inline KernelPlan select(const GpuModule& module) {
+    std::vector<std::string> kinds;
+    for (const GpuAssign& a : module.entry.assignments) {
+        const std::string k = classify(a);
+        if (k.empty()) throw Unsupported(module.name + ": no prebuilt kernel for `" + a.op + "`");
+        if (k != "scalar") kinds.push_back(k);
+    }
+    const std::string symbol = module.source_name.empty() ? module.name : symbol_for(module.source_name);
+    auto is = [&](std::initializer_list<const char*> want) {
+        if (kinds.size() != want.size()) return false;
+        size_t i = 0;
+        for (const char* w : want)
+            if (kinds[i++] != w) return false;
+        return true;
+    };
+    if (kinds.empty()) return {"host_scalar", symbol, "runs on the host, like the reference's non-materialize code"};
+    if (is({"gemm_f32"})) return {"matmul_f32_kernel", symbol, "bit-exact ascending-k fold, smem-tiled"};
+    if (is({"fold_max", "fold_expsum", "softmax_map"}))
+        return {"softmax_fused", symbol, "two host folds + one map kernel in the reference; one launch here up to 65536 elements"};
+    if (is({"fold_sumsq", "rmsnorm_map"})) return {"rmsnorm_fused", symbol, "host fold + map kernel in the reference"};
+    if (kinds.size() == 1) return {kinds[0], symbol, ""};
+    std::string all;
+    for (const std::string& k : kinds) all += (all.empty() ? "" : ", ") + k;
+    throw Unsupported(module.name + ": unrecognised combination " + all);
+}
+
+}  // namespace lowering
+}  // namespace catena_b200
+
+#endif  // CATENA_B200_LOWERING_HPP

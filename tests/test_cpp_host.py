@@ -35,3 +35,12 @@ def test_cpp_host_mirror_pre_call_checks(binary):
 @pytest.mark.gpu
 def test_cpp_host_mirror_known_answers(binary):
     run(binary, "gpu")
+
+
+def test_cpp_lowering_selector(tmp_path):
+    """The C++ kernel selector over the lowered IR (include/catena_b200_lowering.hpp), same fixtures as test_lowering.py."""
+    out = str(tmp_path / "lowering_test")
+    subprocess.check_call([os.environ.get("CXX", "g++"), "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"),
+                           os.path.join(ROOT, "tests", "cpp", "lowering_test.cpp"), "-o", out])
+    p = subprocess.run([out], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and p.stdout.strip().startswith("ok "), p.stdout + p.stderr
