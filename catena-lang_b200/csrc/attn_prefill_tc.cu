@@ -184,31 +184,35 @@ __device__ __forceinline__ float exp_approx_nonpos(float x) {
     p = cmath::mul(p, cmath::from_bits((k + 0x7Fu) * 0x00800000u));
     return x < 0.0f ? cmath::recip(p) : p;
 }
-// The same function for eight arguments, written stage by stage across them: eight independent dependency chains are in
+// The same function for kExpW (8) arguments, written stage by stage across them: that many independent dependency chains are in
 // flight, so an instruction rarely waits for the result of the one before it (two warps share a scheduler here).
 // Arguments of masked keys must still be <= 0 (the caller passes 0 and discards the result).
-__device__ __forceinline__ void exp_approx_nonpos8(const float (&x)[8], float (&out)[8]) {
-    float mag[8], sh[8], kf[8], xr[8], p[8];
+#ifndef CATENA_PF_EXPW
+#define CATENA_PF_EXPW 8
+#endif
+constexpr int kExpW = CATENA_PF_EXPW;
+__device__ __forceinline__ void exp_approx_nonpos_n(const float (&x)[kExpW], float (&out)[kExpW]) {
+    float mag[kExpW], sh[kExpW], kf[kExpW], xr[kExpW], p[kExpW];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) mag[u] = -x[u];
+    for (int u = 0; u < kExpW; ++u) mag[u] = -x[u];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) sh[u] = cmath::add(cmath::mul(mag[u], cmath::from_bits(0x3FB8AA3Bu)), 12582912.0f);
+    for (int u = 0; u < kExpW; ++u) sh[u] = cmath::add(cmath::mul(mag[u], cmath::from_bits(0x3FB8AA3Bu)), 12582912.0f);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) kf[u] = cmath::sub(sh[u], 12582912.0f);
+    for (int u = 0; u < kExpW; ++u) kf[u] = cmath::sub(sh[u], 12582912.0f);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) xr[u] = cmath::sub(mag[u], cmath::mul(kf[u], cmath::from_bits(0x3F317200u)));
+    for (int u = 0; u < kExpW; ++u) xr[u] = cmath::sub(mag[u], cmath::mul(kf[u], cmath::from_bits(0x3F317200u)));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) xr[u] = cmath::sub(xr[u], cmath::mul(kf[u], cmath::from_bits(0x35BFBE8Eu)));
+    for (int u = 0; u < kExpW; ++u) xr[u] = cmath::sub(xr[u], cmath::mul(kf[u], cmath::from_bits(0x35BFBE8Eu)));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3EEF1187u), cmath::mul(xr[u], cmath::from_bits(0x3E738A8Bu)));
+    for (int u = 0; u < kExpW; ++u) p[u] = cmath::add(cmath::from_bits(0x3EEF1187u), cmath::mul(xr[u], cmath::from_bits(0x3E738A8Bu)));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3F809C7Eu), cmath::mul(xr[u], p[u]));
+    for (int u = 0; u < kExpW; ++u) p[u] = cmath::add(cmath::from_bits(0x3F809C7Eu), cmath::mul(xr[u], p[u]));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr[u], p[u]));
+    for (int u = 0; u < kExpW; ++u) p[u] = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr[u], p[u]));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) p[u] = cmath::mul(p[u], cmath::from_bits((__float_as_uint(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
+    for (int u = 0; u < kExpW; ++u) p[u] = cmath::mul(p[u], cmath::from_bits((__float_as_uint(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
 #pragma unroll
-    for (int u = 0; u < 8; ++u) out[u] = x[u] < 0.0f ? cmath::recip(p[u]) : p[u];
+    for (int u = 0; u < kExpW; ++u) out[u] = x[u] < 0.0f ? cmath::recip(p[u]) : p[u];
 }
 // two probabilities -> packed bf16 hi parts and packed bf16 lo parts (p - hi)
 __device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, uint32_t& lo) {
@@ -393,21 +397,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tmem_ld32(lane_addr + buf * 128 + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (uint32_t e = 0; e < 32; e += 8) {               // eight keys side by side
-                    float xs[8], ps[8];
+                for (uint32_t e = 0; e < 32; e += kExpW) {           // kExpW keys side by side
+                    float xs[kExpW], ps[kExpW];
 #pragma unroll
-                    for (uint32_t u = 0; u < 8; ++u) {               // masked keys: argument 0, result discarded
+                    for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) { // masked keys: argument 0, result discarded
                         xs[u] = cmath::sub(cmath::mul(__uint_as_float(v[e + u]), scale), m);
                         if (MASKED && c * 32 + e + u > r) xs[u] = 0.0f;
                     }
-                    exp_approx_nonpos8(xs, ps);
+                    exp_approx_nonpos_n(xs, ps);
 #pragma unroll
-                    for (uint32_t u = 0; u < 8; ++u) {
+                    for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) {
                         if (MASKED && c * 32 + e + u > r) ps[u] = 0.0f;
                         l = cmath::add(l, ps[u]);                    // ascending key order
                     }
 #pragma unroll
-                    for (uint32_t u = 0; u < 8; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
+                    for (uint32_t u = 0; u < (uint32_t)kExpW; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
                 }
                 // hi parts overwrite columns 16c .. 16c+15 of the score buffer (all of them already read), lo parts go beside
                 tmem_st16(lane_addr + buf * 128 + c * 16, hi);
