@@ -9,16 +9,16 @@
 // One CTA per 128 queries of one head; a consumer thread owns one query row = one TMEM lane, so row maxima and row sums
 // need no cross-thread reduction.  exp~ admits no online rescaling, hence two passes over the key tiles: pass 1
 // multiplies Q K^T for the row maxima only, pass 2 multiplies again and accumulates P V.  A kernel that allocates TMEM
-// gets one CTA per SM, and the polynomial is the bulk of the instructions, so there are TWO consumer warpgroups: group g
-// takes the key tiles kt = g, g+2, ... (score buffer g); the two halves of a row's maximum and of its sum meet in shared
-// memory (sum = even tiles + odd tiles, a fixed order).
-//   warps 0-3 / 4-7  consumer groups 0 / 1 (warp w reads TMEM lanes 32 (w % 4) ..)
-//   warp 8     TMA producer (Q once, then K tiles / K and V tiles through a 5-stage ring)
-//   warp 9     MMA issuer; allocates the CTA's 512 TMEM columns:
-//              S buffer b at [128 b, 128 b + 128); its hi probabilities overwrite its first 64 columns in place (a chunk's
-//              packed result lands behind the columns already read); lo probabilities of buffer b at [256 + 64 b, ..);
+// gets one CTA per SM, and the polynomial is the bulk of the instructions, so the CTA carries FOUR consumer warpgroups:
+// key tiles are 64 wide, group g takes the tiles kt = g, g+4, ... (score buffer g); the four parts of a row's maximum
+// and of its sum meet in shared memory (sum = ((part 0 + part 1) + part 2) + part 3, a fixed order).
+//   warps 4g .. 4g+3  consumer group g (warp w reads TMEM lanes 32 (w % 4) ..)
+//   warp 16    TMA producer (Q once, then K tiles / K and V tiles through a 10-stage ring of 16 KiB)
+//   warp 17    MMA issuer; allocates the CTA's 512 TMEM columns:
+//              S buffer b at [64 b, 64 b + 64); its hi probabilities overwrite its first 32 columns in place (a chunk's
+//              packed result lands behind the columns already read); lo probabilities of buffer b at [256 + 32 b, ..);
 //              outputs at [384, 512)
-// Score tile kt+1 is multiplied while the consumers turn tile kt into probabilities.  All waits are bounded.
+// Score tiles run three ahead of the probabilities.  All waits are bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -32,14 +32,17 @@ namespace catena {
 namespace attn3 {
 
 constexpr int kD = 128;
-constexpr int kTile = 128;                   // queries per CTA, keys per ring stage
-constexpr int kStages = 5;
-constexpr int kHalfBytes = kTile * 128;      // 16 KiB: 128 rows x 64 d
-constexpr int kStageBytes = 2 * kHalfBytes;  // [d-half 2][row 128][128 B]
+constexpr int kTile = 128;                   // queries per CTA
+constexpr int kKeys = 64;                    // keys per ring stage / score buffer
+constexpr int kGroups = 4;                   // consumer warpgroups = score buffers
+constexpr int kStages = 10;
+constexpr int kQBytes = 2 * kTile * 128;     // [d-half 2][row 128][128 B]
+constexpr int kKeyHalfBytes = kKeys * 128;   // 8 KiB: 64 keys x 64 d
+constexpr int kStageBytes = 2 * kKeyHalfBytes;
 constexpr int kConsumers = 128;              // per group
-constexpr int kThreads = 2 * kConsumers + 64;
+constexpr int kThreads = kGroups * kConsumers + 64;
 constexpr int kTmemCols = 512;
-constexpr int kLoCol = 256;                  // lo probabilities of buffer b at kLoCol + 64 b
+constexpr int kLoCol = 256;                  // lo probabilities of buffer b at kLoCol + 32 b
 constexpr int kOCol = 384;
 constexpr uint64_t kWaitNs = 1000000000ull;
 constexpr uint32_t kSuspendHintNs = 20000;
@@ -47,10 +50,10 @@ constexpr uint32_t kSuspendHintNs = 20000;
 struct __align__(16) Control {
     uint64_t q_full;
     uint64_t full[kStages], empty[kStages];
-    uint64_t s_full[2], s_free[2];   // score buffers
-    uint64_t p_ready[2];             // probabilities of the buffer written to TMEM
+    uint64_t s_full[kGroups], s_free[kGroups];   // score buffers
+    uint64_t p_ready[kGroups];       // probabilities of the buffer written to TMEM
     uint64_t o_full;
-    float xch[2][kTile];             // per-row partial maxima / sums of the two consumer groups
+    float xch[kGroups][kTile];       // per-row partial maxima / sums of the consumer groups
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -164,9 +167,10 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo) {
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
 }
-// instruction descriptors: fp32 accumulate, bf16 operands, M = 128, N = 128; bit 16 = B is MN-major
-constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-constexpr uint32_t kIdescPV = kIdescQK | (1u << 16);
+// instruction descriptors: fp32 accumulate, bf16 operands, M = 128; N = 64 keys for the scores, N = 128 d for the outputs,
+// where bit 16 says that B (the V tile) is MN-major
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24) | (1u << 16);
 
 // math.exp-approx (catena-lang/stdlib/math.hex:148-199) for x <= 0, bit-identical to cmath::exp_approx there; the
 // round-to-nearest-even of t in [0, 2^22) goes through the 1.5 * 2^23 constant (same integer, same float).
@@ -223,7 +227,7 @@ __device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, ui
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-// grid (ceil(S / 128), Hq, B), 320 threads, one CTA per SM.
+// grid (ceil(S / 128), Hq, B), 576 threads, one CTA per SM.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, uint32_t S, uint32_t Hq,
@@ -231,19 +235,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* q_tile = smem;                                   // 32 KiB
-    uint8_t* ring = smem + kStageBytes;                       // kStages x 32 KiB
+    uint8_t* ring = smem + kQBytes;                           // kStages x 16 KiB
     Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t qt = gridDim.x - 1 - blockIdx.x;           // heavy tiles first
     const uint32_t h = blockIdx.y, b = blockIdx.z, kvh = h / (Hq / Hkv);
-    const uint32_t n = qt + 1;                                // visible key tiles
+    const uint32_t n = 2 * (qt + 1);                          // visible 64-key tiles; the last two hold masked keys
     const int kv_unit = (int)(b * Hkv + kvh);
+    constexpr uint32_t kProducerWarp = kGroups * 4, kIssuerWarp = kGroups * 4 + 1;
 
     if (tid == 0) {
         mbar_init(&ctl->q_full, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kGroups; ++i) {
             mbar_init(&ctl->s_full[i], 1);
             mbar_init(&ctl->s_free[i], kConsumers);
             mbar_init(&ctl->p_ready[i], kConsumers);
@@ -252,7 +257,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == kIssuerWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)),
                      "r"((uint32_t)kTmemCols)
                      : "memory");
@@ -263,14 +268,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
 
-    if (warp == 8) {
+    if (warp == kProducerWarp) {
         // =============================== TMA producer ===============================
-        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) K(1) V(0) K(2) V(1) .. V(n-1)
+        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) K(1) K(2) V(0) K(3) V(1) .. V(n-1)
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-            mbar_expect_tx(&ctl->q_full, kStageBytes);
+            mbar_expect_tx(&ctl->q_full, kQBytes);
             tma_load_5d(smem_u32(q_tile), &map_q, 0, (int)(qt * kTile), 0, (int)h, (int)b, &ctl->q_full);
             uint32_t g = 0;
             bool ok = true;
@@ -279,20 +284,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const uint32_t st = g % kStages;
                 if (!mbar_wait(&ctl->empty[st], ((g / kStages) & 1u) ^ 1u, ctl, err)) { ok = false; return; }
                 mbar_expect_tx(&ctl->full[st], kStageBytes);
-                tma_load_4d(smem_u32(ring + st * kStageBytes), map, 0, (int)(kt * kTile), 0, kv_unit, &ctl->full[st]);
+                tma_load_4d(smem_u32(ring + st * kStageBytes), map, 0, (int)(kt * kKeys), 0, kv_unit, &ctl->full[st]);
                 ++g;
             };
             for (uint32_t kt = 0; kt < n; ++kt) issue(&map_k, kt);
-            issue(&map_k, 0);
+            for (uint32_t kt = 0; kt < n && kt < (uint32_t)kGroups - 1; ++kt) issue(&map_k, kt);
             for (uint32_t kt = 0; kt < n; ++kt) {
-                if (kt + 1 < n) issue(&map_k, kt + 1);
+                if (kt + kGroups - 1 < n) issue(&map_k, kt + kGroups - 1);
                 issue(&map_v, kt);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == kIssuerWarp) {
         // =============================== MMA issuer ===============================
         if (lane == 0) {
-            uint32_t g = 0, uses[2] = {0, 0};
+            uint32_t g = 0, uses[kGroups] = {0, 0, 0, 0};
             bool ok = mbar_wait(&ctl->q_full, 0, ctl, err);
             const uint32_t qa = smem_u32(q_tile);
             // S[buffer] = Q K^T with the K tile at the head of the ring
@@ -303,33 +308,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc_fence_after();
                 const uint32_t ka = smem_u32(ring + (g % kStages) * kStageBytes);
 #pragma unroll
-                for (uint32_t ks = 0; ks < 8; ++ks) {   // 16 d per MMA: d-half ks/4, 32 B steps inside the row
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3u) * 32;
-                    tc_mma_ss(tmem + buf * 128, desc_kmajor(qa + off), desc_kmajor(ka + off), kIdescQK, ks != 0 ? 1u : 0u);
-                }
+                for (uint32_t ks = 0; ks < 8; ++ks)      // 16 d per MMA: d-half ks/4, 32 B steps inside the row
+                    tc_mma_ss(tmem + buf * kKeys, desc_kmajor(qa + (ks >> 2) * (kQBytes / 2) + (ks & 3u) * 32),
+                              desc_kmajor(ka + (ks >> 2) * kKeyHalfBytes + (ks & 3u) * 32), kIdescQK, ks != 0 ? 1u : 0u);
                 tc_commit(&ctl->empty[g % kStages]);
                 tc_commit(&ctl->s_full[buf]);
                 ++g;
                 ++uses[buf];
             };
             // pass 1
-            for (uint32_t kt = 0; kt < n; ++kt) score_tile(kt & 1u);
-            // pass 2
-            score_tile(0);
+            for (uint32_t kt = 0; kt < n; ++kt) score_tile(kt % kGroups);
+            // pass 2: the scores run kGroups - 1 tiles ahead of the probabilities
+            for (uint32_t kt = 0; kt < n && kt < (uint32_t)kGroups - 1; ++kt) score_tile(kt % kGroups);
             for (uint32_t kt = 0; kt < n && ok; ++kt) {
-                const uint32_t buf = kt & 1u;
-                if (kt + 1 < n) score_tile(buf ^ 1u);
+                const uint32_t buf = kt % kGroups;
+                if (kt + kGroups - 1 < n) score_tile((kt + kGroups - 1) % kGroups);
                 if (!ok) break;
-                if (!mbar_wait(&ctl->p_ready[buf], (kt >> 1) & 1u, ctl, err)) { ok = false; break; }
+                if (!mbar_wait(&ctl->p_ready[buf], (kt / kGroups) & 1u, ctl, err)) { ok = false; break; }
                 if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t va = smem_u32(ring + (g % kStages) * kStageBytes);
 #pragma unroll
                 for (uint32_t part = 0; part < 2; ++part) {          // hi probabilities, then lo
-                    const uint32_t pa = part == 0 ? tmem + buf * 128 : tmem + kLoCol + buf * 64;
+                    const uint32_t pa = part == 0 ? tmem + buf * kKeys : tmem + kLoCol + buf * (kKeys / 2);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 8; ++kk)              // 16 keys per MMA = 8 TMEM columns of packed bf16
-                        tc_mma_ts(tmem + kOCol, pa + kk * 8, desc_mnmajor(va + kk * 2048, kHalfBytes), kIdescPV,
+                    for (uint32_t kk = 0; kk < (uint32_t)kKeys / 16; ++kk)   // 16 keys per MMA = 8 TMEM columns of packed bf16
+                        tc_mma_ts(tmem + kOCol, pa + kk * 8, desc_mnmajor(va + kk * 2048, kKeyHalfBytes), kIdescPV,
                                   (kt | part | kk) != 0 ? 1u : 0u);
                 }
                 tc_commit(&ctl->empty[g % kStages]);
@@ -346,55 +350,56 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool aborted = false;
         uint32_t uses = 0;                                           // score tiles of this group's buffer consumed
         // ---- pass 1: row maximum over this group's tiles (of the raw scores: scaling by a positive constant is
-        // monotonic, so max_i fl(s_i * scale) = fl((max_i s_i) * scale); only the diagonal tile has masked keys) ----
+        // monotonic, so max_i fl(s_i * scale) = fl((max_i s_i) * scale); only the last two tiles have masked keys) ----
         float m_raw = ninf;
-        for (uint32_t kt = wg; kt < n; kt += 2) {
+        for (uint32_t kt = wg; kt < n; kt += kGroups) {
             if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], uses & 1u, ctl, err))) {
                 aborted = true;
                 continue;
             }
             ++uses;
             tc_fence_after();
-            const bool diag = kt == qt;
+            const bool diag = kt + 2 >= n;
+            const uint32_t rel = (kt + 2 - n) * kKeys;               // first key of the tile relative to the query tile (diag only)
             uint32_t va[32], vb[32];
-            tmem_ld32(lane_addr + buf * 128, va);
+            tmem_ld32(lane_addr + buf * kKeys, va);
+            tmem_ld32(lane_addr + buf * kKeys + 32, vb);
             tmem_ld_wait();
+            if (diag) {
 #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {                       // the next 32 columns are in flight while these are scanned
-                uint32_t (&cur)[32] = (c & 1u) ? vb : va;
-                uint32_t (&nxt)[32] = (c & 1u) ? va : vb;
-                if (c < 3) tmem_ld32(lane_addr + buf * 128 + (c + 1) * 32, nxt);
-                if (diag) {
-#pragma unroll
-                    for (uint32_t e = 0; e < 32; ++e)
-                        if (c * 32 + e <= r) m_raw = fmaxf(m_raw, __uint_as_float(cur[e]));
-                } else {
-#pragma unroll
-                    for (uint32_t e = 0; e < 32; ++e) m_raw = fmaxf(m_raw, __uint_as_float(cur[e]));
+                for (uint32_t e = 0; e < 32; ++e) {
+                    if (rel + e <= r) m_raw = fmaxf(m_raw, __uint_as_float(va[e]));
+                    if (rel + 32 + e <= r) m_raw = fmaxf(m_raw, __uint_as_float(vb[e]));
                 }
-                if (c < 3) tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (uint32_t e = 0; e < 32; ++e) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(va[e]), __uint_as_float(vb[e])));
             }
             tc_fence_before();
             mbar_arrive(&ctl->s_free[buf]);
         }
         ctl->xch[wg][r] = m_raw;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        const float m = cmath::mul(fmaxf(ctl->xch[0][r], ctl->xch[1][r]), scale);
-        asm volatile("bar.sync 1, 256;" ::: "memory");               // both halves read before xch is reused for the sums
+        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * kConsumers) : "memory");
+        float m = ctl->xch[0][r];
+#pragma unroll
+        for (int gI = 1; gI < kGroups; ++gI) m = fmaxf(m, ctl->xch[gI][r]);
+        m = cmath::mul(m, scale);
+        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * kConsumers) : "memory");   // all parts read before xch is reused for the sums
         // ---- pass 2: probabilities into TMEM, row sum ----
         float l = 0.0f;
-        for (uint32_t kt = wg; kt < n; kt += 2) {
+        for (uint32_t kt = wg; kt < n; kt += kGroups) {
             if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], uses & 1u, ctl, err))) {
                 aborted = true;
                 continue;
             }
             ++uses;
             tc_fence_after();
-            // one chunk of 32 keys, ascending; MASKED only on the diagonal tile (keys past the query's own position)
+            const uint32_t rel = (kt + 2 - n) * kKeys;               // meaningful on the last two tiles only
+            // one chunk of 32 keys, ascending; MASKED only on the last two tiles (keys past the query's own position)
             auto chunk = [&](uint32_t c, auto masked_tag) {
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 uint32_t v[32], hi[16], lo[16];
-                tmem_ld32(lane_addr + buf * 128 + c * 32, v);
+                tmem_ld32(lane_addr + buf * kKeys + c * 32, v);
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t e = 0; e < 32; e += kExpW) {           // kExpW keys side by side
@@ -402,27 +407,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) { // masked keys: argument 0, result discarded
                         xs[u] = cmath::sub(cmath::mul(__uint_as_float(v[e + u]), scale), m);
-                        if (MASKED && c * 32 + e + u > r) xs[u] = 0.0f;
+                        if (MASKED && rel + c * 32 + e + u > r) xs[u] = 0.0f;
                     }
                     exp_approx_nonpos_n(xs, ps);
 #pragma unroll
                     for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) {
-                        if (MASKED && c * 32 + e + u > r) ps[u] = 0.0f;
+                        if (MASKED && rel + c * 32 + e + u > r) ps[u] = 0.0f;
                         l = cmath::add(l, ps[u]);                    // ascending key order
                     }
 #pragma unroll
                     for (uint32_t u = 0; u < (uint32_t)kExpW; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
                 }
                 // hi parts overwrite columns 16c .. 16c+15 of the score buffer (all of them already read), lo parts go beside
-                tmem_st16(lane_addr + buf * 128 + c * 16, hi);
-                tmem_st16(lane_addr + kLoCol + buf * 64 + c * 16, lo);
+                tmem_st16(lane_addr + buf * kKeys + c * 16, hi);
+                tmem_st16(lane_addr + kLoCol + buf * (kKeys / 2) + c * 16, lo);
             };
-            if (kt == qt) {
+            if (kt + 2 >= n) {
 #pragma unroll 1
-                for (uint32_t c = 0; c < 4; ++c) chunk(c, std::true_type{});
+                for (uint32_t c = 0; c < (uint32_t)kKeys / 32; ++c) chunk(c, std::true_type{});
             } else {
 #pragma unroll 1
-                for (uint32_t c = 0; c < 4; ++c) chunk(c, std::false_type{});
+                for (uint32_t c = 0; c < (uint32_t)kKeys / 32; ++c) chunk(c, std::false_type{});
             }
             tmem_st_wait();
             tc_fence_before();
@@ -430,35 +435,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(&ctl->s_free[buf]);
         }
         ctl->xch[wg][r] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        l = cmath::add(ctl->xch[0][r], ctl->xch[1][r]);
-        // ---- outputs: O / l, group g takes d columns 64 g .. 64 g + 63 ----
+        asm volatile("bar.sync 1, %0;" ::"n"(kGroups * kConsumers) : "memory");
+        l = ctl->xch[0][r];
+#pragma unroll
+        for (int gI = 1; gI < kGroups; ++gI) l = cmath::add(l, ctl->xch[gI][r]);
+        // ---- outputs: O / l, group g takes d columns 32 g .. 32 g + 31 ----
         if (!aborted && __all_sync(0xFFFFFFFFu, mbar_wait(&ctl->o_full, 0, ctl, err))) {
             tc_fence_after();
             __nv_bfloat16* orow = out + (((size_t)b * S + row) * Hq + h) * kD;
-#pragma unroll 1
-            for (uint32_t c = 2 * wg; c < 2 * wg + 2; ++c) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + kOCol + c * 32, v);
-                tmem_ld_wait();
-                if (row < S && !ctl->abort_flag) {
-                    uint32_t pk[16];
+            const uint32_t c = wg;
+            uint32_t v[32];
+            tmem_ld32(lane_addr + kOCol + c * 32, v);
+            tmem_ld_wait();
+            if (row < S && !ctl->abort_flag) {
+                uint32_t pk[16];
 #pragma unroll
-                    for (uint32_t e = 0; e < 32; e += 2) {
-                        const __nv_bfloat162 hv = __floats2bfloat162_rn(cmath::div(__uint_as_float(v[e]), l), cmath::div(__uint_as_float(v[e + 1]), l));
-                        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
-                    }
-#pragma unroll
-                    for (uint32_t qd = 0; qd < 4; ++qd)
-                        reinterpret_cast<uint4*>(orow + c * 32)[qd] = make_uint4(pk[4 * qd], pk[4 * qd + 1], pk[4 * qd + 2], pk[4 * qd + 3]);
+                for (uint32_t e = 0; e < 32; e += 2) {
+                    const __nv_bfloat162 hv = __floats2bfloat162_rn(cmath::div(__uint_as_float(v[e]), l), cmath::div(__uint_as_float(v[e + 1]), l));
+                    pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
                 }
+#pragma unroll
+                for (uint32_t qd = 0; qd < 4; ++qd)
+                    reinterpret_cast<uint4*>(orow + c * 32)[qd] = make_uint4(pk[4 * qd], pk[4 * qd + 1], pk[4 * qd + 2], pk[4 * qd + 3]);
             }
         }
     }
     __syncwarp();
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kIssuerWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
     }
@@ -529,14 +534,14 @@ catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, cons
         // cache as (64 d, seq visible rows, 2 d-halves, batch * hkv units owning `cap` rows each)
         cuuint64_t dims[4] = {64, seq, 2, batch * hkv};
         cuuint64_t strides[3] = {256, 128, cap * 256};
-        cuuint32_t box[4] = {64, (cuuint32_t)attn3::kTile, 2, 1};
+        cuuint32_t box[4] = {64, (cuuint32_t)attn3::kKeys, 2, 1};
         cuuint32_t estr[4] = {1, 1, 1, 1};
         CUresult r = fn(which ? &map_v : &map_k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_cache : k_cache), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled (kv cache) failed");
     }
-    const size_t smem = 1024 + (size_t)(1 + attn3::kStages) * attn3::kStageBytes + sizeof(attn3::Control) + 16;
+    const size_t smem = 1024 + (size_t)attn3::kQBytes + (size_t)attn3::kStages * attn3::kStageBytes + sizeof(attn3::Control) + 16;
     static thread_local bool attr_done[16] = {false};
     if (!attr_done[dev]) {
         CATENA_CUDA(cudaFuncSetAttribute(attn3::attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
