@@ -10,15 +10,16 @@
 // need no cross-thread reduction.  exp~ admits no online rescaling, hence two passes over the key tiles: pass 1
 // multiplies Q K^T for the row maxima only, pass 2 multiplies again and accumulates P V.  A kernel that allocates TMEM
 // gets one CTA per SM, and the polynomial is the bulk of the instructions, so the CTA carries FOUR consumer warpgroups:
-// key tiles are 64 wide, group g takes the tiles kt = g, g+4, ... (score buffer g); the four parts of a row's maximum
-// and of its sum meet in shared memory (sum = ((part 0 + part 1) + part 2) + part 3, a fixed order).
+// key tiles are 64 wide, group g takes the tiles kt = g, g+4, ...; the four parts of a row's maximum and of its sum meet
+// in shared memory (sum = ((part 0 + part 1) + part 2) + part 3, a fixed order).
 //   warps 4g .. 4g+3  consumer group g (warp w reads TMEM lanes 32 (w % 4) ..)
 //   warp 16    TMA producer (Q once, then K tiles / K and V tiles through a 10-stage ring of 16 KiB)
-//   warp 17    MMA issuer; allocates the CTA's 512 TMEM columns:
-//              S buffer b at [64 b, 64 b + 64); its hi probabilities overwrite its first 32 columns in place (a chunk's
-//              packed result lands behind the columns already read); lo probabilities of buffer b at [256 + 32 b, ..);
-//              outputs at [384, 512)
-// Score tiles run three ahead of the probabilities.  All waits are bounded.
+//   warp 17    MMA issuer; allocates the CTA's 512 TMEM columns: six score buffers of 64 columns, used round robin by
+//              the sequence of score tiles (both passes), and the outputs at [384, 512).  The probabilities of 16 keys
+//              replace their 16 score columns in place: 8 columns of packed bf16 hi parts, then 8 of lo parts, each an
+//              A operand of one K = 16 MMA.
+// Score tiles run five ahead of the probabilities, so a group finds its next tile multiplied when it finishes one.
+// All waits are bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -34,7 +35,8 @@ namespace attn3 {
 constexpr int kD = 128;
 constexpr int kTile = 128;                   // queries per CTA
 constexpr int kKeys = 64;                    // keys per ring stage / score buffer
-constexpr int kGroups = 4;                   // consumer warpgroups = score buffers
+constexpr int kGroups = 4;                   // consumer warpgroups
+constexpr int kBufs = 6;                     // score buffers
 constexpr int kStages = 10;
 constexpr int kQBytes = 2 * kTile * 128;     // [d-half 2][row 128][128 B]
 constexpr int kKeyHalfBytes = kKeys * 128;   // 8 KiB: 64 keys x 64 d
@@ -42,16 +44,15 @@ constexpr int kStageBytes = 2 * kKeyHalfBytes;
 constexpr int kConsumers = 128;              // per group
 constexpr int kThreads = kGroups * kConsumers + 64;
 constexpr int kTmemCols = 512;
-constexpr int kLoCol = 256;                  // lo probabilities of buffer b at kLoCol + 32 b
-constexpr int kOCol = 384;
+constexpr int kOCol = kBufs * kKeys;         // 384
 constexpr uint64_t kWaitNs = 1000000000ull;
 constexpr uint32_t kSuspendHintNs = 20000;
 
 struct __align__(16) Control {
     uint64_t q_full;
     uint64_t full[kStages], empty[kStages];
-    uint64_t s_full[kGroups], s_free[kGroups];   // score buffers
-    uint64_t p_ready[kGroups];       // probabilities of the buffer written to TMEM
+    uint64_t s_full[kBufs], s_free[kBufs];   // score buffers
+    uint64_t p_ready[kBufs];         // probabilities of the buffer written to TMEM
     uint64_t o_full;
     float xch[kGroups][kTile];       // per-row partial maxima / sums of the consumer groups
     uint32_t tmem_base;
@@ -154,6 +155,20 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -248,7 +263,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (tid == 0) {
         mbar_init(&ctl->q_full, 1);
         for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
-        for (int i = 0; i < kGroups; ++i) {
+        for (int i = 0; i < kBufs; ++i) {
             mbar_init(&ctl->s_full[i], 1);
             mbar_init(&ctl->s_free[i], kConsumers);
             mbar_init(&ctl->p_ready[i], kConsumers);
@@ -270,7 +285,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (warp == kProducerWarp) {
         // =============================== TMA producer ===============================
-        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) K(1) K(2) V(0) K(3) V(1) .. V(n-1)
+        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) .. K(4) V(0) K(5) V(1) .. V(n-1)
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
@@ -288,76 +303,75 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ++g;
             };
             for (uint32_t kt = 0; kt < n; ++kt) issue(&map_k, kt);
-            for (uint32_t kt = 0; kt < n && kt < (uint32_t)kGroups - 1; ++kt) issue(&map_k, kt);
+            for (uint32_t kt = 0; kt < n && kt < (uint32_t)kBufs - 1; ++kt) issue(&map_k, kt);
             for (uint32_t kt = 0; kt < n; ++kt) {
-                if (kt + kGroups - 1 < n) issue(&map_k, kt + kGroups - 1);
+                if (kt + kBufs - 1 < n) issue(&map_k, kt + kBufs - 1);
                 issue(&map_v, kt);
             }
         }
     } else if (warp == kIssuerWarp) {
         // =============================== MMA issuer ===============================
         if (lane == 0) {
-            uint32_t g = 0, uses[kGroups] = {0, 0, 0, 0};
+            uint32_t g = 0, j = 0, jbuf = 0, jround = 0;     // ring position; score tile sequence number, j % kBufs, j / kBufs
             bool ok = mbar_wait(&ctl->q_full, 0, ctl, err);
             const uint32_t qa = smem_u32(q_tile);
-            // S[buffer] = Q K^T with the K tile at the head of the ring
-            auto score_tile = [&](uint32_t buf) {
+            // S[buffer j % kBufs] = Q K^T with the K tile at the head of the ring
+            auto score_tile = [&]() {
                 if (!ok) return;
-                if (!mbar_wait(&ctl->s_free[buf], (uses[buf] & 1u) ^ 1u, ctl, err)) { ok = false; return; }
+                if (!mbar_wait(&ctl->s_free[jbuf], (jround & 1u) ^ 1u, ctl, err)) { ok = false; return; }
                 if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; return; }
                 tc_fence_after();
                 const uint32_t ka = smem_u32(ring + (g % kStages) * kStageBytes);
 #pragma unroll
                 for (uint32_t ks = 0; ks < 8; ++ks)      // 16 d per MMA: d-half ks/4, 32 B steps inside the row
-                    tc_mma_ss(tmem + buf * kKeys, desc_kmajor(qa + (ks >> 2) * (kQBytes / 2) + (ks & 3u) * 32),
+                    tc_mma_ss(tmem + jbuf * kKeys, desc_kmajor(qa + (ks >> 2) * (kQBytes / 2) + (ks & 3u) * 32),
                               desc_kmajor(ka + (ks >> 2) * kKeyHalfBytes + (ks & 3u) * 32), kIdescQK, ks != 0 ? 1u : 0u);
                 tc_commit(&ctl->empty[g % kStages]);
-                tc_commit(&ctl->s_full[buf]);
+                tc_commit(&ctl->s_full[jbuf]);
                 ++g;
-                ++uses[buf];
+                ++j;
+                if (++jbuf == (uint32_t)kBufs) { jbuf = 0; ++jround; }
             };
             // pass 1
-            for (uint32_t kt = 0; kt < n; ++kt) score_tile(kt % kGroups);
-            // pass 2: the scores run kGroups - 1 tiles ahead of the probabilities
-            for (uint32_t kt = 0; kt < n && kt < (uint32_t)kGroups - 1; ++kt) score_tile(kt % kGroups);
+            for (uint32_t kt = 0; kt < n; ++kt) score_tile();
+            // pass 2: the scores run kBufs - 1 tiles ahead of the probabilities; tile kt sits in buffer (n + kt) % kBufs
+            for (uint32_t kt = 0; kt < n && kt < (uint32_t)kBufs - 1; ++kt) score_tile();
+            uint32_t pbuf = n % kBufs;
             for (uint32_t kt = 0; kt < n && ok; ++kt) {
-                const uint32_t buf = kt % kGroups;
-                if (kt + kGroups - 1 < n) score_tile((kt + kGroups - 1) % kGroups);
+                if (kt + kBufs - 1 < n) score_tile();
                 if (!ok) break;
-                if (!mbar_wait(&ctl->p_ready[buf], (kt / kGroups) & 1u, ctl, err)) { ok = false; break; }
+                if (!mbar_wait(&ctl->p_ready[pbuf], (kt / kBufs) & 1u, ctl, err)) { ok = false; break; }
                 if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t va = smem_u32(ring + (g % kStages) * kStageBytes);
 #pragma unroll
-                for (uint32_t part = 0; part < 2; ++part) {          // hi probabilities, then lo
-                    const uint32_t pa = part == 0 ? tmem + buf * kKeys : tmem + kLoCol + buf * (kKeys / 2);
-#pragma unroll
-                    for (uint32_t kk = 0; kk < (uint32_t)kKeys / 16; ++kk)   // 16 keys per MMA = 8 TMEM columns of packed bf16
-                        tc_mma_ts(tmem + kOCol, pa + kk * 8, desc_mnmajor(va + kk * 2048, kKeyHalfBytes), kIdescPV,
-                                  (kt | part | kk) != 0 ? 1u : 0u);
+                for (uint32_t kk = 0; kk < (uint32_t)kKeys / 16; ++kk) {     // 16 keys: hi parts in 8 columns, lo parts in the next 8
+                    const uint64_t vdesc = desc_mnmajor(va + kk * 2048, kKeyHalfBytes);
+                    tc_mma_ts(tmem + kOCol, tmem + pbuf * kKeys + kk * 16, vdesc, kIdescPV, (kt | kk) != 0 ? 1u : 0u);
+                    tc_mma_ts(tmem + kOCol, tmem + pbuf * kKeys + kk * 16 + 8, vdesc, kIdescPV, 1u);
                 }
                 tc_commit(&ctl->empty[g % kStages]);
                 ++g;
+                if (++pbuf == (uint32_t)kBufs) pbuf = 0;
             }
             if (ok) tc_commit(&ctl->o_full);
         }
     } else {
         // =============================== consumers: group wg, thread r = query row r ===============================
-        const uint32_t wg = warp >> 2, r = tid & 127u, buf = wg;
+        const uint32_t wg = warp >> 2, r = tid & 127u;
         const uint32_t row = qt * kTile + r;                         // position of this query in its sequence
         const uint32_t lane_addr = tmem + (((warp & 3u) * 32u) << 16);
         const float ninf = __uint_as_float(0xFF800000u);
         bool aborted = false;
-        uint32_t uses = 0;                                           // score tiles of this group's buffer consumed
         // ---- pass 1: row maximum over this group's tiles (of the raw scores: scaling by a positive constant is
         // monotonic, so max_i fl(s_i * scale) = fl((max_i s_i) * scale); only the last two tiles have masked keys) ----
         float m_raw = ninf;
         for (uint32_t kt = wg; kt < n; kt += kGroups) {
-            if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], uses & 1u, ctl, err))) {
+            const uint32_t buf = kt % kBufs, par = (kt / kBufs) & 1u;    // score tile number kt
+            if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], par, ctl, err))) {
                 aborted = true;
                 continue;
             }
-            ++uses;
             tc_fence_after();
             const bool diag = kt + 2 >= n;
             const uint32_t rel = (kt + 2 - n) * kKeys;               // first key of the tile relative to the query tile (diag only)
@@ -388,47 +402,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ---- pass 2: probabilities into TMEM, row sum ----
         float l = 0.0f;
         for (uint32_t kt = wg; kt < n; kt += kGroups) {
-            if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], uses & 1u, ctl, err))) {
+            const uint32_t buf = (n + kt) % kBufs, par = ((n + kt) / kBufs) & 1u;   // score tile number n + kt
+            if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], par, ctl, err))) {
                 aborted = true;
                 continue;
             }
-            ++uses;
             tc_fence_after();
             const uint32_t rel = (kt + 2 - n) * kKeys;               // meaningful on the last two tiles only
-            // one chunk of 32 keys, ascending; MASKED only on the last two tiles (keys past the query's own position)
-            auto chunk = [&](uint32_t c, auto masked_tag) {
+            const uint32_t base = lane_addr + buf * kKeys;
+            // 16 keys per trip, ascending; the next 16 scores are in flight meanwhile.  MASKED only on the last two tiles
+            // (keys past the query's own position).  The loop stays rolled: four groups at four places of an unrolled
+            // body do not fit the instruction cache.
+            auto tile = [&](auto masked_tag) {
                 constexpr bool MASKED = decltype(masked_tag)::value;
-                uint32_t v[32], hi[16], lo[16];
-                tmem_ld32(lane_addr + buf * kKeys + c * 32, v);
-                tmem_ld_wait();
+                uint32_t v[16];
+                tmem_ld16(base, v);
+#pragma unroll 1
+                for (uint32_t c = 0; c < (uint32_t)kKeys / 16; ++c) {
+                    float sc[16];
+                    uint32_t hi[8], lo[8];
+                    tmem_ld_wait();
 #pragma unroll
-                for (uint32_t e = 0; e < 32; e += kExpW) {           // kExpW keys side by side
-                    float xs[kExpW], ps[kExpW];
+                    for (uint32_t e = 0; e < 16; ++e) sc[e] = __uint_as_float(v[e]);
+                    if (c + 1 < (uint32_t)kKeys / 16) tmem_ld16(base + (c + 1) * 16, v);
 #pragma unroll
-                    for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) { // masked keys: argument 0, result discarded
-                        xs[u] = cmath::sub(cmath::mul(__uint_as_float(v[e + u]), scale), m);
-                        if (MASKED && rel + c * 32 + e + u > r) xs[u] = 0.0f;
+                    for (uint32_t e = 0; e < 16; e += kExpW) {       // kExpW keys side by side
+                        float xs[kExpW], ps[kExpW];
+#pragma unroll
+                        for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) { // masked keys: argument 0, result discarded
+                            xs[u] = cmath::sub(cmath::mul(sc[e + u], scale), m);
+                            if (MASKED && rel + c * 16 + e + u > r) xs[u] = 0.0f;
+                        }
+                        exp_approx_nonpos_n(xs, ps);
+#pragma unroll
+                        for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) {
+                            if (MASKED && rel + c * 16 + e + u > r) ps[u] = 0.0f;
+                            l = cmath::add(l, ps[u]);                // ascending key order
+                        }
+#pragma unroll
+                        for (uint32_t u = 0; u < (uint32_t)kExpW; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
                     }
-                    exp_approx_nonpos_n(xs, ps);
-#pragma unroll
-                    for (uint32_t u = 0; u < (uint32_t)kExpW; ++u) {
-                        if (MASKED && rel + c * 32 + e + u > r) ps[u] = 0.0f;
-                        l = cmath::add(l, ps[u]);                    // ascending key order
-                    }
-#pragma unroll
-                    for (uint32_t u = 0; u < (uint32_t)kExpW; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
+                    // in place: the 16 score columns just read become 8 columns of hi parts and 8 of lo parts
+                    tmem_st8(base + c * 16, hi);
+                    tmem_st8(base + c * 16 + 8, lo);
                 }
-                // hi parts overwrite columns 16c .. 16c+15 of the score buffer (all of them already read), lo parts go beside
-                tmem_st16(lane_addr + buf * kKeys + c * 16, hi);
-                tmem_st16(lane_addr + kLoCol + buf * (kKeys / 2) + c * 16, lo);
             };
-            if (kt + 2 >= n) {
-#pragma unroll 1
-                for (uint32_t c = 0; c < (uint32_t)kKeys / 32; ++c) chunk(c, std::true_type{});
-            } else {
-#pragma unroll 1
-                for (uint32_t c = 0; c < (uint32_t)kKeys / 32; ++c) chunk(c, std::false_type{});
-            }
+            if (kt + 2 >= n) tile(std::true_type{});
+            else tile(std::false_type{});
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&ctl->p_ready[buf]);
