@@ -32,7 +32,12 @@ namespace tc2 {
 constexpr int BM = 128;            // rows per CTA (pair tile: 256)
 constexpr int BN = 256;            // pair-tile columns = TMEM columns per accumulator
 constexpr int BK_BYTES = 128;
-constexpr int STAGES = 6;
+#ifndef CATENA_GEMM_STAGES
+#define CATENA_GEMM_STAGES 7
+#endif
+constexpr int MAX_STAGES = 7;
+// ring depth: the plain kernel fills shared memory with stages; the gather-fused one keeps 16 KiB for its transposes
+constexpr int stages_for(bool has_peers) { return has_peers ? 6 : CATENA_GEMM_STAGES; }
 constexpr int A_BYTES = BM * BK_BYTES;              // 16 KiB
 constexpr int B_BYTES = (BN / 2) * BK_BYTES;        // 16 KiB: this CTA's half of N
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;      // 32 KiB
@@ -54,15 +59,18 @@ struct PeerOut {
 };
 
 struct __align__(8) Control {
-    uint64_t full[STAGES];       // used in the leader CTA
-    uint64_t empty[STAGES];      // one per CTA, signalled by the leader's commit (multicast)
+    uint64_t full[MAX_STAGES];       // used in the leader CTA
+    uint64_t empty[MAX_STAGES];      // one per CTA, signalled by the leader's commit (multicast)
     uint64_t tmem_full[2];       // one per CTA, signalled by the leader's commit (multicast)
     uint64_t tmem_empty[2];      // used in the leader CTA: 2 x 128 epilogue threads arrive
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
 constexpr int PEER_STAGE_BYTES = 32 * 128;           // per epilogue warp: 32 rows x 32 int32 (or bf16) columns, for peer stores
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + (int)((sizeof(Control) + 15) / 16 * 16) + 4 * PEER_STAGE_BYTES;
+constexpr int smem_bytes(bool has_peers) {
+    return stages_for(has_peers) * STAGE_BYTES + 1024 + (int)((sizeof(Control) + 15) / 16 * 16) + (has_peers ? 4 * PEER_STAGE_BYTES : 0);
+}
+static_assert(smem_bytes(false) <= 232448 && smem_bytes(true) <= 232448, "shared memory per CTA");
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
@@ -218,6 +226,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 void* __restrict__ c_out, PeerOut peers, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int STAGES = HAS_PEERS ? 6 : CATENA_GEMM_STAGES;
     Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
     uint8_t* peer_stage = smem + STAGES * STAGE_BYTES + (sizeof(Control) + 15) / 16 * 16;
 
@@ -231,7 +240,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tiles = mb * nb;
     const uint32_t kblocks = (K + K_ELEMS - 1) / K_ELEMS;
 
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled as soon as every CTA of this grid
+    // has got here, so its launch latency and set-up run under this grid's tail; this grid in turn does its own set-up
+    // (barriers, TMEM, tensor maps) and then waits below for everything launched before it to complete.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b128)) : "memory");
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
@@ -256,12 +271,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    asm volatile("griddepcontrol.wait;" ::: "memory");     // no global memory is read or written above this line
 
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- TMA producer (both CTAs) ----------------
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b128)) : "memory");
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             Work w;
@@ -498,7 +512,8 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
                              uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*);
     KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, true> : tc2::gemm_tc2_kernel<true, false>)
                             : (n_peers ? tc2::gemm_tc2_kernel<false, true> : tc2::gemm_tc2_kernel<false, false>);
-    CATENA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc2::SMEM_BYTES));
+    const int smem_bytes = tc2::smem_bytes(n_peers != 0);
+    CATENA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     const uint64_t tiles = ceil_div_u64(m, 2 * tc2::BM) * ceil_div_u64(n, tc2::BN);
     const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
     uint64_t pairs = (uint64_t)(sms / 2);
@@ -508,10 +523,20 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     const uint32_t split = rem == 0 ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
     const unsigned grid = (unsigned)(pairs * 2);
     cudaStream_t st = tls().stream;
-    kernel<<<grid, tc2::NUM_THREADS, tc2::SMEM_BYTES, st>>>(map_a, map_b128, map_b64, map_b32, c, peers, (uint32_t)m, (uint32_t)n, (uint32_t)k,
-                                                           ldc, split, err_dev);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(tc2::NUM_THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool pdl = [] { const char* v = getenv("CATENA_B200_GEMM_PDL"); return !(v && v[0] == '0'); }();
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b128, map_b64, map_b32, c, peers, (uint32_t)m, (uint32_t)n, (uint32_t)k, ldc,
+                                       split, err_dev);
     count_launch();
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "gemm_tc2 launch");
     return CATENA_OK;
 }
