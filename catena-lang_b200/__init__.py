@@ -141,6 +141,7 @@ def lib():
     proto("catena_b200_debug_set_attn_tc", None, [C.c_int])
     proto("catena_b200_debug_attn_last_launch", None, [C.POINTER(C.c_uint32)])
     proto("catena_b200_debug_set_prefill_tc", None, [C.c_int])
+    proto("catena_b200_debug_rcp_check", C.c_int, [C.POINTER(C.c_uint64)])
     _lib = L
     return L
 

@@ -203,6 +203,24 @@ __device__ __forceinline__ float exp_approx_nonpos(float x) {
     p = cmath::mul(p, cmath::from_bits((k + 0x7Fu) * 0x00800000u));
     return x < 0.0f ? cmath::recip(p) : p;
 }
+// Correctly rounded 1 / p for 0.5 <= p < 2^100 without the range checks and the call of the general routine: the
+// hardware approximation, one Newton step, then one more whose residual is taken against the refined value
+// (Markstein's final correction).  catena_b200_debug_rcp_check compares it with __frcp_rn over every float of that
+// range; the caller takes the general routine when any argument of a batch is outside it.
+constexpr float kRcpFastBelow = 1.2676506e30f;   // 2^100
+__device__ __forceinline__ float rcp_fast(float p) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(p));
+    float e = __fmaf_rn(-p, r, 1.0f);
+    r = __fmaf_rn(r, e, r);
+    e = __fmaf_rn(-p, r, 1.0f);
+    return __fmaf_rn(r, e, r);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // The same function for kExpW (8) arguments, written stage by stage across them: that many independent dependency chains are in
 // flight, so an instruction rarely waits for the result of the one before it (two warps share a scheduler here).
 // Arguments of masked keys must still be <= 0 (the caller passes 0 and discards the result).
@@ -230,8 +248,18 @@ __device__ __forceinline__ void exp_approx_nonpos_n(const float (&x)[kExpW], flo
     for (int u = 0; u < kExpW; ++u) p[u] = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr[u], p[u]));
 #pragma unroll
     for (int u = 0; u < kExpW; ++u) p[u] = cmath::mul(p[u], cmath::from_bits((__float_as_uint(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
+    // p >= 0.5 always (a polynomial near 1 times 2^k, k >= 0); NaNs pass the test and stay NaNs either way
+    float big = p[0];
 #pragma unroll
-    for (int u = 0; u < kExpW; ++u) out[u] = x[u] < 0.0f ? cmath::recip(p[u]) : p[u];
+    for (int u = 1; u + 1 < kExpW; u += 2) big = max3(big, p[u], p[u + 1]);
+    if (kExpW % 2 == 0) big = fmaxf(big, p[kExpW - 1]);
+    if (big < kRcpFastBelow) {
+#pragma unroll
+        for (int u = 0; u < kExpW; ++u) out[u] = x[u] < 0.0f ? rcp_fast(p[u]) : p[u];
+    } else {
+#pragma unroll
+        for (int u = 0; u < kExpW; ++u) out[u] = x[u] < 0.0f ? cmath::recip(p[u]) : p[u];
+    }
 }
 // two probabilities -> packed bf16 hi parts and packed bf16 lo parts (p - hi)
 __device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, uint32_t& lo) {
@@ -489,6 +517,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
+// every float in [0.5, 2^100): rcp_fast against __frcp_rn; counts[0] = values compared, counts[1] = mismatches
+__global__ void rcp_check_kernel(unsigned long long* counts) {
+    unsigned long long seen = 0, bad = 0;
+    const uint32_t lo = 0x3F000000u, hi = __float_as_uint(kRcpFastBelow);
+    for (uint64_t b = lo + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; b < hi; b += (uint64_t)gridDim.x * blockDim.x) {
+        const float p = __uint_as_float((uint32_t)b);
+        ++seen;
+        if (__float_as_uint(rcp_fast(p)) != __float_as_uint(__frcp_rn(p))) ++bad;
+    }
+    atomicAdd(&counts[0], seen);
+    atomicAdd(&counts[1], bad);
+}
 }  // namespace attn3
 
 typedef CUresult (*EncodeTiledFnA3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -574,6 +614,22 @@ catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, cons
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "attn_prefill_tc launch");
+    return CATENA_OK;
+}
+
+// runs rcp_check_kernel over the whole range and returns {values compared, mismatches}
+catena_status_t attn_prefill_rcp_check(uint64_t out[2]) {
+    unsigned long long* dev = nullptr;
+    CATENA_CUDA(cudaMalloc(&dev, 2 * sizeof(unsigned long long)));
+    CATENA_CUDA(cudaMemset(dev, 0, 2 * sizeof(unsigned long long)));
+    attn3::rcp_check_kernel<<<148 * 8, 256, 0, tls().stream>>>(dev);
+    unsigned long long h[2] = {0, 0};
+    cudaError_t e = cudaMemcpyAsync(h, dev, sizeof(h), cudaMemcpyDeviceToHost, tls().stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(tls().stream);
+    cudaFree(dev);
+    if (e != cudaSuccess) return fail_cuda(e, "rcp check");
+    out[0] = h[0];
+    out[1] = h[1];
     return CATENA_OK;
 }
 

@@ -62,6 +62,9 @@ catena_status_t launch_identity_matmul_f32(const float* a, float* c, uint64_t n,
 // gemm_tc.cu
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8);
+bool gemm_tc_fuses_residual(uint64_t m);
+catena_status_t launch_gemm_tc_residual(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                        const void* residual);
 catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                      int is_i8, void* const* peer_c, uint32_t n_peers);
 catena_status_t gemm_tc_check_errors();
@@ -70,6 +73,7 @@ void gemm_tc_set_pair_mode(int on);
 void attn_set_cluster_limit(int limit);
 void attn_set_tc_mode(int on);
 void attn_last_launch(uint32_t out[4]);
+catena_status_t attn_prefill_rcp_check(uint64_t out[2]);
 extern thread_local uint32_t g_attn_last_launch[4];
 // attn_decode.cu
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,

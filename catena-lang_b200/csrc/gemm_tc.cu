@@ -423,7 +423,7 @@ static bool gemm_pair_mode(uint64_t m) {
 }
 void gemm_tc_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers);
+                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual);
 
 struct ErrWord {
     uint32_t* dev = nullptr;
@@ -443,14 +443,28 @@ static catena_status_t err_word(ErrWord** out) {
     return CATENA_OK;
 }
 
+static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                          int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual);
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8) {
-    return launch_gemm_tc_peers(a, b, c, m, n, k, ldc, is_i8, nullptr, 0);
+    return launch_gemm_tc_any(a, b, c, m, n, k, ldc, is_i8, nullptr, 0, nullptr);
+}
+// true when launch_gemm_tc_residual can take this shape (the CTA-pair kernel does the sum in its epilogue)
+bool gemm_tc_fuses_residual(uint64_t m) { return gemm_pair_mode(m); }
+// bf16 C = round(round(A B^T) + residual): `residual` is bf16 [m, ldc] and may be C itself
+catena_status_t launch_gemm_tc_residual(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                        const void* residual) {
+    if (!residual || !gemm_pair_mode(m)) return fail(CATENA_E_UNSUPPORTED, "gemm: residual epilogue needs the CTA-pair kernel");
+    return launch_gemm_tc_any(a, b, c, m, n, k, ldc, 0, nullptr, 0, residual);
 }
 
 // The same GEMM whose epilogue also stores every output tile to `n_peers` peer-mapped copies of C (pair kernel only).
 catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                      int is_i8, void* const* peer_c, uint32_t n_peers) {
+    return launch_gemm_tc_any(a, b, c, m, n, k, ldc, is_i8, peer_c, n_peers, nullptr);
+}
+static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
+                                          int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual) {
     CATENA_TRY(ensure_device());
     if (m == 0 || n == 0) return CATENA_OK;
     if (!a || !b || !c) return fail(CATENA_E_BAD_ARG, "gemm: null operand");
@@ -467,7 +481,7 @@ catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint
     if (n_peers > 0 && !gemm_pair_mode(m))
         return fail(CATENA_E_UNSUPPORTED, "gemm: peer outputs need the CTA-pair kernel (more than 128 rows)");
     if (gemm_pair_mode(m)) {
-        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev, peer_c, n_peers));
+        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev, peer_c, n_peers, residual));
     } else {
         CUtensorMap map_a, map_b, map_b128, map_b64;
         CATENA_TRY(make_operand_map(&map_a, a, m, k, eb, tc::BM));

@@ -56,7 +56,12 @@ constexpr int kMaxPeers = 7;       // other GPUs of an 8-GPU box
 struct PeerOut {
     void* ptr[kMaxPeers];
     uint32_t n;
+    const void* residual;         // EPI_RESIDUAL: bf16 [M, ldc] added to the rounded product
 };
+// epilogue variants (separate instantiations: the plain kernel carries none of the others' code or registers)
+constexpr int EPI_PLAIN = 0;      // C = round(A B^T)
+constexpr int EPI_PEERS = 1;      // the same, also stored to peer-mapped copies of C (gather-fused)
+constexpr int EPI_RESIDUAL = 2;   // bf16 only: C = round(round(A B^T) + residual), the sum taken in fp32
 
 struct __align__(8) Control {
     uint64_t full[MAX_STAGES];       // used in the leader CTA
@@ -218,14 +223,14 @@ __device__ __forceinline__ bool get_work(uint32_t it, uint32_t pair, uint32_t pa
     return true;
 }
 
-// HAS_PEERS = the gather-fused variant (the plain one carries none of its code or registers)
-template <bool IS_I8, bool HAS_PEERS>
+template <bool IS_I8, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b128,
                 const __grid_constant__ CUtensorMap map_b64, const __grid_constant__ CUtensorMap map_b32,
                 void* __restrict__ c_out, PeerOut peers, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr bool HAS_PEERS = EPI == EPI_PEERS;
     constexpr int STAGES = HAS_PEERS ? 6 : CATENA_GEMM_STAGES;
     Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
     uint8_t* peer_stage = smem + STAGES * STAGE_BYTES + (sizeof(Control) + 15) / 16 * 16;
@@ -342,6 +347,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (uint32_t c = 0; c < w.width; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
+                uint4 res[4];
+                bool res_whole = false;
+                if (EPI == EPI_RESIDUAL && row < M) {          // in flight together with the accumulator load
+                    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(peers.residual) + (uint64_t)row * ldc + w.col0 + c;
+                    res_whole = w.col0 + c + 32 <= N && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+                    if (res_whole) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) res[q] = reinterpret_cast<const uint4*>(src)[q];
+                    }
+                }
                 tmem_ld_wait();
                 if (row < M) {
                     const uint32_t col = w.col0 + c;
@@ -358,6 +373,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * q + 2 * e]),
                                                                          __uint_as_float(v[8 * q + 2 * e + 1]));
                                 p[e] = *reinterpret_cast<uint32_t*>(&h);
+                                if (EPI == EPI_RESIDUAL && res_whole) {
+                                    const uint32_t rw = e == 0 ? res[q].x : (e == 1 ? res[q].y : (e == 2 ? res[q].z : res[q].w));
+                                    h = __floats2bfloat162_rn(__fadd_rn(__uint_as_float(p[e] << 16), __uint_as_float(rw << 16)),
+                                                              __fadd_rn(__uint_as_float(p[e] & 0xFFFF0000u), __uint_as_float(rw & 0xFFFF0000u)));
+                                    p[e] = *reinterpret_cast<uint32_t*>(&h);
+                                }
                             }
                             out[q] = make_uint4(p[0], p[1], p[2], p[3]);
                         }
@@ -378,8 +399,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                             for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = out[q];
                         } else {
-                            for (int q = 0; q < 32; ++q)
-                                if (col + q < N) dst[q] = __float2bfloat16_rn(__uint_as_float(v[q]));
+                            for (int q = 0; q < 32; ++q) {
+                                if (col + q >= N) break;
+                                __nv_bfloat16 o = __float2bfloat16_rn(__uint_as_float(v[q]));
+                                if (EPI == EPI_RESIDUAL) {
+                                    const __nv_bfloat16 r = (reinterpret_cast<const __nv_bfloat16*>(peers.residual) + (uint64_t)row * ldc + col)[q];
+                                    o = __float2bfloat16_rn(__fadd_rn(__bfloat162float(o), __bfloat162float(r)));
+                                }
+                                dst[q] = o;
+                            }
                         }
                     }
                 }
@@ -494,10 +522,12 @@ static catena_status_t make_map2(CUtensorMap* map, const void* base, uint64_t ro
 
 // Enqueues the CTA-pair GEMM.  `err_dev` is the device error word shared with the single-CTA kernel.
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers) {
+                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual) {
+    if (residual && (is_i8 || n_peers)) return fail(CATENA_E_BAD_ARG, "gemm: a residual goes with the plain bf16 kernel only");
     if (n_peers > (uint32_t)tc2::kMaxPeers) return fail(CATENA_E_BAD_ARG, "gemm: more than 7 peer outputs");
     tc2::PeerOut peers = {};
     peers.n = n_peers;
+    peers.residual = residual;
     for (uint32_t i = 0; i < n_peers; ++i) {
         if (!peer_c || !peer_c[i] || ((uintptr_t)peer_c[i] & 15)) return fail(CATENA_E_BAD_ARG, "gemm: null or unaligned peer output");
         peers.ptr[i] = peer_c[i];
@@ -510,8 +540,9 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     CATENA_TRY(make_map2(&map_b32, b, n, k, eb, 32));
     typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, void*, tc2::PeerOut, uint32_t,
                              uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*);
-    KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, true> : tc2::gemm_tc2_kernel<true, false>)
-                            : (n_peers ? tc2::gemm_tc2_kernel<false, true> : tc2::gemm_tc2_kernel<false, false>);
+    KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, tc2::EPI_PEERS> : tc2::gemm_tc2_kernel<true, tc2::EPI_PLAIN>)
+                            : (n_peers ? tc2::gemm_tc2_kernel<false, tc2::EPI_PEERS>
+                                       : (residual ? tc2::gemm_tc2_kernel<false, tc2::EPI_RESIDUAL> : tc2::gemm_tc2_kernel<false, tc2::EPI_PLAIN>));
     const int smem_bytes = tc2::smem_bytes(n_peers != 0);
     CATENA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     const uint64_t tiles = ceil_div_u64(m, 2 * tc2::BM) * ceil_div_u64(n, tc2::BN);

@@ -778,6 +778,8 @@ static catena_status_t launch_linear(const void* x, const void* w, const void* r
         return launch_pdl("skinny_gemm_kernel", llama::skinny_gemm_kernel, dim3(grid), dim3(256), 0, (const __nv_bfloat16*)x,
                           (const __nv_bfloat16*)w, (const __nv_bfloat16*)res, (__nv_bfloat16*)y, (uint32_t)m, (uint32_t)n, (uint32_t)k, 0u);
     }
+    // the CTA-pair kernel adds the residual in its epilogue (the same two roundings as the GEMM followed by the add)
+    if (res && gemm_tc_fuses_residual(m) && !(((uintptr_t)res | (uintptr_t)y) & 15)) return launch_gemm_tc_residual(x, w, y, m, n, k, n, res);
     CATENA_TRY(launch_gemm_tc(x, w, y, m, n, k, n, 0));
     if (res) CATENA_TRY(launch_add(y, res, y, m * n));
     return CATENA_OK;

@@ -286,6 +286,11 @@ void catena_b200_debug_set_cta_limit(int limit) {
 void catena_b200_debug_set_gemm_pair(int on) { gemm_tc_set_pair_mode(on); }
 void catena_b200_debug_set_attn_tc(int on) { attn_set_tc_mode(on); }
 void catena_b200_debug_attn_last_launch(uint32_t out[4]) { attn_last_launch(out); }
+catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]) {
+    if (!out) return fail(CATENA_E_BAD_ARG, "rcp check: null argument");
+    CATENA_TRY(ensure_device());
+    return attn_prefill_rcp_check(out);
+}
 
 catena_status_t catena_b200_check_device_errors(void) {
     CATENA_TRY(gemm_tc_check_errors());

@@ -286,6 +286,10 @@ void catena_b200_debug_set_prefill_tc(int on);
  * out[1] = clusters of 8 CTAs that can be resident at once, out[2] = clusters launched, out[3] = dynamic shared
  * memory per CTA in bytes.  No counterpart in the reference. */
 void catena_b200_debug_attn_last_launch(uint32_t out[4]);
+/* test hook: the prefill attention kernel takes reciprocals by a short correctly-rounded sequence for arguments in
+ * [0.5, 2^100); this compares that sequence with the IEEE reciprocal for EVERY float of the range on the device:
+ * out[0] = values compared, out[1] = mismatches (must be 0).  No counterpart in the reference. */
+catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]);
 /* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry */
 catena_status_t catena_b200_check_device_errors(void);
 

@@ -65,7 +65,7 @@ def test_embed_and_bad_id(orc):
         cb.free(m)
 
 
-@pytest.mark.parametrize("rows,hidden", [(3, 256), (5, 2048), (2, 4096 + 64)])
+@pytest.mark.parametrize("rows,hidden", [(3, 256), (5, 2048), (2, 4096 + 64), (200, 256), (1500, 2048)])
 def test_rmsnorm_rows(orc, rows, hidden):
     x = bits(np.random.default_rng(1), (rows, hidden), 3.0)
     xm, ym = dev(x), alloc(x.nbytes)
@@ -73,6 +73,14 @@ def test_rmsnorm_rows(orc, rows, hidden):
     # the sum of squares is a fixed tree here and a sequential fold in the oracle: the quotient moves by an ulp at most
     close(cb.download(ym, np.uint16), orc.rmsnorm_rows_bf16(x, threads=4), rel=2.0 ** -7, frac_exact=0.98)
     cb.free(xm), cb.free(ym)
+
+
+def test_prefill_reciprocal_sequence_is_the_ieee_reciprocal_for_every_float_of_its_range():
+    """The tcgen05 prefill kernel replaces __frcp_rn by a rcp.approx + two FMA steps for arguments in [0.5, 2^100);
+    the device compares the two for all ~8.6e8 floats of that range."""
+    out = (C.c_uint64 * 2)()
+    cb.check(cb.lib().catena_b200_debug_rcp_check(out))
+    assert out[0] == 0x71800000 - 0x3F000000 and out[1] == 0
 
 
 @pytest.mark.parametrize("B,S,hq,hkv", [(2, 5, 4, 2), (1, 3, 2, 1)])      # angles from a table / evaluated in place
@@ -191,6 +199,25 @@ def test_linear(orc, m, n, k, res):
     cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, rm.data if res else None, ym.data, m, n, k))
     assert np.array_equal(got, cb.download(ym, np.uint16))
     for mm in (xm, wm, ym) + ((rm,) if res else ()):
+        cb.free(mm)
+
+
+@pytest.mark.parametrize("m,n,k", [(300, 512, 256), (700, 1000, 512), (129, 40, 64)])
+def test_linear_residual_in_the_gemm_epilogue_equals_gemm_then_add(orc, m, n, k):
+    """More than 128 rows: the tcgen05 GEMM adds the residual in its epilogue.  Same two roundings as the product
+    followed by the add kernel, so the results are equal bit for bit; the output may be the residual buffer itself."""
+    rng = np.random.default_rng(8)
+    x, w, r = bits(rng, (m, k)), bits(rng, (n, k), 1.0 / math.sqrt(k)), bits(rng, (m, n))
+    xm, wm, rm, ym, y2 = dev(x), dev(w), dev(r), alloc(m * n * 2), alloc(m * n * 2)
+    cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, rm.data, ym.data, m, n, k))
+    cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, None, y2.data, m, n, k))
+    cb.check(cb.lib().catena_b200_add_bf16_into(y2.data, rm.data, y2.data, m * n))
+    got = cb.download(ym, np.uint16)
+    assert np.array_equal(got, cb.download(y2, np.uint16))
+    close(got, orc.linear_bf16(x, w, r, threads=orc.max_threads()), rel=2.0 ** -7, floor=3e-2, frac_exact=0.9)
+    cb.check(cb.lib().catena_b200_linear_bf16_into(xm.data, wm.data, rm.data, rm.data, m, n, k))   # in place
+    assert np.array_equal(got, cb.download(rm, np.uint16))
+    for mm in (xm, wm, rm, ym, y2):
         cb.free(mm)
 
 
