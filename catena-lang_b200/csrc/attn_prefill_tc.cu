@@ -203,24 +203,9 @@ __device__ __forceinline__ float exp_approx_nonpos(float x) {
     p = cmath::mul(p, cmath::from_bits((k + 0x7Fu) * 0x00800000u));
     return x < 0.0f ? cmath::recip(p) : p;
 }
-// Correctly rounded 1 / p for 0.5 <= p < 2^100 without the range checks and the call of the general routine: the
-// hardware approximation, one Newton step, then one more whose residual is taken against the refined value
-// (Markstein's final correction).  catena_b200_debug_rcp_check compares it with __frcp_rn over every float of that
-// range; the caller takes the general routine when any argument of a batch is outside it.
-constexpr float kRcpFastBelow = 1.2676506e30f;   // 2^100
-__device__ __forceinline__ float rcp_fast(float p) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(p));
-    float e = __fmaf_rn(-p, r, 1.0f);
-    r = __fmaf_rn(r, e, r);
-    e = __fmaf_rn(-p, r, 1.0f);
-    return __fmaf_rn(r, e, r);
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
+using cmath::kRcpFastBelow;
+using cmath::max3;
+using cmath::rcp_fast;
 // The same function for kExpW (8) arguments, written stage by stage across them: that many independent dependency chains are in
 // flight, so an instruction rarely waits for the result of the one before it (two warps share a scheduler here).
 // Arguments of masked keys must still be <= 0 (the caller passes 0 and discards the result).

@@ -173,6 +173,11 @@ def test_attn_decode_with_capacity(orc, B, hq, hkv, L, cap):
 def test_swiglu_and_add(orc):
     rng = np.random.default_rng(5)
     gu = bits(rng, (7, 2 * 264), 2.0)
+    # gates beyond +-64 leave the kernel's short reciprocal / rounding forms for the general routine; specials too
+    gu[1, :264] = bits(rng, (264,), 60.0)
+    gu[2, :16] = np.array([0x42800000, 0xC2800000, 0x42810000, 0xC2810000, 0x7F800000, 0xC3000000, 0x43000000, 0x00000000,
+                           0x80000000, 0x47000000, 0xC7000000, 0x7F7F0000, 0xFF7F0000, 0x00010000, 0x42B40000, 0xC2B40000],
+                          dtype=np.uint32) >> 16
     gm, am = dev(gu), alloc(7 * 264 * 2)
     cb.check(cb.lib().catena_b200_swiglu_bf16_into(gm.data, am.data, 7, 264))
     assert np.array_equal(cb.download(am, np.uint16).reshape(7, 264), orc.swiglu_bf16(gu))   # bit-exact
