@@ -175,6 +175,119 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+
+// ---- the exp~ family for W values at once, stage by stage across them (W dependency chains in flight) -------------------
+// When every |x| <= 64 the steps that carry range checks take short forms that are bit-identical there: the
+// round-to-nearest-even of t = |x| * log2(e) < 2^22 goes through the 1.5 * 2^23 constant (same integer, same float),
+// exp~(|x|) < 2^94 so its reciprocal and that of 1 + exp~(-x) in [1, 2^94] are rcp_fast's.  One larger magnitude
+// sends the whole batch through the scalar functions above.  NaNs pass the test and come out as NaNs either way.
+template <int W>
+__device__ __forceinline__ bool all_within_64(const float (&x)[W]) {
+    float big = fabsf(x[0]);
+#pragma unroll
+    for (int u = 1; u + 1 < W; u += 2) big = max3(big, fabsf(x[u]), fabsf(x[u + 1]));
+    if (W % 2 == 0) big = fmaxf(big, fabsf(x[W - 1]));
+    return big <= 64.0f;
+}
+// exp~(x) for a batch that passed all_within_64
+template <int W>
+__device__ __forceinline__ void exp_fast_n(const float (&x)[W], float (&out)[W]) {
+    float mag[W], sh[W], kf[W], xr[W], p[W];
+#pragma unroll
+    for (int u = 0; u < W; ++u) mag[u] = fabsf(x[u]);
+#pragma unroll
+    for (int u = 0; u < W; ++u) sh[u] = add(mul(mag[u], from_bits(0x3FB8AA3Bu)), 12582912.0f);
+#pragma unroll
+    for (int u = 0; u < W; ++u) kf[u] = sub(sh[u], 12582912.0f);
+#pragma unroll
+    for (int u = 0; u < W; ++u) xr[u] = sub(mag[u], mul(kf[u], from_bits(0x3F317200u)));
+#pragma unroll
+    for (int u = 0; u < W; ++u) xr[u] = sub(xr[u], mul(kf[u], from_bits(0x35BFBE8Eu)));
+#pragma unroll
+    for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3EEF1187u), mul(xr[u], from_bits(0x3E738A8Bu)));
+#pragma unroll
+    for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3F809C7Eu), mul(xr[u], p[u]));
+#pragma unroll
+    for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3F7FF8FCu), mul(xr[u], p[u]));
+#pragma unroll
+    for (int u = 0; u < W; ++u) p[u] = mul(p[u], from_bits((to_bits(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
+#pragma unroll
+    for (int u = 0; u < W; ++u) out[u] = x[u] < 0.0f ? rcp_fast(p[u]) : p[u];
+}
+template <int W>
+__device__ __forceinline__ void exp_approx_n(const float (&x)[W], float (&out)[W]) {
+    if (all_within_64(x)) {
+        exp_fast_n(x, out);
+    } else {
+#pragma unroll
+        for (int u = 0; u < W; ++u) out[u] = exp_approx(x[u]);
+    }
+}
+template <int W>
+__device__ __forceinline__ void sigmoid_n(const float (&x)[W], float (&out)[W]) {
+    if (all_within_64(x)) {
+        float nx[W], e[W];
+#pragma unroll
+        for (int u = 0; u < W; ++u) nx[u] = -x[u];
+        exp_fast_n(nx, e);
+#pragma unroll
+        for (int u = 0; u < W; ++u) out[u] = rcp_fast(add(1.0f, e[u]));
+    } else {
+#pragma unroll
+        for (int u = 0; u < W; ++u) out[u] = sigmoid(x[u]);
+    }
+}
+template <int W>
+__device__ __forceinline__ void silu_n(const float (&x)[W], float (&out)[W]) {
+    float s[W];
+    sigmoid_n(x, s);
+#pragma unroll
+    for (int u = 0; u < W; ++u) out[u] = mul(x[u], s[u]);
+}
+template <int W>
+__device__ __forceinline__ void tanh_n(const float (&x)[W], float (&out)[W]) {
+    float y[W], s[W];
+#pragma unroll
+    for (int u = 0; u < W; ++u) y[u] = mul(x[u], 2.0f);
+    sigmoid_n(y, s);
+#pragma unroll
+    for (int u = 0; u < W; ++u) out[u] = sub(mul(s[u], 2.0f), 1.0f);
+}
+template <int W>
+__device__ __forceinline__ void gelu_n(const float (&x)[W], float (&out)[W]) {
+    float z[W], t[W];
+#pragma unroll
+    for (int u = 0; u < W; ++u) {
+        const float x3 = mul(mul(x[u], x[u]), x[u]);
+        z[u] = mul(add(x[u], mul(x3, from_bits(0x3D372713u))), from_bits(0x3F4C422Au));
+    }
+    tanh_n(z, t);
+#pragma unroll
+    for (int u = 0; u < W; ++u) out[u] = mul(mul(x[u], add(1.0f, t[u])), 0.5f);
+}
+// apply<OP> to W values: the exp~ family in its batched form, everything else value by value
+template <int OP, int W>
+__device__ __forceinline__ void apply_n(const float (&x)[W], float (&out)[W]) {
+    if (OP == OP_EXP) {
+        exp_approx_n(x, out);
+    } else if (OP == OP_EXP2) {
+        float y[W];
+#pragma unroll
+        for (int u = 0; u < W; ++u) y[u] = mul(x[u], from_bits(0x3F317218u));
+        exp_approx_n(y, out);
+    } else if (OP == OP_SIGMOID) {
+        sigmoid_n(x, out);
+    } else if (OP == OP_SILU) {
+        silu_n(x, out);
+    } else if (OP == OP_TANH) {
+        tanh_n(x, out);
+    } else if (OP == OP_GELU) {
+        gelu_n(x, out);
+    } else {
+#pragma unroll
+        for (int u = 0; u < W; ++u) out[u] = apply<OP>(x[u]);
+    }
+}
 #endif
 
 }  // namespace cmath

@@ -210,46 +210,6 @@ __global__ void rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_b
 }
 
 // ---------------------------------------------------------------- SwiGLU and residual add
-// nn.silu (x * 1 / (1 + exp~(-x)), catena-lang/stdlib/nn.hex:2-20 over math.hex:148-199) of eight values, written stage by
-// stage across them so that eight dependency chains are in flight.  For |x| <= 64 (every argument of the batch) the
-// three steps with range checks inside take their short forms, bit-identical there: round-to-nearest-even of
-// t < 2^22 through the 1.5 * 2^23 constant, and both reciprocals (of exp~(|x|) < 2^94 and of 1 + exp~(-x) in [1, 2^94])
-// by cmath::rcp_fast.  Any larger magnitude sends the batch through cmath::silu.  NaNs pass the test and stay NaNs.
-__device__ __forceinline__ void silu8(const float (&x)[8], float (&out)[8]) {
-    float big = fabsf(x[0]);
-#pragma unroll
-    for (int u = 1; u < 7; u += 2) big = cmath::max3(big, fabsf(x[u]), fabsf(x[u + 1]));
-    big = fmaxf(big, fabsf(x[7]));
-    if (big <= 64.0f) {
-        float mag[8], sh[8], kf[8], xr[8], p[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) mag[u] = fabsf(x[u]);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) sh[u] = cmath::add(cmath::mul(mag[u], cmath::from_bits(0x3FB8AA3Bu)), 12582912.0f);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) kf[u] = cmath::sub(sh[u], 12582912.0f);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) xr[u] = cmath::sub(mag[u], cmath::mul(kf[u], cmath::from_bits(0x3F317200u)));
-#pragma unroll
-        for (int u = 0; u < 8; ++u) xr[u] = cmath::sub(xr[u], cmath::mul(kf[u], cmath::from_bits(0x35BFBE8Eu)));
-#pragma unroll
-        for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3EEF1187u), cmath::mul(xr[u], cmath::from_bits(0x3E738A8Bu)));
-#pragma unroll
-        for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3F809C7Eu), cmath::mul(xr[u], p[u]));
-#pragma unroll
-        for (int u = 0; u < 8; ++u) p[u] = cmath::add(cmath::from_bits(0x3F7FF8FCu), cmath::mul(xr[u], p[u]));
-#pragma unroll
-        for (int u = 0; u < 8; ++u) p[u] = cmath::mul(p[u], cmath::from_bits((__float_as_uint(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
-#pragma unroll
-        for (int u = 0; u < 8; ++u) p[u] = x[u] > 0.0f ? cmath::rcp_fast(p[u]) : p[u];      // exp~(-x): its argument is negative when x > 0
-#pragma unroll
-        for (int u = 0; u < 8; ++u) out[u] = cmath::mul(x[u], cmath::rcp_fast(cmath::add(1.0f, p[u])));
-    } else {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) out[u] = cmath::silu(x[u]);
-    }
-}
-
 // gu [T, 2F] bf16 (gate columns, then up columns) -> a [T, F] = silu(gate) * up
 __global__ void swiglu_kernel(const uint4* __restrict__ gu, uint4* __restrict__ a, uint64_t T, uint32_t F8) {
     pdl_trigger();
@@ -265,7 +225,7 @@ __global__ void swiglu_kernel(const uint4* __restrict__ gu, uint4* __restrict__ 
             gx[2 * e] = bf16_bits_to_f32(gw[e] & 0xFFFFu);
             gx[2 * e + 1] = bf16_bits_to_f32(gw[e] >> 16);
         }
-        silu8(gx, sg);
+        cmath::silu_n<8>(gx, sg);                      // nn.silu of the eight gates side by side (catena_math.cuh)
         uint32_t r[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e)

@@ -108,6 +108,14 @@ __global__ void __launch_bounds__(kThreads) fold_tree_kernel(const float* __rest
 #pragma unroll 4
         for (int j = 0; j < (int)(kChunk / 4 / kThreads); ++j) {
             float4 v = in4[j * kThreads + threadIdx.x];
+            if (GETK == F_EXPSUM) {                       // the four exp~ side by side, added in the same order
+                const float x[4] = {cmath::sub(v.x, shift), cmath::sub(v.y, shift), cmath::sub(v.z, shift), cmath::sub(v.w, shift)};
+                float e[4];
+                cmath::exp_approx_n<4>(x, e);
+                v = make_float4(e[0], e[1], e[2], e[3]);
+                acc = fold_add<ADDK>(fold_add<ADDK>(fold_add<ADDK>(fold_add<ADDK>(acc, v.x), v.y), v.z), v.w);
+                continue;
+            }
             acc = fold_add<ADDK>(acc, fold_get<GETK>(v.x, shift));
             acc = fold_add<ADDK>(acc, fold_get<GETK>(v.y, shift));
             acc = fold_add<ADDK>(acc, fold_get<GETK>(v.z, shift));
@@ -198,13 +206,15 @@ __global__ void __launch_bounds__(kThreads) map_unary_kernel(const float* __rest
     uint64_t n4 = vec ? n / 4 : 0;
     const float4* in4 = reinterpret_cast<const float4*>(in);
     float4* out4 = reinterpret_cast<float4*>(out);
-    for (uint64_t i = tid; i < n4; i += stride) {
-        float4 v = in4[i];
-        v.x = cmath::apply<OP>(v.x);
-        v.y = cmath::apply<OP>(v.y);
-        v.z = cmath::apply<OP>(v.z);
-        v.w = cmath::apply<OP>(v.w);
-        out4[i] = v;
+    // two float4 per trip: eight values go through the batched form of the op together (zeros pad a lone last one)
+    for (uint64_t i = tid; i < n4; i += 2 * stride) {
+        const bool two = i + stride < n4;
+        const float4 a = in4[i], b = two ? in4[i + stride] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        float y[8];
+        cmath::apply_n<OP, 8>(x, y);
+        out4[i] = make_float4(y[0], y[1], y[2], y[3]);
+        if (two) out4[i + stride] = make_float4(y[4], y[5], y[6], y[7]);
     }
     for (uint64_t i = n4 * 4 + tid; i < n; i += stride) out[i] = cmath::apply<OP>(in[i]);
 }
@@ -220,13 +230,15 @@ __global__ void __launch_bounds__(kThreads) softmax_map_kernel(const float* __re
     uint64_t n4 = vec ? n / 4 : 0;
     const float4* in4 = reinterpret_cast<const float4*>(in);
     float4* out4 = reinterpret_cast<float4*>(out);
-    for (uint64_t i = tid; i < n4; i += stride) {
-        float4 v = in4[i];
-        v.x = cmath::div(cmath::exp_approx(cmath::sub(v.x, m)), d);
-        v.y = cmath::div(cmath::exp_approx(cmath::sub(v.y, m)), d);
-        v.z = cmath::div(cmath::exp_approx(cmath::sub(v.z, m)), d);
-        v.w = cmath::div(cmath::exp_approx(cmath::sub(v.w, m)), d);
-        out4[i] = v;
+    for (uint64_t i = tid; i < n4; i += 2 * stride) {
+        const bool two = i + stride < n4;
+        const float4 a = in4[i], b = two ? in4[i + stride] : make_float4(m, m, m, m);
+        const float x[8] = {cmath::sub(a.x, m), cmath::sub(a.y, m), cmath::sub(a.z, m), cmath::sub(a.w, m),
+                            cmath::sub(b.x, m), cmath::sub(b.y, m), cmath::sub(b.z, m), cmath::sub(b.w, m)};
+        float e[8];
+        cmath::exp_approx_n<8>(x, e);
+        out4[i] = make_float4(cmath::div(e[0], d), cmath::div(e[1], d), cmath::div(e[2], d), cmath::div(e[3], d));
+        if (two) out4[i + stride] = make_float4(cmath::div(e[4], d), cmath::div(e[5], d), cmath::div(e[6], d), cmath::div(e[7], d));
     }
     for (uint64_t i = n4 * 4 + tid; i < n; i += stride)
         out[i] = cmath::div(cmath::exp_approx(cmath::sub(in[i], m)), d);
