@@ -9,17 +9,19 @@
 // One CTA per 128 queries of one head; a consumer thread owns one query row = one TMEM lane, so row maxima and row sums
 // need no cross-thread reduction.  exp~ admits no online rescaling, hence two passes over the key tiles: pass 1
 // multiplies Q K^T for the row maxima only, pass 2 multiplies again and accumulates P V.  A kernel that allocates TMEM
-// gets one CTA per SM, and the polynomial is the bulk of the instructions, so the CTA carries FOUR consumer warpgroups:
-// key tiles are 64 wide, group g takes the tiles kt = g, g+4, ...; the four parts of a row's maximum and of its sum meet
-// in shared memory (sum = ((part 0 + part 1) + part 2) + part 3, a fixed order).
+// gets one CTA per SM, and the polynomial is the bulk of the instructions, so the CTA carries FOUR consumer warpgroups;
+// group g takes keys 32 g .. 32 g + 31 of every 128-key tile, and the four parts of a row's maximum and of its sum
+// meet in shared memory (sum = ((part 0 + part 1) + part 2) + part 3, a fixed order).
 //   warps 4g .. 4g+3  consumer group g (warp w reads TMEM lanes 32 (w % 4) ..)
-//   warp 16    TMA producer (Q once, then K tiles / K and V tiles through a 10-stage ring of 16 KiB)
-//   warp 17    MMA issuer; allocates the CTA's 512 TMEM columns: six score buffers of 64 columns, used round robin by
-//              the sequence of score tiles (both passes), and the outputs at [384, 512).  The probabilities of 16 keys
-//              replace their 16 score columns in place: 8 columns of packed bf16 hi parts, then 8 of lo parts, each an
-//              A operand of one K = 16 MMA.
-// Score tiles run five ahead of the probabilities, so a group finds its next tile multiplied when it finishes one.
-// All waits are bounded.
+//   warp 16    TMA producer (Q once, then K tiles / K and V tiles through a 5-stage ring of 32 KiB)
+//   warp 17    MMA issuer; allocates the CTA's 512 TMEM columns: three score buffers of 128 columns, used round robin
+//              by the sequence of score tiles (both passes), and the outputs at [384, 512).  The probabilities of 16
+//              keys replace their 16 score columns in place: 8 columns of packed bf16 hi parts, then 8 of lo parts, each
+//              an A operand of one K = 16 MMA.
+// Tile width: a tcgen05.mma of M = 128 costs the issuer about as many cycles at N = 64 as at N = 128 (measured with
+// the cycle accounting below: ~80 per instruction either way), so 64-key tiles made the tensor pipe the bottleneck
+// (consumers waited for scores half of pass 2); 128-key tiles halve the score instructions per key.
+// Score tiles run two ahead of the probabilities.  All waits are bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -34,12 +36,12 @@ namespace attn3 {
 
 constexpr int kD = 128;
 constexpr int kTile = 128;                   // queries per CTA
-constexpr int kKeys = 64;                    // keys per ring stage / score buffer
-constexpr int kGroups = 4;                   // consumer warpgroups
-constexpr int kBufs = 6;                     // score buffers
-constexpr int kStages = 10;
+constexpr int kKeys = 128;                   // keys per ring stage / score buffer
+constexpr int kGroups = 4;                   // consumer warpgroups; each takes kKeys / kGroups = 32 keys of every tile
+constexpr int kBufs = 3;                     // score buffers
+constexpr int kStages = 5;
 constexpr int kQBytes = 2 * kTile * 128;     // [d-half 2][row 128][128 B]
-constexpr int kKeyHalfBytes = kKeys * 128;   // 8 KiB: 64 keys x 64 d
+constexpr int kKeyHalfBytes = kKeys * 128;   // 16 KiB: 128 keys x 64 d
 constexpr int kStageBytes = 2 * kKeyHalfBytes;
 constexpr int kConsumers = 128;              // per group
 constexpr int kThreads = kGroups * kConsumers + 64;
@@ -184,7 +186,7 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo) {
 }
 // instruction descriptors: fp32 accumulate, bf16 operands, M = 128; N = 64 keys for the scores, N = 128 d for the outputs,
 // where bit 16 says that B (the V tile) is MN-major
-constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24) | (1u << 16);
 
 // math.exp-approx (catena-lang/stdlib/math.hex:148-199) for x <= 0, bit-identical to cmath::exp_approx there; the
@@ -255,6 +257,18 @@ __device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, ui
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
+// Optional cycle accounting of the consumers (build with -DCATENA_PF_PROFILE; one lane per consumer warp adds up where
+// its cycles go): [0] whole kernel, [1] pass 1, [2] pass 2, [3] pass 2 waiting for scores, [4] first TMEM load of a
+// tile, [5] waiting for the TMEM stores, [6] waiting for the outputs, [7] set-up before the roles start.
+#ifdef CATENA_PF_PROFILE
+__device__ unsigned long long g_pf_prof[16];
+#define PF_T(var) const long long var = clock64()
+#define PF_ADD(slot, cycles) do { if (lane == 0) atomicAdd(&g_pf_prof[slot], (unsigned long long)(cycles)); } while (0)
+#else
+#define PF_T(var) do { } while (0)
+#define PF_ADD(slot, cycles) do { } while (0)
+#endif
+
 // grid (ceil(S / 128), Hq, B), 576 threads, one CTA per SM.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -267,9 +281,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     Control* ctl = reinterpret_cast<Control*>(ring + kStages * kStageBytes);
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    PF_T(pf_start);
     const uint32_t qt = gridDim.x - 1 - blockIdx.x;           // heavy tiles first
     const uint32_t h = blockIdx.y, b = blockIdx.z, kvh = h / (Hq / Hkv);
-    const uint32_t n = 2 * (qt + 1);                          // visible 64-key tiles; the last two hold masked keys
+    const uint32_t n = qt + 1;                                // visible key tiles; the last one holds masked keys
     const int kv_unit = (int)(b * Hkv + kvh);
     constexpr uint32_t kProducerWarp = kGroups * 4, kIssuerWarp = kGroups * 4 + 1;
 
@@ -278,8 +293,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
         for (int i = 0; i < kBufs; ++i) {
             mbar_init(&ctl->s_full[i], 1);
-            mbar_init(&ctl->s_free[i], kConsumers);
-            mbar_init(&ctl->p_ready[i], kConsumers);
+            mbar_init(&ctl->s_free[i], kGroups * kConsumers);   // all groups share every tile
+            mbar_init(&ctl->p_ready[i], kGroups * kConsumers);
         }
         mbar_init(&ctl->o_full, 1);
         ctl->abort_flag = 0;
@@ -298,7 +313,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (warp == kProducerWarp) {
         // =============================== TMA producer ===============================
-        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) .. K(4) V(0) K(5) V(1) .. V(n-1)
+        // ring order = the issuer's consumption order: pass 1  K(0) .. K(n-1);  pass 2  K(0) K(1) V(0) K(2) V(1) .. V(n-1)
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
@@ -331,8 +346,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // S[buffer j % kBufs] = Q K^T with the K tile at the head of the ring
             auto score_tile = [&]() {
                 if (!ok) return;
+                PF_T(pf_a);
                 if (!mbar_wait(&ctl->s_free[jbuf], (jround & 1u) ^ 1u, ctl, err)) { ok = false; return; }
+                PF_T(pf_b);
                 if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; return; }
+                PF_T(pf_c);
+                PF_ADD(j < n ? 8 : 10, pf_b - pf_a);       // issuer: waiting for a free score buffer (pass 1 / pass 2)
+                PF_ADD(j < n ? 9 : 11, pf_c - pf_b);       // issuer: waiting for the K tile
                 tc_fence_after();
                 const uint32_t ka = smem_u32(ring + (g % kStages) * kStageBytes);
 #pragma unroll
@@ -341,6 +361,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                               desc_kmajor(ka + (ks >> 2) * kKeyHalfBytes + (ks & 3u) * 32), kIdescQK, ks != 0 ? 1u : 0u);
                 tc_commit(&ctl->empty[g % kStages]);
                 tc_commit(&ctl->s_full[jbuf]);
+                PF_ADD(j < n ? 15 : 7, clock64() - pf_c);   // issuer: issuing the score MMAs and commits (pass 1 / pass 2; slot 7 shared with set-up)
                 ++g;
                 ++j;
                 if (++jbuf == (uint32_t)kBufs) { jbuf = 0; ++jround; }
@@ -353,8 +374,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (uint32_t kt = 0; kt < n && ok; ++kt) {
                 if (kt + kBufs - 1 < n) score_tile();
                 if (!ok) break;
+                PF_T(pf_d);
                 if (!mbar_wait(&ctl->p_ready[pbuf], (kt / kBufs) & 1u, ctl, err)) { ok = false; break; }
+                PF_T(pf_e);
                 if (!mbar_wait(&ctl->full[g % kStages], (g / kStages) & 1u, ctl, err)) { ok = false; break; }
+                PF_T(pf_f);
+                PF_ADD(12, pf_e - pf_d);                   // issuer: waiting for the probabilities
+                PF_ADD(13, pf_f - pf_e);                   // issuer: waiting for the V tile
                 tc_fence_after();
                 const uint32_t va = smem_u32(ring + (g % kStages) * kStageBytes);
 #pragma unroll
@@ -368,39 +394,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (++pbuf == (uint32_t)kBufs) pbuf = 0;
             }
             if (ok) tc_commit(&ctl->o_full);
+            PF_ADD(14, clock64() - pf_start);          // issuer: whole
         }
     } else {
         // =============================== consumers: group wg, thread r = query row r ===============================
-        const uint32_t wg = warp >> 2, r = tid & 127u;
+        // All groups work on the same tile, a quarter of its keys each, so two multiplied tiles wait behind the one in work.
+        const uint32_t wg = warp >> 2, r = tid & 127u, part = wg * (kKeys / kGroups);   // first key of this group's share
         const uint32_t row = qt * kTile + r;                         // position of this query in its sequence
         const uint32_t lane_addr = tmem + (((warp & 3u) * 32u) << 16);
         const float ninf = __uint_as_float(0xFF800000u);
         bool aborted = false;
+        PF_T(pf_roles);
+        PF_ADD(7, pf_roles - pf_start);
         // ---- pass 1: row maximum over this group's tiles (of the raw scores: scaling by a positive constant is
-        // monotonic, so max_i fl(s_i * scale) = fl((max_i s_i) * scale); only the last two tiles have masked keys) ----
+        // monotonic, so max_i fl(s_i * scale) = fl((max_i s_i) * scale); only the last tile has masked keys) ----
         float m_raw = ninf;
-        for (uint32_t kt = wg; kt < n; kt += kGroups) {
+        for (uint32_t kt = 0; kt < n; ++kt) {
             const uint32_t buf = kt % kBufs, par = (kt / kBufs) & 1u;    // score tile number kt
             if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], par, ctl, err))) {
                 aborted = true;
                 continue;
             }
             tc_fence_after();
-            const bool diag = kt + 2 >= n;
-            const uint32_t rel = (kt + 2 - n) * kKeys;               // first key of the tile relative to the query tile (diag only)
-            uint32_t va[32], vb[32];
-            tmem_ld32(lane_addr + buf * kKeys, va);
-            tmem_ld32(lane_addr + buf * kKeys + 32, vb);
+            const bool diag = kt + 1 == n;
+            const uint32_t rel = part;                               // first key of the share relative to the query tile (diag only)
+            uint32_t va[32];
+            tmem_ld32(lane_addr + buf * kKeys + part, va);
             tmem_ld_wait();
             if (diag) {
 #pragma unroll
-                for (uint32_t e = 0; e < 32; ++e) {
+                for (uint32_t e = 0; e < 32; ++e)
                     if (rel + e <= r) m_raw = fmaxf(m_raw, __uint_as_float(va[e]));
-                    if (rel + 32 + e <= r) m_raw = fmaxf(m_raw, __uint_as_float(vb[e]));
-                }
             } else {
 #pragma unroll
-                for (uint32_t e = 0; e < 32; ++e) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(va[e]), __uint_as_float(vb[e])));
+                for (uint32_t e = 0; e < 32; e += 2) m_raw = cmath::max3(m_raw, __uint_as_float(va[e]), __uint_as_float(va[e + 1]));
             }
             tc_fence_before();
             mbar_arrive(&ctl->s_free[buf]);
@@ -413,17 +440,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         m = cmath::mul(m, scale);
         asm volatile("bar.sync 1, %0;" ::"n"(kGroups * kConsumers) : "memory");   // all parts read before xch is reused for the sums
         // ---- pass 2: probabilities into TMEM, row sum ----
+        PF_T(pf_p2);
+        PF_ADD(1, pf_p2 - pf_roles);
         float l = 0.0f;
-        for (uint32_t kt = wg; kt < n; kt += kGroups) {
+        for (uint32_t kt = 0; kt < n; ++kt) {
             const uint32_t buf = (n + kt) % kBufs, par = ((n + kt) / kBufs) & 1u;   // score tile number n + kt
+            PF_T(pf_w0);
             if (aborted || !__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->s_full[buf], par, ctl, err))) {
                 aborted = true;
                 continue;
             }
             tc_fence_after();
-            const uint32_t rel = (kt + 2 - n) * kKeys;               // meaningful on the last two tiles only
-            const uint32_t base = lane_addr + buf * kKeys;
-            // 16 keys per trip, ascending; the next 16 scores are in flight meanwhile.  MASKED only on the last two tiles
+            PF_T(pf_w1);
+            PF_ADD(3, pf_w1 - pf_w0);
+            const uint32_t rel = part;                               // meaningful on the last tile only
+            const uint32_t base = lane_addr + buf * kKeys + part;
+            // 16 keys per trip, ascending; the next 16 scores are in flight meanwhile.  MASKED only on the last tile
             // (keys past the query's own position).  The loop stays rolled: four groups at four places of an unrolled
             // body do not fit the instruction cache.
             auto tile = [&](auto masked_tag) {
@@ -431,13 +463,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 uint32_t v[16];
                 tmem_ld16(base, v);
 #pragma unroll 1
-                for (uint32_t c = 0; c < (uint32_t)kKeys / 16; ++c) {
+                for (uint32_t c = 0; c < (uint32_t)kKeys / kGroups / 16; ++c) {
                     float sc[16];
                     uint32_t hi[8], lo[8];
+                    PF_T(pf_l0);
                     tmem_ld_wait();
+                    PF_T(pf_l1);
+                    if (c == 0) PF_ADD(4, pf_l1 - pf_l0);
 #pragma unroll
                     for (uint32_t e = 0; e < 16; ++e) sc[e] = __uint_as_float(v[e]);
-                    if (c + 1 < (uint32_t)kKeys / 16) tmem_ld16(base + (c + 1) * 16, v);
+                    if (c + 1 < (uint32_t)kKeys / kGroups / 16) tmem_ld16(base + (c + 1) * 16, v);
 #pragma unroll
                     for (uint32_t e = 0; e < 16; e += kExpW) {       // kExpW keys side by side
                         float xs[kExpW], ps[kExpW];
@@ -460,21 +495,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tmem_st8(base + c * 16 + 8, lo);
                 }
             };
-            if (kt + 2 >= n) tile(std::true_type{});
+            if (kt + 1 == n) tile(std::true_type{});
             else tile(std::false_type{});
+            PF_T(pf_s0);
             tmem_st_wait();
+            PF_T(pf_s1);
+            PF_ADD(5, pf_s1 - pf_s0);
             tc_fence_before();
             mbar_arrive(&ctl->p_ready[buf]);
             mbar_arrive(&ctl->s_free[buf]);
         }
+        PF_T(pf_p2e);
+        PF_ADD(2, pf_p2e - pf_p2);
         ctl->xch[wg][r] = l;
         asm volatile("bar.sync 1, %0;" ::"n"(kGroups * kConsumers) : "memory");
         l = ctl->xch[0][r];
 #pragma unroll
         for (int gI = 1; gI < kGroups; ++gI) l = cmath::add(l, ctl->xch[gI][r]);
         // ---- outputs: O / l, group g takes d columns 32 g .. 32 g + 31 ----
+        PF_T(pf_o0);
         if (!aborted && __all_sync(0xFFFFFFFFu, mbar_wait(&ctl->o_full, 0, ctl, err))) {
             tc_fence_after();
+            PF_T(pf_o1);
+            PF_ADD(6, pf_o1 - pf_o0);
             __nv_bfloat16* orow = out + (((size_t)b * S + row) * Hq + h) * kD;
             const uint32_t c = wg;
             uint32_t v[32];
@@ -496,6 +539,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncwarp();
     tc_fence_before();
     __syncthreads();
+#ifdef CATENA_PF_PROFILE
+    if (warp < kGroups * 4) PF_ADD(0, clock64() - pf_start);
+#endif
     if (warp == kIssuerWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmemCols) : "memory");
@@ -602,6 +648,14 @@ catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, cons
     return CATENA_OK;
 }
 
+#ifdef CATENA_PF_PROFILE
+extern "C" void catena_b200_debug_pf_prof(unsigned long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, attn3::g_pf_prof, sizeof(unsigned long long) * 16);
+    unsigned long long zero[16] = {0};
+    cudaMemcpyToSymbol(attn3::g_pf_prof, zero, sizeof(zero));
+}
+#endif
 // runs rcp_check_kernel over the whole range and returns {values compared, mismatches}
 catena_status_t attn_prefill_rcp_check(uint64_t out[2]) {
     unsigned long long* dev = nullptr;
