@@ -184,7 +184,7 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo) {
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            (1ull << 46) | (2ull << 61);
 }
-// instruction descriptors: fp32 accumulate, bf16 operands, M = 128; N = 64 keys for the scores, N = 128 d for the outputs,
+// instruction descriptors: fp32 accumulate, bf16 operands, M = 128; N = 128 keys for the scores, N = 128 d for the outputs,
 // where bit 16 says that B (the V tile) is MN-major
 constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24) | (1u << 16);
