@@ -33,19 +33,42 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;  // bit pattern 0x00000000 (matrix.hex:249)
 
+    // The next k-slab travels from global memory into registers while the current one is multiplied out of shared
+    // memory (small products are latency bound: eight exposed slab loads were most of a 256^3 launch).
+    constexpr int PA = (BM * BK + THREADS - 1) / THREADS, PB = (BK * BN + THREADS - 1) / THREADS;
+    float ra[PA], rb[PB];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int p = 0; p < PA; ++p) {
+            const int idx = tid + p * THREADS, r = idx / BK, kk = idx % BK;
+            const int gr = row0 + r, gk = k0 + kk;
+            ra[p] = (idx < BM * BK && gr < n && gk < k) ? A[(size_t)gr * k + gk] : 0.0f;
+        }
+#pragma unroll
+        for (int p = 0; p < PB; ++p) {
+            const int idx = tid + p * THREADS, kk = idx / BN, c = idx % BN;
+            const int gk = k0 + kk, gc = col0 + c;
+            rb[p] = (idx < BK * BN && gk < k && gc < m) ? B[(size_t)gk * m + gc] : 0.0f;
+        }
+    };
+    // A[row0.., k0..] transposed and B[k0.., col0..]
+    auto stage = [&]() {
+#pragma unroll
+        for (int p = 0; p < PA; ++p) {
+            const int idx = tid + p * THREADS;
+            if (idx < BM * BK) As[idx % BK][idx / BK] = ra[p];
+        }
+#pragma unroll
+        for (int p = 0; p < PB; ++p) {
+            const int idx = tid + p * THREADS;
+            if (idx < BK * BN) Bs[idx / BN][idx % BN] = rb[p];
+        }
+    };
+    if (k > 0) fetch(0);
     for (int k0 = 0; k0 < k; k0 += BK) {
         const int kb = min(BK, k - k0);
-        // stage A[row0.., k0..] transposed and B[k0.., col0..]
-        for (int idx = tid; idx < BM * BK; idx += THREADS) {
-            int r = idx / BK, kk = idx % BK;
-            int gr = row0 + r, gk = k0 + kk;
-            As[kk][r] = (gr < n && gk < k) ? A[(size_t)gr * k + gk] : 0.0f;
-        }
-        for (int idx = tid; idx < BK * BN; idx += THREADS) {
-            int kk = idx / BN, c = idx % BN;
-            int gk = k0 + kk, gc = col0 + c;
-            Bs[kk][c] = (gk < k && gc < m) ? B[(size_t)gk * m + gc] : 0.0f;
-        }
+        stage();
+        if (k0 + BK < k) fetch(k0 + BK);
         __syncthreads();
         if (kb == BK) {
 #pragma unroll
@@ -111,7 +134,7 @@ catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint
     } else {
         // small products are latency bound: more, smaller tiles to cover the SMs
         dim3 grid((unsigned)ceil_div_u64(m, 16), (unsigned)ceil_div_u64(n, 16));
-        matmul_f32_kernel<16, 16, 32, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+        matmul_f32_kernel<16, 16, 128, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
     }
     count_launch();
     return CATENA_OK;
