@@ -62,6 +62,17 @@ catena_status_t launch_identity_matmul_f32(const float* a, float* c, uint64_t n,
 // gemm_tc.cu
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8);
+// Where the epilogue of a q/k/v projection puts its output instead of a [tokens, (hq + 2 hkv) * 128] matrix: rotated
+// queries into q_out [tokens, hq, 128], rotated keys and plain values into the caches [batch, hkv, cap, 128] at position
+// pos0 + (token % seq); `table` holds (cos, sin) of the `seq` positions, [seq][64].
+struct GemmRopeOut {
+    const float2* table;
+    void* q_out;
+    void* k_cache;
+    void* v_cache;
+    uint32_t seq, pos0, hq, hkv, cap;
+};
+catena_status_t launch_gemm_tc_rope(const void* a, const void* b, uint64_t m, uint64_t n, uint64_t k, const GemmRopeOut& rope);
 bool gemm_tc_fuses_residual(uint64_t m);
 catena_status_t launch_gemm_tc_residual(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                         const void* residual);

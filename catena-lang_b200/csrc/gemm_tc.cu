@@ -423,7 +423,8 @@ static bool gemm_pair_mode(uint64_t m) {
 }
 void gemm_tc_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual);
+                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual,
+                                 const GemmRopeOut* rope);
 
 struct ErrWord {
     uint32_t* dev = nullptr;
@@ -444,7 +445,8 @@ static catena_status_t err_word(ErrWord** out) {
 }
 
 static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                          int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual);
+                                          int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual,
+                                          const GemmRopeOut* rope = nullptr);
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8) {
     return launch_gemm_tc_any(a, b, c, m, n, k, ldc, is_i8, nullptr, 0, nullptr);
@@ -457,6 +459,11 @@ catena_status_t launch_gemm_tc_residual(const void* a, const void* b, void* c, u
     if (!residual || !gemm_pair_mode(m)) return fail(CATENA_E_UNSUPPORTED, "gemm: residual epilogue needs the CTA-pair kernel");
     return launch_gemm_tc_any(a, b, c, m, n, k, ldc, 0, nullptr, 0, residual);
 }
+// bf16 q/k/v projection whose epilogue rotates and scatters into the query buffer and the KV caches (CTA-pair kernel only)
+catena_status_t launch_gemm_tc_rope(const void* a, const void* b, uint64_t m, uint64_t n, uint64_t k, const GemmRopeOut& rope) {
+    if (!gemm_pair_mode(m)) return fail(CATENA_E_UNSUPPORTED, "gemm: rotary epilogue needs the CTA-pair kernel");
+    return launch_gemm_tc_any(a, b, rope.q_out, m, n, k, n, 0, nullptr, 0, nullptr, &rope);
+}
 
 // The same GEMM whose epilogue also stores every output tile to `n_peers` peer-mapped copies of C (pair kernel only).
 catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
@@ -464,7 +471,8 @@ catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint
     return launch_gemm_tc_any(a, b, c, m, n, k, ldc, is_i8, peer_c, n_peers, nullptr);
 }
 static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                          int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual) {
+                                          int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual,
+                                          const GemmRopeOut* rope) {
     CATENA_TRY(ensure_device());
     if (m == 0 || n == 0) return CATENA_OK;
     if (!a || !b || !c) return fail(CATENA_E_BAD_ARG, "gemm: null operand");
@@ -481,7 +489,7 @@ static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c,
     if (n_peers > 0 && !gemm_pair_mode(m))
         return fail(CATENA_E_UNSUPPORTED, "gemm: peer outputs need the CTA-pair kernel (more than 128 rows)");
     if (gemm_pair_mode(m)) {
-        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev, peer_c, n_peers, residual));
+        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev, peer_c, n_peers, residual, rope));
     } else {
         CUtensorMap map_a, map_b, map_b128, map_b64;
         CATENA_TRY(make_operand_map(&map_a, a, m, k, eb, tc::BM));

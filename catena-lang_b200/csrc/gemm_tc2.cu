@@ -57,11 +57,14 @@ struct PeerOut {
     void* ptr[kMaxPeers];
     uint32_t n;
     const void* residual;         // EPI_RESIDUAL: bf16 [M, ldc] added to the rounded product
+    GemmRopeOut rope;             // EPI_ROPE
 };
 // epilogue variants (separate instantiations: the plain kernel carries none of the others' code or registers)
 constexpr int EPI_PLAIN = 0;      // C = round(A B^T)
 constexpr int EPI_PEERS = 1;      // the same, also stored to peer-mapped copies of C (gather-fused)
 constexpr int EPI_RESIDUAL = 2;   // bf16 only: C = round(round(A B^T) + residual), the sum taken in fp32
+constexpr int EPI_ROPE = 3;       // bf16 only, a q/k/v projection: the rounded product is rotated (q, k heads) and stored
+                                  // straight into the query buffer and the KV caches (GemmRopeOut); C itself is not written
 
 struct __align__(8) Control {
     uint64_t full[MAX_STAGES];       // used in the leader CTA
@@ -343,8 +346,62 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tc_fence_after();
             const uint32_t row = w.m_blk * 2 * BM + rank * BM + row_in_cta;
             const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
+            if (EPI == EPI_ROPE) {
+                // A 256-column tile is two heads of 128.  Rotary pairs are (i, i + 64): the thread reads 32 columns of
+                // each half of a head, rounds both to bf16 as the unfused projection would have stored them, rotates with
+                // separately rounded products (llama::rope_append_kernel's arithmetic) and stores 64 B to either half.
+                const GemmRopeOut& ro = peers.rope;
+                const uint32_t seq_i = row / ro.seq, s_pos = row - seq_i * ro.seq, pos = ro.pos0 + s_pos;
+                for (uint32_t hcol = 0; hcol < w.width && w.col0 + hcol < N; hcol += 128) {
+                    const uint32_t head = (w.col0 + hcol) >> 7;
+                    __nv_bfloat16* dst;
+                    bool rotate = true;
+                    if (head < ro.hq) {
+                        dst = static_cast<__nv_bfloat16*>(ro.q_out) + ((uint64_t)row * ro.hq + head) * 128;
+                    } else if (head < ro.hq + ro.hkv) {
+                        dst = static_cast<__nv_bfloat16*>(ro.k_cache) + (((uint64_t)seq_i * ro.hkv + (head - ro.hq)) * ro.cap + pos) * 128;
+                    } else {
+                        dst = static_cast<__nv_bfloat16*>(ro.v_cache) + (((uint64_t)seq_i * ro.hkv + (head - ro.hq - ro.hkv)) * ro.cap + pos) * 128;
+                        rotate = false;
+                    }
 #pragma unroll 1
-            for (uint32_t c = 0; c < w.width; c += 32) {
+                    for (uint32_t j = 0; j < 2; ++j) {
+                        uint32_t va[32], vb[32];
+                        tmem_ld32(taddr + hcol + 32 * j, va);
+                        tmem_ld32(taddr + hcol + 64 + 32 * j, vb);
+                        tmem_ld_wait();
+                        if (row < M) {
+                            const float4* tab = reinterpret_cast<const float4*>(ro.table + (uint64_t)s_pos * 64 + 32 * j);
+                            uint32_t o1[16], o2[16];
+#pragma unroll
+                            for (int e = 0; e < 32; e += 2) {
+                                const float x1a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(va[e])));
+                                const float x1b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(va[e + 1])));
+                                const float x2a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vb[e])));
+                                const float x2b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vb[e + 1])));
+                                float r1a = x1a, r1b = x1b, r2a = x2a, r2b = x2b;
+                                if (rotate) {
+                                    const float4 cs = tab[e >> 1];            // (cos, sin) of pairs e and e + 1
+                                    r1a = __fsub_rn(__fmul_rn(x1a, cs.x), __fmul_rn(x2a, cs.y));
+                                    r2a = __fadd_rn(__fmul_rn(x2a, cs.x), __fmul_rn(x1a, cs.y));
+                                    r1b = __fsub_rn(__fmul_rn(x1b, cs.z), __fmul_rn(x2b, cs.w));
+                                    r2b = __fadd_rn(__fmul_rn(x2b, cs.z), __fmul_rn(x1b, cs.w));
+                                }
+                                const __nv_bfloat162 h1 = __floats2bfloat162_rn(r1a, r1b), h2 = __floats2bfloat162_rn(r2a, r2b);
+                                o1[e >> 1] = *reinterpret_cast<const uint32_t*>(&h1);
+                                o2[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                reinterpret_cast<uint4*>(dst + 32 * j)[q] = make_uint4(o1[4 * q], o1[4 * q + 1], o1[4 * q + 2], o1[4 * q + 3]);
+                                reinterpret_cast<uint4*>(dst + 64 + 32 * j)[q] = make_uint4(o2[4 * q], o2[4 * q + 1], o2[4 * q + 2], o2[4 * q + 3]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll 1
+            for (uint32_t c = 0; EPI != EPI_ROPE && c < w.width; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
                 uint4 res[4];
@@ -522,12 +579,17 @@ static catena_status_t make_map2(CUtensorMap* map, const void* base, uint64_t ro
 
 // Enqueues the CTA-pair GEMM.  `err_dev` is the device error word shared with the single-CTA kernel.
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
-                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual) {
-    if (residual && (is_i8 || n_peers)) return fail(CATENA_E_BAD_ARG, "gemm: a residual goes with the plain bf16 kernel only");
+                                 int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual,
+                                 const GemmRopeOut* rope) {
+    if ((residual || rope) && (is_i8 || n_peers)) return fail(CATENA_E_BAD_ARG, "gemm: a residual / rotary epilogue goes with the plain bf16 kernel only");
+    if (rope && (residual || n % 128 || !rope->table || !rope->q_out || !rope->k_cache || !rope->v_cache || !rope->seq ||
+                 n != (uint64_t)(rope->hq + 2 * rope->hkv) * 128))
+        return fail(CATENA_E_BAD_ARG, "gemm: bad rotary epilogue");
     if (n_peers > (uint32_t)tc2::kMaxPeers) return fail(CATENA_E_BAD_ARG, "gemm: more than 7 peer outputs");
     tc2::PeerOut peers = {};
     peers.n = n_peers;
     peers.residual = residual;
+    if (rope) peers.rope = *rope;
     for (uint32_t i = 0; i < n_peers; ++i) {
         if (!peer_c || !peer_c[i] || ((uintptr_t)peer_c[i] & 15)) return fail(CATENA_E_BAD_ARG, "gemm: null or unaligned peer output");
         peers.ptr[i] = peer_c[i];
@@ -542,7 +604,8 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
                              uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*);
     KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, tc2::EPI_PEERS> : tc2::gemm_tc2_kernel<true, tc2::EPI_PLAIN>)
                             : (n_peers ? tc2::gemm_tc2_kernel<false, tc2::EPI_PEERS>
-                                       : (residual ? tc2::gemm_tc2_kernel<false, tc2::EPI_RESIDUAL> : tc2::gemm_tc2_kernel<false, tc2::EPI_PLAIN>));
+                                       : (rope ? tc2::gemm_tc2_kernel<false, tc2::EPI_ROPE>
+                                               : (residual ? tc2::gemm_tc2_kernel<false, tc2::EPI_RESIDUAL> : tc2::gemm_tc2_kernel<false, tc2::EPI_PLAIN>)));
     const int smem_bytes = tc2::smem_bytes(n_peers != 0);
     CATENA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     const uint64_t tiles = ceil_div_u64(m, 2 * tc2::BM) * ceil_div_u64(n, tc2::BN);
@@ -551,7 +614,8 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     if (cta_limit > 0 && pairs > (uint64_t)(cta_limit / 2 > 0 ? cta_limit / 2 : 1)) pairs = (uint64_t)(cta_limit / 2 > 0 ? cta_limit / 2 : 1);
     if (tiles < pairs) pairs = tiles;
     const uint64_t rem = tiles % pairs;
-    const uint32_t split = rem == 0 ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
+    // (the rotary epilogue needs whole heads in a unit: no cut along N)
+    const uint32_t split = rem == 0 || rope ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
     const unsigned grid = (unsigned)(pairs * 2);
     cudaStream_t st = tls().stream;
     cudaLaunchConfig_t cfg = {};

@@ -692,6 +692,46 @@ static catena_status_t launch_embed_rmsnorm(const void* table, const int32_t* id
     return launch_pdl("rmsnorm_rows_kernel", llama::rmsnorm_rows_kernel, dim3((unsigned)tokens), dim3(256), 0, (const uint4*)table, ids,
                       (uint32_t)vocab, bad, (uint4*)x, (uint4*)y, (uint32_t)hidden);
 }
+// enqueues the (cos, sin) table of positions pos0 .. pos0 + seq - 1 into the thread's buffer
+static catena_status_t launch_rope_angles(const float* inv, uint64_t seq, uint64_t pos0, const float2** table) {
+    RopeAngles& ra = g_rope_angles[tls().device & 15];
+    if (ra.positions < seq) {
+        if (ra.dev) {
+            CATENA_CUDA(cudaStreamSynchronize(tls().stream));
+            CATENA_CUDA(cudaFree(ra.dev));
+            ra.dev = nullptr;
+        }
+        CATENA_CUDA(cudaMalloc(&ra.dev, seq * 64 * sizeof(float2)));
+        ra.positions = seq;
+    }
+    CATENA_TRY(launch_pdl("rope_table_kernel", llama::rope_table_kernel, dim3((unsigned)ceil_div_u64(seq * 64, 256)), dim3(256), 0, inv,
+                          ra.dev, (uint32_t)pos0, (uint32_t)seq));
+    *table = ra.dev;
+    return CATENA_OK;
+}
+// q/k/v projection of a prefill with the rotation and the cache append in the GEMM's epilogue (no [tokens, qkv] matrix,
+// no separate pass over it); false when the shape has to take the projection followed by launch_rope_append
+static bool qkv_rope_fusable(uint64_t tokens, uint64_t seq, uint64_t hq, uint64_t hkv) {
+    return seq >= 16 && tokens / seq * (hq + hkv) >= 8 && gemm_tc_fuses_residual(tokens) && tokens <= 0xFFFFFFFFull;
+}
+static catena_status_t launch_qkv_rope(const void* x, const void* w_qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens,
+                                       uint64_t seq, uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, uint64_t hidden, float base) {
+    if (seq == 0 || tokens % seq) return fail(CATENA_E_BAD_ARG, "rope: tokens must be batch * seq");
+    if (pos0 + seq > cap) return fail(CATENA_E_BAD_ARG, "rope: positions beyond the cache capacity");
+    const float* inv = nullptr;
+    CATENA_TRY(rope_table(base, &inv));
+    GemmRopeOut ro = {};
+    CATENA_TRY(launch_rope_angles(inv, seq, pos0, &ro.table));
+    ro.q_out = q_out;
+    ro.k_cache = k_cache;
+    ro.v_cache = v_cache;
+    ro.seq = (uint32_t)seq;
+    ro.pos0 = (uint32_t)pos0;
+    ro.hq = (uint32_t)hq;
+    ro.hkv = (uint32_t)hkv;
+    ro.cap = (uint32_t)cap;
+    return launch_gemm_tc_rope(x, w_qkv, tokens, (hq + 2 * hkv) * llama::kHeadDim, hidden, ro);
+}
 static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens, uint64_t seq,
                                           uint64_t pos0, uint64_t hq, uint64_t hkv, uint64_t cap, float base) {
     if (!tokens) return CATENA_OK;
@@ -700,22 +740,12 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
     const float* inv = nullptr;
     CATENA_TRY(rope_table(base, &inv));
     if (seq >= 16 && tokens / seq * (hq + hkv) >= 8) {   // many (sequence, head) pairs per position: evaluate each angle once
-        RopeAngles& ra = g_rope_angles[tls().device & 15];
-        if (ra.positions < seq) {
-            if (ra.dev) {
-                CATENA_CUDA(cudaStreamSynchronize(tls().stream));
-                CATENA_CUDA(cudaFree(ra.dev));
-                ra.dev = nullptr;
-            }
-            CATENA_CUDA(cudaMalloc(&ra.dev, seq * 64 * sizeof(float2)));
-            ra.positions = seq;
-        }
-        CATENA_TRY(launch_pdl("rope_table_kernel", llama::rope_table_kernel, dim3((unsigned)ceil_div_u64(seq * 64, 256)), dim3(256), 0, inv,
-                              ra.dev, (uint32_t)pos0, (uint32_t)seq));
+        const float2* table = nullptr;
+        CATENA_TRY(launch_rope_angles(inv, seq, pos0, &table));
         const uint64_t work = tokens * (hq + 2 * hkv) * 8;
         return launch_pdl("rope_append_kernel", llama::rope_append_kernel, dim3((unsigned)ceil_div_u64(work, 256)), dim3(256), 0,
                           (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-                          (const float2*)ra.dev, (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
+                          table, (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
     }
     const uint64_t work = tokens * (hq + 2 * hkv) * 64;
     return launch_pdl("rope_append_small_kernel", llama::rope_append_small_kernel, dim3((unsigned)ceil_div_u64(work, 128)), dim3(128), 0,
@@ -866,8 +896,12 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
     __nv_bfloat16* act = ws;
     return composite([&]() -> catena_status_t {
         CATENA_TRY(launch_embed_rmsnorm(blk->embedding, ids, x, nrm, T, d.H, blk->vocab));
-        CATENA_TRY(launch_linear(nrm, blk->w_qkv, nullptr, qkv, T, d.qkv_cols, d.H));
-        CATENA_TRY(launch_rope_append(qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, blk->rope_base));
+        if (qkv_rope_fusable(T, seq, d.Hq, d.Hkv) && !(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
+            CATENA_TRY(launch_qkv_rope(nrm, blk->w_qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, d.H, blk->rope_base));
+        } else {
+            CATENA_TRY(launch_linear(nrm, blk->w_qkv, nullptr, qkv, T, d.qkv_cols, d.H));
+            CATENA_TRY(launch_rope_append(qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, blk->rope_base));
+        }
         if (seq == 1) {
             CATENA_TRY(launch_attn_decode(q, k_cache, v_cache, att, batch, d.Hq, d.Hkv, llama::kHeadDim, pos0 + 1, blk->max_len, 0,
                                           batch * d.Hkv));

@@ -279,6 +279,29 @@ def test_block_prefill_then_decode(orc, n_heads, n_kv_heads):
         blk.close()
 
 
+def test_block_prefill_fused_epilogues_equal_separate_kernels():
+    """With the CTA-pair GEMM the prefill rotates q / k and appends k / v in the q/k/v projection's epilogue and adds the
+    residuals in the o / down projections' epilogues; on the single-CTA GEMM it runs the projection, the rotary kernel
+    and the add kernel one after the other.  Same roundings in the same places: outputs and caches agree bit for bit."""
+    hidden, n_heads, n_kv_heads, ffn, vocab, max_len, B, S = 256, 3, 1, 512, 300, 200, 2, 150     # three tiles of q/k/v columns, odd head count
+    rng = np.random.default_rng(9)
+    weights = make_block(rng, hidden, n_heads, n_kv_heads, ffn, vocab)
+    ids = rng.integers(0, vocab, B * S).astype(np.int32)
+    results = []
+    for pair in (1, 0):
+        cb.lib().catena_b200_debug_set_gemm_pair(pair)
+        blk = cb.LlamaBlock(hidden, n_heads, n_kv_heads, ffn, vocab, max_len, weights, B)
+        try:
+            out = blk.prefill(ids, S)
+            gk, gv = blk.caches()
+            results.append((out.copy(), gk[:, :, :S].copy(), gv[:, :, :S].copy()))
+        finally:
+            blk.close()
+            cb.lib().catena_b200_debug_set_gemm_pair(1)
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)
+
+
 def test_block_argument_errors():
     """Bad arguments come back as statuses before anything is launched (the generated code of the reference would
     have trapped on the device)."""
