@@ -73,6 +73,7 @@ struct GemmRopeOut {
     uint32_t seq, pos0, hq, hkv, cap;
 };
 catena_status_t launch_gemm_tc_rope(const void* a, const void* b, uint64_t m, uint64_t n, uint64_t k, const GemmRopeOut& rope);
+catena_status_t launch_gemm_tc_swiglu(const void* x, const void* w, void* act, uint64_t m, uint64_t ffn, uint64_t k);
 bool gemm_tc_fuses_residual(uint64_t m);
 catena_status_t launch_gemm_tc_residual(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                         const void* residual);

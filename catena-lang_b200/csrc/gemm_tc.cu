@@ -424,7 +424,7 @@ static bool gemm_pair_mode(uint64_t m) {
 void gemm_tc_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                  int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual,
-                                 const GemmRopeOut* rope);
+                                 const GemmRopeOut* rope, int swiglu);
 
 struct ErrWord {
     uint32_t* dev = nullptr;
@@ -446,7 +446,7 @@ static catena_status_t err_word(ErrWord** out) {
 
 static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                           int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual,
-                                          const GemmRopeOut* rope = nullptr);
+                                          const GemmRopeOut* rope = nullptr, int swiglu = 0);
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8) {
     return launch_gemm_tc_any(a, b, c, m, n, k, ldc, is_i8, nullptr, 0, nullptr);
@@ -458,6 +458,12 @@ catena_status_t launch_gemm_tc_residual(const void* a, const void* b, void* c, u
                                         const void* residual) {
     if (!residual || !gemm_pair_mode(m)) return fail(CATENA_E_UNSUPPORTED, "gemm: residual epilogue needs the CTA-pair kernel");
     return launch_gemm_tc_any(a, b, c, m, n, k, ldc, 0, nullptr, 0, residual);
+}
+// act [m, ffn] = silu(round(x w_gate^T)) * round(x w_up^T) with w = [2 ffn, k] (gate rows, then up rows), the activation in the
+// GEMM's epilogue (CTA-pair kernel only, ffn a multiple of 128)
+catena_status_t launch_gemm_tc_swiglu(const void* x, const void* w, void* act, uint64_t m, uint64_t ffn, uint64_t k) {
+    if (!gemm_pair_mode(m) || ffn % 128) return fail(CATENA_E_UNSUPPORTED, "gemm: SwiGLU epilogue needs the CTA-pair kernel and ffn % 128 == 0");
+    return launch_gemm_tc_any(x, w, act, m, 2 * ffn, k, ffn, 0, nullptr, 0, nullptr, nullptr, 1);
 }
 // bf16 q/k/v projection whose epilogue rotates and scatters into the query buffer and the KV caches (CTA-pair kernel only)
 catena_status_t launch_gemm_tc_rope(const void* a, const void* b, uint64_t m, uint64_t n, uint64_t k, const GemmRopeOut& rope) {
@@ -472,7 +478,7 @@ catena_status_t launch_gemm_tc_peers(const void* a, const void* b, void* c, uint
 }
 static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                           int is_i8, void* const* peer_c, uint32_t n_peers, const void* residual,
-                                          const GemmRopeOut* rope) {
+                                          const GemmRopeOut* rope, int swiglu) {
     CATENA_TRY(ensure_device());
     if (m == 0 || n == 0) return CATENA_OK;
     if (!a || !b || !c) return fail(CATENA_E_BAD_ARG, "gemm: null operand");
@@ -481,7 +487,7 @@ static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c,
         return fail(CATENA_E_BAD_ARG, "gemm: K must be a positive multiple of 16 bytes (TMA row pitch)");
     if (((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return fail(CATENA_E_BAD_ARG, "gemm: operands must be 16-byte aligned");
     if (m > 0x7FFFFF00ull || n > 0x7FFFFF00ull || k > 0x7FFFFF00ull) return fail(CATENA_E_TOO_LARGE, "gemm: dimension too large");
-    if (ldc < n) return fail(CATENA_E_BAD_ARG, "gemm: ldc < n");
+    if (ldc < (swiglu ? n / 2 : n)) return fail(CATENA_E_BAD_ARG, "gemm: ldc < n");
 
     ErrWord* ew = nullptr;
     CATENA_TRY(err_word(&ew));
@@ -489,7 +495,7 @@ static catena_status_t launch_gemm_tc_any(const void* a, const void* b, void* c,
     if (n_peers > 0 && !gemm_pair_mode(m))
         return fail(CATENA_E_UNSUPPORTED, "gemm: peer outputs need the CTA-pair kernel (more than 128 rows)");
     if (gemm_pair_mode(m)) {
-        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev, peer_c, n_peers, residual, rope));
+        CATENA_TRY(enqueue_gemm_tc2(a, b, c, m, n, k, ldc, is_i8, g_cta_limit, ew->dev, peer_c, n_peers, residual, rope, swiglu));
     } else {
         CUtensorMap map_a, map_b, map_b128, map_b64;
         CATENA_TRY(make_operand_map(&map_a, a, m, k, eb, tc::BM));

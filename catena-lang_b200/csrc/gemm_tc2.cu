@@ -23,6 +23,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "catena_math.cuh"
 #include "common.cuh"
 
 namespace catena {
@@ -63,6 +64,9 @@ struct PeerOut {
 constexpr int EPI_PLAIN = 0;      // C = round(A B^T)
 constexpr int EPI_PEERS = 1;      // the same, also stored to peer-mapped copies of C (gather-fused)
 constexpr int EPI_RESIDUAL = 2;   // bf16 only: C = round(round(A B^T) + residual), the sum taken in fp32
+constexpr int EPI_SWIGLU = 4;     // bf16 only, B = [2 F, K] (gate rows, then up rows): C [M, F] = silu(round(gate)) * round(up).  The
+                                  // leader CTA loads 128 gate rows, its peer the 128 up rows of the same outputs, so a 256-column
+                                  // accumulator holds gate and up of 128 outputs side by side; N is 2 F in the tile arithmetic
 constexpr int EPI_ROPE = 3;       // bf16 only, a q/k/v projection: the rounded product is rotated (q, k heads) and stored
                                   // straight into the query buffer and the KV caches (GemmRopeOut); C itself is not written
 
@@ -292,7 +296,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const CUtensorMap* mapb = half == 128u ? &map_b128 : (half == 64u ? &map_b64 : &map_b32);
                 const uint32_t bytes_pair = 2u * (A_BYTES + half * BK_BYTES);
                 const int a_row = (int)(w.m_blk * 2 * BM + rank * BM);
-                const int b_row = (int)(w.col0 + rank * half);
+                const int b_row = EPI == EPI_SWIGLU ? (int)(w.col0 / 2 + rank * (N / 2)) : (int)(w.col0 + rank * half);
                 for (uint32_t kb = 0; kb < kblocks; ++kb) {
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, ctl, err, 1u)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(&ctl->full[stage], bytes_pair);
@@ -346,6 +350,43 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tc_fence_after();
             const uint32_t row = w.m_blk * 2 * BM + rank * BM + row_in_cta;
             const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * BN;
+            if (EPI == EPI_SWIGLU) {
+                // columns 0..127 = gate, 128..255 = up of outputs col0 / 2 .. col0 / 2 + 127: both are rounded to bf16 as the
+                // unfused projection would have stored them, then nn.silu(gate) * up, eight outputs side by side
+                const uint32_t F = N / 2, out0 = w.col0 / 2;
+#pragma unroll 1
+                for (uint32_t c = 0; c < 128; c += 32) {
+                    uint32_t vg[32], vu[32];
+                    tmem_ld32(taddr + c, vg);
+                    tmem_ld32(taddr + 128 + c, vu);
+                    tmem_ld_wait();
+                    if (row < M) {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            float g[8], sg[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) g[u] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[e + u])));
+                            cmath::silu_n<8>(g, sg);
+#pragma unroll
+                            for (int u = 0; u < 8; u += 2) {
+                                const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[e + u])));
+                                const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[e + u + 1])));
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(sg[u], u0), __fmul_rn(sg[u + 1], u1));
+                                o[(e + u) >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                        }
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c_out) + (uint64_t)row * ldc + out0 + c;
+                        if (out0 + c + 32 <= F && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                        } else {
+                            for (int q = 0; q < 32; ++q)
+                                if (out0 + c + q < F) reinterpret_cast<uint16_t*>(dst)[q] = (uint16_t)(q & 1 ? o[q >> 1] >> 16 : o[q >> 1] & 0xFFFFu);
+                        }
+                    }
+                }
+            }
             if (EPI == EPI_ROPE) {
                 // A 256-column tile is two heads of 128.  Rotary pairs are (i, i + 64): the thread reads 32 columns of
                 // each half of a head, rounds both to bf16 as the unfused projection would have stored them, rotates with
@@ -401,7 +442,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
             }
 #pragma unroll 1
-            for (uint32_t c = 0; EPI != EPI_ROPE && c < w.width; c += 32) {
+            for (uint32_t c = 0; EPI != EPI_ROPE && EPI != EPI_SWIGLU && c < w.width; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
                 uint4 res[4];
@@ -580,7 +621,8 @@ static catena_status_t make_map2(CUtensorMap* map, const void* base, uint64_t ro
 // Enqueues the CTA-pair GEMM.  `err_dev` is the device error word shared with the single-CTA kernel.
 catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k, uint64_t ldc,
                                  int is_i8, int cta_limit, uint32_t* err_dev, void* const* peer_c, uint32_t n_peers, const void* residual,
-                                 const GemmRopeOut* rope) {
+                                 const GemmRopeOut* rope, int swiglu) {
+    if (swiglu && (is_i8 || n_peers || residual || rope || n % 256)) return fail(CATENA_E_BAD_ARG, "gemm: bad SwiGLU epilogue");
     if ((residual || rope) && (is_i8 || n_peers)) return fail(CATENA_E_BAD_ARG, "gemm: a residual / rotary epilogue goes with the plain bf16 kernel only");
     if (rope && (residual || n % 128 || !rope->table || !rope->q_out || !rope->k_cache || !rope->v_cache || !rope->seq ||
                  n != (uint64_t)(rope->hq + 2 * rope->hkv) * 128))
@@ -604,6 +646,7 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
                              uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*);
     KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, tc2::EPI_PEERS> : tc2::gemm_tc2_kernel<true, tc2::EPI_PLAIN>)
                             : (n_peers ? tc2::gemm_tc2_kernel<false, tc2::EPI_PEERS>
+                                       : swiglu ? tc2::gemm_tc2_kernel<false, tc2::EPI_SWIGLU>
                                        : (rope ? tc2::gemm_tc2_kernel<false, tc2::EPI_ROPE>
                                                : (residual ? tc2::gemm_tc2_kernel<false, tc2::EPI_RESIDUAL> : tc2::gemm_tc2_kernel<false, tc2::EPI_PLAIN>)));
     const int smem_bytes = tc2::smem_bytes(n_peers != 0);
@@ -615,7 +658,7 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     if (tiles < pairs) pairs = tiles;
     const uint64_t rem = tiles % pairs;
     // (the rotary epilogue needs whole heads in a unit: no cut along N)
-    const uint32_t split = rem == 0 || rope ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
+    const uint32_t split = rem == 0 || rope || swiglu ? 1u : (rem * 4 <= pairs ? 4u : (rem * 2 <= pairs ? 2u : 1u));
     const unsigned grid = (unsigned)(pairs * 2);
     cudaStream_t st = tls().stream;
     cudaLaunchConfig_t cfg = {};

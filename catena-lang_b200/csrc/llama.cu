@@ -833,6 +833,9 @@ static catena_status_t launch_linear_swiglu(const void* x, const void* w, void* 
                           (const __nv_bfloat16*)w, (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)act, (uint32_t)m, (uint32_t)(2 * ffn),
                           (uint32_t)k, (uint32_t)ffn);
     }
+    // the CTA-pair kernel applies the activation in its epilogue (gate and up rows of the same outputs side by side in one tile)
+    if (gemm_tc_fuses_residual(m) && ffn % 128 == 0 && k % 8 == 0 && !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)act) & 15))
+        return launch_gemm_tc_swiglu(x, w, act, m, ffn, k);
     CATENA_TRY(launch_linear(x, w, nullptr, gu, m, 2 * ffn, k));
     return launch_swiglu(gu, act, m, ffn);
 }

@@ -226,9 +226,10 @@ def test_linear_residual_in_the_gemm_epilogue_equals_gemm_then_add(orc, m, n, k)
         cb.free(mm)
 
 
-@pytest.mark.parametrize("m,ffn,k", [(4, 264, 512), (16, 512, 2048), (20, 256, 512)])
+@pytest.mark.parametrize("m,ffn,k", [(4, 264, 512), (16, 512, 2048), (20, 256, 512), (300, 256, 512), (700, 384, 256), (129, 200, 64)])
 def test_linear_swiglu_equals_two_steps(orc, m, ffn, k):
-    """The fused gate/up projection + SwiGLU (one launch for m <= 16) gives the bits of the two separate operators."""
+    """The fused gate/up projection + SwiGLU (one launch for m <= 16: skinny kernel; for m > 128 and ffn % 128 == 0: the
+    tcgen05 GEMM with the activation in its epilogue) gives the bits of the two separate operators."""
     rng = np.random.default_rng(8)
     x, w = bits(rng, (m, k)), bits(rng, (2 * ffn, k), 1.0 / math.sqrt(k))
     xm, wm, gm, am, bm = dev(x), dev(w), alloc(m * 2 * ffn * 2), alloc(m * ffn * 2), alloc(m * ffn * 2)
