@@ -30,6 +30,16 @@ class CatenaMem(C.Structure):
     _fields_ = [("data", C.c_void_p), ("len", C.c_uint64)]
 
 
+class Dim3(C.Structure):
+    """catena_dim3_t (codegen/prelude.rs:13-17)."""
+    _fields_ = [("x", C.c_uint32), ("y", C.c_uint32), ("z", C.c_uint32)]
+
+
+class LaunchParams(C.Structure):
+    """catena_launch_params_t {grid_dim, block_dim} (codegen/prelude.rs:23-26)."""
+    _fields_ = [("grid_dim", Dim3), ("block_dim", Dim3)]
+
+
 class LlamaBlockStruct(C.Structure):
     """catena_llama_block_t (include/catena_b200.h)."""
     _fields_ = [("hidden", C.c_uint64), ("n_heads", C.c_uint64), ("n_kv_heads", C.c_uint64), ("ffn", C.c_uint64),
@@ -107,6 +117,8 @@ def lib():
     proto("program_matmul_right_identity_2x2_via_mem", None, [mem, u64, u64, pm])
     proto("program_matmul_left_identity_2x2_via_mem", None, [mem, u64, u64, pm])
     proto("catena_b200_map_f32_s", st, [C.c_char_p, mem, pm])
+    proto("catena_b200_launch_len", u64, [LaunchParams])
+    proto("catena_b200_gpu_materialize_f32_s", st, [C.c_char_p, LaunchParams, mem, pm])
     for base in ["program_gemm_bf16_rc", "program_gemm_i8_rc"]:
         proto(base, None, [mem, mem, u64, u64, u64, pm])
         proto(base + "_s", st, [mem, mem, u64, u64, u64, pm])

@@ -184,6 +184,23 @@ catena_status_t catena_b200_map_f32_s(const char* op, catena_mem_t in, catena_me
     uint64_t n = f32_len(in);
     return with_output(n * 4, out, [&](void* p) { return launch_map_unary(id, (const float*)in.data, (float*)p, n); });
 }
+uint64_t catena_b200_launch_len(catena_launch_params_t p) {
+    return (uint64_t)p.grid_dim.x * p.grid_dim.y * p.grid_dim.z * p.block_dim.x * p.block_dim.y * p.block_dim.z;
+}
+catena_status_t catena_b200_gpu_materialize_f32_s(const char* op, catena_launch_params_t params, catena_mem_t in, catena_mem_t* out) {
+    if (out) { out->data = nullptr; out->len = 0; }
+    int id = map_op_from_name(op);
+    if (id < 0) return fail(CATENA_E_BAD_ARG, "gpu.materialize: unknown scalar program");
+    // the product of six u32 dimensions can pass 2^64: refuse instead of wrapping
+    const long double exact = (long double)params.grid_dim.x * params.grid_dim.y * params.grid_dim.z * (long double)params.block_dim.x *
+                              params.block_dim.y * params.block_dim.z;
+    if (exact > 9.0e18L) return fail(CATENA_E_TOO_LARGE, "gpu.materialize: launch length beyond 2^63");
+    const uint64_t n = catena_b200_launch_len(params);
+    if (n == 0) return with_output(0, out, [&](void*) { return CATENA_OK; });
+    CATENA_TRY(check_mem(in, "gpu.materialize: null environment buffer"));
+    if (f32_len(in) < n) return fail(CATENA_E_ASSERT, "gpu.materialize: environment buffer shorter than the launch length");
+    return with_output(n * 4, out, [&](void* p) { return launch_map_unary(id, (const float*)in.data, (float*)p, n); });
+}
 catena_status_t catena_b200_map_f32_into(const char* op, const void* in, void* out, uint64_t n) {
     int id = map_op_from_name(op);
     if (id < 0) return fail(CATENA_E_BAD_ARG, "map: unknown scalar program");

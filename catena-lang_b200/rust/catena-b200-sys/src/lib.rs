@@ -84,6 +84,28 @@ extern "C" {
                                     workspace_bytes: u64) -> catena_status_t;
     pub fn catena_b200_linear_bf16_into(x: *const c_void, w: *const c_void, residual: *const c_void, y: *mut c_void, m: u64,
                                         n: u64, k: u64) -> catena_status_t;
+
+    // gpu.materialize (stdlib/gpu.hex:39-49) over the prebuilt scalar programs
+    pub fn catena_b200_launch_len(params: catena_launch_params_t) -> u64;
+    pub fn catena_b200_gpu_materialize_f32_s(op: *const c_char, params: catena_launch_params_t, input: catena_mem_t,
+                                             out: *mut catena_mem_t) -> catena_status_t;
+}
+
+/// catena_dim3_t / catena_launch_params_t of the reference's prelude (src/codegen/prelude.rs:13-26).
+#[repr(C)]
+#[derive(Clone, Copy)]
+#[allow(non_camel_case_types)]
+pub struct catena_dim3_t {
+    pub x: u32,
+    pub y: u32,
+    pub z: u32,
+}
+#[repr(C)]
+#[derive(Clone, Copy)]
+#[allow(non_camel_case_types)]
+pub struct catena_launch_params_t {
+    pub grid_dim: catena_dim3_t,
+    pub block_dim: catena_dim3_t,
 }
 
 /// catena_llama_block_t of include/catena_b200.h.

@@ -150,6 +150,18 @@ void program_matmul_left_identity_2x2_via_mem(catena_mem_t a, uint64_t n, uint64
  * `op` is the hexpr name, e.g. "nn.silu", "math.exp-approx". */
 catena_status_t catena_b200_map_f32_s(const char* op, catena_mem_t in, catena_mem_t* out);
 
+/* `gpu.materialize` (catena-lang/stdlib/gpu.hex:39-49, renderer catena-lang/src/codegen/gpu.rs:998-1065): the same map
+ * with explicit launch parameters.  The types are the reference's (catena-lang/src/codegen/prelude.rs:13-26); the
+ * buffer it materialises has catena_launch_len(params) elements (prelude.rs:59-62), element i being the kernel's
+ * value for thread_id = i.  Here the kernel is one of the prebuilt scalar programs applied to the environment buffer
+ * `in` at thread_id (arbitrary kernels would need the producer JIT, which this backend does not have); the launch
+ * parameters fix only the length — the geometry that runs is the library's, and never enters the result.
+ * CATENA_E_ASSERT when `in` holds fewer than catena_launch_len(params) floats. */
+typedef struct { uint32_t x, y, z; } catena_dim3_t;
+typedef struct { catena_dim3_t grid_dim, block_dim; } catena_launch_params_t;
+uint64_t catena_b200_launch_len(catena_launch_params_t params);
+catena_status_t catena_b200_gpu_materialize_f32_s(const char* op, catena_launch_params_t params, catena_mem_t in, catena_mem_t* out);
+
 /* ---- programs with no counterpart in the reference (it has no bf16, int8 or attention);
  *      same calling convention; semantics composed from the reference's rules -------------- */
 /* C[M,N] = A[M,K] * B, A row-major bf16, B column-major bf16 (stored [N,K]); fp32 accumulation in

@@ -106,6 +106,30 @@ def test_map_bit_exact(rt, orc, name):
     assert np.array_equal(u32(got), u32(want))
 
 
+def test_gpu_materialize_with_explicit_launch_parameters(rt, orc):
+    """gpu.materialize (stdlib/gpu.hex:39-49): the buffer has catena_launch_len(params) elements, element i the kernel's
+    value for thread_id = i; the geometry given does not enter the result."""
+    x = np.random.default_rng(5).uniform(-8, 8, 100).astype(np.float32)
+    m = cb.upload(x)
+    want = orc.map_unary("nn.silu", x, threads=1)
+    for grid, block in (((3, 2, 1), (5, 1, 2)), ((1, 1, 1), (60, 1, 1)), ((60, 1, 1), (1, 1, 1))):
+        params = cb.LaunchParams(cb.Dim3(*grid), cb.Dim3(*block))
+        assert cb.lib().catena_b200_launch_len(params) == 60
+        out = cb.CatenaMem()
+        cb.check(cb.lib().catena_b200_gpu_materialize_f32_s(b"nn.silu", params, m, C.byref(out)))
+        assert out.len == 240 and np.array_equal(u32(cb.download(out, np.float32)), u32(want[:60]))
+        cb.free(out)
+    out = cb.CatenaMem()
+    too_long = cb.LaunchParams(cb.Dim3(101, 1, 1), cb.Dim3(1, 1, 1))
+    assert cb.lib().catena_b200_gpu_materialize_f32_s(b"nn.silu", too_long, m, C.byref(out)) == cb.E_ASSERT
+    huge = cb.LaunchParams(cb.Dim3(2 ** 32 - 1, 2 ** 32 - 1, 2 ** 32 - 1), cb.Dim3(1024, 1, 1))
+    assert cb.lib().catena_b200_gpu_materialize_f32_s(b"nn.silu", huge, m, C.byref(out)) == cb.E_TOO_LARGE
+    empty = cb.LaunchParams(cb.Dim3(0, 1, 1), cb.Dim3(32, 1, 1))
+    cb.check(cb.lib().catena_b200_gpu_materialize_f32_s(b"nn.silu", empty, m, C.byref(out)))
+    assert out.len == 0 and not out.data
+    cb.free(m)
+
+
 # ---------------------------------------------------------------- folds
 def test_fold_reference_vectors(rt):
     # tests/cases/reducec.rs:50-90
