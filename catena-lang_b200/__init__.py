@@ -19,7 +19,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# CATENA_B200_LIB overrides the location of the kernel library (same role as in INTEGRATION.md)
+# CATENA_B200_LIB overrides the location of the kernel library (for hosts that install it elsewhere)
 LIB_PATH = os.environ.get("CATENA_B200_LIB") or os.path.join(_HERE, "libcatena_b200.so")
 
 OK, E_ASSERT, E_CUDA, E_NO_DEVICE, E_BAD_ARG, E_TIMEOUT, E_TOO_LARGE, E_UNSUPPORTED = range(8)
@@ -154,6 +154,8 @@ def lib():
     proto("catena_b200_debug_attn_last_launch", None, [C.POINTER(C.c_uint32)])
     proto("catena_b200_debug_set_prefill_tc", None, [C.c_int])
     proto("catena_b200_debug_rcp_check", C.c_int, [C.POINTER(C.c_uint64)])
+    proto("catena_b200_debug_set_wait_limit_ns", None, [u64])
+    proto("catena_b200_debug_stall_next", None, [C.c_int, C.c_uint32])
     _lib = L
     return L
 

@@ -545,7 +545,7 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     if (((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)q & 3)) return fail(CATENA_E_BAD_ARG, "attn_decode: alignment");
     if (kv_len > 0x7FFFFFFFull || kv_cap > 0x7FFFFFFFull || units > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "attn_decode: size");
     const uint32_t G = (uint32_t)(hq / hkv);
-    int dev = tls().device & 15;
+    int dev = tls().device;
     if (!g_attn_err_dev[dev]) {
         CATENA_CUDA(cudaMalloc(&g_attn_err_dev[dev], sizeof(uint32_t)));
         CATENA_CUDA(cudaMemset(g_attn_err_dev[dev], 0, sizeof(uint32_t)));
@@ -599,7 +599,7 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
 
 catena_status_t attn_check_errors() {
     CATENA_TRY(ensure_device());
-    int dev = tls().device & 15;
+    int dev = tls().device;
     if (!g_attn_err_dev[dev]) return CATENA_OK;
     cudaStream_t st = tls().stream;
     CATENA_CUDA(cudaMemcpyAsync(g_attn_err_host[dev], g_attn_err_dev[dev], sizeof(uint32_t), cudaMemcpyDeviceToHost, st));

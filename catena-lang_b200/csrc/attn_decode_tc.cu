@@ -66,7 +66,6 @@ constexpr int kPSlots = 2;                   // probability operands of single t
 constexpr int kPTileBytes = 2 * 2048;        // per 64-position atom 16 rows x 128 B: rows 0..7 = bf16 hi part of p per
                                              //   head, rows 8..15 = lo part
 constexpr int kOpsBytes = 2 * kQBytes + kPSlots * kPTileBytes;   // operand bytes per pipe (Q double-buffered)
-constexpr uint64_t kWaitNs = 1000000000ull;
 // a waiting thread may be suspended by the hardware for up to this long (it is woken when the phase completes)
 constexpr uint32_t kSuspendHintNs = 20000;
 
@@ -84,6 +83,7 @@ struct __align__(16) Control {
     float gmax[kMaxG];
 };
 struct __align__(16) Common {
+    uint64_t wait_ns;              // limit of every bounded wait of this launch
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -117,7 +117,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Common
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255u) == 0) {
             if (com->abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitNs) {
+            if (globaltimer_ns() - t0 > com->wait_ns) {
                 com->abort_flag = 1;
                 atomicCAS(err, 0u, 2u);
                 return false;
@@ -251,7 +251,8 @@ struct Exchange {
 __global__ void __launch_bounds__(kThreads, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ o, uint32_t L, uint32_t G,
-                      uint32_t unit0, uint32_t items, uint32_t chunk, float scale, Exchange ex, uint32_t* err) {
+                      uint32_t unit0, uint32_t items, uint32_t chunk, float scale, Exchange ex, uint32_t* err, uint64_t wait_ns,
+                      uint32_t stall) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -288,7 +289,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         }
         mbar_init(&c->fin_ready, kConsumers);
         mbar_init(&c->fin_done, 1);
-        if (tid == 0) com->abort_flag = 0;
+        if (tid == 0) {
+            com->abort_flag = 0;
+            com->wait_ns = wait_ns;
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // operand buffers start as zeros: head rows >= G of Q and P are never written
@@ -338,7 +342,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         if ((seen & 7u) == 0) break;
                         if ((++spins & 63u) == 0) {
                             if (com->abort_flag) { ok = 0; break; }
-                            if (globaltimer_ns() - t0 > kWaitNs) {
+                            if (globaltimer_ns() - t0 > com->wait_ns) {
                                 com->abort_flag = 1;
                                 atomicCAS(err, 0u, 4u);
                                 ok = 0;
@@ -524,7 +528,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                     for (int h = 0; h < kMaxG; ++h) ctl->warp_max[cw][h] = m[h];
                 }
                 consumer_sync(pipe);
-                if (ct < G) {
+                // (test hook `stall`: item 0 never publishes its maxima, so the polls of its unit's pipes run out)
+                if (ct < G && !(stall != 0 && w == 0)) {
                     float mm = fmaxf(fmaxf(ctl->warp_max[0][ct], ctl->warp_max[1][ct]), fmaxf(ctl->warp_max[2][ct], ctl->warp_max[3][ct]));
                     st_relaxed_u64(ex.maxima + (size_t)w * 8 + ct, ((uint64_t)ex.epoch << 32) | (uint64_t)__float_as_uint(mm));
                 }
@@ -573,7 +578,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                             while ((uint32_t)((val = ld_relaxed_u64(slots + r * 8 + h)) >> 32) != ex.epoch) {
                                 if ((++spins & 63u) == 0) {
                                     if (com->abort_flag) break;
-                                    if (globaltimer_ns() - t0 > kWaitNs) {
+                                    if (globaltimer_ns() - t0 > com->wait_ns) {
                                         com->abort_flag = 1;
                                         atomicCAS(err, 0u, 3u);
                                         break;
@@ -745,7 +750,7 @@ static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 // After a launch that reported an expired wait: its tickets may be left part-way, so the area is cleared (stream-ordered).
 void attn_tc_reset_exchange() {
-    AttnExchange& xa = g_attn_exchange[tls().device & 15];
+    AttnExchange& xa = g_attn_exchange[tls().device];
     if (xa.base) cudaMemsetAsync(xa.base, 0, xa.bytes, tls().stream);
     if (xa.tickets) cudaMemsetAsync(xa.tickets, 0, xa.ticket_units * sizeof(uint32_t), tls().stream);
     xa.epoch = 0;
@@ -757,7 +762,7 @@ catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void
                                        uint32_t* err_dev) {
     const uint32_t chunk = chunk_for2(kv_len);
     const size_t smem = attn2_smem_bytes();
-    const int dev = tls().device & 15;
+    const int dev = tls().device;
     const uint64_t n_units = unit1 - unit0, items = n_units * attn2::kSplits;
     if (items > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "attn_decode: too many chunk items");
     CUtensorMap map_k, map_v;
@@ -832,7 +837,8 @@ catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void
     g_attn_last_launch[2] = (uint32_t)ctas; g_attn_last_launch[3] = (uint32_t)smem;
     float scale = 1.0f / sqrtf((float)attn2::kD);
     CATENA_CUDA(cudaLaunchKernelEx(&cfg, attn2::attn_decode_tc_kernel, map_k, map_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)o,
-                                   (uint32_t)kv_len, G, (uint32_t)unit0, (uint32_t)items, chunk, scale, ex, err_dev));
+                                   (uint32_t)kv_len, G, (uint32_t)unit0, (uint32_t)items, chunk, scale, ex, err_dev,
+                                   debug_wait_limit_ns(), debug_take_stall(2)));
     count_launch();
     return CATENA_OK;
 }

@@ -587,7 +587,7 @@ bool attn_prefill_tc_supports(const void* q, const void* k_cache, const void* v_
 
 // Reports (and clears) an expired wait of an earlier launch; synchronises the stream.
 catena_status_t attn_prefill_tc_check_errors() {
-    const int dev = tls().device & 15;
+    const int dev = tls().device;
     if (!g_attn3_err_dev[dev]) return CATENA_OK;
     uint32_t h = 0;
     CATENA_CUDA(cudaMemcpyAsync(&h, g_attn3_err_dev[dev], sizeof(h), cudaMemcpyDeviceToHost, tls().stream));
@@ -604,7 +604,7 @@ catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, cons
                                         uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t cap) {
     EncodeTiledFnA3 fn = attn3_encode_fn();
     if (!fn) return fail(CATENA_E_CUDA, "cuTensorMapEncodeTiled is unavailable");
-    const int dev = tls().device & 15;
+    const int dev = tls().device;
     if (!g_attn3_err_dev[dev]) {
         CATENA_CUDA(cudaMalloc(&g_attn3_err_dev[dev], sizeof(uint32_t)));
         CATENA_CUDA(cudaMemset(g_attn3_err_dev[dev], 0, sizeof(uint32_t)));

@@ -13,6 +13,9 @@ namespace catena {
 // Per-host-thread library state.  The generated code of the reference uses the process-global
 // current device and the default stream (catena-lang/doc/CODEGEN.md:164-166); here both are
 // explicit so one process per GPU (or one thread per GPU) can drive the library.
+// Per-device tables (pools, scratch, error words) hold this many devices; catena_b200_init refuses larger indices.
+constexpr int kMaxDevices = 16;
+
 struct ThreadState {
     int device = -1;           // -1: not initialised
     cudaStream_t stream = 0;   // legacy default stream unless set
@@ -32,6 +35,12 @@ catena_status_t fail(catena_status_t s, const char* what);
 catena_status_t fail_cuda(cudaError_t e, const char* what);
 
 void count_launch(uint64_t n = 1);
+
+// Test knobs of the bounded device-side waits (process-wide).  The limit applies to tcgen05 GEMM and decode-attention
+// launches made after it is set; a stall request is taken (and cleared) by the next launch of that kernel family:
+// 1 = CTA-pair GEMM (value = k-block + 1 at which the TMA producers stop), 2 = tcgen05 decode attention.
+uint64_t debug_wait_limit_ns();
+uint32_t debug_take_stall(int family);
 
 // Pool allocator (mem.cu).
 catena_status_t pool_alloc(uint64_t bytes, void** out);

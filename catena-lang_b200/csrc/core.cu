@@ -16,7 +16,15 @@ namespace catena {
 static thread_local ThreadState g_tls;
 static std::atomic<uint64_t> g_launches{0};
 
+static std::atomic<uint64_t> g_wait_limit_ns{1000000000ull};
+static std::atomic<uint32_t> g_stall[3] = {{0}, {0}, {0}};
+
 ThreadState& tls() { return g_tls; }
+uint64_t debug_wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+uint32_t debug_take_stall(int family) {
+    if (family < 1 || family > 2) return 0;
+    return g_stall[family].exchange(0u, std::memory_order_relaxed);
+}
 void count_launch(uint64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 catena_status_t fail(catena_status_t s, const char* what) {
@@ -42,6 +50,7 @@ static catena_status_t bind_device(int device) {
         return fail(CATENA_E_NO_DEVICE, "no CUDA device is visible (this library has no CPU path)");
     }
     if (device < 0 || device >= count) return fail(CATENA_E_BAD_ARG, "device index out of range");
+    if (device >= kMaxDevices) return fail(CATENA_E_UNSUPPORTED, "device index beyond the 16 devices the per-device tables hold");
     CATENA_CUDA(cudaSetDevice(device));
     cudaDeviceProp prop;
     CATENA_CUDA(cudaGetDeviceProperties(&prop, device));
@@ -77,12 +86,24 @@ catena_status_t finish(const char* what) {
 // allocator sits on the hot path.  Blocks are rounded up to a size class (256 B granules up to
 // 1 MiB, then 2 MiB granules), cached per device on free and handed back without touching the
 // driver; cudaMalloc/cudaFree only run on a miss or on catena_b200_mem_trim.
+//
+// Reuse is ordered after the work that may still read or write a freed block.  In blocking mode every
+// entry point has synchronised its stream before it returns, so a block is idle when it is freed.  In
+// non-blocking mode pool_free records an event on the freeing thread's stream; pool_alloc on the same
+// stream needs nothing more (stream order), pool_alloc on another stream makes that stream wait for the
+// event first.  The pool is shared by all host threads of a device.
+struct FreeBlock {
+    void* ptr;
+    cudaStream_t stream;   // stream the block was freed on
+    cudaEvent_t idle;      // nullptr: nothing was in flight when the block was freed
+};
 struct Pool {
     std::mutex mu;
-    std::multimap<uint64_t, void*> free_blocks;       // size class -> block
+    std::multimap<uint64_t, FreeBlock> free_blocks;   // size class -> block
     std::unordered_map<void*, uint64_t> live;         // block -> size class
+    std::vector<cudaEvent_t> spare_events;
 };
-static Pool g_pools[16];
+static Pool g_pools[kMaxDevices];
 
 static uint64_t size_class(uint64_t bytes) {
     if (bytes <= (1ull << 20)) return (bytes + 255) & ~255ull;
@@ -93,15 +114,25 @@ catena_status_t pool_alloc(uint64_t bytes, void** out) {
     *out = nullptr;
     if (bytes == 0) return CATENA_OK;
     CATENA_TRY(ensure_device());
-    Pool& p = g_pools[g_tls.device & 15];
+    Pool& p = g_pools[g_tls.device];
     uint64_t cls = size_class(bytes);
     {
-        std::lock_guard<std::mutex> lk(p.mu);
+        std::unique_lock<std::mutex> lk(p.mu);
         auto it = p.free_blocks.find(cls);
         if (it != p.free_blocks.end()) {
-            *out = it->second;
+            FreeBlock fb = it->second;
             p.free_blocks.erase(it);
-            p.live[*out] = cls;
+            p.live[fb.ptr] = cls;
+            lk.unlock();
+            if (fb.idle) {
+                cudaError_t e = cudaSuccess;
+                if (fb.stream != g_tls.stream) e = cudaStreamWaitEvent(g_tls.stream, fb.idle, 0);
+                lk.lock();
+                p.spare_events.push_back(fb.idle);
+                lk.unlock();
+                if (e != cudaSuccess) return fail_cuda(e, "cudaStreamWaitEvent (pool reuse)");
+            }
+            *out = fb.ptr;
             return CATENA_OK;
         }
     }
@@ -122,12 +153,34 @@ catena_status_t pool_alloc(uint64_t bytes, void** out) {
 catena_status_t pool_free(void* ptr) {
     if (!ptr) return CATENA_OK;
     CATENA_TRY(ensure_device());
-    Pool& p = g_pools[g_tls.device & 15];
+    Pool& p = g_pools[g_tls.device];
+    uint64_t cls = 0;
+    cudaEvent_t ev = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(p.mu);
+        auto it = p.live.find(ptr);
+        if (it == p.live.end()) return fail(CATENA_E_BAD_ARG, "mem_free: pointer was not allocated by this library");
+        cls = it->second;
+        p.live.erase(it);
+        if (!g_tls.blocking && !p.spare_events.empty()) {
+            ev = p.spare_events.back();
+            p.spare_events.pop_back();
+        }
+    }
+    if (!g_tls.blocking) {
+        // kernels that use the block may still be queued on this thread's stream
+        cudaError_t e = ev ? cudaSuccess : cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventRecord(ev, g_tls.stream);
+        if (e != cudaSuccess) {
+            // no event: fall back to waiting here, so the block is idle when it goes back on the list
+            (void)cudaGetLastError();
+            if (ev) cudaEventDestroy(ev);
+            ev = nullptr;
+            cudaStreamSynchronize(g_tls.stream);
+        }
+    }
     std::lock_guard<std::mutex> lk(p.mu);
-    auto it = p.live.find(ptr);
-    if (it == p.live.end()) return fail(CATENA_E_BAD_ARG, "mem_free: pointer was not allocated by this library");
-    p.free_blocks.emplace(it->second, ptr);
-    p.live.erase(it);
+    p.free_blocks.emplace(cls, FreeBlock{ptr, g_tls.stream, ev});
     return CATENA_OK;
 }
 
@@ -149,6 +202,12 @@ int catena_b200_device_count(void) {
 }
 
 catena_status_t catena_b200_set_stream(void* stream) {
+    // The thread's scratch (attention exchange area, rotary table, error words) is ordered by its stream: work still
+    // queued on the old stream must be done before the same scratch is used from the new one.
+    if ((cudaStream_t)stream != tls().stream && tls().device >= 0 && !tls().blocking) {
+        CATENA_TRY(ensure_device());
+        CATENA_CUDA(cudaStreamSynchronize(tls().stream));
+    }
     tls().stream = (cudaStream_t)stream;
     return CATENA_OK;
 }
@@ -180,6 +239,13 @@ const char* catena_b200_status_string(catena_status_t s) {
 
 const char* catena_b200_version(void) { return "catena_b200 0.1 (sm_100a)"; }
 uint64_t catena_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void catena_b200_debug_set_wait_limit_ns(uint64_t ns) {
+    g_wait_limit_ns.store(ns ? ns : 1000000000ull, std::memory_order_relaxed);
+}
+void catena_b200_debug_stall_next(int family, uint32_t value) {
+    if (family >= 1 && family <= 2) g_stall[family].store(value, std::memory_order_relaxed);
+}
 
 catena_status_t catena_b200_mem_alloc(uint64_t bytes, catena_mem_t* out) {
     if (!out) return fail(CATENA_E_BAD_ARG, "mem_alloc: null out");
@@ -226,15 +292,21 @@ catena_status_t catena_b200_mem_download(catena_mem_t mem, void* host, uint64_t 
 
 catena_status_t catena_b200_mem_trim(void) {
     CATENA_TRY(ensure_device());
-    Pool& p = g_pools[tls().device & 15];
-    std::vector<void*> blocks;
+    Pool& p = g_pools[tls().device];
+    std::vector<FreeBlock> blocks;
+    std::vector<cudaEvent_t> events;
     {
         std::lock_guard<std::mutex> lk(p.mu);
         for (auto& kv : p.free_blocks) blocks.push_back(kv.second);
         p.free_blocks.clear();
+        events.swap(p.spare_events);
     }
     if (!blocks.empty()) cudaDeviceSynchronize();
-    for (void* b : blocks) cudaFree(b);
+    for (FreeBlock& b : blocks) {
+        cudaFree(b.ptr);
+        if (b.idle) cudaEventDestroy(b.idle);
+    }
+    for (cudaEvent_t ev : events) cudaEventDestroy(ev);
     return CATENA_OK;
 }
 
@@ -244,7 +316,7 @@ catena_status_t catena_b200_ipc_export(catena_mem_t mem, void* handle64, uint64_
     // IPC handles name whole allocations.  Blocks of the pool are whole cudaMalloc allocations,
     // so a `mem` returned by catena_b200_mem_alloc starts at offset 0 of the exported base.
     {
-        Pool& p = g_pools[tls().device & 15];
+        Pool& p = g_pools[tls().device];
         std::lock_guard<std::mutex> lk(p.mu);
         if (p.live.find(mem.data) == p.live.end())
             return fail(CATENA_E_BAD_ARG, "ipc_export: not the start of an allocation of this library");

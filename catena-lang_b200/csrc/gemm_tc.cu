@@ -433,7 +433,7 @@ struct ErrWord {
 static thread_local ErrWord g_err[16];
 
 static catena_status_t err_word(ErrWord** out) {
-    ErrWord& e = g_err[tls().device & 15];
+    ErrWord& e = g_err[tls().device];
     if (!e.dev) {
         CATENA_CUDA(cudaMalloc(&e.dev, sizeof(uint32_t)));
         CATENA_CUDA(cudaMemset(e.dev, 0, sizeof(uint32_t)));

@@ -49,7 +49,6 @@ constexpr int TMEM_COLS = 512;
 #define CATENA_GEMM_GROUP_M 8
 #endif
 constexpr int GROUP_M = CATENA_GEMM_GROUP_M;   // rasterisation in pair-tile rows (8 x 256 rows)
-constexpr uint64_t WAIT_NS = 1000000000ull;
 constexpr int kMaxPeers = 7;       // other GPUs of an 8-GPU box
 
 // Where the epilogue stores each output tile besides this GPU's C: peer-mapped pointers (CUDA IPC / P2P) to the same
@@ -75,6 +74,7 @@ struct __align__(8) Control {
     uint64_t empty[MAX_STAGES];      // one per CTA, signalled by the leader's commit (multicast)
     uint64_t tmem_full[2];       // one per CTA, signalled by the leader's commit (multicast)
     uint64_t tmem_empty[2];      // used in the leader CTA: 2 x 128 epilogue threads arrive
+    uint64_t wait_ns;            // limit of every bounded wait of this launch
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -130,7 +130,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, Contro
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255u) == 0) {
             if (ctl->abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_NS) {
+            if (globaltimer_ns() - t0 > ctl->wait_ns) {
                 ctl->abort_flag = 1;
                 atomicCAS(err, 0u, code);
                 return false;
@@ -234,7 +234,8 @@ template <bool IS_I8, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b128,
                 const __grid_constant__ CUtensorMap map_b64, const __grid_constant__ CUtensorMap map_b32,
-                void* __restrict__ c_out, PeerOut peers, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err) {
+                void* __restrict__ c_out, PeerOut peers, uint32_t M, uint32_t N, uint32_t K, uint64_t ldc, uint32_t split, uint32_t* err,
+                uint64_t wait_ns, uint32_t stall_kb) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr bool HAS_PEERS = EPI == EPI_PEERS;
@@ -268,6 +269,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(&ctl->tmem_empty[b], 2 * EPI_THREADS);
         }
         ctl->abort_flag = 0;
+        ctl->wait_ns = wait_ns;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // both CTAs' barriers exist before anything in the pair signals them
@@ -298,6 +300,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int a_row = (int)(w.m_blk * 2 * BM + rank * BM);
                 const int b_row = EPI == EPI_SWIGLU ? (int)(w.col0 / 2 + rank * (N / 2)) : (int)(w.col0 + rank * half);
                 for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                    // test hook: the producers of both CTAs stop before k-block stall_kb - 1 of their first tile, so the
+                    // issuer's wait for that stage runs out and the whole pair takes the give-up path
+                    if (stall_kb != 0 && it == 0 && kb + 1 == stall_kb) { ok = false; break; }
                     if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, ctl, err, 1u)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(&ctl->full[stage], bytes_pair);
                     const uint32_t bar = mapa(smem_u32(&ctl->full[stage]), 0);
@@ -643,7 +648,7 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     CATENA_TRY(make_map2(&map_b64, b, n, k, eb, 64));
     CATENA_TRY(make_map2(&map_b32, b, n, k, eb, 32));
     typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, void*, tc2::PeerOut, uint32_t,
-                             uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*);
+                             uint32_t, uint32_t, uint64_t, uint32_t, uint32_t*, uint64_t, uint32_t);
     KernelFn kernel = is_i8 ? (n_peers ? tc2::gemm_tc2_kernel<true, tc2::EPI_PEERS> : tc2::gemm_tc2_kernel<true, tc2::EPI_PLAIN>)
                             : (n_peers ? tc2::gemm_tc2_kernel<false, tc2::EPI_PEERS>
                                        : swiglu ? tc2::gemm_tc2_kernel<false, tc2::EPI_SWIGLU>
@@ -673,7 +678,7 @@ catena_status_t enqueue_gemm_tc2(const void* a, const void* b, void* c, uint64_t
     cfg.attrs = at;
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b128, map_b64, map_b32, c, peers, (uint32_t)m, (uint32_t)n, (uint32_t)k, ldc,
-                                       split, err_dev);
+                                       split, err_dev, debug_wait_limit_ns(), debug_take_stall(1));
     count_launch();
     if (e != cudaSuccess) return fail_cuda(e, "gemm_tc2 launch");
     return CATENA_OK;

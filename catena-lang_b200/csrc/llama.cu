@@ -625,7 +625,7 @@ static thread_local RopeTable g_rope[16];
 static thread_local uint32_t* g_embed_bad[16] = {nullptr};
 
 static catena_status_t rope_table(float base, const float** out) {
-    RopeTable& t = g_rope[tls().device & 15];
+    RopeTable& t = g_rope[tls().device];
     const uint32_t bits = cmath::to_bits(base);
     if (!t.dev) CATENA_CUDA(cudaMalloc(&t.dev, 64 * sizeof(float)));
     if (t.base_bits != bits) {
@@ -645,7 +645,7 @@ static catena_status_t rope_table(float base, const float** out) {
 static catena_status_t launch_embed(const void* table, const int32_t* ids, void* out, uint64_t tokens, uint64_t hidden, uint64_t vocab) {
     if (hidden % 8) return fail(CATENA_E_BAD_ARG, "embed: hidden must be a multiple of 8");
     if (!tokens) return CATENA_OK;
-    uint32_t*& bad = g_embed_bad[tls().device & 15];
+    uint32_t*& bad = g_embed_bad[tls().device];
     if (!bad) {
         CATENA_CUDA(cudaMalloc(&bad, sizeof(uint32_t)));
         CATENA_CUDA(cudaMemset(bad, 0, sizeof(uint32_t)));
@@ -655,7 +655,7 @@ static catena_status_t launch_embed(const void* table, const int32_t* ids, void*
 }
 // reports (and clears) an out-of-range token id seen by an earlier embedding launch; synchronises the stream
 static catena_status_t embed_check() {
-    uint32_t*& bad = g_embed_bad[tls().device & 15];
+    uint32_t*& bad = g_embed_bad[tls().device];
     if (!bad) return CATENA_OK;
     uint32_t h = 0;
     CATENA_CUDA(cudaMemcpyAsync(&h, bad, sizeof(h), cudaMemcpyDeviceToHost, tls().stream));
@@ -684,7 +684,7 @@ static catena_status_t launch_embed_rmsnorm(const void* table, const int32_t* id
                                             uint64_t vocab) {
     if (hidden % 8) return fail(CATENA_E_BAD_ARG, "embed: hidden must be a multiple of 8");
     if (!tokens) return CATENA_OK;
-    uint32_t*& bad = g_embed_bad[tls().device & 15];
+    uint32_t*& bad = g_embed_bad[tls().device];
     if (!bad) {
         CATENA_CUDA(cudaMalloc(&bad, sizeof(uint32_t)));
         CATENA_CUDA(cudaMemset(bad, 0, sizeof(uint32_t)));
@@ -694,7 +694,7 @@ static catena_status_t launch_embed_rmsnorm(const void* table, const int32_t* id
 }
 // enqueues the (cos, sin) table of positions pos0 .. pos0 + seq - 1 into the thread's buffer
 static catena_status_t launch_rope_angles(const float* inv, uint64_t seq, uint64_t pos0, const float2** table) {
-    RopeAngles& ra = g_rope_angles[tls().device & 15];
+    RopeAngles& ra = g_rope_angles[tls().device];
     if (ra.positions < seq) {
         if (ra.dev) {
             CATENA_CUDA(cudaStreamSynchronize(tls().stream));

@@ -362,7 +362,7 @@ catena_status_t launch_map_unary(int op, const float* in, float* out, uint64_t n
 }
 
 // Enqueues the fold of `in[0..n)` into the device scalar `d_out`.  `d_shift` feeds F_EXPSUM.
-// Scratch for the tree comes from the pool and is released in stream order.
+// Scratch for the tree comes from the pool; pool_free orders its reuse after the kernels queued here (core.cu).
 template <int KIND>
 static catena_status_t enqueue_fold(const float* in, uint64_t n, const float* d_shift, float* d_out) {
     cudaStream_t st = tls().stream;
@@ -545,7 +545,7 @@ catena_status_t sum_f32_noalloc(const float* in, uint64_t n, float* d_out) {
     if (!d_out || (n != 0 && !in)) return fail(CATENA_E_BAD_ARG, "sum_f32_noalloc: null pointer");
     if (n > kNoAllocMaxElems)
         return fail(CATENA_E_TOO_LARGE, "sum_f32_noalloc: more than 2^30 elements (fixed scratch array)");
-    const int dev = tls().device & 15;
+    const int dev = tls().device;
     if (!g_sum_scratch_dev[dev]) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, g_sum_scratch);

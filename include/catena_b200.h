@@ -302,6 +302,16 @@ void catena_b200_debug_attn_last_launch(uint32_t out[4]);
  * [0.5, 2^100); this compares that sequence with the IEEE reciprocal for EVERY float of the range on the device:
  * out[0] = values compared, out[1] = mismatches (must be 0).  No counterpart in the reference. */
 catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]);
+/* test hooks for the give-up path of the bounded device-side waits (catena-lang/src/codegen/prelude.rs:38-55 traps
+ * instead; here a wait that runs out makes the kernel drain its copies, free its tensor memory and return, and the host
+ * reports CATENA_E_TIMEOUT).  set_wait_limit_ns: limit of every wait in the tcgen05 GEMM (CTA-pair kernel) and the
+ * tcgen05 decode attention launched from now on (0 = the default, one second).  stall_next: the NEXT launch of that
+ * family leaves one hand-over out on purpose — family 1 (CTA-pair GEMM): the TMA producers stop before k-block
+ * `value - 1` of their first tile; family 2 (tcgen05 decode attention): item 0 never publishes its chunk maxima
+ * (`value` non-zero).  Nothing faults or spins without bound: the waiting roles give up after the limit.  The output of
+ * such a launch is undefined; the library stays usable.  No counterpart in the reference. */
+void catena_b200_debug_set_wait_limit_ns(uint64_t ns);
+void catena_b200_debug_stall_next(int family, uint32_t value);
 /* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry */
 catena_status_t catena_b200_check_device_errors(void);
 

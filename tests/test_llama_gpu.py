@@ -263,8 +263,12 @@ def test_block_prefill_then_decode(orc, n_heads, n_kv_heads):
     try:
         got = blk.prefill(ids, S)
         want = orc.llama_block(cfg, weights, ids, B, S, 0, kc, vc, threads=orc.max_threads())
-        # a chain of nine rounded stages: a few bf16 ulps against the sequential-fold oracle
-        close(got, want, rel=2.0 ** -5, floor=2e-2)
+        # A chain of nine rounded stages against the sequential-fold oracle.  The output is the residual stream (values up
+        # to about 5, bf16 ulp 2^-6 .. 2^-5 there) plus a small addend, so its error is an ulp of the OUTPUT plus what an
+        # ulp of the residual leaves behind where the two nearly cancel: measured worst |got - want| - 2^-7 |want| over
+        # prefill and decode steps 1.53e-2 (one ulp of a residual in [2, 4)); the floor is twice that.  The operator
+        # tests above (one ulp each) and the fused-equals-separate bit tests carry the weight; this one guards the wiring.
+        close(got, want, rel=2.0 ** -7, floor=3.1e-2)
         gk, gv = blk.caches()
         close(gk[:, :, :S], kc[:, :, :S], rel=2.0 ** -6, floor=1e-2)
         close(gv[:, :, :S], vc[:, :, :S], rel=2.0 ** -6, floor=1e-2)
@@ -274,7 +278,7 @@ def test_block_prefill_then_decode(orc, n_heads, n_kv_heads):
             kc, vc = blk.caches()
             want = orc.llama_block(cfg, weights, nxt, B, 1, S + step, kc, vc, threads=orc.max_threads())
             got = blk.decode(nxt)
-            close(got, want, rel=2.0 ** -5, floor=2e-2)
+            close(got, want, rel=2.0 ** -7, floor=3.1e-2)
         assert blk.pos == S + 3
     finally:
         blk.close()
