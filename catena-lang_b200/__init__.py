@@ -116,6 +116,9 @@ def lib():
     proto("program_matmul_2x2_via_mem_s", st, [mem, mem, u64, u64, u64, u64, u64, u64, pm])
     proto("program_matmul_right_identity_2x2_via_mem", None, [mem, u64, u64, pm])
     proto("program_matmul_left_identity_2x2_via_mem", None, [mem, u64, u64, pm])
+    for base, args in (("program_sum_u64", [mem, pu]), ("program_dot_u64", [mem, mem, pu]), ("program_array_head_u64", [mem, pu])):
+        proto(base, None, args)
+        proto(base + "_s", st, args)
     proto("catena_b200_map_f32_s", st, [C.c_char_p, mem, pm])
     proto("catena_b200_launch_len", u64, [LaunchParams])
     proto("catena_b200_gpu_materialize_f32_s", st, [C.c_char_p, LaunchParams, mem, pm])

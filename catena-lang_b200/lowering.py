@@ -16,7 +16,11 @@ recognises the shapes the stdlib lowers to:
   * squared-sum fold + `nn.rmsnorm-at` map (nn.hex:154-182)                  -> fused rmsnorm
   * `materializec` over tensor.broadcast-at / arange-at / slice-at / concat-f32-at
     (tensor.hex)                                                             -> fill / copy kernels
-  * a module of scalar primitives only                                       -> host execution
+  * `reducec` over u64 buffers with `u64.add-env` and an element / product getter
+    (catena-lang/tests/cases/reducec/basic.hex)                              -> u64 fold kernels
+  * `mem.cast.u64`, `ix.zero`, `ix` (catena-lang/tests/runtime.rs:713-726)   -> buffer-head copy
+  * a module of scalar primitives, `bool.ifc`, `eval`, calls of scalar modules and `reducec` whose
+    closures are scalar (catena-lang/tests/cases/closures/*.hex)             -> host execution (evaluator.py)
 Anything else is reported as unsupported (the reference would render a generic one-thread-per-element
 kernel for it; this backend ships no source generator).
 
@@ -44,6 +48,10 @@ class GpuAssign:
     inputs: list            # GpuVar | FnSymbol
     outputs: List[GpuVar]
     call_symbol: Optional[str] = None
+    # how the flattened inputs / outputs group into components (env, function, flag, ...) for the structural
+    # operations `bool.ifc`, `reducec`, `u64.to-ix` (catena-lang/src/codegen/components.rs:13-60)
+    input_sizes: Optional[List[int]] = None
+    output_sizes: Optional[List[int]] = None
 
 
 @dataclass
@@ -64,8 +72,35 @@ class GpuModule:
 @dataclass
 class KernelPlan:
     kernel: str                       # name of the prebuilt kernel family
-    symbol: str                       # C symbol of the entry point that runs it
+    symbol: str                       # C symbol the reference would have generated for this module
     notes: List[str] = field(default_factory=list)
+
+    @property
+    def entry(self):
+        """Entry point of the kernel library that implements this plan (None: host evaluation, or a family that is
+        only reachable through the program of the same name)."""
+        return LIBRARY_ENTRY.get(self.kernel)
+
+
+# kernel family -> (library entry point, runtime inputs, runtime outputs) for the families a user-named program can map to
+LIBRARY_ENTRY = {
+    "fold_sum_u64": "program_sum_u64", "fold_dot_u64": "program_dot_u64", "array_head_u64": "program_array_head_u64",
+    "fold_sum": "program_sum_f32", "fold_max": "program_max_f32", "fold_argmax": "program_tensor_argmax_f32",
+    "softmax_fused": "program_nn_softmax", "rmsnorm_fused": "program_nn_rmsnorm",
+    "fill_broadcast": "program_tensor_broadcast_f32", "fill_arange": "program_tensor_arange_f32",
+    "copy_slice": "program_tensor_slice_f32", "copy_concat": "program_tensor_concat_f32",
+    "matmul_f32_kernel": "program_matmul_2x2_via_mem",
+}
+ENTRY_SIGNATURE = {
+    "program_sum_u64": (["mem"], ["u64"]), "program_dot_u64": (["mem", "mem"], ["u64"]),
+    "program_array_head_u64": (["mem"], ["u64"]),
+    "program_sum_f32": (["mem"], ["f32"]), "program_max_f32": (["mem"], ["f32"]),
+    "program_tensor_argmax_f32": (["mem"], ["u64"]),
+    "program_nn_softmax": (["mem"], ["mem"]), "program_nn_rmsnorm": (["mem"], ["mem"]),
+    "program_tensor_broadcast_f32": (["f32", "u64"], ["mem"]), "program_tensor_arange_f32": (["u64"], ["mem"]),
+    "program_tensor_slice_f32": (["mem", "u64", "u64"], ["mem"]), "program_tensor_concat_f32": (["mem", "mem"], ["mem"]),
+    "program_matmul_2x2_via_mem": (["mem", "mem"] + ["u64"] * 6, ["mem"]),
+}
 
 
 class Unsupported(Exception):
@@ -77,7 +112,7 @@ def module_from_dict(d):
         return FnSymbol(v["fn"]) if "fn" in v else GpuVar(v["name"], v.get("lowered", "erased"))
     fn = d["entry"]
     assigns = [GpuAssign(a["op"], [var(v) for v in a.get("inputs", [])], [var(v) for v in a.get("outputs", [])],
-                         a.get("call_symbol")) for a in fn["assignments"]]
+                         a.get("call_symbol"), a.get("input_sizes"), a.get("output_sizes")) for a in fn["assignments"]]
     return GpuModule(d["name"], d.get("source_name"),
                      GpuFunction(fn["name"], [var(v) for v in fn.get("sources", [])],
                                  [var(v) for v in fn.get("targets", [])], assigns))
@@ -87,7 +122,8 @@ def _fn_symbols(assign):
     return [v.name for v in assign.inputs if isinstance(v, FnSymbol)]
 
 
-_FOLDS = {("f32.add-env", "f32-at"): "fold_sum", ("f32.max-env", "f32-at"): "fold_max",
+_FOLDS = {("u64.add-env", "sum-u64-at"): "fold_sum_u64", ("u64.add-env", "dot-u64-product-at"): "fold_dot_u64",
+          ("f32.add-env", "f32-at"): "fold_sum", ("f32.max-env", "f32-at"): "fold_max",
           ("f32.add-env", "nn.squared-at"): "fold_sumsq", ("f32.add-env", "nn.softmax-exp-shifted-at"): "fold_expsum",
           ("tensor.argmax-env", "tensor.argmax-pair-at"): "fold_argmax"}
 _MAPS = {"tensor.broadcast-at": "fill_broadcast", "tensor.arange-at": "fill_arange", "tensor.slice-at": "copy_slice",
@@ -97,13 +133,34 @@ _SCALAR_PREFIXES = ("f32.", "u32.", "u64.", "bool.", "const.", "ix", "unit.", ":
                     "row-major-", "math.", "nn.sigmoid", "nn.silu", "nn.tanh", "nn.gelu")
 
 
-def classify(assign):
-    """One assignment -> kernel family, 'scalar' or None."""
+def _touches_memory(assign):
+    return any(isinstance(v, GpuVar) and (v.lowered == "mem" or v.lowered.startswith("ptr<")) for v in list(assign.inputs) + list(assign.outputs))
+
+
+def _scalar_function(name, modules, seen, allow_memory=False):
+    """True when the function a symbol names is a primitive or a module (of `modules`) made of scalar assignments;
+    unless `allow_memory`, none of them may touch a buffer (the host cannot dereference device memory)."""
+    from .evaluator import is_primitive
+    if is_primitive(name):
+        return True
+    module = find_module(modules, name)
+    if module is None or name in seen:
+        return False
+    seen = seen | {name}
+    return all(classify(a, modules, seen) == "scalar" and (allow_memory or not _touches_memory(a)) for a in module.entry.assignments)
+
+
+def classify(assign, modules=None, _seen=frozenset()):
+    """One assignment -> kernel family, 'scalar' or None.  `modules` maps source names (and generated symbols) to the
+    lowered modules of the program, so that calls and closure symbols can be looked through."""
     if assign.op == "reducec":
         fns = _fn_symbols(assign)
         for (add, get), kernel in _FOLDS.items():
             if add in fns and get in fns:
                 return kernel
+        # a fold whose closures are scalar functions over scalar environments runs on the host, as in the reference
+        if fns and not _touches_memory(assign) and all(_scalar_function(f, modules, _seen) for f in fns):
+            return "scalar"
         return None
     if assign.op in ("materializec", "gpu.materialize"):
         fns = _fn_symbols(assign)
@@ -113,25 +170,62 @@ def classify(assign):
             if f in _MAPS:
                 return _MAPS[f]
         return None
-    if assign.op.startswith(_SCALAR_PREFIXES) or assign.call_symbol:
+    if assign.op in ("bool.ifc", "eval"):
+        fns = _fn_symbols(assign)
+        return "scalar" if fns and all(_scalar_function(f, modules, _seen) for f in fns) else None
+    if assign.call_symbol:
+        # a callee may cast and pass buffers on (e.g. `mem.cast.u64.same-length`): whether the caller as a whole can run
+        # on the host is decided in `select`
+        return "scalar" if modules is None or _scalar_function(assign.call_symbol, modules, _seen, allow_memory=True) else None
+    if assign.op.startswith(_SCALAR_PREFIXES):
         return "scalar"
     return None
 
 
-def select(module, symbol_for=None):
+def module_map(modules):
+    """{generated symbol, source name, `program.<source name>` -> module} for a list of lowered modules."""
+    out = {}
+    for m in modules:
+        out[m.name] = m
+        if m.source_name:
+            out[m.source_name] = m
+            out["program." + m.source_name] = m
+    return out
+
+
+def find_module(modules, name):
+    """The module a call symbol, a source name or a function symbol's target names.  A function symbol `f` is called as
+    `program.f` with every non-alphanumeric character replaced (catena-lang/src/codegen/components.rs:100-105)."""
+    if not modules:
+        return None
+    m = modules.get(name)
+    if m is None:
+        from . import symbol_for
+        m = modules.get(symbol_for(name))
+    return m
+
+
+def select(module, symbol_for=None, modules=None):
     """GpuModule -> KernelPlan (or raises Unsupported)."""
     if symbol_for is None:
         from . import symbol_for as _sf
         symbol_for = _sf
     kinds = []
     for a in module.entry.assignments:
-        k = classify(a)
+        k = classify(a, modules)
         if k is None:
             raise Unsupported(f"{module.name}: no prebuilt kernel for `{a.op}` with {_fn_symbols(a)}")
         if k != "scalar":
             kinds.append(k)
     symbol = symbol_for(module.source_name) if module.source_name else module.name
+    ops = [a.op for a in module.entry.assignments]
     if not kinds:
+        if any(_touches_memory(a) for a in module.entry.assignments):
+            # scalar code that reads a buffer: the host cannot dereference device memory, so only the shape with a
+            # kernel-side counterpart is taken — the first element of a u64 buffer
+            if "mem.cast.u64" in ops and "ix.zero" in ops and ops.count("ix") == 1 and not any(o.startswith("mem.cast.f32") for o in ops):
+                return KernelPlan("array_head_u64", symbol, ["8-byte device-to-host copy after the non-empty assertion"])
+            raise Unsupported(f"{module.name}: scalar code over a buffer other than the head of a u64 buffer")
         return KernelPlan("host_scalar", symbol, ["runs on the host, like the reference's non-materialize code"])
     if kinds == ["gemm_f32"]:
         return KernelPlan("matmul_f32_kernel", symbol, ["bit-exact ascending-k fold, smem-tiled"])

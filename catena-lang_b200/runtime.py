@@ -206,6 +206,43 @@ class Runtime:
                     table[name] = (symbol_for(name), ins, outs)
         return cls(table)
 
+    @classmethod
+    def from_modules(cls, modules, sources=(), dialect=GpuDialect.Cuda):
+        """Registers LOWERED modules (`lowering.GpuModule`, the reference's IR after `codegen::codegen`,
+        codegen/mod.rs:107-146) next to what `from_sources` registers.  Every module with a source name whose runtime
+        interface is made of `ValueKind`s (signature.rs:63-72) becomes callable through `exec`: the lowering selector
+        picks its plan — the kernel library's entry point for the recognised kernel shapes, the host evaluator
+        (evaluator.py) for scalar modules, as the reference runs non-materialize code on the host.  A module no plan
+        exists for is an InitError (the reference would have generated source for it; this backend ships no generator)."""
+        from . import lib
+        from .evaluator import Evaluator
+        from .lowering import ENTRY_SIGNATURE, Unsupported, module_map, select
+        rt = cls.from_sources(sources, dialect)
+        mm = module_map(modules)
+        evaluator = Evaluator(modules)
+        kinds = {"bool": K.Bool, "u32": K.U32, "u64": K.U64, "f32": K.F32, "mem": K.Mem}
+        for m in modules:
+            if not m.source_name:
+                continue
+            ins = [v.lowered for v in m.entry.sources if v.lowered != "erased"]
+            outs = [v.lowered for v in m.entry.targets if v.lowered != "erased"]
+            if any(t not in kinds for t in ins + outs):
+                continue                                   # a `buf` pointer on the boundary: internal, no signature
+            try:
+                plan = select(m, modules=mm)
+            except Unsupported as exc:
+                raise InitError(f"no prebuilt kernel or host plan for program '{m.source_name}': {exc}") from exc
+            if plan.kernel == "host_scalar":
+                rt.signatures[m.source_name] = (plan.symbol, [kinds[t] for t in ins], [kinds[t] for t in outs],
+                                                (lambda args, _name=m.name: evaluator.call(_name, args)))
+                continue
+            entry = plan.entry
+            if entry is None or ENTRY_SIGNATURE.get(entry) != (ins, outs) or not hasattr(lib(), entry):
+                raise InitError(f"program '{m.source_name}' lowers to {plan.kernel}, which the library has no entry point for "
+                                f"with the interface {ins} -> {outs}")
+            rt.signatures[m.source_name] = (entry, [kinds[t] for t in ins], [kinds[t] for t in outs])
+        return rt
+
     # -- memory constructors (runtime.rs:166-172; mem_bytes is additive: Mem is untyped bytes) --
     def mem_f32(self, values):
         return self.mem_bytes(np.ascontiguousarray(values, dtype=np.float32))
@@ -223,7 +260,8 @@ class Runtime:
         sig = self.signatures.get(name)
         if sig is None:
             raise ExecError("UnknownSourceFunction", f"Unknown source function '{name}'")
-        symbol, ins, outs = sig
+        symbol, ins, outs = sig[:3]
+        host = sig[3] if len(sig) > 3 else None
         args = [Value.of(a) for a in args]
         if len(args) != len(ins):
             raise ExecError("InputArityMismatch", f"Function '{name}' expected {len(ins)} inputs, got {len(args)}")
@@ -232,6 +270,8 @@ class Runtime:
         for index, (value, expected) in enumerate(zip(args, ins)):
             if value.kind is not expected:
                 raise ExecError("TypeMismatch", f"Argument {index} expected {expected.value}, got {value.kind.value}")
+        if host is not None:
+            return self._exec_on_host(name, host, args, outs)
         from . import CatenaMem
         cargs = []
         for value in args:
@@ -260,3 +300,17 @@ class Runtime:
             else:
                 results.append(Value(kind, int(o.value)))
         return results
+
+    def _exec_on_host(self, name, host, args, outs):
+        """A scalar module: evaluated on the host.  A failed `assert` is the Device error the kernels report as
+        CATENA_E_ASSERT (the generated code of the reference would have trapped)."""
+        from . import E_ASSERT
+        from .evaluator import AssertFailed
+        values = [np.float32(a.v) if a.kind is K.F32 else int(a.v) for a in args]
+        try:
+            got = host(values)
+        except AssertFailed as exc:
+            raise ExecError("Device", f"program '{name}' failed: {exc}", E_ASSERT) from exc
+        if len(got) != len(outs):
+            raise ExecError("OutputArityMismatch", f"Function '{name}' expected {len(outs)} outputs, got {len(got)}")
+        return [Value.f32(v) if kind is K.F32 else Value(kind, int(v)) for kind, v in zip(outs, got)]

@@ -145,6 +145,19 @@ catena_status_t program_matmul_2x2_via_mem_s(catena_mem_t a, catena_mem_t b, uin
 void program_matmul_right_identity_2x2_via_mem(catena_mem_t a, uint64_t n, uint64_t nn, catena_mem_t* out);
 void program_matmul_left_identity_2x2_via_mem(catena_mem_t a, uint64_t n, uint64_t nn, catena_mem_t* out);
 
+/* Integer programs of the reference's tests over `mem` buffers of u64.  catena-lang/tests/cases/reducec/basic.hex:27-58
+ * (`sum-u64`: mem.cast.u64, then reducec with u64.add from 0), :60-122 (`dot-u64`: both buffers cast, lengths asserted equal,
+ * reducec over the element products), catena-lang/tests/runtime.rs:713-726 (`array-head-u64`: mem.cast.u64, u64.assert-nz,
+ * element 0; called directly by catena-lang/smoketest/src/array_head.cpp:37-43).  Arithmetic is modulo 2^64, so the
+ * kernels' tree order gives the bits of the sequential fold for every length.  A length mismatch / an empty buffer is
+ * CATENA_E_ASSERT. */
+void program_sum_u64(catena_mem_t in, uint64_t* out);
+void program_dot_u64(catena_mem_t lhs, catena_mem_t rhs, uint64_t* out);
+void program_array_head_u64(catena_mem_t in, uint64_t* out);
+catena_status_t program_sum_u64_s(catena_mem_t in, uint64_t* out);
+catena_status_t program_dot_u64_s(catena_mem_t lhs, catena_mem_t rhs, uint64_t* out);
+catena_status_t program_array_head_u64_s(catena_mem_t in, uint64_t* out);
+
 /* elementwise application of a scalar stdlib program over an f32 buffer: the map kernel a
  * `materializec` with that producer lowers to (catena-lang/src/codegen/ops/materializec.rs:36-145).
  * `op` is the hexpr name, e.g. "nn.silu", "math.exp-approx". */

@@ -12,6 +12,10 @@
 //   * from_sources does not run the catena compiler (its front end is Rust and not part of this build): it scans the
 //     sources for `(def program <name>` and registers the programs the library ships a kernel for.  A program without
 //     a kernel stays out of the table, so exec reports UnknownSourceFunction for it.  The stdlib is always present.
+//   * register_modules takes LOWERED modules (the reference's IR after codegen, catena-lang/src/codegen/mod.rs:107-146):
+//     the lowering selector (catena_b200_lowering.hpp) picks a plan for each — an entry point of the kernel library for the
+//     recognised kernel shapes, the host evaluator (catena_b200_eval.hpp) for scalar modules, which the reference also
+//     runs on the host.
 //   * GpuDialect::Hip is refused with InitError.
 //   * Mem owns DEVICE memory and copies on to_*_vec.  Like the Rust API, exec consumes its Mem arguments: they are
 //     freed when the call returns (runtime.rs:175-179, mem.rs:119-125).
@@ -26,6 +30,7 @@
 #include <fstream>
 #include <functional>
 #include <map>
+#include <memory>
 #include <sstream>
 #include <stdexcept>
 #include <string>
@@ -33,6 +38,7 @@
 #include <vector>
 
 #include "catena_b200.h"
+#include "catena_b200_eval.hpp"
 
 namespace catena_b200 {
 
@@ -190,6 +196,88 @@ public:
             texts.push_back(ss.str());
         }
         return from_sources(texts, dialect);
+    }
+
+    // Registers lowered modules: every module with a source name whose runtime interface is made of ValueKinds
+    // (catena-lang/src/runtime/signature.rs:63-72) becomes callable through exec.  A module no plan exists for is an
+    // InitError (the reference would have generated source for it; this backend ships no generator).
+    void register_modules(std::vector<lowering::GpuModule> modules) {
+        auto shared = std::make_shared<std::vector<lowering::GpuModule>>(std::move(modules));
+        auto evaluator = std::make_shared<eval::Evaluator>(*shared);
+        auto kind_of = [](const std::string& l, K* k) {
+            if (l == "bool") *k = K::Bool; else if (l == "u32") *k = K::U32; else if (l == "u64") *k = K::U64;
+            else if (l == "f32") *k = K::F32; else if (l == "mem") *k = K::Mem; else return false;
+            return true;
+        };
+        for (const lowering::GpuModule& m : *shared) {
+            if (m.source_name.empty()) continue;
+            std::vector<K> ins, outs;
+            bool callable = true;
+            for (const auto& s : m.entry.sources) { K k; if (s.lowered == "erased") continue; if (!kind_of(s.lowered, &k)) callable = false; else ins.push_back(k); }
+            for (const auto& t : m.entry.targets) { K k; if (t.lowered == "erased") continue; if (!kind_of(t.lowered, &k)) callable = false; else outs.push_back(k); }
+            if (!callable) continue;                                   // a `buf` pointer on the boundary: internal
+            lowering::KernelPlan plan;
+            try {
+                plan = lowering::select(m);
+            } catch (const lowering::Unsupported& e) {
+                throw InitError("no prebuilt kernel or host plan for program '" + m.source_name + "': " + e.what());
+            }
+            if (plan.kernel == "host_scalar") {
+                const std::string name = m.name;
+                std::vector<K> out_kinds = outs;
+                table_[m.source_name] = Signature{plan.symbol, ins, outs, [shared, evaluator, name, out_kinds](std::vector<Value>& a, std::vector<Value>& o) {
+                    std::vector<eval::Val> args;
+                    for (Value& v : a) {
+                        switch (v.kind()) {
+                            case K::Bool: args.push_back(eval::Val::scalar(v.as_bool())); break;
+                            case K::U32: args.push_back(eval::Val::scalar(v.as_u32())); break;
+                            case K::U64: args.push_back(eval::Val::scalar(v.as_u64())); break;
+                            case K::F32: args.push_back(eval::Val::f32(v.as_f32())); break;
+                            default: return (catena_status_t)CATENA_E_BAD_ARG;       // device memory cannot be read on the host
+                        }
+                    }
+                    std::vector<eval::Val> got;
+                    try {
+                        got = evaluator->call(name, args);
+                    } catch (const eval::AssertFailed&) {
+                        return (catena_status_t)CATENA_E_ASSERT;
+                    }
+                    if (got.size() != out_kinds.size()) return (catena_status_t)CATENA_E_BAD_ARG;
+                    for (size_t i = 0; i < got.size(); ++i) {
+                        switch (out_kinds[i]) {
+                            case K::Bool: o.push_back(Value::boolean(got[i].bits != 0)); break;
+                            case K::U32: o.push_back(Value::u32((uint32_t)got[i].bits)); break;
+                            case K::U64: o.push_back(Value::u64(got[i].bits)); break;
+                            default: o.push_back(Value::f32(got[i].as_f32())); break;
+                        }
+                    }
+                    return (catena_status_t)CATENA_OK;
+                }};
+                continue;
+            }
+            // kernel shapes a user-named program can lower to: the library's entry point of that family
+            typedef catena_status_t (*MemToU64)(catena_mem_t, uint64_t*);
+            MemToU64 unary = plan.kernel == "fold_sum_u64" ? program_sum_u64_s : plan.kernel == "array_head_u64" ? program_array_head_u64_s : nullptr;
+            if (unary && ins == std::vector<K>{K::Mem} && outs == std::vector<K>{K::U64}) {
+                table_[m.source_name] = Signature{plan.symbol, ins, outs, [unary](std::vector<Value>& a, std::vector<Value>& o) {
+                    uint64_t r = 0;
+                    catena_status_t s = unary(a[0].as_mem().raw(), &r);
+                    if (s == CATENA_OK) o.push_back(Value::u64(r));
+                    return s;
+                }};
+            } else if (plan.kernel == "fold_dot_u64" && ins == std::vector<K>{K::Mem, K::Mem} && outs == std::vector<K>{K::U64}) {
+                table_[m.source_name] = Signature{plan.symbol, ins, outs, [](std::vector<Value>& a, std::vector<Value>& o) {
+                    uint64_t r = 0;
+                    catena_status_t s = program_dot_u64_s(a[0].as_mem().raw(), a[1].as_mem().raw(), &r);
+                    if (s == CATENA_OK) o.push_back(Value::u64(r));
+                    return s;
+                }};
+            } else if (stdlib().count(m.source_name) || user_programs().count(m.source_name)) {
+                table_[m.source_name] = stdlib().count(m.source_name) ? stdlib().at(m.source_name) : user_programs().at(m.source_name);
+            } else {
+                throw InitError("program '" + m.source_name + "' lowers to " + plan.kernel + ", which is only reachable under its stdlib name");
+            }
+        }
     }
 
     // memory constructors (runtime.rs:166-172; mem_bytes is additive: Mem is untyped bytes)

@@ -13,7 +13,11 @@
 //   * max fold + exp-shifted sum fold + `nn.softmax-at` map (nn.hex:93-122)    -> fused softmax
 //   * squared-sum fold + `nn.rmsnorm-at` map (nn.hex:154-182)                  -> fused rmsnorm
 //   * `materializec` over tensor.broadcast-at / arange-at / slice-at / concat-f32-at (tensor.hex) -> fill / copy kernels
-//   * a module of scalar primitives only                                       -> host execution
+//   * `reducec` over u64 buffers with `u64.add-env` and an element / product getter
+//     (catena-lang/tests/cases/reducec/basic.hex)                              -> u64 fold kernels
+//   * `mem.cast.u64`, `ix.zero`, `ix` (catena-lang/tests/runtime.rs:713-726)   -> buffer-head copy
+//   * a module of scalar primitives, `bool.ifc`, `eval`, `reducec` over scalar closures and calls
+//     (catena-lang/tests/cases/closures/*.hex)                                 -> host execution (catena_b200_eval.hpp)
 // Anything else is reported as unsupported (the reference would render a generic one-thread-per-element kernel for it;
 // this backend ships no source generator).  The Rust front end that produces the IR is not part of this build, so the
 // fixtures of the tests are written by hand from the lowering rules cited above.
@@ -40,6 +44,9 @@ struct GpuAssign {
     std::string op;
     std::vector<Operand> inputs, outputs;
     std::string call_symbol;  // non-empty for a call of another program
+    // how the flattened inputs / outputs group into components (environment, function, flag, ...) for `bool.ifc`, `reducec`
+    // and `u64.to-ix` (catena-lang/src/codegen/components.rs:13-60); empty for everything else
+    std::vector<size_t> input_sizes, output_sizes;
 };
 struct GpuFunction {
     std::string name;
@@ -80,15 +87,21 @@ inline bool starts_with(const std::string& s, const char* prefix) { return s.rfi
 inline std::string classify(const GpuAssign& a) {
     using detail::has_fn;
     if (a.op == "reducec") {
-        static const char* folds[][3] = {{"f32.add-env", "f32-at", "fold_sum"},
+        static const char* folds[][3] = {{"u64.add-env", "sum-u64-at", "fold_sum_u64"},
+                                         {"u64.add-env", "dot-u64-product-at", "fold_dot_u64"},
+                                         {"f32.add-env", "f32-at", "fold_sum"},
                                          {"f32.max-env", "f32-at", "fold_max"},
                                          {"f32.add-env", "nn.squared-at", "fold_sumsq"},
                                          {"f32.add-env", "nn.softmax-exp-shifted-at", "fold_expsum"},
                                          {"tensor.argmax-env", "tensor.argmax-pair-at", "fold_argmax"}};
         for (auto& f : folds)
             if (has_fn(a, f[0]) && has_fn(a, f[1])) return f[2];
-        return "";
+        // a fold whose environments hold no buffer runs on the host (its closures are checked when it is evaluated)
+        for (const Operand& o : a.inputs)
+            if (!o.is_fn && (o.lowered == "mem" || detail::starts_with(o.lowered, "ptr<"))) return "";
+        return "scalar";
     }
+    if (a.op == "bool.ifc" || a.op == "eval") return "scalar";
     if (a.op == "materializec" || a.op == "gpu.materialize") {
         for (const Operand& o : a.inputs)
             if (o.is_fn && (o.name.find("f32.matmul.row-major.cell-at") != std::string::npos || detail::starts_with(o.name, "closure.f32.matmul")))
@@ -126,7 +139,23 @@ inline KernelPlan select(const GpuModule& module) {
             if (kinds[i++] != w) return false;
         return true;
     };
-    if (kinds.empty()) return {"host_scalar", symbol, "runs on the host, like the reference's non-materialize code"};
+    if (kinds.empty()) {
+        bool memory = false, cast_u64 = false, ix_zero = false;
+        size_t ix_count = 0;
+        for (const GpuAssign& a : module.entry.assignments) {
+            for (const Operand& o : a.inputs) memory = memory || (!o.is_fn && (o.lowered == "mem" || detail::starts_with(o.lowered, "ptr<")));
+            cast_u64 = cast_u64 || a.op == "mem.cast.u64";
+            ix_zero = ix_zero || a.op == "ix.zero";
+            ix_count += a.op == "ix";
+        }
+        if (memory) {
+            // scalar code that reads a buffer: the host cannot dereference device memory; only the head of a u64 buffer
+            // has a kernel-side counterpart
+            if (cast_u64 && ix_zero && ix_count == 1) return {"array_head_u64", symbol, "8-byte device-to-host copy after the non-empty assertion"};
+            throw Unsupported(module.name + ": scalar code over a buffer other than the head of a u64 buffer");
+        }
+        return {"host_scalar", symbol, "runs on the host, like the reference's non-materialize code"};
+    }
     if (is({"gemm_f32"})) return {"matmul_f32_kernel", symbol, "bit-exact ascending-k fold, smem-tiled"};
     if (is({"fold_max", "fold_expsum", "softmax_map"}))
         return {"softmax_fused", symbol, "two host folds + one map kernel in the reference; one launch here up to 65536 elements"};

@@ -83,6 +83,7 @@ def lib():
         L.orc_llama_block.restype = None
         L.orc_llama_block.argtypes = [u64, u64, u64, u64, u64, f32, vp, vp, vp, vp, vp, vp, u64, u64, u64, vp, vp, vp, i32]
         L.orc_max_threads.restype = i32
+        L.orc_prim.restype, L.orc_prim.argtypes = u64, [C.c_char_p, u64, u64, u64, C.POINTER(i32)]
         L.orc_f32_to_bf16.restype, L.orc_f32_to_bf16.argtypes = C.c_uint16, [f32]
         _lib = L
     return _lib
@@ -279,6 +280,40 @@ def llama_block(cfg, weights, ids, batch, seq, pos0, k_cache, v_cache, threads=1
                           _p(w["w_gate_up"]), _p(w["w_down"]), _p(ids), batch, seq, pos0, _p(k_cache), _p(v_cache),
                           _p(out), threads)
     return out
+
+
+# operand and result kinds of the primitive table (codegen/gpu.rs:322-447): op -> ((inputs), output)
+PRIM_KINDS = {
+    "bool.not": (("bool",), "bool"), "bool.and": (("bool", "bool"), "bool"), "bool.or": (("bool", "bool"), "bool"),
+    "u64.add": (("u64", "u64"), "u64"), "u64.sub": (("u64", "u64"), "u64"), "u64.mul": (("u64", "u64"), "u64"),
+    "u64.ne": (("u64", "u64"), "bool"), "u64.lt": (("u64", "u64"), "bool"), "u64.lte": (("u64", "u64"), "bool"),
+    "u64.gte": (("u64", "u64"), "bool"), "u64.eq": (("u64", "u64"), "bool"), "u64.gt": (("u64", "u64"), "bool"),
+    "u32.add": (("u32", "u32"), "u32"), "u32.sub": (("u32", "u32"), "u32"), "u32.mul": (("u32", "u32"), "u32"),
+    "u32.and": (("u32", "u32"), "u32"), "u32.or": (("u32", "u32"), "u32"), "u32.xor": (("u32", "u32"), "u32"),
+    "u32.shl": (("u32", "u32"), "u32"), "u32.shr": (("u32", "u32"), "u32"), "u32.not": (("u32",), "u32"),
+    "u32.eq": (("u32", "u32"), "bool"), "u32.ne": (("u32", "u32"), "bool"), "u32.lt": (("u32", "u32"), "bool"),
+    "u32.gt": (("u32", "u32"), "bool"), "u32.lte": (("u32", "u32"), "bool"), "u32.gte": (("u32", "u32"), "bool"),
+    "u32.to-f32": (("u32",), "f32"), "u64.to-f32": (("u64",), "f32"), "u32.bitcast-f32": (("u32",), "f32"),
+    "f32.add": (("f32", "f32"), "f32"), "f32.sub": (("f32", "f32"), "f32"), "f32.mul": (("f32", "f32"), "f32"),
+    "f32.div": (("f32", "f32"), "f32"), "f32.neg": (("f32",), "f32"), "f32.fma": (("f32", "f32", "f32"), "f32"),
+    "f32.eq": (("f32", "f32"), "bool"), "f32.ne": (("f32", "f32"), "bool"), "f32.lt": (("f32", "f32"), "bool"),
+    "f32.gt": (("f32", "f32"), "bool"), "f32.lte": (("f32", "f32"), "bool"), "f32.gte": (("f32", "f32"), "bool"),
+    "f32.select": (("bool", "f32", "f32"), "f32"), "u32.select": (("bool", "u32", "u32"), "u32"),
+    "u64.select": (("bool", "u64", "u64"), "u64"), "bool.select": (("bool", "bool", "bool"), "bool"),
+    "f32.round-to-u32": (("f32",), "u32"), "f32.bitcast-u32": (("f32",), "u32"),
+    "bool.t": ((), "bool"), "bool.f": ((), "bool"), "u64.zero": ((), "u64"), "u64.one": ((), "u64"), "u32.one": ((), "u32"),
+    "f32.one": ((), "f32"),
+}
+
+
+def prim(op, *raw):
+    """One primitive of the table on raw operand bits -> raw result bits (f32 values as their 32-bit patterns)."""
+    known = C.c_int(0)
+    a, b, c = (list(raw) + [0, 0, 0])[:3]
+    r = lib().orc_prim(op.encode(), a, b, c, C.byref(known))
+    if not known.value:
+        raise KeyError(op)
+    return int(r)
 
 
 def f32_to_bf16_bits(x):

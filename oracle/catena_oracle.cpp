@@ -25,6 +25,7 @@
 #include <cstdint>
 #include <cstring>
 #include <cstdlib>
+#include <string>
 #include <thread>
 #include <vector>
 
@@ -538,6 +539,86 @@ void orc_llama_block(uint64_t hidden, uint64_t hq, uint64_t hkv, uint64_t ffn, u
     orc_linear_bf16(nrm.data(), w_gate_up, nullptr, gu.data(), T, 2 * ffn, hidden, threads);
     orc_swiglu_bf16(gu.data(), act.data(), T, ffn);
     orc_linear_bf16(act.data(), w_down, x2.data(), out, T, hidden, ffn, threads);
+}
+
+// ---- codegen/gpu.rs:322-447 : the primitive table, one generated C expression per operation ----------
+// `op` is the hexpr name; operands and result travel as raw bits (an f32 in the low 32 bits, a bool as 0 / 1).  The body
+// of each case is the expression the renderer prints for that primitive (gpu.rs file:line beside each group), compiled by
+// the host compiler exactly as the reference's generated code would be (uint32_t / uint64_t / float / uint8_t operands,
+// the usual C conversions, no contraction).  Returns 0 and sets *known = 0 for a name outside the table.
+uint64_t orc_prim(const char* op, uint64_t a, uint64_t b, uint64_t c, int* known) {
+    const std::string o(op);
+    const uint32_t a32 = (uint32_t)a, b32 = (uint32_t)b, c32 = (uint32_t)c;
+    const float af = bits_f32(a32), bf = bits_f32(b32), cf = bits_f32(c32);
+    const uint8_t ab = a ? 1 : 0, bb = b ? 1 : 0;
+    auto F = [](float x) { return (uint64_t)f32_bits(x); };
+    if (known) *known = 1;
+    // gpu.rs:327-369 (bool)
+    if (o == "bool.t") return 1;
+    if (o == "bool.f") return 0;
+    if (o == "bool.not") return (uint8_t)(!ab);
+    if (o == "bool.id") return ab;
+    if (o == "bool.and") return (uint8_t)(ab && bb);
+    if (o == "bool.or") return (uint8_t)(ab || bb);
+    // gpu.rs:379-389 (u64), :402-403, :697-733 (u64.eq / u64.gt: the flag output)
+    if (o == "u64.zero") return 0;
+    if (o == "u64.one") return 1;
+    if (o == "u64.add") return a + b;
+    if (o == "u64.sub") return a - b;
+    if (o == "u64.mul") return a * b;
+    if (o == "u64.ne") return a != b;
+    if (o == "u64.lt") return a < b;
+    if (o == "u64.lte") return a <= b;
+    if (o == "u64.gte") return a >= b;
+    if (o == "u64.eq") return a == b;
+    if (o == "u64.gt") return a > b;
+    if (o == "u64.name" || o == "ix.to-u64") return a;
+    // gpu.rs:390-412 (u32)
+    if (o == "u32.one") return 1;
+    if (o == "u32.add") return (uint32_t)(a32 + b32);
+    if (o == "u32.sub") return (uint32_t)(a32 - b32);
+    if (o == "u32.mul") return (uint32_t)(a32 * b32);
+    if (o == "u32.and") return (uint32_t)(a32 & b32);
+    if (o == "u32.or") return (uint32_t)(a32 | b32);
+    if (o == "u32.xor") return (uint32_t)(a32 ^ b32);
+    if (o == "u32.shl") return (uint32_t)(a32 << b32);      // defined for shifts below 32 only
+    if (o == "u32.shr") return (uint32_t)(a32 >> b32);
+    if (o == "u32.not") return (uint32_t)(~a32);
+    if (o == "u32.eq") return a32 == b32;
+    if (o == "u32.ne") return a32 != b32;
+    if (o == "u32.lt") return a32 < b32;
+    if (o == "u32.gt") return a32 > b32;
+    if (o == "u32.lte") return a32 <= b32;
+    if (o == "u32.gte") return a32 >= b32;
+    if (o == "u32.to-f32") return F((float)(a32));                       // gpu.rs:535-548
+    if (o == "u64.to-f32") return F((float)(a));                         // gpu.rs:550-563
+    if (o == "u32.bitcast-f32") return F(bits_f32(a32));                 // gpu.rs:565-578, prelude.rs:64-71
+    // gpu.rs:418-436 (f32)
+    if (o == "f32.one") return F(1.0);
+    if (o == "f32.add") return F(af + bf);
+    if (o == "f32.sub") return F(af - bf);
+    if (o == "f32.neg") return F(-af);
+    if (o == "f32.mul") return F(af * bf);
+    if (o == "f32.div") return F(af / bf);
+    if (o == "f32.fma") return F(fmaf(af, bf, cf));                      // gpu.rs:589-604
+    if (o == "f32.eq") return af == bf;
+    if (o == "f32.ne") return af != bf;
+    if (o == "f32.lt") return af < bf;
+    if (o == "f32.gt") return af > bf;
+    if (o == "f32.lte") return af <= bf;
+    if (o == "f32.gte") return af >= bf;
+    if (o == "f32.select") return F(ab ? bf : cf);                       // gpu.rs:624-640
+    if (o == "u32.select") return ab ? b32 : c32;
+    if (o == "u64.select") return ab ? b : c;
+    if (o == "bool.select") return ab ? (uint8_t)(b != 0) : (uint8_t)(c != 0);
+    if (o == "f32.round-to-u32") return (uint32_t)nearbyintf(af);        // gpu.rs:642-655, defined for 0 <= x < 2^32
+    if (o == "f32.bitcast-u32") return f32_bits(af);                     // gpu.rs:657-670, prelude.rs:73-80
+    // ops/row_major.rs:9-68 with (cols, row, col) / (cols, flat)
+    if (o == "row-major-index") return b * a + c;
+    if (o == "row-major-row") return b / a;
+    if (o == "row-major-col") return b % a;
+    if (known) *known = 0;
+    return 0;
 }
 
 uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16_rne(f); }

@@ -33,6 +33,42 @@ static bool throws_kind(ExecError::Kind kind, F f) {
     return false;
 }
 
+// Hand-lowered modules (catena-lang/src/codegen/mod.rs:107-146) of reference test programs, for Runtime::register_modules.
+namespace lw = catena_b200::lowering;
+static lw::Operand var(const std::string& n, const std::string& l) { return lw::Operand::var(n, l); }
+static lw::GpuModule module(const std::string& source_name, std::vector<lw::Operand> sources, std::vector<lw::Operand> targets,
+                            std::vector<lw::GpuAssign> assigns) {
+    lw::GpuModule m;
+    m.name = lw::symbol_for(source_name);
+    m.source_name = source_name;
+    m.entry.name = m.name;
+    m.entry.sources = std::move(sources);
+    m.entry.targets = std::move(targets);
+    m.entry.assignments = std::move(assigns);
+    return m;
+}
+static std::vector<lw::GpuModule> lowered_modules() {
+    std::vector<lw::GpuModule> mods;
+    // tests/runtime.rs:448-473
+    mods.push_back(module("shift-and-sub", {}, {var("r", "u32")},
+                          {{"const.u32.0x00000020", {}, {var("lhs", "u32")}, ""}, {"const.u32.0x00000003", {}, {var("shift", "u32")}, ""},
+                           {"const.u32.0x00000001", {}, {var("one", "u32")}, ""}, {"u32.shr", {var("lhs", "u32"), var("shift", "u32")}, {var("shr", "u32")}, ""},
+                           {"u32.shl", {var("one", "u32"), var("shift", "u32")}, {var("shl", "u32")}, ""},
+                           {"u32.sub", {var("shr", "u32"), var("shl", "u32")}, {var("r", "u32")}, ""}}));
+    // tests/cases/reducec/basic.hex:27-58 and tests/runtime.rs:713-726
+    mods.push_back(module("sum-u64", {var("m", "mem")}, {var("r", "u64")},
+                          {{"mem.cast.u64", {var("m", "mem")}, {var("len", "u64"), var("input", "ptr<u64>")}, ""},
+                           {"const.u64.0x0000000000000000", {}, {var("zero", "u64")}, ""}, {"unit.intro", {}, {var("unit", "erased")}, ""},
+                           {"reducec", {var("zero", "u64"), var("unit", "erased"), lw::Operand::fn("u64.add-env"), var("input", "ptr<u64>"),
+                                        lw::Operand::fn("sum-u64-at"), var("len", "u64")}, {var("r", "u64")}, "", {1, 1, 1, 1, 1, 1}, {1}}}));
+    mods.push_back(module("array-head-u64", {var("m", "mem")}, {var("head", "u64")},
+                          {{"mem.cast.u64", {var("m", "mem")}, {var("n", "u64"), var("buf", "ptr<u64>")}, ""}, {"u64.zero", {}, {var("z", "u64")}, ""},
+                           {"u64.gt", {var("n", "u64"), var("z", "u64")}, {var("nz", "bool"), var("ht", "erased"), var("hf", "erased")}, ""},
+                           {"assert", {var("nz", "bool")}, {var("h", "erased")}, ""}, {"ax-mp", {var("h", "erased"), var("ht", "erased")}, {var("proof", "erased")}, ""},
+                           {"ix.zero", {var("proof", "erased")}, {var("i0", "u64")}, ""}, {"ix", {var("i0", "u64"), var("buf", "ptr<u64>")}, {var("head", "u64")}, ""}}));
+    return mods;
+}
+
 static const char* kMatmulSource = "(def program matmul-2x2-via-mem : x -> y = ())";
 
 static int run_cpu() {
@@ -66,6 +102,13 @@ static int run_cpu() {
         hip_refused = true;
     }
     CHECK(hip_refused);
+    // lowered modules: a scalar module runs on the host through the evaluator (no device needed)
+    rt.register_modules(lowered_modules());
+    CHECK(rt.has("shift-and-sub") && rt.has("sum-u64") && rt.has("array-head-u64"));
+    {
+        std::vector<Value> out = rt.exec("shift-and-sub", {}, 1);
+        CHECK(out.size() == 1 && out[0].kind() == ValueKind::U32 && out[0].as_u32() == 0xFFFFFFFCu);     // tests/runtime.rs:471
+    }
     Value v = Value::u32(7);
     CHECK(v.kind() == ValueKind::U32 && v.as_u32() == 7);
     Mem empty;
@@ -132,6 +175,21 @@ static int run_gpu() {
         uint32_t bits;
         std::memcpy(&bits, &r, 4);
         CHECK(bits == 0x3F7FF8FCu);
+    }
+    // lowered modules that select the u64 kernels: tests/cases/reducec.rs:6-20 and tests/runtime.rs:713-740
+    rt.register_modules(lowered_modules());
+    {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_u64({2, 3, 5, 7, 11})));
+        CHECK(rt.exec("sum-u64", std::move(a))[0].as_u64() == 28);
+        std::vector<Value> b;
+        b.push_back(Value::mem(rt.mem_u64({0x123456789abcdef0ull, 7, 11})));
+        CHECK(rt.exec("array-head-u64", std::move(b))[0].as_u64() == 0x123456789abcdef0ull);
+        CHECK(throws_kind(ExecError::Kind::Device, [&] {
+            std::vector<Value> c;
+            c.push_back(Value::mem(rt.mem_u64({})));
+            rt.exec("array-head-u64", std::move(c));
+        }));
     }
     // bf16 GEMM through Runtime::exec: 256 x 256 x 64 of ones and twos -> every element 128 (exact in bf16)
     {

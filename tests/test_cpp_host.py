@@ -15,7 +15,7 @@ LIBDIR = os.path.dirname(cb.LIB_PATH)
 def binary(tmp_path_factory):
     out = str(tmp_path_factory.mktemp("cpp") / "host_mirror_test")
     gxx = os.environ.get("CXX", "g++")
-    cmd = [gxx, "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include",
+    cmd = [gxx, "-std=c++17", "-O1", "-Wall", "-ffp-contract=off", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include",
            os.path.join(ROOT, "tests", "cpp", "host_mirror_test.cpp"), "-o", out, "-L", LIBDIR, "-lcatena_b200",
            "-Wl,-rpath," + LIBDIR, "-L/usr/local/cuda/lib64", "-Wl,-rpath,/usr/local/cuda/lib64"]
     subprocess.check_call(cmd)
@@ -42,5 +42,15 @@ def test_cpp_lowering_selector(tmp_path):
     out = str(tmp_path / "lowering_test")
     subprocess.check_call([os.environ.get("CXX", "g++"), "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"),
                            os.path.join(ROOT, "tests", "cpp", "lowering_test.cpp"), "-o", out])
+    p = subprocess.run([out], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and p.stdout.strip().startswith("ok "), p.stdout + p.stderr
+
+
+def test_cpp_host_evaluator(tmp_path):
+    """The C++ host evaluator of lowered scalar modules (include/catena_b200_eval.hpp) on the reference's integer, bit,
+    conditional and fold vectors; built with -ffp-contract=off, the reference's own rule for generated code."""
+    out = str(tmp_path / "eval_test")
+    subprocess.check_call([os.environ.get("CXX", "g++"), "-std=c++17", "-O1", "-Wall", "-ffp-contract=off", "-I", os.path.join(ROOT, "include"),
+                           os.path.join(ROOT, "tests", "cpp", "eval_test.cpp"), "-o", out])
     p = subprocess.run([out], capture_output=True, text=True, timeout=60)
     assert p.returncode == 0 and p.stdout.strip().startswith("ok "), p.stdout + p.stderr

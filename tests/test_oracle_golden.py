@@ -138,3 +138,35 @@ def test_threads_do_not_change_bits(orc):
     c1 = orc.matmul_f32(a, b, 64, 48, 96, threads=1)
     c4 = orc.matmul_f32(a, b, 64, 48, 96, threads=4)
     assert np.array_equal(c1.view(np.uint32), c4.view(np.uint32))
+
+
+def test_primitive_table_reference_vectors(orc):
+    """The integer / bit / compare primitives of the oracle's table on the reference's own vectors."""
+    p = orc.prim
+    # tests/runtime.rs:170-188, 190-212, 273-290 (two-times-two, sub-basic)
+    two = p("u64.add", p("u64.one"), p("u64.one"))
+    assert p("u64.mul", two, two) == 4 and p("u64.sub", two, p("u64.one")) == 1
+    two32 = p("u32.add", p("u32.one"), p("u32.one"))
+    assert p("u32.mul", two32, two32) == 4
+    # tests/runtime.rs:214-271
+    assert [p(f"u64.{op}", 2, 3) for op in ("ne", "lt", "lte", "gte")] == [1, 1, 1, 0]
+    # tests/runtime.rs:313-331, 333-363 (fma-basic; fused against separate bits)
+    one = p("f32.one")
+    assert p("f32.fma", one, one, one) == 0x40000000
+    assert p("f32.fma", 0x3F800001, 0x3F800001, 0x33800000) == 0x3F800003
+    assert p("f32.add", p("f32.mul", 0x3F800001, 0x3F800001), 0x33800000) == 0x3F800002
+    # tests/runtime.rs:408-446 (bitcasts)
+    assert p("u32.bitcast-f32", 0x3F800000) == 0x3F800000 and p("f32.bitcast-u32", one) == 0x3F800000
+    # tests/runtime.rs:448-473 (shift-and-sub: (0x20 >> 3) - (1 << 3) wraps)
+    assert p("u32.sub", p("u32.shr", 0x20, 3), p("u32.shl", 1, 3)) == 0xFFFFFFFC
+    # tests/runtime.rs:475-530
+    assert p("u32.and", 0x00FF00FF, 0x0F0F0F0F) == 0x000F000F and p("u32.or", 0x00FF00FF, 0x0F0F0F0F) == 0x0FFF0FFF
+    assert p("u32.xor", 0x00FF00FF, 0x0F0F0F0F) == 0x0FF00FF0 and p("u32.not", 0x00FF00FF) == 0xFF00FF00
+    # tests/runtime.rs:532-605, 607-680 (2 against 3; 1.5 against 2.5)
+    assert [p(f"u32.{op}", 2, 3) for op in ("eq", "ne", "lt", "gt", "lte", "gte")] == [0, 1, 1, 0, 1, 0]
+    assert [p(f"f32.{op}", 0x3FC00000, 0x40200000) for op in ("lt", "eq", "ne", "gt", "lte", "gte")] == [1, 0, 1, 0, 1, 0]
+    # tests/runtime.rs:15-35 of tests/cases (bool), tests/runtime.rs:37-52
+    assert p("bool.not", 0) == 1 and p("bool.and", 1, 0) == 0 and p("bool.or", 0, 1) == 1
+    # conversions: exact below 2^24 (stdlib/data.hex:127-128), to nearest even above
+    assert p("u64.to-f32", (1 << 24) + 1) == 0x4B800000 and p("u64.to-f32", (1 << 24) + 3) == 0x4B800002
+    assert p("f32.round-to-u32", 0x40200000) == 2 and p("f32.round-to-u32", 0x40600000) == 4      # 2.5 -> 2, 3.5 -> 4
