@@ -30,6 +30,7 @@ sys.path.insert(0, ROOT)
 
 GEMM_M = GEMM_N = GEMM_K = 4096
 ATT = dict(B=32, Hq=32, Hkv=8, D=128, L=4096)
+TIMED_SECONDS = 0.5        # minimum length of the headline's timed region
 GEMM_FLOP = 2.0 * GEMM_M * GEMM_N * GEMM_K
 ATT_BYTES = 2 * ATT["B"] * ATT["Hkv"] * ATT["L"] * ATT["D"] * 2 + 2 * ATT["B"] * ATT["Hq"] * ATT["D"] * 2
 
@@ -221,12 +222,29 @@ def run_gpu(args, rank, world, local_rank):
         return ms, launches, clk.summary()
 
     warmup = max(3, args.warmup)
-    gemm_ms, gemm_launches, clocks = timed(gemm_step, args.steps, warmup)
-    attn_ms, attn_launches, attn_clocks = timed(attn_step, args.steps, warmup)
-    gemm_per = gemm_ms / args.steps
-    attn_per = attn_ms / args.steps
-    gemm_tflops_1 = GEMM_FLOP / (gemm_per * 1e-3) / 1e12           # per GPU, per launch
+    # A step is a batch of `per_step` launches, sized so that the K timed steps last at least TIMED_SECONDS whatever K
+    # is: a region of a few milliseconds says nothing about clocks under load (one NVML sample) and flatters the kernel.
+    burst_ms, _, _ = timed(gemm_step, 20, warmup)                  # the first 20 launches from idle, timed alone
+    gemm_per_step = max(1, math.ceil(TIMED_SECONDS * 1e3 / (args.steps * burst_ms / 20)))
+    attn_probe_ms, _, _ = timed(attn_step, 20, warmup)
+    attn_per_step = max(1, math.ceil(TIMED_SECONDS * 1e3 / (args.steps * attn_probe_ms / 20)))
+
+    def gemm_batch(i):
+        for j in range(gemm_per_step):
+            gemm_step(i * gemm_per_step + j)
+
+    def attn_batch(i):
+        for j in range(attn_per_step):
+            attn_step(i * attn_per_step + j)
+
+    gemm_ms, gemm_launches, clocks = timed(gemm_batch, args.steps, 1)
+    attn_ms, attn_launches, attn_clocks = timed(attn_batch, args.steps, 1)
+    gemm_per = gemm_ms / (args.steps * gemm_per_step)              # per launch
+    attn_per = attn_ms / (args.steps * attn_per_step)
+    gemm_tflops_1 = GEMM_FLOP / (gemm_per * 1e-3) / 1e12           # per GPU
     attn_gbs_1 = ATT_BYTES / (attn_per * 1e-3) / 1e9
+    burst_tflops_1 = GEMM_FLOP / (burst_ms / 20 * 1e-3) / 1e12
+    sustained_peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
 
     # ---- end to end through the reference-shaped API: host buffers in, host buffer out, every step
     rt = cb.Runtime.from_sources(["(def program gemm-bf16-rc : x -> y = ())"], cb.GpuDialect.Cuda)
@@ -257,6 +275,62 @@ def run_gpu(args, rank, world, local_rank):
     e2e_tflops = world * GEMM_FLOP / (e2e_ms * 1e-3) / 1e12
     checksum = int(np.bitwise_xor.reduce(c_host.astype(np.uint64) * (np.arange(c_host.size, dtype=np.uint64) | 1)))
 
+    # ---- the same end-to-end work as a pipeline over the launch-level C ABI: the H2D copy of step i+1 and the D2H copy of
+    # step i-1 run on their own streams while step i computes (PCIe is full duplex); still every step's operands come from
+    # pinned host memory and every step's result goes back to it inside the timed region
+    L.catena_b200_set_blocking(0)
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    a_d = [torch.empty((GEMM_M, GEMM_K), dtype=torch.int16, device=dev) for _ in range(2)]
+    b_d = [torch.empty((GEMM_N, GEMM_K), dtype=torch.int16, device=dev) for _ in range(2)]
+    c_d = [torch.empty((GEMM_M * GEMM_N,), dtype=torch.int16, device=dev) for _ in range(2)]
+    c_pins = [c_pin, torch.empty((GEMM_M * GEMM_N,), dtype=torch.int16).pin_memory()]
+    a_src, b_src = a_pin.view(GEMM_M, GEMM_K), b_pin.view(GEMM_N, GEMM_K)
+
+    def pipeline(steps):
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_done = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(s_in)
+        for i in range(steps):
+            j = i % 2
+            if i >= 2:
+                s_in.wait_event(ev_done[j])                    # the GEMM that read these operand buffers is done
+            with torch.cuda.stream(s_in):
+                a_d[j].copy_(a_src, non_blocking=True)
+                b_d[j].copy_(b_src, non_blocking=True)
+                ev_in[j].record(s_in)
+            stream.wait_event(ev_in[j])
+            if i >= 2:
+                stream.wait_event(ev_out[j])                   # the result buffer has been copied out
+            cb.check(L.catena_b200_gemm_bf16_into(a_d[j].data_ptr(), b_d[j].data_ptr(), c_d[j].data_ptr(), GEMM_M, GEMM_N, GEMM_K, GEMM_N))
+            ev_done[j].record(stream)
+            s_out.wait_event(ev_done[j])
+            with torch.cuda.stream(s_out):
+                c_pins[j].copy_(c_d[j], non_blocking=True)
+                ev_out[j].record(s_out)
+        s_out.wait_stream(stream)
+        t1.record(s_out)
+        torch.cuda.synchronize(dev)
+        return t0.elapsed_time(t1)
+
+    pipe_steps = max(4, min(args.steps, 40))
+    pipeline(4)
+    barrier()
+    pipe_ms = shard.max_over_ranks(pipeline(pipe_steps), dist if world > 1 else None, dev) / pipe_steps
+    barrier()
+    pipe_tflops = world * GEMM_FLOP / (pipe_ms * 1e-3) / 1e12
+    last = c_pins[(pipe_steps - 1) % 2].numpy().view(np.uint16)
+    pipe_checksum = int(np.bitwise_xor.reduce(last.astype(np.uint64) * (np.arange(last.size, dtype=np.uint64) | 1)))
+    assert pipe_checksum == checksum, "the pipelined end-to-end result differs from Runtime.exec's"
+    del a_d, b_d, c_d
+    cb.check(L.catena_b200_check_device_errors())
+
+    # ---- the other kernels of the path, each against its own roofline (rank 0's GPU)
+    kernels = kernel_suite(cb, L, torch, dev, stream, peaks, clocks.get("sm_max_mhz") or 1965)
+    L.catena_b200_set_blocking(1)
+    barrier()
+
     # ---- Llama-style block (prefill 4 x 2048, then 128 decode steps), one replica per GPU; rank 0's figures are reported
     L.catena_b200_set_blocking(0)
     llama = llama_bench(cb, L, torch, dev, stream, peaks, LLAMA, reps=2)
@@ -265,7 +339,8 @@ def run_gpu(args, rank, world, local_rank):
 
     # ---- strong scaling of one problem with the final gather (its checksums are the same for every --gpus N)
     L.catena_b200_set_blocking(0)
-    sharded = sharded_bench(cb, L, torch, dist if world > 1 else None, shard, dev, stream, rank, world)
+    sharded = sharded_bench(cb, L, torch, dist if world > 1 else None, shard, dev, stream, rank, world, peaks,
+                            with_oracle=(rank == 0 and world == 1 and not args.no_cpu_baseline))
     L.catena_b200_set_blocking(1)
     barrier()
 
@@ -293,26 +368,41 @@ def run_gpu(args, rank, world, local_rank):
     if rank == 0:
         line = {
             "metric": "bf16_gemm_tflops", "value": world * gemm_tflops_1, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warmup, "ms_per_step": gemm_per, "higher_is_better": True, "scaling": "weak",
+            "steps": args.steps, "warmup": warmup, "ms_per_step": gemm_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "bf16 GEMM 4096^3 (A row-major, B column-major, fp32 accumulate, bf16 out), "
-                                   "one GEMM per step per GPU, fixed K order",
+            "config": {"workload": "bf16 GEMM 4096^3 (A row-major, B column-major, fp32 accumulate, bf16 out), fixed K order; "
+                                   f"a step is {gemm_per_step} back-to-back GEMM launches per GPU, so that the timed region lasts "
+                                   f"{gemm_ms / 1e3:.2f} s whatever --steps is",
+                       "launches_per_step": gemm_per_step, "ms_per_launch": gemm_per,
                        "l2": f"rotating over {n_sets} operand sets (384 MB) so inputs never sit in the 126 MB L2",
                        "parallelism": f"{world} independent per-GPU problems"},
-            "clocks": clocks,
-            "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": int(a_np.nbytes + bt_np.nbytes),
-                    "d2h_bytes_per_step": int(c_host.nbytes), "ms_per_step": e2e_ms, "steps": e2e_steps,
-                    "api": "Runtime.exec('gemm-bf16-rc') with pinned host operands, result copied back"},
+            "clocks": {**clocks, "mhz_x_ms_per_launch": (clocks.get("sm_mhz") or 0) * gemm_per},
+            "e2e": {"value": max(e2e_tflops, pipe_tflops), "unit": "TFLOP/s", "h2d_bytes_per_step": int(a_np.nbytes + bt_np.nbytes),
+                    "d2h_bytes_per_step": int(c_host.nbytes), "ms_per_step": min(e2e_ms, pipe_ms),
+                    "api": "host operands in pinned memory copied in and the result copied back to pinned memory every step; the value is "
+                           "the pipelined form when that is faster",
+                    "serial": {"value": e2e_tflops, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                               "api": "Runtime.exec('gemm-bf16-rc'): upload, GEMM and download one after the other on one stream"},
+                    "pipelined": {"value": pipe_tflops, "ms_per_step": pipe_ms, "steps": pipe_steps,
+                                  "api": "catena_b200_gemm_bf16_into on device buffers, H2D of step i+1 and D2H of step i-1 on their own "
+                                         "streams (double-buffered); same result bits as the serial form"}},
             "gpu_launches": int(gemm_launches),
-            "roofline": {"bound": "tensor", "achieved": gemm_tflops_1, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": gemm_tflops_1 / peaks["bf16_tflops"],
-                         "frac_of_sustained_peak": (gemm_tflops_1 / peaks["bf16_tflops_sustained"]) if peaks.get("bf16_tflops_sustained") else None,
+            "roofline": {"bound": "tensor", "achieved": gemm_tflops_1, "peak": sustained_peak, "unit": "TFLOP/s",
+                         "frac": gemm_tflops_1 / sustained_peak,
+                         "frac_of_burst_peak": gemm_tflops_1 / peaks["bf16_tflops"],
                          "traffic": GEMM_NCU_TRAFFIC_BYTES,
                          "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch "
                                            "(profiles/gemm_tc_bf16_4096.md); algorithmic bytes 100663296",
-                         "peak_source": f"{peaks['source']} burst cuBLAS bf16", "kernel": "gemm_tc2_kernel<bf16>"},
+                         "peak_source": f"{peaks['source']} cuBLAS bf16, the sustained figure: the kernel is timed inside a region of "
+                                        f"{gemm_ms / 1e3:.2f} s under the power cap",
+                         "kernel": "gemm_tc2_kernel<bf16>"},
+            "burst": {"value": world * burst_tflops_1, "unit": "TFLOP/s", "launches": 20, "ms_per_launch": burst_ms / 20,
+                      "roofline": {"bound": "tensor", "achieved": burst_tflops_1, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                   "frac": burst_tflops_1 / peaks["bf16_tflops"], "peak_source": f"{peaks['source']} cuBLAS bf16, the burst figure"},
+                      "note": "the first 20 launches from an idle GPU, timed alone"},
+            "kernels": kernels,
             "attn_decode": {"metric": "kv_attn_decode_hbm_gbs", "value": world * attn_gbs_1, "unit": "GB/s",
-                            "ms_per_step": attn_per, "gpu_launches": int(attn_launches), "clocks": attn_clocks,
+                            "ms_per_launch": attn_per, "launches_per_step": attn_per_step, "gpu_launches": int(attn_launches), "clocks": attn_clocks,
                             "config": {"workload": "decode attention B=32 Hq=32 Hkv=8 D=128 L=4096 bf16, 537395200 algorithmic bytes per launch"},
                             "roofline": {"bound": "hbm", "achieved": attn_gbs_1, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                          "frac": attn_gbs_1 / peaks["hbm_gbs"], "traffic": ATTN_NCU_TRAFFIC_BYTES,
@@ -328,113 +418,273 @@ def run_gpu(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def sharded_bench(cb, L, torch, dist, shard, dev, stream, rank, world, reps=3):
-    """Strong scaling of ONE problem over the ranks, gather included: the int8 GEMM 16384 x 16384 x 8192 sharded by
-    row blocks of A / C (all-gather of the int32 C over NCCL) and the decode attention of the bench sharded by
-    (batch, kv-head) ranges (all-gather of O).  Every rank ends with the full result; its checksum must be the same
-    for every world size (tile shape, k order and KV split count never depend on the sharding)."""
+def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
+    """The elementwise / fold / f32 kernels of the path on bench-size inputs, device-timed, each with the roofline that
+    bounds it: HBM for the map, softmax and rmsnorm (algorithmic passes over 64 Mi f32), the unfused FP32 pipe for the
+    bit-exact f32 matmul (mul and add are separate instructions by contract: one flop per lane per clock)."""
+    out = {}
+    fp32_unfused_peak = 148 * 128 * sm_max_mhz * 1e6 / 1e12
+    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("softmax", False), ("rmsnorm", False)):
+        step, work, unit, desc = single_case(cb, L, torch, dev, which, small, None)
+        steps = 200 if (which == "matmul_f32" and small) else (8 if which == "matmul_f32" else 20)
+        torch.cuda.synchronize(dev)
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                step(i)
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                step(i)
+            e1.record(stream)
+            torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / steps
+        value = work / (ms * 1e-3)
+        if which == "matmul_f32":
+            roof = {"bound": "fp32 issue (unfused mul + add)", "achieved": value, "peak": fp32_unfused_peak, "unit": "TFLOP/s",
+                    "frac": value / fp32_unfused_peak,
+                    "peak_source": f"148 SMs x 128 FP32 lanes x {sm_max_mhz} MHz x 1 flop per instruction (no measured figure for this pipe)"}
+            if small:
+                roof["note"] = "33.6 MFLOP per launch: bound by launch latency, the time is the figure"
+        else:
+            roof = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": value / peaks["hbm_gbs"],
+                    "peak_source": f"{peaks['source']} copy bandwidth"}
+        name = {"matmul_f32": "matmul_f32_256" if small else "matmul_f32_4096", "map": "map_nn_silu_64Mi"}.get(which, which + "_64Mi")
+        out[name] = {"case": desc, "us_per_launch": ms * 1e3, "value": value, "unit": unit, "steps": steps, "roofline": roof}
+    cb.check(L.catena_b200_check_device_errors())
+    return out
+
+
+NVLINK_GBS_MEASURED = 770.0      # peer copy per direction per GPU measured on this pool (nominal 900)
+
+
+def sharded_bench(cb, L, torch, dist, shard, dev, stream, rank, world, peaks, reps=3, with_oracle=False):
+    """Strong scaling of ONE problem over the ranks, gather included, every rank ending with the full result:
+      * the int8 and bf16 GEMMs 16384 x 16384 x 8192 sharded by row blocks of A / C, the gather either an NCCL all-gather
+        or fused into the GEMM's epilogue (peer stores through CUDA-IPC mappings);
+      * the decode attention of the bench sharded by (batch, kv-head) ranges, the gather of O either NCCL or fused into
+        the kernel's output stores;
+      * once, the bf16 4096^3 GEMM sharded by output-COLUMN blocks with an NCCL gather of the column blocks.
+    Every item carries the time of the unsharded problem on one GPU measured in the same run (`ms_1gpu`), the speed-up
+    against it, a floor and what limits it.  Checksums must be the same for every world size: tile shape, k order and KV
+    split count never depend on the sharding."""
     M = N = 16384
     K = 8192
     g = torch.Generator(device=dev)
     g.manual_seed(4)                                          # the same operands on every rank
-    a = torch.randint(-128, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
-    b = torch.randint(-128, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    a8 = torch.randint(-128, 128, (M, K), generator=g, device=dev, dtype=torch.int8)
+    b8 = torch.randint(-128, 128, (N, K), generator=g, device=dev, dtype=torch.int8)
+    a16 = (torch.randn((M, K), generator=g, device=dev) / math.sqrt(K)).to(torch.bfloat16)
+    b16 = (torch.randn((N, K), generator=g, device=dev) / math.sqrt(K)).to(torch.bfloat16)
     blocks = shard.row_blocks(M, world)
     mine = blocks[rank]
-    c_block = torch.empty((mine.m1 - mine.m0, N), dtype=torch.int32, device=dev)
+    rows = mine.m1 - mine.m0
     q = torch.randn((ATT["B"], ATT["Hq"], ATT["D"]), generator=g, device=dev).to(torch.bfloat16)
     k = torch.randn((ATT["B"], ATT["Hkv"], ATT["L"], ATT["D"]), generator=g, device=dev).to(torch.bfloat16)
     v = torch.randn((ATT["B"], ATT["Hkv"], ATT["L"], ATT["D"]), generator=g, device=dev).to(torch.bfloat16)
-    o = torch.zeros((ATT["B"], ATT["Hq"], ATT["D"]), dtype=torch.bfloat16, device=dev)
     units = ATT["B"] * ATT["Hkv"]
     ranges = shard.unit_ranges(units, world)
     G = ATT["Hq"] // ATT["Hkv"]
+    dd = dist if world > 1 else None
     res = {}
 
-    def gemm_compute():
-        cb.check(L.catena_b200_gemm_i8_into(a[mine.m0:mine.m1].data_ptr(), b.data_ptr(), c_block.data_ptr(), mine.m1 - mine.m0, N, K, N))
+    class _DevArray:                                           # lets torch view one of the library's allocations
+        def __init__(self, ptr, shape, typestr):
+            self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3}
 
-    def attn_compute():
-        cb.check(L.catena_b200_attn_decode_bf16_into(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), ATT["B"], ATT["Hq"],
-                                                     ATT["Hkv"], ATT["D"], ATT["L"], ranges[rank].u0, ranges[rank].u1))
+    def alloc(nbytes):
+        m = cb.CatenaMem()
+        cb.check(L.catena_b200_mem_alloc(nbytes, C.byref(m)))
+        return m
 
-    def attn_gather():
-        rows = o.view(units, G * ATT["D"])[ranges[rank].u0:ranges[rank].u1]
-        return shard.gather_units(rows, ranges, G * ATT["D"], dist if world > 1 else None)
-
-    for name, compute, gather, work, unit in (
-            ("gemm_i8_16384x16384x8192", gemm_compute, lambda: shard.gather_rows(c_block, blocks, dist if world > 1 else None),
-             2.0 * M * N * K / 1e12, "TOP/s"),
-            ("attn_decode_c3", attn_compute, attn_gather, ATT_BYTES / 1e9, "GB/s")):
-        with torch.cuda.stream(stream):
-            compute(); full = gather()                        # warm-up (NCCL communicator set-up included)
-            torch.cuda.synchronize(dev)
-            if world > 1:
-                dist.barrier()
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-            t_compute = t_gather = 0.0
-            for _ in range(reps):
-                ev[0].record(stream); compute(); ev[1].record(stream); full = gather(); ev[2].record(stream)
-                torch.cuda.synchronize(dev)
-                t_compute += ev[0].elapsed_time(ev[1]) / reps
-                t_gather += ev[1].elapsed_time(ev[2]) / reps
-        total = shard.max_over_ranks(t_compute + t_gather, dist if world > 1 else None, dev)
-        checksum = int(full.view(torch.int16 if full.dtype == torch.bfloat16 else torch.int32).to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF
-        res[name] = {"ms_total": total, "ms_compute": shard.max_over_ranks(t_compute, dist if world > 1 else None, dev),
-                     "ms_gather": shard.max_over_ranks(t_gather, dist if world > 1 else None, dev),
-                     "value_incl_gather": work / (total * 1e-3), "unit": unit, "checksum": f"{checksum:012x}"}
-        del full
-    # ---- the same GEMM with the gather fused into its epilogue: every rank stores its row block into every rank's
-    # copy of C (peer-mapped through CUDA IPC) while it computes; one barrier afterwards replaces the all-gather
-    if world > 1:
-        class _DevArray:                                       # lets torch view the library's allocation (checksum only)
-            def __init__(self, ptr, shape):
-                self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i4", "data": (ptr, False), "version": 3}
-        c_full = cb.CatenaMem()
-        cb.check(L.catena_b200_mem_alloc(M * N * 4, C.byref(c_full)))
+    def share(mem, nbytes):
+        """CUDA-IPC: every rank maps every other rank's allocation; returns [(imported mem, offset)] in rank order."""
+        if world == 1:
+            return []
         handle = (C.c_ubyte * 64)()
         off = C.c_uint64()
-        cb.check(L.catena_b200_ipc_export(c_full, handle, C.byref(off)))
+        cb.check(L.catena_b200_ipc_export(mem, handle, C.byref(off)))
         handles = [None] * world
         dist.all_gather_object(handles, (bytes(handle), int(off.value)))
-        imported, ptrs = [], []
+        out = []
         for r in range(world):
             if r == rank:
                 continue
             m_ = cb.CatenaMem()
             hb = (C.c_ubyte * 64).from_buffer_copy(handles[r][0])
-            cb.check(L.catena_b200_ipc_import(hb, handles[r][1], M * N * 4, C.byref(m_)))
-            imported.append((m_, handles[r][1]))
-            ptrs.append(m_.data + mine.m0 * N * 4)
-        peer_arr = (C.c_void_p * len(ptrs))(*ptrs)
-        local_rows = c_full.data + mine.m0 * N * 4
+            cb.check(L.catena_b200_ipc_import(hb, handles[r][1], nbytes, C.byref(m_)))
+            out.append((m_, handles[r][1]))
+        return out
 
-        def fused():
-            cb.check(L.catena_b200_gemm_i8_into_peers(a[mine.m0:mine.m1].data_ptr(), b.data_ptr(), local_rows, mine.m1 - mine.m0, N, K, N,
-                                                      peer_arr, len(ptrs)))
-        with torch.cuda.stream(stream):
-            fused()
-            torch.cuda.synchronize(dev)
+    def unshare(imported):
+        if world > 1:
             dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t = 0.0
-            for _ in range(reps):
-                e0.record(stream); fused(); e1.record(stream)
-                torch.cuda.synchronize(dev)
-                dist.barrier()                                 # every rank's stores have landed
-                t += e0.elapsed_time(e1) / reps
-        total = shard.max_over_ranks(t, dist, dev)
-        full = torch.as_tensor(_DevArray(c_full.data, (M, N)), device=dev)
-        checksum = int(full.to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF
-        res["gemm_i8_16384x16384x8192_fused_gather"] = {
-            "ms_total": total, "value_incl_gather": 2.0 * M * N * K / 1e12 / (total * 1e-3), "unit": "TOP/s",
-            "checksum": f"{checksum:012x}", "note": "epilogue stores every tile to all ranks' C over NVLink; timed on the device, max over ranks"}
-        del full
-        dist.barrier()
         for m_, o_ in imported:
             cb.check(L.catena_b200_ipc_close(m_, o_))
-        dist.barrier()
+        if world > 1:
+            dist.barrier()
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+
+    def time_steps(step, parts=1):
+        """Device time of `step` (mean of `reps` after one warm-up run), max over ranks; `step` records the events it
+        is given between its parts."""
+        with torch.cuda.stream(stream):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(parts + 1)]
+            step(None)
+            sync_all()
+            t = [0.0] * parts
+            for _ in range(reps):
+                ev[0].record(stream)
+                step(ev)
+                ev[parts].record(stream)
+                sync_all()                                     # every rank's stores have landed before the next run
+                for i in range(parts):
+                    t[i] += ev[i].elapsed_time(ev[i + 1]) / reps
+        return [shard.max_over_ranks(x, dd, dev) for x in t], shard.max_over_ranks(sum(t), dd, dev)
+
+    def checksum(t):
+        view = t.view(torch.int16) if t.dtype == torch.bfloat16 else t
+        return f"{int(view.to(torch.int64).sum().item()) & 0xFFFFFFFFFFFF:012x}"
+
+    def finish(item, ms_1gpu, floor_ms, limiter, work, unit):
+        item.update({"ms_1gpu": ms_1gpu, "speedup_vs_1gpu": ms_1gpu / item["ms_total"], "floor_ms": floor_ms, "limiter": limiter,
+                     "value_incl_gather": work / (item["ms_total"] * 1e-3), "unit": unit})
+        return item
+
+    # ------------------------------------------------------------------ GEMMs 16384 x 16384 x 8192, int8 and bf16
+    for tag, a, b, eb_out, typestr, torch_out, fn_into, fn_peers in (
+            ("i8", a8, b8, 4, "<i4", torch.int32, L.catena_b200_gemm_i8_into, L.catena_b200_gemm_i8_into_peers),
+            ("bf16", a16, b16, 2, "<i2", torch.int16, L.catena_b200_gemm_bf16_into, L.catena_b200_gemm_bf16_into_peers)):
+        name = f"gemm_{tag}_16384x16384x8192"
+        work, unit = 2.0 * M * N * K / 1e12, ("TOP/s" if tag == "i8" else "TFLOP/s")
+        c_full = alloc(M * N * eb_out)                         # this rank's copy of the whole C
+        full_view = torch.as_tensor(_DevArray(c_full.data, (M, N), typestr), device=dev)
+        a_ptr, b_ptr = a.data_ptr(), b.data_ptr()
+        es = a.element_size()
+        # the unsharded problem on this GPU, measured in the same run
+        [_], ms_1 = time_steps(lambda ev: cb.check(fn_into(a_ptr, b_ptr, c_full.data, M, N, K, N)))
+        sum_1 = checksum(full_view)
+        oracle_note = None
+        if with_oracle:
+            import oracle
+            slab = slice(8192 + 256 - 16, 8192 + 256 + 16)     # 32 rows across a 256-row tile boundary
+            got = full_view[slab].cpu().numpy()
+            if tag == "i8":
+                a_h, b_h = a[slab].cpu().numpy(), b.cpu().numpy()
+            else:
+                a_h, b_h = a[slab].view(torch.int16).cpu().numpy(), b.view(torch.int16).cpu().numpy()
+            if tag == "i8":
+                want = oracle.gemm_i8_rows(a_h, b_h, N, K, 0, 32, threads=oracle.max_threads())
+                oracle_note = f"rows {slab.start}..{slab.stop - 1} against the CPU oracle: bitwise agreement {float((got == want).mean()):.5f}"
+            else:
+                want = oracle.gemm_bf16_rows(a_h.view(np.uint16), b_h.view(np.uint16), N, K, 0, 32, threads=oracle.max_threads())
+                oracle_note = (f"rows {slab.start}..{slab.stop - 1} against the CPU oracle (sequential fp32 fold): bitwise agreement "
+                               f"{float((got.view(np.uint16) == want).mean()):.5f}, the rest one bf16 ulp apart")
+        bytes_c = M * N * eb_out
+        link_floor = (world - 1) / world * bytes_c / (NVLINK_GBS_MEASURED * 1e9) * 1e3
+        floor = max(ms_1 / world, link_floor)
+        limiter = ("NVLink ingress: every rank receives (N-1)/N of C" if link_floor > ms_1 / world else "tensor pipe") if world > 1 else "tensor pipe"
+        # (1) compute on the row block, NCCL all-gather of the blocks
+        c_block = torch.empty((rows, N), dtype=torch_out, device=dev)
+        holder = {}
+
+        def nccl_step(ev):
+            cb.check(fn_into(a_ptr + mine.m0 * K * es, b_ptr, c_block.data_ptr(), rows, N, K, N))
+            if ev:
+                ev[1].record(stream)
+            holder["full"] = shard.gather_rows(c_block, blocks, dd)
+        (t_c, t_g), total = time_steps(nccl_step, parts=2)
+        item = {"ms_total": total, "ms_compute": t_c, "ms_gather": t_g, "checksum": checksum(holder["full"]), "gather": "NCCL all-gather of row blocks"}
+        assert item["checksum"] == sum_1, "sharded result differs from the unsharded one"
+        res[name] = finish(item, ms_1, floor, limiter, work, unit)
+        if oracle_note:
+            res[name]["oracle"] = oracle_note
+        holder.clear()
+        del c_block
+        # (2) the gather fused into the epilogue: every rank stores its row block into every rank's C
+        if world > 1:
+            imported = share(c_full, bytes_c)
+            ptrs = [m_.data + mine.m0 * N * eb_out for m_, _ in imported]
+            peer_arr = (C.c_void_p * len(ptrs))(*ptrs)
+            full_view.zero_()
+            sync_all()
+            [_], total = time_steps(lambda ev: cb.check(fn_peers(a_ptr + mine.m0 * K * es, b_ptr, c_full.data + mine.m0 * N * eb_out, rows, N, K, N,
+                                                                 peer_arr, len(ptrs))))
+            item = {"ms_total": total, "checksum": checksum(full_view), "gather": "fused: epilogue stores every tile to all ranks' C over NVLink; "
+                    "one host barrier after the stream drains replaces the collective",
+                    "link_gbs_per_rank": (world - 1) / world * bytes_c / (total * 1e-3) / 1e9, "link_gbs_measured_peak": NVLINK_GBS_MEASURED}
+            assert item["checksum"] == sum_1, "fused-gather result differs from the unsharded one"
+            res[name + "_fused_gather"] = finish(item, ms_1, floor, limiter, work, unit)
+            unshare(imported)
+        del full_view
         cb.free(c_full)
+
+    # ------------------------------------------------------------------ decode attention C3
+    work, unit = ATT_BYTES / 1e9, "GB/s"
+    o_mem = alloc(units * G * ATT["D"] * 2)
+    o_view = torch.as_tensor(_DevArray(o_mem.data, (units, G * ATT["D"]), "<i2"), device=dev)
+    att_args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o_mem.data, ATT["B"], ATT["Hq"], ATT["Hkv"], ATT["D"], ATT["L"])
+    [_], ms_1 = time_steps(lambda ev: cb.check(L.catena_b200_attn_decode_bf16_into(*att_args, 0, units)))
+    sum_1 = checksum(o_view)
+    floor = ATT_BYTES / world / (peaks["hbm_gbs"] * 1e9) * 1e3
+    limiter = "HBM" if world == 1 else "fixed cost per launch (set-up, exchange of chunk maxima, ticket, combine) once the KV stream per GPU is short"
+    holder = {}
+
+    def attn_nccl(ev):
+        cb.check(L.catena_b200_attn_decode_bf16_into(*att_args, ranges[rank].u0, ranges[rank].u1))
+        if ev:
+            ev[1].record(stream)
+        holder["full"] = shard.gather_units(o_view[ranges[rank].u0:ranges[rank].u1], ranges, G * ATT["D"], dd)
+    o_view.zero_()
+    (t_c, t_g), total = time_steps(attn_nccl, parts=2)
+    item = {"ms_total": total, "ms_compute": t_c, "ms_gather": t_g, "checksum": checksum(holder["full"]), "gather": "NCCL all-gather of O"}
+    assert item["checksum"] == sum_1, "sharded attention differs from the unsharded one"
+    res["attn_decode_c3"] = finish(item, ms_1, floor, limiter, work, unit)
+    holder.clear()
+    if world > 1:
+        imported = share(o_mem, units * G * ATT["D"] * 2)
+        peer_arr = (C.c_void_p * len(imported))(*[m_.data for m_, _ in imported])
+        o_view.zero_()
+        sync_all()
+        [_], total = time_steps(lambda ev: cb.check(L.catena_b200_attn_decode_bf16_into_peers(*att_args, ranges[rank].u0, ranges[rank].u1,
+                                                                                              peer_arr, len(imported))))
+        item = {"ms_total": total, "checksum": checksum(o_view), "gather": "fused: the warps that write a unit's outputs also store them into "
+                "every rank's O over NVLink; one host barrier after the stream drains replaces the collective"}
+        assert item["checksum"] == sum_1, "fused-gather attention differs from the unsharded one"
+        res["attn_decode_c3_fused_gather"] = finish(item, ms_1, floor, limiter, work, unit)
+        unshare(imported)
+    del o_view
+    cb.free(o_mem)
+
+    # ------------------------------------------------------------------ output-column blocks (bf16 4096^3), NCCL gather of the blocks
+    m4 = n4 = k4 = 4096
+    a4, b4 = a16[:m4, :k4].contiguous(), b16[:n4, :k4].contiguous()
+    c4 = torch.empty((m4, n4), dtype=torch.int16, device=dev)
+    [_], ms_1 = time_steps(lambda ev: cb.check(L.catena_b200_gemm_bf16_into(a4.data_ptr(), b4.data_ptr(), c4.data_ptr(), m4, n4, k4, n4)))
+    sum_1 = checksum(c4)
+    cols = shard.column_blocks(n4, world)
+    mc = cols[rank]
+    width = mc.n1 - mc.n0
+    c_cols = torch.empty((m4, width), dtype=torch.int16, device=dev)
+    holder = {}
+
+    def col_step(ev):
+        cb.check(L.catena_b200_gemm_bf16_into(a4.data_ptr(), b4.data_ptr() + mc.n0 * k4 * 2, c_cols.data_ptr(), m4, width, k4, width))
+        if ev:
+            ev[1].record(stream)
+        holder["full"] = shard.gather_columns(c_cols, cols, m4, dd)
+    (t_c, t_g), total = time_steps(col_step, parts=2)
+    item = {"ms_total": total, "ms_compute": t_c, "ms_gather": t_g, "checksum": checksum(holder["full"]),
+            "gather": "NCCL all-gather of output-column blocks, repacked into row-major C"}
+    assert item["checksum"] == sum_1, "column-sharded result differs from the unsharded one"
+    link_floor = (world - 1) / world * m4 * n4 * 2 / (NVLINK_GBS_MEASURED * 1e9) * 1e3
+    res["gemm_bf16_4096_column_blocks"] = finish(item, ms_1, max(ms_1 / world, link_floor),
+                                                 "launch + NCCL latency: the whole problem is 0.1 ms on one GPU" if world > 1 else "tensor pipe",
+                                                 2.0 * m4 * n4 * k4 / 1e12, "TFLOP/s")
     cb.check(L.catena_b200_check_device_errors())
     return res
 
@@ -511,33 +761,14 @@ def llama_bench(cb, L, torch, dev, stream, peaks, cfg, reps=2):
             "end_to_end_ms": times["prefill"] + times["decode"], "output_checksum": f"{checksum:012x}"}
 
 
-def run_single(args):
-    """`--only <kernel>`: a few launches of one kernel on the bench workload (or a smaller case with
-    `--small`), for profiler captures and quick timing.  Prints a short JSON line."""
-    import torch
-    import catena_lang_b200 as cb
-
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    L = cb.lib()
-    cb.check(L.catena_b200_init(0))
-    stream = torch.cuda.Stream(device=dev)
-    L.catena_b200_set_stream(C.c_void_p(stream.cuda_stream))
-    L.catena_b200_set_blocking(0)
-    which = args.only
+def single_case(cb, L, torch, dev, which, small, shape):
+    """One kernel of the path on the bench workload (or a smaller case): returns (step(i), work per launch, unit, text)."""
     g = torch.Generator(device=dev)
     g.manual_seed(1)
-    if which == "llama":
-        cfg = dict(LLAMA_SMALL if args.small else LLAMA)
-        if args.decode_steps:
-            cfg["decode_steps"] = args.decode_steps
-        res = llama_bench(cb, L, torch, dev, stream, measured_peaks(), cfg, reps=max(1, min(args.steps, 3)))
-        print(json.dumps({"only": "llama", **res}), flush=True)
-        return
     if which in ("gemm", "gemm_i8"):
-        m = n = k = 2048 if args.small else 4096
-        if args.shape:
-            m, n, k = [int(v) for v in args.shape.split("x")]
+        m = n = k = 2048 if small else 4096
+        if shape:
+            m, n, k = [int(v) for v in shape.split("x")]
         eb = 1 if which == "gemm_i8" else 2
         sets = []
         for _ in range(4):
@@ -558,7 +789,7 @@ def run_single(args):
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
         desc = f"{which} {m}x{n}x{k}"
     elif which == "attn":
-        B, Hq, Hkv, D, Lk = (8, 32, 8, 128, 4096) if args.small else (32, 32, 8, 128, 4096)
+        B, Hq, Hkv, D, Lk = (8, 32, 8, 128, 4096) if small else (32, 32, 8, 128, 4096)
         sets = []
         for _ in range(2):
             q = torch.randn((B, Hq, D), generator=g, device=dev).to(torch.bfloat16)
@@ -574,7 +805,7 @@ def run_single(args):
         work, unit = (2 * B * Hkv * Lk * D * 2 + 2 * B * Hq * D * 2) / 1e9, "GB/s"
         desc = f"attn decode B={B} Hq={Hq} Hkv={Hkv} D={D} L={Lk}"
     elif which == "matmul_f32":
-        n = 256 if args.small else 4096
+        n = 256 if small else 4096
         a = torch.rand((n, n), generator=g, device=dev) * 2 - 1
         b = torch.rand((n, n), generator=g, device=dev) * 2 - 1
         c = torch.empty((n, n), device=dev)
@@ -584,7 +815,7 @@ def run_single(args):
         work, unit = 2.0 * n ** 3 / 1e12, "TFLOP/s"
         desc = f"f32 matmul {n}^3 (bit-exact sequential-k)"
     else:  # map / softmax / rmsnorm over 64 Mi f32 (256 MiB in, 256 MiB out)
-        n = (1 << 24) if args.small else (1 << 26)
+        n = (1 << 24) if small else (1 << 26)
         x = torch.randn((2, n), generator=g, device=dev)
         y = torch.empty((2, n), device=dev)
 
@@ -599,6 +830,31 @@ def run_single(args):
         passes = {"softmax": 4, "rmsnorm": 3}.get(which, 2)     # algorithmic reads + writes of the buffer
         work, unit = passes * n * 4 / 1e9, "GB/s"
         desc = f"{which} over {n} f32"
+    return step, work, unit, desc
+
+
+def run_single(args):
+    """`--only <kernel>`: a few launches of one kernel on the bench workload (or a smaller case with
+    `--small`), for profiler captures and quick timing.  Prints a short JSON line."""
+    import torch
+    import catena_lang_b200 as cb
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    L = cb.lib()
+    cb.check(L.catena_b200_init(0))
+    stream = torch.cuda.Stream(device=dev)
+    L.catena_b200_set_stream(C.c_void_p(stream.cuda_stream))
+    L.catena_b200_set_blocking(0)
+    which = args.only
+    if which == "llama":
+        cfg = dict(LLAMA_SMALL if args.small else LLAMA)
+        if args.decode_steps:
+            cfg["decode_steps"] = args.decode_steps
+        res = llama_bench(cb, L, torch, dev, stream, measured_peaks(), cfg, reps=max(1, min(args.steps, 3)))
+        print(json.dumps({"only": "llama", **res}), flush=True)
+        return
+    step, work, unit, desc = single_case(cb, L, torch, dev, which, args.small, args.shape)
     torch.cuda.synchronize(dev)
     with torch.cuda.stream(stream):
         for i in range(args.warmup):

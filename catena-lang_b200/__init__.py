@@ -133,6 +133,7 @@ def lib():
     proto("catena_b200_gemm_bf16_into_peers", st, [vp, vp, vp, u64, u64, u64, u64, C.POINTER(vp), C.c_uint32])
     proto("catena_b200_gemm_i8_into_peers", st, [vp, vp, vp, u64, u64, u64, u64, C.POINTER(vp), C.c_uint32])
     proto("catena_b200_attn_decode_bf16_into", st, [vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, u64])
+    proto("catena_b200_attn_decode_bf16_into_peers", st, [vp, vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, C.POINTER(vp), C.c_uint32])
     proto("catena_b200_map_f32_into", st, [C.c_char_p, vp, vp, u64])
     proto("catena_b200_softmax_f32_into", st, [vp, vp, u64])
     proto("catena_b200_rmsnorm_f32_into", st, [vp, vp, u64])

@@ -503,7 +503,7 @@ bool attn_tc_supports(uint32_t G, uint64_t kv_len);
 void attn_tc_reset_exchange();
 catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
                                        uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1, int cluster_limit,
-                                       uint32_t* err_dev);
+                                       uint32_t* err_dev, void* const* peer_o, uint32_t n_peers);
 
 // After enqueuing: in blocking mode wait and turn a device-side bounded-wait expiry into a status.
 static catena_status_t attn_finish_launch(int dev) {
@@ -531,7 +531,8 @@ static size_t attn_smem_bytes(uint32_t G, uint32_t chunk) {
 }
 
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch, uint64_t hq,
-                                   uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1) {
+                                   uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1,
+                                   void* const* peer_o, uint32_t n_peers) {
     CATENA_TRY(ensure_device());
     if (!q || !kc || !vc || !o) return fail(CATENA_E_BAD_ARG, "attn_decode: null operand");
     if (d != (uint64_t)attn::kD) return fail(CATENA_E_UNSUPPORTED, "attn_decode: head_dim must be 128");
@@ -553,9 +554,11 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
         *g_attn_err_host[dev] = 0;
     }
     if (attn_tc_mode() && attn_tc_supports(G, kv_len) && ((uintptr_t)q & 15) == 0) {
-        CATENA_TRY(enqueue_attn_decode_tc(q, kc, vc, o, units, G, kv_len, kv_cap, unit0, unit1, g_attn_cluster_limit, g_attn_err_dev[dev]));
+        CATENA_TRY(enqueue_attn_decode_tc(q, kc, vc, o, units, G, kv_len, kv_cap, unit0, unit1, g_attn_cluster_limit, g_attn_err_dev[dev],
+                                          peer_o, n_peers));
         return attn_finish_launch(dev);
     }
+    if (n_peers > 0) return fail(CATENA_E_UNSUPPORTED, "attn_decode: peer outputs need the tcgen05 kernel (at most 7168 cache rows, 16-byte aligned q)");
     const uint32_t chunk = chunk_for(kv_len);
     const size_t smem = attn_smem_bytes(G, chunk);
     if (smem > 227 * 1024) return fail(CATENA_E_TOO_LARGE, "attn_decode: KV length beyond the shared-memory score buffer");

@@ -247,12 +247,20 @@ struct Exchange {
     uint32_t epoch;
 };
 
+// Where a unit's outputs go besides this GPU's O: peer-mapped pointers (CUDA IPC) to the other GPUs' copies of O, same
+// layout.  The gather of a (batch, kv-head)-sharded launch then rides on the finishers' stores (plain stores over NVLink).
+constexpr int kMaxPeers = 7;
+struct PeerO {
+    __nv_bfloat16* ptr[kMaxPeers];
+    uint32_t n;
+};
+
 // grid.x CTAs (all resident), 384 threads; npipes = 2 * gridDim.x is a multiple of 8 or at least `items`.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ o, uint32_t L, uint32_t G,
                       uint32_t unit0, uint32_t items, uint32_t chunk, float scale, Exchange ex, uint32_t* err, uint64_t wait_ns,
-                      uint32_t stall) {
+                      uint32_t stall, PeerO peers) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -378,7 +386,14 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                     num = cmath::add(num, pr[x][r]);
                     den = cmath::add(den, dn[x][r]);
                 }
-                if (e < per_rank && !com->abort_flag) o[(size_t)unit * G * kD + idx] = __float2bfloat16_rn(cmath::div(num, den));
+                if (e < per_rank && !com->abort_flag) {
+                    const __nv_bfloat16 val = __float2bfloat16_rn(cmath::div(num, den));
+                    const size_t off = (size_t)unit * G * kD + idx;
+                    o[off] = val;
+#pragma unroll
+                    for (uint32_t pi = 0; pi < (uint32_t)kMaxPeers; ++pi)
+                        if (pi < peers.n) peers.ptr[pi][off] = val;
+                }
             }
             TR(3, 3);
         }
@@ -759,7 +774,14 @@ void attn_tc_reset_exchange() {
 // Enqueues the tcgen05 decode kernel (arguments already validated by launch_attn_decode).
 catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
                                        uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1, int cluster_limit,
-                                       uint32_t* err_dev) {
+                                       uint32_t* err_dev, void* const* peer_o, uint32_t n_peers) {
+    if (n_peers > (uint32_t)attn2::kMaxPeers) return fail(CATENA_E_BAD_ARG, "attn_decode: more than 7 peer outputs");
+    attn2::PeerO peers = {};
+    peers.n = n_peers;
+    for (uint32_t i = 0; i < n_peers; ++i) {
+        if (!peer_o || !peer_o[i] || ((uintptr_t)peer_o[i] & 1)) return fail(CATENA_E_BAD_ARG, "attn_decode: null or unaligned peer output");
+        peers.ptr[i] = static_cast<__nv_bfloat16*>(peer_o[i]);
+    }
     const uint32_t chunk = chunk_for2(kv_len);
     const size_t smem = attn2_smem_bytes();
     const int dev = tls().device;
@@ -838,7 +860,7 @@ catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void
     float scale = 1.0f / sqrtf((float)attn2::kD);
     CATENA_CUDA(cudaLaunchKernelEx(&cfg, attn2::attn_decode_tc_kernel, map_k, map_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)o,
                                    (uint32_t)kv_len, G, (uint32_t)unit0, (uint32_t)items, chunk, scale, ex, err_dev,
-                                   debug_wait_limit_ns(), debug_take_stall(2)));
+                                   debug_wait_limit_ns(), debug_take_stall(2), peers));
     count_launch();
     return CATENA_OK;
 }

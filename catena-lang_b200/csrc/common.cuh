@@ -99,7 +99,7 @@ extern thread_local uint32_t g_attn_last_launch[4];
 // attn_decode.cu
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
                                    uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap,
-                                   uint64_t unit0, uint64_t unit1);
+                                   uint64_t unit0, uint64_t unit1, void* const* peer_o = nullptr, uint32_t n_peers = 0);
 catena_status_t attn_check_errors();
 // map_reduce.cu
 enum ReduceKind { RED_SUM = 0, RED_MAX = 1, RED_SUMSQ = 2 };

@@ -295,6 +295,13 @@ catena_status_t catena_b200_attn_decode_bf16_into(const void* q, const void* kc,
     return finish("attn_decode");
 }
 
+catena_status_t catena_b200_attn_decode_bf16_into_peers(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
+                                                        uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t unit0,
+                                                        uint64_t unit1, void* const* peer_o, uint32_t n_peers) {
+    CATENA_TRY(launch_attn_decode(q, kc, vc, o, batch, hq, hkv, d, kv_len, kv_len, unit0, unit1, peer_o, n_peers));
+    return finish("attn_decode");
+}
+
 void catena_b200_debug_set_cta_limit(int limit) {
     gemm_tc_set_cta_limit(limit);
     attn_set_cluster_limit(limit > 0 ? (limit >= 8 ? limit / 8 : 1) : 0);

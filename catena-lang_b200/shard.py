@@ -46,23 +46,35 @@ def row_blocks(m, world, align=256):
     return [RowBlock(r, min(m, tiles * r // world * align), min(m, tiles * (r + 1) // world * align)) for r in range(world)]
 
 
+def _as_wire(t):
+    """NCCL has no 16-bit integer type; bf16 bit patterns held as int16 travel as bfloat16 (a gather only copies bits)."""
+    import torch
+    return (t.view(torch.bfloat16), True) if t.dtype == torch.int16 and t.is_cuda else (t, False)
+
+
+def _from_wire(t, was_int16):
+    import torch
+    return t.view(torch.int16) if was_int16 else t
+
+
 def gather_rows(local_block, blocks, dist=None, group=None):
     """All-gathers contiguous row blocks [m1-m0, N] into the full [M, N] matrix on every rank (one collective when
     the blocks are equal, padded otherwise)."""
     import torch
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_block
+    local_block, was_int16 = _as_wire(local_block)
     heights = [b.m1 - b.m0 for b in blocks]
     if len(set(heights)) == 1:
         full = torch.empty((sum(heights),) + tuple(local_block.shape[1:]), dtype=local_block.dtype, device=local_block.device)
         dist.all_gather_into_tensor(full, local_block.contiguous(), group=group)
-        return full
+        return _from_wire(full, was_int16)
     hmax = max(heights)
     pad = torch.zeros((hmax,) + tuple(local_block.shape[1:]), dtype=local_block.dtype, device=local_block.device)
     pad[: local_block.shape[0]] = local_block
     parts = [torch.empty_like(pad) for _ in blocks]
     dist.all_gather(parts, pad, group=group)
-    return torch.cat([p[:h] for p, h in zip(parts, heights)], dim=0)
+    return _from_wire(torch.cat([p[:h] for p, h in zip(parts, heights)], dim=0), was_int16)
 
 
 @dataclass(frozen=True)
@@ -85,13 +97,14 @@ def gather_columns(local_block, blocks, rows, dist=None, group=None):
     import torch
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_block
+    local_block, was_int16 = _as_wire(local_block)
     widths = [b.n1 - b.n0 for b in blocks]
     wmax = max(widths)
     pad = torch.zeros((rows, wmax), dtype=local_block.dtype, device=local_block.device)
     pad[:, : local_block.shape[1]] = local_block
     parts = [torch.empty_like(pad) for _ in blocks]
     dist.all_gather(parts, pad, group=group)
-    return torch.cat([p[:, :w] for p, w in zip(parts, widths)], dim=1)
+    return _from_wire(torch.cat([p[:, :w] for p, w in zip(parts, widths)], dim=1), was_int16)
 
 
 def gather_units(local_rows, ranges, row_width, dist=None, group=None):
@@ -99,17 +112,18 @@ def gather_units(local_rows, ranges, row_width, dist=None, group=None):
     import torch
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_rows
+    local_rows, was_int16 = _as_wire(local_rows)
     counts = [r.u1 - r.u0 for r in ranges]
     if len(set(counts)) == 1:                                  # equal ranges: one collective straight into place
         full = torch.empty((sum(counts), row_width), dtype=local_rows.dtype, device=local_rows.device)
         dist.all_gather_into_tensor(full, local_rows.contiguous(), group=group)
-        return full
+        return _from_wire(full, was_int16)
     cmax = max(counts)
     pad = torch.zeros((cmax, row_width), dtype=local_rows.dtype, device=local_rows.device)
     pad[: local_rows.shape[0]] = local_rows
     parts = [torch.empty_like(pad) for _ in ranges]
     dist.all_gather(parts, pad, group=group)
-    return torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0)
+    return _from_wire(torch.cat([p[:c] for p, c in zip(parts, counts)], dim=0), was_int16)
 
 
 def max_over_ranks(ms, dist=None, device="cpu"):

@@ -220,6 +220,14 @@ catena_status_t catena_b200_matmul_f32_into(const void* a, const void* b, void* 
 catena_status_t catena_b200_attn_decode_bf16_into(const void* q, const void* k_cache, const void* v_cache,
                                                   void* o, uint64_t batch, uint64_t hq, uint64_t hkv,
                                                   uint64_t d, uint64_t kv_len, uint64_t unit0, uint64_t unit1);
+/* The same launch fused with the gather of a (batch, kv-head)-sharded decode: the warps that write a unit's outputs to
+ * `o` also store them, with plain stores over NVLink, into up to 7 other GPUs' copies of O at the same offsets.  peer_o[i]
+ * are peer-mapped DEVICE pointers to the start of the peer's O (catena_b200_ipc_import).  The stores are complete when
+ * the stream has drained; ranks then need one barrier before they read each other's units.  Needs the tcgen05 kernel
+ * (kv_len <= 7168, q 16-byte aligned): CATENA_E_UNSUPPORTED otherwise.  No counterpart in the reference. */
+catena_status_t catena_b200_attn_decode_bf16_into_peers(const void* q, const void* k_cache, const void* v_cache, void* o,
+                                                        uint64_t batch, uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len,
+                                                        uint64_t unit0, uint64_t unit1, void* const* peer_o, uint32_t n_peers);
 /* elementwise / fold kernels into caller memory (device pointers; `n` in elements) */
 catena_status_t catena_b200_map_f32_into(const char* op, const void* in, void* out, uint64_t n);
 catena_status_t catena_b200_softmax_f32_into(const void* in, void* out, uint64_t n);

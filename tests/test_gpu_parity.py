@@ -497,6 +497,36 @@ def test_attn_decode_c3_partition_and_determinism(rt, orc, attn_kernel):
     assert np.array_equal(got, sharded)
 
 
+def test_attn_peer_stores_write_every_copy(rt):
+    """The gather-fused decode stores every unit's outputs to O and to the peer copies of O: here the "peers" are two more
+    buffers of the same GPU.  Two launches over disjoint unit ranges must leave the plain launch's bits in all three
+    buffers, and nothing outside the launched ranges."""
+    B, Hq, Hkv, L = 4, 8, 2, 900
+    q, k, v = attn_inputs(B, Hq, Hkv, L)
+    want = run_attn(rt, q, k, v, B, Hq, Hkv, L)
+    G = Hq // Hkv
+    qm, km, vm = cb.upload(q), cb.upload(k), cb.upload(v)
+    fill = np.full((B * Hkv, G * 128), 0x7FC0, np.uint16)
+    outs = [cb.upload(fill) for _ in range(3)]
+    ptrs = (C.c_void_p * 2)(outs[1].data, outs[2].data)
+    L_ = cb.lib()
+    for lo, hi in ((0, 3), (5, 8)):                            # units 3 and 4 are left out
+        cb.check(L_.catena_b200_attn_decode_bf16_into_peers(qm.data, km.data, vm.data, outs[0].data, B, Hq, Hkv, 128, L, lo, hi, ptrs, 2))
+    w = want.reshape(B * Hkv, G * 128)
+    for o in outs:
+        got = cb.download(o, np.uint16).reshape(B * Hkv, G * 128)
+        assert np.array_equal(got[:3], w[:3]) and np.array_equal(got[5:], w[5:])
+        assert (got[3:5] == 0x7FC0).all()
+    # the mma.sync kernel has no peer stores
+    cb.lib().catena_b200_debug_set_attn_tc(0)
+    try:
+        assert L_.catena_b200_attn_decode_bf16_into_peers(qm.data, km.data, vm.data, outs[0].data, B, Hq, Hkv, 128, L, 0, 8, ptrs, 2) == cb.E_UNSUPPORTED
+    finally:
+        cb.lib().catena_b200_debug_set_attn_tc(1)
+    for x in [qm, km, vm] + outs:
+        cb.free(x)
+
+
 def test_attn_rejects_unsupported(rt):
     q, k, v = attn_inputs(1, 4, 1, 16)
     with pytest.raises(cb.ExecError) as e:
