@@ -101,6 +101,17 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
                                    uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap,
                                    uint64_t unit0, uint64_t unit1, void* const* peer_o = nullptr, uint32_t n_peers = 0);
 catena_status_t attn_check_errors();
+// llama_decode_fused.cu: the part of a decode step after its attention as one persistent kernel
+int decode_fused_mode();      // bit 0: the tail kernel, bit 1: the head kernel
+void decode_fused_set_mode(int mode);
+bool decode_tail_supported(uint64_t m, uint64_t hidden, uint64_t ko, uint64_t ffn);
+catena_status_t launch_decode_tail(const void* att, const void* x, const void* w_o, const void* w_gate_up, const void* w_down, void* x2,
+                                   void* act, void* out, uint64_t m, uint64_t hidden, uint64_t ko, uint64_t ffn);
+bool decode_head_supported(uint64_t m, uint64_t hidden, uint64_t hq, uint64_t hkv);
+catena_status_t launch_decode_head(const void* table, const int32_t* ids, const void* w_qkv, const float* inv_freq, uint32_t* bad, void* x,
+                                   void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t m, uint64_t hidden, uint64_t vocab,
+                                   uint64_t hq, uint64_t hkv, uint64_t cap, uint64_t pos);
+catena_status_t decode_fused_check_errors();
 // map_reduce.cu
 enum ReduceKind { RED_SUM = 0, RED_MAX = 1, RED_SUMSQ = 2 };
 int map_op_from_name(const char* name);  // -1 if unknown

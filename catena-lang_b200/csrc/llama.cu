@@ -19,6 +19,7 @@
 
 #include "catena_math.cuh"
 #include "common.cuh"
+#include "skinny.cuh"
 
 namespace catena {
 
@@ -250,109 +251,20 @@ __global__ void add_rows_kernel(const uint4* x, const uint4* y, uint4* out, uint
     }
 }
 
-// ---------------------------------------------------------------- skinny GEMM (M <= 16 rows)
-// y[m, n] = sum_k x[m, k] * w[n, k], optionally + res[m, n]; x [M, K] bf16, w [N, K] bf16 (K contiguous), y [M, N] bf16.
-// HBM-bound on w: every weight is read exactly once, 16 bytes per lane, and the few rows of x ride along as the other
-// operand of mma.sync m16n8k16 (tokens = the 16 rows of A, 8 weight rows = the columns of B).  On CUDA cores the
-// unfused multiply-adds of even 4 tokens would cost as many issue slots as the weights cost bandwidth.
-// A CTA owns 8 weight rows; its 8 warps take the 32-wide k blocks round-robin (warp v: blocks v, v+8, ...) and their
-// partial sums are added in ascending warp order.  Inside a k block lane (g, t) holds k = 8t..8t+7 of weight row g
-// and of tokens g, g+8: the MMA's k index is a permutation of the true one, the same for both operands.
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-constexpr int kSkinnyUnroll = 8;
-// CTAs are persistent and software-pipelined: the weight loads of the next batch of k blocks (of this or the next
-// group of rows) are issued before the current batch is multiplied and reduced, so the stream never drains.
-// With swiglu_f = F > 0 the weights are the [2F, K] gate / up matrix and y [M, F] = silu(gate) * up: a CTA multiplies the 8
-// gate rows of a group, then the matching 8 up rows, and combines them in the epilogue (both products rounded to bf16
-// first, exactly what the separate SwiGLU kernel reads back from memory).
+// ---------------------------------------------------------------- skinny GEMM (M <= 16 rows): arithmetic in skinny.cuh
+// CTAs are persistent and software-pipelined (skinny.cuh); the first batch of weight loads is issued before the wait for the
+// predecessor's results.
 __global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ y,
                                                          uint32_t M, uint32_t N, uint32_t K, uint32_t swiglu_f) {
     __shared__ float part[8][16][8];    // [warp][token][weight row]
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t kblocks = (K + 31) / 32;
-    const uint32_t batches = (kblocks + 8 * kSkinnyUnroll - 1) / (8 * kSkinnyUnroll);   // per group and warp
-    const uint32_t halves = swiglu_f ? 2u : 1u;             // row groups multiplied per output group
-    const uint32_t groups = swiglu_f ? swiglu_f / 8 : (N + 7) / 8;
-    const uint32_t my_groups = blockIdx.x < groups ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const uint32_t steps = my_groups * halves * batches;
-    // first weight row of step s
-    auto row0_of = [&](uint32_t s) {
-        const uint32_t grp = blockIdx.x + (s / (halves * batches)) * gridDim.x;
-        return ((s / batches) % halves) * swiglu_f + grp * 8;
-    };
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    const __nv_bfloat16* xa = x + (size_t)g * K + 8 * t;
-    const __nv_bfloat16* xb = x + (size_t)(g + 8) * K + 8 * t;
-
-    // weights of step s: rows row0_of(s) .. +7, k blocks warp + 8 (u + kSkinnyUnroll (s % batches))
-    auto load_w = [&](uint32_t s, uint4 (&wv)[kSkinnyUnroll]) {
-        const uint32_t n0 = row0_of(s);
-        const uint32_t kb0 = warp + 8 * kSkinnyUnroll * (s % batches);
-        const __nv_bfloat16* wr = w + (size_t)(n0 + g) * K + 8 * t;
-#pragma unroll
-        for (int u = 0; u < kSkinnyUnroll; ++u) {
-            const uint32_t k = (kb0 + 8 * u) * 32;
-            wv[u] = zero;
-            if (n0 + g < N && k + 8 * t < K)   // volatile: the whole batch is issued here, ahead of the (volatile) MMAs
-                asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(wv[u].x), "=r"(wv[u].y), "=r"(wv[u].z), "=r"(wv[u].w)
-                             : "l"(wr + k));
-        }
-    };
-
-    uint4 cur[kSkinnyUnroll], nxt[kSkinnyUnroll];
+    const SkinnyJob job = {x, w, res, y, M, N, K, swiglu_f};
+    const SkinnySchedule sc(job, blockIdx.x, gridDim.x);
+    uint4 cur[kSkinnyUnroll];
     pdl_trigger();
-    if (steps > 0) load_w(0, cur);      // weights are never written by a kernel: they may be fetched before the wait
+    if (sc.steps > 0) skinny_load_w(job, sc, 0, cur);      // weights are never written by a kernel: they may be fetched before the wait
     pdl_wait();
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float gate = 0.0f;                   // SwiGLU: the gate value of this thread's (token, row) until the up rows are done
-    for (uint32_t s = 0; s < steps; ++s) {
-        if (s + 1 < steps) load_w(s + 1, nxt);
-        const uint32_t kb0 = warp + 8 * kSkinnyUnroll * (s % batches);
-#pragma unroll
-        for (int u = 0; u < kSkinnyUnroll; ++u) {
-            const uint32_t k = (kb0 + 8 * u) * 32;
-            const bool ok = k + 8 * t < K;
-            const uint4 av = ok && g < M ? __ldg(reinterpret_cast<const uint4*>(xa + k)) : zero;
-            const uint4 bv = ok && g + 8 < M ? __ldg(reinterpret_cast<const uint4*>(xb + k)) : zero;
-            mma_bf16_16816(acc, av.x, bv.x, av.y, bv.y, cur[u].x, cur[u].y);
-            mma_bf16_16816(acc, av.z, bv.z, av.w, bv.w, cur[u].z, cur[u].w);
-        }
-        if (s % batches == batches - 1) {    // the group is complete: add the warps' partial sums in ascending order
-            const uint32_t n0 = row0_of(s);
-            __syncthreads();                 // the previous group's partials have been read
-            part[warp][g][2 * t] = acc[0];
-            part[warp][g][2 * t + 1] = acc[1];
-            part[warp][g + 8][2 * t] = acc[2];
-            part[warp][g + 8][2 * t + 1] = acc[3];
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
-            __syncthreads();
-            if (threadIdx.x < 128) {
-                const uint32_t m = threadIdx.x >> 3, r = threadIdx.x & 7;
-                if (m < M && n0 + r < N) {
-                    float v = part[0][m][r];
-#pragma unroll
-                    for (int wv2 = 1; wv2 < 8; ++wv2) v = cmath::add(v, part[wv2][m][r]);
-                    if (swiglu_f) {
-                        const float rounded = __bfloat162float(__float2bfloat16_rn(v));
-                        if (n0 < swiglu_f) gate = rounded;
-                        else y[(size_t)m * swiglu_f + (n0 - swiglu_f) + r] = __float2bfloat16_rn(cmath::mul(cmath::silu(gate), rounded));
-                    } else {
-                        if (res) v = cmath::add(__bfloat162float(__float2bfloat16_rn(v)), __bfloat162float(res[(size_t)m * N + n0 + r]));
-                        y[(size_t)m * N + n0 + r] = __float2bfloat16_rn(v);
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kSkinnyUnroll; ++u) cur[u] = nxt[u];
-    }
+    skinny_run<A_READONLY>(job, sc, part, cur);
 }
 
 // ---------------------------------------------------------------- causal prefill attention (mma.sync)
@@ -855,6 +767,7 @@ static catena_status_t composite(F body) {
         CATENA_TRY(gemm_tc_check_errors());
         CATENA_TRY(attn_check_errors());
         CATENA_TRY(attn_prefill_tc_check_errors());
+        CATENA_TRY(decode_fused_check_errors());
         CATENA_TRY(embed_check());
     }
     return CATENA_OK;
@@ -898,6 +811,19 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
     __nv_bfloat16* gu = ws;                                  ws += T * 2 * d.F;
     __nv_bfloat16* act = ws;
     return composite([&]() -> catena_status_t {
+        const bool fused_step = seq == 1 && !((uintptr_t)out & 15);
+        if (fused_step && (decode_fused_mode() & 2) && decode_head_supported(T, d.H, d.Hq, d.Hkv) && !(((uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
+            // a decode step, when asked for: embedding, norm, q/k/v projection, rotation and cache append in one persistent kernel
+            const float* inv = nullptr;
+            CATENA_TRY(rope_table(blk->rope_base, &inv));
+            uint32_t*& bad = g_embed_bad[tls().device];
+            if (!bad) {
+                CATENA_CUDA(cudaMalloc(&bad, sizeof(uint32_t)));
+                CATENA_CUDA(cudaMemset(bad, 0, sizeof(uint32_t)));
+            }
+            CATENA_TRY(launch_decode_head(blk->embedding, ids, blk->w_qkv, inv, bad, x, qkv, q, k_cache, v_cache, T, d.H, blk->vocab, d.Hq,
+                                          d.Hkv, blk->max_len, pos0));
+        } else {
         CATENA_TRY(launch_embed_rmsnorm(blk->embedding, ids, x, nrm, T, d.H, blk->vocab));
         if (qkv_rope_fusable(T, seq, d.Hq, d.Hkv) && !(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
             CATENA_TRY(launch_qkv_rope(nrm, blk->w_qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, d.H, blk->rope_base));
@@ -905,12 +831,17 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
             CATENA_TRY(launch_linear(nrm, blk->w_qkv, nullptr, qkv, T, d.qkv_cols, d.H));
             CATENA_TRY(launch_rope_append(qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, blk->rope_base));
         }
+        }
         if (seq == 1) {
             CATENA_TRY(launch_attn_decode(q, k_cache, v_cache, att, batch, d.Hq, d.Hkv, llama::kHeadDim, pos0 + 1, blk->max_len, 0,
                                           batch * d.Hkv));
         } else {
             if (pos0 != 0) return fail(CATENA_E_UNSUPPORTED, "llama: a multi-token step must start at position 0");
             CATENA_TRY(launch_attn_prefill(q, k_cache, v_cache, att, batch, seq, d.Hq, d.Hkv, blk->max_len));
+        }
+        if (fused_step && (decode_fused_mode() & 1) && decode_tail_supported(T, d.H, d.Hq * llama::kHeadDim, d.F)) {
+            // a decode step, when asked for: everything after the attention in one persistent kernel (llama_decode_fused.cu), same bits
+            return launch_decode_tail(att, x, blk->w_o, blk->w_gate_up, blk->w_down, x2, act, out, T, d.H, d.Hq * llama::kHeadDim, d.F);
         }
         CATENA_TRY(launch_linear(att, blk->w_o, x, x2, T, d.H, d.Hq * llama::kHeadDim));
         CATENA_TRY(launch_rmsnorm_rows(x2, nrm, T, d.H));

@@ -309,6 +309,7 @@ void catena_b200_debug_set_cta_limit(int limit) {
 
 void catena_b200_debug_set_gemm_pair(int on) { gemm_tc_set_pair_mode(on); }
 void catena_b200_debug_set_attn_tc(int on) { attn_set_tc_mode(on); }
+void catena_b200_debug_set_decode_fused(int on) { decode_fused_set_mode(on ? 3 : 0); }
 void catena_b200_debug_attn_last_launch(uint32_t out[4]) { attn_last_launch(out); }
 catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]) {
     if (!out) return fail(CATENA_E_BAD_ARG, "rcp check: null argument");
@@ -318,6 +319,7 @@ catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]) {
 
 catena_status_t catena_b200_check_device_errors(void) {
     CATENA_TRY(gemm_tc_check_errors());
+    CATENA_TRY(decode_fused_check_errors());
     return attn_check_errors();
 }
 
