@@ -757,6 +757,9 @@ struct AttnExchange {
     uint32_t* tickets = nullptr;   // always at the same place: they carry their count (a multiple of 8) between launches
     size_t ticket_units = 0;
     uint32_t epoch = 0;
+    size_t maxima_bytes = 0;       // extent of the last launch's epoch-tagged maxima (the whole area while it is all zeros):
+                                   // bytes beyond it may hold raw floats of that launch's denominators / partial outputs
+                                   // and are cleared before a later launch's maxima move onto them
 };
 static thread_local AttnExchange g_attn_exchange[16];
 static thread_local int g_attn2_max_ctas[16] = {0};
@@ -767,6 +770,7 @@ static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 void attn_tc_reset_exchange() {
     AttnExchange& xa = g_attn_exchange[tls().device];
     if (xa.base) cudaMemsetAsync(xa.base, 0, xa.bytes, tls().stream);
+    xa.maxima_bytes = xa.bytes;
     if (xa.tickets) cudaMemsetAsync(xa.tickets, 0, xa.ticket_units * sizeof(uint32_t), tls().stream);
     xa.epoch = 0;
 }
@@ -824,7 +828,14 @@ catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void
         CATENA_CUDA(cudaMemset(xa.base, 0, want));          // epoch 0 never matches a launch
         xa.bytes = want;
         xa.epoch = 0;
+        xa.maxima_bytes = want;                             // all zeros: epoch 0 everywhere
     }
+    if (off_denom > xa.maxima_bytes) {
+        // the maxima of this launch reach into what earlier launches used for denominators and partial outputs: a stale
+        // float there could by chance carry this launch's epoch in its upper half, so the new part is cleared first
+        CATENA_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(xa.base) + xa.maxima_bytes, 0, off_denom - xa.maxima_bytes, tls().stream));
+    }
+    xa.maxima_bytes = off_denom;
     if (xa.ticket_units < n_units) {
         if (xa.tickets) {
             CATENA_CUDA(cudaStreamSynchronize(tls().stream));

@@ -128,6 +128,9 @@ catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint
     cudaStream_t st = tls().stream;
     int sms = tls().sm_count > 0 ? tls().sm_count : 148;
     uint64_t big_tiles = ceil_div_u64(n, 64) * ceil_div_u64(m, 64);
+    // row tiles ride on grid.y (at most 65535): 4 194 240 rows with the 64-row tiles; taller products are refused, not mis-launched
+    if (ceil_div_u64(n, big_tiles >= (uint64_t)sms ? 64 : 16) > 65535)
+        return fail(CATENA_E_TOO_LARGE, "matmul f32: more than 65535 row tiles (4194240 rows)");
     if (big_tiles >= (uint64_t)sms) {
         dim3 grid((unsigned)ceil_div_u64(m, 64), (unsigned)ceil_div_u64(n, 64));
         matmul_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);

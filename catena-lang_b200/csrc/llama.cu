@@ -649,6 +649,9 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
     if (!tokens) return CATENA_OK;
     if (seq == 0 || tokens % seq) return fail(CATENA_E_BAD_ARG, "rope: tokens must be batch * seq");
     if (pos0 + seq > cap) return fail(CATENA_E_BAD_ARG, "rope: positions beyond the cache capacity");
+    // the kernels take 32-bit token, position and head counts, and one thread per (token, head, pair)
+    if (tokens > 0xFFFFFFFFull || cap > 0xFFFFFFFFull || hq + 2 * hkv > 0xFFFFull || tokens * (hq + 2 * hkv) > (1ull << 40))
+        return fail(CATENA_E_TOO_LARGE, "rope: more tokens, cache rows or heads than the kernels index");
     const float* inv = nullptr;
     CATENA_TRY(rope_table(base, &inv));
     if (seq >= 16 && tokens / seq * (hq + hkv) >= 8) {   // many (sequence, head) pairs per position: evaluate each angle once
@@ -799,6 +802,9 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
     const uint64_t T = batch * seq;
     if (!T) return CATENA_OK;
     if (pos0 + seq > blk->max_len) return fail(CATENA_E_BAD_ARG, "llama: positions beyond max_len");
+    // token counts and per-token workspace offsets are 32-bit in the kernels
+    if (T > 0xFFFFFFFFull || blk->max_len > 0xFFFFFFFFull || T * workspace_elems_per_token(d) > (1ull << 46))
+        return fail(CATENA_E_TOO_LARGE, "llama: more tokens than the kernels index");
     if (workspace_bytes < T * workspace_elems_per_token(d) * 2) return fail(CATENA_E_BAD_ARG, "llama: workspace too small");
     if ((uintptr_t)workspace & 255) return fail(CATENA_E_BAD_ARG, "llama: workspace must be 256-byte aligned");
     __nv_bfloat16* ws = static_cast<__nv_bfloat16*>(workspace);

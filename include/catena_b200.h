@@ -109,7 +109,10 @@ void program_nn_tanh(float x, float* out);
 void program_nn_gelu_approx(float x, float* out);
 
 /* ---- buffer programs ------------------------------------------------------------------ */
-/* catena-lang/stdlib/nn.hex:93-122 and :154-182 */
+/* catena-lang/stdlib/nn.hex:93-122 and :154-182.  Bit-exact with the reference's sequential folds up to 65536 elements for
+ * inputs without NaN: the reference's max fold keeps the accumulator when `acc >= v` (catena-lang/stdlib/sum.hex:73-84), so
+ * with a NaN in the input its result depends on where the NaN stands, and the parallel maximum here does not reproduce
+ * that.  A zero of either sign as the maximum gives the same output bits. */
 void program_nn_softmax(catena_mem_t in, catena_mem_t* out);
 void program_nn_rmsnorm(catena_mem_t in, catena_mem_t* out);
 catena_status_t program_nn_softmax_s(catena_mem_t in, catena_mem_t* out);

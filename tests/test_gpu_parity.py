@@ -197,6 +197,20 @@ def test_softmax_rmsnorm_bit_exact_up_to_65536(rt, orc, n):
     assert np.array_equal(u32(y), u32(orc.rmsnorm(x)))
 
 
+def test_softmax_signed_zero_maximum_and_nan_input(rt, orc):
+    """The parallel maximum may return either zero of a +0 / -0 tie where the reference's fold keeps the first: the output
+    bits are the same.  With a NaN in the input the reference's result depends on the NaN's position (out of contract for
+    the bit-exact claim): the call must still return, and the library must stay usable."""
+    for x in ([-0.0, 0.0, -1.0, -2.5], [0.0, -0.0, -1.0, -2.5], [-3.0, -0.0, 0.0]):
+        x = np.array(x, np.float32)
+        y = rt.exec("nn.softmax", [rt.mem_f32(x)])[0].v.to_f32_vec()
+        assert np.array_equal(u32(y), u32(orc.softmax(x)))
+    y = rt.exec("nn.softmax", [rt.mem_f32(np.array([1.0, np.nan, 2.0], np.float32))])[0].v.to_f32_vec()
+    assert y.size == 3
+    x = np.array([1.0, 2.0, 4.0], np.float32)
+    assert np.array_equal(u32(rt.exec("nn.softmax", [rt.mem_f32(x)])[0].v.to_f32_vec()), u32(orc.softmax(x)))
+
+
 def test_softmax_rmsnorm_long_rows(rt, orc):
     """Beyond 65536 elements the denominator is a fixed-shape tree sum.  It is compared with the exact
     (float64) sum of the same fp32 terms: relative 1e-6.  The reference's sequential fp32 fold is itself
