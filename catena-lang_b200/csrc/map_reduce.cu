@@ -133,6 +133,25 @@ __global__ void __launch_bounds__(kThreads) fold_tree_kernel(const float* __rest
     if (threadIdx.x == 0) partials[blockIdx.x] = r;
 }
 
+// The second level of the tree inside a consumer kernel: what fold_tree_kernel<ADDK, ADDK> computes with ONE block over
+// `count` <= kChunk partials — the same elements per thread in the same order, the same butterfly, the same order of
+// the warps — evaluated by every CTA of the consumer for itself (the partials sit in L2), so the consumer needs no
+// separate launch for it.  Returns the value in every thread.
+template <int ADDK>
+__device__ __forceinline__ float fold_level1(const float* __restrict__ partials, uint32_t count, float* warp_part, float* result) {
+    float acc = fold_identity<ADDK>();
+    for (int j = 0; j < (int)(kChunk / 4 / kThreads); ++j) {
+        const uint32_t i0 = ((uint32_t)j * kThreads + threadIdx.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (i0 + e < count) acc = fold_add<ADDK>(acc, partials[i0 + e]);
+    }
+    const float r = block_tree<ADDK>(acc, warp_part);
+    if (threadIdx.x == 0) *result = r;
+    __syncthreads();
+    return *result;
+}
+
 // ---- argmax ------------------------------------------------------------------------------------
 struct IdxVal { uint64_t i; float v; };
 __device__ __forceinline__ IdxVal better(IdxVal a, IdxVal b) {
@@ -206,39 +225,61 @@ __global__ void __launch_bounds__(kThreads) map_unary_kernel(const float* __rest
     uint64_t n4 = vec ? n / 4 : 0;
     const float4* in4 = reinterpret_cast<const float4*>(in);
     float4* out4 = reinterpret_cast<float4*>(out);
-    // two float4 per trip: eight values go through the batched form of the op together (zeros pad a lone last one)
-    for (uint64_t i = tid; i < n4; i += 2 * stride) {
-        const bool two = i + stride < n4;
-        const float4 a = in4[i], b = two ? in4[i + stride] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    // Four float4 per trip, all four loads issued before the first value is used (a thread with one 16-byte load in flight
+    // per trip keeps only 32 KB per SM in flight, which caps the stream near 5 TB/s).  Eight values at a time go through
+    // the batched form of the op (zeros pad missing ones).
+    const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint64_t i = tid; i < n4; i += 4 * stride) {
+        const bool h1 = i + stride < n4, h2 = i + 2 * stride < n4, h3 = i + 3 * stride < n4;
+        const float4 a = in4[i], b = h1 ? in4[i + stride] : zero4, c = h2 ? in4[i + 2 * stride] : zero4, d = h3 ? in4[i + 3 * stride] : zero4;
         const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         float y[8];
         cmath::apply_n<OP, 8>(x, y);
         out4[i] = make_float4(y[0], y[1], y[2], y[3]);
-        if (two) out4[i + stride] = make_float4(y[4], y[5], y[6], y[7]);
+        if (h1) out4[i + stride] = make_float4(y[4], y[5], y[6], y[7]);
+        if (h2) {
+            const float x2[8] = {c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+            cmath::apply_n<OP, 8>(x2, y);
+            out4[i + 2 * stride] = make_float4(y[0], y[1], y[2], y[3]);
+            if (h3) out4[i + 3 * stride] = make_float4(y[4], y[5], y[6], y[7]);
+        }
     }
     for (uint64_t i = n4 * 4 + tid; i < n; i += stride) out[i] = cmath::apply<OP>(in[i]);
 }
 
 // softmax-at (nn.hex:75-90): exp~(x_i - max) / denom
+// With `chunks` > 0 denom_ptr holds the level-0 partials of the exp-shifted sum and every CTA finishes that tree itself
+// (fold_level1); with chunks == 0 it points at the scalar.
 __global__ void __launch_bounds__(kThreads) softmax_map_kernel(const float* __restrict__ in,
                                                                float* __restrict__ out, uint64_t n,
-                                                               const float* max_ptr, const float* denom_ptr) {
-    float m = *max_ptr, d = *denom_ptr;
+                                                               const float* max_ptr, const float* denom_ptr, uint32_t chunks) {
+    __shared__ float warp_part[kThreads / 32];
+    __shared__ float result;
+    const float m = *max_ptr;
+    const float d = chunks ? fold_level1<F_SUM>(denom_ptr, chunks, warp_part, &result) : *denom_ptr;
     uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     bool vec = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     uint64_t n4 = vec ? n / 4 : 0;
     const float4* in4 = reinterpret_cast<const float4*>(in);
     float4* out4 = reinterpret_cast<float4*>(out);
-    for (uint64_t i = tid; i < n4; i += 2 * stride) {
-        const bool two = i + stride < n4;
-        const float4 a = in4[i], b = two ? in4[i + stride] : make_float4(m, m, m, m);
+    const float4 m4 = make_float4(m, m, m, m);
+    for (uint64_t i = tid; i < n4; i += 4 * stride) {       // four loads in flight per thread (see map_unary_kernel)
+        const bool h1 = i + stride < n4, h2 = i + 2 * stride < n4, h3 = i + 3 * stride < n4;
+        const float4 a = in4[i], b = h1 ? in4[i + stride] : m4, c = h2 ? in4[i + 2 * stride] : m4, f = h3 ? in4[i + 3 * stride] : m4;
         const float x[8] = {cmath::sub(a.x, m), cmath::sub(a.y, m), cmath::sub(a.z, m), cmath::sub(a.w, m),
                             cmath::sub(b.x, m), cmath::sub(b.y, m), cmath::sub(b.z, m), cmath::sub(b.w, m)};
         float e[8];
         cmath::exp_approx_n<8>(x, e);
         out4[i] = make_float4(cmath::div(e[0], d), cmath::div(e[1], d), cmath::div(e[2], d), cmath::div(e[3], d));
-        if (two) out4[i + stride] = make_float4(cmath::div(e[4], d), cmath::div(e[5], d), cmath::div(e[6], d), cmath::div(e[7], d));
+        if (h1) out4[i + stride] = make_float4(cmath::div(e[4], d), cmath::div(e[5], d), cmath::div(e[6], d), cmath::div(e[7], d));
+        if (h2) {
+            const float x2[8] = {cmath::sub(c.x, m), cmath::sub(c.y, m), cmath::sub(c.z, m), cmath::sub(c.w, m),
+                                 cmath::sub(f.x, m), cmath::sub(f.y, m), cmath::sub(f.z, m), cmath::sub(f.w, m)};
+            cmath::exp_approx_n<8>(x2, e);
+            out4[i + 2 * stride] = make_float4(cmath::div(e[0], d), cmath::div(e[1], d), cmath::div(e[2], d), cmath::div(e[3], d));
+            if (h3) out4[i + 3 * stride] = make_float4(cmath::div(e[4], d), cmath::div(e[5], d), cmath::div(e[6], d), cmath::div(e[7], d));
+        }
     }
     for (uint64_t i = n4 * 4 + tid; i < n; i += stride)
         out[i] = cmath::div(cmath::exp_approx(cmath::sub(in[i], m)), d);
@@ -266,10 +307,14 @@ __global__ void __launch_bounds__(kThreads) softmax_small_kernel(const float* __
 }
 
 // rmsnorm-at (nn.hex:139-151) with rms = sqrt~(sumsq/len + eps) (nn.hex:169-174)
+// With `chunks` > 0 sumsq_ptr holds the level-0 partials of the sum of squares and every CTA finishes the tree itself.
 __global__ void __launch_bounds__(kThreads) rmsnorm_map_kernel(const float* __restrict__ in,
                                                                float* __restrict__ out, uint64_t n,
-                                                               const float* sumsq_ptr) {
-    float mean_sq = cmath::div(*sumsq_ptr, cmath::u64_to_f32(n));
+                                                               const float* sumsq_ptr, uint32_t chunks) {
+    __shared__ float warp_part[kThreads / 32];
+    __shared__ float result;
+    const float sumsq = chunks ? fold_level1<F_SUM>(sumsq_ptr, chunks, warp_part, &result) : *sumsq_ptr;
+    float mean_sq = cmath::div(sumsq, cmath::u64_to_f32(n));
     float rms = cmath::sqrt_newton(cmath::add(mean_sq, cmath::from_bits(0x3727C5ACu)));
     uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -277,13 +322,21 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_map_kernel(const float* __re
     uint64_t n4 = vec ? n / 4 : 0;
     const float4* in4 = reinterpret_cast<const float4*>(in);
     float4* out4 = reinterpret_cast<float4*>(out);
-    for (uint64_t i = tid; i < n4; i += stride) {
-        float4 v = in4[i];
-        v.x = cmath::div(v.x, rms);
-        v.y = cmath::div(v.y, rms);
-        v.z = cmath::div(v.z, rms);
-        v.w = cmath::div(v.w, rms);
-        out4[i] = v;
+    for (uint64_t i = tid; i < n4; i += 4 * stride) {       // four loads in flight per thread (see map_unary_kernel)
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + u * stride < n4) v[u] = in4[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i + u * stride < n4) {
+                v[u].x = cmath::div(v[u].x, rms);
+                v[u].y = cmath::div(v[u].y, rms);
+                v[u].z = cmath::div(v[u].z, rms);
+                v[u].w = cmath::div(v[u].w, rms);
+                out4[i + u * stride] = v[u];
+            }
+        }
     }
     for (uint64_t i = n4 * 4 + tid; i < n; i += stride) out[i] = cmath::div(in[i], rms);
 }
@@ -464,6 +517,7 @@ catena_status_t argmax_f32(const float* in, uint64_t n, uint64_t* host_out) {
     return s;
 }
 
+static catena_status_t launch_softmax_fused_levels(const float* in, float* out, uint64_t n);
 catena_status_t launch_softmax(const float* in, float* out, uint64_t n) {
     if (n == 0) return CATENA_OK;
     cudaStream_t st = tls().stream;
@@ -472,6 +526,7 @@ catena_status_t launch_softmax(const float* in, float* out, uint64_t n) {
         count_launch();
         return CATENA_OK;
     }
+    if (ceil_div_u64(n, kChunk) <= kChunk) return launch_softmax_fused_levels(in, out, n);
     void* d = nullptr;
     CATENA_TRY(pool_alloc(2 * sizeof(float), &d));
     float* d_max = (float*)d;
@@ -479,20 +534,55 @@ catena_status_t launch_softmax(const float* in, float* out, uint64_t n) {
     catena_status_t s = enqueue_fold<F_MAX>(in, n, nullptr, d_max);
     if (s == CATENA_OK) s = enqueue_fold<F_EXPSUM>(in, n, d_max, d_den);
     if (s == CATENA_OK) {
-        softmax_map_kernel<<<grid_for(ceil_div_u64(n, 4)), kThreads, 0, st>>>(in, out, n, d_max, d_den);
+        softmax_map_kernel<<<grid_for(ceil_div_u64(n, 4)), kThreads, 0, st>>>(in, out, n, d_max, d_den, 0u);
         count_launch();
     }
     pool_free(d);
     return s;
 }
 
+// Long rows whose level-0 partials fit one block of the second level (n <= kChunk^2 = 2^28): the map kernel's CTAs finish
+// the tree of the denominator themselves, which saves one tiny dependent launch; same tree, same bits.  (The maximum
+// keeps its own second-level launch: the exp-shifted sum needs it as a scalar in every one of its 4096 short-lived CTAs,
+// and a persistent form of that kernel measured slower — 77 against 64 us at 64 Mi elements, it is bound by the exp~
+// arithmetic and balances worse.)
+static catena_status_t launch_softmax_fused_levels(const float* in, float* out, uint64_t n) {
+    const uint64_t chunks = ceil_div_u64(n, kChunk);
+    void* d = nullptr;
+    CATENA_TRY(pool_alloc((2 * chunks + 1) * sizeof(float), &d));
+    float* p_max = static_cast<float*>(d);
+    float* p_sum = p_max + chunks;
+    float* d_max = p_sum + chunks;
+    cudaStream_t st = tls().stream;
+    fold_tree_kernel<F_MAX, F_MAX><<<(unsigned)chunks, kThreads, 0, st>>>(in, n, nullptr, p_max);
+    fold_tree_kernel<F_MAX, F_MAX><<<1, kThreads, 0, st>>>(p_max, chunks, nullptr, d_max);
+    fold_tree_kernel<F_EXPSUM, F_SUM><<<(unsigned)chunks, kThreads, 0, st>>>(in, n, d_max, p_sum);
+    softmax_map_kernel<<<grid_for(ceil_div_u64(n, 4)), kThreads, 0, st>>>(in, out, n, d_max, p_sum, (uint32_t)chunks);
+    count_launch(4);
+    cudaError_t e = cudaGetLastError();
+    pool_free(d);
+    return e == cudaSuccess ? CATENA_OK : fail_cuda(e, "softmax launch");
+}
+
 catena_status_t launch_rmsnorm(const float* in, float* out, uint64_t n) {
     if (n == 0) return CATENA_OK;
+    const uint64_t chunks = ceil_div_u64(n, kChunk);
+    if (n > kExactFoldMax && chunks <= kChunk) {
+        // two launches: sum-of-squares partials, then the map whose CTAs finish the tree themselves (same bits)
+        void* d = nullptr;
+        CATENA_TRY(pool_alloc(chunks * sizeof(float), &d));
+        fold_tree_kernel<F_SUMSQ, F_SUM><<<(unsigned)chunks, kThreads, 0, tls().stream>>>(in, n, nullptr, static_cast<float*>(d));
+        rmsnorm_map_kernel<<<grid_for(ceil_div_u64(n, 4)), kThreads, 0, tls().stream>>>(in, out, n, static_cast<float*>(d), (uint32_t)chunks);
+        count_launch(2);
+        cudaError_t e = cudaGetLastError();
+        pool_free(d);
+        return e == cudaSuccess ? CATENA_OK : fail_cuda(e, "rmsnorm launch");
+    }
     void* d = nullptr;
     CATENA_TRY(pool_alloc(sizeof(float), &d));
     catena_status_t s = enqueue_fold<F_SUMSQ>(in, n, nullptr, (float*)d);
     if (s == CATENA_OK) {
-        rmsnorm_map_kernel<<<grid_for(ceil_div_u64(n, 4)), kThreads, 0, tls().stream>>>(in, out, n, (float*)d);
+        rmsnorm_map_kernel<<<grid_for(ceil_div_u64(n, 4)), kThreads, 0, tls().stream>>>(in, out, n, (float*)d, 0u);
         count_launch();
     }
     pool_free(d);

@@ -277,6 +277,8 @@ catena_status_t program_attn_decode_bf16_s(catena_mem_t q, catena_mem_t kc, cate
                                            uint64_t hkv, uint64_t d, uint64_t kv_len, catena_mem_t* o) {
     if (o) { o->data = nullptr; o->len = 0; }
     CATENA_TRY(check_mem(q, "attn: null q"));
+    CATENA_TRY(check_mem(kc, "attn: null key cache"));
+    CATENA_TRY(check_mem(vc, "attn: null value cache"));
     if (q.len != batch * hq * d * 2) return fail(CATENA_E_ASSERT, "attn: q.len does not match batch*hq*d");
     if (kc.len != batch * hkv * kv_len * d * 2 || vc.len != kc.len)
         return fail(CATENA_E_ASSERT, "attn: cache length does not match batch*hkv*kv_len*d");
