@@ -31,6 +31,7 @@ sys.path.insert(0, ROOT)
 GEMM_M = GEMM_N = GEMM_K = 4096
 ATT = dict(B=32, Hq=32, Hkv=8, D=128, L=4096)
 TIMED_SECONDS = 0.5        # minimum length of the headline's timed region
+WORKLOAD = "bf16 GEMM 4096^3 (A row-major, B column-major, fp32 accumulate, bf16 out), fixed K order"
 GEMM_FLOP = 2.0 * GEMM_M * GEMM_N * GEMM_K
 ATT_BYTES = 2 * ATT["B"] * ATT["Hkv"] * ATT["L"] * ATT["D"] * 2 + 2 * ATT["B"] * ATT["Hq"] * ATT["D"] * 2
 
@@ -141,8 +142,7 @@ def run_reference(args, rank):
         "impl": "reference", "metric": "bf16_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "bf16 GEMM 4096^3 (A row-major, B column-major, fp32 accumulate, bf16 out)",
-                   "sample": sample},
+        "config": {"workload": WORKLOAD, "step": sample},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -225,9 +225,9 @@ def run_gpu(args, rank, world, local_rank):
     # A step is a batch of `per_step` launches, sized so that the K timed steps last at least TIMED_SECONDS whatever K
     # is: a region of a few milliseconds says nothing about clocks under load (one NVML sample) and flatters the kernel.
     burst_ms, _, _ = timed(gemm_step, 20, warmup)                  # the first 20 launches from idle, timed alone
-    gemm_per_step = max(1, math.ceil(TIMED_SECONDS * 1e3 / (args.steps * burst_ms / 20)))
+    gemm_per_step = args.launches_per_step or max(1, math.ceil(TIMED_SECONDS * 1e3 / (args.steps * burst_ms / 20)))
     attn_probe_ms, _, _ = timed(attn_step, 20, warmup)
-    attn_per_step = max(1, math.ceil(TIMED_SECONDS * 1e3 / (args.steps * attn_probe_ms / 20)))
+    attn_per_step = args.launches_per_step or max(1, math.ceil(TIMED_SECONDS * 1e3 / (args.steps * attn_probe_ms / 20)))
 
     def gemm_batch(i):
         for j in range(gemm_per_step):
@@ -370,12 +370,13 @@ def run_gpu(args, rank, world, local_rank):
             "metric": "bf16_gemm_tflops", "value": world * gemm_tflops_1, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": gemm_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "bf16 GEMM 4096^3 (A row-major, B column-major, fp32 accumulate, bf16 out), fixed K order; "
-                                   f"a step is {gemm_per_step} back-to-back GEMM launches per GPU, so that the timed region lasts "
-                                   f"{gemm_ms / 1e3:.2f} s whatever --steps is",
+            "config": {"workload": WORKLOAD,
+                       "step": f"{gemm_per_step} back-to-back GEMM launches per GPU, so that the timed region lasts {gemm_ms / 1e3:.2f} s "
+                               "whatever --steps is",
                        "launches_per_step": gemm_per_step, "ms_per_launch": gemm_per,
                        "l2": f"rotating over {n_sets} operand sets (384 MB) so inputs never sit in the 126 MB L2",
-                       "parallelism": f"{world} independent per-GPU problems"},
+                       "parallelism": f"{world} independent per-GPU problems (weak scaling of replicas; strong scaling of one "
+                                      "problem with its gather is under `sharded`)"},
             "clocks": {**clocks, "mhz_x_ms_per_launch": (clocks.get("sm_mhz") or 0) * gemm_per},
             "e2e": {"value": max(e2e_tflops, pipe_tflops), "unit": "TFLOP/s", "h2d_bytes_per_step": int(a_np.nbytes + bt_np.nbytes),
                     "d2h_bytes_per_step": int(c_host.nbytes), "ms_per_step": min(e2e_ms, pipe_ms),
@@ -424,7 +425,8 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
     bit-exact f32 matmul (mul and add are separate instructions by contract: one flop per lane per clock)."""
     out = {}
     fp32_unfused_peak = 148 * 128 * sm_max_mhz * 1e6 / 1e12
-    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("softmax", False), ("rmsnorm", False)):
+    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("softmax", False), ("rmsnorm", False),
+                         ("sum_u64", False), ("dot_u64", False)):
         step, work, unit, desc = single_case(cb, L, torch, dev, which, small, None)
         steps = 200 if (which == "matmul_f32" and small) else (8 if which == "matmul_f32" else 20)
         torch.cuda.synchronize(dev)
@@ -450,6 +452,8 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
             roof = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": value / peaks["hbm_gbs"],
                     "peak_source": f"{peaks['source']} copy bandwidth"}
         name = {"matmul_f32": "matmul_f32_256" if small else "matmul_f32_4096", "map": "map_nn_silu_64Mi"}.get(which, which + "_64Mi")
+        if which in ("sum_u64", "dot_u64"):
+            roof["note"] = "each step is a whole program call: two kernels, an 8-byte copy back and a stream synchronisation"
         out[name] = {"case": desc, "us_per_launch": ms * 1e3, "value": value, "unit": unit, "steps": steps, "roofline": roof}
     cb.check(L.catena_b200_check_device_errors())
     return out
@@ -814,6 +818,21 @@ def single_case(cb, L, torch, dev, which, small, shape):
             cb.check(L.catena_b200_matmul_f32_into(a.data_ptr(), b.data_ptr(), c.data_ptr(), n, n, n))
         work, unit = 2.0 * n ** 3 / 1e12, "TFLOP/s"
         desc = f"f32 matmul {n}^3 (bit-exact sequential-k)"
+    elif which in ("sum_u64", "dot_u64"):
+        n = (1 << 22) if small else (1 << 26)                   # 64 Mi u64 = 512 MiB per buffer
+        x = torch.randint(-2 ** 62, 2 ** 62, (2, n), generator=g, device=dev, dtype=torch.int64)
+        y = torch.randint(-2 ** 62, 2 ** 62, (2, n), generator=g, device=dev, dtype=torch.int64) if which == "dot_u64" else None
+        res = C.c_uint64(0)
+
+        def step(i):
+            s = i % 2
+            xm = cb.CatenaMem(x[s].data_ptr(), n * 8)
+            if which == "dot_u64":
+                cb.check(L.program_dot_u64_s(xm, cb.CatenaMem(y[s].data_ptr(), n * 8), C.byref(res)))
+            else:
+                cb.check(L.program_sum_u64_s(xm, C.byref(res)))
+        work, unit = (2 if which == "dot_u64" else 1) * n * 8 / 1e9, "GB/s"
+        desc = f"{which} over {n} u64 (exact: arithmetic modulo 2^64)"
     else:  # map / softmax / rmsnorm over 64 Mi f32 (256 MiB in, 256 MiB out)
         n = (1 << 24) if small else (1 << 26)
         x = torch.randn((2, n), generator=g, device=dev)
@@ -875,7 +894,7 @@ def run_single(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None,
-                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm", "llama"])
+                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm", "sum_u64", "dot_u64", "llama"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
     ap.add_argument("--decode-steps", type=int, default=0, help="decode steps for --only llama (default: the workload's 128)")
@@ -884,6 +903,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--launches-per-step", type=int, default=0,
+                    help="launches per step of the headline loops (default: sized from a 20-launch probe so that the timed region "
+                         "lasts 0.5 s; a profiler serialises the probe, so profile runs pin the number the plain run printed)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

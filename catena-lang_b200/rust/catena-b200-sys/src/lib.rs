@@ -62,6 +62,14 @@ extern "C" {
     // catena-lang/tests/cases/matrix/matmul.hex:2-15
     pub fn program_matmul_2x2_via_mem(a: catena_mem_t, b: catena_mem_t, n: u64, m: u64, k: u64, nk: u64, km: u64,
                                       nm: u64, out: *mut catena_mem_t);
+    // catena-lang/tests/cases/reducec/basic.hex:27-58, :60-122; catena-lang/tests/runtime.rs:713-726
+    // (catena-lang/smoketest/src/array_head.cpp:37-43 calls the last one directly)
+    pub fn program_sum_u64(input: catena_mem_t, out: *mut u64);
+    pub fn program_dot_u64(lhs: catena_mem_t, rhs: catena_mem_t, out: *mut u64);
+    pub fn program_array_head_u64(input: catena_mem_t, out: *mut u64);
+    pub fn program_sum_u64_s(input: catena_mem_t, out: *mut u64) -> catena_status_t;
+    pub fn program_dot_u64_s(lhs: catena_mem_t, rhs: catena_mem_t, out: *mut u64) -> catena_status_t;
+    pub fn program_array_head_u64_s(input: catena_mem_t, out: *mut u64) -> catena_status_t;
     // programs without a counterpart in catena-lang
     pub fn program_gemm_bf16_rc(a: catena_mem_t, b_colmajor: catena_mem_t, m: u64, n: u64, k: u64, c: *mut catena_mem_t);
     pub fn program_gemm_i8_rc(a: catena_mem_t, b_colmajor: catena_mem_t, m: u64, n: u64, k: u64, c: *mut catena_mem_t);
@@ -73,6 +81,15 @@ extern "C" {
     pub fn catena_b200_attn_decode_bf16_into(q: *const c_void, k: *const c_void, v: *const c_void, o: *mut c_void,
                                              batch: u64, hq: u64, hkv: u64, d: u64, kv_len: u64, unit0: u64,
                                              unit1: u64) -> catena_status_t;
+    // the same launches fused with the gather of a sharded result: stores into peer-mapped copies of the output
+    pub fn catena_b200_gemm_bf16_into_peers(a: *const c_void, b: *const c_void, c: *mut c_void, m: u64, n: u64, k: u64, ldc: u64,
+                                            peer_c: *const *mut c_void, n_peers: u32) -> catena_status_t;
+    pub fn catena_b200_gemm_i8_into_peers(a: *const c_void, b: *const c_void, c: *mut c_void, m: u64, n: u64, k: u64, ldc: u64,
+                                          peer_c: *const *mut c_void, n_peers: u32) -> catena_status_t;
+    pub fn catena_b200_attn_decode_bf16_into_peers(q: *const c_void, k: *const c_void, v: *const c_void, o: *mut c_void,
+                                                   batch: u64, hq: u64, hkv: u64, d: u64, kv_len: u64, unit0: u64, unit1: u64,
+                                                   peer_o: *const *mut c_void, n_peers: u32) -> catena_status_t;
+    pub fn catena_b200_check_device_errors() -> catena_status_t;
     pub fn catena_b200_sum_f32_noalloc(input: *const c_void, n: u64, out: *mut c_void) -> catena_status_t;
     // Llama-style block (device pointers throughout)
     pub fn catena_b200_llama_workspace_bytes(blk: *const catena_llama_block_t, tokens: u64) -> u64;
