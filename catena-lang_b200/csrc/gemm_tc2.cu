@@ -514,13 +514,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                     }
                 }
-                // peer copies: NVLink wants whole lines, so the warp's 32 x 32 block is transposed through shared memory
-                // (16-byte chunk index xor-ed with the row) and written with lanes along the columns
+                // peer copies: NVLink wants whole 128-byte lines, so the warp's block is transposed through shared memory (rows
+                // of 128 B, the 16-byte chunk index xor-ed with the row) and written with lanes along the columns.  A row of
+                // 32 int32 columns is one line; of bf16 it is half a line, so two consecutive 32-column steps share a row
+                // of the stage and are written out together (64 B segments reached only 400 GB/s per rank, lines 650).
                 if (HAS_PEERS && peers.n > 0) {
-                    constexpr uint32_t CH = IS_I8 ? 8u : 4u;              // 16-byte chunks per row of the block
-                    const uint32_t col = w.col0 + c;
+                    constexpr uint32_t EB = IS_I8 ? 4u : 2u;              // bytes per output element
+                    constexpr uint32_t CH = IS_I8 ? 8u : 4u;              // 16-byte chunks this step adds to a stage row
+                    const uint32_t half = IS_I8 ? 0u : ((c >> 5) & 1u);   // bf16: which half of the line this step is
+                    const uint32_t col = w.col0 + c, col_line = col - half * 32u;
                     uint8_t* stage = peer_stage + quad * PEER_STAGE_BYTES;
-                    const bool whole = col + 32 <= N && ((ldc * (IS_I8 ? 4u : 2u)) & 15u) == 0 && ((col * (IS_I8 ? 4u : 2u)) & 15u) == 0;
+                    const bool whole = col_line + (IS_I8 ? 32u : 64u) <= N && ((ldc * EB) & 15u) == 0 && ((col_line * EB) & 15u) == 0;
                     if (whole) {
                         uint4 out[8];
                         if (IS_I8) {
@@ -541,21 +545,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
 #pragma unroll
                         for (uint32_t q = 0; q < CH; ++q)
-                            *reinterpret_cast<uint4*>(stage + lane * (CH * 16) + ((q ^ (lane & (CH - 1))) << 4)) = out[q];
+                            *reinterpret_cast<uint4*>(stage + lane * 128u + (((q + half * 4u) ^ (lane & 7u)) << 4)) = out[q];
                         __syncwarp();
-                        const uint32_t row_base = w.m_blk * 2 * BM + rank * BM + quad * 32;
+                        if (IS_I8 || half == 1u) {
+                            const uint32_t row_base = w.m_blk * 2 * BM + rank * BM + quad * 32;
 #pragma unroll
-                        for (uint32_t j = 0; j < CH; ++j) {              // 32 / CH rows per instruction
-                            const uint32_t r = j * (32 / CH) + lane / CH, q = lane % CH;
-                            const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (CH * 16) + ((q ^ (r & (CH - 1))) << 4));
-                            if (row_base + r < M) {
-                                const uint64_t off = ((uint64_t)(row_base + r) * ldc + col) * (IS_I8 ? 4u : 2u) + q * 16;
+                            for (uint32_t j = 0; j < 8; ++j) {              // 4 rows of 128 B per instruction
+                                const uint32_t r = j * 4 + lane / 8, q = lane % 8;
+                                const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 128u + ((q ^ (r & 7u)) << 4));
+                                if (row_base + r < M) {
+                                    const uint64_t off = ((uint64_t)(row_base + r) * ldc + col_line) * EB + q * 16;
 #pragma unroll
-                                for (uint32_t pi = 0; pi < (uint32_t)kMaxPeers; ++pi)
-                                    if (pi < peers.n) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(peers.ptr[pi]) + off) = val;
+                                    for (uint32_t pi = 0; pi < (uint32_t)kMaxPeers; ++pi)
+                                        if (pi < peers.n) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(peers.ptr[pi]) + off) = val;
+                                }
                             }
+                            __syncwarp();
                         }
-                        __syncwarp();
                     } else if (row < M) {
 #pragma unroll
                         for (uint32_t pi = 0; pi < (uint32_t)kMaxPeers; ++pi) {
