@@ -410,7 +410,10 @@ def run_gpu(args, rank, world, local_rank):
                                          "traffic_source": "4 x the ncu capture of the B=8 case (profiles/attn_decode_tc_small_B8.md)",
                                          "peak_source": f"{peaks['source']} copy bandwidth", "kernel": "attn_decode_tc_kernel"}},
             "llama_block": llama,
-            "sharded": {"scaling": "strong", "n_gpus": world, **sharded},
+            "sharded": {"scaling": "strong", "n_gpus": world,
+                        "timing": "ms_total and ms_1gpu: CUDA events around 8 back-to-back steps, mean of 3 regions, max over ranks; "
+                                  "ms_compute / ms_gather: events inside single steps",
+                        **sharded},
             "cpu_baseline": cpu_baseline,
             "output_checksum": f"{checksum:016x}",
         }
@@ -533,22 +536,35 @@ def sharded_bench(cb, L, torch, dist, shard, dev, stream, rank, world, peaks, re
         if world > 1:
             dist.barrier()
 
-    def time_steps(step, parts=1):
-        """Device time of `step` (mean of `reps` after one warm-up run), max over ranks; `step` records the events it
-        is given between its parts."""
+    def time_steps(step, parts=1, inner=8):
+        """Device time of `step`, max over ranks.  The total is taken over `inner` back-to-back steps per timed region (mean
+        of `reps` regions after a warm-up step), the way a serving loop issues them — a lone step launched into an idle
+        stream measures the launch latency of its first kernel as much as the work.  With parts > 1 the split between the
+        parts comes from a second pass of single steps, `step` recording the events it is given between its parts."""
         with torch.cuda.stream(stream):
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(parts + 1)]
             step(None)
             sync_all()
-            t = [0.0] * parts
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            total = 0.0
             for _ in range(reps):
-                ev[0].record(stream)
-                step(ev)
-                ev[parts].record(stream)
-                sync_all()                                     # every rank's stores have landed before the next run
-                for i in range(parts):
-                    t[i] += ev[i].elapsed_time(ev[i + 1]) / reps
-        return [shard.max_over_ranks(x, dd, dev) for x in t], shard.max_over_ranks(sum(t), dd, dev)
+                e0.record(stream)
+                for _ in range(inner):
+                    step(None)
+                e1.record(stream)
+                sync_all()                                     # every rank's stores have landed before the next region
+                total += e0.elapsed_time(e1) / inner / reps
+            t = [total]
+            if parts > 1:
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(parts + 1)]
+                t = [0.0] * parts
+                for _ in range(reps):
+                    ev[0].record(stream)
+                    step(ev)
+                    ev[parts].record(stream)
+                    sync_all()
+                    for i in range(parts):
+                        t[i] += ev[i].elapsed_time(ev[i + 1]) / reps
+        return [shard.max_over_ranks(x, dd, dev) for x in t], shard.max_over_ranks(total, dd, dev)
 
     def checksum(t):
         view = t.view(torch.int16) if t.dtype == torch.bfloat16 else t
@@ -595,12 +611,13 @@ def sharded_bench(cb, L, torch, dist, shard, dev, stream, rank, world, peaks, re
         # (1) compute on the row block, NCCL all-gather of the blocks
         c_block = torch.empty((rows, N), dtype=torch_out, device=dev)
         holder = {}
+        full_view.zero_()
 
         def nccl_step(ev):
             cb.check(fn_into(a_ptr + mine.m0 * K * es, b_ptr, c_block.data_ptr(), rows, N, K, N))
             if ev:
                 ev[1].record(stream)
-            holder["full"] = shard.gather_rows(c_block, blocks, dd)
+            holder["full"] = shard.gather_rows(c_block, blocks, dd, out=full_view if world > 1 else None)
         (t_c, t_g), total = time_steps(nccl_step, parts=2)
         item = {"ms_total": total, "ms_compute": t_c, "ms_gather": t_g, "checksum": checksum(holder["full"]), "gather": "NCCL all-gather of row blocks"}
         assert item["checksum"] == sum_1, "sharded result differs from the unsharded one"
@@ -642,7 +659,9 @@ def sharded_bench(cb, L, torch, dist, shard, dev, stream, rank, world, peaks, re
         cb.check(L.catena_b200_attn_decode_bf16_into(*att_args, ranges[rank].u0, ranges[rank].u1))
         if ev:
             ev[1].record(stream)
-        holder["full"] = shard.gather_units(o_view[ranges[rank].u0:ranges[rank].u1], ranges, G * ATT["D"], dd)
+        holder["full"] = shard.gather_units(o_view[ranges[rank].u0:ranges[rank].u1], ranges, G * ATT["D"], dd,
+                                            out=o_full if world > 1 else None)
+    o_full = torch.zeros((units, G * ATT["D"]), dtype=torch.int16, device=dev)
     o_view.zero_()
     (t_c, t_g), total = time_steps(attn_nccl, parts=2)
     item = {"ms_total": total, "ms_compute": t_c, "ms_gather": t_g, "checksum": checksum(holder["full"]), "gather": "NCCL all-gather of O"}

@@ -57,16 +57,20 @@ def _from_wire(t, was_int16):
     return t.view(torch.int16) if was_int16 else t
 
 
-def gather_rows(local_block, blocks, dist=None, group=None):
+def gather_rows(local_block, blocks, dist=None, group=None, out=None):
     """All-gathers contiguous row blocks [m1-m0, N] into the full [M, N] matrix on every rank (one collective when
-    the blocks are equal, padded otherwise)."""
+    the blocks are equal, padded otherwise).  `out`: a preallocated [M, N] tensor to gather into when the blocks are
+    equal (a serving loop reuses its output buffer instead of allocating one per step)."""
     import torch
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_block
     local_block, was_int16 = _as_wire(local_block)
     heights = [b.m1 - b.m0 for b in blocks]
     if len(set(heights)) == 1:
-        full = torch.empty((sum(heights),) + tuple(local_block.shape[1:]), dtype=local_block.dtype, device=local_block.device)
+        if out is not None:
+            full = _as_wire(out)[0]
+        else:
+            full = torch.empty((sum(heights),) + tuple(local_block.shape[1:]), dtype=local_block.dtype, device=local_block.device)
         dist.all_gather_into_tensor(full, local_block.contiguous(), group=group)
         return _from_wire(full, was_int16)
     hmax = max(heights)
@@ -107,15 +111,15 @@ def gather_columns(local_block, blocks, rows, dist=None, group=None):
     return _from_wire(torch.cat([p[:, :w] for p, w in zip(parts, widths)], dim=1), was_int16)
 
 
-def gather_units(local_rows, ranges, row_width, dist=None, group=None):
-    """All-gathers per-unit output rows (attention O) in unit order."""
+def gather_units(local_rows, ranges, row_width, dist=None, group=None, out=None):
+    """All-gathers per-unit output rows (attention O) in unit order; `out` as in gather_rows."""
     import torch
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_rows
     local_rows, was_int16 = _as_wire(local_rows)
     counts = [r.u1 - r.u0 for r in ranges]
     if len(set(counts)) == 1:                                  # equal ranges: one collective straight into place
-        full = torch.empty((sum(counts), row_width), dtype=local_rows.dtype, device=local_rows.device)
+        full = _as_wire(out)[0] if out is not None else torch.empty((sum(counts), row_width), dtype=local_rows.dtype, device=local_rows.device)
         dist.all_gather_into_tensor(full, local_rows.contiguous(), group=group)
         return _from_wire(full, was_int16)
     cmax = max(counts)
