@@ -784,7 +784,7 @@ def llama_bench(cb, L, torch, dev, stream, peaks, cfg, reps=2):
             "end_to_end_ms": times["prefill"] + times["decode"], "output_checksum": f"{checksum:012x}"}
 
 
-def single_case(cb, L, torch, dev, which, small, shape):
+def single_case(cb, L, torch, dev, which, small, shape, units=0):
     """One kernel of the path on the bench workload (or a smaller case): returns (step(i), work per launch, unit, text)."""
     g = torch.Generator(device=dev)
     g.manual_seed(1)
@@ -821,12 +821,14 @@ def single_case(cb, L, torch, dev, which, small, shape):
             o = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=dev)
             sets.append((q, kk, vv, o))
 
+        n_units = min(units, B * Hkv) if units else B * Hkv      # --units: only the first (batch, kv-head) units, as one rank of a sharded run
+
         def step(i):
             q, kk, vv, o = sets[i % 2]
             cb.check(L.catena_b200_attn_decode_bf16_into(q.data_ptr(), kk.data_ptr(), vv.data_ptr(), o.data_ptr(), B, Hq,
-                                                         Hkv, D, Lk, 0, B * Hkv))
-        work, unit = (2 * B * Hkv * Lk * D * 2 + 2 * B * Hq * D * 2) / 1e9, "GB/s"
-        desc = f"attn decode B={B} Hq={Hq} Hkv={Hkv} D={D} L={Lk}"
+                                                         Hkv, D, Lk, 0, n_units))
+        work, unit = n_units * (2 * Lk * D * 2 + 2 * (Hq // Hkv) * D * 2) / 1e9, "GB/s"
+        desc = f"attn decode B={B} Hq={Hq} Hkv={Hkv} D={D} L={Lk}, units 0..{n_units - 1}"
     elif which == "matmul_f32":
         n = 256 if small else 4096
         a = torch.rand((n, n), generator=g, device=dev) * 2 - 1
@@ -892,7 +894,7 @@ def run_single(args):
         res = llama_bench(cb, L, torch, dev, stream, measured_peaks(), cfg, reps=max(1, min(args.steps, 3)))
         print(json.dumps({"only": "llama", **res}), flush=True)
         return
-    step, work, unit, desc = single_case(cb, L, torch, dev, which, args.small, args.shape)
+    step, work, unit, desc = single_case(cb, L, torch, dev, which, args.small, args.shape, args.units)
     torch.cuda.synchronize(dev)
     with torch.cuda.stream(stream):
         for i in range(args.warmup):
@@ -916,6 +918,7 @@ def main():
                     choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm", "sum_u64", "dot_u64", "llama"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
+    ap.add_argument("--units", type=int, default=0, help="--only attn: launch only the first N (batch, kv-head) units")
     ap.add_argument("--decode-steps", type=int, default=0, help="decode steps for --only llama (default: the workload's 128)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)

@@ -72,3 +72,42 @@ def test_stdlib_extension_registers_the_added_programs():
         assert name in rt.signatures and rt.signatures[name][0] == cb.symbol_for(name)
     text = open(path).read()
     assert text.count("(") == text.count(")") and text.count("{") == text.count("}") and text.count("[") == text.count("]")
+
+
+def test_integer_and_scalar_modules_of_the_reference_tests():
+    """The hand-lowered test programs of the reference (tests/lowered_fixtures.py): buffer folds over u64 select the u64
+    kernels, the buffer-head program the 8-byte copy, everything scalar the host evaluator; a scalar module that walks a
+    buffer in any other way has no plan."""
+    import lowered_fixtures as fx
+    from catena_lang_b200.lowering import LIBRARY_ENTRY, module_map
+    mods = fx.reducec_programs() + fx.array_head_program() + fx.all_host_modules()
+    mm = module_map(mods)
+    def callable_through_exec(m):       # no `buf` pointer on the boundary (runtime/signature.rs:63-72)
+        return m.source_name and not any(v.lowered.startswith("ptr<") for v in m.entry.sources + m.entry.targets)
+    plans = {m.source_name: lo.select(m, modules=mm) for m in mods if callable_through_exec(m)}
+    assert plans["sum-u64"].kernel == "fold_sum_u64" and plans["sum-u64"].entry == "program_sum_u64"
+    assert plans["dot-u64"].kernel == "fold_dot_u64" and plans["dot-u64"].entry == "program_dot_u64"
+    assert plans["array-head-u64"].kernel == "array_head_u64" and LIBRARY_ENTRY["array_head_u64"] == "program_array_head_u64"
+    for name in ("not", "bool-ifc-primitives", "shift-and-sub", "fma-fused-bits", "ordered-pair", "sum-progression", "progression-moments",
+                 "u64.add-env"):
+        assert plans[name].kernel == "host_scalar", name
+    # `sum-u64-at` reads a buffer element on its own: on the host that is a dereference of device memory
+    with pytest.raises(lo.Unsupported):
+        lo.select(mm["sum-u64-at"], modules=mm)
+    # a fold whose getter is unknown to the selector and whose environment holds a buffer has no plan either
+    odd = fx.M("odd-fold", [fx.v("m", "mem")], [fx.v("r", "u64")], [
+        fx.A("mem.cast.u64", [fx.v("m", "mem")], [fx.v("len", "u64"), fx.v("buf", "ptr<u64>")]),
+        fx.A("const.u64.0x0000000000000000", [], [fx.v("zero", "u64")]),
+        fx.A("reducec", [fx.v("zero", "u64"), fx.fn("u64.add-env"), fx.v("buf", "ptr<u64>"), fx.fn("some-other-getter"), fx.v("len", "u64")],
+             [fx.v("r", "u64")], [1, 0, 1, 1, 1, 1], [1])])
+    with pytest.raises(lo.Unsupported):
+        lo.select(odd, modules=mm)
+
+
+def test_runtime_from_modules_refuses_what_it_cannot_run():
+    import catena_lang_b200 as cb
+    import lowered_fixtures as fx
+    odd = fx.M("materialize-something", [fx.v("n", "u64")], [fx.v("out", "mem")], [
+        fx.A("materializec", [fx.v("n", "u64"), fx.fn("some.unknown-producer")], [fx.v("out", "mem")])])
+    with pytest.raises(cb.InitError):
+        cb.Runtime.from_modules([odd])
