@@ -503,7 +503,7 @@ bool attn_tc_supports(uint32_t G, uint64_t kv_len);
 void attn_tc_reset_exchange();
 catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
                                        uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1, int cluster_limit,
-                                       uint32_t* err_dev, void* const* peer_o, uint32_t n_peers);
+                                       uint32_t* err_dev, void* const* peer_o, uint32_t n_peers, const AttnPrefetch* prefetch);
 
 // After enqueuing: in blocking mode wait and turn a device-side bounded-wait expiry into a status.
 static catena_status_t attn_finish_launch(int dev) {
@@ -532,7 +532,7 @@ static size_t attn_smem_bytes(uint32_t G, uint32_t chunk) {
 
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch, uint64_t hq,
                                    uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1,
-                                   void* const* peer_o, uint32_t n_peers) {
+                                   void* const* peer_o, uint32_t n_peers, const AttnPrefetch* prefetch) {
     CATENA_TRY(ensure_device());
     if (!q || !kc || !vc || !o) return fail(CATENA_E_BAD_ARG, "attn_decode: null operand");
     if (d != (uint64_t)attn::kD) return fail(CATENA_E_UNSUPPORTED, "attn_decode: head_dim must be 128");
@@ -555,7 +555,7 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
     }
     if (attn_tc_mode() && attn_tc_supports(G, kv_len) && ((uintptr_t)q & 15) == 0) {
         CATENA_TRY(enqueue_attn_decode_tc(q, kc, vc, o, units, G, kv_len, kv_cap, unit0, unit1, g_attn_cluster_limit, g_attn_err_dev[dev],
-                                          peer_o, n_peers));
+                                          peer_o, n_peers, prefetch));
         return attn_finish_launch(dev);
     }
     if (n_peers > 0) return fail(CATENA_E_UNSUPPORTED, "attn_decode: peer outputs need the tcgen05 kernel (at most 7168 cache rows, 16-byte aligned q)");

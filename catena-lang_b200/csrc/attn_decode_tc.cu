@@ -255,12 +255,26 @@ struct PeerO {
     uint32_t n;
 };
 
+// Optional L2 prefetch hint: ranges of this GPU's memory that the kernels launched AFTER this one will stream (weights of
+// the projections that follow a decode step's attention).  This kernel is latency-bound for short caches and leaves HBM
+// bandwidth unused; an otherwise idle warp per CTA (the finisher of pipe 0, before its first item can be ready) issues
+// paced bulk prefetches into L2 for the CTA's share of the ranges.  A hint only: nothing waits for it, results never
+// depend on it.
+constexpr int kMaxPrefetch = 4;
+struct PrefetchHint {
+    const uint8_t* ptr[kMaxPrefetch];
+    uint32_t chunks[kMaxPrefetch];          // 16 KiB chunks of each range
+    uint32_t n;
+    uint32_t pace_ns;                       // pause between two chunks of a CTA
+};
+constexpr uint32_t kPrefetchChunk = 16384;
+
 // grid.x CTAs (all resident), 384 threads; npipes = 2 * gridDim.x is a multiple of 8 or at least `items`.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ o, uint32_t L, uint32_t G,
                       uint32_t unit0, uint32_t items, uint32_t chunk, float scale, Exchange ex, uint32_t* err, uint64_t wait_ns,
-                      uint32_t stall, PeerO peers) {
+                      uint32_t stall, PeerO peers, PrefetchHint pf) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -329,6 +343,16 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         // in ascending chunk order.  (One pipe combining the whole unit would be slower than its seven mates, which
         // all wait for it at the next exchange of maxima.)
         const uint32_t per_rank = G * kD / kSplits;          // outputs per pipe and unit: G * 16
+        if (warp == 12 && lane == 0 && pf.n != 0) {
+            for (uint32_t r = 0; r < pf.n && r < (uint32_t)kMaxPrefetch; ++r) {
+                for (uint32_t c = blockIdx.x; c < pf.chunks[r]; c += gridDim.x) {
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ptr[r] + (size_t)c * kPrefetchChunk), "r"(kPrefetchChunk)
+                                 : "memory");
+                    if (pf.pace_ns) __nanosleep(pf.pace_ns);
+                }
+            }
+        }
+        __syncwarp();
         for (uint32_t j = 0; j < n; ++j) {
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(&ctl->fin_ready, j & 1u, com, err))) break;
             TR(3, 1);
@@ -778,7 +802,18 @@ void attn_tc_reset_exchange() {
 // Enqueues the tcgen05 decode kernel (arguments already validated by launch_attn_decode).
 catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void* vc, void* o, uint64_t units, uint32_t G,
                                        uint64_t kv_len, uint64_t kv_cap, uint64_t unit0, uint64_t unit1, int cluster_limit,
-                                       uint32_t* err_dev, void* const* peer_o, uint32_t n_peers) {
+                                       uint32_t* err_dev, void* const* peer_o, uint32_t n_peers, const AttnPrefetch* prefetch) {
+    attn2::PrefetchHint pf = {};
+    if (prefetch) {
+        for (uint32_t i = 0; i < prefetch->n && pf.n < (uint32_t)attn2::kMaxPrefetch; ++i) {
+            const uint64_t chunks = prefetch->bytes[i] / attn2::kPrefetchChunk;          // whole chunks only: never past the end
+            if (!prefetch->ptr[i] || ((uintptr_t)prefetch->ptr[i] & 15) || chunks == 0) continue;
+            pf.ptr[pf.n] = static_cast<const uint8_t*>(prefetch->ptr[i]);
+            pf.chunks[pf.n] = (uint32_t)(chunks > 0xFFFFFFFFull ? 0xFFFFFFFFull : chunks);
+            ++pf.n;
+        }
+        pf.pace_ns = prefetch->pace_ns;
+    }
     if (n_peers > (uint32_t)attn2::kMaxPeers) return fail(CATENA_E_BAD_ARG, "attn_decode: more than 7 peer outputs");
     attn2::PeerO peers = {};
     peers.n = n_peers;
@@ -871,7 +906,7 @@ catena_status_t enqueue_attn_decode_tc(const void* q, const void* kc, const void
     float scale = 1.0f / sqrtf((float)attn2::kD);
     CATENA_CUDA(cudaLaunchKernelEx(&cfg, attn2::attn_decode_tc_kernel, map_k, map_v, (const __nv_bfloat16*)q, (__nv_bfloat16*)o,
                                    (uint32_t)kv_len, G, (uint32_t)unit0, (uint32_t)items, chunk, scale, ex, err_dev,
-                                   debug_wait_limit_ns(), debug_take_stall(2), peers));
+                                   debug_wait_limit_ns(), debug_take_stall(2), peers, pf));
     count_launch();
     return CATENA_OK;
 }

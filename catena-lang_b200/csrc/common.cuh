@@ -97,9 +97,18 @@ void attn_last_launch(uint32_t out[4]);
 catena_status_t attn_prefill_rcp_check(uint64_t out[2]);
 extern thread_local uint32_t g_attn_last_launch[4];
 // attn_decode.cu
+// Ranges of memory that the kernels queued after a decode-attention launch will stream: the tcgen05 kernel prefetches
+// them into L2 from an idle warp while it runs (a hint; results never depend on it).
+struct AttnPrefetch {
+    const void* ptr[4];
+    uint64_t bytes[4];
+    uint32_t n;
+    uint32_t pace_ns;
+};
 catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc, void* o, uint64_t batch,
                                    uint64_t hq, uint64_t hkv, uint64_t d, uint64_t kv_len, uint64_t kv_cap,
-                                   uint64_t unit0, uint64_t unit1, void* const* peer_o = nullptr, uint32_t n_peers = 0);
+                                   uint64_t unit0, uint64_t unit1, void* const* peer_o = nullptr, uint32_t n_peers = 0,
+                                   const AttnPrefetch* prefetch = nullptr);
 catena_status_t attn_check_errors();
 // llama_decode_fused.cu: the part of a decode step after its attention as one persistent kernel
 int decode_fused_mode();      // bit 0: the tail kernel, bit 1: the head kernel

@@ -839,8 +839,27 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
         }
         }
         if (seq == 1) {
+            // While the attention runs (latency-bound for a cache of a few thousand rows) it prefetches into L2 what the
+            // projections behind it will stream first: W_o, then the leading gate and up rows, then the leading down rows.
+            static const uint64_t budget = [] { const char* v = getenv("CATENA_B200_DECODE_PREFETCH_MB"); return (uint64_t)(v ? atoi(v) : 0) << 20; }();
+            static const uint32_t pace = [] { const char* v = getenv("CATENA_B200_DECODE_PREFETCH_PACE_NS"); return (uint32_t)(v ? atoi(v) : 400); }();
+            AttnPrefetch pf = {};
+            if (budget) {
+                uint64_t left = budget;
+                auto add = [&](const void* p, uint64_t bytes) {
+                    const uint64_t take = bytes < left ? bytes : left;
+                    if (take >= 16384 && pf.n < 4) { pf.ptr[pf.n] = p; pf.bytes[pf.n] = take; ++pf.n; left -= take; }
+                };
+                const uint64_t wo = d.H * d.Hq * llama::kHeadDim * 2, half = d.F * d.H * 2;
+                add(blk->w_o, wo);
+                const uint64_t gu = left / 2 < half ? left / 2 : half;
+                add(blk->w_gate_up, gu);
+                add(static_cast<const char*>(blk->w_gate_up) + half, gu);
+                add(blk->w_down, d.H * d.F * 2);
+                pf.pace_ns = pace;
+            }
             CATENA_TRY(launch_attn_decode(q, k_cache, v_cache, att, batch, d.Hq, d.Hkv, llama::kHeadDim, pos0 + 1, blk->max_len, 0,
-                                          batch * d.Hkv));
+                                          batch * d.Hkv, nullptr, 0, pf.n ? &pf : nullptr));
         } else {
             if (pos0 != 0) return fail(CATENA_E_UNSUPPORTED, "llama: a multi-token step must start at position 0");
             CATENA_TRY(launch_attn_prefill(q, k_cache, v_cache, att, batch, seq, d.Hq, d.Hkv, blk->max_len));

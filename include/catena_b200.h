@@ -55,7 +55,14 @@ enum {
 catena_status_t catena_b200_init(int device);
 int catena_b200_device_count(void);
 /* Entry points launch on this stream (default: the legacy default stream, as the generated
- * code does).  `stream` is a cudaStream_t. */
+ * code does).  `stream` is a cudaStream_t.
+ * Threads and streams: device, stream, blocking flag, last status and the scratch that kernels share between launches
+ * (attention exchange area, rotary tables, device error words) belong to the calling HOST THREAD, per device.  One thread
+ * drives one stream at a time: set_stream waits (in non-blocking mode) for the work queued on the old stream before the
+ * same scratch can be used from the new one.  Several host threads may drive one device on their own streams; they share
+ * only the memory pool, which orders the reuse of a freed block after the freeing stream's queued work.  As in the
+ * reference (a device-wide synchronisation after every launch, catena-lang/src/codegen/ops/materializec.rs:138-141) the
+ * compute entry points are not re-entrant on one thread's state. */
 catena_status_t catena_b200_set_stream(void* stream);
 void* catena_b200_get_stream(void);
 /* 1 (default): every entry point synchronises before returning, as the generated code's
@@ -70,7 +77,10 @@ const char* catena_b200_version(void);
 /* number of kernels this library launched since load (all threads) */
 uint64_t catena_b200_launch_count(void);
 
-/* ---- allocator (replaces GpuRuntime::{alloc,free}, catena-lang/src/runtime/mem.rs:152-190) */
+/* ---- allocator (replaces GpuRuntime::{alloc,free}, catena-lang/src/runtime/mem.rs:152-190)
+ * A size-class pool over cudaMalloc, per device, shared by the host threads of that device.  mem_free in non-blocking mode
+ * records an event on the calling thread's stream; a later mem_alloc that reuses the block from another stream makes
+ * that stream wait for the event, so kernels still queued on the freeing stream never see the block change under them. */
 catena_status_t catena_b200_mem_alloc(uint64_t bytes, catena_mem_t* out);
 catena_status_t catena_b200_mem_free(catena_mem_t mem);
 /* Mem::from_slice (catena-lang/src/runtime/mem.rs:72-106): allocate + copy host bytes in */
