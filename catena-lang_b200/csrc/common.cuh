@@ -121,6 +121,8 @@ catena_status_t launch_decode_head(const void* table, const int32_t* ids, const 
                                    void* qkv, void* q_out, void* k_cache, void* v_cache, uint64_t m, uint64_t hidden, uint64_t vocab,
                                    uint64_t hq, uint64_t hkv, uint64_t cap, uint64_t pos);
 catena_status_t decode_fused_check_errors();
+// map_program.cu
+catena_status_t map_program_check_errors();
 // map_reduce.cu
 enum ReduceKind { RED_SUM = 0, RED_MAX = 1, RED_SUMSQ = 2 };
 int map_op_from_name(const char* name);  // -1 if unknown

@@ -322,6 +322,7 @@ catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]) {
 catena_status_t catena_b200_check_device_errors(void) {
     CATENA_TRY(gemm_tc_check_errors());
     CATENA_TRY(decode_fused_check_errors());
+    CATENA_TRY(map_program_check_errors());
     return attn_check_errors();
 }
 

@@ -22,8 +22,10 @@ IEEE binary32 operations, never contracted (catena-lang/src/runtime/artifact.rs:
 A failed `assert` raises `AssertFailed` (the generated code traps, catena-lang/src/codegen/prelude.rs:38-55).
 
 Values: bool / u32 / u64 are Python ints, f32 is numpy.float32, `ptr<u64>` / `ptr<f32>` are numpy arrays (host
-views), `mem` is a numpy uint8 array, erased wires are None.  `materializec` and `gpu.materialize` are kernel
-launches and are not evaluated here: the selector sends modules that contain them to the prebuilt kernels.
+views) or `DeviceMem`s (device buffers: cast and passed on, never dereferenced), `mem` is a numpy uint8 array or a
+`DeviceMem`, erased wires are None.  `materializec` is a kernel launch: the evaluator hands it to the `materialize`
+callback it was built with (runtime.py launches the generic map kernel there) and refuses it otherwise; modules whose
+`materializec` matches a prebuilt kernel never come here.
 """
 import ctypes
 import ctypes.util
@@ -133,6 +135,31 @@ def _select(flag, a, b):
     return [a if flag else b]
 
 
+class DeviceMem:
+    """A buffer in device memory as host code sees it: it can be cast, truncated and handed to a kernel, but not
+    dereferenced (the reference's host code reads managed memory; this backend's buffers are plain device memory)."""
+    __slots__ = ("ptr", "nbytes", "dtype")
+
+    def __init__(self, ptr, nbytes, dtype=np.uint8):
+        self.ptr, self.nbytes, self.dtype = int(ptr or 0), int(nbytes), np.dtype(dtype)
+
+    @property
+    def size(self):
+        return self.nbytes // self.dtype.itemsize
+
+    def view(self, dtype):
+        return DeviceMem(self.ptr, self.nbytes, dtype)
+
+    def truncated(self, length):
+        return DeviceMem(self.ptr, int(length) * self.dtype.itemsize, self.dtype)
+
+
+def _to_mem(length, buffer):
+    if isinstance(buffer, DeviceMem):
+        return [buffer.truncated(length).view(np.uint8)]
+    return [np.ascontiguousarray(buffer[: int(length)]).view(np.uint8)]
+
+
 # op -> function(*positional inputs) -> list of outputs (erased outputs are padded with None by the caller)
 PRIMITIVES = {
     "bool.t": lambda: [1], "bool.f": lambda: [0],
@@ -167,13 +194,15 @@ PRIMITIVES = {
     "buf.f32.cast-same-length": lambda buffer, _same: [buffer],
     "mem.cast.u64": lambda mem: [mem.size // 8, mem.view(np.uint64)],
     "mem.cast.f32": lambda mem: [mem.size // 4, mem.view(np.float32)],
-    "buf.to-mem": lambda length, buffer: [np.ascontiguousarray(buffer[: int(length)]).view(np.uint8)],
+    "buf.to-mem": _to_mem,
 }
 # rendered as nothing (gpu.rs:372-373): their outputs are type-level
 NO_OPS = {"unit.intro", "ax-mp", "assert-then", ":.param"}
 
 
 def _load(buffer, index):
+    if isinstance(buffer, DeviceMem):
+        raise NotScalar("host code cannot dereference device memory")
     v = buffer[int(index)]          # an index past the end is out of contract (the type system bounds `ix n`)
     return np.float32(v) if buffer.dtype == np.float32 else int(v)
 
@@ -186,9 +215,12 @@ def is_primitive(op):
 class Evaluator:
     """Evaluates functions of a module map {symbol or source name -> GpuModule}."""
 
-    def __init__(self, modules):
+    def __init__(self, modules, materialize=None):
+        """`materialize(assignment, length, environment values, function symbol) -> buffer` runs a `materializec` (a kernel
+        launch); without it such an assignment is refused."""
         from .lowering import module_map
         self.by_name = module_map(modules)
+        self.materialize = materialize
 
     # ---- one function ----
     def call(self, name, args):
@@ -272,6 +304,10 @@ class Evaluator:
                 self._apply(scratch, add_sym, list(add_env) + acc + values, nexts)
                 acc = [scratch[x.name] for x in nexts]
             self._bind(env, a.outputs, acc)
+        elif a.op == "materializec" and self.materialize is not None:       # ops/materializec.rs:84-145: len, env..., producer
+            from .lowering import materializec_parts
+            length, env_values, fn_sym = materializec_parts(a, ins)
+            self._bind(env, a.outputs, [self.materialize(a, int(length), env_values, fn_sym)])
         else:
             raise NotScalar(f"`{a.op}` is not a scalar assignment")
 

@@ -21,8 +21,10 @@ recognises the shapes the stdlib lowers to:
   * `mem.cast.u64`, `ix.zero`, `ix` (catena-lang/tests/runtime.rs:713-726)   -> buffer-head copy
   * a module of scalar primitives, `bool.ifc`, `eval`, calls of scalar modules and `reducec` whose
     closures are scalar (catena-lang/tests/cases/closures/*.hex)             -> host execution (evaluator.py)
-Anything else is reported as unsupported (the reference would render a generic one-thread-per-element
-kernel for it; this backend ships no source generator).
+  * any other `materializec` whose producer is scalar code over its environment and index
+    (catena-lang/examples/materializec.hex, tests/cases/materialize/basic.hex) -> the generic map kernel, which
+    interprets the producer as a register program (map_program.py); the code around it runs on the host
+Anything else is reported as unsupported (an allocation inside a producer, a buffer chosen at run time).
 
 The Rust front end that produces the IR is not part of this build, so fixtures for the tests are
 written by hand from the lowering rules cited above.
@@ -150,6 +152,33 @@ def _scalar_function(name, modules, seen, allow_memory=False):
     return all(classify(a, modules, seen) == "scalar" and (allow_memory or not _touches_memory(a)) for a in module.entry.assignments)
 
 
+def materializec_parts(assign, values=None):
+    """(len, environment, producer symbol) of a `materializec` — the closure-converted call shape `len, env..., producer_fn`
+    (catena-lang/src/codegen/ops/materializec.rs:147-189) — taken from `values` (one per input) or from the inputs."""
+    items = list(assign.inputs if values is None else values)
+    if assign.input_sizes is not None:
+        if len(assign.input_sizes) != 3 or sum(assign.input_sizes) != len(items) or assign.input_sizes[0] != 1:
+            raise Unsupported("materializec expects the components len, env, producer")
+        env = items[1:1 + assign.input_sizes[1]]
+        fn = items[1 + assign.input_sizes[1]:]
+    else:
+        env, fn = items[1:-1], items[-1:]
+    fns = [v for v in fn if isinstance(v, FnSymbol)]
+    if len(fns) != 1:
+        raise Unsupported("materializec needs one producer symbol")
+    return items[0], env, fns[0]
+
+
+def map_program_for(assign, modules):
+    """The register program of a `materializec` whose producer has no prebuilt kernel (map_program.py); raises Unsupported."""
+    from .map_program import compile_producer
+    if len(assign.outputs) != 1 or not assign.outputs[0].lowered.startswith("ptr<"):
+        raise Unsupported("materializec produces one buffer")
+    _, env, fn = materializec_parts(assign)
+    env_vars = [v for v in env if isinstance(v, GpuVar) and v.lowered != "erased"]
+    return compile_producer(modules or {}, fn.name, env_vars, assign.outputs[0].lowered[4:-1])
+
+
 def classify(assign, modules=None, _seen=frozenset()):
     """One assignment -> kernel family, 'scalar' or None.  `modules` maps source names (and generated symbols) to the
     lowered modules of the program, so that calls and closure symbols can be looked through."""
@@ -169,6 +198,12 @@ def classify(assign, modules=None, _seen=frozenset()):
         for f in fns:
             if f in _MAPS:
                 return _MAPS[f]
+        if assign.op == "materializec" and modules is not None:
+            try:
+                map_program_for(assign, modules)
+                return "map_generic"
+            except Unsupported:
+                return None
         return None
     if assign.op in ("bool.ifc", "eval"):
         fns = _fn_symbols(assign)
@@ -219,6 +254,12 @@ def select(module, symbol_for=None, modules=None):
             kinds.append(k)
     symbol = symbol_for(module.source_name) if module.source_name else module.name
     ops = [a.op for a in module.entry.assignments]
+    if kinds and all(k == "map_generic" for k in kinds):
+        # host code around one or more generic map kernels: the host part may cast and pass buffers on, not read them
+        for a in module.entry.assignments:
+            if a.op != "materializec" and _touches_memory(a) and not a.op.startswith(("mem.cast.", "buf.")) and not a.call_symbol:
+                raise Unsupported(f"{module.name}: host code reads a device buffer (`{a.op}`)")
+        return KernelPlan("host_with_map_kernels", symbol, ["producers interpreted by the generic map kernel; the code around them runs on the host"])
     if not kinds:
         if any(_touches_memory(a) for a in module.entry.assignments):
             # scalar code that reads a buffer: the host cannot dereference device memory, so only the shape with a

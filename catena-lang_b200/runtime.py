@@ -184,6 +184,9 @@ class Runtime:
         from . import lib
         self._lib = lib()
         self.signatures = signatures
+        self._map_programs = {}          # id(materializec assignment) -> map_program.MapProgram
+        self._map_eval = None
+        self._map_outputs = {}           # device pointer -> CatenaMem of the buffers the current exec materialised
 
     @classmethod
     def new(cls, paths, dialect=GpuDialect.Cuda):
@@ -235,6 +238,16 @@ class Runtime:
             if plan.kernel == "host_scalar":
                 rt.signatures[m.source_name] = (plan.symbol, [kinds[t] for t in ins], [kinds[t] for t in outs],
                                                 (lambda args, _name=m.name: evaluator.call(_name, args)))
+                continue
+            if plan.kernel == "host_with_map_kernels":
+                # the producers' register programs are built now, so that a producer the map kernel cannot run is an
+                # InitError and `exec` only binds the environment and launches
+                from .lowering import map_program_for
+                for a in m.entry.assignments:
+                    if a.op == "materializec":
+                        rt._map_programs[id(a)] = map_program_for(a, mm)
+                rt.signatures[m.source_name] = (plan.symbol, [kinds[t] for t in ins], [kinds[t] for t in outs],
+                                                (lambda args, _name=m.name: rt._map_evaluator(modules).call(_name, args)))
                 continue
             entry = plan.entry
             if entry is None or ENTRY_SIGNATURE.get(entry) != (ins, outs) or not hasattr(lib(), entry):
@@ -301,16 +314,66 @@ class Runtime:
                 results.append(Value(kind, int(o.value)))
         return results
 
+    def _map_evaluator(self, modules):
+        """Host evaluator whose `materializec` launches the generic map kernel with the producer's register program."""
+        if self._map_eval is None:
+            from .evaluator import DeviceMem, Evaluator
+
+            def materialize(assign, length, env_values, fn_sym):
+                program = self._map_programs[id(assign)]
+                env = [(v.ptr, v.nbytes) if isinstance(v, DeviceMem) else v for v in env_values if v is not None]
+                raw = program.launch(length, env)
+                if raw.data:
+                    self._map_outputs[int(raw.data)] = raw
+                return DeviceMem(raw.data, raw.len, {8: np.uint64, 4: np.float32}[program.elem_bytes])
+
+            self._map_eval = Evaluator(modules, materialize)
+        return self._map_eval
+
     def _exec_on_host(self, name, host, args, outs):
-        """A scalar module: evaluated on the host.  A failed `assert` is the Device error the kernels report as
-        CATENA_E_ASSERT (the generated code of the reference would have trapped)."""
-        from . import E_ASSERT
-        from .evaluator import AssertFailed
-        values = [np.float32(a.v) if a.kind is K.F32 else int(a.v) for a in args]
+        """A module evaluated on the host — scalar code, possibly around launches of the generic map kernel.  A failed
+        `assert` is the Device error the kernels report as CATENA_E_ASSERT (the generated code of the reference would
+        have trapped).  `Mem` arguments are consumed, as in `exec`; a `Mem` result owns the buffer it was materialised
+        into (or takes over the argument it aliases)."""
+        from . import CatenaMem, E_ASSERT, CatenaError, free
+        from .evaluator import AssertFailed, DeviceMem
+        values = []
+        for a in args:
+            if a.kind is K.Mem:
+                values.append(DeviceMem(a.v.raw.data, a.v.raw.len))
+            else:
+                values.append(np.float32(a.v) if a.kind is K.F32 else int(a.v))
+        self._map_outputs = {}
+        taken = set()
         try:
-            got = host(values)
-        except AssertFailed as exc:
-            raise ExecError("Device", f"program '{name}' failed: {exc}", E_ASSERT) from exc
-        if len(got) != len(outs):
-            raise ExecError("OutputArityMismatch", f"Function '{name}' expected {len(outs)} outputs, got {len(got)}")
-        return [Value.f32(v) if kind is K.F32 else Value(kind, int(v)) for kind, v in zip(outs, got)]
+            try:
+                got = host(values)
+            except AssertFailed as exc:
+                raise ExecError("Device", f"program '{name}' failed: {exc}", E_ASSERT) from exc
+            except CatenaError as exc:
+                raise ExecError("Device", f"program '{name}' failed: {exc}", exc.status) from exc
+            if len(got) != len(outs):
+                raise ExecError("OutputArityMismatch", f"Function '{name}' expected {len(outs)} outputs, got {len(got)}")
+            arguments = {int(a.v.raw.data): a.v for a in args if a.kind is K.Mem and a.v.raw.data}
+            results = []
+            for kind, v in zip(outs, got):
+                if kind is not K.Mem:
+                    results.append(Value.f32(v) if kind is K.F32 else Value(kind, int(v)))
+                elif not v.ptr or v.nbytes == 0:
+                    results.append(Value.mem(Mem()))
+                elif v.ptr in taken or (v.ptr not in self._map_outputs and v.ptr not in arguments):
+                    raise ExecError("Device", f"program '{name}' returned a buffer it does not own")
+                else:
+                    taken.add(v.ptr)
+                    if v.ptr in arguments and v.ptr not in self._map_outputs:
+                        arguments[v.ptr].raw = CatenaMem()          # an argument handed back: the result takes it over
+                    results.append(Value.mem(Mem(CatenaMem(v.ptr, v.nbytes))))
+            return results
+        finally:
+            for ptr, raw in self._map_outputs.items():
+                if ptr not in taken:
+                    free(raw)
+            self._map_outputs = {}
+            for a in args:
+                if a.kind is K.Mem:
+                    a.v.free()

@@ -188,6 +188,52 @@ typedef struct { catena_dim3_t grid_dim, block_dim; } catena_launch_params_t;
 uint64_t catena_b200_launch_len(catena_launch_params_t params);
 catena_status_t catena_b200_gpu_materialize_f32_s(const char* op, catena_launch_params_t params, catena_mem_t in, catena_mem_t* out);
 
+/* ---- generic map: `materializec` with a producer that no prebuilt kernel matches -------------------------------------
+ * The reference renders and compiles one kernel per `materializec` — out[i] = producer(env..., i), one thread per element
+ * (catena-lang/src/codegen/ops/materializec.rs:36-82).  This backend compiles nothing at run time: the lowering backend
+ * (catena-lang_b200/map_program.py, include/catena_b200_map_program.hpp) turns the producer's scalar assignments into a
+ * register program — calls inlined, one instruction per primitive of catena-lang/src/codegen/gpu.rs:322-447, `bool.ifc` as
+ * a conditional jump, a `reducec` inside the producer as a loop — and one prebuilt kernel interprets it for every index.
+ *
+ * Registers hold 64 bits: bool 0 / 1, u32 zero-extended, f32 as its bit pattern in the low half (the bitcasts are MOV).
+ * Registers 0 .. n_init-1 are preset from `init` (environment scalars, constants, buffer lengths) and read-only;
+ * `index_reg` receives i; the element written is the low `elem_bytes` (4 or 8) of `result_reg` after HALT.  LOAD reads
+ * buffers[b][register a], bounds-checked.  The program is validated before the launch (opcodes, register and buffer
+ * numbers, jump targets, HALT last); a program cannot fault or hang the GPU.  Where the reference's generated code would
+ * trap or be undefined — a failed assert, an index past its buffer, a u32 shift by 32 or more, round-to-u32 outside
+ * [0, 2^32), division by zero columns, more than 2^22 loop iterations for one element — that element is 0 and the call returns
+ * CATENA_E_ASSERT (in non-blocking mode: the next catena_b200_check_device_errors does).  len == 0: {NULL, 0}, no launch. */
+enum catena_b200_map_op {
+    CATENA_MAP_HALT = 0,
+    CATENA_MAP_MOV,             /* dst = a */
+    CATENA_MAP_JMP,             /* pc = target */
+    CATENA_MAP_JZ,              /* if (a == 0) pc = target */
+    CATENA_MAP_ASSERT,          /* `assert`: a != 0, else CATENA_E_ASSERT */
+    CATENA_MAP_SELECT,          /* dst = a ? b : c   (bool / u32 / u64 / f32 .select) */
+    CATENA_MAP_BOOL_NOT, CATENA_MAP_BOOL_AND, CATENA_MAP_BOOL_OR,
+    CATENA_MAP_U64_ADD, CATENA_MAP_U64_SUB, CATENA_MAP_U64_MUL,
+    CATENA_MAP_U64_DIV, CATENA_MAP_U64_REM,     /* row-major-row / row-major-col (catena-lang/src/codegen/ops/row_major.rs:30-68) */
+    CATENA_MAP_U64_EQ, CATENA_MAP_U64_NE, CATENA_MAP_U64_LT, CATENA_MAP_U64_LTE, CATENA_MAP_U64_GT, CATENA_MAP_U64_GTE,
+    CATENA_MAP_U64_TO_F32,
+    CATENA_MAP_U32_ADD, CATENA_MAP_U32_SUB, CATENA_MAP_U32_MUL, CATENA_MAP_U32_AND, CATENA_MAP_U32_OR, CATENA_MAP_U32_XOR,
+    CATENA_MAP_U32_NOT, CATENA_MAP_U32_SHL, CATENA_MAP_U32_SHR,
+    CATENA_MAP_U32_EQ, CATENA_MAP_U32_NE, CATENA_MAP_U32_LT, CATENA_MAP_U32_LTE, CATENA_MAP_U32_GT, CATENA_MAP_U32_GTE,
+    CATENA_MAP_U32_TO_F32,
+    CATENA_MAP_F32_ADD, CATENA_MAP_F32_SUB, CATENA_MAP_F32_MUL, CATENA_MAP_F32_DIV, CATENA_MAP_F32_NEG,
+    CATENA_MAP_F32_FMA,         /* dst = fmaf(a, b, c) */
+    CATENA_MAP_F32_EQ, CATENA_MAP_F32_NE, CATENA_MAP_F32_LT, CATENA_MAP_F32_LTE, CATENA_MAP_F32_GT, CATENA_MAP_F32_GTE,
+    CATENA_MAP_F32_ROUND_TO_U32,
+    CATENA_MAP_LOAD_U64, CATENA_MAP_LOAD_F32,   /* `ix`: dst = buffers[b][register a]; b is a buffer number */
+    CATENA_MAP_OP_COUNT
+};
+typedef struct {
+    uint16_t op, dst, a, b, c, reserved;
+    uint32_t target;            /* JMP / JZ: index of the next instruction */
+} catena_b200_map_insn_t;
+catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, uint32_t n_init,
+                                          uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, const catena_mem_t* buffers,
+                                          uint32_t n_buffers, uint32_t elem_bytes, uint64_t len, catena_mem_t* out);
+
 /* ---- programs with no counterpart in the reference (it has no bf16, int8 or attention);
  *      same calling convention; semantics composed from the reference's rules -------------- */
 /* C[M,N] = A[M,K] * B, A row-major bf16, B column-major bf16 (stored [N,K]); fp32 accumulation in
@@ -351,7 +397,7 @@ catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]);
  * such a launch is undefined; the library stays usable.  No counterpart in the reference. */
 void catena_b200_debug_set_wait_limit_ns(uint64_t ns);
 void catena_b200_debug_stall_next(int family, uint32_t value);
-/* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry */
+/* after non-blocking launches: reports (and clears) a device-side bounded-wait expiry or what a map program ran into */
 catena_status_t catena_b200_check_device_errors(void);
 
 #ifdef __cplusplus

@@ -193,3 +193,107 @@ def progression_programs():
 
 def all_host_modules():
     return bool_programs() + arithmetic_programs() + bit_programs() + conditional_programs() + progression_programs()
+
+
+# ---------------------------------------------------------------- examples/materializec.hex, tests/cases/materialize/basic.hex
+def materialize_programs():
+    u = lambda n: v(n, "u64")                                                # noqa: E731
+    e = lambda n: v(n, "erased")                                             # noqa: E731
+    p = lambda n: v(n, "ptr<u64>")                                           # noqa: E731
+    # materialize-index-producer: ([env i.] u64.one) — unit environment, the index is not used
+    one_producer = M("materialize-index-producer", [e("env"), u("i")], [u("r")], [A("u64.one", [], [u("r")])])
+    indexes = M("materialize-indexes", [u("len")], [v("out", "mem")], [
+        A("unit.intro", [], [e("unit")]), A(":.param", [u("len")], [e("n")]),
+        A("materializec", [u("len"), e("unit"), fn("materialize-index-producer")], [p("buf")], [1, 1, 1], [1]),
+        A("buf.to-mem", [u("len"), p("buf")], [v("out", "mem")])])
+    # materialize-copy-u64-producer: ([input i.] {[.i input]} ix)
+    copy_producer = M("materialize-copy-u64-producer", [p("input"), u("i")], [u("r")], [A("ix", [u("i"), p("input")], [u("r")])])
+    copy = M("materialize-copy-u64", [v("m", "mem")], [v("out", "mem")], [
+        A("mem.cast.u64", [v("m", "mem")], [u("len"), p("input")]), A(":.param", [u("len")], [e("n")]),
+        A("materializec", [u("len"), p("input"), fn("materialize-copy-u64-producer")], [p("buf")], [1, 1, 1], [1]),
+        A("buf.to-mem", [u("len"), p("buf")], [v("out", "mem")])])
+    # cast-index: ([i.] [.i] ix.to-u64); source-level `materialize` closure-converts to materializec with a unit environment
+    cast_index = M("cast-index", [u("i")], [u("r")], [A("ix.to-u64", [u("i")], [u("r")])])
+    indexes_source = M("materialize-indexes-source", [u("len")], [v("out", "mem")], [
+        A(":.param", [u("len")], [e("n")]),
+        A("materializec", [u("len"), fn("cast-index")], [p("buf")], [1, 0, 1], [1]),
+        A("buf.to-mem", [u("len"), p("buf")], [v("out", "mem")])])
+    return [one_producer, indexes, copy_producer, copy, cast_index, indexes_source]
+
+
+# ---------------------------------------------------------------- stdlib/math.hex:148-199, stdlib/nn.hex:2-22 (scalar programs)
+def silu_programs():
+    f = lambda n: v(n, "f32")                                                # noqa: E731
+    w = lambda n: v(n, "u32")                                                # noqa: E731
+
+    def const_f32(bits, name):
+        return [A(f"const.u32.0x{bits:08X}", [], [w(name + "_b")]), A("u32.bitcast-f32", [w(name + "_b")], [f(name)])]
+
+    nonneg = M("math.exp-approx-nonneg", [f("x")], [f("result")],
+               const_f32(0x3FB8AA3B, "inv_ln2") + const_f32(0x3F317200, "ln2_hi") + const_f32(0x35BFBE8E, "ln2_lo") +
+               const_f32(0x3F7FF8FC, "c0") + const_f32(0x3F809C7E, "c1") + const_f32(0x3EEF1187, "c2") + const_f32(0x3E738A8B, "c3") + [
+        A("f32.mul", [f("x"), f("inv_ln2")], [f("scaled")]), A("f32.round-to-u32", [f("scaled")], [w("k_u32")]),
+        A("u32.to-f32", [w("k_u32")], [f("k_f32")]),
+        A("f32.mul", [f("k_f32"), f("ln2_hi")], [f("k_ln2_hi")]), A("f32.mul", [f("k_f32"), f("ln2_lo")], [f("k_ln2_lo")]),
+        A("f32.sub", [f("x"), f("k_ln2_hi")], [f("r1")]), A("f32.sub", [f("r1"), f("k_ln2_lo")], [f("xr")]),
+        A("f32.mul", [f("xr"), f("c3")], [f("xr_c3")]), A("f32.add", [f("c2"), f("xr_c3")], [f("p2")]),
+        A("f32.mul", [f("xr"), f("p2")], [f("xr_p2")]), A("f32.add", [f("c1"), f("xr_p2")], [f("p1")]),
+        A("f32.mul", [f("xr"), f("p1")], [f("xr_p1")]), A("f32.add", [f("c0"), f("xr_p1")], [f("poly")]),
+        A("const.u32.0x0000007F", [], [w("bias_u32")]), A("const.u32.0x00800000", [], [w("exp_step_u32")]),
+        A("u32.add", [w("k_u32"), w("bias_u32")], [w("biased_exp")]), A("u32.mul", [w("biased_exp"), w("exp_step_u32")], [w("pow2_bits")]),
+        A("u32.bitcast-f32", [w("pow2_bits")], [f("pow2k")]), A("f32.mul", [f("poly"), f("pow2k")], [f("result")])])
+    exp = M("math.exp-approx", [f("x")], [f("result")], [
+        A("const.u32.0x00000000", [], [w("zero_b")]), A("u32.to-f32", [w("zero_b")], [f("zero")])] + const_f32(0x3F800000, "one") + [
+        A("f32.neg", [f("x")], [f("neg_x")]), A("f32.lt", [f("x"), f("zero")], [v("is_negative", "bool")]),
+        A("f32.select", [v("is_negative", "bool"), f("neg_x"), f("x")], [f("magnitude")]),
+        A("math.exp-approx-nonneg", [f("magnitude")], [f("base")], call=nonneg.name),
+        A("f32.div", [f("one"), f("base")], [f("reciprocal")]),
+        A("f32.select", [v("is_negative", "bool"), f("reciprocal"), f("base")], [f("result")])])
+    sigmoid = M("nn.sigmoid", [f("x")], [f("result")], [
+        A("f32.one", [], [f("one")]), A("f32.neg", [f("x")], [f("neg_x")]),
+        A("math.exp-approx", [f("neg_x")], [f("exp_neg_x")], call=exp.name),
+        A("f32.add", [f("one"), f("exp_neg_x")], [f("denominator")]), A("f32.div", [f("one"), f("denominator")], [f("result")])])
+    silu = M("nn.silu", [f("x")], [f("result")], [
+        A("nn.sigmoid", [f("x")], [f("gate")], call=sigmoid.name), A("f32.mul", [f("x"), f("gate")], [f("result")])])
+    return [nonneg, exp, sigmoid, silu]
+
+
+# ---------------------------------------------------------------- user programs in the reference's idiom (no file there): a map
+# over a buffer through a stdlib activation, a producer with a conditional, a producer with a fold inside
+def custom_map_programs():
+    f = lambda n: v(n, "f32")                                                # noqa: E731
+    u = lambda n: v(n, "u64")                                                # noqa: E731
+    e = lambda n: v(n, "erased")                                             # noqa: E731
+    pf = lambda n: v(n, "ptr<f32>")                                          # noqa: E731
+    silu = silu_programs()
+    silu_at = M("my.silu-at", [pf("x"), u("i")], [f("r")], [
+        A("ix", [u("i"), pf("x")], [f("xi")]), A("nn.silu", [f("xi")], [f("r")], call=symbol_for("nn.silu"))])
+    silu_map = M("my.silu-map", [v("m", "mem")], [v("out", "mem")], [
+        A("mem.cast.f32", [v("m", "mem")], [u("len"), pf("x")]),
+        A("materializec", [u("len"), pf("x"), fn("my.silu-at")], [pf("buf")], [1, 1, 1], [1]),
+        A("buf.to-mem", [u("len"), pf("buf")], [v("out", "mem")])])
+    # out[i] = x[i] >= floor ? x[i] : floor, through bool.ifc over two closures that return their capture (conditionals.hex)
+    keep = closure("program_closure_my_clamp_0", [f("x")], [f("x")])
+    low = closure("program_closure_my_clamp_1", [f("x")], [f("x")])
+    clamp_at = M("my.clamp-at", [pf("x"), f("floor"), u("i")], [f("r")], [
+        A("ix", [u("i"), pf("x")], [f("xi")]), A("f32.gte", [f("xi"), f("floor")], [v("keep", "bool")]), A("unit.intro", [], [e("unit")]),
+        A("bool.ifc", [f("xi"), fn("closure.my-clamp.0"), f("floor"), fn("closure.my-clamp.1"), v("keep", "bool"), e("unit")], [f("r")],
+          [1, 1, 1, 1, 1, 1], [1])])
+    clamp_map = M("my.clamp-map", [v("m", "mem"), f("floor")], [v("out", "mem")], [
+        A("mem.cast.f32", [v("m", "mem")], [u("len"), pf("x")]),
+        A("materializec", [u("len"), pf("x"), f("floor"), fn("my.clamp-at")], [pf("buf")], [1, 2, 1], [1]),
+        A("buf.to-mem", [u("len"), pf("buf")], [v("out", "mem")])])
+    # out[row] = fold over k < cols of a[row * cols + k] * b[k], separately rounded, ascending k (the matmul cell rule for one vector)
+    add_env = M("f32.add-env", [f("acc"), f("value")], [f("r")], [A("f32.add", [f("acc"), f("value")], [f("r")])])
+    term_at = M("my.matvec-term-at", [pf("a"), pf("b"), u("cols"), u("row"), u("k")], [f("r")], [
+        A("row-major-index", [u("cols"), u("row"), u("k")], [u("flat")]), A("ix", [u("flat"), pf("a")], [f("av")]),
+        A("ix", [u("k"), pf("b")], [f("bv")]), A("f32.mul", [f("av"), f("bv")], [f("r")])])
+    cell_at = M("my.matvec-at", [pf("a"), pf("b"), u("cols"), u("row")], [f("r")], [
+        A("const.u32.0x00000000", [], [v("zb", "u32")]), A("u32.bitcast-f32", [v("zb", "u32")], [f("zero")]), A("unit.intro", [], [e("unit")]),
+        A("reducec", [f("zero"), e("unit"), fn("f32.add-env"), pf("a"), pf("b"), u("cols"), u("row"), fn("my.matvec-term-at"), u("cols")], [f("r")],
+          [1, 1, 1, 4, 1, 1], [1])])
+    matvec = M("my.matvec", [v("ma", "mem"), v("mb", "mem"), u("rows")], [v("out", "mem")], [
+        A("mem.cast.f32", [v("ma", "mem")], [u("alen"), pf("a")]), A("mem.cast.f32", [v("mb", "mem")], [u("cols"), pf("b")]),
+        A("materializec", [u("rows"), pf("a"), pf("b"), u("cols"), fn("my.matvec-at")], [pf("buf")], [1, 3, 1], [1]),
+        A("buf.to-mem", [u("rows"), pf("buf")], [v("out", "mem")])])
+    return silu + [silu_at, silu_map, keep, low, clamp_at, clamp_map, add_env, term_at, cell_at, matvec]

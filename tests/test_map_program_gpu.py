@@ -1,0 +1,148 @@
+"""The generic map kernel on the GPU: `materializec` with producers that no prebuilt kernel matches, run through
+`Runtime.from_modules(...).exec(...)` — the reference's own vectors, equality with the prebuilt bit-exact kernels and the
+oracle, the CPU interpreter of tests/map_vm.py at sizes that need many CTAs, and the refusals that keep a malformed or
+faulting program away from the device."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import catena_lang_b200 as cb
+from catena_lang_b200 import lowering as lo
+from catena_lang_b200.map_program import OP, Insn
+import lowered_fixtures as fx
+import map_vm
+import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    return cb.Runtime.from_modules(fx.materialize_programs() + fx.custom_map_programs())
+
+
+def test_reference_materialize_vectors(rt):
+    """catena-lang/tests/cases/materializec.rs:5-31, tests/cases/materialize.rs:5-31"""
+    [out] = rt.exec("materialize-indexes", [4])
+    assert out.v.to_u64_vec().tolist() == [1, 1, 1, 1]
+    [out] = rt.exec("materialize-copy-u64", [rt.mem_u64([3, 5, 8, 13])])
+    assert out.v.to_u64_vec().tolist() == [3, 5, 8, 13]
+    [out] = rt.exec("materialize-indexes-source", [4])
+    assert out.v.to_u64_vec().tolist() == [0, 1, 2, 3]
+    [out] = rt.exec("materialize-indexes-source", [0])
+    assert out.v.is_null() and out.v.to_u64_vec().tolist() == []
+
+
+@pytest.mark.parametrize("n", [1, 255, 257, 100_003, 1 << 21])
+def test_interpreted_silu_equals_the_prebuilt_kernel(rt, n):
+    """nn.silu built from its primitives and interpreted = the prebuilt map kernel = the oracle, bit for bit."""
+    rng = np.random.default_rng(n)
+    x = rng.normal(0, 4, n).astype(np.float32)
+    x[: min(n, 6)] = np.array([0.0, -0.0, 88.0, -87.0, 1e-30, -1e-30], np.float32)[: min(n, 6)]
+    [out] = rt.exec("my.silu-map", [rt.mem_f32(x)])
+    got = out.v.to_f32_vec().view(np.uint32)
+    m = cb.upload(x)
+    o = cb.CatenaMem()
+    cb.check(cb.lib().catena_b200_map_f32_s(b"nn.silu", m, C.byref(o)))
+    prebuilt = cb.download(o, np.float32).view(np.uint32)
+    cb.free(m)
+    cb.free(o)
+    assert np.array_equal(got, prebuilt)
+    if n <= 100_003:
+        assert np.array_equal(got, orc.map_unary("nn.silu", x).view(np.uint32))
+
+
+def test_conditional_and_fold_inside_a_producer(rt):
+    x = np.random.default_rng(5).normal(0, 1, 10_000).astype(np.float32)
+    [out] = rt.exec("my.clamp-map", [rt.mem_f32(x), np.float32(0.25)])
+    assert np.array_equal(out.v.to_f32_vec(), np.maximum(x, np.float32(0.25)))
+    rows, cols = 300, 257
+    rng = np.random.default_rng(6)
+    a = rng.uniform(-1, 1, rows * cols).astype(np.float32)
+    b = rng.uniform(-1, 1, cols).astype(np.float32)
+    [out] = rt.exec("my.matvec", [rt.mem_f32(a), rt.mem_f32(b), rows])
+    want = np.asarray(orc.matmul_f32(a, b, rows, 1, cols)).reshape(-1)
+    assert np.array_equal(out.v.to_f32_vec().view(np.uint32), want.view(np.uint32))
+
+
+def test_kernel_equals_the_cpu_interpreter_on_integer_programs():
+    """u64 / u32 arithmetic with wraparound, shifts, compares and selects over the index: one program, every opcode family."""
+    u, w, b = (lambda n: fx.v(n, "u64")), (lambda n: fx.v(n, "u32")), (lambda n: fx.v(n, "bool"))
+    producer = fx.M("my.hash-at", [u("seed"), u("i")], [u("r")], [
+        fx.A("const.u64.0x9E3779B97F4A7C15", [], [u("g")]), fx.A("u64.mul", [u("i"), u("g")], [u("h0")]),
+        fx.A("u64.add", [u("h0"), u("seed")], [u("h1")]), fx.A("u64.sub", [u("h1"), u("i")], [u("h2")]),
+        fx.A("const.u64.0x00000000FFFFFFFF", [], [u("mask")]), fx.A("u64.lt", [u("h2"), u("mask")], [b("small")]),
+        fx.A("u64.select", [b("small"), u("h1"), u("h2")], [u("h3")]),
+        fx.A("const.u32.0x0000000D", [], [w("s13")]), fx.A("const.u32.0x85EBCA6B", [], [w("m1")]),
+        fx.A("const.u32.0x00000011", [], [w("s17")]),
+        # the low word through u32 operations: a bitcast round trip narrows nothing, so take it by comparing and selecting
+        fx.A("u64.to-f32", [u("h3")], [fx.v("hf", "f32")]), fx.A("f32.bitcast-u32", [fx.v("hf", "f32")], [w("x0")]),
+        fx.A("u32.shl", [w("x0"), w("s13")], [w("x1")]), fx.A("u32.xor", [w("x0"), w("x1")], [w("x2")]),
+        fx.A("u32.mul", [w("x2"), w("m1")], [w("x3")]), fx.A("u32.shr", [w("x3"), w("s17")], [w("x4")]),
+        fx.A("u32.not", [w("x4")], [w("x5")]), fx.A("u32.or", [w("x5"), w("x1")], [w("x6")]), fx.A("u32.and", [w("x6"), w("x3")], [w("x7")]),
+        fx.A("u32.sub", [w("x7"), w("x2")], [w("x8")]), fx.A("u32.add", [w("x8"), w("s13")], [w("x9")]),
+        fx.A("u32.gte", [w("x9"), w("m1")], [b("big")]), fx.A("bool.not", [b("big")], [b("nb")]), fx.A("bool.or", [b("nb"), b("small")], [b("c")]),
+        fx.A("u32.to-f32", [w("x9")], [fx.v("xf", "f32")]), fx.A("f32.bitcast-u32", [fx.v("xf", "f32")], [w("y")]),
+        fx.A("u32.select", [b("c"), w("y"), w("x9")], [w("z")]),
+        fx.A("u32.bitcast-f32", [w("z")], [fx.v("zf", "f32")]), fx.A("f32.bitcast-u32", [fx.v("zf", "f32")], [w("z2")]),
+        fx.A("u32.eq", [w("z"), w("z2")], [b("same")]), fx.A("assert", [b("same")], [fx.v("h", "erased")]),
+        fx.A("u64.add", [u("h3"), u("h0")], [u("r")])])
+    entry = fx.M("my.hash", [u("n"), u("seed")], [fx.v("out", "mem")], [
+        fx.A("materializec", [u("n"), u("seed"), fx.fn("my.hash-at")], [fx.v("buf", "ptr<u64>")], [1, 1, 1], [1]),
+        fx.A("buf.to-mem", [u("n"), fx.v("buf", "ptr<u64>")], [fx.v("out", "mem")])])
+    mods = [producer, entry]
+    rt = cb.Runtime.from_modules(mods)
+    n, seed = 5000, 0xFFFFFFFFFFFFFF00
+    [out] = rt.exec("my.hash", [n, seed])
+    mm = lo.module_map(mods)
+    prog = lo.map_program_for(entry.entry.assignments[0], mm)
+    assert np.array_equal(out.v.to_u64_vec(), map_vm.run(prog, [seed], n, []))
+
+
+def test_faults_of_a_program_come_back_as_statuses(rt):
+    """An index past its buffer (the reference would read out of bounds) and a failed assert: CATENA_E_ASSERT, nothing faults,
+    and the library works afterwards."""
+    mods = fx.materialize_programs()
+    mm = lo.module_map(mods)
+    prog = lo.map_program_for([a for a in mm["materialize-copy-u64"].entry.assignments if a.op == "materializec"][0], mm)
+    data = cb.upload(np.array([3, 5], np.uint64))
+    with pytest.raises(cb.CatenaError) as err:
+        prog.launch(3, [(data.data, data.len)])
+    assert err.value.status == cb.E_ASSERT
+    out = prog.launch(2, [(data.data, data.len)])
+    assert cb.download(out, np.uint64).tolist() == [3, 5]
+    cb.free(out)
+    cb.free(data)
+    [ok] = rt.exec("materialize-indexes", [3])
+    assert ok.v.to_u64_vec().tolist() == [1, 1, 1]
+
+
+def test_malformed_programs_are_refused_before_the_launch():
+    L = cb.lib()
+
+    def call(code, n_init=0, n_regs=4, index_reg=0, result_reg=0, n_buffers=0, elem=8, length=4):
+        arr = (Insn * len(code))(*code)
+        init = (C.c_uint64 * 4)()
+        bufs = (cb.CatenaMem * 1)()
+        out = cb.CatenaMem()
+        s = L.catena_b200_map_program_s(arr, len(code), init, n_init, n_regs, index_reg, result_reg, bufs, n_buffers, elem, length, C.byref(out))
+        if s == cb.OK:
+            cb.free(out)
+        return s
+
+    halt = Insn(OP["HALT"], 0, 0, 0, 0, 0, 0)
+    assert call([halt]) == cb.OK
+    assert call([Insn(OP["MOV"], 1, 0, 0, 0, 0, 0)]) == cb.E_BAD_ARG                       # no HALT at the end
+    assert call([Insn(OP["MOV"], 9, 0, 0, 0, 0, 0), halt]) == cb.E_BAD_ARG                 # register past the file
+    assert call([Insn(OP["MOV"], 1, 9, 0, 0, 0, 0), halt]) == cb.E_BAD_ARG
+    assert call([Insn(OP["JMP"], 0, 0, 0, 0, 0, 7), halt]) == cb.E_BAD_ARG                 # jump target past the program
+    assert call([Insn(len(OP), 1, 0, 0, 0, 0, 0), halt]) == cb.E_BAD_ARG                   # unknown opcode
+    assert call([Insn(OP["LOAD_U64"], 1, 0, 0, 0, 0, 0), halt]) == cb.E_BAD_ARG            # buffer 0 of none
+    assert call([Insn(OP["MOV"], 0, 1, 0, 0, 0, 0), halt]) == cb.E_BAD_ARG                 # writes the index register
+    assert call([Insn(OP["MOV"], 0, 1, 0, 0, 0, 0), halt], n_init=1, index_reg=1) == cb.E_BAD_ARG   # writes a preset register
+    assert call([halt], elem=2) == cb.E_BAD_ARG
+    assert call([halt], n_regs=300) == cb.E_BAD_ARG
+    # an endless loop ends at the budget of backward jumps and is reported; the library stays usable
+    assert call([Insn(OP["JMP"], 0, 0, 0, 0, 0, 0), halt], length=1) == cb.E_ASSERT
+    assert call([halt]) == cb.OK
