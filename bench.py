@@ -428,8 +428,8 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
     bit-exact f32 matmul (mul and add are separate instructions by contract: one flop per lane per clock)."""
     out = {}
     fp32_unfused_peak = 148 * 128 * sm_max_mhz * 1e6 / 1e12
-    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("softmax", False), ("rmsnorm", False),
-                         ("sum_u64", False), ("dot_u64", False)):
+    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("map_program", False), ("softmax", False),
+                         ("rmsnorm", False), ("sum_u64", False), ("dot_u64", False)):
         step, work, unit, desc = single_case(cb, L, torch, dev, which, small, None)
         steps = 200 if (which == "matmul_f32" and small) else (8 if which == "matmul_f32" else 20)
         torch.cuda.synchronize(dev)
@@ -454,7 +454,11 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
         else:
             roof = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": value / peaks["hbm_gbs"],
                     "peak_source": f"{peaks['source']} copy bandwidth"}
-        name = {"matmul_f32": "matmul_f32_256" if small else "matmul_f32_4096", "map": "map_nn_silu_64Mi"}.get(which, which + "_64Mi")
+        name = {"matmul_f32": "matmul_f32_256" if small else "matmul_f32_4096", "map": "map_nn_silu_64Mi",
+                "map_program": "map_program_nn_silu_64Mi"}.get(which, which + "_64Mi")
+        if which == "map_program":
+            roof["note"] = ("the generic path for producers without a prebuilt kernel: bound by the interpreter's instruction issue, "
+                            "not by HBM; the same function as map_nn_silu_64Mi, bit for bit")
         if which in ("sum_u64", "dot_u64"):
             roof["note"] = "each step is a whole program call: two kernels, an 8-byte copy back and a stream synchronisation"
         out[name] = {"case": desc, "us_per_launch": ms * 1e3, "value": value, "unit": unit, "steps": steps, "roofline": roof}
@@ -859,9 +863,26 @@ def single_case(cb, L, torch, dev, which, small, shape, units=0):
         x = torch.randn((2, n), generator=g, device=dev)
         y = torch.empty((2, n), device=dev)
 
+        program = None
+        if which == "map_program":
+            # nn.silu again, but as a user's `materializec` producer would arrive: lowered modules of the stdlib programs
+            # (exp~ from its primitives), compiled to a register program and interpreted by the generic map kernel
+            from catena_lang_b200 import lowering as lo
+            from catena_lang_b200.lowered_stdlib import silu_modules
+            mods = silu_modules()
+            at = lo.GpuModule("program_bench_silu_at", "bench.silu-at", lo.GpuFunction("program_bench_silu_at",
+                [lo.GpuVar("x", "ptr<f32>"), lo.GpuVar("i", "u64")], [lo.GpuVar("r", "f32")],
+                [lo.GpuAssign("ix", [lo.GpuVar("i", "u64"), lo.GpuVar("x", "ptr<f32>")], [lo.GpuVar("xi", "f32")]),
+                 lo.GpuAssign("nn.silu", [lo.GpuVar("xi", "f32")], [lo.GpuVar("r", "f32")], cb.symbol_for("nn.silu"))]))
+            launch = lo.GpuAssign("materializec", [lo.GpuVar("len", "u64"), lo.GpuVar("x", "ptr<f32>"), lo.FnSymbol("bench.silu-at")],
+                                  [lo.GpuVar("buf", "ptr<f32>")], None, [1, 1, 1], [1])
+            program = lo.map_program_for(launch, lo.module_map(mods + [at]))
+
         def step(i):
             s = i % 2
-            if which == "softmax":
+            if program is not None:
+                cb.free(program.launch(n, [(x[s].data_ptr(), n * 4)]))       # the program allocates its output, as materializec does
+            elif which == "softmax":
                 cb.check(L.catena_b200_softmax_f32_into(x[s].data_ptr(), y[s].data_ptr(), n))
             elif which == "rmsnorm":
                 cb.check(L.catena_b200_rmsnorm_f32_into(x[s].data_ptr(), y[s].data_ptr(), n))
@@ -870,6 +891,8 @@ def single_case(cb, L, torch, dev, which, small, shape, units=0):
         passes = {"softmax": 4, "rmsnorm": 3}.get(which, 2)     # algorithmic reads + writes of the buffer
         work, unit = passes * n * 4 / 1e9, "GB/s"
         desc = f"{which} over {n} f32"
+        if program is not None:
+            desc = f"nn.silu as an interpreted register program ({len(program.code)} instructions, {program.n_regs} registers) over {n} f32"
     return step, work, unit, desc
 
 
@@ -915,7 +938,7 @@ def run_single(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None,
-                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "softmax", "rmsnorm", "sum_u64", "dot_u64", "llama"])
+                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "map_program", "softmax", "rmsnorm", "sum_u64", "dot_u64", "llama"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
     ap.add_argument("--units", type=int, default=0, help="--only attn: launch only the first N (batch, kv-head) units")

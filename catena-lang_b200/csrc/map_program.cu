@@ -8,8 +8,8 @@
 // for every index.  All threads run the same instruction stream (it lives in shared memory), so the interpreter's
 // dispatch does not diverge; only `bool.ifc` branches and `reducec` loops of the program itself can.
 //
-// Values are 64-bit registers: bool as 0 / 1, u32 zero-extended, f32 as its bit pattern in the low half, u64 as is, so the
-// bitcasts are moves.  f32 arithmetic goes through the explicitly rounded operations of catena_math.cuh (never contracted),
+// Values are 64-bit registers: bool as 0 / 1, u32 and the bit pattern of an f32 in the low half, u64 as is, so the bitcasts are
+// moves.  f32 arithmetic goes through the explicitly rounded operations of catena_math.cuh (never contracted),
 // `f32.fma` is one fused operation, `f32.round-to-u32` rounds to nearest even, `u64.to-f32` / `u32.to-f32` round once.
 //
 // Nothing a program does can fault or hang the GPU: the host checks every register number, buffer number and jump target
@@ -17,6 +17,8 @@
 // Where the reference's generated C would trap (`catena_assert`), read past a buffer or be undefined (a u32 shift by 32 or
 // more, `f32.round-to-u32` outside [0, 2^32), a row-major division by zero columns) the element yields 0, the launch carries on
 // and the entry point reports CATENA_E_ASSERT.
+#include <string.h>
+
 #include "catena_math.cuh"
 #include "common.cuh"
 
@@ -39,115 +41,191 @@ struct Buffers {
 __device__ __forceinline__ float as_f32(uint64_t r) { return __uint_as_float((uint32_t)r); }
 __device__ __forceinline__ uint64_t from_f32(float f) { return (uint64_t)__float_as_uint(f); }
 
-template <int REGS>
-__global__ void __launch_bounds__(256) map_program_kernel(const uint4* __restrict__ code, uint32_t n_insn, const uint64_t* __restrict__ init,
-                                                          uint32_t n_init, uint32_t index_reg, uint32_t result_reg, const Buffers bufs,
+// Small programs travel as kernel parameters (no copy, no scratch, and the constant cache broadcasts an instruction to the
+// warp); larger ones are copied to the device and staged in shared memory.
+constexpr uint32_t kParamInsns = 192, kParamInit = 48;
+struct ParamProgram {
+    uint4 code[kParamInsns];
+    uint64_t init[kParamInit];
+};
+
+// REGS: capacity of the register file (local memory).  V: elements a thread carries through the program in lockstep — one
+// fetch, decode and dispatch per V elements; V > 1 only for programs without jumps (the host decides).  PARAM: the program
+// sits in the kernel parameters instead of shared memory.
+template <int REGS, int V, bool PARAM>
+__global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant__ ParamProgram prm, const uint4* __restrict__ code,
+                                                          uint32_t n_insn, const uint64_t* __restrict__ init, uint32_t n_init, uint32_t n_regs,
+                                                          uint32_t index_reg, uint32_t result_reg, const __grid_constant__ Buffers bufs,
                                                           void* __restrict__ out, uint32_t elem_bytes, uint64_t len, uint32_t* err) {
     extern __shared__ uint4 s_code[];
-    for (uint32_t k = threadIdx.x; k < n_insn; k += blockDim.x) s_code[k] = code[k];
-    __syncthreads();
-    uint64_t r[REGS];
+    if (!PARAM) {
+        for (uint32_t k = threadIdx.x; k < n_insn; k += blockDim.x) s_code[k] = code[k];
+        __syncthreads();
+    }
+    // The register file, in local memory, as separate low and high halves: bool / u32 / f32 instructions touch the low halves
+    // only (a third of the traffic of whole registers — the file's bandwidth through L1 is what bounds an interpreted map).  The
+    // high half of a register that holds such a value is stale; nothing reads it: flags are tested on the low half, and the
+    // type system never feeds a 32-bit value to a u64 instruction (there is no u32 -> u64 conversion in the table).
+    uint32_t lo[REGS][V], hi[REGS][V];
 #pragma unroll 1
-    for (uint32_t k = 0; k < (uint32_t)REGS; ++k) r[k] = k < n_init ? init[k] : 0ull;
+    for (uint32_t k = 0; k < n_regs; ++k) {
+        const uint64_t x = k < n_init ? (PARAM ? prm.init[k] : init[k]) : 0ull;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            lo[k][v] = (uint32_t)x;
+            hi[k][v] = (uint32_t)(x >> 32);
+        }
+    }
     uint32_t fault = ERR_NONE;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride) {
-        r[index_reg] = i;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < len; i += stride * V) {
+        // element v of this trip is i + v * stride; past the end it repeats element i (valid), and is not stored
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const uint64_t e = i + v * stride < len ? i + v * stride : i;
+            lo[index_reg][v] = (uint32_t)e;
+            hi[index_reg][v] = (uint32_t)(e >> 32);
+        }
         uint32_t pc = 0, back = 0;
-        bool running = true;
-        while (running) {
-            const uint4 w = s_code[pc++];
+        bool gave_up = false;
+        while (true) {
+            const uint4 w = PARAM ? prm.code[pc] : s_code[pc];
+            ++pc;
             const uint32_t op = w.x & 0xFFFFu, dst = w.x >> 16, ra = w.y & 0xFFFFu, rb = w.y >> 16, rc = w.z & 0xFFFFu;
-            const uint64_t a = r[ra], b = r[rb];
-            uint64_t v = 0;
-            bool write = true;
-            switch (op) {
-            case CATENA_MAP_HALT: running = false; write = false; break;
-            case CATENA_MAP_MOV: v = a; break;
-            case CATENA_MAP_JMP:
-            case CATENA_MAP_JZ:
-                write = false;
-                if (op == CATENA_MAP_JMP || a == 0) {
+            if (op == CATENA_MAP_HALT) break;
+            if (op == CATENA_MAP_JMP || op == CATENA_MAP_JZ) {          // V == 1 here
+                if (op == CATENA_MAP_JMP || lo[ra][0] == 0) {
                     if (w.w < pc && ++back > kBackJumpBudget) {
                         fault = max(fault, (uint32_t)ERR_BUDGET);
-                        r[result_reg] = 0;
-                        running = false;
-                    } else {
-                        pc = w.w;
+                        gave_up = true;
+                        break;
                     }
+                    pc = w.w;
+                }
+                continue;
+            }
+            // one dispatch per instruction; inside a case the V elements are independent
+#define CATENA_R64(R, v) (((uint64_t)hi[R][v] << 32) | lo[R][v])
+#define CATENA_W64(v, X)                       \
+    do {                                       \
+        const uint64_t x_ = (X);               \
+        lo[dst][v] = (uint32_t)x_;             \
+        hi[dst][v] = (uint32_t)(x_ >> 32);     \
+    } while (0)
+#define CATENA_LANES _Pragma("unroll") for (int v = 0; v < V; ++v)
+// 32-bit operands and result
+#define CATENA_W(EXPR)      CATENA_LANES { const uint32_t a = lo[ra][v], b = lo[rb][v]; (void)b; lo[dst][v] = (uint32_t)(EXPR); } break
+#define CATENA_W1(EXPR)     CATENA_LANES { const uint32_t a = lo[ra][v]; lo[dst][v] = (uint32_t)(EXPR); } break
+// 64-bit operands, 64-bit result
+#define CATENA_D(EXPR)      CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; CATENA_W64(v, EXPR); } break
+// 64-bit operands, 32-bit result (compares, conversions)
+#define CATENA_DW(EXPR)     CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; lo[dst][v] = (uint32_t)(EXPR); } break
+#define CATENA_DW1(EXPR)    CATENA_LANES { const uint64_t a = CATENA_R64(ra, v); lo[dst][v] = (uint32_t)(EXPR); } break
+#define CATENA_F(EXPR)      CATENA_LANES { const float a = __uint_as_float(lo[ra][v]), b = __uint_as_float(lo[rb][v]); (void)b; lo[dst][v] = __float_as_uint(EXPR); } break
+#define CATENA_FC(EXPR)     CATENA_LANES { const float a = __uint_as_float(lo[ra][v]), b = __uint_as_float(lo[rb][v]); lo[dst][v] = (EXPR) ? 1u : 0u; } break
+#define CATENA_UNDEF        (fault = max(fault, (uint32_t)ERR_UNDEFINED), 0)
+            switch (op) {
+            case CATENA_MAP_ASSERT:
+                CATENA_LANES { if (lo[ra][v] == 0) fault = max(fault, (uint32_t)ERR_ASSERT); }
+                break;
+            case CATENA_MAP_MOV:
+                CATENA_LANES { lo[dst][v] = lo[ra][v]; hi[dst][v] = hi[ra][v]; }
+                break;
+            case CATENA_MAP_SELECT:
+                CATENA_LANES {
+                    const bool t = lo[ra][v] != 0;
+                    const uint32_t l = t ? lo[rb][v] : lo[rc][v], h = t ? hi[rb][v] : hi[rc][v];
+                    lo[dst][v] = l;
+                    hi[dst][v] = h;
                 }
                 break;
-            case CATENA_MAP_ASSERT: write = false; if (a == 0) fault = max(fault, (uint32_t)ERR_ASSERT); break;
-            case CATENA_MAP_SELECT: v = a ? b : r[rc]; break;
-            case CATENA_MAP_BOOL_NOT: v = a ? 0 : 1; break;
-            case CATENA_MAP_BOOL_AND: v = (a && b) ? 1 : 0; break;
-            case CATENA_MAP_BOOL_OR: v = (a || b) ? 1 : 0; break;
-            case CATENA_MAP_U64_ADD: v = a + b; break;
-            case CATENA_MAP_U64_SUB: v = a - b; break;
-            case CATENA_MAP_U64_MUL: v = a * b; break;
-            case CATENA_MAP_U64_DIV:
-            case CATENA_MAP_U64_REM:
-                if (b == 0) fault = max(fault, (uint32_t)ERR_UNDEFINED);
-                else v = op == CATENA_MAP_U64_DIV ? a / b : a % b;
+            case CATENA_MAP_BOOL_NOT: CATENA_W1(a ? 0u : 1u);
+            case CATENA_MAP_BOOL_AND: CATENA_W((a && b) ? 1u : 0u);
+            case CATENA_MAP_BOOL_OR: CATENA_W((a || b) ? 1u : 0u);
+            case CATENA_MAP_U64_ADD: CATENA_D(a + b);
+            case CATENA_MAP_U64_SUB: CATENA_D(a - b);
+            case CATENA_MAP_U64_MUL: CATENA_D(a * b);
+            case CATENA_MAP_U64_DIV: CATENA_D(b == 0 ? (uint64_t)CATENA_UNDEF : a / b);
+            case CATENA_MAP_U64_REM: CATENA_D(b == 0 ? (uint64_t)CATENA_UNDEF : a % b);
+            case CATENA_MAP_U64_EQ: CATENA_DW(a == b);
+            case CATENA_MAP_U64_NE: CATENA_DW(a != b);
+            case CATENA_MAP_U64_LT: CATENA_DW(a < b);
+            case CATENA_MAP_U64_LTE: CATENA_DW(a <= b);
+            case CATENA_MAP_U64_GT: CATENA_DW(a > b);
+            case CATENA_MAP_U64_GTE: CATENA_DW(a >= b);
+            case CATENA_MAP_U64_TO_F32: CATENA_DW1(__float_as_uint(cmath::u64_to_f32(a)));
+            case CATENA_MAP_U32_ADD: CATENA_W(a + b);
+            case CATENA_MAP_U32_SUB: CATENA_W(a - b);
+            case CATENA_MAP_U32_MUL: CATENA_W(a * b);
+            case CATENA_MAP_U32_AND: CATENA_W(a & b);
+            case CATENA_MAP_U32_OR: CATENA_W(a | b);
+            case CATENA_MAP_U32_XOR: CATENA_W(a ^ b);
+            case CATENA_MAP_U32_NOT: CATENA_W1(~a);
+            case CATENA_MAP_U32_SHL: CATENA_W(b >= 32u ? (uint32_t)CATENA_UNDEF : a << b);
+            case CATENA_MAP_U32_SHR: CATENA_W(b >= 32u ? (uint32_t)CATENA_UNDEF : a >> b);
+            case CATENA_MAP_U32_EQ: CATENA_W(a == b);
+            case CATENA_MAP_U32_NE: CATENA_W(a != b);
+            case CATENA_MAP_U32_LT: CATENA_W(a < b);
+            case CATENA_MAP_U32_LTE: CATENA_W(a <= b);
+            case CATENA_MAP_U32_GT: CATENA_W(a > b);
+            case CATENA_MAP_U32_GTE: CATENA_W(a >= b);
+            case CATENA_MAP_U32_TO_F32: CATENA_W1(__float_as_uint(cmath::u32_to_f32(a)));
+            case CATENA_MAP_F32_ADD: CATENA_F(cmath::add(a, b));
+            case CATENA_MAP_F32_SUB: CATENA_F(cmath::sub(a, b));
+            case CATENA_MAP_F32_MUL: CATENA_F(cmath::mul(a, b));
+            case CATENA_MAP_F32_DIV: CATENA_F(cmath::div(a, b));
+            case CATENA_MAP_F32_NEG: CATENA_W1(a ^ 0x80000000u);
+            case CATENA_MAP_F32_FMA:
+                CATENA_LANES { lo[dst][v] = __float_as_uint(__fmaf_rn(__uint_as_float(lo[ra][v]), __uint_as_float(lo[rb][v]), __uint_as_float(lo[rc][v]))); }
                 break;
-            case CATENA_MAP_U64_EQ: v = a == b; break;
-            case CATENA_MAP_U64_NE: v = a != b; break;
-            case CATENA_MAP_U64_LT: v = a < b; break;
-            case CATENA_MAP_U64_LTE: v = a <= b; break;
-            case CATENA_MAP_U64_GT: v = a > b; break;
-            case CATENA_MAP_U64_GTE: v = a >= b; break;
-            case CATENA_MAP_U64_TO_F32: v = from_f32(cmath::u64_to_f32(a)); break;
-            case CATENA_MAP_U32_ADD: v = (uint32_t)((uint32_t)a + (uint32_t)b); break;
-            case CATENA_MAP_U32_SUB: v = (uint32_t)((uint32_t)a - (uint32_t)b); break;
-            case CATENA_MAP_U32_MUL: v = (uint32_t)((uint32_t)a * (uint32_t)b); break;
-            case CATENA_MAP_U32_AND: v = (uint32_t)a & (uint32_t)b; break;
-            case CATENA_MAP_U32_OR: v = (uint32_t)a | (uint32_t)b; break;
-            case CATENA_MAP_U32_XOR: v = (uint32_t)a ^ (uint32_t)b; break;
-            case CATENA_MAP_U32_NOT: v = (uint32_t)~(uint32_t)a; break;
-            case CATENA_MAP_U32_SHL:
-            case CATENA_MAP_U32_SHR:
-                if ((uint32_t)b >= 32u) fault = max(fault, (uint32_t)ERR_UNDEFINED);
-                else v = op == CATENA_MAP_U32_SHL ? (uint32_t)((uint32_t)a << (uint32_t)b) : ((uint32_t)a >> (uint32_t)b);
-                break;
-            case CATENA_MAP_U32_EQ: v = (uint32_t)a == (uint32_t)b; break;
-            case CATENA_MAP_U32_NE: v = (uint32_t)a != (uint32_t)b; break;
-            case CATENA_MAP_U32_LT: v = (uint32_t)a < (uint32_t)b; break;
-            case CATENA_MAP_U32_LTE: v = (uint32_t)a <= (uint32_t)b; break;
-            case CATENA_MAP_U32_GT: v = (uint32_t)a > (uint32_t)b; break;
-            case CATENA_MAP_U32_GTE: v = (uint32_t)a >= (uint32_t)b; break;
-            case CATENA_MAP_U32_TO_F32: v = from_f32(cmath::u32_to_f32((uint32_t)a)); break;
-            case CATENA_MAP_F32_ADD: v = from_f32(cmath::add(as_f32(a), as_f32(b))); break;
-            case CATENA_MAP_F32_SUB: v = from_f32(cmath::sub(as_f32(a), as_f32(b))); break;
-            case CATENA_MAP_F32_MUL: v = from_f32(cmath::mul(as_f32(a), as_f32(b))); break;
-            case CATENA_MAP_F32_DIV: v = from_f32(cmath::div(as_f32(a), as_f32(b))); break;
-            case CATENA_MAP_F32_NEG: v = (uint32_t)a ^ 0x80000000u; break;
-            case CATENA_MAP_F32_FMA: v = from_f32(__fmaf_rn(as_f32(a), as_f32(b), as_f32(r[rc]))); break;
-            case CATENA_MAP_F32_EQ: v = as_f32(a) == as_f32(b); break;
-            case CATENA_MAP_F32_NE: v = as_f32(a) != as_f32(b); break;
-            case CATENA_MAP_F32_LT: v = as_f32(a) < as_f32(b); break;
-            case CATENA_MAP_F32_LTE: v = as_f32(a) <= as_f32(b); break;
-            case CATENA_MAP_F32_GT: v = as_f32(a) > as_f32(b); break;
-            case CATENA_MAP_F32_GTE: v = as_f32(a) >= as_f32(b); break;
-            case CATENA_MAP_F32_ROUND_TO_U32: {
-                const float x = as_f32(a);
-                if (!(x >= 0.0f && x < 4294967296.0f)) fault = max(fault, (uint32_t)ERR_UNDEFINED);
-                else v = cmath::round_to_u32(x);
-                break;
-            }
+            case CATENA_MAP_F32_EQ: CATENA_FC(a == b);
+            case CATENA_MAP_F32_NE: CATENA_FC(a != b);
+            case CATENA_MAP_F32_LT: CATENA_FC(a < b);
+            case CATENA_MAP_F32_LTE: CATENA_FC(a <= b);
+            case CATENA_MAP_F32_GT: CATENA_FC(a > b);
+            case CATENA_MAP_F32_GTE: CATENA_FC(a >= b);
+            case CATENA_MAP_F32_ROUND_TO_U32: CATENA_F(__uint_as_float(!(a >= 0.0f && a < 4294967296.0f) ? (uint32_t)CATENA_UNDEF : cmath::round_to_u32(a)));
+            // loads: buffer rb [register ra]; rb is a buffer number (checked by the host), not a register
             case CATENA_MAP_LOAD_U64:
-            case CATENA_MAP_LOAD_F32: {       // dst = buffer rb [a]; rb is a buffer number (checked by the host), not a register
-                const uint32_t shift = op == CATENA_MAP_LOAD_U64 ? 3u : 2u;
-                if (a >= (bufs.bytes[rb] >> shift)) fault = max(fault, (uint32_t)ERR_RANGE);
-                else if (shift == 3u) v = __ldg(reinterpret_cast<const uint64_t*>(bufs.base[rb]) + a);
-                else v = __ldg(reinterpret_cast<const uint32_t*>(bufs.base[rb]) + a);
+                CATENA_LANES {
+                    const uint64_t a = CATENA_R64(ra, v);
+                    uint64_t x = 0;
+                    if (a >= (bufs.bytes[rb] >> 3)) fault = max(fault, (uint32_t)ERR_RANGE);
+                    else x = __ldg(reinterpret_cast<const uint64_t*>(bufs.base[rb]) + a);
+                    CATENA_W64(v, x);
+                }
                 break;
+            case CATENA_MAP_LOAD_F32:
+                CATENA_LANES {
+                    const uint64_t a = CATENA_R64(ra, v);
+                    uint32_t x = 0;
+                    if (a >= (bufs.bytes[rb] >> 2)) fault = max(fault, (uint32_t)ERR_RANGE);
+                    else x = __ldg(reinterpret_cast<const uint32_t*>(bufs.base[rb]) + a);
+                    lo[dst][v] = x;
+                }
+                break;
+            default: break;      // unreachable: the host validated every opcode
             }
-            default: running = false; write = false; break;      // unreachable: the host validated every opcode
-            }
-            if (write) r[dst] = v;
+#undef CATENA_R64
+#undef CATENA_W64
+#undef CATENA_LANES
+#undef CATENA_W
+#undef CATENA_W1
+#undef CATENA_D
+#undef CATENA_DW
+#undef CATENA_DW1
+#undef CATENA_F
+#undef CATENA_FC
+#undef CATENA_UNDEF
         }
-        if (elem_bytes == 8) static_cast<uint64_t*>(out)[i] = r[result_reg];
-        else static_cast<uint32_t*>(out)[i] = (uint32_t)r[result_reg];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const uint64_t e = i + v * stride;
+            if (e < len) {
+                if (elem_bytes == 8) static_cast<uint64_t*>(out)[e] = gave_up ? 0ull : (((uint64_t)hi[result_reg][v] << 32) | lo[result_reg][v]);
+                else static_cast<uint32_t*>(out)[e] = gave_up ? 0u : lo[result_reg][v];
+            }
+        }
     }
     if (fault != ERR_NONE) atomicMax(err, fault);
 }
@@ -254,42 +332,65 @@ catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, ui
     if (len == 0) return CATENA_OK;                        // no allocation, no launch (materializec.rs:108-116)
     mapvm::State* st = nullptr;
     CATENA_TRY(mapvm::state(&st));
-    // instructions and preset registers travel in one scratch block
+    bool straight = true;                                  // no jumps: V elements per thread can run in lockstep
+    for (uint32_t k = 0; k < n_insn; ++k) straight = straight && code[k].op != CATENA_MAP_JMP && code[k].op != CATENA_MAP_JZ;
+    const bool by_param = n_insn <= mapvm::kParamInsns && n_init <= mapvm::kParamInit;
     const size_t code_bytes = (size_t)n_insn * sizeof(catena_b200_map_insn_t), init_bytes = (size_t)n_init * sizeof(uint64_t);
     void* scratch = nullptr;
     void* result = nullptr;
-    CATENA_TRY(pool_alloc(code_bytes + init_bytes + 16, &scratch));
     catena_status_t s = pool_alloc(len * elem_bytes, &result);
-    if (s != CATENA_OK) {
-        pool_free(scratch);
-        return s;
-    }
+    if (s != CATENA_OK) return s;
     cudaStream_t stream = tls().stream;
-    cudaError_t e = cudaMemcpyAsync(scratch, code, code_bytes, cudaMemcpyHostToDevice, stream);
-    if (e == cudaSuccess && init_bytes)
-        e = cudaMemcpyAsync(static_cast<uint8_t*>(scratch) + code_bytes, init, init_bytes, cudaMemcpyHostToDevice, stream);
-    // the host arrays are pageable and may change when this call returns: the copies must have read them
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    cudaError_t e = cudaSuccess;
+    static_assert(sizeof(catena_b200_map_insn_t) == sizeof(uint4), "instruction layout");
+    mapvm::ParamProgram prm;
+    memset(&prm, 0, sizeof(prm));
+    if (by_param) {
+        memcpy(prm.code, code, code_bytes);
+        if (init_bytes) memcpy(prm.init, init, init_bytes);
+    } else {
+        // instructions and preset registers travel in one scratch block
+        s = pool_alloc(code_bytes + init_bytes + 16, &scratch);
+        if (s != CATENA_OK) {
+            pool_free(result);
+            return s;
+        }
+        e = cudaMemcpyAsync(scratch, code, code_bytes, cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess && init_bytes)
+            e = cudaMemcpyAsync(static_cast<uint8_t*>(scratch) + code_bytes, init, init_bytes, cudaMemcpyHostToDevice, stream);
+        // the host arrays are pageable and may change when this call returns: the copies must have read them
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    }
     if (e == cudaSuccess) {
         const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
-        uint64_t blocks = ceil_div_u64(len, 256);
+        const int lanes = straight && n_regs <= 128 ? 4 : 1;
+        uint64_t blocks = ceil_div_u64(len, 256ull * lanes);
         if (blocks > (uint64_t)sms * 8) blocks = (uint64_t)sms * 8;
         const uint4* dcode = static_cast<const uint4*>(scratch);
-        const uint64_t* dinit = reinterpret_cast<const uint64_t*>(static_cast<uint8_t*>(scratch) + code_bytes);
-#define CATENA_MAP_LAUNCH(R)                                                                                                         \
-    mapvm::map_program_kernel<R><<<(unsigned)blocks, 256, code_bytes, stream>>>(dcode, n_insn, dinit, n_init, index_reg, result_reg, bufs, \
-                                                                                result, elem_bytes, len, st->err)
-        if (n_regs <= 32) CATENA_MAP_LAUNCH(32);
-        else if (n_regs <= 64) CATENA_MAP_LAUNCH(64);
-        else if (n_regs <= 128) CATENA_MAP_LAUNCH(128);
-        else CATENA_MAP_LAUNCH(256);
+        const uint64_t* dinit = scratch ? reinterpret_cast<const uint64_t*>(static_cast<uint8_t*>(scratch) + code_bytes) : nullptr;
+#define CATENA_MAP_LAUNCH(R, V, P)                                                                                                  \
+    mapvm::map_program_kernel<R, V, P><<<(unsigned)blocks, 256, (P) ? 0 : code_bytes, stream>>>(                                    \
+        prm, dcode, n_insn, dinit, n_init, n_regs, index_reg, result_reg, bufs, result, elem_bytes, len, st->err)
+#define CATENA_MAP_PICK(R)                                                   \
+    do {                                                                     \
+        if (lanes == 4 && by_param) CATENA_MAP_LAUNCH(R, 4, true);           \
+        else if (lanes == 4) CATENA_MAP_LAUNCH(R, 4, false);                 \
+        else if (by_param) CATENA_MAP_LAUNCH(R, 1, true);                    \
+        else CATENA_MAP_LAUNCH(R, 1, false);                                 \
+    } while (0)
+        if (n_regs <= 32) CATENA_MAP_PICK(32);
+        else if (n_regs <= 64) CATENA_MAP_PICK(64);
+        else if (n_regs <= 128) CATENA_MAP_PICK(128);
+        else if (by_param) CATENA_MAP_LAUNCH(256, 1, true);
+        else CATENA_MAP_LAUNCH(256, 1, false);
+#undef CATENA_MAP_PICK
 #undef CATENA_MAP_LAUNCH
         count_launch();
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) s = fail_cuda(e, "map program");
     if (s == CATENA_OK && tls().blocking) s = map_program_check_errors();
-    pool_free(scratch);
+    if (scratch) pool_free(scratch);
     if (s != CATENA_OK) {
         pool_free(result);
         return s;

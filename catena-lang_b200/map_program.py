@@ -22,7 +22,7 @@ import ctypes as C
 
 import numpy as np
 
-from .evaluator import NO_OPS, _parse_const, f32_bits
+from .evaluator import NO_OPS, PRIMITIVES, UndefinedBehaviour, _parse_const, bits_f32, f32_bits
 from .lowering import FnSymbol, GpuVar, Unsupported
 
 # opcodes: enum catena_b200_map_op of include/catena_b200.h, in order
@@ -137,9 +137,30 @@ class _Builder:
     def fresh(self):
         r = self.next_reg
         self.next_reg += 1
-        if self.next_reg > MAX_REGS:
+        if self.fixed_presets is not None and self.next_reg > MAX_REGS:
             raise Unsupported("the producer needs more than 256 registers")
         return r
+
+    def const_value(self, reg):
+        what = self.presets[reg] if reg < len(self.presets) else None
+        return what[1] if what is not None and what[0] == "const" else None
+
+    def fold(self, op, regs, outputs):
+        """A primitive over constants is a constant: evaluated now with the host evaluator's table, unless the reference's
+        generated code leaves it undefined for these operands (then it stays an instruction and is reported at run time)."""
+        values = [self.const_value(x) for x in regs]
+        if not values or any(v is None for v in values):
+            return None
+        family = op.split(".")[0]
+        typed = [bits_f32(v) if family == "f32" else v for v in values]
+        if op.endswith(".select"):
+            typed[0] = values[0]
+        try:
+            [result] = PRIMITIVES[op](*typed)
+        except (UndefinedBehaviour, ZeroDivisionError):
+            return None
+        [out] = [o for o in outputs if o.lowered != "erased"]
+        return self.const(f32_bits(result) if out.lowered == "f32" else int(result))
 
     def emit(self, op, dst=0, a=0, b=0, c=0, target=0):
         if len(self.code) >= MAX_INSNS - 1:
@@ -277,6 +298,10 @@ class _Builder:
         if op in _DIRECT:
             if any(isinstance(x, _Buffer) for x in rt):
                 raise Unsupported(f"`{op}` applied to a buffer")
+            folded = self.fold(op, rt, outputs)
+            if folded is not None:
+                self.bind(env, outputs, [folded])
+                return True
             d = self.fresh()
             regs = rt + [0] * (3 - len(rt))
             self.emit(_DIRECT[op], dst=d, a=regs[0], b=regs[1], c=regs[2])
@@ -349,6 +374,49 @@ class _Builder:
         return False
 
 
+_READS_B = {OP[n] for n in _OPS if n not in ("HALT", "MOV", "JMP", "JZ", "ASSERT", "BOOL_NOT", "U64_TO_F32", "U32_NOT", "U32_TO_F32", "F32_NEG",
+                                              "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32")}
+_READS_C = {OP["SELECT"], OP["F32_FMA"]}
+_NO_WRITE = {OP["HALT"], OP["JMP"], OP["JZ"], OP["ASSERT"]}
+
+
+def _reuse_registers(code, n_init, index_reg, result_reg):
+    """Straight-line code only: every temporary is written once, so a register is free again after its last read.  Keeps
+    the preset registers and the index register where they are; returns (code, number of registers, result register)."""
+    def reads(c):
+        out = [] if c.op in (OP["HALT"], OP["JMP"]) else [c.a]
+        if c.op in _READS_B:
+            out.append(c.b)
+        if c.op in _READS_C:
+            out.append(c.c)
+        return out
+
+    last = {}
+    for k, c in enumerate(code):
+        for reg in reads(c):
+            last[reg] = k
+    last[result_reg] = len(code)
+    mapping, free, top = {index_reg: index_reg}, [], index_reg + 1
+    out = []
+    for k, c in enumerate(code):
+        used = reads(c)
+        a, b, cc = (mapping.get(c.a, c.a) if c.a in used else 0), c.b, (mapping.get(c.c, c.c) if c.c in used else 0)
+        if c.op in _READS_B:
+            b = mapping.get(c.b, c.b)
+        for reg in sorted(set(used)):
+            if reg >= n_init and reg != index_reg and last.get(reg) == k and reg in mapping:
+                free.append(mapping[reg])
+        dst = 0
+        if c.op not in _NO_WRITE:
+            if free:
+                dst = free.pop()
+            else:
+                dst, top = top, top + 1
+            mapping[c.dst] = dst
+        out.append(Insn(c.op, dst, a, b, cc, 0, c.target))
+    return out, top, mapping.get(result_reg, result_reg)
+
+
 def compile_producer(modules, producer, env_vars, elem_lowered):
     """Register program for `out[i] = producer(env_vars..., i)`.
 
@@ -390,7 +458,7 @@ def compile_producer(modules, producer, env_vars, elem_lowered):
 
     # pass 1 discovers the presets (constants appear while walking), pass 2 emits with the registers behind them
     first = _Builder(modules)
-    first.next_reg = 0
+    first.next_reg = 1 << 20              # away from the preset numbers; pass 1 only discovers the presets
     run(first)
     presets = list(first.presets)
     second = _Builder(modules)
@@ -400,7 +468,10 @@ def compile_producer(modules, producer, env_vars, elem_lowered):
     if second.next_reg >= MAX_REGS:
         raise Unsupported("the producer needs more than 256 registers")
     index, result = run(second)
+    code, n_regs = second.code, max(second.next_reg, 1)
+    if not any(c.op in (OP["JMP"], OP["JZ"]) for c in code):
+        code, n_regs, result = _reuse_registers(code, len(presets), index, result)
     # ("buflen", slot, bytes) presets name buffer slots; launches index the environment: translate
     slot_position = {slot: position for position, slot in buffer_slot.items()}
     presets = [("buflen", slot_position[w[1]], w[2]) if w[0] == "buflen" else w for w in presets]
-    return MapProgram(producer, second.code, presets, max(second.next_reg, 1), index, result, env_kinds, elem_bytes)
+    return MapProgram(producer, code, presets, n_regs, index, result, env_kinds, elem_bytes)

@@ -15,7 +15,8 @@
 //   * register_modules takes LOWERED modules (the reference's IR after codegen, catena-lang/src/codegen/mod.rs:107-146):
 //     the lowering selector (catena_b200_lowering.hpp) picks a plan for each — an entry point of the kernel library for the
 //     recognised kernel shapes, the host evaluator (catena_b200_eval.hpp) for scalar modules, which the reference also
-//     runs on the host.
+//     runs on the host, and for a `materializec` with any other scalar producer the generic map kernel, which interprets
+//     the producer as a register program (catena_b200_map_program.hpp).
 //   * GpuDialect::Hip is refused with InitError.
 //   * Mem owns DEVICE memory and copies on to_*_vec.  Like the Rust API, exec consumes its Mem arguments: they are
 //     freed when the call returns (runtime.rs:175-179, mem.rs:119-125).
@@ -39,6 +40,7 @@
 
 #include "catena_b200.h"
 #include "catena_b200_eval.hpp"
+#include "catena_b200_map_program.hpp"
 
 namespace catena_b200 {
 
@@ -87,6 +89,8 @@ public:
     uint64_t len_bytes() const { return raw_.len; }
     bool is_null() const { return raw_.data == nullptr; }
     catena_mem_t raw() const { return raw_; }
+    // gives the buffer up without freeing it (its owner is now whoever holds raw())
+    void forget() { raw_ = {nullptr, 0}; }
 
     template <class T>
     std::vector<T> to_vec() const {
@@ -130,6 +134,7 @@ public:
     uint64_t as_u64() const { expect(ValueKind::U64); return u_; }
     float as_f32() const { expect(ValueKind::F32); return f_; }
     const Mem& as_mem() const { expect(ValueKind::Mem); return m_; }
+    Mem& as_mem() { expect(ValueKind::Mem); return m_; }
     Mem take_mem() { expect(ValueKind::Mem); return std::move(m_); }
 
 private:
@@ -252,6 +257,92 @@ public:
                         }
                     }
                     return (catena_status_t)CATENA_OK;
+                }};
+                continue;
+            }
+            if (plan.kernel == "host_with_map_kernels") {
+                // the producers' register programs are built now: one the map kernel cannot run is an InitError
+                auto programs = std::make_shared<std::map<const lowering::GpuAssign*, map_program::Program>>();
+                try {
+                    for (const lowering::GpuAssign& a : m.entry.assignments)
+                        if (a.op == "materializec") (*programs)[&a] = map_program::for_assignment(*shared, a);
+                } catch (const lowering::Unsupported& e) {
+                    throw InitError("program '" + m.source_name + "': " + e.what());
+                }
+                const std::string name = m.name;
+                std::vector<K> out_kinds = outs;
+                table_[m.source_name] = Signature{plan.symbol, ins, outs, [shared, programs, name, out_kinds](std::vector<Value>& a, std::vector<Value>& o) {
+                    // buffers materialised during this call; what the results do not take over is freed at the end
+                    std::map<void*, catena_mem_t> made;
+                    catena_status_t failed = CATENA_OK;
+                    eval::Evaluator ev(*shared);
+                    ev.materialize = [&](const lowering::GpuAssign& assign, uint64_t len, const std::vector<eval::Val>& env, const std::string&) {
+                        const map_program::Program& prog = programs->at(&assign);
+                        std::vector<map_program::EnvValue> bound;
+                        for (const eval::Val& v : env)
+                            bound.push_back(v.kind == eval::Val::Scalar ? map_program::EnvValue::scalar(v.bits)
+                                                                        : map_program::EnvValue::mem(catena_mem_t{v.ptr, v.bytes}));
+                        catena_mem_t out{nullptr, 0};
+                        const catena_status_t s = prog.launch(len, bound, &out);
+                        if (s != CATENA_OK) { failed = s; throw eval::AssertFailed("map program failed"); }
+                        if (out.data) made[out.data] = out;
+                        eval::Val p = eval::Val::pointer(out.data, prog.elem_bytes);
+                        p.device = true;
+                        p.bytes = out.len;
+                        return p;
+                    };
+                    std::vector<eval::Val> args;
+                    std::map<void*, Value*> arguments;
+                    for (Value& v : a) {
+                        switch (v.kind()) {
+                            case K::Bool: args.push_back(eval::Val::scalar(v.as_bool())); break;
+                            case K::U32: args.push_back(eval::Val::scalar(v.as_u32())); break;
+                            case K::U64: args.push_back(eval::Val::scalar(v.as_u64())); break;
+                            case K::F32: args.push_back(eval::Val::f32(v.as_f32())); break;
+                            default:
+                                args.push_back(eval::Val::device_mem(v.as_mem().raw().data, v.as_mem().raw().len));
+                                if (v.as_mem().raw().data) arguments[v.as_mem().raw().data] = &v;
+                        }
+                    }
+                    auto release = [&]() { for (auto& kv : made) catena_b200_mem_free(kv.second); made.clear(); };
+                    std::vector<eval::Val> got;
+                    try {
+                        got = ev.call(name, args);
+                    } catch (const eval::AssertFailed&) {
+                        release();
+                        return failed != CATENA_OK ? failed : (catena_status_t)CATENA_E_ASSERT;
+                    } catch (const std::exception&) {
+                        release();
+                        return (catena_status_t)CATENA_E_BAD_ARG;
+                    }
+                    catena_status_t s = got.size() == out_kinds.size() ? CATENA_OK : CATENA_E_BAD_ARG;
+                    for (size_t i = 0; s == CATENA_OK && i < got.size(); ++i) {
+                        switch (out_kinds[i]) {
+                            case K::Bool: o.push_back(Value::boolean(got[i].bits != 0)); break;
+                            case K::U32: o.push_back(Value::u32((uint32_t)got[i].bits)); break;
+                            case K::U64: o.push_back(Value::u64(got[i].bits)); break;
+                            case K::F32: o.push_back(Value::f32(got[i].as_f32())); break;
+                            default: {
+                                if (got[i].kind != eval::Val::Mem) { s = CATENA_E_BAD_ARG; break; }
+                                if (!got[i].ptr || got[i].bytes == 0) { o.push_back(Value::mem(Mem())); break; }
+                                auto mine = made.find(got[i].ptr);
+                                auto theirs = arguments.find(got[i].ptr);
+                                if (mine != made.end()) {
+                                    made.erase(mine);
+                                } else if (theirs != arguments.end()) {
+                                    theirs->second->as_mem().forget();       // an argument handed back: the result takes it over
+                                    arguments.erase(theirs);
+                                } else {
+                                    s = CATENA_E_BAD_ARG;                    // a buffer the program does not own
+                                    break;
+                                }
+                                o.push_back(Value::mem(Mem(catena_mem_t{got[i].ptr, got[i].bytes})));
+                            }
+                        }
+                    }
+                    release();
+                    if (s != CATENA_OK) o.clear();
+                    return s;
                 }};
                 continue;
             }

@@ -16,14 +16,16 @@
 // f32.fma is fmaf; f32.round-to-u32 is (uint32_t)nearbyintf(x).  A failed `assert` throws AssertFailed (the generated code
 // traps, catena-lang/src/codegen/prelude.rs:38-55); operands for which the generated C is undefined (u32 shifts by 32 or
 // more, round-to-u32 outside [0, 2^32), row-major division by zero) throw UndefinedBehaviour.
-// Buffers are HOST pointers here: `ptr<u64>` / `ptr<f32>` / `mem` values are what a caller with host-addressable memory
-// passes in.  materializec / gpu.materialize are kernel launches and are refused (NotScalar).
+// Buffers are HOST pointers — what a caller with host-addressable memory passes in — or DEVICE buffers (Val::device_mem),
+// which host code may cast and pass on but not read.  `materializec` is a kernel launch: it goes to the `materialize`
+// callback (catena_b200.hpp launches the generic map kernel there) and is refused without one (NotScalar).
 #ifndef CATENA_B200_EVAL_HPP
 #define CATENA_B200_EVAL_HPP
 
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <map>
 #include <stdexcept>
 #include <string>
@@ -51,11 +53,13 @@ struct Val {
     void* ptr = nullptr;
     uint64_t bytes = 0;   // Mem: length in bytes
     uint32_t elem = 8;    // Ptr: bytes per element (8 for ptr<u64>, 4 for ptr<f32>)
+    bool device = false;  // Ptr / Mem: device memory — host code may cast it and pass it on, never read it
     std::string fn;       // Fn: target of the function symbol
     static Val scalar(uint64_t b) { Val v; v.kind = Scalar; v.bits = b; return v; }
     static Val f32(float f) { uint32_t u; std::memcpy(&u, &f, 4); return scalar(u); }
     static Val mem(void* p, uint64_t n) { Val v; v.kind = Mem; v.ptr = p; v.bytes = n; return v; }
     static Val pointer(void* p, uint32_t elem_bytes) { Val v; v.kind = Ptr; v.ptr = p; v.elem = elem_bytes; return v; }
+    static Val device_mem(void* p, uint64_t n) { Val v = mem(p, n); v.device = true; return v; }
     float as_f32() const { uint32_t u = (uint32_t)bits; float f; std::memcpy(&f, &u, 4); return f; }
 };
 
@@ -65,6 +69,10 @@ using lowering::Operand;
 
 class Evaluator {
 public:
+    // Runs a `materializec` (a kernel launch): (assignment, length, values of the environment component, producer symbol) ->
+    // the buffer produced (a Ptr value).  Without it such an assignment is refused (NotScalar).
+    std::function<Val(const GpuAssign&, uint64_t, const std::vector<Val>&, const std::string&)> materialize;
+
     explicit Evaluator(const std::vector<GpuModule>& modules) {
         for (const GpuModule& m : modules) {
             by_name_[m.name] = &m;
@@ -93,6 +101,27 @@ public:
             if (t.lowered != "erased") out.push_back(env.at(t.name));
         return out;
     }
+
+    // Value (bit pattern) of a scalar primitive with one runtime output over constant operands (bit patterns); false when
+    // `op` is not such a primitive or the reference's generated code leaves it undefined for these operands.  Used by the
+    // map-program compiler to fold constants.
+    bool fold(const std::string& op, const std::vector<uint64_t>& operands, uint64_t* out) const {
+        std::vector<Val> in;
+        for (uint64_t b : operands) in.push_back(Val::scalar(b));
+        Env env;
+        const std::vector<Operand> outputs = {Operand::var("folded", "u64")};
+        try {
+            if (!primitive(env, op, in, outputs, {})) return false;
+        } catch (const std::exception&) {
+            return false;
+        }
+        auto it = env.find("folded");
+        if (it == env.end() || it->second.kind != Val::Scalar) return false;
+        *out = it->second.bits;
+        return true;
+    }
+    // The module a generated symbol, a source name or a function symbol's target names; nullptr when there is none.
+    const GpuModule* module(const std::string& name) const { return find(name); }
 
 private:
     using Env = std::map<std::string, Val>;
@@ -196,6 +225,16 @@ private:
                 for (size_t k = 0; k < nexts.size(); ++k) acc[k] = scratch.at(nexts[k].name);
             }
             bind(env, a.outputs, acc);
+        } else if (a.op == "materializec" && materialize) {                 // ops/materializec.rs:84-145: len, env..., producer
+            if (a.inputs.size() < 2) throw std::invalid_argument("materializec: expected len, env..., producer");
+            size_t env_end = a.inputs.size() - 1;
+            if (!a.input_sizes.empty()) {
+                if (a.input_sizes.size() != 3 || a.input_sizes[0] != 1) throw std::invalid_argument("materializec expects the components len, env, producer");
+                env_end = 1 + a.input_sizes[1];
+            }
+            std::vector<Val> env_values(ins.begin() + 1, ins.begin() + env_end);
+            std::vector<Val> rest(ins.begin() + env_end, ins.end());
+            bind(env, a.outputs, {materialize(a, ins[0].bits, runtime(env_values), single_fn(rest).fn)});
         } else {
             throw NotScalar("`" + a.op + "` is not a scalar assignment");
         }
@@ -301,6 +340,7 @@ private:
         if (op == "ix") {                                                    // gpu.rs:850-864: buffer[index]
             need(2);
             if (in[1].kind != Val::Ptr) throw std::invalid_argument("ix: expected (index, buffer)");
+            if (in[1].device) throw NotScalar("host code cannot dereference device memory");
             if (in[1].elem == 4) return out1(reinterpret_cast<const uint32_t*>(in[1].ptr)[A(0)]);
             return out1(reinterpret_cast<const uint64_t*>(in[1].ptr)[A(0)]);
         }
@@ -308,14 +348,19 @@ private:
             need(1);
             if (in[0].kind != Val::Mem) throw std::invalid_argument(op + ": expected a mem");
             const uint32_t elem = op == "mem.cast.u64" ? 8 : 4;
-            bind(env, outputs, {Val::scalar(in[0].bytes / elem), Val::pointer(in[0].ptr, elem)});
+            Val p = Val::pointer(in[0].ptr, elem);
+            p.device = in[0].device;
+            p.bytes = in[0].bytes;
+            bind(env, outputs, {Val::scalar(in[0].bytes / elem), p});
             return true;
         }
         if (op == "buf.u64.cast-same-length" || op == "buf.f32.cast-same-length") { need(2); bind(env, outputs, {in[0]}); return true; }
         if (op == "buf.to-mem") {                                            // gpu.rs:808-836
             need(2);
             if (in[1].kind != Val::Ptr) throw std::invalid_argument("buf.to-mem: expected (len, buffer)");
-            bind(env, outputs, {Val::mem(in[1].ptr, A(0) * in[1].elem)});
+            Val m = Val::mem(in[1].ptr, A(0) * in[1].elem);
+            m.device = in[1].device;
+            bind(env, outputs, {m});
             return true;
         }
         if (op == "u64.to-ix") {                                             // gpu.rs:866-892: components [index, bound, proof]

@@ -18,8 +18,10 @@
 //   * `mem.cast.u64`, `ix.zero`, `ix` (catena-lang/tests/runtime.rs:713-726)   -> buffer-head copy
 //   * a module of scalar primitives, `bool.ifc`, `eval`, `reducec` over scalar closures and calls
 //     (catena-lang/tests/cases/closures/*.hex)                                 -> host execution (catena_b200_eval.hpp)
-// Anything else is reported as unsupported (the reference would render a generic one-thread-per-element kernel for it;
-// this backend ships no source generator).  The Rust front end that produces the IR is not part of this build, so the
+//   * any other `materializec` (catena-lang/examples/materializec.hex, tests/cases/materialize/basic.hex)
+//                                                                              -> the generic map kernel, which interprets the
+//     producer as a register program (catena_b200_map_program.hpp); the code around it runs on the host
+// Anything else is reported as unsupported.  The Rust front end that produces the IR is not part of this build, so the
 // fixtures of the tests are written by hand from the lowering rules cited above.
 #ifndef CATENA_B200_LOWERING_HPP
 #define CATENA_B200_LOWERING_HPP
@@ -113,7 +115,9 @@ inline std::string classify(const GpuAssign& a) {
             if (o.is_fn)
                 for (auto& m : maps)
                     if (o.name == m[0]) return m[1];
-        return "";
+        // any other producer: the generic map kernel interprets it as a register program, if it compiles to one
+        // (catena_b200_map_program.hpp; the caller of select() builds the program and reports a producer that does not)
+        return a.op == "materializec" ? "map_generic" : "";
     }
     // scalar primitives the renderer prints as single C expressions (catena-lang/src/codegen/gpu.rs:322-447)
     static const char* scalar_prefixes[] = {"f32.", "u32.", "u64.", "bool.", "const.", "ix", "unit.", ":.", "ax-mp", "assert", "mem.cast",
@@ -139,6 +143,18 @@ inline KernelPlan select(const GpuModule& module) {
             if (kinds[i++] != w) return false;
         return true;
     };
+    bool generic_only = !kinds.empty();
+    for (const std::string& k : kinds) generic_only = generic_only && k == "map_generic";
+    if (generic_only) {
+        // host code around generic map kernels: it may cast buffers and pass them on, not read them
+        for (const GpuAssign& a : module.entry.assignments) {
+            if (a.op == "materializec" || !a.call_symbol.empty() || detail::starts_with(a.op, "mem.cast.") || detail::starts_with(a.op, "buf.")) continue;
+            for (const Operand& o : a.inputs)
+                if (!o.is_fn && (o.lowered == "mem" || detail::starts_with(o.lowered, "ptr<")))
+                    throw Unsupported(module.name + ": host code reads a device buffer (`" + a.op + "`)");
+        }
+        return {"host_with_map_kernels", symbol, "producers interpreted by the generic map kernel; the code around them runs on the host"};
+    }
     if (kinds.empty()) {
         bool memory = false, cast_u64 = false, ix_zero = false;
         size_t ix_count = 0;

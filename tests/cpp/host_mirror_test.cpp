@@ -66,6 +66,21 @@ static std::vector<lw::GpuModule> lowered_modules() {
                            {"u64.gt", {var("n", "u64"), var("z", "u64")}, {var("nz", "bool"), var("ht", "erased"), var("hf", "erased")}, ""},
                            {"assert", {var("nz", "bool")}, {var("h", "erased")}, ""}, {"ax-mp", {var("h", "erased"), var("ht", "erased")}, {var("proof", "erased")}, ""},
                            {"ix.zero", {var("proof", "erased")}, {var("i0", "u64")}, ""}, {"ix", {var("i0", "u64"), var("buf", "ptr<u64>")}, {var("head", "u64")}, ""}}));
+    // catena-lang/examples/materializec.hex: a `materializec` whose producer has no prebuilt kernel (generic map kernel)
+    mods.push_back(module("materialize-copy-u64-producer", {var("input", "ptr<u64>"), var("i", "u64")}, {var("r", "u64")},
+                          {{"ix", {var("i", "u64"), var("input", "ptr<u64>")}, {var("r", "u64")}, ""}}));
+    mods.push_back(module("materialize-copy-u64", {var("m", "mem")}, {var("out", "mem")},
+                          {{"mem.cast.u64", {var("m", "mem")}, {var("len", "u64"), var("input", "ptr<u64>")}, ""},
+                           {":.param", {var("len", "u64")}, {var("n", "erased")}, ""},
+                           {"materializec", {var("len", "u64"), var("input", "ptr<u64>"), lw::Operand::fn("materialize-copy-u64-producer")},
+                            {var("buf", "ptr<u64>")}, "", {1, 1, 1}, {1}},
+                           {"buf.to-mem", {var("len", "u64"), var("buf", "ptr<u64>")}, {var("out", "mem")}, ""}}));
+    // tests/cases/materialize/basic.hex: out[i] = i
+    mods.push_back(module("cast-index", {var("i", "u64")}, {var("r", "u64")}, {{"ix.to-u64", {var("i", "u64")}, {var("r", "u64")}, ""}}));
+    mods.push_back(module("materialize-indexes-source", {var("len", "u64")}, {var("out", "mem")},
+                          {{":.param", {var("len", "u64")}, {var("n", "erased")}, ""},
+                           {"materializec", {var("len", "u64"), lw::Operand::fn("cast-index")}, {var("buf", "ptr<u64>")}, "", {1, 0, 1}, {1}},
+                           {"buf.to-mem", {var("len", "u64"), var("buf", "ptr<u64>")}, {var("out", "mem")}, ""}}));
     return mods;
 }
 
@@ -105,6 +120,20 @@ static int run_cpu() {
     // lowered modules: a scalar module runs on the host through the evaluator (no device needed)
     rt.register_modules(lowered_modules());
     CHECK(rt.has("shift-and-sub") && rt.has("sum-u64") && rt.has("array-head-u64"));
+    CHECK(rt.has("materialize-copy-u64") && rt.has("materialize-indexes-source") && !rt.has("materialize-copy-u64-producer"));
+    {
+        // a producer that is not among the modules cannot be compiled: refused when the modules are registered
+        bool refused = false;
+        try {
+            Runtime other = Runtime::from_sources({});
+            other.register_modules({module("bad-map", {var("n", "u64")}, {var("out", "mem")},
+                                           {{"materializec", {var("n", "u64"), lw::Operand::fn("no.such-producer")}, {var("buf", "ptr<u64>")}, "", {1, 0, 1}, {1}},
+                                            {"buf.to-mem", {var("n", "u64"), var("buf", "ptr<u64>")}, {var("out", "mem")}, ""}})});
+        } catch (const InitError&) {
+            refused = true;
+        }
+        CHECK(refused);
+    }
     {
         std::vector<Value> out = rt.exec("shift-and-sub", {}, 1);
         CHECK(out.size() == 1 && out[0].kind() == ValueKind::U32 && out[0].as_u32() == 0xFFFFFFFCu);     // tests/runtime.rs:471
@@ -190,6 +219,20 @@ static int run_gpu() {
             c.push_back(Value::mem(rt.mem_u64({})));
             rt.exec("array-head-u64", std::move(c));
         }));
+    }
+    // the generic map kernel behind Runtime::exec: catena-lang/tests/cases/materializec.rs:18-31, tests/cases/materialize.rs:5-31
+    {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_u64({3, 5, 8, 13})));
+        std::vector<Value> out = rt.exec("materialize-copy-u64", std::move(a), 1);
+        CHECK(out[0].as_mem().to_u64_vec() == (std::vector<uint64_t>{3, 5, 8, 13}));
+        std::vector<Value> n;
+        n.push_back(Value::u64(4));
+        CHECK(rt.exec("materialize-indexes-source", std::move(n))[0].as_mem().to_u64_vec() == (std::vector<uint64_t>{0, 1, 2, 3}));
+        std::vector<Value> z;
+        z.push_back(Value::u64(0));
+        std::vector<Value> empty = rt.exec("materialize-indexes-source", std::move(z));
+        CHECK(empty[0].as_mem().is_null() && empty[0].as_mem().to_u64_vec().empty());
     }
     // bf16 GEMM through Runtime::exec: 256 x 256 x 64 of ones and twos -> every element 128 (exact in bf16)
     {

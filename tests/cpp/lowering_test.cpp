@@ -65,7 +65,14 @@ int main() {
     CHECK(select(mod("tensor.concat-f32", {cast, cast, materializec("tensor.concat-f32-at"), to_mem})).kernel == "copy_concat");
     CHECK(select(mod("nn.silu", {prim("f32.neg"), prim("math.exp-approx", "program_math_exp_approx"), prim("f32.add"), prim("f32.div"), prim("f32.mul")})).kernel ==
           "host_scalar");
-    CHECK(refused(mod("my-map", {cast, materializec("my.custom-at"), to_mem})));
+    // a producer without a prebuilt kernel goes to the generic map kernel (whether it compiles to a register program is decided
+    // when the modules are registered); a `gpu.materialize` with an unknown kernel stays refused
+    CHECK(select(mod("my-map", {cast, materializec("my.custom-at"), to_mem})).kernel == "host_with_map_kernels");
+    {
+        GpuAssign g = materializec("my.custom-at");
+        g.op = "gpu.materialize";
+        CHECK(refused(mod("my-launch", {cast, g, to_mem})));
+    }
     CHECK(refused(mod("odd", {cast, reducec("f32.add-env", "my.getter")})));
     CHECK(refused(mod("two-maps", {cast, materializec("tensor.arange-at"), materializec("tensor.slice-at"), to_mem})));
     std::printf("ok %d checks\n", g_checks);

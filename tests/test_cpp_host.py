@@ -54,3 +54,37 @@ def test_cpp_host_evaluator(tmp_path):
                            os.path.join(ROOT, "tests", "cpp", "eval_test.cpp"), "-o", out])
     p = subprocess.run([out], capture_output=True, text=True, timeout=60)
     assert p.returncode == 0 and p.stdout.strip().startswith("ok "), p.stdout + p.stderr
+
+
+@pytest.fixture(scope="module")
+def map_program_binary(tmp_path_factory):
+    out = str(tmp_path_factory.mktemp("cpp") / "map_program_test")
+    subprocess.check_call([os.environ.get("CXX", "g++"), "-std=c++17", "-O1", "-Wall", "-ffp-contract=off", "-I", os.path.join(ROOT, "include"),
+                           "-I", "/usr/local/cuda/include", os.path.join(ROOT, "tests", "cpp", "map_program_test.cpp"), "-o", out, "-L", LIBDIR,
+                           "-lcatena_b200", "-Wl,-rpath," + LIBDIR, "-L/usr/local/cuda/lib64", "-Wl,-rpath,/usr/local/cuda/lib64"])
+    return out
+
+
+def test_cpp_map_program_compiler_agrees_with_python(map_program_binary):
+    """The C++ and the Python compiler of register programs (include/catena_b200_map_program.hpp, map_program.py) give the same
+    program — presets, registers, every instruction — for the reference's materializec programs, a conditional and a fold."""
+    import lowered_fixtures as fx
+    from catena_lang_b200 import lowering as lo
+    p = subprocess.run([map_program_binary, "list"], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0, p.stdout + p.stderr
+    mm = lo.module_map(fx.materialize_programs() + fx.custom_map_programs())
+    lines = []
+    for name in ("materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec"):
+        [assign] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+        prog = lo.map_program_for(assign, mm)
+        lines.append(f"program {name} regs={prog.n_regs} index={prog.index_reg} result={prog.result_reg} elem={prog.elem_bytes}")
+        for what in prog.presets:
+            lines.append(f"  preset {what[0]} {what[1]} {what[2] if what[0] == 'buflen' else 0}")
+        for c in prog.code:
+            lines.append(f"  insn {c.op} {c.dst} {c.a} {c.b} {c.c} {c.target}")
+    assert p.stdout.strip().splitlines() == lines
+
+
+@pytest.mark.gpu
+def test_cpp_map_program_on_the_gpu(map_program_binary):
+    run(map_program_binary, "gpu")
