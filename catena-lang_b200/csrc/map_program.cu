@@ -49,30 +49,35 @@ struct ParamProgram {
     uint64_t init[kParamInit];
 };
 
-// REGS: capacity of the register file (local memory).  V: elements a thread carries through the program in lockstep — one
-// fetch, decode and dispatch per V elements; V > 1 only for programs without jumps (the host decides).  PARAM: the program
-// sits in the kernel parameters instead of shared memory.
-template <int REGS, int V, bool PARAM>
-__global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant__ ParamProgram prm, const uint4* __restrict__ code,
+// The register file.  Low halves: shared memory, [register][lane][thread] (conflict-free, and unlike a local-memory array it
+// cannot be evicted: with the file in local memory an SM's resident threads touched several times the L1 and the spill to L2
+// and HBM cost ten times the algorithmic traffic).  High halves: a local-memory array — bool / u32 / f32 instructions never
+// touch them, so a program without u64 arithmetic uses them for the index only.  The high half of a register that holds a
+// 32-bit value is stale; nothing reads it: flags are tested on the low half, and the type system never feeds a 32-bit value
+// to a u64 instruction (the primitive table has no u32 -> u64 conversion).
+// REGS: capacity of the high-half file.  V: elements a thread carries through the program in lockstep — one fetch, decode
+// and dispatch per V elements; V > 1 only for programs without jumps (the host decides).  PARAM: the program sits in the
+// kernel parameters instead of shared memory.  T: threads per CTA.
+template <int REGS, int V, bool PARAM, int T>
+__global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ ParamProgram prm, const uint4* __restrict__ code,
                                                           uint32_t n_insn, const uint64_t* __restrict__ init, uint32_t n_init, uint32_t n_regs,
                                                           uint32_t index_reg, uint32_t result_reg, const __grid_constant__ Buffers bufs,
                                                           void* __restrict__ out, uint32_t elem_bytes, uint64_t len, uint32_t* err) {
-    extern __shared__ uint4 s_code[];
+    extern __shared__ uint4 s_dyn[];
+    const uint4* s_code = s_dyn;
+    uint32_t* s_lo = reinterpret_cast<uint32_t*>(s_dyn + (PARAM ? 0 : n_insn)) + threadIdx.x;
     if (!PARAM) {
-        for (uint32_t k = threadIdx.x; k < n_insn; k += blockDim.x) s_code[k] = code[k];
+        for (uint32_t k = threadIdx.x; k < n_insn; k += T) s_dyn[k] = code[k];
         __syncthreads();
     }
-    // The register file, in local memory, as separate low and high halves: bool / u32 / f32 instructions touch the low halves
-    // only (a third of the traffic of whole registers — the file's bandwidth through L1 is what bounds an interpreted map).  The
-    // high half of a register that holds such a value is stale; nothing reads it: flags are tested on the low half, and the
-    // type system never feeds a 32-bit value to a u64 instruction (there is no u32 -> u64 conversion in the table).
-    uint32_t lo[REGS][V], hi[REGS][V];
+#define lo(R, v) s_lo[((R) * V + (v)) * T]
+    uint32_t hi[REGS][V];
 #pragma unroll 1
     for (uint32_t k = 0; k < n_regs; ++k) {
         const uint64_t x = k < n_init ? (PARAM ? prm.init[k] : init[k]) : 0ull;
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            lo[k][v] = (uint32_t)x;
+            lo(k, v) = (uint32_t)x;
             hi[k][v] = (uint32_t)(x >> 32);
         }
     }
@@ -83,7 +88,7 @@ __global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant_
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             const uint64_t e = i + v * stride < len ? i + v * stride : i;
-            lo[index_reg][v] = (uint32_t)e;
+            lo(index_reg, v) = (uint32_t)e;
             hi[index_reg][v] = (uint32_t)(e >> 32);
         }
         uint32_t pc = 0, back = 0;
@@ -94,7 +99,7 @@ __global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant_
             const uint32_t op = w.x & 0xFFFFu, dst = w.x >> 16, ra = w.y & 0xFFFFu, rb = w.y >> 16, rc = w.z & 0xFFFFu;
             if (op == CATENA_MAP_HALT) break;
             if (op == CATENA_MAP_JMP || op == CATENA_MAP_JZ) {          // V == 1 here
-                if (op == CATENA_MAP_JMP || lo[ra][0] == 0) {
+                if (op == CATENA_MAP_JMP || lo(ra, 0) == 0) {
                     if (w.w < pc && ++back > kBackJumpBudget) {
                         fault = max(fault, (uint32_t)ERR_BUDGET);
                         gave_up = true;
@@ -105,39 +110,43 @@ __global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant_
                 continue;
             }
             // one dispatch per instruction; inside a case the V elements are independent
-#define CATENA_R64(R, v) (((uint64_t)hi[R][v] << 32) | lo[R][v])
+#define CATENA_R64(R, v) (((uint64_t)hi[R][v] << 32) | lo(R, v))
 #define CATENA_W64(v, X)                       \
     do {                                       \
         const uint64_t x_ = (X);               \
-        lo[dst][v] = (uint32_t)x_;             \
+        lo(dst, v) = (uint32_t)x_;             \
         hi[dst][v] = (uint32_t)(x_ >> 32);     \
     } while (0)
 #define CATENA_LANES _Pragma("unroll") for (int v = 0; v < V; ++v)
 // 32-bit operands and result
-#define CATENA_W(EXPR)      CATENA_LANES { const uint32_t a = lo[ra][v], b = lo[rb][v]; (void)b; lo[dst][v] = (uint32_t)(EXPR); } break
-#define CATENA_W1(EXPR)     CATENA_LANES { const uint32_t a = lo[ra][v]; lo[dst][v] = (uint32_t)(EXPR); } break
+#define CATENA_W(EXPR)      CATENA_LANES { const uint32_t a = lo(ra, v), b = lo(rb, v); (void)b; lo(dst, v) = (uint32_t)(EXPR); } break
+#define CATENA_W1(EXPR)     CATENA_LANES { const uint32_t a = lo(ra, v); lo(dst, v) = (uint32_t)(EXPR); } break
 // 64-bit operands, 64-bit result
 #define CATENA_D(EXPR)      CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; CATENA_W64(v, EXPR); } break
 // 64-bit operands, 32-bit result (compares, conversions)
-#define CATENA_DW(EXPR)     CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; lo[dst][v] = (uint32_t)(EXPR); } break
-#define CATENA_DW1(EXPR)    CATENA_LANES { const uint64_t a = CATENA_R64(ra, v); lo[dst][v] = (uint32_t)(EXPR); } break
-#define CATENA_F(EXPR)      CATENA_LANES { const float a = __uint_as_float(lo[ra][v]), b = __uint_as_float(lo[rb][v]); (void)b; lo[dst][v] = __float_as_uint(EXPR); } break
-#define CATENA_FC(EXPR)     CATENA_LANES { const float a = __uint_as_float(lo[ra][v]), b = __uint_as_float(lo[rb][v]); lo[dst][v] = (EXPR) ? 1u : 0u; } break
+#define CATENA_DW(EXPR)     CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; lo(dst, v) = (uint32_t)(EXPR); } break
+#define CATENA_DW1(EXPR)    CATENA_LANES { const uint64_t a = CATENA_R64(ra, v); lo(dst, v) = (uint32_t)(EXPR); } break
+#define CATENA_F(EXPR)      CATENA_LANES { const float a = __uint_as_float(lo(ra, v)), b = __uint_as_float(lo(rb, v)); (void)b; lo(dst, v) = __float_as_uint(EXPR); } break
+#define CATENA_FC(EXPR)     CATENA_LANES { const float a = __uint_as_float(lo(ra, v)), b = __uint_as_float(lo(rb, v)); lo(dst, v) = (EXPR) ? 1u : 0u; } break
 #define CATENA_UNDEF        (fault = max(fault, (uint32_t)ERR_UNDEFINED), 0)
             switch (op) {
             case CATENA_MAP_ASSERT:
-                CATENA_LANES { if (lo[ra][v] == 0) fault = max(fault, (uint32_t)ERR_ASSERT); }
+                CATENA_LANES { if (lo(ra, v) == 0) fault = max(fault, (uint32_t)ERR_ASSERT); }
                 break;
             case CATENA_MAP_MOV:
-                CATENA_LANES { lo[dst][v] = lo[ra][v]; hi[dst][v] = hi[ra][v]; }
+                CATENA_LANES { lo(dst, v) = lo(ra, v); hi[dst][v] = hi[ra][v]; }
                 break;
             case CATENA_MAP_SELECT:
                 CATENA_LANES {
-                    const bool t = lo[ra][v] != 0;
-                    const uint32_t l = t ? lo[rb][v] : lo[rc][v], h = t ? hi[rb][v] : hi[rc][v];
-                    lo[dst][v] = l;
+                    const bool t = lo(ra, v) != 0;
+                    const uint32_t l = t ? lo(rb, v) : lo(rc, v), h = t ? hi[rb][v] : hi[rc][v];
+                    lo(dst, v) = l;
                     hi[dst][v] = h;
                 }
+                break;
+            case CATENA_MAP_MOV32: CATENA_W1(a);
+            case CATENA_MAP_SELECT32:
+                CATENA_LANES { lo(dst, v) = lo(ra, v) != 0 ? lo(rb, v) : lo(rc, v); }
                 break;
             case CATENA_MAP_BOOL_NOT: CATENA_W1(a ? 0u : 1u);
             case CATENA_MAP_BOOL_AND: CATENA_W((a && b) ? 1u : 0u);
@@ -176,7 +185,7 @@ __global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant_
             case CATENA_MAP_F32_DIV: CATENA_F(cmath::div(a, b));
             case CATENA_MAP_F32_NEG: CATENA_W1(a ^ 0x80000000u);
             case CATENA_MAP_F32_FMA:
-                CATENA_LANES { lo[dst][v] = __float_as_uint(__fmaf_rn(__uint_as_float(lo[ra][v]), __uint_as_float(lo[rb][v]), __uint_as_float(lo[rc][v]))); }
+                CATENA_LANES { lo(dst, v) = __float_as_uint(__fmaf_rn(__uint_as_float(lo(ra, v)), __uint_as_float(lo(rb, v)), __uint_as_float(lo(rc, v)))); }
                 break;
             case CATENA_MAP_F32_EQ: CATENA_FC(a == b);
             case CATENA_MAP_F32_NE: CATENA_FC(a != b);
@@ -201,7 +210,7 @@ __global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant_
                     uint32_t x = 0;
                     if (a >= (bufs.bytes[rb] >> 2)) fault = max(fault, (uint32_t)ERR_RANGE);
                     else x = __ldg(reinterpret_cast<const uint32_t*>(bufs.base[rb]) + a);
-                    lo[dst][v] = x;
+                    lo(dst, v) = x;
                 }
                 break;
             default: break;      // unreachable: the host validated every opcode
@@ -222,11 +231,12 @@ __global__ void __launch_bounds__(256) map_program_kernel(const __grid_constant_
         for (int v = 0; v < V; ++v) {
             const uint64_t e = i + v * stride;
             if (e < len) {
-                if (elem_bytes == 8) static_cast<uint64_t*>(out)[e] = gave_up ? 0ull : (((uint64_t)hi[result_reg][v] << 32) | lo[result_reg][v]);
-                else static_cast<uint32_t*>(out)[e] = gave_up ? 0u : lo[result_reg][v];
+                if (elem_bytes == 8) static_cast<uint64_t*>(out)[e] = gave_up ? 0ull : (((uint64_t)hi[result_reg][v] << 32) | lo(result_reg, v));
+                else static_cast<uint32_t*>(out)[e] = gave_up ? 0u : lo(result_reg, v);
             }
         }
     }
+#undef lo
     if (fault != ERR_NONE) atomicMax(err, fault);
 }
 
@@ -253,9 +263,9 @@ static uint32_t operand_mask(uint32_t op) {
     switch (op) {
     case CATENA_MAP_HALT: case CATENA_MAP_JMP: return 0;
     case CATENA_MAP_JZ: case CATENA_MAP_ASSERT: return 1;
-    case CATENA_MAP_MOV: case CATENA_MAP_BOOL_NOT: case CATENA_MAP_U64_TO_F32: case CATENA_MAP_U32_NOT: case CATENA_MAP_U32_TO_F32:
-    case CATENA_MAP_F32_NEG: case CATENA_MAP_F32_ROUND_TO_U32: return 1 | 8;
-    case CATENA_MAP_SELECT: case CATENA_MAP_F32_FMA: return 1 | 2 | 4 | 8;
+    case CATENA_MAP_MOV: case CATENA_MAP_MOV32: case CATENA_MAP_BOOL_NOT: case CATENA_MAP_U64_TO_F32: case CATENA_MAP_U32_NOT:
+    case CATENA_MAP_U32_TO_F32: case CATENA_MAP_F32_NEG: case CATENA_MAP_F32_ROUND_TO_U32: return 1 | 8;
+    case CATENA_MAP_SELECT: case CATENA_MAP_SELECT32: case CATENA_MAP_F32_FMA: return 1 | 2 | 4 | 8;
     case CATENA_MAP_LOAD_U64: case CATENA_MAP_LOAD_F32: return 1 | 8;      // b is a buffer number
     default: return op < CATENA_MAP_OP_COUNT ? (1 | 2 | 8) : 0xFF;
     }
@@ -363,26 +373,43 @@ catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, ui
     }
     if (e == cudaSuccess) {
         const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
-        const int lanes = straight && n_regs <= 128 ? 4 : 1;
-        uint64_t blocks = ceil_div_u64(len, 256ull * lanes);
-        if (blocks > (uint64_t)sms * 8) blocks = (uint64_t)sms * 8;
+        // geometry: the low halves of the register file take n_regs x lanes x threads x 4 bytes of shared memory per CTA
+        const size_t smem_limit = 200 * 1024, staged = by_param ? 0 : code_bytes;
+        int lanes = straight && n_regs <= 128 ? 4 : 1, threads = 256;
+        if ((size_t)n_regs * lanes * threads * 4 + staged > smem_limit) lanes = 1;
+        if ((size_t)n_regs * lanes * threads * 4 + staged > smem_limit) threads = 128;
+        const size_t smem = (size_t)n_regs * lanes * threads * 4 + staged;
+        uint64_t per_sm = (227ull * 1024) / (smem + 1024);
+        per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+        uint64_t blocks = ceil_div_u64(len, (uint64_t)threads * lanes);
+        if (blocks > (uint64_t)sms * per_sm) blocks = (uint64_t)sms * per_sm;
         const uint4* dcode = static_cast<const uint4*>(scratch);
         const uint64_t* dinit = scratch ? reinterpret_cast<const uint64_t*>(static_cast<uint8_t*>(scratch) + code_bytes) : nullptr;
-#define CATENA_MAP_LAUNCH(R, V, P)                                                                                                  \
-    mapvm::map_program_kernel<R, V, P><<<(unsigned)blocks, 256, (P) ? 0 : code_bytes, stream>>>(                                    \
-        prm, dcode, n_insn, dinit, n_init, n_regs, index_reg, result_reg, bufs, result, elem_bytes, len, st->err)
+#define CATENA_MAP_LAUNCH(R, V, P, TT)                                                                                                 \
+    do {                                                                                                                            \
+        static thread_local size_t attr_[kMaxDevices] = {0};                                                                        \
+        if (smem > 48 * 1024 && attr_[tls().device] < smem) {                                                                       \
+            e = cudaFuncSetAttribute(mapvm::map_program_kernel<R, V, P, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e == cudaSuccess) attr_[tls().device] = smem;                                                                       \
+        }                                                                                                                           \
+        if (e == cudaSuccess)                                                                                                       \
+            mapvm::map_program_kernel<R, V, P, TT><<<(unsigned)blocks, TT, smem, stream>>>(                                         \
+                prm, dcode, n_insn, dinit, n_init, n_regs, index_reg, result_reg, bufs, result, elem_bytes, len, st->err);          \
+    } while (0)
 #define CATENA_MAP_PICK(R)                                                   \
     do {                                                                     \
-        if (lanes == 4 && by_param) CATENA_MAP_LAUNCH(R, 4, true);           \
-        else if (lanes == 4) CATENA_MAP_LAUNCH(R, 4, false);                 \
-        else if (by_param) CATENA_MAP_LAUNCH(R, 1, true);                    \
-        else CATENA_MAP_LAUNCH(R, 1, false);                                 \
+        if (lanes == 4 && by_param) CATENA_MAP_LAUNCH(R, 4, true, 256);      \
+        else if (lanes == 4) CATENA_MAP_LAUNCH(R, 4, false, 256);            \
+        else if (by_param) CATENA_MAP_LAUNCH(R, 1, true, 256);               \
+        else CATENA_MAP_LAUNCH(R, 1, false, 256);                            \
     } while (0)
         if (n_regs <= 32) CATENA_MAP_PICK(32);
         else if (n_regs <= 64) CATENA_MAP_PICK(64);
         else if (n_regs <= 128) CATENA_MAP_PICK(128);
-        else if (by_param) CATENA_MAP_LAUNCH(256, 1, true);
-        else CATENA_MAP_LAUNCH(256, 1, false);
+        else if (threads == 256 && by_param) CATENA_MAP_LAUNCH(256, 1, true, 256);
+        else if (threads == 256) CATENA_MAP_LAUNCH(256, 1, false, 256);
+        else if (by_param) CATENA_MAP_LAUNCH(256, 1, true, 128);
+        else CATENA_MAP_LAUNCH(256, 1, false, 128);
 #undef CATENA_MAP_PICK
 #undef CATENA_MAP_LAUNCH
         count_launch();

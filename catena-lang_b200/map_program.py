@@ -31,7 +31,7 @@ _OPS = ["HALT", "MOV", "JMP", "JZ", "ASSERT", "SELECT", "BOOL_NOT", "BOOL_AND", 
         "U32_ADD", "U32_SUB", "U32_MUL", "U32_AND", "U32_OR", "U32_XOR", "U32_NOT", "U32_SHL", "U32_SHR",
         "U32_EQ", "U32_NE", "U32_LT", "U32_LTE", "U32_GT", "U32_GTE", "U32_TO_F32",
         "F32_ADD", "F32_SUB", "F32_MUL", "F32_DIV", "F32_NEG", "F32_FMA", "F32_EQ", "F32_NE", "F32_LT", "F32_LTE", "F32_GT", "F32_GTE",
-        "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32"]
+        "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32", "MOV32", "SELECT32"]
 OP = {name: i for i, name in enumerate(_OPS)}
 
 # primitive -> opcode, for the primitives that are one instruction over their runtime inputs
@@ -45,7 +45,7 @@ _DIRECT = {
     "f32.add": "F32_ADD", "f32.sub": "F32_SUB", "f32.mul": "F32_MUL", "f32.div": "F32_DIV", "f32.neg": "F32_NEG", "f32.fma": "F32_FMA",
     "f32.eq": "F32_EQ", "f32.ne": "F32_NE", "f32.lt": "F32_LT", "f32.lte": "F32_LTE", "f32.gt": "F32_GT", "f32.gte": "F32_GTE",
     "f32.round-to-u32": "F32_ROUND_TO_U32",
-    "f32.select": "SELECT", "u32.select": "SELECT", "u64.select": "SELECT", "bool.select": "SELECT",
+    "f32.select": "SELECT32", "u32.select": "SELECT32", "u64.select": "SELECT", "bool.select": "SELECT32",
 }
 # primitives whose single runtime output is their single runtime input (bitcasts included: registers hold bit patterns)
 _ALIASES = {"bool.id", ":.forget", "u64.name", "ix.to-u64", "u32.bitcast-f32", "f32.bitcast-u32", ":.ty"}
@@ -53,6 +53,11 @@ _PRESETS = {"bool.t": 1, "bool.f": 0, "u64.zero": 0, "u64.one": 1, "u32.one": 1,
 _ELEM = {"ptr<f32>": ("LOAD_F32", 4), "ptr<u64>": ("LOAD_U64", 8)}
 
 MAX_REGS, MAX_INSNS, MAX_BUFFERS = 256, 2048, 16
+
+
+def _mov(lowered):
+    """bool / u32 / f32 values live in the low half of a register: their moves leave the high half alone"""
+    return "MOV32" if lowered in ("f32", "u32", "bool") else "MOV"
 
 
 class Insn(C.Structure):
@@ -253,7 +258,7 @@ class _Builder:
             src = scratch[o.name]
             if isinstance(src, _Buffer):
                 raise Unsupported("bool.ifc that chooses between buffers")
-            self.emit("MOV", dst=d, a=src)
+            self.emit(_mov(o.lowered), dst=d, a=src)
 
     def reduce(self, env, a, ins):
         comps = self.components(a.input_sizes, ins, "reducec")
@@ -266,8 +271,8 @@ class _Builder:
         if len(zero) != len(a.outputs) or not a.outputs or any(isinstance(z, _Buffer) for z in zero):
             raise Unsupported("reducec: the zero input must match a scalar accumulator")
         acc = [self.fresh() for _ in zero]
-        for d, z in zip(acc, zero):
-            self.emit("MOV", dst=d, a=z)
+        for d, z, o in zip(acc, zero, a.outputs):
+            self.emit(_mov(o.lowered), dst=d, a=z)
         counter, more = self.fresh(), self.fresh()
         self.emit("MOV", dst=counter, a=self.const(0))
         top = self.emit("U64_LT", dst=more, a=counter, b=count)
@@ -278,7 +283,7 @@ class _Builder:
         self.apply(scratch, get_sym, list(get_env) + [counter], slots)
         self.apply(scratch, add_sym, list(add_env) + acc + [scratch[s.name] for s in slots], nexts)
         for d, x in zip(acc, nexts):
-            self.emit("MOV", dst=d, a=scratch[x.name])
+            self.emit(_mov(x.lowered), dst=d, a=scratch[x.name])
         self.emit("U64_ADD", dst=counter, a=counter, b=self.const(1))
         self.emit("JMP", target=top)
         self.code[leave].target = len(self.code)
@@ -374,9 +379,9 @@ class _Builder:
         return False
 
 
-_READS_B = {OP[n] for n in _OPS if n not in ("HALT", "MOV", "JMP", "JZ", "ASSERT", "BOOL_NOT", "U64_TO_F32", "U32_NOT", "U32_TO_F32", "F32_NEG",
-                                              "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32")}
-_READS_C = {OP["SELECT"], OP["F32_FMA"]}
+_READS_B = {OP[n] for n in _OPS if n not in ("HALT", "MOV", "MOV32", "JMP", "JZ", "ASSERT", "BOOL_NOT", "U64_TO_F32", "U32_NOT", "U32_TO_F32",
+                                              "F32_NEG", "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32")}
+_READS_C = {OP["SELECT"], OP["SELECT32"], OP["F32_FMA"]}
 _NO_WRITE = {OP["HALT"], OP["JMP"], OP["JZ"], OP["ASSERT"]}
 
 

@@ -224,6 +224,7 @@ enum catena_b200_map_op {
     CATENA_MAP_F32_EQ, CATENA_MAP_F32_NE, CATENA_MAP_F32_LT, CATENA_MAP_F32_LTE, CATENA_MAP_F32_GT, CATENA_MAP_F32_GTE,
     CATENA_MAP_F32_ROUND_TO_U32,
     CATENA_MAP_LOAD_U64, CATENA_MAP_LOAD_F32,   /* `ix`: dst = buffers[b][register a]; b is a buffer number */
+    CATENA_MAP_MOV32, CATENA_MAP_SELECT32,      /* MOV / SELECT of a bool, u32 or f32 value: only the low half of the register moves */
     CATENA_MAP_OP_COUNT
 };
 typedef struct {

@@ -107,19 +107,21 @@ inline int direct_op(const std::string& op) {
         {"f32.neg", CATENA_MAP_F32_NEG}, {"f32.fma", CATENA_MAP_F32_FMA}, {"f32.eq", CATENA_MAP_F32_EQ}, {"f32.ne", CATENA_MAP_F32_NE},
         {"f32.lt", CATENA_MAP_F32_LT}, {"f32.lte", CATENA_MAP_F32_LTE}, {"f32.gt", CATENA_MAP_F32_GT}, {"f32.gte", CATENA_MAP_F32_GTE},
         {"f32.round-to-u32", CATENA_MAP_F32_ROUND_TO_U32},
-        {"f32.select", CATENA_MAP_SELECT}, {"u32.select", CATENA_MAP_SELECT}, {"u64.select", CATENA_MAP_SELECT}, {"bool.select", CATENA_MAP_SELECT}};
+        {"f32.select", CATENA_MAP_SELECT32}, {"u32.select", CATENA_MAP_SELECT32}, {"u64.select", CATENA_MAP_SELECT}, {"bool.select", CATENA_MAP_SELECT32}};
     auto it = table.find(op);
     return it == table.end() ? -1 : it->second;
 }
 inline bool reads_b(int op) {
     switch (op) {
-    case CATENA_MAP_HALT: case CATENA_MAP_MOV: case CATENA_MAP_JMP: case CATENA_MAP_JZ: case CATENA_MAP_ASSERT: case CATENA_MAP_BOOL_NOT:
+    case CATENA_MAP_HALT: case CATENA_MAP_MOV: case CATENA_MAP_MOV32: case CATENA_MAP_JMP: case CATENA_MAP_JZ: case CATENA_MAP_ASSERT: case CATENA_MAP_BOOL_NOT:
     case CATENA_MAP_U64_TO_F32: case CATENA_MAP_U32_NOT: case CATENA_MAP_U32_TO_F32: case CATENA_MAP_F32_NEG: case CATENA_MAP_F32_ROUND_TO_U32:
     case CATENA_MAP_LOAD_U64: case CATENA_MAP_LOAD_F32: return false;
     default: return true;
     }
 }
-inline bool reads_c(int op) { return op == CATENA_MAP_SELECT || op == CATENA_MAP_F32_FMA; }
+inline bool reads_c(int op) { return op == CATENA_MAP_SELECT || op == CATENA_MAP_SELECT32 || op == CATENA_MAP_F32_FMA; }
+// bool / u32 / f32 values live in the low half of a register: their moves leave the high half alone
+inline int mov_for(const std::string& lowered) { return (lowered == "f32" || lowered == "u32" || lowered == "bool") ? CATENA_MAP_MOV32 : CATENA_MAP_MOV; }
 inline bool writes(int op) { return op != CATENA_MAP_HALT && op != CATENA_MAP_JMP && op != CATENA_MAP_JZ && op != CATENA_MAP_ASSERT; }
 
 class Builder {
@@ -276,9 +278,9 @@ private:
             const Sym& get_fn = single_fn(c[4]);
             const uint32_t count = single_reg(c[5]);
             std::vector<Sym> acc;
-            for (const Sym& z : c[0]) {
+            for (size_t k = 0; k < c[0].size(); ++k) {
                 const uint32_t d = fresh();
-                emit(CATENA_MAP_MOV, d, reg_of(z, "reducec"));
+                emit(mov_for(a.outputs[k].lowered), d, reg_of(c[0][k], "reducec"));
                 acc.push_back(Sym::r(d));
             }
             const uint32_t counter = fresh(), more = fresh();
@@ -298,7 +300,7 @@ private:
             ai.insert(ai.end(), acc.begin(), acc.end());
             for (const Operand& s : slots) ai.push_back(scratch.at(s.name));
             apply(scratch, add_fn, ai, nexts);
-            for (size_t k = 0; k < nexts.size(); ++k) emit(CATENA_MAP_MOV, acc[k].reg, reg_of(scratch.at(nexts[k].name), "reducec"));
+            for (size_t k = 0; k < nexts.size(); ++k) emit(mov_for(nexts[k].lowered), acc[k].reg, reg_of(scratch.at(nexts[k].name), "reducec"));
             emit(CATENA_MAP_U64_ADD, counter, counter, constant(1));
             emit(CATENA_MAP_JMP, 0, 0, 0, 0, (uint32_t)top);
             code[leave].target = (uint32_t)code.size();
@@ -314,7 +316,7 @@ private:
         std::vector<Sym> inputs = env_values;
         inputs.insert(inputs.end(), argument.begin(), argument.end());
         apply(scratch, single_fn(fn_values), inputs, outs);
-        for (size_t k = 0; k < outs.size(); ++k) emit(CATENA_MAP_MOV, dst[k], reg_of(scratch.at(outs[k].name), "bool.ifc"));
+        for (size_t k = 0; k < outs.size(); ++k) emit(mov_for(outs[k].lowered), dst[k], reg_of(scratch.at(outs[k].name), "bool.ifc"));
     }
 
     bool const_value(uint32_t reg, uint64_t* v) const {

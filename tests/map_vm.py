@@ -51,14 +51,16 @@ def run(program, env, length, buffers_host):
                 if op == "HALT":
                     break
                 elif op == "MOV": v = x
+                elif op == "MOV32": v = (r[dst] & ~M32) | (x & M32)
                 elif op == "JMP": pc = target; continue
                 elif op == "JZ":
-                    if x == 0: pc = target
+                    if x & M32 == 0: pc = target
                     continue
                 elif op == "ASSERT":
-                    if x == 0: raise Fault("assert")
+                    if x & M32 == 0: raise Fault("assert")
                     continue
-                elif op == "SELECT": v = y if x else r[c]
+                elif op == "SELECT": v = y if x & M32 else r[c]
+                elif op == "SELECT32": v = (r[dst] & ~M32) | ((y if x & M32 else r[c]) & M32)
                 elif op == "BOOL_NOT": v = 0 if x else 1
                 elif op == "BOOL_AND": v = 1 if (x and y) else 0
                 elif op == "BOOL_OR": v = 1 if (x or y) else 0

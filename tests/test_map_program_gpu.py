@@ -146,3 +146,44 @@ def test_malformed_programs_are_refused_before_the_launch():
     # an endless loop ends at the budget of backward jumps and is reported; the library stays usable
     assert call([Insn(OP["JMP"], 0, 0, 0, 0, 0, 0), halt], length=1) == cb.E_ASSERT
     assert call([halt]) == cb.OK
+
+
+@pytest.mark.parametrize("n_insn,n_regs", [(300, 8), (300, 70), (240, 250), (150, 140), (2000, 40)])
+def test_every_kernel_geometry_agrees_with_the_cpu_interpreter(n_insn, n_regs):
+    """Programs built by hand so that every launch shape is taken: programs carried in the kernel parameters and programs
+    staged in shared memory (more than 192 instructions), four lanes per thread and one (more than 128 registers), 256
+    threads per CTA and 128 (a register file that would not fit otherwise)."""
+    from catena_lang_b200.map_program import MapProgram
+    index = 3
+    presets = [("const", 0x9E3779B97F4A7C15), ("const", 7), ("env", 0)]
+    # well typed, as the compiler's programs are: even registers hold u64 values, odd ones bool / u32 values
+    wide_ops, narrow_ops = ["U64_ADD", "U64_MUL", "U64_SUB", "MOV", "SELECT"], ["U64_LT", "U32_XOR", "U32_ADD", "U32_MUL", "MOV32", "U64_GTE"]
+    rng = np.random.default_rng(n_insn * 1000 + n_regs)
+    code, wide, narrow = [], [0, 1, 2, index], []
+    for k in range(n_insn - 2):
+        slot = 4 + k % (n_regs - 4)
+        if slot % 2 == 0:
+            op = wide_ops[(k // 2) % len(wide_ops)]
+            if op == "SELECT" and not narrow:
+                op = "U64_ADD"
+            a = int(rng.choice(narrow)) if op == "SELECT" else int(rng.choice(wide))
+            code.append(Insn(OP[op], slot, a, int(rng.choice(wide)), int(rng.choice(wide)), 0, 0))
+            if slot not in wide:
+                wide.append(slot)
+        else:
+            op = narrow_ops[(k // 2) % len(narrow_ops)]
+            if not narrow:
+                op = "U64_LT"
+            src = wide if op.startswith("U64") else narrow
+            code.append(Insn(OP[op], slot, int(rng.choice(src)), int(rng.choice(src)), 0, 0, 0))
+            if slot not in narrow:
+                narrow.append(slot)
+    last = max(w for w in wide if w >= 4)
+    code.append(Insn(OP["U64_ADD"], last, last, index, 0, 0, 0))            # every element differs
+    code.append(Insn(OP["HALT"], 0, 0, 0, 0, 0, 0))
+    prog = MapProgram("by-hand", code, presets, n_regs, index, code[-2].dst, ["u64"], 8)
+    length = 3000
+    out = prog.launch(length, [123456789])
+    got = cb.download(out, np.uint64)
+    cb.free(out)
+    assert np.array_equal(got, map_vm.run(prog, [123456789], length, []))
