@@ -26,6 +26,19 @@ pub const CATENA_E_TIMEOUT: catena_status_t = 5;
 pub const CATENA_E_TOO_LARGE: catena_status_t = 6;
 pub const CATENA_E_UNSUPPORTED: catena_status_t = 7;
 
+/// One instruction of a register program for the generic map kernel (`enum catena_b200_map_op` numbers the opcodes).
+#[repr(C)]
+#[derive(Clone, Copy, Debug, Default)]
+pub struct catena_b200_map_insn_t {
+    pub op: u16,
+    pub dst: u16,
+    pub a: u16,
+    pub b: u16,
+    pub c: u16,
+    pub reserved: u16,
+    pub target: u32,
+}
+
 extern "C" {
     // runtime
     pub fn catena_b200_init(device: c_int) -> catena_status_t;
@@ -90,6 +103,10 @@ extern "C" {
                                                    batch: u64, hq: u64, hkv: u64, d: u64, kv_len: u64, unit0: u64, unit1: u64,
                                                    peer_o: *const *mut c_void, n_peers: u32) -> catena_status_t;
     pub fn catena_b200_check_device_errors() -> catena_status_t;
+    // generic map: out[i] = producer(env.., i) for a producer compiled to a register program (include/catena_b200.h)
+    pub fn catena_b200_map_program_s(code: *const catena_b200_map_insn_t, n_insn: u32, init: *const u64, n_init: u32, n_regs: u32,
+                                     index_reg: u32, result_reg: u32, buffers: *const catena_mem_t, n_buffers: u32,
+                                     elem_bytes: u32, len: u64, out: *mut catena_mem_t) -> catena_status_t;
     pub fn catena_b200_sum_f32_noalloc(input: *const c_void, n: u64, out: *mut c_void) -> catena_status_t;
     // Llama-style block (device pointers throughout)
     pub fn catena_b200_llama_workspace_bytes(blk: *const catena_llama_block_t, tokens: u64) -> u64;
