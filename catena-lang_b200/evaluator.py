@@ -215,12 +215,15 @@ def is_primitive(op):
 class Evaluator:
     """Evaluates functions of a module map {symbol or source name -> GpuModule}."""
 
-    def __init__(self, modules, materialize=None):
+    def __init__(self, modules, materialize=None, reduce=None):
         """`materialize(assignment, length, environment values, function symbol) -> buffer` runs a `materializec` (a kernel
-        launch); without it such an assignment is refused."""
+        launch); without it such an assignment is refused.  `reduce(assignment, input values) -> accumulator values` runs a
+        `reducec` one of whose inputs is a device buffer (the host cannot read it); without it such a fold fails when its
+        getter dereferences the buffer."""
         from .lowering import module_map
         self.by_name = module_map(modules)
         self.materialize = materialize
+        self.reduce = reduce
 
     # ---- one function ----
     def call(self, name, args):
@@ -284,6 +287,8 @@ class Evaluator:
         elif a.op == "eval":                                                 # gpu.rs:986-991
             *args, fn_sym = ins
             self._apply(env, fn_sym, args, a.outputs)
+        elif a.op == "reducec" and self.reduce is not None and any(isinstance(x, DeviceMem) for x in ins):
+            self._bind(env, a.outputs, self.reduce(a, ins))
         elif a.op == "reducec":                                              # ops/reducec.rs:34-133
             comps = self._components(a.input_sizes, ins, "reducec")
             if len(comps) != 6:

@@ -24,6 +24,9 @@ recognises the shapes the stdlib lowers to:
   * any other `materializec` whose producer is scalar code over its environment and index
     (catena-lang/examples/materializec.hex, tests/cases/materialize/basic.hex) -> the generic map kernel, which
     interprets the producer as a register program (map_program.py); the code around it runs on the host
+  * any other `reducec` whose closures read device buffers                   -> the same kernel: the getter's values are
+    materialised and folded by a prebuilt fold when `add` is one (`u64.add-env`, `f32.add-env`, `f32.max-env`), else the
+    reference's sequential loop runs as a register program on one device thread
 Anything else is reported as unsupported (an allocation inside a producer, a buffer chosen at run time).
 
 The Rust front end that produces the IR is not part of this build, so fixtures for the tests are
@@ -179,6 +182,37 @@ def map_program_for(assign, modules):
     return compile_producer(modules or {}, fn.name, env_vars, assign.outputs[0].lowered[4:-1])
 
 
+# `add` closures whose fold a prebuilt kernel computes: (accumulator type, fold kind).  With one of them a generic fold runs in
+# two stages — the getter's values materialised by the generic map kernel, then the prebuilt fold over them.
+_STAGED_ADDS = {"u64.add-env": ("u64", "sum_u64"), "f32.add-env": ("f32", "sum_f32"), "f32.max-env": ("f32", "max_f32")}
+
+
+@dataclass
+class FoldPlan:
+    """How a `reducec` over device buffers that matches no fold kernel runs (map_program.py).  `sequential`: one register
+    program per accumulator component, the reference's own loop run by one device thread (bit-exact for every `add`).
+    `staged`: (getter program, its environment variables, fold kind) when `add` is a prebuilt fold's."""
+    sequential: list
+    staged: Optional[tuple] = None
+
+
+def fold_plan_for(assign, modules):
+    from .map_program import compile_fold, compile_getter
+    outs = [o for o in assign.outputs if o.lowered != "erased"]
+    if assign.op != "reducec" or not outs:
+        raise Unsupported("not a reducec")
+    plan = FoldPlan([compile_fold(modules or {}, assign, k) for k in range(len(outs))])
+    if len(outs) == 1:
+        for add, (lowered, kind) in _STAGED_ADDS.items():
+            if add in _fn_symbols(assign) and outs[0].lowered == lowered:
+                try:
+                    program, env_vars = compile_getter(modules or {}, assign)
+                    plan.staged = (program, env_vars, kind)
+                except Unsupported:
+                    pass
+    return plan
+
+
 def classify(assign, modules=None, _seen=frozenset()):
     """One assignment -> kernel family, 'scalar' or None.  `modules` maps source names (and generated symbols) to the
     lowered modules of the program, so that calls and closure symbols can be looked through."""
@@ -190,6 +224,12 @@ def classify(assign, modules=None, _seen=frozenset()):
         # a fold whose closures are scalar functions over scalar environments runs on the host, as in the reference
         if fns and not _touches_memory(assign) and all(_scalar_function(f, modules, _seen) for f in fns):
             return "scalar"
+        if modules is not None:
+            try:
+                fold_plan_for(assign, modules)
+                return "fold_generic"
+            except Unsupported:
+                return None
         return None
     if assign.op in ("materializec", "gpu.materialize"):
         fns = _fn_symbols(assign)
@@ -254,12 +294,22 @@ def select(module, symbol_for=None, modules=None):
             kinds.append(k)
     symbol = symbol_for(module.source_name) if module.source_name else module.name
     ops = [a.op for a in module.entry.assignments]
-    if kinds and all(k == "map_generic" for k in kinds):
-        # host code around one or more generic map kernels: the host part may cast and pass buffers on, not read them
+    generic = ("map_generic", "fold_generic")
+    if any(k in generic for k in kinds) and not all(k in generic for k in kinds) and modules is not None:
+        # a module is one of the recognised shapes, or everything in it runs generically: the recognised maps and folds it
+        # also holds must compile to register programs too (their producers' modules have to be there)
         for a in module.entry.assignments:
-            if a.op != "materializec" and _touches_memory(a) and not a.op.startswith(("mem.cast.", "buf.")) and not a.call_symbol:
+            if a.op == "materializec":
+                map_program_for(a, modules)
+            elif a.op == "reducec" and _touches_memory(a):
+                fold_plan_for(a, modules)
+        kinds = [k if k in generic else "map_generic" for k in kinds]
+    if kinds and all(k in generic for k in kinds):
+        # host code around generic map / fold kernels: the host part may cast and pass buffers on, not read them
+        for a in module.entry.assignments:
+            if a.op not in ("materializec", "reducec") and _touches_memory(a) and not a.op.startswith(("mem.cast.", "buf.")) and not a.call_symbol:
                 raise Unsupported(f"{module.name}: host code reads a device buffer (`{a.op}`)")
-        return KernelPlan("host_with_map_kernels", symbol, ["producers interpreted by the generic map kernel; the code around them runs on the host"])
+        return KernelPlan("host_with_map_kernels", symbol, ["producers and folds interpreted by the generic map kernel; the code around them runs on the host"])
     if not kinds:
         if any(_touches_memory(a) for a in module.entry.assignments):
             # scalar code that reads a buffer: the host cannot dereference device memory, so only the shape with a

@@ -422,16 +422,12 @@ def _reuse_registers(code, n_init, index_reg, result_reg):
     return out, top, mapping.get(result_reg, result_reg)
 
 
-def compile_producer(modules, producer, env_vars, elem_lowered):
-    """Register program for `out[i] = producer(env_vars..., i)`.
-
-    `env_vars`: the runtime values of the materializec's environment component as `lowering.GpuVar`s (their `lowered`
-    types decide how a launch binds them); `elem_lowered`: element type of the buffer produced ('u64', 'f32', 'u32',
-    'bool').  Raises `lowering.Unsupported` for a producer a map kernel cannot run (an allocation inside it, a buffer
-    chosen at run time, too many registers or instructions)."""
-    elem_bytes = {"u64": 8, "f32": 4, "u32": 4}.get(elem_lowered)
+def _compile(modules, name, env_vars, elem_lowered, body):
+    """Shared driver: binds `env_vars` (GpuVars) to preset registers / buffer slots, lets `body(builder, args, index)` emit
+    the code and return the result register, finishes with HALT, folds the two passes and the register reuse."""
+    elem_bytes = {"u64": 8, "f32": 4, "u32": 4, "bool": 4}.get(elem_lowered)
     if elem_bytes is None:
-        raise Unsupported(f"materializec of `{elem_lowered}` elements")
+        raise Unsupported(f"a buffer of `{elem_lowered}` elements")
     env_kinds, buffer_slot = [], {}
     for position, v in enumerate(env_vars):
         if v.lowered in ("f32", "u32", "u64", "bool"):
@@ -452,11 +448,8 @@ def compile_producer(modules, producer, env_vars, elem_lowered):
             else:
                 args.append(builder.preset(("env", position)))
         index = builder.fresh()
-        result = GpuVar("value", elem_lowered)
-        scratch = {}
-        builder.apply(scratch, FnSymbol(producer), args + [index], [result])
+        got = body(builder, args, index)
         builder.emit("HALT")
-        got = scratch[result.name]
         if isinstance(got, _Buffer):
             raise Unsupported("the producer returns a buffer")
         return index, got
@@ -479,4 +472,66 @@ def compile_producer(modules, producer, env_vars, elem_lowered):
     # ("buflen", slot, bytes) presets name buffer slots; launches index the environment: translate
     slot_position = {slot: position for position, slot in buffer_slot.items()}
     presets = [("buflen", slot_position[w[1]], w[2]) if w[0] == "buflen" else w for w in presets]
-    return MapProgram(producer, code, presets, n_regs, index, result, env_kinds, elem_bytes)
+    return MapProgram(name, code, presets, n_regs, index, result, env_kinds, elem_bytes)
+
+
+def compile_producer(modules, producer, env_vars, elem_lowered):
+    """Register program for `out[i] = producer(env_vars..., i)`.
+
+    `env_vars`: the runtime values of the materializec's environment component as `lowering.GpuVar`s (their `lowered`
+    types decide how a launch binds them); `elem_lowered`: element type of the buffer produced ('u64', 'f32', 'u32').
+    Raises `lowering.Unsupported` for a producer a map kernel cannot run (an allocation inside it, a buffer chosen at run
+    time, too many registers or instructions)."""
+    if elem_lowered == "bool":
+        raise Unsupported("materializec of `bool` elements")
+
+    def body(builder, args, index):
+        result = GpuVar("value", elem_lowered)
+        scratch = {}
+        builder.apply(scratch, FnSymbol(producer), args + [index], [result])
+        return scratch[result.name]
+
+    return _compile(modules, producer, env_vars, elem_lowered, body)
+
+
+def fold_inputs(assign):
+    """The runtime inputs of a `reducec` assignment, in order: what a launch of its fold programs binds."""
+    return [v for v in assign.inputs if isinstance(v, GpuVar) and v.lowered != "erased"]
+
+
+def compile_fold(modules, assign, component):
+    """Register program whose ONE element is component `component` of a `reducec`'s result: the sequential left fold
+    `acc = zero; for i < n: acc = add(add_env, acc, get(get_env, i))` (catena-lang/src/codegen/ops/reducec.rs:34-133) as a loop,
+    run by one thread — the reference runs the same loop on one host core.  For folds whose closures read device buffers
+    and match no prebuilt fold kernel.  Launch with length 1 and the values of `fold_inputs(assign)`."""
+    outs = [o for o in assign.outputs if o.lowered != "erased"]
+    if not 0 <= component < len(outs):
+        raise Unsupported("reducec: no such accumulator component")
+    env_vars = fold_inputs(assign)
+
+    def body(builder, args, index):
+        env, k = {}, 0
+        for v in assign.inputs:
+            if isinstance(v, GpuVar) and v.lowered != "erased":
+                env[v.name] = args[k]
+                k += 1
+        builder.assign(env, assign)
+        return env[outs[component].name]
+
+    return _compile(modules, f"reducec[{component}]", env_vars, outs[component].lowered, body)
+
+
+def compile_getter(modules, assign):
+    """Register program for out[i] = get(get_env..., i) of a `reducec` with ONE accumulator component: the first stage of a
+    fold whose `add` is a prebuilt kernel's (the second stage folds the materialised values).  Launch with the values of the
+    runtime variables of the getter's environment component."""
+    if assign.input_sizes is None or len(assign.input_sizes) != 6:
+        raise Unsupported("reducec expects 6 input components")
+    outs = [o for o in assign.outputs if o.lowered != "erased"]
+    if len(outs) != 1:
+        raise Unsupported("a two-stage fold has one accumulator component")
+    sizes, items = assign.input_sizes, list(assign.inputs)
+    begin = sum(sizes[:3])
+    get_env = [v for v in items[begin:begin + sizes[3]] if isinstance(v, GpuVar) and v.lowered != "erased"]
+    [get_fn] = [v for v in items[begin + sizes[3]:begin + sizes[3] + sizes[4]] if isinstance(v, FnSymbol)]
+    return compile_producer(modules, get_fn.name, get_env, outs[0].lowered), get_env

@@ -242,10 +242,12 @@ class Runtime:
             if plan.kernel == "host_with_map_kernels":
                 # the producers' register programs are built now, so that a producer the map kernel cannot run is an
                 # InitError and `exec` only binds the environment and launches
-                from .lowering import map_program_for
+                from .lowering import _touches_memory, fold_plan_for, map_program_for
                 for a in m.entry.assignments:
                     if a.op == "materializec":
                         rt._map_programs[id(a)] = map_program_for(a, mm)
+                    elif a.op == "reducec" and _touches_memory(a):
+                        rt._map_programs[id(a)] = fold_plan_for(a, mm)
                 rt.signatures[m.source_name] = (plan.symbol, [kinds[t] for t in ins], [kinds[t] for t in outs],
                                                 (lambda args, _name=m.name: rt._map_evaluator(modules).call(_name, args)))
                 continue
@@ -317,7 +319,8 @@ class Runtime:
     def _map_evaluator(self, modules):
         """Host evaluator whose `materializec` launches the generic map kernel with the producer's register program."""
         if self._map_eval is None:
-            from .evaluator import DeviceMem, Evaluator
+            from .evaluator import DeviceMem, Evaluator, _runtime, f32_bits
+            from .lowering import FnSymbol
 
             def materialize(assign, length, env_values, fn_sym):
                 program = self._map_programs[id(assign)]
@@ -327,7 +330,45 @@ class Runtime:
                     self._map_outputs[int(raw.data)] = raw
                 return DeviceMem(raw.data, raw.len, {8: np.uint64, 4: np.float32}[program.elem_bytes])
 
-            self._map_eval = Evaluator(modules, materialize)
+            def bind(values):
+                return [(v.ptr, v.nbytes) if isinstance(v, DeviceMem) else v for v in values if v is not None and not isinstance(v, FnSymbol)]
+
+            def scalar_of(raw, lowered):
+                from . import download, free
+                value = download(raw, np.float32 if lowered == "f32" else np.uint64 if lowered == "u64" else np.uint32)[0]
+                free(raw)
+                return np.float32(value) if lowered == "f32" else int(value)
+
+            def reduce(assign, ins):
+                """A `reducec` over device buffers (see lowering.FoldPlan): staged through a prebuilt fold when `add` is one
+                and the fold is long enough to be worth two launches, else the sequential loop on one device thread."""
+                from . import CatenaMem, check, free
+                plan = self._map_programs[id(assign)]
+                outs = [o for o in assign.outputs if o.lowered != "erased"]
+                comps = Evaluator._components(None, assign.input_sizes, ins, "reducec")
+                zero, get_env, count = comps[0], comps[3], int(_runtime(comps[5])[0])
+                if plan.staged is not None and count >= 1024:
+                    program, _, kind = plan.staged
+                    [z] = _runtime(zero)
+                    if kind != "sum_f32" or f32_bits(z) == 0:          # the prebuilt f32 sum starts from +0, like `sum-f32`
+                        raw = program.launch(count, bind(get_env))
+                        try:
+                            if kind == "sum_u64":
+                                total = C.c_uint64(0)
+                                check(self._lib.program_sum_u64_s(raw, C.byref(total)))
+                                return [(int(z) + total.value) & 0xFFFFFFFFFFFFFFFF]
+                            value = C.c_float(0)
+                            check((self._lib.program_sum_f32_s if kind == "sum_f32" else self._lib.program_max_f32_s)(raw, C.byref(value)))
+                            value = np.float32(value.value)
+                            if kind == "max_f32":                       # f32.max-env keeps the accumulator on ties (sum.hex:73-84)
+                                return [np.float32(z) if np.float32(z) >= value else value]
+                            return [value]
+                        finally:
+                            free(raw)
+                env = bind(ins)
+                return [scalar_of(p.launch(1, env), o.lowered) for p, o in zip(plan.sequential, outs)]
+
+            self._map_eval = Evaluator(modules, materialize, reduce)
         return self._map_eval
 
     def _exec_on_host(self, name, host, args, outs):

@@ -266,3 +266,47 @@ def custom_map_programs():
         A("materializec", [u("rows"), pf("a"), pf("b"), u("cols"), fn("my.matvec-at")], [pf("buf")], [1, 3, 1], [1]),
         A("buf.to-mem", [u("rows"), pf("buf")], [v("out", "mem")])])
     return silu + [silu_at, silu_map, keep, low, clamp_at, clamp_map, add_env, term_at, cell_at, matvec]
+
+
+# ---------------------------------------------------------------- folds over device buffers that match no fold kernel (user programs in
+# the reference's idiom: tests/cases/reducec/basic.hex with other closures)
+def custom_fold_programs():
+    f = lambda n: v(n, "f32")                                                # noqa: E731
+    u = lambda n: v(n, "u64")                                                # noqa: E731
+    e = lambda n: v(n, "erased")                                             # noqa: E731
+    pf = lambda n: v(n, "ptr<f32>")                                          # noqa: E731
+    pu = lambda n: v(n, "ptr<u64>")                                          # noqa: E731
+    base = custom_map_programs()                                             # nn.silu and friends, my.silu-at, f32.add-env
+    # sum over i of silu(x[i]): `add` is the stdlib's f32.add-env (a prebuilt fold), the getter is not
+    sum_silu = M("my.sum-silu", [v("m", "mem")], [f("r")], [
+        A("mem.cast.f32", [v("m", "mem")], [u("len"), pf("x")]),
+        A("const.u32.0x00000000", [], [v("zb", "u32")]), A("u32.bitcast-f32", [v("zb", "u32")], [f("zero")]), A("unit.intro", [], [e("unit")]),
+        A("reducec", [f("zero"), e("unit"), fn("f32.add-env"), pf("x"), fn("my.silu-at"), u("len")], [f("r")], [1, 1, 1, 1, 1, 1], [1])])
+    # acc = acc * 31 + x[i]: an `add` that is not associative — only the sequential loop gives the reference's value
+    horner_add = M("my.horner-add", [u("k"), u("acc"), u("value")], [u("r")], [
+        A("u64.mul", [u("acc"), u("k")], [u("t")]), A("u64.add", [u("t"), u("value")], [u("r")])])
+    u64_at = M("sum-u64-at", [pu("input"), u("i")], [u("r")], [A("ix", [u("i"), pu("input")], [u("r")])])
+    horner = M("my.horner", [v("m", "mem"), u("k")], [u("r")], [
+        A("mem.cast.u64", [v("m", "mem")], [u("len"), pu("input")]), A("const.u64.0x0000000000000007", [], [u("seed")]),
+        A("reducec", [u("seed"), u("k"), fn("my.horner-add"), pu("input"), fn("sum-u64-at"), u("len")], [u("r")], [1, 1, 1, 1, 1, 1], [1])])
+    # (sum, sum of squares) of a u64 buffer: a two-component accumulator (tests/cases/closures/progression.hex, over a buffer)
+    moments_at = M("my.moments-at", [pu("input"), u("i")], [u("value"), u("square")], [
+        A("ix", [u("i"), pu("input")], [u("value")]), A("u64.mul", [u("value"), u("value")], [u("square")])])
+    moments_add = M("my.moments-add", [u("ls"), u("lq"), u("rs"), u("rq")], [u("s"), u("q")], [
+        A("u64.add", [u("ls"), u("rs")], [u("s")]), A("u64.add", [u("lq"), u("rq")], [u("q")])])
+    moments = M("my.moments", [v("m", "mem")], [u("sum"), u("squares")], [
+        A("mem.cast.u64", [v("m", "mem")], [u("len"), pu("input")]),
+        A("const.u64.0x0000000000000000", [], [u("z0")]), A("const.u64.0x0000000000000000", [], [u("z1")]),
+        A("reducec", [u("z0"), u("z1"), fn("my.moments-add"), pu("input"), fn("my.moments-at"), u("len")], [u("sum"), u("squares")],
+          [2, 0, 1, 1, 1, 1], [2])])
+    # x[i] / sum(x): a recognised fold (f32.add-env over f32-at) next to a producer no kernel matches — the module runs generically
+    f32_at = M("f32-at", [pf("input"), u("i")], [f("r")], [A("ix", [u("i"), pf("input")], [f("r")])])
+    scale_at = M("my.scale-at", [pf("x"), f("total"), u("i")], [f("r")], [
+        A("ix", [u("i"), pf("x")], [f("xi")]), A("f32.div", [f("xi"), f("total")], [f("r")])])
+    normalize = M("my.normalize", [v("m", "mem")], [v("out", "mem")], [
+        A("mem.cast.f32", [v("m", "mem")], [u("len"), pf("x")]),
+        A("const.u32.0x00000000", [], [v("zb", "u32")]), A("u32.bitcast-f32", [v("zb", "u32")], [f("zero")]), A("unit.intro", [], [e("unit")]),
+        A("reducec", [f("zero"), e("unit"), fn("f32.add-env"), pf("x"), fn("f32-at"), u("len")], [f("total")], [1, 1, 1, 1, 1, 1], [1]),
+        A("materializec", [u("len"), pf("x"), f("total"), fn("my.scale-at")], [pf("buf")], [1, 2, 1], [1]),
+        A("buf.to-mem", [u("len"), pf("buf")], [v("out", "mem")])])
+    return base + [sum_silu, horner_add, u64_at, horner, moments_at, moments_add, moments, f32_at, scale_at, normalize]

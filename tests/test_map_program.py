@@ -100,3 +100,37 @@ def test_programs_stay_within_the_kernel_limits():
         for c in prog.code:
             if c.op not in (OP["HALT"], OP["JMP"], OP["JZ"], OP["ASSERT"]):
                 assert n_init <= c.dst < prog.n_regs and c.dst != prog.index_reg
+
+
+def test_generic_folds_compile_and_match_the_sequential_loop():
+    """A `reducec` over buffers that matches no fold kernel: the selector's plan, and its sequential register programs
+    against the loop written out in Python (the reference's left fold, catena-lang/src/codegen/ops/reducec.rs:75-131)."""
+    mods = fx.custom_fold_programs()
+    mm = modules_by_name(mods)
+    for name in ("my.sum-silu", "my.horner", "my.moments", "my.normalize"):
+        assert lo.select(mm[name], modules=mm).kernel == "host_with_map_kernels"
+    fold = lambda name: [a for a in mm[name].entry.assignments if a.op == "reducec"][0]        # noqa: E731
+    # acc = acc * k + x[i] from 7: not associative
+    plan = lo.fold_plan_for(fold("my.horner"), mm)
+    assert plan.staged is None and len(plan.sequential) == 1
+    data = np.array([3, 5, 8, 13, 2 ** 63 + 5], np.uint64)
+    # runtime inputs of the reducec in order: seed, k, input, len
+    [got] = map_vm.run(plan.sequential[0], [7, 31, (0, data.nbytes), data.size], 1, [data.view(np.uint8)])
+    want = 7
+    for x in data.tolist():
+        want = (want * 31 + x) % 2 ** 64
+    assert int(got) == want
+    # two accumulator components: one program each
+    plan = lo.fold_plan_for(fold("my.moments"), mm)
+    assert plan.staged is None and len(plan.sequential) == 2
+    got = [int(map_vm.run(p, [0, 0, (0, data.nbytes), data.size], 1, [data.view(np.uint8)])[0]) for p in plan.sequential]
+    assert got == [sum(data.tolist()) % 2 ** 64, sum(x * x for x in data.tolist()) % 2 ** 64]
+    # the stdlib's f32.add-env with another getter: staged through the prebuilt sum, and sequential = the oracle's fold
+    plan = lo.fold_plan_for(fold("my.sum-silu"), mm)
+    assert plan.staged is not None and plan.staged[2] == "sum_f32"
+    x = np.random.default_rng(8).normal(0, 2, 300).astype(np.float32)
+    [got] = map_vm.run(plan.sequential[0], [np.float32(0.0), (0, x.nbytes), x.size], 1, [x.view(np.uint8)])
+    assert int(got) == int(np.float32(orc.sum_f32(orc.map_unary("nn.silu", x))).view(np.uint32))
+    # an empty fold returns its zero
+    [got] = map_vm.run(plan.sequential[0], [np.float32(2.5), (0, 0), 0], 1, [np.zeros(0, np.uint8)])
+    assert int(got) == int(np.float32(2.5).view(np.uint32))

@@ -187,3 +187,38 @@ def test_every_kernel_geometry_agrees_with_the_cpu_interpreter(n_insn, n_regs):
     got = cb.download(out, np.uint64)
     cb.free(out)
     assert np.array_equal(got, map_vm.run(prog, [123456789], length, []))
+
+
+def test_generic_folds_through_the_runtime():
+    """`reducec` over device buffers with closures that match no fold kernel: the sequential loop on one device thread for an
+    `add` that is not associative and for a two-component accumulator; two stages (generic map + prebuilt fold) for the
+    stdlib's adds with another getter; and a module where a recognised fold sits next to a generic producer."""
+    rt = cb.Runtime.from_modules(fx.custom_fold_programs())
+    rng = np.random.default_rng(21)
+    data = rng.integers(0, 2 ** 63, 5000, dtype=np.uint64)
+    [got] = rt.exec("my.horner", [rt.mem_u64(data), 31])
+    want = 7
+    for x in data.tolist():
+        want = (want * 31 + x) % 2 ** 64
+    assert got.v == want
+    s, q = rt.exec("my.moments", [rt.mem_u64(data)])
+    assert s.v == sum(data.tolist()) % 2 ** 64 and q.v == sum(x * x for x in data.tolist()) % 2 ** 64
+    # an empty buffer: the fold's zero
+    s, q = rt.exec("my.moments", [rt.mem_u64([])])
+    assert (s.v, q.v) == (0, 0)
+    # sum of silu(x[i]): sequential below 1024 elements, staged above; both are the oracle's sequential sum up to 65536 elements
+    for n in (300, 40_000):
+        x = rng.normal(0, 2, n).astype(np.float32)
+        [got] = rt.exec("my.sum-silu", [rt.mem_f32(x)])
+        want = np.float32(orc.sum_f32(orc.map_unary("nn.silu", x)))
+        assert np.float32(got.v).view(np.uint32) == want.view(np.uint32)
+    # x[i] / sum(x)
+    x = rng.uniform(0.5, 1.5, 3000).astype(np.float32)
+    [out] = rt.exec("my.normalize", [rt.mem_f32(x)])
+    total = np.float32(orc.sum_f32(x))
+    assert np.array_equal(out.v.to_f32_vec().view(np.uint32), (x / total).astype(np.float32).view(np.uint32))
+    # a fold longer than the loop budget of one thread is reported, not run forever
+    big = cb.Runtime.from_modules(fx.custom_fold_programs())
+    with pytest.raises(cb.ExecError) as err:
+        big.exec("my.horner", [big.mem_u64(np.zeros((1 << 22) + 10, np.uint64)), 3])
+    assert err.value.status == cb.E_ASSERT
