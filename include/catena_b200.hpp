@@ -263,15 +263,18 @@ public:
             if (plan.kernel == "host_with_map_kernels") {
                 // the producers' register programs are built now: one the map kernel cannot run is an InitError
                 auto programs = std::make_shared<std::map<const lowering::GpuAssign*, map_program::Program>>();
+                auto folds = std::make_shared<std::map<const lowering::GpuAssign*, map_program::FoldPlan>>();
                 try {
-                    for (const lowering::GpuAssign& a : m.entry.assignments)
+                    for (const lowering::GpuAssign& a : m.entry.assignments) {
                         if (a.op == "materializec") (*programs)[&a] = map_program::for_assignment(*shared, a);
+                        if (a.op == "reducec" && lowering::classify(a) != "scalar") (*folds)[&a] = map_program::fold_plan_for(*shared, a);
+                    }
                 } catch (const lowering::Unsupported& e) {
                     throw InitError("program '" + m.source_name + "': " + e.what());
                 }
                 const std::string name = m.name;
                 std::vector<K> out_kinds = outs;
-                table_[m.source_name] = Signature{plan.symbol, ins, outs, [shared, programs, name, out_kinds](std::vector<Value>& a, std::vector<Value>& o) {
+                table_[m.source_name] = Signature{plan.symbol, ins, outs, [shared, programs, folds, name, out_kinds](std::vector<Value>& a, std::vector<Value>& o) {
                     // buffers materialised during this call; what the results do not take over is freed at the end
                     std::map<void*, catena_mem_t> made;
                     catena_status_t failed = CATENA_OK;
@@ -290,6 +293,53 @@ public:
                         p.device = true;
                         p.bytes = out.len;
                         return p;
+                    };
+                    auto bind_env = [](const std::vector<eval::Val>& values) {
+                        std::vector<map_program::EnvValue> bound;
+                        for (const eval::Val& v : values) {
+                            if (v.kind == eval::Val::Scalar) bound.push_back(map_program::EnvValue::scalar(v.bits));
+                            else if (v.kind == eval::Val::Ptr || v.kind == eval::Val::Mem) bound.push_back(map_program::EnvValue::mem(catena_mem_t{v.ptr, v.bytes}));
+                        }
+                        return bound;
+                    };
+                    // a `reducec` over device buffers: staged through a prebuilt fold when `add` is one and the fold is long
+                    // enough to be worth two launches, else the sequential loop on one device thread
+                    ev.reduce = [&](const lowering::GpuAssign& assign, const std::vector<eval::Val>& ins) {
+                        const map_program::FoldPlan& plan = folds->at(&assign);
+                        auto fail_with = [&](catena_status_t s) { failed = s; throw eval::AssertFailed("fold program failed"); };
+                        const uint64_t count = ins.back().bits;                       // the last component is the length
+                        std::vector<eval::Val> result;
+                        if (plan.staged && count >= 1024 && (plan.kind != "sum_f32" || (uint32_t)ins[0].bits == 0)) {
+                            std::vector<eval::Val> get_env(ins.begin() + plan.get_env_begin, ins.begin() + plan.get_env_begin + plan.get_env_size);
+                            catena_mem_t values{nullptr, 0};
+                            catena_status_t s = plan.getter.launch(count, bind_env(get_env), &values);
+                            if (s != CATENA_OK) fail_with(s);
+                            if (plan.kind == "sum_u64") {
+                                uint64_t total = 0;
+                                s = program_sum_u64_s(values, &total);
+                                result.push_back(eval::Val::scalar(ins[0].bits + total));
+                            } else {
+                                float value = 0.0f;
+                                s = plan.kind == "sum_f32" ? program_sum_f32_s(values, &value) : program_max_f32_s(values, &value);
+                                const float zero = ins[0].as_f32();                   // f32.max-env keeps the accumulator on ties
+                                result.push_back(eval::Val::f32(plan.kind == "max_f32" && zero >= value ? zero : value));
+                            }
+                            catena_b200_mem_free(values);
+                            if (s != CATENA_OK) fail_with(s);
+                            return result;
+                        }
+                        const std::vector<map_program::EnvValue> env = bind_env(ins);
+                        for (const map_program::Program& p : plan.sequential) {
+                            catena_mem_t one{nullptr, 0};
+                            catena_status_t s = p.launch(1, env, &one);
+                            if (s != CATENA_OK) fail_with(s);
+                            uint64_t bits = 0;
+                            s = catena_b200_mem_download(one, &bits, p.elem_bytes);
+                            catena_b200_mem_free(one);
+                            if (s != CATENA_OK) fail_with(s);
+                            result.push_back(eval::Val::scalar(bits));
+                        }
+                        return result;
                     };
                     std::vector<eval::Val> args;
                     std::map<void*, Value*> arguments;

@@ -72,6 +72,9 @@ public:
     // Runs a `materializec` (a kernel launch): (assignment, length, values of the environment component, producer symbol) ->
     // the buffer produced (a Ptr value).  Without it such an assignment is refused (NotScalar).
     std::function<Val(const GpuAssign&, uint64_t, const std::vector<Val>&, const std::string&)> materialize;
+    // Runs a `reducec` one of whose inputs is a device buffer (the host cannot read it): (assignment, input values) -> the
+    // accumulator's values.  Without it such a fold is refused when its getter dereferences the buffer.
+    std::function<std::vector<Val>(const GpuAssign&, const std::vector<Val>&)> reduce;
 
     explicit Evaluator(const std::vector<GpuModule>& modules) {
         for (const GpuModule& m : modules) {
@@ -168,6 +171,11 @@ private:
         }
         return out;
     }
+    static bool touches_device(const std::vector<Val>& vs) {
+        for (const Val& v : vs)
+            if ((v.kind == Val::Ptr || v.kind == Val::Mem) && v.device) return true;
+        return false;
+    }
     static const Val& single_fn(const std::vector<Val>& comp) {
         const Val* f = nullptr;
         for (const Val& v : comp)
@@ -200,6 +208,8 @@ private:
             if (ins.empty() || ins.back().kind != Val::Fn) throw std::invalid_argument("eval: the last input must be a function symbol");
             std::vector<Val> args(ins.begin(), ins.end() - 1);
             apply(env, ins.back(), args, a.outputs);
+        } else if (a.op == "reducec" && reduce && touches_device(ins)) {
+            bind(env, a.outputs, reduce(a, ins));
         } else if (a.op == "reducec") {                                     // ops/reducec.rs:34-133
             auto c = components(a.input_sizes, ins, "reducec");
             if (c.size() != 6) throw std::invalid_argument("reducec expects 6 input components");

@@ -98,9 +98,11 @@ inline std::string classify(const GpuAssign& a) {
                                          {"tensor.argmax-env", "tensor.argmax-pair-at", "fold_argmax"}};
         for (auto& f : folds)
             if (has_fn(a, f[0]) && has_fn(a, f[1])) return f[2];
-        // a fold whose environments hold no buffer runs on the host (its closures are checked when it is evaluated)
+        // a fold whose environments hold no buffer runs on the host (its closures are checked when it is evaluated); any other
+        // fold over buffers goes to the generic map kernel (catena_b200_map_program.hpp: staged through a prebuilt fold when
+        // `add` is one, else the sequential loop as a register program; the caller of select() builds the programs)
         for (const Operand& o : a.inputs)
-            if (!o.is_fn && (o.lowered == "mem" || detail::starts_with(o.lowered, "ptr<"))) return "";
+            if (!o.is_fn && (o.lowered == "mem" || detail::starts_with(o.lowered, "ptr<"))) return "fold_generic";
         return "scalar";
     }
     if (a.op == "bool.ifc" || a.op == "eval") return "scalar";
@@ -143,17 +145,21 @@ inline KernelPlan select(const GpuModule& module) {
             if (kinds[i++] != w) return false;
         return true;
     };
-    bool generic_only = !kinds.empty();
-    for (const std::string& k : kinds) generic_only = generic_only && k == "map_generic";
-    if (generic_only) {
-        // host code around generic map kernels: it may cast buffers and pass them on, not read them
+    // a module is one of the recognised shapes, or — as soon as it holds a generic producer or fold — everything in it runs
+    // generically (the recognised maps and folds it also holds are compiled to register programs by the caller)
+    bool any_generic = false;
+    for (const std::string& k : kinds) any_generic = any_generic || k == "map_generic" || k == "fold_generic";
+    if (any_generic) {
+        // host code around generic map / fold kernels: it may cast buffers and pass them on, not read them
         for (const GpuAssign& a : module.entry.assignments) {
-            if (a.op == "materializec" || !a.call_symbol.empty() || detail::starts_with(a.op, "mem.cast.") || detail::starts_with(a.op, "buf.")) continue;
+            if (a.op == "materializec" || a.op == "reducec" || !a.call_symbol.empty() || detail::starts_with(a.op, "mem.cast.") || detail::starts_with(a.op, "buf.")) continue;
             for (const Operand& o : a.inputs)
                 if (!o.is_fn && (o.lowered == "mem" || detail::starts_with(o.lowered, "ptr<")))
                     throw Unsupported(module.name + ": host code reads a device buffer (`" + a.op + "`)");
         }
-        return {"host_with_map_kernels", symbol, "producers interpreted by the generic map kernel; the code around them runs on the host"};
+        for (const GpuAssign& a : module.entry.assignments)
+            if (a.op == "gpu.materialize") throw Unsupported(module.name + ": gpu.materialize with an unknown kernel");
+        return {"host_with_map_kernels", symbol, "producers and folds interpreted by the generic map kernel; the code around them runs on the host"};
     }
     if (kinds.empty()) {
         bool memory = false, cast_u64 = false, ix_zero = false;

@@ -175,6 +175,8 @@ public:
         return out;
     }
 
+    void assign_in(Env& env, const GpuAssign& a) { assign(env, a); }
+
     void apply(Env& env, const Sym& fn, const std::vector<Sym>& inputs, const std::vector<Operand>& outputs) {
         if (fn.kind != Sym::Fn) throw Unsupported("function application needs a function symbol");
         if (primitive(env, fn.fn, inputs, outputs, {})) return;
@@ -453,17 +455,17 @@ inline void reuse_registers(std::vector<catena_b200_map_insn_t>& code, uint32_t 
 
 }  // namespace detail
 
-// Register program for out[i] = producer(env_vars..., i).  `env_vars`: the runtime values of the materializec's environment
-// component (their `lowered` types decide how a launch binds them); `elem_lowered`: element type of the buffer produced.
-// Throws lowering::Unsupported for a producer a map kernel cannot run.
-inline Program compile_producer(const std::vector<GpuModule>& modules, const std::string& producer, const std::vector<Operand>& env_vars,
-                                const std::string& elem_lowered) {
-    using namespace detail;
+namespace detail {
+// Shared driver: binds `env_vars` to preset registers / buffer slots, lets body(builder, args, index) emit the code and
+// return the result, finishes with HALT, runs the two passes and the register reuse.
+template <class Body>
+inline Program compile(const std::vector<GpuModule>& modules, const std::string& name, const std::vector<Operand>& env_vars,
+                       const std::string& elem_lowered, Body body) {
     Program prog;
-    prog.producer = producer;
+    prog.producer = name;
     if (elem_lowered == "u64") prog.elem_bytes = 8;
-    else if (elem_lowered == "f32" || elem_lowered == "u32") prog.elem_bytes = 4;
-    else throw Unsupported("materializec of `" + elem_lowered + "` elements");
+    else if (elem_lowered == "f32" || elem_lowered == "u32" || elem_lowered == "bool") prog.elem_bytes = 4;
+    else throw Unsupported("a buffer of `" + elem_lowered + "` elements");
     std::vector<int> slot_of(env_vars.size(), -1);
     uint32_t n_buffers = 0;
     for (size_t k = 0; k < env_vars.size(); ++k) {
@@ -487,15 +489,8 @@ inline Program compile_producer(const std::vector<GpuModule>& modules, const std
             args.push_back(Sym::r(b.preset(p)));
         }
         index = b.fresh();
-        args.push_back(Sym::r(index));
-        Env scratch;
-        Sym fn;
-        fn.kind = Sym::Fn;
-        fn.fn = producer;
-        const std::vector<Operand> outs = {Operand::var("value", elem_lowered)};
-        b.apply(scratch, fn, args, outs);
+        result = body(b, args, index);
         b.emit(CATENA_MAP_HALT);
-        result = scratch.at("value");
         if (result.kind != Sym::Reg) throw Unsupported("the producer returns a buffer");
     };
     // pass 1 discovers the presets (constants appear while walking), pass 2 emits with the registers behind them
@@ -521,6 +516,99 @@ inline Program compile_producer(const std::vector<GpuModule>& modules, const std
                 if (slot_of[k] == (int)p.value) { p.value = k; break; }
     prog.presets = presets;
     return prog;
+}
+}  // namespace detail
+
+// Register program for out[i] = producer(env_vars..., i).  `env_vars`: the runtime values of the materializec's environment
+// component (their `lowered` types decide how a launch binds them); `elem_lowered`: element type of the buffer produced.
+// Throws lowering::Unsupported for a producer a map kernel cannot run.
+inline Program compile_producer(const std::vector<GpuModule>& modules, const std::string& producer, const std::vector<Operand>& env_vars,
+                                const std::string& elem_lowered) {
+    using namespace detail;
+    if (elem_lowered == "bool") throw Unsupported("materializec of `bool` elements");
+    return compile(modules, producer, env_vars, elem_lowered, [&](Builder& b, std::vector<Sym> args, uint32_t index) {
+        args.push_back(Sym::r(index));
+        Env scratch;
+        Sym fn;
+        fn.kind = Sym::Fn;
+        fn.fn = producer;
+        const std::vector<Operand> outs = {Operand::var("value", elem_lowered)};
+        b.apply(scratch, fn, args, outs);
+        return scratch.at("value");
+    });
+}
+
+// The runtime inputs of a `reducec` assignment, in order: what a launch of its fold programs binds.
+inline std::vector<Operand> fold_inputs(const GpuAssign& a) {
+    std::vector<Operand> out;
+    for (const Operand& o : a.inputs)
+        if (!o.is_fn && o.lowered != "erased") out.push_back(o);
+    return out;
+}
+
+// Register program whose ONE element is component `component` of a reducec's result: the sequential left fold
+// acc = zero; for i < n: acc = add(add_env, acc, get(get_env, i)) (catena-lang/src/codegen/ops/reducec.rs:34-133) as a loop run
+// by one thread — the reference runs the same loop on one host core.  Launch with length 1 and the values of fold_inputs(a).
+inline Program compile_fold(const std::vector<GpuModule>& modules, const GpuAssign& a, size_t component) {
+    using namespace detail;
+    std::vector<Operand> outs;
+    for (const Operand& o : a.outputs)
+        if (o.lowered != "erased") outs.push_back(o);
+    if (a.op != "reducec" || component >= outs.size()) throw Unsupported("reducec: no such accumulator component");
+    return compile(modules, "reducec[" + std::to_string(component) + "]", fold_inputs(a), outs[component].lowered,
+                   [&](Builder& b, std::vector<Sym> args, uint32_t) {
+                       Env env;
+                       size_t k = 0;
+                       for (const Operand& o : a.inputs)
+                           if (!o.is_fn && o.lowered != "erased") env[o.name] = args[k++];
+                       b.assign_in(env, a);
+                       return env.at(outs[component].name);
+                   });
+}
+
+// How a reducec over device buffers that matches no fold kernel runs.  `sequential`: one program per accumulator component
+// (bit-exact for every `add`).  `staged`: when `add` is a prebuilt fold's (u64.add-env, f32.add-env, f32.max-env) the getter's
+// values are materialised by `getter` (launched with the getter's environment) and folded by the prebuilt kernel `kind`.
+struct FoldPlan {
+    std::vector<Program> sequential;
+    bool staged = false;
+    Program getter;
+    size_t get_env_begin = 0, get_env_size = 0;    // the getter's environment component among the assignment's inputs
+    std::string kind;                              // "sum_u64", "sum_f32", "max_f32"
+};
+inline FoldPlan fold_plan_for(const std::vector<GpuModule>& modules, const GpuAssign& a) {
+    FoldPlan plan;
+    std::vector<Operand> outs;
+    for (const Operand& o : a.outputs)
+        if (o.lowered != "erased") outs.push_back(o);
+    if (a.op != "reducec" || outs.empty()) throw Unsupported("not a reducec");
+    for (size_t k = 0; k < outs.size(); ++k) plan.sequential.push_back(compile_fold(modules, a, k));
+    if (outs.size() == 1 && a.input_sizes.size() == 6) {
+        static const char* adds[][3] = {{"u64.add-env", "u64", "sum_u64"}, {"f32.add-env", "f32", "sum_f32"}, {"f32.max-env", "f32", "max_f32"}};
+        for (auto& ad : adds) {
+            bool has = false;
+            for (const Operand& o : a.inputs) has = has || (o.is_fn && o.name == ad[0]);
+            if (!has || outs[0].lowered != ad[1]) continue;
+            const size_t begin = a.input_sizes[0] + a.input_sizes[1] + a.input_sizes[2];
+            std::vector<Operand> get_env;
+            for (size_t k = begin; k < begin + a.input_sizes[3]; ++k)
+                if (!a.inputs[k].is_fn && a.inputs[k].lowered != "erased") get_env.push_back(a.inputs[k]);
+            const Operand* get_fn = nullptr;
+            for (size_t k = begin + a.input_sizes[3]; k < begin + a.input_sizes[3] + a.input_sizes[4]; ++k)
+                if (a.inputs[k].is_fn) get_fn = &a.inputs[k];
+            if (!get_fn) break;
+            try {
+                plan.getter = compile_producer(modules, get_fn->name, get_env, outs[0].lowered);
+                plan.staged = true;
+                plan.get_env_begin = begin;
+                plan.get_env_size = a.input_sizes[3];
+                plan.kind = ad[2];
+            } catch (const Unsupported&) {
+            }
+            break;
+        }
+    }
+    return plan;
 }
 
 // The register program of a `materializec` assignment: inputs `len, env..., producer` (input_sizes {1, n, 1} when given).

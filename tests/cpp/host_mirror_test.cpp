@@ -75,6 +75,17 @@ static std::vector<lw::GpuModule> lowered_modules() {
                            {"materializec", {var("len", "u64"), var("input", "ptr<u64>"), lw::Operand::fn("materialize-copy-u64-producer")},
                             {var("buf", "ptr<u64>")}, "", {1, 1, 1}, {1}},
                            {"buf.to-mem", {var("len", "u64"), var("buf", "ptr<u64>")}, {var("out", "mem")}, ""}}));
+    // a fold over a buffer whose `add` is not associative (acc = acc * k + x[i] from 7): the generic map kernel runs the loop
+    mods.push_back(module("my.horner-add", {var("k", "u64"), var("acc", "u64"), var("value", "u64")}, {var("r", "u64")},
+                          {{"u64.mul", {var("acc", "u64"), var("k", "u64")}, {var("t", "u64")}, ""},
+                           {"u64.add", {var("t", "u64"), var("value", "u64")}, {var("r", "u64")}, ""}}));
+    mods.push_back(module("sum-u64-at", {var("input", "ptr<u64>"), var("i", "u64")}, {var("r", "u64")},
+                          {{"ix", {var("i", "u64"), var("input", "ptr<u64>")}, {var("r", "u64")}, ""}}));
+    mods.push_back(module("my.horner", {var("m", "mem"), var("k", "u64")}, {var("r", "u64")},
+                          {{"mem.cast.u64", {var("m", "mem")}, {var("len", "u64"), var("input", "ptr<u64>")}, ""},
+                           {"const.u64.0x0000000000000007", {}, {var("seed", "u64")}, ""},
+                           {"reducec", {var("seed", "u64"), var("k", "u64"), lw::Operand::fn("my.horner-add"), var("input", "ptr<u64>"),
+                                        lw::Operand::fn("sum-u64-at"), var("len", "u64")}, {var("r", "u64")}, "", {1, 1, 1, 1, 1, 1}, {1}}}));
     // tests/cases/materialize/basic.hex: out[i] = i
     mods.push_back(module("cast-index", {var("i", "u64")}, {var("r", "u64")}, {{"ix.to-u64", {var("i", "u64")}, {var("r", "u64")}, ""}}));
     mods.push_back(module("materialize-indexes-source", {var("len", "u64")}, {var("out", "mem")},
@@ -233,6 +244,14 @@ static int run_gpu() {
         z.push_back(Value::u64(0));
         std::vector<Value> empty = rt.exec("materialize-indexes-source", std::move(z));
         CHECK(empty[0].as_mem().is_null() && empty[0].as_mem().to_u64_vec().empty());
+    }
+    {
+        std::vector<Value> a;
+        a.push_back(Value::mem(rt.mem_u64({3, 5, 8, 13})));
+        a.push_back(Value::u64(31));
+        uint64_t want = 7;
+        for (uint64_t x : {3ull, 5ull, 8ull, 13ull}) want = want * 31 + x;
+        CHECK(rt.exec("my.horner", std::move(a))[0].as_u64() == want);
     }
     // bf16 GEMM through Runtime::exec: 256 x 256 x 64 of ones and twos -> every element 128 (exact in bf16)
     {

@@ -91,7 +91,22 @@ static std::vector<GpuModule> fixtures() {
                   {A("mem.cast.f32", {v("ma", "mem")}, {u("alen"), pf("a")}), A("mem.cast.f32", {v("mb", "mem")}, {u("cols"), pf("b")}),
                    A("materializec", {u("rows"), pf("a"), pf("b"), u("cols"), fn("my.matvec-at")}, {pf("buf")}, {1, 3, 1}, {1}),
                    A("buf.to-mem", {u("rows"), pf("buf")}, {v("out", "mem")})}));
+    // acc = acc * k + x[i] from 7: a fold over a buffer whose `add` is not associative (tests/lowered_fixtures.py: custom_fold_programs)
+    m.push_back(M("my.horner-add", {u("k"), u("acc"), u("value")}, {u("r")},
+                  {A("u64.mul", {u("acc"), u("k")}, {u("t")}), A("u64.add", {u("t"), u("value")}, {u("r")})}));
+    m.push_back(M("sum-u64-at", {pu("input"), u("i")}, {u("r")}, {A("ix", {u("i"), pu("input")}, {u("r")})}));
+    m.push_back(M("my.horner", {v("m", "mem"), u("k")}, {u("r")},
+                  {A("mem.cast.u64", {v("m", "mem")}, {u("len"), pu("input")}), A("const.u64.0x0000000000000007", {}, {u("seed")}),
+                   A("reducec", {u("seed"), u("k"), fn("my.horner-add"), pu("input"), fn("sum-u64-at"), u("len")}, {u("r")}, {1, 1, 1, 1, 1, 1}, {1})}));
     return m;
+}
+
+static const GpuAssign& reducec_of(const std::vector<GpuModule>& mods, const std::string& source_name) {
+    for (const GpuModule& m : mods)
+        if (m.source_name == source_name)
+            for (const GpuAssign& a : m.entry.assignments)
+                if (a.op == "reducec") return a;
+    throw std::runtime_error("no such fixture");
 }
 
 static const GpuAssign& materializec_of(const std::vector<GpuModule>& mods, const std::string& source_name) {
@@ -116,6 +131,7 @@ int main(int argc, char** argv) {
     const char* names[] = {"materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec"};
     if (mode == "list") {
         for (const char* n : names) list(n, map_program::for_assignment(mods, materializec_of(mods, n)));
+        list("my.horner", map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0));
         return 0;
     }
     // ---- gpu: the reference's vectors (catena-lang/tests/cases/materializec.rs:5-31, materialize.rs:5-31) and the two user producers
@@ -186,6 +202,21 @@ int main(int argc, char** argv) {
         catena_b200_mem_free(out);
         catena_b200_mem_free(ma);
         catena_b200_mem_free(mb);
+    }
+    {
+        // the sequential fold as a register program on one device thread
+        const auto p = map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0);
+        const uint64_t data[5] = {3, 5, 8, 13, 0x8000000000000005ull};
+        catena_mem_t in = upload(data, 40), out{nullptr, 0};
+        // runtime inputs of the reducec in order: seed, k, input, len
+        CHECK(p.launch(1, {map_program::EnvValue::scalar(7), map_program::EnvValue::scalar(31), map_program::EnvValue::mem(in),
+                           map_program::EnvValue::scalar(5)}, &out) == CATENA_OK);
+        uint64_t got = 0, want = 7;
+        CHECK(catena_b200_mem_download(out, &got, 8) == CATENA_OK);
+        for (uint64_t x : data) want = want * 31 + x;
+        CHECK(got == want);
+        catena_b200_mem_free(out);
+        catena_b200_mem_free(in);
     }
     std::printf("ok %d checks\n", g_checks);
     return 0;

@@ -82,6 +82,14 @@ def test_cpp_map_program_compiler_agrees_with_python(map_program_binary):
             lines.append(f"  preset {what[0]} {what[1]} {what[2] if what[0] == 'buflen' else 0}")
         for c in prog.code:
             lines.append(f"  insn {c.op} {c.dst} {c.a} {c.b} {c.c} {c.target}")
+    fm = lo.module_map(fx.custom_fold_programs())
+    [fold] = [a for a in fm["my.horner"].entry.assignments if a.op == "reducec"]
+    prog = lo.fold_plan_for(fold, fm).sequential[0]
+    lines.append(f"program my.horner regs={prog.n_regs} index={prog.index_reg} result={prog.result_reg} elem={prog.elem_bytes}")
+    for what in prog.presets:
+        lines.append(f"  preset {what[0]} {what[1]} {what[2] if what[0] == 'buflen' else 0}")
+    for c in prog.code:
+        lines.append(f"  insn {c.op} {c.dst} {c.a} {c.b} {c.c} {c.target}")
     assert p.stdout.strip().splitlines() == lines
 
 
