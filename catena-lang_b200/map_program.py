@@ -121,20 +121,19 @@ class _Builder:
         self.by_name = modules if isinstance(modules, dict) else module_map(modules)
         self.code = []
         self.presets = []             # register k < len(presets) is preset: ("const", value) | ("env", position) | ("buflen", position, bytes)
-        self.const_regs = {}
-        self.buflen_regs = {}
-        self.next_reg = None          # set once the presets are known: compile() runs twice (see compile_producer)
-        self.fixed_presets = None
+        self.preset_regs = {}
+        self.next_reg = None          # first temporary; set by _compile, which walks the producer twice
+        self.fixed_presets = None     # pass 2: preset -> register, as pass 1 discovered them
         self.depth = 0
 
     # ---- registers ----
     def preset(self, what):
         if self.fixed_presets is not None:
             return self.fixed_presets[what]
-        if what not in self.const_regs:
-            self.const_regs[what] = len(self.presets)
+        if what not in self.preset_regs:
+            self.preset_regs[what] = len(self.presets)
             self.presets.append(what)
-        return self.const_regs[what]
+        return self.preset_regs[what]
 
     def const(self, value):
         return self.preset(("const", int(value)))
