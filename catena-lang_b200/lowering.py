@@ -21,6 +21,8 @@ recognises the shapes the stdlib lowers to:
   * `mem.cast.u64`, `ix.zero`, `ix` (catena-lang/tests/runtime.rs:713-726)   -> buffer-head copy
   * a module of scalar primitives, `bool.ifc`, `eval`, calls of scalar modules and `reducec` whose
     closures are scalar (catena-lang/tests/cases/closures/*.hex)             -> host execution (evaluator.py)
+  * a `materializec` whose producer applies a scalar stdlib program to every element of one f32 buffer
+    (`out[i] = nn.silu(x[i])` and the like)                                  -> the prebuilt unary map kernel
   * any other `materializec` whose producer is scalar code over its environment and index
     (catena-lang/examples/materializec.hex, tests/cases/materialize/basic.hex) -> the generic map kernel, which
     interprets the producer as a register program (map_program.py); the code around it runs on the host
@@ -172,6 +174,39 @@ def materializec_parts(assign, values=None):
     return items[0], env, fns[0]
 
 
+def unary_map_op(module, assign, modules):
+    """`out[i] = S(x[i])` over the whole of one f32 buffer, S a scalar stdlib program with a prebuilt map kernel
+    (`catena_b200_map_f32_s`): returns S's hexpr name, else None.  The shape: the environment is one `ptr<f32>`, the producer
+    is `ix` of that buffer at the index followed by a call of S, and the length is the buffer's own (the `mem.cast.f32` that
+    made the pointer)."""
+    from . import SCALAR_PROGRAMS
+    from .evaluator import NO_OPS
+    try:
+        length, env, fn = materializec_parts(assign)
+    except Unsupported:
+        return None
+    env = [v for v in env if isinstance(v, GpuVar) and v.lowered != "erased"]
+    producer = find_module(modules, fn.name)
+    if producer is None or len(env) != 1 or env[0].lowered != "ptr<f32>" or not isinstance(length, GpuVar):
+        return None
+    if not any(a.op == "mem.cast.f32" and [o.name for o in a.outputs] == [length.name, env[0].name] for a in module.entry.assignments):
+        return None
+    sources = [v for v in producer.entry.sources if v.lowered != "erased"]
+    targets = [v for v in producer.entry.targets if v.lowered != "erased"]
+    body = [a for a in producer.entry.assignments if a.op not in NO_OPS]
+    if [v.lowered for v in sources] != ["ptr<f32>", "u64"] or len(targets) != 1 or len(body) != 2:
+        return None
+    load, call = body
+    if load.op != "ix" or [v.name for v in load.inputs if isinstance(v, GpuVar)] != [sources[1].name, sources[0].name]:
+        return None
+    callee = find_module(modules, call.call_symbol) if call.call_symbol else None
+    name = callee.source_name if callee is not None else call.op
+    args = [v.name for v in call.inputs if isinstance(v, GpuVar) and v.lowered != "erased"]
+    if name not in SCALAR_PROGRAMS or args != [load.outputs[0].name] or [o.name for o in call.outputs if o.lowered != "erased"] != [targets[0].name]:
+        return None
+    return name
+
+
 def map_program_for(assign, modules):
     """The register program of a `materializec` whose producer has no prebuilt kernel (map_program.py); raises Unsupported."""
     from .map_program import compile_producer
@@ -294,6 +329,14 @@ def select(module, symbol_for=None, modules=None):
             kinds.append(k)
     symbol = symbol_for(module.source_name) if module.source_name else module.name
     ops = [a.op for a in module.entry.assignments]
+    if kinds == ["map_generic"] and modules is not None:
+        # one custom producer that only applies a scalar stdlib program to every element of a buffer: the prebuilt map kernel
+        [launch] = [a for a in module.entry.assignments if a.op == "materializec"]
+        rest = [a.op for a in module.entry.assignments if a is not launch]
+        from .evaluator import NO_OPS
+        op = unary_map_op(module, launch, modules)
+        if op is not None and sorted(o for o in rest if o not in NO_OPS) == ["buf.to-mem", "mem.cast.f32"]:
+            return KernelPlan("map_unary", symbol, [op])
     generic = ("map_generic", "fold_generic")
     if any(k in generic for k in kinds) and not all(k in generic for k in kinds) and modules is not None:
         # a module is one of the recognised shapes, or everything in it runs generically: the recognised maps and folds it

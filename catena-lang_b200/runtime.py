@@ -239,7 +239,18 @@ class Runtime:
                 rt.signatures[m.source_name] = (plan.symbol, [kinds[t] for t in ins], [kinds[t] for t in outs],
                                                 (lambda args, _name=m.name: evaluator.call(_name, args)))
                 continue
-            if plan.kernel == "host_with_map_kernels":
+            if plan.kernel == "map_unary" and ins == ["mem"] and outs == ["mem"]:
+                def run_map(args, _op=plan.notes[0].encode()):
+                    from . import CatenaMem, check
+                    from .evaluator import DeviceMem
+                    raw = CatenaMem()
+                    check(rt._lib.catena_b200_map_f32_s(_op, CatenaMem(args[0].ptr or None, args[0].nbytes), C.byref(raw)))
+                    if raw.data:
+                        rt._map_outputs[int(raw.data)] = raw
+                    return [DeviceMem(raw.data, raw.len)]
+                rt.signatures[m.source_name] = (plan.symbol, [K.Mem], [K.Mem], run_map)
+                continue
+            if plan.kernel in ("host_with_map_kernels", "map_unary"):
                 # the producers' register programs are built now, so that a producer the map kernel cannot run is an
                 # InitError and `exec` only binds the environment and launches
                 from .lowering import _touches_memory, fold_plan_for, map_program_for

@@ -223,7 +223,7 @@ public:
             if (!callable) continue;                                   // a `buf` pointer on the boundary: internal
             lowering::KernelPlan plan;
             try {
-                plan = lowering::select(m);
+                plan = lowering::select(m, *shared);
             } catch (const lowering::Unsupported& e) {
                 throw InitError("no prebuilt kernel or host plan for program '" + m.source_name + "': " + e.what());
             }
@@ -260,7 +260,17 @@ public:
                 }};
                 continue;
             }
-            if (plan.kernel == "host_with_map_kernels") {
+            if (plan.kernel == "map_unary" && ins == std::vector<K>{K::Mem} && outs == std::vector<K>{K::Mem}) {
+                const std::string op = plan.note;
+                table_[m.source_name] = Signature{plan.symbol, ins, outs, [op](std::vector<Value>& a, std::vector<Value>& o) {
+                    catena_mem_t out{nullptr, 0};
+                    const catena_status_t s = catena_b200_map_f32_s(op.c_str(), a[0].as_mem().raw(), &out);
+                    if (s == CATENA_OK) o.push_back(Value::mem(Mem(out)));
+                    return s;
+                }};
+                continue;
+            }
+            if (plan.kernel == "host_with_map_kernels" || plan.kernel == "map_unary") {
                 // the producers' register programs are built now: one the map kernel cannot run is an InitError
                 auto programs = std::make_shared<std::map<const lowering::GpuAssign*, map_program::Program>>();
                 auto folds = std::make_shared<std::map<const lowering::GpuAssign*, map_program::FoldPlan>>();

@@ -188,6 +188,79 @@ inline KernelPlan select(const GpuModule& module) {
     throw Unsupported(module.name + ": unrecognised combination " + all);
 }
 
+// `out[i] = S(x[i])` over the whole of one f32 buffer, S a scalar stdlib program with a prebuilt map kernel
+// (catena_b200_map_f32_s): S's hexpr name, else "".  The shape: the environment of the materializec is one ptr<f32>, the
+// producer is `ix` of that buffer at the index followed by a call of S, and the length is the buffer's own (the mem.cast.f32
+// that made the pointer).
+inline std::string unary_map_op(const GpuModule& module, const GpuAssign& a, const std::vector<GpuModule>& modules) {
+    static const char* scalar_programs[] = {"math.sin-approx", "math.cos-approx", "math.sin-approx-full-nonneg", "math.sin-approx-full",
+                                            "math.log-approx", "math.exp-approx-nonneg", "math.exp-approx", "math.exp2-approx",
+                                            "math.log2-approx", "math.sqrt", "nn.sigmoid", "nn.silu", "nn.tanh", "nn.gelu-approx"};
+    auto find = [&](const std::string& name) -> const GpuModule* {
+        for (const GpuModule& m : modules)
+            if (m.name == name || (!m.source_name.empty() && (m.source_name == name || symbol_for(m.source_name) == name))) return &m;
+        for (const GpuModule& m : modules)
+            if (m.name == symbol_for(name)) return &m;
+        return nullptr;
+    };
+    auto runtime = [](const std::vector<Operand>& v) {
+        std::vector<Operand> out;
+        for (const Operand& o : v)
+            if (!o.is_fn && o.lowered != "erased") out.push_back(o);
+        return out;
+    };
+    if (a.op != "materializec" || a.inputs.size() < 3 || a.inputs[0].is_fn) return "";
+    size_t env_end = a.inputs.size() - 1;
+    if (!a.input_sizes.empty()) {
+        if (a.input_sizes.size() != 3 || a.input_sizes[0] != 1) return "";
+        env_end = 1 + a.input_sizes[1];
+    }
+    const std::vector<Operand> env = runtime(std::vector<Operand>(a.inputs.begin() + 1, a.inputs.begin() + env_end));
+    const Operand* fn = nullptr;
+    for (size_t k = env_end; k < a.inputs.size(); ++k)
+        if (a.inputs[k].is_fn) fn = &a.inputs[k];
+    if (!fn || env.size() != 1 || env[0].lowered != "ptr<f32>") return "";
+    bool own_length = false;
+    for (const GpuAssign& c : module.entry.assignments)
+        own_length = own_length || (c.op == "mem.cast.f32" && c.outputs.size() == 2 && c.outputs[0].name == a.inputs[0].name && c.outputs[1].name == env[0].name);
+    const GpuModule* producer = find(fn->name);
+    if (!own_length || !producer) return "";
+    const std::vector<Operand> sources = runtime(producer->entry.sources), targets = runtime(producer->entry.targets);
+    std::vector<const GpuAssign*> body;
+    for (const GpuAssign& c : producer->entry.assignments)
+        if (c.op != "unit.intro" && c.op != "ax-mp" && c.op != "assert-then" && c.op != ":.param") body.push_back(&c);
+    if (sources.size() != 2 || sources[0].lowered != "ptr<f32>" || sources[1].lowered != "u64" || targets.size() != 1 || body.size() != 2) return "";
+    const GpuAssign &load = *body[0], &call = *body[1];
+    const std::vector<Operand> load_in = runtime(load.inputs), call_in = runtime(call.inputs), call_out = runtime(call.outputs);
+    if (load.op != "ix" || load_in.size() != 2 || load_in[0].name != sources[1].name || load_in[1].name != sources[0].name || load.outputs.empty()) return "";
+    const GpuModule* callee = call.call_symbol.empty() ? nullptr : find(call.call_symbol);
+    const std::string name = callee ? callee->source_name : call.op;
+    bool known = false;
+    for (const char* p : scalar_programs) known = known || name == p;
+    if (!known || call_in.size() != 1 || call_in[0].name != load.outputs[0].name || call_out.size() != 1 || call_out[0].name != targets[0].name) return "";
+    return name;
+}
+
+// select() with the program's other modules at hand: a lone custom producer that only applies a scalar stdlib program to every
+// element of a buffer takes the prebuilt map kernel (plan "map_unary", the program's name in `note`).
+inline KernelPlan select(const GpuModule& module, const std::vector<GpuModule>& modules) {
+    KernelPlan plan = select(module);
+    if (plan.kernel != "host_with_map_kernels") return plan;
+    const GpuAssign* launch = nullptr;
+    size_t launches = 0, casts = 0, to_mem = 0, other = 0;
+    for (const GpuAssign& a : module.entry.assignments) {
+        if (a.op == "materializec") { launch = &a; ++launches; }
+        else if (a.op == "mem.cast.f32") ++casts;
+        else if (a.op == "buf.to-mem") ++to_mem;
+        else if (a.op != "unit.intro" && a.op != "ax-mp" && a.op != "assert-then" && a.op != ":.param") ++other;
+    }
+    if (launches == 1 && casts == 1 && to_mem == 1 && other == 0) {
+        const std::string op = unary_map_op(module, *launch, modules);
+        if (!op.empty()) return {"map_unary", plan.symbol, op};
+    }
+    return plan;
+}
+
 }  // namespace lowering
 }  // namespace catena_b200
 

@@ -76,6 +76,24 @@ int main() {
     // the same for a fold over a buffer whose closures match no fold kernel
     CHECK(select(mod("odd", {cast, reducec("f32.add-env", "my.getter")})).kernel == "host_with_map_kernels");
     CHECK(refused(mod("two-maps", {cast, materializec("tensor.arange-at"), materializec("tensor.slice-at"), to_mem})));
+    {
+        // out[i] = nn.silu(x[i]) written as a user's producer: with the modules at hand the selector takes the prebuilt map kernel
+        GpuModule at = mod("my.silu-at", {GpuAssign{"ix", {Operand::var("i", "u64"), Operand::var("x", "ptr<f32>")}, {Operand::var("xi", "f32")}, ""},
+                                          GpuAssign{"nn.silu", {Operand::var("xi", "f32")}, {Operand::var("r", "f32")}, "program_nn_silu"}});
+        at.entry.sources = {Operand::var("x", "ptr<f32>"), Operand::var("i", "u64")};
+        at.entry.targets = {Operand::var("r", "f32")};
+        GpuModule silu = mod("nn.silu", {prim("f32.mul")});
+        GpuModule entry = mod("my.silu-map", {GpuAssign{"mem.cast.f32", {Operand::var("m", "mem")}, {Operand::var("len", "u64"), Operand::var("x", "ptr<f32>")}, ""},
+                                              GpuAssign{"materializec", {Operand::var("len", "u64"), Operand::var("x", "ptr<f32>"), Operand::fn("my.silu-at")},
+                                                        {Operand::var("buf", "ptr<f32>")}, "", {1, 1, 1}, {1}},
+                                              GpuAssign{"buf.to-mem", {Operand::var("len", "u64"), Operand::var("buf", "ptr<f32>")}, {Operand::var("out", "mem")}, ""}});
+        const std::vector<GpuModule> all = {at, silu, entry};
+        KernelPlan p = select(entry, all);
+        CHECK(p.kernel == "map_unary" && p.note == "nn.silu");
+        // with another length than the buffer's own it stays on the generic path
+        entry.entry.assignments[1].inputs[0] = Operand::var("other", "u64");
+        CHECK(select(entry, all).kernel == "host_with_map_kernels");
+    }
     std::printf("ok %d checks\n", g_checks);
     return 0;
 }

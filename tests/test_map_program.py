@@ -26,8 +26,11 @@ def program_of(mods, entry):
 def test_selector_takes_arbitrary_producers():
     mods = fx.materialize_programs() + fx.custom_map_programs()
     mm = modules_by_name(mods)
-    for name in ("materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.silu-map", "my.clamp-map", "my.matvec"):
+    for name in ("materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec"):
         assert lo.select(mm[name], modules=mm).kernel == "host_with_map_kernels"
+    # a producer that only applies a scalar stdlib program to every element of a buffer has a prebuilt kernel
+    plan = lo.select(mm["my.silu-map"], modules=mm)
+    assert (plan.kernel, plan.notes) == ("map_unary", ["nn.silu"])
     # a producer that is not there, or is not scalar code, stays unsupported
     bad = fx.M("bad-map", [fx.v("n", "u64")], [fx.v("out", "mem")], [
         fx.A("materializec", [fx.v("n", "u64"), fx.fn("no.such-producer")], [fx.v("buf", "ptr<u64>")], [1, 0, 1], [1]),

@@ -40,8 +40,18 @@ def test_interpreted_silu_equals_the_prebuilt_kernel(rt, n):
     rng = np.random.default_rng(n)
     x = rng.normal(0, 4, n).astype(np.float32)
     x[: min(n, 6)] = np.array([0.0, -0.0, 88.0, -87.0, 1e-30, -1e-30], np.float32)[: min(n, 6)]
+    # through the runtime the selector recognises `out[i] = nn.silu(x[i])` and takes the prebuilt kernel; the register
+    # program of the same producer is launched directly
     [out] = rt.exec("my.silu-map", [rt.mem_f32(x)])
-    got = out.v.to_f32_vec().view(np.uint32)
+    selected = out.v.to_f32_vec().view(np.uint32)
+    mm = lo.module_map(fx.custom_map_programs())
+    [launch] = [a for a in mm["my.silu-map"].entry.assignments if a.op == "materializec"]
+    m = cb.upload(x)
+    raw = lo.map_program_for(launch, mm).launch(n, [(m.data, m.len)])
+    got = cb.download(raw, np.float32).view(np.uint32)
+    cb.free(raw)
+    cb.free(m)
+    assert np.array_equal(got, selected)
     m = cb.upload(x)
     o = cb.CatenaMem()
     cb.check(cb.lib().catena_b200_map_f32_s(b"nn.silu", m, C.byref(o)))
