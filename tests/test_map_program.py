@@ -137,3 +137,24 @@ def test_generic_folds_compile_and_match_the_sequential_loop():
     # an empty fold returns its zero
     [got] = map_vm.run(plan.sequential[0], [np.float32(2.5), (0, 0), 0], 1, [np.zeros(0, np.uint8)])
     assert int(got) == int(np.float32(2.5).view(np.uint32))
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_producers_compile_to_what_the_evaluator_computes(seed):
+    """Random well-typed producers (tests/random_programs.py): the register program run by the CPU interpreter gives, index by
+    index, the bits the host evaluator computes from the lowered assignments — folding, aliasing, register reuse, the
+    conditional and the loop included."""
+    import random_programs as rp
+    result = "u64" if seed % 2 == 0 else "f32"
+    mods, name = rp.generate(seed, n_ops=40, result=result, control=seed % 3 != 0)
+    mm = modules_by_name(mods)
+    [launch] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+    prog = lo.map_program_for(launch, mm)
+    table, xs = rp.tables(seed)
+    n, sd, scale = 24, 0x0123456789ABCDEF ^ seed, np.float32(1.5 + seed)
+    got = map_vm.run(prog, [sd, scale, (0, table.nbytes), (0, xs.nbytes)], n, [table.view(np.uint8), xs.view(np.uint8)])
+    ev = Evaluator(mods)
+    for i in range(n):
+        [want] = ev.call(f"{name}.at", [sd, scale, table, xs, i])
+        bits = int(want) if result == "u64" else int(np.float32(want).view(np.uint32))
+        assert int(got[i]) == bits, (seed, i)

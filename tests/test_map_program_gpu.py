@@ -232,3 +232,23 @@ def test_generic_folds_through_the_runtime():
     with pytest.raises(cb.ExecError) as err:
         big.exec("my.horner", [big.mem_u64(np.zeros((1 << 22) + 10, np.uint64)), 3])
     assert err.value.status == cb.E_ASSERT
+
+
+@pytest.mark.parametrize("seed,control", [(100, True), (101, True), (102, False), (103, False), (104, True), (105, False)])
+def test_random_producers_on_the_device(seed, control):
+    """Random well-typed producers (tests/random_programs.py) through `Runtime.exec`: the kernel gives the bits of the CPU
+    interpreter (which test_map_program.py ties to the host evaluator) — with a conditional and a loop (one element per
+    thread) and without (four per thread)."""
+    import random_programs as rp
+    result = "u64" if seed % 2 == 0 else "f32"
+    mods, name = rp.generate(seed, n_ops=60, result=result, control=control)
+    rt = cb.Runtime.from_modules(mods)
+    table, xs = rp.tables(seed)
+    n, sd, scale = 2500, 0xFEDCBA9876543210 ^ seed, np.float32(0.75 * seed)
+    [out] = rt.exec(name, [sd, scale, rt.mem_u64(table), rt.mem_f32(xs), n])
+    got = out.v.to_u64_vec() if result == "u64" else out.v.to_f32_vec().view(np.uint32)
+    mm = lo.module_map(mods)
+    [launch] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+    prog = lo.map_program_for(launch, mm)
+    want = map_vm.run(prog, [sd, scale, (0, table.nbytes), (0, xs.nbytes)], n, [table.view(np.uint8), xs.view(np.uint8)])
+    assert np.array_equal(got, want.astype(got.dtype))
