@@ -254,7 +254,7 @@ __global__ void add_rows_kernel(const uint4* x, const uint4* y, uint4* out, uint
 // ---------------------------------------------------------------- skinny GEMM (M <= 16 rows): arithmetic in skinny.cuh
 // CTAs are persistent and software-pipelined (skinny.cuh); the first batch of weight loads is issued before the wait for the
 // predecessor's results.
-__global__ void __launch_bounds__(256, 2) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+__global__ void __launch_bounds__(256, kSkinnyCtasPerSm) skinny_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ y,
                                                          uint32_t M, uint32_t N, uint32_t K, uint32_t swiglu_f) {
     __shared__ float part[8][16][8];    // [warp][token][weight row]
@@ -721,7 +721,7 @@ static catena_status_t launch_linear(const void* x, const void* w, const void* r
         if (n > 0x7FFFFFFFull || k > 0x7FFFFFFFull) return fail(CATENA_E_TOO_LARGE, "linear: dimension too large");
         int sms = tls().sm_count > 0 ? tls().sm_count : 148;
         // persistent CTAs (two per SM), the same number of row groups for each of them where possible
-        const uint64_t groups = ceil_div_u64(n, 8), slots = (uint64_t)sms * 2;
+        const uint64_t groups = ceil_div_u64(n, 8), slots = (uint64_t)sms * llama::kSkinnyCtasPerSm;
         const uint64_t rounds = ceil_div_u64(groups, slots);
         const unsigned grid = (unsigned)ceil_div_u64(groups, rounds);
         return launch_pdl("skinny_gemm_kernel", llama::skinny_gemm_kernel, dim3(grid), dim3(256), 0, (const __nv_bfloat16*)x,
@@ -741,7 +741,7 @@ static catena_status_t launch_linear_swiglu(const void* x, const void* w, void* 
     if (ffn % 8) return fail(CATENA_E_BAD_ARG, "swiglu: ffn must be a multiple of 8");
     if (m <= 16 && k % 8 == 0 && k > 0 && ffn <= 0x3FFFFFFFull && k <= 0x7FFFFFFFull && !(((uintptr_t)x | (uintptr_t)w) & 15)) {
         int sms = tls().sm_count > 0 ? tls().sm_count : 148;
-        const uint64_t groups = ffn / 8, slots = (uint64_t)sms * 2;
+        const uint64_t groups = ffn / 8, slots = (uint64_t)sms * llama::kSkinnyCtasPerSm;
         const uint64_t rounds = ceil_div_u64(groups, slots);
         const unsigned grid = (unsigned)ceil_div_u64(groups, rounds);
         return launch_pdl("skinny_gemm_kernel", llama::skinny_gemm_kernel, dim3(grid), dim3(256), 0, (const __nv_bfloat16*)x,

@@ -43,13 +43,16 @@ __device__ __forceinline__ uint64_t from_f32(float f) { return (uint64_t)__float
 
 // Small programs travel as kernel parameters (no copy, no scratch, and the constant cache broadcasts an instruction to the
 // warp); larger ones are copied to the device and staged in shared memory.
-constexpr uint32_t kParamInsns = 192, kParamInit = 48;
+#ifndef CATENA_MAP_PARAM_INSNS
+#define CATENA_MAP_PARAM_INSNS 192
+#endif
+constexpr uint32_t kParamInsns = CATENA_MAP_PARAM_INSNS, kParamInit = 48;
 struct ParamProgram {
     uint4 code[kParamInsns];
     uint64_t init[kParamInit];
 };
 
-// The register file.  Low halves: shared memory, [register][lane][thread] (conflict-free, and unlike a local-memory array it
+// The register file.  Low halves: shared memory, [register][thread][lane] (conflict-free, and unlike a local-memory array it
 // cannot be evicted: with the file in local memory an SM's resident threads touched several times the L1 and the spill to L2
 // and HBM cost ten times the algorithmic traffic).  High halves: a local-memory array — bool / u32 / f32 instructions never
 // touch them, so a program without u64 arithmetic uses them for the index only.  The high half of a register that holds a
@@ -65,12 +68,14 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
                                                           void* __restrict__ out, uint32_t elem_bytes, uint64_t len, uint32_t* err) {
     extern __shared__ uint4 s_dyn[];
     const uint4* s_code = s_dyn;
-    uint32_t* s_lo = reinterpret_cast<uint32_t*>(s_dyn + (PARAM ? 0 : n_insn)) + threadIdx.x;
+    // low halves: the V lanes of a register sit side by side, [register][thread][lane], so that one 16-byte access moves all
+    // four (a warp's access is 512 contiguous bytes: four conflict-free wavefronts)
+    uint32_t* s_lo = reinterpret_cast<uint32_t*>(s_dyn + (PARAM ? 0 : n_insn)) + threadIdx.x * V;
     if (!PARAM) {
         for (uint32_t k = threadIdx.x; k < n_insn; k += T) s_dyn[k] = code[k];
         __syncthreads();
     }
-#define lo(R, v) s_lo[((R) * V + (v)) * T]
+#define lo(R, v) s_lo[(R) * (V * T) + (v)]
     uint32_t hi[REGS][V];
 #pragma unroll 1
     for (uint32_t k = 0; k < n_regs; ++k) {
@@ -118,16 +123,28 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
         hi[dst][v] = (uint32_t)(x_ >> 32);     \
     } while (0)
 #define CATENA_LANES _Pragma("unroll") for (int v = 0; v < V; ++v)
+// all lanes of a register's low half in one access (16 bytes for four lanes)
+#define CATENA_LD(R, X)                                                                    \
+    uint32_t X[V];                                                                         \
+    if (V == 4) {                                                                          \
+        const uint4 t_ = *reinterpret_cast<const uint4*>(&lo(R, 0));                       \
+        X[0] = t_.x; X[V > 1 ? 1 : 0] = t_.y; X[V > 2 ? 2 : 0] = t_.z; X[V > 3 ? 3 : 0] = t_.w; \
+    } else {                                                                               \
+        CATENA_LANES X[v] = lo(R, v);                                                      \
+    }
+#define CATENA_ST(X)                                                                       \
+    if (V == 4) *reinterpret_cast<uint4*>(&lo(dst, 0)) = make_uint4(X[0], X[V > 1 ? 1 : 0], X[V > 2 ? 2 : 0], X[V > 3 ? 3 : 0]); \
+    else CATENA_LANES lo(dst, v) = X[v]
 // 32-bit operands and result
-#define CATENA_W(EXPR)      CATENA_LANES { const uint32_t a = lo(ra, v), b = lo(rb, v); (void)b; lo(dst, v) = (uint32_t)(EXPR); } break
-#define CATENA_W1(EXPR)     CATENA_LANES { const uint32_t a = lo(ra, v); lo(dst, v) = (uint32_t)(EXPR); } break
+#define CATENA_W(EXPR)      { CATENA_LD(ra, A_) CATENA_LD(rb, B_) uint32_t R_[V]; CATENA_LANES { const uint32_t a = A_[v], b = B_[v]; (void)b; R_[v] = (uint32_t)(EXPR); } CATENA_ST(R_); } break
+#define CATENA_W1(EXPR)     { CATENA_LD(ra, A_) uint32_t R_[V]; CATENA_LANES { const uint32_t a = A_[v]; R_[v] = (uint32_t)(EXPR); } CATENA_ST(R_); } break
 // 64-bit operands, 64-bit result
 #define CATENA_D(EXPR)      CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; CATENA_W64(v, EXPR); } break
 // 64-bit operands, 32-bit result (compares, conversions)
 #define CATENA_DW(EXPR)     CATENA_LANES { const uint64_t a = CATENA_R64(ra, v), b = CATENA_R64(rb, v); (void)b; lo(dst, v) = (uint32_t)(EXPR); } break
 #define CATENA_DW1(EXPR)    CATENA_LANES { const uint64_t a = CATENA_R64(ra, v); lo(dst, v) = (uint32_t)(EXPR); } break
-#define CATENA_F(EXPR)      CATENA_LANES { const float a = __uint_as_float(lo(ra, v)), b = __uint_as_float(lo(rb, v)); (void)b; lo(dst, v) = __float_as_uint(EXPR); } break
-#define CATENA_FC(EXPR)     CATENA_LANES { const float a = __uint_as_float(lo(ra, v)), b = __uint_as_float(lo(rb, v)); lo(dst, v) = (EXPR) ? 1u : 0u; } break
+#define CATENA_F(EXPR)      { CATENA_LD(ra, A_) CATENA_LD(rb, B_) uint32_t R_[V]; CATENA_LANES { const float a = __uint_as_float(A_[v]), b = __uint_as_float(B_[v]); (void)b; R_[v] = __float_as_uint(EXPR); } CATENA_ST(R_); } break
+#define CATENA_FC(EXPR)     { CATENA_LD(ra, A_) CATENA_LD(rb, B_) uint32_t R_[V]; CATENA_LANES { const float a = __uint_as_float(A_[v]), b = __uint_as_float(B_[v]); R_[v] = (EXPR) ? 1u : 0u; } CATENA_ST(R_); } break
 #define CATENA_UNDEF        (fault = max(fault, (uint32_t)ERR_UNDEFINED), 0)
             switch (op) {
             case CATENA_MAP_ASSERT:
@@ -145,9 +162,12 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
                 }
                 break;
             case CATENA_MAP_MOV32: CATENA_W1(a);
-            case CATENA_MAP_SELECT32:
-                CATENA_LANES { lo(dst, v) = lo(ra, v) != 0 ? lo(rb, v) : lo(rc, v); }
+            case CATENA_MAP_SELECT32: {
+                CATENA_LD(ra, A_) CATENA_LD(rb, B_) CATENA_LD(rc, C_) uint32_t R_[V];
+                CATENA_LANES R_[v] = A_[v] != 0 ? B_[v] : C_[v];
+                CATENA_ST(R_);
                 break;
+            }
             case CATENA_MAP_BOOL_NOT: CATENA_W1(a ? 0u : 1u);
             case CATENA_MAP_BOOL_AND: CATENA_W((a && b) ? 1u : 0u);
             case CATENA_MAP_BOOL_OR: CATENA_W((a || b) ? 1u : 0u);
@@ -184,9 +204,12 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
             case CATENA_MAP_F32_MUL: CATENA_F(cmath::mul(a, b));
             case CATENA_MAP_F32_DIV: CATENA_F(cmath::div(a, b));
             case CATENA_MAP_F32_NEG: CATENA_W1(a ^ 0x80000000u);
-            case CATENA_MAP_F32_FMA:
-                CATENA_LANES { lo(dst, v) = __float_as_uint(__fmaf_rn(__uint_as_float(lo(ra, v)), __uint_as_float(lo(rb, v)), __uint_as_float(lo(rc, v)))); }
+            case CATENA_MAP_F32_FMA: {
+                CATENA_LD(ra, A_) CATENA_LD(rb, B_) CATENA_LD(rc, C_) uint32_t R_[V];
+                CATENA_LANES R_[v] = __float_as_uint(__fmaf_rn(__uint_as_float(A_[v]), __uint_as_float(B_[v]), __uint_as_float(C_[v])));
+                CATENA_ST(R_);
                 break;
+            }
             case CATENA_MAP_F32_EQ: CATENA_FC(a == b);
             case CATENA_MAP_F32_NE: CATENA_FC(a != b);
             case CATENA_MAP_F32_LT: CATENA_FC(a < b);
@@ -218,6 +241,8 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
 #undef CATENA_R64
 #undef CATENA_W64
 #undef CATENA_LANES
+#undef CATENA_LD
+#undef CATENA_ST
 #undef CATENA_W
 #undef CATENA_W1
 #undef CATENA_D

@@ -26,7 +26,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-constexpr int kSkinnyUnroll = 8;
+#ifndef CATENA_SKINNY_UNROLL
+#define CATENA_SKINNY_UNROLL 8
+#endif
+#ifndef CATENA_SKINNY_CTAS
+#define CATENA_SKINNY_CTAS 2
+#endif
+constexpr int kSkinnyUnroll = CATENA_SKINNY_UNROLL;   // 16-byte weight loads per lane and batch (a batch is issued at once)
+constexpr int kSkinnyCtasPerSm = CATENA_SKINNY_CTAS;  // resident CTAs per SM the stand-alone kernel is sized for
 
 // How the activations (and the residual) are read: through the read-only path when no kernel in flight writes them, with
 // L2-coherent loads when an earlier phase of the SAME kernel wrote them, with plain loads from shared memory.
