@@ -210,6 +210,20 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
                 CATENA_ST(R_);
                 break;
             }
+#define CATENA_F3(EXPR)                                                                                            \
+    {                                                                                                              \
+        CATENA_LD(ra, A_) CATENA_LD(rb, B_) CATENA_LD(rc, C_) uint32_t R_[V];                                      \
+        CATENA_LANES {                                                                                             \
+            const float p = cmath::mul(__uint_as_float(A_[v]), __uint_as_float(B_[v])), c = __uint_as_float(C_[v]); \
+            R_[v] = __float_as_uint(EXPR);                                                                         \
+        }                                                                                                          \
+        CATENA_ST(R_);                                                                                             \
+    }                                                                                                              \
+    break
+            case CATENA_MAP_F32_MULADD: CATENA_F3(cmath::add(p, c));
+            case CATENA_MAP_F32_MULSUB: CATENA_F3(cmath::sub(p, c));
+            case CATENA_MAP_F32_SUBMUL: CATENA_F3(cmath::sub(c, p));
+#undef CATENA_F3
             case CATENA_MAP_F32_EQ: CATENA_FC(a == b);
             case CATENA_MAP_F32_NE: CATENA_FC(a != b);
             case CATENA_MAP_F32_LT: CATENA_FC(a < b);
@@ -290,7 +304,8 @@ static uint32_t operand_mask(uint32_t op) {
     case CATENA_MAP_JZ: case CATENA_MAP_ASSERT: return 1;
     case CATENA_MAP_MOV: case CATENA_MAP_MOV32: case CATENA_MAP_BOOL_NOT: case CATENA_MAP_U64_TO_F32: case CATENA_MAP_U32_NOT:
     case CATENA_MAP_U32_TO_F32: case CATENA_MAP_F32_NEG: case CATENA_MAP_F32_ROUND_TO_U32: return 1 | 8;
-    case CATENA_MAP_SELECT: case CATENA_MAP_SELECT32: case CATENA_MAP_F32_FMA: return 1 | 2 | 4 | 8;
+    case CATENA_MAP_SELECT: case CATENA_MAP_SELECT32: case CATENA_MAP_F32_FMA: case CATENA_MAP_F32_MULADD: case CATENA_MAP_F32_MULSUB:
+    case CATENA_MAP_F32_SUBMUL: return 1 | 2 | 4 | 8;
     case CATENA_MAP_LOAD_U64: case CATENA_MAP_LOAD_F32: return 1 | 8;      // b is a buffer number
     default: return op < CATENA_MAP_OP_COUNT ? (1 | 2 | 8) : 0xFF;
     }

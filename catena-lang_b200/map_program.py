@@ -31,7 +31,7 @@ _OPS = ["HALT", "MOV", "JMP", "JZ", "ASSERT", "SELECT", "BOOL_NOT", "BOOL_AND", 
         "U32_ADD", "U32_SUB", "U32_MUL", "U32_AND", "U32_OR", "U32_XOR", "U32_NOT", "U32_SHL", "U32_SHR",
         "U32_EQ", "U32_NE", "U32_LT", "U32_LTE", "U32_GT", "U32_GTE", "U32_TO_F32",
         "F32_ADD", "F32_SUB", "F32_MUL", "F32_DIV", "F32_NEG", "F32_FMA", "F32_EQ", "F32_NE", "F32_LT", "F32_LTE", "F32_GT", "F32_GTE",
-        "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32", "MOV32", "SELECT32"]
+        "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32", "MOV32", "SELECT32", "F32_MULADD", "F32_MULSUB", "F32_SUBMUL"]
 OP = {name: i for i, name in enumerate(_OPS)}
 
 # primitive -> opcode, for the primitives that are one instruction over their runtime inputs
@@ -380,21 +380,56 @@ class _Builder:
 
 _READS_B = {OP[n] for n in _OPS if n not in ("HALT", "MOV", "MOV32", "JMP", "JZ", "ASSERT", "BOOL_NOT", "U64_TO_F32", "U32_NOT", "U32_TO_F32",
                                               "F32_NEG", "F32_ROUND_TO_U32", "LOAD_U64", "LOAD_F32")}
-_READS_C = {OP["SELECT"], OP["SELECT32"], OP["F32_FMA"]}
+_READS_C = {OP["SELECT"], OP["SELECT32"], OP["F32_FMA"], OP["F32_MULADD"], OP["F32_MULSUB"], OP["F32_SUBMUL"]}
 _NO_WRITE = {OP["HALT"], OP["JMP"], OP["JZ"], OP["ASSERT"]}
+
+
+def _reads(c):
+    out = [] if c.op in (OP["HALT"], OP["JMP"]) else [c.a]
+    if c.op in _READS_B:
+        out.append(c.b)
+    if c.op in _READS_C:
+        out.append(c.c)
+    return out
+
+
+def _fuse_mul_add(code, result_reg):
+    """Straight-line code before register reuse (every register is written once): an F32_MUL whose only reader is an F32_ADD /
+    F32_SUB sinks into it as one instruction (two roundings, as before: not an fma) — one dispatch and one round trip through
+    the register file less.  A sum takes at most one product."""
+    uses, reader = {}, {}
+    for k, c in enumerate(code):
+        for reg in _reads(c):
+            uses[reg] = uses.get(reg, 0) + 1
+            reader.setdefault(reg, k)
+    uses[result_reg] = uses.get(result_reg, 0) + 1
+    fused = {}                                    # index of the sum -> index of the product it takes
+    for k, c in enumerate(code):
+        if c.op != OP["F32_MUL"] or uses.get(c.dst) != 1 or c.dst == result_reg:
+            continue
+        j = reader[c.dst]
+        n = code[j]
+        if j > k and j not in fused and n.op in (OP["F32_ADD"], OP["F32_SUB"]) and (n.a == c.dst) != (n.b == c.dst):
+            fused[j] = k
+    gone = set(fused.values())
+    out = []
+    for k, c in enumerate(code):
+        if k in gone:
+            continue
+        if k in fused:
+            m = code[fused[k]]
+            other = c.b if c.a == m.dst else c.a
+            op = "F32_MULADD" if c.op == OP["F32_ADD"] else ("F32_MULSUB" if c.a == m.dst else "F32_SUBMUL")
+            out.append(Insn(OP[op], c.dst, m.a, m.b, other, 0, 0))
+        else:
+            out.append(c)
+    return out
 
 
 def _reuse_registers(code, n_init, index_reg, result_reg):
     """Straight-line code only: every temporary is written once, so a register is free again after its last read.  Keeps
     the preset registers and the index register where they are; returns (code, number of registers, result register)."""
-    def reads(c):
-        out = [] if c.op in (OP["HALT"], OP["JMP"]) else [c.a]
-        if c.op in _READS_B:
-            out.append(c.b)
-        if c.op in _READS_C:
-            out.append(c.c)
-        return out
-
+    reads = _reads
     last = {}
     for k, c in enumerate(code):
         for reg in reads(c):
@@ -467,6 +502,7 @@ def _compile(modules, name, env_vars, elem_lowered, body):
     index, result = run(second)
     code, n_regs = second.code, max(second.next_reg, 1)
     if not any(c.op in (OP["JMP"], OP["JZ"]) for c in code):
+        code = _fuse_mul_add(code, result)
         code, n_regs, result = _reuse_registers(code, len(presets), index, result)
     # ("buflen", slot, bytes) presets name buffer slots; launches index the environment: translate
     slot_position = {slot: position for position, slot in buffer_slot.items()}

@@ -202,7 +202,9 @@ catena_status_t catena_b200_gpu_materialize_f32_s(const char* op, catena_launch_
  * numbers, jump targets, HALT last); a program cannot fault or hang the GPU.  Where the reference's generated code would
  * trap or be undefined — a failed assert, an index past its buffer, a u32 shift by 32 or more, round-to-u32 outside
  * [0, 2^32), division by zero columns, more than 2^22 loop iterations for one element — that element is 0 and the call returns
- * CATENA_E_ASSERT (in non-blocking mode: the next catena_b200_check_device_errors does).  len == 0: {NULL, 0}, no launch. */
+ * CATENA_E_ASSERT (in non-blocking mode: the next catena_b200_check_device_errors does).  len == 0: {NULL, 0}, no launch.
+ * A program of up to 192 instructions and 48 preset registers travels in the kernel parameters; a longer one is copied to
+ * the device first, and that copy synchronises the stream even in non-blocking mode (the host arrays are the caller's). */
 enum catena_b200_map_op {
     CATENA_MAP_HALT = 0,
     CATENA_MAP_MOV,             /* dst = a */
@@ -225,6 +227,11 @@ enum catena_b200_map_op {
     CATENA_MAP_F32_ROUND_TO_U32,
     CATENA_MAP_LOAD_U64, CATENA_MAP_LOAD_F32,   /* `ix`: dst = buffers[b][register a]; b is a buffer number */
     CATENA_MAP_MOV32, CATENA_MAP_SELECT32,      /* MOV / SELECT of a bool, u32 or f32 value: only the low half of the register moves */
+    /* an f32.mul whose only reader is the f32.add / f32.sub right behind it, as one instruction: the product and the sum are
+     * rounded separately, exactly as the two instructions round them (this is not an fma) */
+    CATENA_MAP_F32_MULADD,      /* dst = (a * b) + c */
+    CATENA_MAP_F32_MULSUB,      /* dst = (a * b) - c */
+    CATENA_MAP_F32_SUBMUL,      /* dst = c - (a * b) */
     CATENA_MAP_OP_COUNT
 };
 typedef struct {

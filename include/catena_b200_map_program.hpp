@@ -119,7 +119,10 @@ inline bool reads_b(int op) {
     default: return true;
     }
 }
-inline bool reads_c(int op) { return op == CATENA_MAP_SELECT || op == CATENA_MAP_SELECT32 || op == CATENA_MAP_F32_FMA; }
+inline bool reads_c(int op) {
+    return op == CATENA_MAP_SELECT || op == CATENA_MAP_SELECT32 || op == CATENA_MAP_F32_FMA || op == CATENA_MAP_F32_MULADD ||
+           op == CATENA_MAP_F32_MULSUB || op == CATENA_MAP_F32_SUBMUL;
+}
 // bool / u32 / f32 values live in the low half of a register: their moves leave the high half alone
 inline int mov_for(const std::string& lowered) { return (lowered == "f32" || lowered == "u32" || lowered == "bool") ? CATENA_MAP_MOV32 : CATENA_MAP_MOV; }
 inline bool writes(int op) { return op != CATENA_MAP_HALT && op != CATENA_MAP_JMP && op != CATENA_MAP_JZ && op != CATENA_MAP_ASSERT; }
@@ -413,15 +416,55 @@ private:
     }
 };
 
+inline std::vector<uint32_t> reads_of(const catena_b200_map_insn_t& c) {
+    std::vector<uint32_t> out;
+    if (c.op != CATENA_MAP_HALT && c.op != CATENA_MAP_JMP) out.push_back(c.a);
+    if (reads_b(c.op)) out.push_back(c.b);
+    if (reads_c(c.op)) out.push_back(c.c);
+    return out;
+}
+
+// Straight-line code before register reuse (every register is written once): an F32_MUL whose only reader is an F32_ADD /
+// F32_SUB sinks into it as one instruction (two roundings, as before: not an fma) — one dispatch and one round trip through the
+// register file less.  A sum takes at most one product.
+inline void fuse_mul_add(std::vector<catena_b200_map_insn_t>& code, uint32_t result_reg) {
+    std::map<uint32_t, uint32_t> uses;
+    std::map<uint32_t, size_t> reader;
+    for (size_t k = 0; k < code.size(); ++k)
+        for (uint32_t r : reads_of(code[k])) {
+            ++uses[r];
+            reader.emplace(r, k);
+        }
+    ++uses[result_reg];
+    std::map<size_t, size_t> fused;               // index of the sum -> index of the product it takes
+    for (size_t k = 0; k < code.size(); ++k) {
+        const catena_b200_map_insn_t& c = code[k];
+        if (c.op != CATENA_MAP_F32_MUL || uses[c.dst] != 1 || c.dst == result_reg) continue;
+        const size_t j = reader.at(c.dst);
+        const catena_b200_map_insn_t& n = code[j];
+        if (j > k && !fused.count(j) && (n.op == CATENA_MAP_F32_ADD || n.op == CATENA_MAP_F32_SUB) && ((n.a == c.dst) != (n.b == c.dst))) fused[j] = k;
+    }
+    std::set<size_t> gone;
+    for (const auto& kv : fused) gone.insert(kv.second);
+    std::vector<catena_b200_map_insn_t> out;
+    for (size_t k = 0; k < code.size(); ++k) {
+        if (gone.count(k)) continue;
+        auto it = fused.find(k);
+        if (it == fused.end()) {
+            out.push_back(code[k]);
+            continue;
+        }
+        const catena_b200_map_insn_t &c = code[k], &m = code[it->second];
+        const uint16_t other = c.a == m.dst ? c.b : c.a;
+        const int op = c.op == CATENA_MAP_F32_ADD ? CATENA_MAP_F32_MULADD : (c.a == m.dst ? CATENA_MAP_F32_MULSUB : CATENA_MAP_F32_SUBMUL);
+        out.push_back(catena_b200_map_insn_t{(uint16_t)op, c.dst, m.a, m.b, other, 0, 0});
+    }
+    code.swap(out);
+}
+
 // Straight-line code only: every temporary is written once, so a register is free again after its last read.
 inline void reuse_registers(std::vector<catena_b200_map_insn_t>& code, uint32_t n_init, uint32_t index_reg, uint32_t* result_reg, uint32_t* n_regs) {
-    auto reads = [](const catena_b200_map_insn_t& c) {
-        std::vector<uint32_t> out;
-        if (c.op != CATENA_MAP_HALT && c.op != CATENA_MAP_JMP) out.push_back(c.a);
-        if (reads_b(c.op)) out.push_back(c.b);
-        if (reads_c(c.op)) out.push_back(c.c);
-        return out;
-    };
+    auto reads = [](const catena_b200_map_insn_t& c) { return reads_of(c); };
     std::map<uint32_t, size_t> last;
     for (size_t k = 0; k < code.size(); ++k)
         for (uint32_t r : reads(code[k])) last[r] = k;
@@ -508,7 +551,10 @@ inline Program compile(const std::vector<GpuModule>& modules, const std::string&
     prog.result_reg = result.reg;
     bool straight = true;
     for (const auto& c : prog.code) straight = straight && c.op != CATENA_MAP_JMP && c.op != CATENA_MAP_JZ;
-    if (straight) reuse_registers(prog.code, (uint32_t)presets.size(), prog.index_reg, &prog.result_reg, &prog.n_regs);
+    if (straight) {
+        fuse_mul_add(prog.code, prog.result_reg);
+        reuse_registers(prog.code, (uint32_t)presets.size(), prog.index_reg, &prog.result_reg, &prog.n_regs);
+    }
     // BufLen presets name buffer slots; launches index the environment
     for (Preset& p : presets)
         if (p.kind == Preset::BufLen)

@@ -91,6 +91,15 @@ static std::vector<GpuModule> fixtures() {
                   {A("mem.cast.f32", {v("ma", "mem")}, {u("alen"), pf("a")}), A("mem.cast.f32", {v("mb", "mem")}, {u("cols"), pf("b")}),
                    A("materializec", {u("rows"), pf("a"), pf("b"), u("cols"), fn("my.matvec-at")}, {pf("buf")}, {1, 3, 1}, {1}),
                    A("buf.to-mem", {u("rows"), pf("buf")}, {v("out", "mem")})}));
+    // straight-line f32 arithmetic: three products that feed exactly one sum or difference (fused by the compiler), one that feeds two
+    m.push_back(M("my.poly-at", {pf("x"), f("s"), u("i")}, {f("r")},
+                  {A("ix", {u("i"), pf("x")}, {f("xi")}), A("f32.mul", {f("xi"), f("s")}, {f("t1")}), A("f32.mul", {f("xi"), f("xi")}, {f("sq")}),
+                   A("f32.add", {f("t1"), f("xi")}, {f("t2")}), A("f32.mul", {f("t2"), f("t2")}, {f("t3")}), A("f32.sub", {f("s"), f("t3")}, {f("t4")}),
+                   A("f32.mul", {f("t4"), f("sq")}, {f("t5")}), A("f32.sub", {f("t5"), f("sq")}, {f("r")})}));
+    m.push_back(M("my.poly-map", {v("m", "mem"), f("s")}, {v("out", "mem")},
+                  {A("mem.cast.f32", {v("m", "mem")}, {u("len"), pf("x")}),
+                   A("materializec", {u("len"), pf("x"), f("s"), fn("my.poly-at")}, {pf("buf")}, {1, 2, 1}, {1}),
+                   A("buf.to-mem", {u("len"), pf("buf")}, {v("out", "mem")})}));
     // acc = acc * k + x[i] from 7: a fold over a buffer whose `add` is not associative (tests/lowered_fixtures.py: custom_fold_programs)
     m.push_back(M("my.horner-add", {u("k"), u("acc"), u("value")}, {u("r")},
                   {A("u64.mul", {u("acc"), u("k")}, {u("t")}), A("u64.add", {u("t"), u("value")}, {u("r")})}));
@@ -128,7 +137,7 @@ static void list(const std::string& name, const map_program::Program& p) {
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "list";
     const std::vector<GpuModule> mods = fixtures();
-    const char* names[] = {"materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec"};
+    const char* names[] = {"materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec", "my.poly-map"};
     if (mode == "list") {
         for (const char* n : names) list(n, map_program::for_assignment(mods, materializec_of(mods, n)));
         list("my.horner", map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0));
@@ -202,6 +211,30 @@ int main(int argc, char** argv) {
         catena_b200_mem_free(out);
         catena_b200_mem_free(ma);
         catena_b200_mem_free(mb);
+    }
+    {
+        const auto p = map_program::for_assignment(mods, materializec_of(mods, "my.poly-map"));
+        bool fused = false;
+        for (const auto& c : p.code) fused = fused || c.op == CATENA_MAP_F32_MULADD || c.op == CATENA_MAP_F32_SUBMUL || c.op == CATENA_MAP_F32_MULSUB;
+        CHECK(fused);
+        std::vector<float> x(777);
+        for (size_t i = 0; i < x.size(); ++i) x[i] = std::sin((float)i * 0.7f) * 3.0f;
+        const float sc = 1.25f;
+        catena_mem_t in = upload(x.data(), x.size() * 4), out{nullptr, 0};
+        CHECK(p.launch(x.size(), {map_program::EnvValue::mem(in), map_program::EnvValue::f32(sc)}, &out) == CATENA_OK);
+        std::vector<float> got(x.size());
+        CHECK(catena_b200_mem_download(out, got.data(), got.size() * 4) == CATENA_OK);
+        for (size_t i = 0; i < x.size(); ++i) {          // every operation rounded on its own (built with -ffp-contract=off)
+            volatile float t1 = x[i] * sc, sq = x[i] * x[i];
+            volatile float t2 = t1 + x[i];
+            volatile float t3 = t2 * t2;
+            volatile float t4 = sc - t3;
+            volatile float t5 = t4 * sq;
+            const float want = t5 - sq;
+            CHECK(std::memcmp(&want, &got[i], 4) == 0);
+        }
+        catena_b200_mem_free(out);
+        catena_b200_mem_free(in);
     }
     {
         // the sequential fold as a register program on one device thread

@@ -265,7 +265,16 @@ def custom_map_programs():
         A("mem.cast.f32", [v("ma", "mem")], [u("alen"), pf("a")]), A("mem.cast.f32", [v("mb", "mem")], [u("cols"), pf("b")]),
         A("materializec", [u("rows"), pf("a"), pf("b"), u("cols"), fn("my.matvec-at")], [pf("buf")], [1, 3, 1], [1]),
         A("buf.to-mem", [u("rows"), pf("buf")], [v("out", "mem")])])
-    return silu + [silu_at, silu_map, keep, low, clamp_at, clamp_map, add_env, term_at, cell_at, matvec]
+    # straight-line f32 arithmetic: three products that feed exactly one sum or difference (fused by the compiler), one that feeds two
+    poly_at = M("my.poly-at", [pf("x"), f("s"), u("i")], [f("r")], [
+        A("ix", [u("i"), pf("x")], [f("xi")]), A("f32.mul", [f("xi"), f("s")], [f("t1")]), A("f32.mul", [f("xi"), f("xi")], [f("sq")]),
+        A("f32.add", [f("t1"), f("xi")], [f("t2")]), A("f32.mul", [f("t2"), f("t2")], [f("t3")]), A("f32.sub", [f("s"), f("t3")], [f("t4")]),
+        A("f32.mul", [f("t4"), f("sq")], [f("t5")]), A("f32.sub", [f("t5"), f("sq")], [f("r")])])
+    poly_map = M("my.poly-map", [v("m", "mem"), f("s")], [v("out", "mem")], [
+        A("mem.cast.f32", [v("m", "mem")], [u("len"), pf("x")]),
+        A("materializec", [u("len"), pf("x"), f("s"), fn("my.poly-at")], [pf("buf")], [1, 2, 1], [1]),
+        A("buf.to-mem", [u("len"), pf("buf")], [v("out", "mem")])])
+    return silu + [silu_at, silu_map, keep, low, clamp_at, clamp_map, add_env, term_at, cell_at, matvec, poly_at, poly_map]
 
 
 # ---------------------------------------------------------------- folds over device buffers that match no fold kernel (user programs in

@@ -93,6 +93,9 @@ def run(program, env, length, buffers_host):
                 elif op == "F32_DIV": v = _b(_f(x) / _f(y))
                 elif op == "F32_NEG": v = (x ^ 0x80000000) & M32
                 elif op == "F32_FMA": v = _b(_libm.fmaf(float(_f(x)), float(_f(y)), float(_f(r[c]))))
+                elif op == "F32_MULADD": v = _b(np.float32(_f(x) * _f(y)) + _f(r[c]))
+                elif op == "F32_MULSUB": v = _b(np.float32(_f(x) * _f(y)) - _f(r[c]))
+                elif op == "F32_SUBMUL": v = _b(_f(r[c]) - np.float32(_f(x) * _f(y)))
                 elif op == "F32_EQ": v = int(_f(x) == _f(y))
                 elif op == "F32_NE": v = int(_f(x) != _f(y))
                 elif op == "F32_LT": v = int(_f(x) < _f(y))

@@ -74,7 +74,7 @@ def test_cpp_map_program_compiler_agrees_with_python(map_program_binary):
     assert p.returncode == 0, p.stdout + p.stderr
     mm = lo.module_map(fx.materialize_programs() + fx.custom_map_programs())
     lines = []
-    for name in ("materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec"):
+    for name in ("materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec", "my.poly-map"):
         [assign] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
         prog = lo.map_program_for(assign, mm)
         lines.append(f"program {name} regs={prog.n_regs} index={prog.index_reg} result={prog.result_reg} elem={prog.elem_bytes}")

@@ -7,7 +7,7 @@ import pytest
 import catena_lang_b200 as cb
 from catena_lang_b200 import lowering as lo
 from catena_lang_b200.evaluator import Evaluator
-from catena_lang_b200.map_program import compile_producer, OP
+from catena_lang_b200.map_program import compile_producer, OP, _OPS
 import lowered_fixtures as fx
 import map_vm
 import oracle as orc
@@ -158,3 +158,18 @@ def test_random_producers_compile_to_what_the_evaluator_computes(seed):
         [want] = ev.call(f"{name}.at", [sd, scale, table, xs, i])
         bits = int(want) if result == "u64" else int(np.float32(want).view(np.uint32))
         assert int(got[i]) == bits, (seed, i)
+
+
+def test_products_sink_into_the_sums_that_alone_read_them():
+    """F32_MUL + F32_ADD / F32_SUB as one instruction when the product has no other reader: fewer instructions, the same bits
+    (two roundings, not an fma)."""
+    prog, mm = program_of(fx.custom_map_programs(), "my.poly-map")
+    ops = [c.op for c in prog.code]
+    # x*s feeds one sum, (..)^2 one difference, t4*x^2 one difference; x^2 has two readers and stays a product
+    assert [_OPS[o] for o in ops] == ["LOAD_F32", "F32_MUL", "F32_MULADD", "F32_SUBMUL", "F32_MULSUB", "HALT"]
+    x = np.random.default_rng(9).normal(0, 3, 200).astype(np.float32)
+    got = map_vm.run(prog, [(0, x.nbytes), np.float32(1.25)], x.size, [x.view(np.uint8)]).astype(np.uint32)
+    ev = Evaluator(list({id(m): m for m in mm.values()}.values()))
+    for i in range(x.size):
+        [want] = ev.call("my.poly-at", [x, np.float32(1.25), i])
+        assert int(got[i]) == int(np.float32(want).view(np.uint32))
