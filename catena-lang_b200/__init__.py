@@ -140,6 +140,8 @@ def lib():
     proto("catena_b200_check_device_errors", st, [])
     proto("catena_b200_map_program_s", st, [vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32, C.c_uint32,
                                             u64, pm])
+    proto("catena_b200_map_program_range_s", st, [vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32, C.c_uint32,
+                                                  u64, u64, pm])
     pblk = C.POINTER(LlamaBlockStruct)
     proto("catena_b200_llama_workspace_bytes", u64, [pblk, u64])
     proto("catena_b200_llama_prefill", st, [pblk, vp, u64, u64, vp, vp, vp, vp, u64])

@@ -65,7 +65,7 @@ template <int REGS, int V, bool PARAM, int T>
 __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ ParamProgram prm, const uint4* __restrict__ code,
                                                           uint32_t n_insn, const uint64_t* __restrict__ init, uint32_t n_init, uint32_t n_regs,
                                                           uint32_t index_reg, uint32_t result_reg, const __grid_constant__ Buffers bufs,
-                                                          void* __restrict__ out, uint32_t elem_bytes, uint64_t len, uint32_t* err) {
+                                                          void* __restrict__ out, uint32_t elem_bytes, uint64_t index0, uint64_t len, uint32_t* err) {
     extern __shared__ uint4 s_dyn[];
     const uint4* s_code = s_dyn;
     // low halves: the V lanes of a register sit side by side, [register][thread][lane], so that one 16-byte access moves all
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(T) map_program_kernel(const __grid_constant__ 
         // element v of this trip is i + v * stride; past the end it repeats element i (valid), and is not stored
 #pragma unroll
         for (int v = 0; v < V; ++v) {
-            const uint64_t e = i + v * stride < len ? i + v * stride : i;
+            const uint64_t e = index0 + (i + v * stride < len ? i + v * stride : i);     // out[j] is element index0 + j
             lo(index_reg, v) = (uint32_t)e;
             hi[index_reg][v] = (uint32_t)(e >> 32);
         }
@@ -364,6 +364,12 @@ extern "C" {
 catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, uint32_t n_init,
                                           uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, const catena_mem_t* buffers,
                                           uint32_t n_buffers, uint32_t elem_bytes, uint64_t len, catena_mem_t* out) {
+    return catena_b200_map_program_range_s(code, n_insn, init, n_init, n_regs, index_reg, result_reg, buffers, n_buffers, elem_bytes, 0, len, out);
+}
+
+catena_status_t catena_b200_map_program_range_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, uint32_t n_init,
+                                                uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, const catena_mem_t* buffers,
+                                                uint32_t n_buffers, uint32_t elem_bytes, uint64_t index0, uint64_t len, catena_mem_t* out) {
     if (!out) return fail(CATENA_E_BAD_ARG, "map program: null output pointer");
     out->data = nullptr;
     out->len = 0;
@@ -377,7 +383,7 @@ catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, ui
         bufs.base[k] = static_cast<const uint8_t*>(buffers[k].data);
         bufs.bytes[k] = buffers[k].len;
     }
-    if (len > (~0ull) / elem_bytes) return fail(CATENA_E_TOO_LARGE, "map program: length overflows");
+    if (len > (~0ull) / elem_bytes || index0 > ~0ull - len) return fail(CATENA_E_TOO_LARGE, "map program: length overflows");
     CATENA_TRY(ensure_device());
     if (len == 0) return CATENA_OK;                        // no allocation, no launch (materializec.rs:108-116)
     mapvm::State* st = nullptr;
@@ -434,7 +440,7 @@ catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, ui
         }                                                                                                                           \
         if (e == cudaSuccess)                                                                                                       \
             mapvm::map_program_kernel<R, V, P, TT><<<(unsigned)blocks, TT, smem, stream>>>(                                         \
-                prm, dcode, n_insn, dinit, n_init, n_regs, index_reg, result_reg, bufs, result, elem_bytes, len, st->err);          \
+                prm, dcode, n_insn, dinit, n_init, n_regs, index_reg, result_reg, bufs, result, elem_bytes, index0, len, st->err);          \
     } while (0)
 #define CATENA_MAP_PICK(R)                                                   \
     do {                                                                     \

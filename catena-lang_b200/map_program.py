@@ -102,16 +102,17 @@ class MapProgram:
                 buffers.append((int(value[0] or 0), int(value[1])))
         return init, buffers
 
-    def launch(self, length, env):
-        """out[i] = producer(env..., i) for i < length on the device; returns the library's CatenaMem (owned by the caller)."""
+    def launch(self, length, env, index0=0):
+        """out[j] = producer(env..., index0 + j) for j < length on the device; returns the library's CatenaMem (owned by the
+        caller).  `index0` is how a map shards over GPUs: contiguous index ranges, the same program on every rank."""
         from . import CatenaMem, check, lib
         init, buffers = self.init_registers(env)
         code = (Insn * len(self.code))(*self.code)
         init_arr = (C.c_uint64 * max(1, len(init)))(*init)
         bufs = (CatenaMem * max(1, len(buffers)))(*[CatenaMem(p, n) for p, n in buffers])
         out = CatenaMem()
-        check(lib().catena_b200_map_program_s(code, len(self.code), init_arr, len(init), self.n_regs, self.index_reg, self.result_reg,
-                                              bufs, len(buffers), self.elem_bytes, int(length), C.byref(out)))
+        check(lib().catena_b200_map_program_range_s(code, len(self.code), init_arr, len(init), self.n_regs, self.index_reg, self.result_reg,
+                                                    bufs, len(buffers), self.elem_bytes, int(index0), int(length), C.byref(out)))
         return out
 
 

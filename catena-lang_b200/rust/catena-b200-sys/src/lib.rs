@@ -107,6 +107,9 @@ extern "C" {
     pub fn catena_b200_map_program_s(code: *const catena_b200_map_insn_t, n_insn: u32, init: *const u64, n_init: u32, n_regs: u32,
                                      index_reg: u32, result_reg: u32, buffers: *const catena_mem_t, n_buffers: u32,
                                      elem_bytes: u32, len: u64, out: *mut catena_mem_t) -> catena_status_t;
+    pub fn catena_b200_map_program_range_s(code: *const catena_b200_map_insn_t, n_insn: u32, init: *const u64, n_init: u32, n_regs: u32,
+                                           index_reg: u32, result_reg: u32, buffers: *const catena_mem_t, n_buffers: u32,
+                                           elem_bytes: u32, index0: u64, len: u64, out: *mut catena_mem_t) -> catena_status_t;
     pub fn catena_b200_sum_f32_noalloc(input: *const c_void, n: u64, out: *mut c_void) -> catena_status_t;
     // Llama-style block (device pointers throughout)
     pub fn catena_b200_llama_workspace_bytes(blk: *const catena_llama_block_t, tokens: u64) -> u64;

@@ -95,6 +95,24 @@ def unit_ranges(units, world):
     return [UnitRange(r, units * r // world, units * (r + 1) // world) for r in range(world)]
 
 
+@dataclass(frozen=True)
+class IndexRange:
+    rank: int
+    i0: int
+    i1: int
+
+
+def index_ranges(n, world, align=1):
+    """Contiguous ranges of the n independent elements of a map (`materializec`: out[i] = f(env, i)) per rank, boundaries on
+    multiples of `align` elements.  Every rank runs the same kernel — or the same register program with its range's first
+    index (`MapProgram.launch(i1 - i0, env, index0=i0)`) — so the bits do not depend on the world size; `gather_units` with a
+    row width of 1 assembles the ranges."""
+    if world <= 0:
+        raise ValueError("world must be positive")
+    chunks = (n + align - 1) // align
+    return [IndexRange(r, min(n, chunks * r // world * align), min(n, chunks * (r + 1) // world * align)) for r in range(world)]
+
+
 def gather_columns(local_block, blocks, rows, dist=None, group=None):
     """All-gathers row-major column blocks [rows, n1-n0] into the full [rows, N] matrix.
     `local_block` is a torch tensor on this rank's device; returns the assembled tensor on every rank."""
@@ -112,12 +130,13 @@ def gather_columns(local_block, blocks, rows, dist=None, group=None):
 
 
 def gather_units(local_rows, ranges, row_width, dist=None, group=None, out=None):
-    """All-gathers per-unit output rows (attention O) in unit order; `out` as in gather_rows."""
+    """All-gathers per-unit output rows (attention O) in unit order — or the elements of a map sharded by `index_ranges`, as
+    rows of width 1; `out` as in gather_rows."""
     import torch
     if dist is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return local_rows
     local_rows, was_int16 = _as_wire(local_rows)
-    counts = [r.u1 - r.u0 for r in ranges]
+    counts = [(r.u1 - r.u0) if isinstance(r, UnitRange) else (r.i1 - r.i0) for r in ranges]
     if len(set(counts)) == 1:                                  # equal ranges: one collective straight into place
         full = _as_wire(out)[0] if out is not None else torch.empty((sum(counts), row_width), dtype=local_rows.dtype, device=local_rows.device)
         dist.all_gather_into_tensor(full, local_rows.contiguous(), group=group)

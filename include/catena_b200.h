@@ -241,6 +241,11 @@ typedef struct {
 catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, uint32_t n_init,
                                           uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, const catena_mem_t* buffers,
                                           uint32_t n_buffers, uint32_t elem_bytes, uint64_t len, catena_mem_t* out);
+/* The same for the index range [index0, index0 + len): out[j] = producer(env..., index0 + j).  Elements are independent, so a
+ * map shards over GPUs by contiguous index ranges (catena-lang_b200/shard.py: index_ranges); every rank runs the same program. */
+catena_status_t catena_b200_map_program_range_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, uint32_t n_init,
+                                                uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, const catena_mem_t* buffers,
+                                                uint32_t n_buffers, uint32_t elem_bytes, uint64_t index0, uint64_t len, catena_mem_t* out);
 
 /* ---- programs with no counterpart in the reference (it has no bf16, int8 or attention);
  *      same calling convention; semantics composed from the reference's rules -------------- */

@@ -61,8 +61,9 @@ struct Program {
     uint32_t n_regs = 1, index_reg = 0, result_reg = 0, elem_bytes = 8;
     std::vector<bool> env_is_buffer;       // one entry per runtime environment value
 
-    // out[i] = producer(env..., i) for i < len on the device; *out is owned by the caller (catena_b200_mem_free).
-    catena_status_t launch(uint64_t len, const std::vector<EnvValue>& env, catena_mem_t* out) const {
+    // out[j] = producer(env..., index0 + j) for j < len on the device; *out is owned by the caller (catena_b200_mem_free).
+    // `index0` is how a map shards over GPUs: contiguous index ranges, the same program on every rank.
+    catena_status_t launch(uint64_t len, const std::vector<EnvValue>& env, catena_mem_t* out, uint64_t index0 = 0) const {
         if (env.size() != env_is_buffer.size()) return CATENA_E_BAD_ARG;
         std::vector<uint64_t> init;
         std::vector<catena_mem_t> buffers;
@@ -73,8 +74,8 @@ struct Program {
         }
         for (size_t k = 0; k < env.size(); ++k)
             if (env_is_buffer[k]) buffers.push_back(env[k].buffer);
-        return catena_b200_map_program_s(code.data(), (uint32_t)code.size(), init.data(), (uint32_t)init.size(), n_regs, index_reg, result_reg,
-                                         buffers.data(), (uint32_t)buffers.size(), elem_bytes, len, out);
+        return catena_b200_map_program_range_s(code.data(), (uint32_t)code.size(), init.data(), (uint32_t)init.size(), n_regs, index_reg,
+                                               result_reg, buffers.data(), (uint32_t)buffers.size(), elem_bytes, index0, len, out);
     }
 };
 

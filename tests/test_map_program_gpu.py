@@ -252,3 +252,33 @@ def test_random_producers_on_the_device(seed, control):
     prog = lo.map_program_for(launch, mm)
     want = map_vm.run(prog, [sd, scale, (0, table.nbytes), (0, xs.nbytes)], n, [table.view(np.uint8), xs.view(np.uint8)])
     assert np.array_equal(got, want.astype(got.dtype))
+
+
+def test_a_map_sharded_by_index_ranges_gives_the_unsharded_bits():
+    """Elements of a map are independent, so it shards over GPUs by contiguous index ranges, every rank running the same
+    register program with its range's first index: the ranges of 1, 2, 4 and 8 ranks, run here one after the other on one
+    GPU, concatenate to the unsharded result (an index-dependent integer producer and a buffer-reading f32 producer)."""
+    from catena_lang_b200 import shard
+    import random_programs as rp
+    for seed, result in ((200, "u64"), (201, "f32")):
+        mods, name = rp.generate(seed, n_ops=50, result=result, control=False)
+        mm = lo.module_map(mods)
+        [launch] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+        prog = lo.map_program_for(launch, mm)
+        table, xs = rp.tables(seed)
+        mt, mx = cb.upload(table), cb.upload(xs)
+        env = [77 + seed, np.float32(2.5), (mt.data, mt.len), (mx.data, mx.len)]
+        dtype = np.uint64 if result == "u64" else np.uint32
+        n = 10_007
+        whole = prog.launch(n, env)
+        want = cb.download(whole, dtype)
+        cb.free(whole)
+        for world in (2, 4, 8):
+            parts = []
+            for r in shard.index_ranges(n, world, align=4):
+                raw = prog.launch(r.i1 - r.i0, env, index0=r.i0)
+                parts.append(cb.download(raw, dtype))
+                cb.free(raw)
+            assert np.array_equal(np.concatenate(parts), want)
+        cb.free(mt)
+        cb.free(mx)

@@ -50,6 +50,13 @@ def _worker(rank, world, port, out_dir):
     ranges = shard.unit_ranges(units, world)
     got = shard.gather_units(rows[ranges[rank].u0:ranges[rank].u1].clone(), ranges, width, dist)
     assert torch.equal(got, rows)
+    # a map sharded by index ranges: every rank produces its range of out[i] = f(i), the gather puts them in order
+    total = 1001
+    iranges = shard.index_ranges(total, world, align=4)
+    mine_i = iranges[rank]
+    local_i = (torch.arange(mine_i.i0, mine_i.i1, dtype=torch.float32) * 3 + 1).reshape(-1, 1)
+    got_i = shard.gather_units(local_i, iranges, 1, dist)
+    assert torch.equal(got_i.reshape(-1), torch.arange(total, dtype=torch.float32) * 3 + 1)
     worst = shard.max_over_ranks(1.0 + rank, dist)
     assert worst == float(world)
     dist.barrier()
@@ -69,6 +76,8 @@ def test_plans_are_tile_aligned_and_cover():
             rows = shard.row_blocks(n, world)
             assert rows[0].m0 == 0 and rows[-1].m1 == n
             assert all(x.m1 == y.m0 and (x.m1 % 256 == 0 or x.m1 == n) for x, y in zip(rows, rows[1:]))
+            idx = shard.index_ranges(n, world, align=4)
+            assert idx[0].i0 == 0 and idx[-1].i1 == n and all(x.i1 == y.i0 and (x.i1 % 4 == 0 or x.i1 == n) for x, y in zip(idx, idx[1:]))
             ranges = shard.unit_ranges(256, world)
             assert ranges[0].u0 == 0 and ranges[-1].u1 == 256
             assert all(x.u1 == y.u0 for x, y in zip(ranges, ranges[1:]))
