@@ -111,7 +111,7 @@ catena_status_t launch_attn_decode(const void* q, const void* kc, const void* vc
                                    const AttnPrefetch* prefetch = nullptr);
 catena_status_t attn_check_errors();
 // llama_decode_fused.cu: the part of a decode step after its attention as one persistent kernel
-int decode_fused_mode();      // bit 0: the tail kernel, bit 1: the head kernel
+int decode_fused_mode();      // bit 0: the tail kernel, bit 1: the head kernel, bit 2: rotation + cache append in the q/k/v projection's epilogue
 void decode_fused_set_mode(int mode);
 bool decode_tail_supported(uint64_t m, uint64_t hidden, uint64_t ko, uint64_t ffn);
 catena_status_t launch_decode_tail(const void* att, const void* x, const void* w_o, const void* w_gate_up, const void* w_down, void* x2,

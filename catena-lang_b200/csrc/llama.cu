@@ -267,6 +267,30 @@ __global__ void __launch_bounds__(256, kSkinnyCtasPerSm) skinny_gemm_kernel(cons
     skinny_run<A_READONLY>(job, sc, part, cur);
 }
 
+// The q/k/v projection of a decode step with the rotation and the cache append in its epilogue (skinny.cuh: SkinnyRope): one
+// launch instead of the projection followed by rope_append_small_kernel, the same bits.  The (cos, sin) of the CTA's pairs
+// depend on the step's position only, so they are evaluated before the wait for the predecessor, like the first weights.
+__global__ void __launch_bounds__(256, kSkinnyCtasPerSm) skinny_qkv_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                                uint32_t M, uint32_t N, uint32_t K, SkinnyRope rope,
+                                                                                const float* __restrict__ inv_freq) {
+    __shared__ float part[8][16][8];
+    __shared__ float pairs[16][8];
+    __shared__ float2 cs_tab[kSkinnyRopeGroups * 4];
+    SkinnyJob job = {x, w, nullptr, nullptr, M, N, K, 0u, rope};
+    job.rope.cs = cs_tab;
+    const SkinnySchedule sc(job, blockIdx.x, gridDim.x);
+    uint4 cur[kSkinnyUnroll];
+    pdl_trigger();
+    if (sc.steps > 0) skinny_load_w<true>(job, sc, 0, cur);
+    const uint32_t my_groups = sc.steps / sc.batches;
+    if (threadIdx.x < my_groups * 4 && threadIdx.x < kSkinnyRopeGroups * 4) {
+        const uint32_t grp = blockIdx.x + (threadIdx.x >> 2) * gridDim.x, i = (grp & 15u) * 4 + (threadIdx.x & 3u);
+        cs_tab[threadIdx.x] = rope_cos_sin(rope.pos, inv_freq[i]);
+    }
+    pdl_wait();
+    skinny_run<A_READONLY, true>(job, sc, part, cur, pairs);
+}
+
 // ---------------------------------------------------------------- causal prefill attention (mma.sync)
 // q [T, Hq, 128] bf16 (rotated), k/v cache [B, Hkv, cap, 128] bf16, out [T, Hq * 128] bf16; token t = b * S + s
 // attends to cache positions 0..s of its sequence.  One CTA (4 warps) per 64 queries of one head; warp w owns
@@ -667,6 +691,29 @@ static catena_status_t launch_rope_append(const void* qkv, void* q_out, void* k_
                       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, inv,
                       (uint32_t)tokens, (uint32_t)seq, (uint32_t)pos0, (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap);
 }
+// A decode step's q/k/v projection with rotation and cache append in the epilogue; false when the shape has to take the
+// projection followed by launch_rope_append.
+static bool qkv_rope_skinny_fusable(uint64_t tokens, uint64_t seq, uint64_t hq, uint64_t hkv, uint64_t hidden) {
+    if (seq != 1 || tokens == 0 || tokens > 16 || hidden == 0 || hidden % 8 || hidden > 0x7FFFFFFFull || hq + 2 * hkv > 0xFFFFull) return false;
+    const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+    const uint64_t groups = (hq + 2 * hkv) * 16, slots = (uint64_t)sms * llama::kSkinnyCtasPerSm;
+    return ceil_div_u64(groups, slots) <= (uint64_t)llama::kSkinnyRopeGroups;
+}
+static catena_status_t launch_qkv_rope_skinny(const void* x, const void* w_qkv, void* q_out, void* k_cache, void* v_cache, uint64_t tokens,
+                                              uint64_t pos, uint64_t hq, uint64_t hkv, uint64_t cap, uint64_t hidden, float base) {
+    if (pos >= cap || cap > 0xFFFFFFFFull) return fail(CATENA_E_BAD_ARG, "rope: positions beyond the cache capacity");
+    if (((uintptr_t)x | (uintptr_t)w_qkv) & 15) return fail(CATENA_E_BAD_ARG, "linear: operands must be 16-byte aligned");
+    const float* inv = nullptr;
+    CATENA_TRY(rope_table(base, &inv));
+    const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
+    const uint64_t groups = (hq + 2 * hkv) * 16, slots = (uint64_t)sms * llama::kSkinnyCtasPerSm;
+    const uint64_t rounds = ceil_div_u64(groups, slots);
+    llama::SkinnyRope rope = {(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nullptr,
+                              (uint32_t)hq, (uint32_t)hkv, (uint32_t)cap, (uint32_t)pos};
+    return launch_pdl("skinny_qkv_rope_kernel", llama::skinny_qkv_rope_kernel, dim3((unsigned)ceil_div_u64(groups, rounds)), dim3(256), 0,
+                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_qkv, (uint32_t)tokens, (uint32_t)((hq + 2 * hkv) * llama::kHeadDim),
+                      (uint32_t)hidden, rope, inv);
+}
 // Kernel selection for the prefill attention: the tcgen05 kernel (attn_prefill_tc.cu) unless CATENA_B200_PREFILL_TC=0
 // (read once) or the test hook asks for the mma.sync kernel of this file; both implement the same semantics.
 bool attn_prefill_tc_supports(const void* q, const void* k_cache, const void* v_cache, uint64_t hq, uint64_t hkv);
@@ -833,6 +880,8 @@ static catena_status_t run_block(const catena_llama_block_t* blk, const int32_t*
         CATENA_TRY(launch_embed_rmsnorm(blk->embedding, ids, x, nrm, T, d.H, blk->vocab));
         if (qkv_rope_fusable(T, seq, d.Hq, d.Hkv) && !(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)) {
             CATENA_TRY(launch_qkv_rope(nrm, blk->w_qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, d.H, blk->rope_base));
+        } else if ((decode_fused_mode() & 4) && qkv_rope_skinny_fusable(T, seq, d.Hq, d.Hkv, d.H)) {
+            CATENA_TRY(launch_qkv_rope_skinny(nrm, blk->w_qkv, q, k_cache, v_cache, T, pos0, d.Hq, d.Hkv, blk->max_len, d.H, blk->rope_base));
         } else {
             CATENA_TRY(launch_linear(nrm, blk->w_qkv, nullptr, qkv, T, d.qkv_cols, d.H));
             CATENA_TRY(launch_rope_append(qkv, q, k_cache, v_cache, T, seq, pos0, d.Hq, d.Hkv, blk->max_len, blk->rope_base));

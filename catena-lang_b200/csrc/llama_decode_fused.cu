@@ -279,16 +279,18 @@ struct FusedState {
 };
 static thread_local FusedState g_fused[kMaxDevices];
 
+constexpr int kDecodeModeDefault = 4;   // rotation + cache append in the q/k/v projection's epilogue: 60.8 against 63.1 us per step
 static int g_decode_fused_mode = -1;
-// Off by default (see the measurements at the top); CATENA_B200_DECODE_FUSED=1..3 (read once) or the test hook selects it.
+// The persistent kernels are off by default (see the measurements at the top); CATENA_B200_DECODE_FUSED=0..7 (read once) or the
+// test hook selects the bits: 1 tail kernel, 2 head kernel, 4 rotation + cache append in the q/k/v projection's epilogue (default).
 int decode_fused_mode() {
     if (g_decode_fused_mode < 0) {
         const char* e = getenv("CATENA_B200_DECODE_FUSED");
-        g_decode_fused_mode = (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 0;
+        g_decode_fused_mode = (e && e[0] >= '0' && e[0] <= '7' && e[1] == 0) ? e[0] - '0' : kDecodeModeDefault;
     }
     return g_decode_fused_mode;
 }
-void decode_fused_set_mode(int mode) { g_decode_fused_mode = mode & 3; }
+void decode_fused_set_mode(int mode) { g_decode_fused_mode = mode < 0 ? -1 : (mode & 7); }   // negative: back to the default
 
 // True when launch_decode_tail takes this shape.
 bool decode_tail_supported(uint64_t m, uint64_t hidden, uint64_t ko, uint64_t ffn) {

@@ -311,7 +311,7 @@ void catena_b200_debug_set_cta_limit(int limit) {
 
 void catena_b200_debug_set_gemm_pair(int on) { gemm_tc_set_pair_mode(on); }
 void catena_b200_debug_set_attn_tc(int on) { attn_set_tc_mode(on); }
-void catena_b200_debug_set_decode_fused(int on) { decode_fused_set_mode(on ? 3 : 0); }
+void catena_b200_debug_set_decode_fused(int mode) { decode_fused_set_mode(mode); }
 void catena_b200_debug_attn_last_launch(uint32_t out[4]) { attn_last_launch(out); }
 catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]) {
     if (!out) return fail(CATENA_E_BAD_ARG, "rcp check: null argument");

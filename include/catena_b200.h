@@ -384,11 +384,13 @@ void catena_b200_debug_set_gemm_pair(int on);
 /* test hook: 1 = decode attention on the tcgen05 kernel, 0 = on the mma.sync kernel (same semantics).
  * No counterpart in the reference. */
 void catena_b200_debug_set_attn_tc(int on);
-/* test hook: 1 = a decode step of the Llama-style block runs as three launches (one persistent kernel before its attention:
- * embedding, norm, q/k/v projection, rotation, cache append; one after it: o projection, norm, gate/up + SwiGLU, down
- * projection), 0 = as eight launches chained by programmatic dependent launch (the default: measured faster).  Both give
- * bit-identical results.  No counterpart in the reference. */
-void catena_b200_debug_set_decode_fused(int on);
+/* test hook: which kernels a decode step of the Llama-style block uses, as bits (a negative value: back to the default).
+ * 1 = everything after the attention (o projection, norm, gate/up + SwiGLU, down projection) as one persistent kernel with
+ * grid barriers; 2 = everything before it (embedding, norm, q/k/v projection, rotation, cache append) likewise — both measured
+ * slower than launches chained by programmatic dependent launch; 4 = rotation and cache append in the epilogue of the q/k/v
+ * projection instead of a launch of their own.  Every combination gives bit-identical results.  No counterpart in the
+ * reference. */
+void catena_b200_debug_set_decode_fused(int mode);
 /* test hook: 1 = prefill attention on the tcgen05 kernel (the default), 0 = on the mma.sync kernel (same semantics).
  * No counterpart in the reference. */
 void catena_b200_debug_set_prefill_tc(int on);

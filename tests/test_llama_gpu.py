@@ -310,19 +310,21 @@ def test_block_prefill_fused_epilogues_equal_separate_kernels():
 @pytest.mark.parametrize("hidden,n_heads,n_kv_heads,ffn,B", [(256, 2, 1, 512, 2), (2048, 16, 16, 8192, 4), (272, 3, 3, 1040, 16),
                                                              (512, 4, 2, 304, 1), (1024, 8, 8, 2048, 7)])
 def test_decode_step_fused_kernels_equal_separate_launches(hidden, n_heads, n_kv_heads, ffn, B):
-    """On request a decode step runs as three launches — one persistent kernel before the attention (embedding, norm, q/k/v projection,
-    rotation, cache append) and one after it (o projection, norm, gate/up + SwiGLU, down projection), with grid barriers
-    between their phases — instead of the default eight.  The arithmetic is the separate kernels' (same k split over the warps, same
-    summation trees, same roundings), so outputs and caches are equal bit for bit over several steps — including shapes
-    with fewer row groups than CTAs, partial k batches and 16 rows."""
+    """A decode step can run on other kernels than the default ones: with the rotation and the cache append in the epilogue
+    of the q/k/v projection (mode 4) or as launches of their own (mode 0); and as three launches — one persistent kernel
+    before the attention (embedding, norm, q/k/v projection, rotation, cache append) and one after it (o projection, norm,
+    gate/up + SwiGLU, down projection), with grid barriers between their phases (mode 3, or 5 with the first half chained).
+    The arithmetic is the same everywhere (same k split over the warps, same summation trees, same roundings), so outputs
+    and caches are equal bit for bit over several steps — including shapes with fewer row groups than CTAs, partial k
+    batches and 16 rows."""
     vocab, max_len, S = 300, 48, 20
     rng = np.random.default_rng(13)
     weights = make_block(rng, hidden, n_heads, n_kv_heads, ffn, vocab)
     ids = rng.integers(0, vocab, B * S).astype(np.int32)
     steps = [rng.integers(0, vocab, B).astype(np.int32) for _ in range(3)]
     results = []
-    for fused in (1, 0):
-        cb.lib().catena_b200_debug_set_decode_fused(fused)
+    for mode in (0, 4, 3, 5):
+        cb.lib().catena_b200_debug_set_decode_fused(mode)
         blk = cb.LlamaBlock(hidden, n_heads, n_kv_heads, ffn, vocab, max_len, weights, B)
         try:
             blk.prefill(ids, S, download=False)
@@ -330,9 +332,10 @@ def test_decode_step_fused_kernels_equal_separate_launches(hidden, n_heads, n_kv
             results.append(outs + list(blk.caches()))
         finally:
             blk.close()
-            cb.lib().catena_b200_debug_set_decode_fused(0)
-    for a, b in zip(*results):
-        assert np.array_equal(a, b)
+            cb.lib().catena_b200_debug_set_decode_fused(-1)         # back to the default
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            assert np.array_equal(a, b)
 
 
 def test_block_argument_errors():
