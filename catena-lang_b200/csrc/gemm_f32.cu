@@ -26,6 +26,10 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     const int ty = tid / (BN / TN);   // row group
     const int row0 = blockIdx.y * BM;
     const int col0 = blockIdx.x * BN;
+    // columns of this thread's register tile: TN consecutive ones, or — for the 8-wide tile — 4 + 4 half a tile apart, so that
+    // a warp's 16-byte reads of a Bs row are contiguous (conflict-free) instead of 32 bytes apart (4-way conflicts)
+    constexpr bool SPLIT = TN == 8;
+    auto col_of = [&](int j) { return SPLIT ? (j / 4) * (BN / 2) + tx * 4 + (j % 4) : tx * TN + j; };
 
     float acc[TM][TN];
 #pragma unroll
@@ -71,13 +75,14 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         if (k0 + BK < k) fetch(k0 + BK);
         __syncthreads();
         if (kb == BK) {
-#pragma unroll
+            // the 8 x 8 tile's body is 132 instructions per kk: unrolled four times it stays inside the instruction cache
+#pragma unroll(TM * TN >= 64 ? 4 : BK)
             for (int kk = 0; kk < BK; ++kk) {
                 float a[TM], b[TN];
 #pragma unroll
                 for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
 #pragma unroll
-                for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+                for (int j = 0; j < TN; ++j) b[j] = Bs[kk][col_of(j)];
 #pragma unroll
                 for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -89,7 +94,7 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
                 for (int i = 0; i < TM; ++i)
 #pragma unroll
                     for (int j = 0; j < TN; ++j)
-                        acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(As[kk][ty * TM + i], Bs[kk][tx * TN + j]));
+                        acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(As[kk][ty * TM + i], Bs[kk][col_of(j)]));
             }
         }
         __syncthreads();
@@ -100,7 +105,7 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         if (gr >= n) continue;
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
-            int gc = col0 + tx * TN + j;
+            int gc = col0 + col_of(j);
             if (gc < m) C[(size_t)gr * m + gc] = acc[i][j];
         }
     }
@@ -128,10 +133,16 @@ catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint
     cudaStream_t st = tls().stream;
     int sms = tls().sm_count > 0 ? tls().sm_count : 148;
     uint64_t big_tiles = ceil_div_u64(n, 64) * ceil_div_u64(m, 64);
+    const uint64_t huge_tiles = ceil_div_u64(n, 128) * ceil_div_u64(m, 128);
     // row tiles ride on grid.y (at most 65535): 4 194 240 rows with the 64-row tiles; taller products are refused, not mis-launched
     if (ceil_div_u64(n, big_tiles >= (uint64_t)sms ? 64 : 16) > 65535)
         return fail(CATENA_E_TOO_LARGE, "matmul f32: more than 65535 row tiles (4194240 rows)");
-    if (big_tiles >= (uint64_t)sms) {
+    if (huge_tiles >= 2 * (uint64_t)sms) {
+        // large products are bound by instruction issue (two FP instructions per multiply-add, by contract): an 8 x 8 register
+        // tile spends 4 shared-memory loads per 128 of them where the 4 x 4 tile spends 2 per 32
+        dim3 grid((unsigned)ceil_div_u64(m, 128), (unsigned)ceil_div_u64(n, 128));
+        matmul_f32_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+    } else if (big_tiles >= (uint64_t)sms) {
         dim3 grid((unsigned)ceil_div_u64(m, 64), (unsigned)ceil_div_u64(n, 64));
         matmul_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
     } else {

@@ -53,8 +53,10 @@ def test_matmul_reference_vectors(rt):
 
 
 @pytest.mark.parametrize("n,m,k", [(256, 256, 256), (1, 1, 1), (37, 53, 29), (130, 70, 257), (64, 64, 1),
-                                   (640, 1280, 96), (1000, 900, 515)])
+                                   (640, 1280, 96), (1000, 900, 515), (2200, 2250, 67)])
 def test_matmul_bit_exact(rt, orc, n, m, k):
+    """Every tile shape gives the oracle's bits: 16 x 16 tiles (small products), 64 x 64 with a 4 x 4 register tile, and — from
+    296 tiles of 128 x 128 on — an 8 x 8 register tile (the last case, with ragged edges and a partial k slab)."""
     rng = np.random.default_rng(0)
     a = rng.uniform(-1, 1, (n, k)).astype(np.float32)
     b = rng.uniform(-1, 1, (k, m)).astype(np.float32)
