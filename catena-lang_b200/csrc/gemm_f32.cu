@@ -19,8 +19,8 @@ __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int n, int m,
                   int k) {
     constexpr int THREADS = (BM / TM) * (BN / TN);
-    __shared__ float As[BK][BM + 4];  // transposed: As[kk][row]
-    __shared__ float Bs[BK][BN + 4];
+    __shared__ __align__(16) float As[BK][BM + 4];  // transposed: As[kk][row]; rows are 16-byte multiples apart
+    __shared__ __align__(16) float Bs[BK][BN + 4];
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN);   // column group
     const int ty = tid / (BN / TN);   // row group
@@ -79,10 +79,20 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
 #pragma unroll(TM * TN >= 64 ? 4 : BK)
             for (int kk = 0; kk < BK; ++kk) {
                 float a[TM], b[TN];
+                if (SPLIT) {      // four 16-byte loads for the 8 + 8 operands
+                    const float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * TM]), a1 = *reinterpret_cast<const float4*>(&As[kk][ty * TM + 4]);
+                    const float4 b0 = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]), b1 = *reinterpret_cast<const float4*>(&Bs[kk][BN / 2 + tx * 4]);
+                    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-                for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+                    for (int i = 0; i < TM; ++i) a[i] = av[i % 8];
 #pragma unroll
-                for (int j = 0; j < TN; ++j) b[j] = Bs[kk][col_of(j)];
+                    for (int j = 0; j < TN; ++j) b[j] = bv[j % 8];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) b[j] = Bs[kk][col_of(j)];
+                }
 #pragma unroll
                 for (int i = 0; i < TM; ++i)
 #pragma unroll
