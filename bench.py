@@ -428,7 +428,7 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
     bit-exact f32 matmul (mul and add are separate instructions by contract: one flop per lane per clock)."""
     out = {}
     fp32_unfused_peak = 148 * 128 * sm_max_mhz * 1e6 / 1e12
-    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("map_program", False), ("softmax", False),
+    for which, small in (("matmul_f32", True), ("matmul_f32", False), ("map", False), ("map_program", False), ("map_interpreted", False), ("softmax", False),
                          ("rmsnorm", False), ("sum_u64", False), ("dot_u64", False)):
         step, work, unit, desc = single_case(cb, L, torch, dev, which, small, None)
         steps = 200 if (which == "matmul_f32" and small) else (16 if which == "matmul_f32" else 20)
@@ -461,10 +461,13 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
             roof = {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": value / peaks["hbm_gbs"],
                     "peak_source": f"{peaks['source']} copy bandwidth"}
         name = {"matmul_f32": "matmul_f32_256" if small else "matmul_f32_4096", "map": "map_nn_silu_64Mi",
-                "map_program": "map_program_nn_silu_64Mi"}.get(which, which + "_64Mi")
+                "map_program": "map_program_nn_silu_64Mi", "map_interpreted": "map_interpreted_nn_silu_64Mi"}.get(which, which + "_64Mi")
         if which == "map_program":
-            roof["note"] = ("the generic path for producers without a prebuilt kernel: bound by the interpreter's instruction issue, "
-                            "not by HBM; the same function as map_nn_silu_64Mi, bit for bit")
+            roof["note"] = ("the generic path for producers without a prebuilt kernel: the producer's register program as a kernel of "
+                            "its own (PTX written by the library, compiled by the driver); the same function as map_nn_silu_64Mi, bit for bit")
+        if which == "map_interpreted":
+            roof["note"] = ("the same register program on the library's interpreter (the cross-check of the compiled kernel): bound by "
+                            "the interpreter's instruction issue, not by HBM; same bits")
         if which in ("sum_u64", "dot_u64"):
             roof["note"] = "each step is a whole program call: two kernels, an 8-byte copy back and a stream synchronisation"
         out[name] = {"case": desc, "us_per_launch": ms * 1e3, "value": value, "unit": unit, "steps": steps, "sm_mhz": sampled_mhz, "roofline": roof}
@@ -870,9 +873,10 @@ def single_case(cb, L, torch, dev, which, small, shape, units=0):
         y = torch.empty((2, n), device=dev)
 
         program = None
-        if which == "map_program":
+        if which in ("map_program", "map_interpreted"):
             # nn.silu again, but as a user's `materializec` producer would arrive: lowered modules of the stdlib programs
-            # (exp~ from its primitives), compiled to a register program and interpreted by the generic map kernel
+            # (exp~ from its primitives), compiled to a register program; that program runs as a kernel of its own
+            # (map_program) or on the generic map kernel's interpreter (map_interpreted)
             from catena_lang_b200 import lowering as lo
             from catena_lang_b200.lowered_stdlib import silu_modules
             mods = silu_modules()
@@ -887,7 +891,8 @@ def single_case(cb, L, torch, dev, which, small, shape, units=0):
         def step(i):
             s = i % 2
             if program is not None:
-                cb.free(program.launch(n, [(x[s].data_ptr(), n * 4)]))       # the program allocates its output, as materializec does
+                # the program allocates its output, as materializec does
+                cb.free(program.launch(n, [(x[s].data_ptr(), n * 4)], compiled=which == "map_program"))
             elif which == "softmax":
                 cb.check(L.catena_b200_softmax_f32_into(x[s].data_ptr(), y[s].data_ptr(), n))
             elif which == "rmsnorm":
@@ -898,7 +903,8 @@ def single_case(cb, L, torch, dev, which, small, shape, units=0):
         work, unit = passes * n * 4 / 1e9, "GB/s"
         desc = f"{which} over {n} f32"
         if program is not None:
-            desc = f"nn.silu as an interpreted register program ({len(program.code)} instructions, {program.n_regs} registers) over {n} f32"
+            how = "compiled to its own kernel" if which == "map_program" else "interpreted"
+            desc = f"nn.silu as a register program ({len(program.code)} instructions, {program.n_regs} registers), {how}, over {n} f32"
     return step, work, unit, desc
 
 
@@ -944,7 +950,7 @@ def run_single(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None,
-                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "map_program", "softmax", "rmsnorm", "sum_u64", "dot_u64", "llama"])
+                    choices=["gemm", "gemm_i8", "attn", "matmul_f32", "map", "map_program", "map_interpreted", "softmax", "rmsnorm", "sum_u64", "dot_u64", "llama"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--shape", default=None, help="MxNxK for --only gemm / gemm_i8")
     ap.add_argument("--units", type=int, default=0, help="--only attn: launch only the first N (batch, kv-head) units")

@@ -75,6 +75,7 @@ def lib():
 
     proto("catena_b200_init", st, [C.c_int])
     proto("catena_b200_device_count", C.c_int, [])
+    proto("catena_b200_current_device", C.c_int, [])
     proto("catena_b200_set_stream", st, [vp])
     proto("catena_b200_get_stream", vp, [])
     proto("catena_b200_set_blocking", None, [C.c_int])
@@ -142,6 +143,12 @@ def lib():
                                             u64, pm])
     proto("catena_b200_map_program_range_s", st, [vp, C.c_uint32, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, vp, C.c_uint32, C.c_uint32,
                                                   u64, u64, pm])
+    # compiled map kernels (csrc/map_jit.cu): code, n_insn, init, init_is_const, n_init, n_regs, index_reg, result_reg, n_buffers, elem_bytes
+    spec = [vp, C.c_uint32, vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
+    proto("catena_b200_map_ptx_s", st, spec + [vp, u64, C.POINTER(u64)])
+    proto("catena_b200_map_compile_s", st, spec + [C.POINTER(vp)])
+    proto("catena_b200_map_kernel_launch_s", st, [vp, vp, C.c_uint32, vp, C.c_uint32, u64, u64, pm])
+    proto("catena_b200_map_kernel_release", None, [vp])
     pblk = C.POINTER(LlamaBlockStruct)
     proto("catena_b200_llama_workspace_bytes", u64, [pblk, u64])
     proto("catena_b200_llama_prefill", st, [pblk, vp, u64, u64, vp, vp, vp, vp, u64])

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libcatena_b200.so")
-SOURCES = ["core.cu", "map_reduce.cu", "map_program.cu", "int_programs.cu", "gemm_f32.cu", "gemm_tc.cu", "gemm_tc2.cu", "attn_decode.cu", "attn_decode_tc.cu", "llama.cu", "llama_decode_fused.cu", "attn_prefill_tc.cu", "programs.cu"]
+SOURCES = ["core.cu", "map_reduce.cu", "map_program.cu", "map_jit.cu", "int_programs.cu", "gemm_f32.cu", "gemm_tc.cu", "gemm_tc2.cu", "attn_decode.cu", "attn_decode_tc.cu", "llama.cu", "llama_decode_fused.cu", "attn_prefill_tc.cu", "programs.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--std=c++17", "--fmad=false",
     "-Xcompiler", "-fPIC,-ffp-contract=off,-fno-fast-math,-Wall,-Wno-unused-function",

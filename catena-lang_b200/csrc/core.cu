@@ -192,6 +192,8 @@ extern "C" {
 
 catena_status_t catena_b200_init(int device) { return bind_device(device); }
 
+int catena_b200_current_device(void) { return tls().device; }
+
 int catena_b200_device_count(void) {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess) {

@@ -335,6 +335,18 @@ static catena_status_t validate(const catena_b200_map_insn_t* code, uint32_t n_i
 
 }  // namespace mapvm
 
+catena_status_t map_program_validate(const catena_b200_map_insn_t* code, uint32_t n_insn, uint32_t n_init, uint32_t n_regs, uint32_t index_reg,
+                                     uint32_t result_reg, uint32_t n_buffers) {
+    return mapvm::validate(code, n_insn, n_init, n_regs, index_reg, result_reg, n_buffers);
+}
+
+catena_status_t map_program_error_word(uint32_t** err) {
+    mapvm::State* st = nullptr;
+    CATENA_TRY(mapvm::state(&st));
+    *err = st->err;
+    return CATENA_OK;
+}
+
 // Reports (and clears) what the programs of earlier launches ran into; synchronises the stream.
 catena_status_t map_program_check_errors() {
     CATENA_TRY(ensure_device());

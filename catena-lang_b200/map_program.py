@@ -17,8 +17,13 @@ producer's lowered assignments are translated ONCE into a small register program
                                    `buf.*.cast-same-length` cost nothing and a buffer's length is a preset register
 
 The environment of the producer (scalars and buffers) is bound at launch time: `MapProgram.launch(len, env)`.
+
+By default a launch runs the program COMPILED: the library writes PTX for it and the driver compiles that for the device
+(csrc/map_jit.cu; once per program and device), which is what the reference's nvcc step amounts to for one producer.
+`CATENA_B200_MAP_COMPILED=0` in the environment runs every launch on the interpreter instead; both give the same bits.
 """
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -102,15 +107,63 @@ class MapProgram:
                 buffers.append((int(value[0] or 0), int(value[1])))
         return init, buffers
 
-    def launch(self, length, env, index0=0):
+    def _spec(self, init):
+        """The arguments every compiled-map entry point starts with; the returned arrays must outlive the call."""
+        code = (Insn * len(self.code))(*self.code)
+        init_arr = (C.c_uint64 * max(1, len(init)))(*init)
+        is_const = (C.c_uint8 * max(1, len(self.presets)))(*[1 if what[0] == "const" else 0 for what in self.presets])
+        n_buffers = sum(1 for kind in self.env_kinds if kind == "buffer")
+        return [code, len(self.code), init_arr, is_const, len(init), self.n_regs, self.index_reg, self.result_reg, n_buffers, self.elem_bytes]
+
+    def ptx(self):
+        """The PTX text of the compiled kernel (needs no GPU).  Environment presets are kernel parameters, so any values do."""
+        from . import check, lib
+        init = [what[1] if what[0] == "const" else 0 for what in self.presets]
+        spec = self._spec(init)
+        need = C.c_uint64(0)
+        check(lib().catena_b200_map_ptx_s(*spec, None, 0, C.byref(need)))
+        text = C.create_string_buffer(need.value)
+        check(lib().catena_b200_map_ptx_s(*spec, text, need.value, None))
+        return text.value.decode()
+
+    def compiled(self):
+        """Handle of the kernel compiled for the current device (built on first use, kept for the program's lifetime)."""
+        from . import check, lib
+        device = int(lib().catena_b200_current_device())
+        if not hasattr(self, "_kernels"):
+            self._kernels = {}
+        if device not in self._kernels:
+            init = [what[1] if what[0] == "const" else 0 for what in self.presets]
+            handle = C.c_void_p()
+            check(lib().catena_b200_map_compile_s(*self._spec(init), C.byref(handle)))
+            self._kernels[device] = handle
+        return self._kernels[device]
+
+    def __del__(self):
+        for handle in getattr(self, "_kernels", {}).values():
+            try:
+                from . import lib
+                lib().catena_b200_map_kernel_release(handle)
+            except Exception:      # interpreter shutdown: the library may be gone already
+                pass
+
+    def launch(self, length, env, index0=0, compiled=None):
         """out[j] = producer(env..., index0 + j) for j < length on the device; returns the library's CatenaMem (owned by the
-        caller).  `index0` is how a map shards over GPUs: contiguous index ranges, the same program on every rank."""
+        caller).  `index0` is how a map shards over GPUs: contiguous index ranges, the same program on every rank.
+        `compiled`: True = the program's own kernel, False = the interpreter, None = what CATENA_B200_MAP_COMPILED says
+        (default: compiled)."""
         from . import CatenaMem, check, lib
         init, buffers = self.init_registers(env)
-        code = (Insn * len(self.code))(*self.code)
         init_arr = (C.c_uint64 * max(1, len(init)))(*init)
         bufs = (CatenaMem * max(1, len(buffers)))(*[CatenaMem(p, n) for p, n in buffers])
         out = CatenaMem()
+        if compiled is None:
+            compiled = os.environ.get("CATENA_B200_MAP_COMPILED", "1") != "0"
+        if compiled and int(length) > 0:
+            check(lib().catena_b200_map_kernel_launch_s(self.compiled(), init_arr, len(init), bufs, len(buffers), int(index0), int(length),
+                                                        C.byref(out)))
+            return out
+        code = (Insn * len(self.code))(*self.code)
         check(lib().catena_b200_map_program_range_s(code, len(self.code), init_arr, len(init), self.n_regs, self.index_reg, self.result_reg,
                                                     bufs, len(buffers), self.elem_bytes, int(index0), int(length), C.byref(out)))
         return out

@@ -27,6 +27,12 @@ pub const CATENA_E_TOO_LARGE: catena_status_t = 6;
 pub const CATENA_E_UNSUPPORTED: catena_status_t = 7;
 
 /// One instruction of a register program for the generic map kernel (`enum catena_b200_map_op` numbers the opcodes).
+/// Opaque handle of a compiled map kernel.
+#[repr(C)]
+pub struct catena_b200_map_kernel_t {
+    _private: [u8; 0],
+}
+
 #[repr(C)]
 #[derive(Clone, Copy, Debug, Default)]
 pub struct catena_b200_map_insn_t {
@@ -43,6 +49,7 @@ extern "C" {
     // runtime
     pub fn catena_b200_init(device: c_int) -> catena_status_t;
     pub fn catena_b200_device_count() -> c_int;
+    pub fn catena_b200_current_device() -> c_int;
     pub fn catena_b200_set_stream(stream: *mut c_void) -> catena_status_t;
     pub fn catena_b200_set_blocking(blocking: c_int);
     pub fn catena_b200_sync() -> catena_status_t;
@@ -110,6 +117,16 @@ extern "C" {
     pub fn catena_b200_map_program_range_s(code: *const catena_b200_map_insn_t, n_insn: u32, init: *const u64, n_init: u32, n_regs: u32,
                                            index_reg: u32, result_reg: u32, buffers: *const catena_mem_t, n_buffers: u32,
                                            elem_bytes: u32, index0: u64, len: u64, out: *mut catena_mem_t) -> catena_status_t;
+    // compiled map kernels: PTX written by the library, compiled by the driver
+    pub fn catena_b200_map_ptx_s(code: *const catena_b200_map_insn_t, n_insn: u32, init: *const u64, init_is_const: *const u8, n_init: u32,
+                                 n_regs: u32, index_reg: u32, result_reg: u32, n_buffers: u32, elem_bytes: u32, text: *mut c_char,
+                                 capacity: u64, length: *mut u64) -> catena_status_t;
+    pub fn catena_b200_map_compile_s(code: *const catena_b200_map_insn_t, n_insn: u32, init: *const u64, init_is_const: *const u8, n_init: u32,
+                                     n_regs: u32, index_reg: u32, result_reg: u32, n_buffers: u32, elem_bytes: u32,
+                                     kernel: *mut *mut catena_b200_map_kernel_t) -> catena_status_t;
+    pub fn catena_b200_map_kernel_launch_s(kernel: *const catena_b200_map_kernel_t, init: *const u64, n_init: u32, buffers: *const catena_mem_t,
+                                           n_buffers: u32, index0: u64, len: u64, out: *mut catena_mem_t) -> catena_status_t;
+    pub fn catena_b200_map_kernel_release(kernel: *mut catena_b200_map_kernel_t);
     pub fn catena_b200_sum_f32_noalloc(input: *const c_void, n: u64, out: *mut c_void) -> catena_status_t;
     // Llama-style block (device pointers throughout)
     pub fn catena_b200_llama_workspace_bytes(blk: *const catena_llama_block_t, tokens: u64) -> u64;

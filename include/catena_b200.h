@@ -54,6 +54,8 @@ enum {
  * (catena-lang/doc/CODEGEN.md:164-166): binds the calling thread's library state to `device`. */
 catena_status_t catena_b200_init(int device);
 int catena_b200_device_count(void);
+/* the device the calling thread's library state is bound to, -1 before the first catena_b200_init / compute call */
+int catena_b200_current_device(void);
 /* Entry points launch on this stream (default: the legacy default stream, as the generated
  * code does).  `stream` is a cudaStream_t.
  * Threads and streams: device, stream, blocking flag, last status and the scratch that kernels share between launches
@@ -246,6 +248,30 @@ catena_status_t catena_b200_map_program_s(const catena_b200_map_insn_t* code, ui
 catena_status_t catena_b200_map_program_range_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, uint32_t n_init,
                                                 uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, const catena_mem_t* buffers,
                                                 uint32_t n_buffers, uint32_t elem_bytes, uint64_t index0, uint64_t len, catena_mem_t* out);
+
+/* ---- compiled map: the same register program as a kernel of its own -------------------------------------------------
+ * What the reference does with nvcc when the Runtime is built (catena-lang/src/codegen/ops/materializec.rs:36-145,
+ * catena-lang/src/runtime/artifact.rs:59-80), done without a compiler toolchain: the library writes PTX for the register
+ * program (every f32 operation explicitly rounded, so nothing is contracted into an fma; program constants as immediates)
+ * and the driver compiles it for the device (cuModuleLoadDataEx).  The compiled kernel gives the bits of the interpreter
+ * above and reports the same faults through the same status, at the speed of a prebuilt map kernel.
+ * `init_is_const[k] != 0` marks preset register k as a constant of the program (its value is taken from `init` now and
+ * baked in); the other presets are environment values, read from the `init` of every launch.  NULL = none is constant.
+ * catena_b200_map_ptx_s only writes the PTX text (`length` receives its size with the terminator; `text` may be NULL to
+ * ask for the size) and needs no GPU.  A kernel belongs to the device that was current when it was compiled and may be
+ * launched from any host thread bound to that device; release it when no launch of it is pending. */
+typedef struct catena_b200_map_kernel catena_b200_map_kernel_t;
+catena_status_t catena_b200_map_ptx_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, const uint8_t* init_is_const,
+                                      uint32_t n_init, uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, uint32_t n_buffers,
+                                      uint32_t elem_bytes, char* text, uint64_t capacity, uint64_t* length);
+catena_status_t catena_b200_map_compile_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, const uint8_t* init_is_const,
+                                          uint32_t n_init, uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, uint32_t n_buffers,
+                                          uint32_t elem_bytes, catena_b200_map_kernel_t** kernel);
+/* out[j] = producer(env..., index0 + j), j < len; `init` / `buffers` as for catena_b200_map_program_range_s */
+catena_status_t catena_b200_map_kernel_launch_s(const catena_b200_map_kernel_t* kernel, const uint64_t* init, uint32_t n_init,
+                                                const catena_mem_t* buffers, uint32_t n_buffers, uint64_t index0, uint64_t len,
+                                                catena_mem_t* out);
+void catena_b200_map_kernel_release(catena_b200_map_kernel_t* kernel);
 
 /* ---- programs with no counterpart in the reference (it has no bf16, int8 or attention);
  *      same calling convention; semantics composed from the reference's rules -------------- */

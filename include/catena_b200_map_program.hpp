@@ -19,8 +19,11 @@
 #define CATENA_B200_MAP_PROGRAM_HPP
 
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <map>
+#include <memory>
+#include <mutex>
 #include <set>
 #include <string>
 #include <tuple>
@@ -54,16 +57,81 @@ struct Preset {
     bool operator<(const Preset& o) const { return std::tie(kind, value, elem) < std::tie(o.kind, o.value, o.elem); }
 };
 
+// The kernels compiled for one program, one per device; shared by the copies of the Program and released with the last one.
+struct CompiledKernels {
+    std::mutex lock;
+    std::map<int, catena_b200_map_kernel_t*> by_device;
+    CompiledKernels() = default;
+    CompiledKernels(const CompiledKernels&) = delete;
+    CompiledKernels& operator=(const CompiledKernels&) = delete;
+    ~CompiledKernels() {
+        for (auto& kv : by_device) catena_b200_map_kernel_release(kv.second);
+    }
+};
+
+// How a launch runs: the program's own compiled kernel (PTX written by the library, compiled by the driver once per device) or
+// the library's interpreter.  Both give the same bits.  Default: compiled, unless CATENA_B200_MAP_COMPILED=0 is in the environment.
+enum class Mode { Default, Compiled, Interpreted };
+
 struct Program {
     std::string producer;
     std::vector<catena_b200_map_insn_t> code;
     std::vector<Preset> presets;           // register k < presets.size() is preset
     uint32_t n_regs = 1, index_reg = 0, result_reg = 0, elem_bytes = 8;
     std::vector<bool> env_is_buffer;       // one entry per runtime environment value
+    mutable std::shared_ptr<CompiledKernels> kernels;      // filled by the first compiled launch; reset it after editing `code`
+
+    uint32_t buffer_count() const {
+        uint32_t n = 0;
+        for (bool b : env_is_buffer) n += b ? 1u : 0u;
+        return n;
+    }
+
+    // The kernel compiled for the calling thread's device (built on first use).
+    catena_status_t compiled(catena_b200_map_kernel_t** kernel) const {
+        const int device = catena_b200_current_device() < 0 ? 0 : catena_b200_current_device();
+        if (!kernels) kernels = std::make_shared<CompiledKernels>();
+        std::lock_guard<std::mutex> hold(kernels->lock);
+        auto it = kernels->by_device.find(device);
+        if (it == kernels->by_device.end()) {
+            std::vector<uint64_t> init;
+            std::vector<uint8_t> is_const;
+            for (const Preset& p : presets) {
+                init.push_back(p.kind == Preset::Const ? p.value : 0);
+                is_const.push_back(p.kind == Preset::Const ? 1 : 0);
+            }
+            catena_b200_map_kernel_t* k = nullptr;
+            const catena_status_t s = catena_b200_map_compile_s(code.data(), (uint32_t)code.size(), init.data(), is_const.data(), (uint32_t)init.size(),
+                                                                n_regs, index_reg, result_reg, buffer_count(), elem_bytes, &k);
+            if (s != CATENA_OK) return s;
+            it = kernels->by_device.emplace(device, k).first;
+        }
+        *kernel = it->second;
+        return CATENA_OK;
+    }
+
+    // The PTX text of the compiled kernel (needs no GPU).
+    catena_status_t ptx(std::string* text) const {
+        std::vector<uint64_t> init;
+        std::vector<uint8_t> is_const;
+        for (const Preset& p : presets) {
+            init.push_back(p.kind == Preset::Const ? p.value : 0);
+            is_const.push_back(p.kind == Preset::Const ? 1 : 0);
+        }
+        uint64_t need = 0;
+        catena_status_t s = catena_b200_map_ptx_s(code.data(), (uint32_t)code.size(), init.data(), is_const.data(), (uint32_t)init.size(), n_regs,
+                                                  index_reg, result_reg, buffer_count(), elem_bytes, nullptr, 0, &need);
+        if (s != CATENA_OK) return s;
+        std::vector<char> buf(need);
+        s = catena_b200_map_ptx_s(code.data(), (uint32_t)code.size(), init.data(), is_const.data(), (uint32_t)init.size(), n_regs, index_reg,
+                                  result_reg, buffer_count(), elem_bytes, buf.data(), need, nullptr);
+        if (s == CATENA_OK) text->assign(buf.data());
+        return s;
+    }
 
     // out[j] = producer(env..., index0 + j) for j < len on the device; *out is owned by the caller (catena_b200_mem_free).
     // `index0` is how a map shards over GPUs: contiguous index ranges, the same program on every rank.
-    catena_status_t launch(uint64_t len, const std::vector<EnvValue>& env, catena_mem_t* out, uint64_t index0 = 0) const {
+    catena_status_t launch(uint64_t len, const std::vector<EnvValue>& env, catena_mem_t* out, uint64_t index0 = 0, Mode mode = Mode::Default) const {
         if (env.size() != env_is_buffer.size()) return CATENA_E_BAD_ARG;
         std::vector<uint64_t> init;
         std::vector<catena_mem_t> buffers;
@@ -74,6 +142,16 @@ struct Program {
         }
         for (size_t k = 0; k < env.size(); ++k)
             if (env_is_buffer[k]) buffers.push_back(env[k].buffer);
+        if (mode == Mode::Default) {
+            const char* e = getenv("CATENA_B200_MAP_COMPILED");
+            mode = e && e[0] == '0' && e[1] == 0 ? Mode::Interpreted : Mode::Compiled;
+        }
+        if (mode == Mode::Compiled && len > 0) {
+            catena_b200_map_kernel_t* k = nullptr;
+            const catena_status_t s = compiled(&k);
+            if (s != CATENA_OK) return s;
+            return catena_b200_map_kernel_launch_s(k, init.data(), (uint32_t)init.size(), buffers.data(), (uint32_t)buffers.size(), index0, len, out);
+        }
         return catena_b200_map_program_range_s(code.data(), (uint32_t)code.size(), init.data(), (uint32_t)init.size(), n_regs, index_reg,
                                                result_reg, buffers.data(), (uint32_t)buffers.size(), elem_bytes, index0, len, out);
     }

@@ -138,6 +138,25 @@ int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "list";
     const std::vector<GpuModule> mods = fixtures();
     const char* names[] = {"materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec", "my.poly-map"};
+    if (mode == "ptx") {
+        // the text of every program's compiled kernel (no GPU needed): one file per program in the directory argv[2]
+        const std::string dir = argc > 2 ? argv[2] : ".";
+        int k = 0;
+        auto write = [&](const map_program::Program& p) {
+            std::string text;
+            CHECK(p.ptx(&text) == CATENA_OK && text.find(".target sm_100a") != std::string::npos);
+            std::FILE* f = std::fopen((dir + "/program_" + std::to_string(k++) + ".ptx").c_str(), "w");
+            CHECK(f != nullptr);
+            if (f) {
+                std::fputs(text.c_str(), f);
+                std::fclose(f);
+            }
+        };
+        for (const char* n : names) write(map_program::for_assignment(mods, materializec_of(mods, n)));
+        write(map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0));
+        std::printf("ok %d checks\n", g_checks);
+        return 0;
+    }
     if (mode == "list") {
         for (const char* n : names) list(n, map_program::for_assignment(mods, materializec_of(mods, n)));
         list("my.horner", map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0));
@@ -146,6 +165,9 @@ int main(int argc, char** argv) {
     // ---- gpu: the reference's vectors (catena-lang/tests/cases/materializec.rs:5-31, materialize.rs:5-31) and the two user producers
     CHECK(catena_b200_init(0) == CATENA_OK);
     auto upload = [](const void* p, uint64_t n) { catena_mem_t m{nullptr, 0}; catena_b200_mem_upload(p, n, &m); return m; };
+    // every case twice: on the program's compiled kernel (the default) and on the interpreter
+    for (const char* compiled : {"1", "0"}) {
+    setenv("CATENA_B200_MAP_COMPILED", compiled, 1);
     {
         const auto p = map_program::for_assignment(mods, materializec_of(mods, "materialize-indexes"));
         catena_mem_t out{nullptr, 0};
@@ -250,6 +272,7 @@ int main(int argc, char** argv) {
         CHECK(got == want);
         catena_b200_mem_free(out);
         catena_b200_mem_free(in);
+    }
     }
     std::printf("ok %d checks\n", g_checks);
     return 0;

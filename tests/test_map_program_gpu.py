@@ -1,7 +1,9 @@
-"""The generic map kernel on the GPU: `materializec` with producers that no prebuilt kernel matches, run through
+"""The generic map on the GPU: `materializec` with producers that no prebuilt kernel matches, run through
 `Runtime.from_modules(...).exec(...)` — the reference's own vectors, equality with the prebuilt bit-exact kernels and the
 oracle, the CPU interpreter of tests/map_vm.py at sizes that need many CTAs, and the refusals that keep a malformed or
-faulting program away from the device."""
+faulting program away from the device.  A register program runs either as its own compiled kernel (csrc/map_jit.cu, the
+default) or on the library's interpreter (csrc/map_program.cu): the tests that launch programs directly run both and want
+the same bits and the same statuses."""
 import ctypes as C
 
 import numpy as np
@@ -35,8 +37,8 @@ def test_reference_materialize_vectors(rt):
 
 
 @pytest.mark.parametrize("n", [1, 255, 257, 100_003, 1 << 21])
-def test_interpreted_silu_equals_the_prebuilt_kernel(rt, n):
-    """nn.silu built from its primitives and interpreted = the prebuilt map kernel = the oracle, bit for bit."""
+def test_silu_from_its_primitives_equals_the_prebuilt_kernel(rt, n):
+    """nn.silu built from its primitives, compiled and interpreted = the prebuilt map kernel = the oracle, bit for bit."""
     rng = np.random.default_rng(n)
     x = rng.normal(0, 4, n).astype(np.float32)
     x[: min(n, 6)] = np.array([0.0, -0.0, 88.0, -87.0, 1e-30, -1e-30], np.float32)[: min(n, 6)]
@@ -47,11 +49,13 @@ def test_interpreted_silu_equals_the_prebuilt_kernel(rt, n):
     mm = lo.module_map(fx.custom_map_programs())
     [launch] = [a for a in mm["my.silu-map"].entry.assignments if a.op == "materializec"]
     m = cb.upload(x)
-    raw = lo.map_program_for(launch, mm).launch(n, [(m.data, m.len)])
-    got = cb.download(raw, np.float32).view(np.uint32)
-    cb.free(raw)
+    prog = lo.map_program_for(launch, mm)
+    for compiled in (True, False):
+        raw = prog.launch(n, [(m.data, m.len)], compiled=compiled)
+        got = cb.download(raw, np.float32).view(np.uint32)
+        cb.free(raw)
+        assert np.array_equal(got, selected)
     cb.free(m)
-    assert np.array_equal(got, selected)
     m = cb.upload(x)
     o = cb.CatenaMem()
     cb.check(cb.lib().catena_b200_map_f32_s(b"nn.silu", m, C.byref(o)))
@@ -117,12 +121,13 @@ def test_faults_of_a_program_come_back_as_statuses(rt):
     mm = lo.module_map(mods)
     prog = lo.map_program_for([a for a in mm["materialize-copy-u64"].entry.assignments if a.op == "materializec"][0], mm)
     data = cb.upload(np.array([3, 5], np.uint64))
-    with pytest.raises(cb.CatenaError) as err:
-        prog.launch(3, [(data.data, data.len)])
-    assert err.value.status == cb.E_ASSERT
-    out = prog.launch(2, [(data.data, data.len)])
-    assert cb.download(out, np.uint64).tolist() == [3, 5]
-    cb.free(out)
+    for compiled in (True, False):
+        with pytest.raises(cb.CatenaError) as err:
+            prog.launch(3, [(data.data, data.len)], compiled=compiled)
+        assert err.value.status == cb.E_ASSERT
+        out = prog.launch(2, [(data.data, data.len)], compiled=compiled)
+        assert cb.download(out, np.uint64).tolist() == [3, 5]
+        cb.free(out)
     cb.free(data)
     [ok] = rt.exec("materialize-indexes", [3])
     assert ok.v.to_u64_vec().tolist() == [1, 1, 1]
@@ -193,10 +198,12 @@ def test_every_kernel_geometry_agrees_with_the_cpu_interpreter(n_insn, n_regs):
     code.append(Insn(OP["HALT"], 0, 0, 0, 0, 0, 0))
     prog = MapProgram("by-hand", code, presets, n_regs, index, code[-2].dst, ["u64"], 8)
     length = 3000
-    out = prog.launch(length, [123456789])
-    got = cb.download(out, np.uint64)
-    cb.free(out)
-    assert np.array_equal(got, map_vm.run(prog, [123456789], length, []))
+    want = map_vm.run(prog, [123456789], length, [])
+    for compiled in (False, True):
+        out = prog.launch(length, [123456789], compiled=compiled)
+        got = cb.download(out, np.uint64)
+        cb.free(out)
+        assert np.array_equal(got, want)
 
 
 def test_generic_folds_through_the_runtime():
@@ -252,6 +259,13 @@ def test_random_producers_on_the_device(seed, control):
     prog = lo.map_program_for(launch, mm)
     want = map_vm.run(prog, [sd, scale, (0, table.nbytes), (0, xs.nbytes)], n, [table.view(np.uint8), xs.view(np.uint8)])
     assert np.array_equal(got, want.astype(got.dtype))
+    mt, mx = cb.upload(table), cb.upload(xs)
+    for compiled in (True, False):
+        raw = prog.launch(n, [sd, scale, (mt.data, mt.len), (mx.data, mx.len)], compiled=compiled)
+        assert np.array_equal(cb.download(raw, got.dtype), got)
+        cb.free(raw)
+    cb.free(mt)
+    cb.free(mx)
 
 
 def test_a_map_sharded_by_index_ranges_gives_the_unsharded_bits():
@@ -273,12 +287,58 @@ def test_a_map_sharded_by_index_ranges_gives_the_unsharded_bits():
         whole = prog.launch(n, env)
         want = cb.download(whole, dtype)
         cb.free(whole)
-        for world in (2, 4, 8):
-            parts = []
-            for r in shard.index_ranges(n, world, align=4):
-                raw = prog.launch(r.i1 - r.i0, env, index0=r.i0)
-                parts.append(cb.download(raw, dtype))
-                cb.free(raw)
-            assert np.array_equal(np.concatenate(parts), want)
+        for compiled in (True, False):
+            for world in (2, 4, 8):
+                parts = []
+                for r in shard.index_ranges(n, world, align=4):
+                    raw = prog.launch(r.i1 - r.i0, env, index0=r.i0, compiled=compiled)
+                    parts.append(cb.download(raw, dtype))
+                    cb.free(raw)
+                assert np.array_equal(np.concatenate(parts), want)
         cb.free(mt)
         cb.free(mx)
+
+
+def test_compiled_kernels_keep_the_bounds_of_the_interpreter():
+    """What keeps a program from hanging or faulting the GPU holds in the compiled kernel too: an endless loop ends at the
+    budget of backward jumps, the undefined cases (shift by 32 or more, round-to-u32 out of range, division by zero) yield 0 and
+    CATENA_E_ASSERT, and the next launch works."""
+    from catena_lang_b200.map_program import MapProgram
+    halt = Insn(OP["HALT"], 0, 0, 0, 0, 0, 0)
+    loop = MapProgram("endless", [Insn(OP["JMP"], 0, 0, 0, 0, 0, 0), halt], [], 2, 0, 1, [], 8)
+    with pytest.raises(cb.CatenaError) as err:
+        loop.launch(1, [], compiled=True)
+    assert err.value.status == cb.E_ASSERT
+    cases = {
+        "shift": [Insn(OP["U32_SHL"], 2, 1, 0, 0, 0, 0), halt],              # index << 40
+        "divide": [Insn(OP["U64_SUB"], 3, 1, 1, 0, 0, 0), Insn(OP["U64_DIV"], 2, 1, 3, 0, 0, 0), halt],
+        "round": [Insn(OP["F32_ROUND_TO_U32"], 2, 0, 0, 0, 0, 0), halt],     # preset 0 holds -1.0f
+    }
+    for name, code in cases.items():
+        preset = 0xBF800000 if name == "round" else 40
+        prog = MapProgram(name, code, [("const", preset)], 4, 1, 2, [], 8 if name == "divide" else 4)
+        for compiled in (True, False):
+            with pytest.raises(cb.CatenaError) as err:
+                prog.launch(5, [], compiled=compiled)
+            assert err.value.status == cb.E_ASSERT, (name, compiled)
+    ok = MapProgram("index", [halt], [], 1, 0, 0, [], 8)
+    out = ok.launch(1000, [], compiled=True)
+    assert cb.download(out, np.uint64).tolist() == list(range(1000))
+    cb.free(out)
+
+
+def test_one_compiled_kernel_serves_every_environment():
+    """Environment scalars and buffers are kernel parameters: one compilation, any number of launches with other values."""
+    mm = lo.module_map(fx.custom_map_programs())
+    [launch] = [a for a in mm["my.clamp-map"].entry.assignments if a.op == "materializec"]
+    prog = lo.map_program_for(launch, mm)
+    handle = prog.compiled().value
+    rng = np.random.default_rng(8)
+    for n, floor in ((10, 0.5), (70_001, -0.25), (3, 7.0)):
+        x = rng.normal(0, 1, n).astype(np.float32)
+        m = cb.upload(x)
+        raw = prog.launch(n, [(m.data, m.len), np.float32(floor)], compiled=True)
+        assert np.array_equal(cb.download(raw, np.float32), np.maximum(x, np.float32(floor)))
+        cb.free(raw)
+        cb.free(m)
+    assert prog.compiled().value == handle
