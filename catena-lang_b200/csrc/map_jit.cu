@@ -21,7 +21,6 @@
 // cases the reference leaves undefined yield 0 and a code in the shared error word.
 #include <cuda.h>
 #include <stdarg.h>
-#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -59,7 +58,6 @@ struct Emitter {
     std::vector<uint32_t> dyn;          // preset registers read from the kernel parameters, in parameter order
 
     explicit Emitter(const Spec& spec) : s(spec), lanes(straight_line(spec) ? 4 : 1) {
-        if (const char* e = getenv("CATENA_TMP_LANES")) if (lanes > 1) lanes = (uint32_t)atoi(e);
         for (uint32_t k = 0; k < s.n_init; ++k)
             if (!(s.is_const && s.is_const[k])) dyn.push_back(k);
     }
@@ -335,12 +333,44 @@ struct Emitter {
         line("mov.b32 %%r0, %%nctaid.x;");
         line("cvt.u64.u32 %%step, %%r0;");
         line("add.u64 %%tiles, %%len, %u;", per_tile - 1);
-        line("shr.u64 %%tiles, %%tiles, %u;", lanes == 8 ? 11 : lanes == 4 ? 10 : lanes == 2 ? 9 : 8);
+        line("shr.u64 %%tiles, %%tiles, %u;", lanes == 4 ? 10 : 8);
         out += "TILE:\n";
         line("setp.ge.u64 %%p0, %%tile, %%tiles;");
         line("@%%p0 bra DONE;");
-        // element v of this thread: tile * per_tile + v * 256 + thread; a thread whose first element is past the end has none
+        // element v of this thread: tile * per_tile + v * 256 + thread
         line("mad.lo.u64 %%e0, %%tile, %u, %%tid64;", per_tile);
+        // Straight-line programs are written twice: for a tile that lies wholly inside the range — no element needs a validity
+        // test, the four indices are one sum plus constants, the stores are unconditional — and for the ragged last tile.
+        const bool split = lanes > 1 && (uint64_t)s.n_insn * lanes <= 1024;
+        if (split) {
+            line("add.u64 %%rd0, %%tile, 1;");
+            line("mul.lo.u64 %%rd0, %%rd0, %u;", per_tile);
+            line("setp.gt.u64 %%p0, %%rd0, %%len;");
+            line("@%%p0 bra RAGGED;");
+            line("add.u64 %%rd0, %%e0, %%index0;");
+            for (uint32_t v = 0; v < lanes; ++v) {
+                if (v) {
+                    line("add.u64 %%e%u, %%e0, %u;", v, v * kThreads);
+                    line("add.u64 %%rd1, %%rd0, %u;", v * kThreads);
+                }
+                unpack(v, s.index_reg, v ? "%rd1" : "%rd0");
+            }
+            for (uint32_t k = 0; k < s.n_insn && s.code[k].op != CATENA_MAP_HALT; ++k)
+                for (uint32_t v = 0; v < lanes; ++v) instruction(k, v);
+            for (uint32_t v = 0; v < lanes; ++v) {
+                if (s.elem_bytes == 8) {
+                    line("mov.b64 %%rd1, {%s, %s};", lo(v, s.result_reg).c_str(), hi(v, s.result_reg).c_str());
+                    line("mad.lo.u64 %%rd0, %%e%u, 8, %%out;", v);
+                    line("st.global.b64 [%%rd0], %%rd1;");
+                } else {
+                    line("mad.lo.u64 %%rd0, %%e%u, 4, %%out;", v);
+                    line("st.global.b32 [%%rd0], %s;", lo(v, s.result_reg).c_str());
+                }
+            }
+            line("bra NEXT;");
+            out += "RAGGED:\n";
+        }
+        // a thread whose first element is past the end has none
         line("setp.lt.u64 %%ok0, %%e0, %%len;");
         line("@!%%ok0 bra NEXT;");
         for (uint32_t v = 1; v < lanes; ++v) {
