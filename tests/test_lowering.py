@@ -72,6 +72,10 @@ def test_stdlib_extension_registers_the_added_programs():
         assert name in rt.signatures and rt.signatures[name][0] == cb.symbol_for(name)
     text = open(path).read()
     assert text.count("(") == text.count(")") and text.count("{") == text.count("}") and text.count("[") == text.count("]")
+    # the operators of the Llama-style block are declared as primitive arrows (no `def program`: exec would drop the weights)
+    for arrow in ("embed.bf16", "rmsnorm.rows.bf16", "rope.append.bf16", "attention.prefill.bf16", "swiglu.bf16",
+                  "llama.block.prefill", "llama.block.decode"):
+        assert f"(arr {arrow} :" in text
 
 
 def test_integer_and_scalar_modules_of_the_reference_tests():
