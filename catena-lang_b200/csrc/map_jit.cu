@@ -576,7 +576,16 @@ catena_status_t catena_b200_map_kernel_launch_s(const catena_b200_map_kernel_t* 
 
 void catena_b200_map_kernel_release(catena_b200_map_kernel_t* kernel) {
     if (!kernel) return;
-    if (mapjit::driver().ok && kernel->module) mapjit::driver().module_unload(kernel->module);
+    if (mapjit::driver().ok && kernel->module) {
+        // launches of the kernel may still be queued (non-blocking mode): the module goes only once its device is idle
+        int current = -1;
+        if (cudaGetDevice(&current) == cudaSuccess && cudaSetDevice(kernel->device) == cudaSuccess) {
+            (void)cudaDeviceSynchronize();
+            mapjit::driver().module_unload(kernel->module);
+            if (current >= 0 && current != kernel->device) (void)cudaSetDevice(current);
+        }
+        (void)cudaGetLastError();
+    }
     delete kernel;
 }
 

@@ -259,7 +259,7 @@ catena_status_t catena_b200_map_program_range_s(const catena_b200_map_insn_t* co
  * baked in); the other presets are environment values, read from the `init` of every launch.  NULL = none is constant.
  * catena_b200_map_ptx_s only writes the PTX text (`length` receives its size with the terminator; `text` may be NULL to
  * ask for the size) and needs no GPU.  A kernel belongs to the device that was current when it was compiled and may be
- * launched from any host thread bound to that device; release it when no launch of it is pending. */
+ * launched from any host thread bound to that device; releasing it waits for the device to be idle first. */
 typedef struct catena_b200_map_kernel catena_b200_map_kernel_t;
 catena_status_t catena_b200_map_ptx_s(const catena_b200_map_insn_t* code, uint32_t n_insn, const uint64_t* init, const uint8_t* init_is_const,
                                       uint32_t n_init, uint32_t n_regs, uint32_t index_reg, uint32_t result_reg, uint32_t n_buffers,

@@ -79,7 +79,8 @@ struct Program {
     std::vector<Preset> presets;           // register k < presets.size() is preset
     uint32_t n_regs = 1, index_reg = 0, result_reg = 0, elem_bytes = 8;
     std::vector<bool> env_is_buffer;       // one entry per runtime environment value
-    mutable std::shared_ptr<CompiledKernels> kernels;      // filled by the first compiled launch; reset it after editing `code`
+    // the kernels compiled from `code`, shared by copies of the program; give an edited copy a fresh one
+    std::shared_ptr<CompiledKernels> kernels = std::make_shared<CompiledKernels>();
 
     uint32_t buffer_count() const {
         uint32_t n = 0;
@@ -90,7 +91,7 @@ struct Program {
     // The kernel compiled for the calling thread's device (built on first use).
     catena_status_t compiled(catena_b200_map_kernel_t** kernel) const {
         const int device = catena_b200_current_device() < 0 ? 0 : catena_b200_current_device();
-        if (!kernels) kernels = std::make_shared<CompiledKernels>();
+        if (!kernels) return CATENA_E_BAD_ARG;
         std::lock_guard<std::mutex> hold(kernels->lock);
         auto it = kernels->by_device.find(device);
         if (it == kernels->by_device.end()) {

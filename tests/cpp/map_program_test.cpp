@@ -3,7 +3,9 @@
 // producers (a conditional, a fold inside the producer, constants to fold).
 //   list   prints every compiled program as text; tests/test_cpp_host.py compares it with the Python compiler's output for
 //          the same fixtures (tests/lowered_fixtures.py), instruction by instruction
-//   gpu    launches the programs through catena_b200_map_program_s and checks the reference's vectors
+//   ptx    writes the PTX text of every program's compiled kernel into a directory (no GPU needed); tests/test_cpp_host.py
+//          compares it with the Python side's text and assembles it
+//   gpu    launches the programs — as their compiled kernels, then on the interpreter — and checks the reference's vectors
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -142,18 +144,17 @@ int main(int argc, char** argv) {
         // the text of every program's compiled kernel (no GPU needed): one file per program in the directory argv[2]
         const std::string dir = argc > 2 ? argv[2] : ".";
         int k = 0;
-        auto write = [&](const map_program::Program& p) {
+        auto write = [&](const map_program::Program& p) -> int {
             std::string text;
             CHECK(p.ptx(&text) == CATENA_OK && text.find(".target sm_100a") != std::string::npos);
             std::FILE* f = std::fopen((dir + "/program_" + std::to_string(k++) + ".ptx").c_str(), "w");
             CHECK(f != nullptr);
-            if (f) {
-                std::fputs(text.c_str(), f);
-                std::fclose(f);
-            }
+            std::fputs(text.c_str(), f);
+            std::fclose(f);
+            return 0;
         };
-        for (const char* n : names) write(map_program::for_assignment(mods, materializec_of(mods, n)));
-        write(map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0));
+        for (const char* n : names) CHECK(write(map_program::for_assignment(mods, materializec_of(mods, n))) == 0);
+        CHECK(write(map_program::compile_fold(mods, reducec_of(mods, "my.horner"), 0)) == 0);
         std::printf("ok %d checks\n", g_checks);
         return 0;
     }

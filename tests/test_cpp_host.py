@@ -93,6 +93,30 @@ def test_cpp_map_program_compiler_agrees_with_python(map_program_binary):
     assert p.stdout.strip().splitlines() == lines
 
 
+def test_cpp_map_programs_compile_to_the_same_ptx_as_python(map_program_binary, tmp_path):
+    """`Program::ptx` (C++) and `MapProgram.ptx` (Python) hand the same program to the library, so the kernel text is the
+    same; every file assembles for sm_100a."""
+    import shutil
+    import lowered_fixtures as fx
+    from catena_lang_b200 import lowering as lo
+    p = subprocess.run([map_program_binary, "ptx", str(tmp_path)], capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0, p.stdout + p.stderr
+    mm = lo.module_map(fx.materialize_programs() + fx.custom_map_programs())
+    programs = []
+    for name in ("materialize-indexes", "materialize-copy-u64", "materialize-indexes-source", "my.clamp-map", "my.matvec", "my.poly-map"):
+        [assign] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+        programs.append(lo.map_program_for(assign, mm))
+    fm = lo.module_map(fx.custom_fold_programs())
+    [fold] = [a for a in fm["my.horner"].entry.assignments if a.op == "reducec"]
+    programs.append(lo.fold_plan_for(fold, fm).sequential[0])
+    ptxas = shutil.which("ptxas") or "/usr/local/cuda/bin/ptxas"
+    for k, prog in enumerate(programs):
+        path = tmp_path / f"program_{k}.ptx"
+        assert path.read_text() == prog.ptx()
+        if os.path.exists(ptxas):
+            subprocess.check_call([ptxas, "-arch=sm_100a", "-o", os.devnull, str(path)])
+
+
 @pytest.mark.gpu
 def test_cpp_map_program_on_the_gpu(map_program_binary):
     run(map_program_binary, "gpu")
