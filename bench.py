@@ -448,7 +448,7 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
         sampled_mhz = sampler.summary().get("sm_mhz")
         value = work / (ms * 1e-3)
         if which == "matmul_f32":
-            roof = {"bound": "fp32 issue (unfused mul + add)", "achieved": value, "peak": fp32_unfused_peak, "unit": "TFLOP/s",
+            roof = {"bound": "fp32 lanes (unfused mul + add)", "achieved": value, "peak": fp32_unfused_peak, "unit": "TFLOP/s",
                     "frac": value / fp32_unfused_peak,
                     "peak_source": f"148 SMs x 128 FP32 lanes x {sm_max_mhz} MHz x 1 flop per instruction (no measured figure for this pipe)"}
             if small:

@@ -9,15 +9,16 @@
 // still owns its own accumulation chain in the same order, so results are bit-identical for
 // every tile shape.  The K loop never pads: a trailing partial slab stops at exactly K (adding
 // `+0` terms could flip a `-0` accumulator to `+0`).  tcgen05 has no fp32 input mode and tensor
-// cores do not accumulate as a sequential IEEE chain, so this kernel is CUDA-core work by design.
+// cores do not accumulate as a sequential IEEE chain, so this kernel is CUDA-core work by design.  What sm_100 does add is
+// packed f32x2 arithmetic (two separately rounded IEEE operations per instruction): the large tile uses it, see below.
 #include "common.cuh"
 
 namespace catena {
 
 template <int BM, int BN, int BK, int TM, int TN>
-__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+__global__ void __launch_bounds__((BM / TM) * (BN / TN), TM * TN >= 64 ? 2 : 1)
 matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int n, int m,
-                  int k) {
+                  int k, uint64_t neg_zero2) {
     constexpr int THREADS = (BM / TM) * (BN / TN);
     __shared__ __align__(16) float As[BK][BM + 4];  // transposed: As[kk][row]; rows are 16-byte multiples apart
     __shared__ __align__(16) float Bs[BK][BN + 4];
@@ -36,6 +37,14 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;  // bit pattern 0x00000000 (matrix.hex:249)
+    // The 8 x 8 tile keeps its accumulators as PAIRS of neighbouring columns and works on them with the packed f32x2
+    // arithmetic of sm_100: each half is the same separately rounded IEEE product and sum, so the bits do not change, but a
+    // k step is 64 arithmetic instructions instead of 128.
+    uint64_t acc2[SPLIT ? TM : 1][SPLIT ? TN / 2 : 1];
+#pragma unroll
+    for (int i = 0; i < (SPLIT ? TM : 1); ++i)
+#pragma unroll
+        for (int j = 0; j < (SPLIT ? TN / 2 : 1); ++j) acc2[i][j] = 0ull;
 
     // The next k-slab travels from global memory into registers while the current one is multiplied out of shared
     // memory (small products are latency bound: eight exposed slab loads were most of a 256^3 launch).
@@ -74,25 +83,44 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         stage();
         if (k0 + BK < k) fetch(k0 + BK);
         __syncthreads();
-        if (kb == BK) {
-            // the 8 x 8 tile's body is 132 instructions per kk: unrolled four times it stays inside the instruction cache
-#pragma unroll(TM * TN >= 64 ? 4 : BK)
+        if constexpr (SPLIT) {
+            // one k step: four 16-byte loads for the 8 + 8 operands, then 32 packed products and 32 packed sums
+            auto step = [&](int kk) {
+                const ulonglong2 b0 = *reinterpret_cast<const ulonglong2*>(&Bs[kk][tx * 4]), b1 = *reinterpret_cast<const ulonglong2*>(&Bs[kk][BN / 2 + tx * 4]);
+                const float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * TM]), a1 = *reinterpret_cast<const float4*>(&As[kk][ty * TM + 4]);
+                const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                const uint64_t bv[4] = {b0.x, b0.y, b1.x, b1.y};      // columns (0,1) (2,3) | (4,5) (6,7) of the register tile
+#pragma unroll
+                for (int i = 0; i < TM; ++i) {
+                    uint64_t aa;
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(aa) : "f"(av[i]));
+#pragma unroll
+                    for (int j = 0; j < TN / 2; ++j) {
+                        // The product is a packed fma with -0 as its addend: a * b + (-0) is the rounded product (a zero product
+                        // keeps its sign).  The -0 arrives as a kernel argument so that ptxas cannot turn the fma back into a
+                        // mul: it merges a packed mul and the packed add behind it into ONE fma — explicit .rn and
+                        // --fmad=false notwithstanding — and that rounds once (measured: the bits of fma.rn.f32x2).  The
+                        // instructions themselves round like their scalar forms (checked against __fmul_rn / __fadd_rn).
+                        uint64_t prod;
+                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(prod) : "l"(aa), "l"(bv[j]), "l"(neg_zero2));
+                        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(acc2[i][j]) : "l"(acc2[i][j]), "l"(prod));
+                    }
+                }
+            };
+            if (kb == BK) {
+#pragma unroll 4
+                for (int kk = 0; kk < BK; ++kk) step(kk);
+            } else {
+                for (int kk = 0; kk < kb; ++kk) step(kk);
+            }
+        } else if (kb == BK) {
+#pragma unroll
             for (int kk = 0; kk < BK; ++kk) {
                 float a[TM], b[TN];
-                if (SPLIT) {      // four 16-byte loads for the 8 + 8 operands
-                    const float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * TM]), a1 = *reinterpret_cast<const float4*>(&As[kk][ty * TM + 4]);
-                    const float4 b0 = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]), b1 = *reinterpret_cast<const float4*>(&Bs[kk][BN / 2 + tx * 4]);
-                    const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-                    for (int i = 0; i < TM; ++i) a[i] = av[i % 8];
+                for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) b[j] = bv[j % 8];
-                } else {
-#pragma unroll
-                    for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
-#pragma unroll
-                    for (int j = 0; j < TN; ++j) b[j] = Bs[kk][col_of(j)];
-                }
+                for (int j = 0; j < TN; ++j) b[j] = Bs[kk][col_of(j)];
 #pragma unroll
                 for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -108,6 +136,15 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
             }
         }
         __syncthreads();
+    }
+    if constexpr (SPLIT) {
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN / 2; ++j) {
+                acc[i][2 * j] = __uint_as_float((uint32_t)acc2[i][j]);
+                acc[i][2 * j + 1] = __uint_as_float((uint32_t)(acc2[i][j] >> 32));
+            }
     }
 #pragma unroll
     for (int i = 0; i < TM; ++i) {
@@ -136,6 +173,9 @@ __global__ void identity_matmul_kernel(const float* __restrict__ A, float* __res
     C[idx] = acc;
 }
 
+// two packed -0.0f: the addend that makes a packed fma a rounded product (passed as an argument: see the kernel)
+static const uint64_t kNegZero2 = 0x8000000080000000ull;
+
 catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint64_t n, uint64_t m, uint64_t k) {
     if (n == 0 || m == 0) return CATENA_OK;
     if (n > 0x7FFFFFFFull || m > 0x7FFFFFFFull || k > 0x7FFFFFFFull)
@@ -151,14 +191,14 @@ catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint
         // large products are bound by instruction issue (two FP instructions per multiply-add, by contract): an 8 x 8 register
         // tile spends 4 shared-memory loads per 128 of them where the 4 x 4 tile spends 2 per 32
         dim3 grid((unsigned)ceil_div_u64(m, 128), (unsigned)ceil_div_u64(n, 128));
-        matmul_f32_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+        matmul_f32_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
     } else if (big_tiles >= (uint64_t)sms) {
         dim3 grid((unsigned)ceil_div_u64(m, 64), (unsigned)ceil_div_u64(n, 64));
-        matmul_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+        matmul_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
     } else {
         // small products are latency bound: more, smaller tiles to cover the SMs
         dim3 grid((unsigned)ceil_div_u64(m, 16), (unsigned)ceil_div_u64(n, 16));
-        matmul_f32_kernel<16, 16, 128, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k);
+        matmul_f32_kernel<16, 16, 128, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
     }
     count_launch();
     return CATENA_OK;

@@ -65,6 +65,25 @@ def test_matmul_bit_exact(rt, orc, n, m, k):
     assert np.array_equal(u32(got), u32(want))
 
 
+def test_matmul_large_tile_keeps_the_bits_of_special_values(rt, orc):
+    """The 128 x 128 tile multiplies and adds PAIRS of columns with the packed f32x2 instructions (the product as a packed fma
+    with -0 as addend): signed zeros, subnormal products and sums, values that overflow to infinity and infinities themselves
+    come out as the oracle's separately rounded scalar chain has them."""
+    n, m, k = 2200, 2250, 5
+    rng = np.random.default_rng(9)
+    pool = np.array([0.0, -0.0, 1.0, -1.0, 1e-30, -1e-30, 1e-20, 3e-39, -3e-39, 1e30, -1e30, 3e38, np.inf, 0.5, -2.0, 1e-45],
+                    np.float32)
+    a = pool[rng.integers(0, len(pool), (n, k))]
+    b = pool[rng.integers(0, len(pool), (k, m))]
+    got = matmul(rt, a, b, n, m, k)
+    want = orc.matmul_f32(a, b, n, m, k, threads=orc.max_threads())
+    assert np.array_equal(np.isnan(got), np.isnan(want))        # NaN payloads are a hardware property
+    ok = ~np.isnan(want)
+    assert np.array_equal(u32(got)[ok], u32(want)[ok])
+    subnormal = (np.abs(want[ok]) > 0) & (np.abs(want[ok]) < np.float32(1.1754944e-38))
+    assert ok.sum() > got.size // 2 and subnormal.any() and np.isinf(want[ok]).any()
+
+
 def test_matmul_signed_zero_and_specials(rt, orc):
     a = np.array([[-0.0, 0.0, -1.0], [np.inf, 1.0, -0.0]], np.float32)
     b = np.array([[0.0, 1.0], [-0.0, 2.0], [0.0, -3.0]], np.float32)
