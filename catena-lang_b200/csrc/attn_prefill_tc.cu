@@ -258,6 +258,85 @@ __device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, ui
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
+// ---- packed f32x2 arithmetic (sm_100): one instruction, two separately rounded IEEE operations --------------------------
+// A product is written as fma(a, b, -0) with the -0 taken from a kernel ARGUMENT: ptxas merges a packed mul with the packed
+// add or sub that consumes it into one fma (explicit .rn and --fmad=false notwithstanding), which would round once; an
+// fma whose addend it cannot see stays an fma, and a * b + (-0) is exactly the rounded product.
+__device__ __forceinline__ uint64_t pk2(uint32_t lo, uint32_t hi) { uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi)); return d; }
+__device__ __forceinline__ uint64_t pk2f(float lo, float hi) { uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi)); return d; }
+__device__ __forceinline__ void unpk2(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) { uint64_t d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__host__ __device__ constexpr uint64_t twice(uint32_t bits) { return ((uint64_t)bits << 32) | bits; }
+
+// p[u] = exp~(scale * score[u] - m) for the 16 scores of one trip of the inner loop, none of them masked, two keys per
+// instruction: the arithmetic of exp_approx_nonpos_n stage by stage (same operations, same order, same roundings), with
+// mag = m - scale * score in place of -(scale * score - m) (round-to-nearest is symmetric, so the two are the same float).
+__device__ __forceinline__ void exp_scores_packed(const uint32_t (&v)[16], uint64_t scale2, uint64_t m2, uint64_t nz2, float (&out)[16]) {
+    uint64_t mag[8], sh[8], xr[8], p[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) mag[q] = sub2(m2, fma2(pk2(v[2 * q], v[2 * q + 1]), scale2, nz2));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) sh[q] = add2(fma2(mag[q], twice(0x3FB8AA3Bu), nz2), twice(0x4B400000u));      // + 12582912
+#pragma unroll
+    for (int q = 0; q < 8; ++q) p[q] = sub2(sh[q], twice(0x4B400000u));                                        // kf
+#pragma unroll
+    for (int q = 0; q < 8; ++q) xr[q] = sub2(mag[q], fma2(p[q], twice(0x3F317200u), nz2));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) xr[q] = sub2(xr[q], fma2(p[q], twice(0x35BFBE8Eu), nz2));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) p[q] = add2(twice(0x3EEF1187u), fma2(xr[q], twice(0x3E738A8Bu), nz2));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) p[q] = add2(twice(0x3F809C7Eu), fma2(xr[q], p[q], nz2));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) p[q] = add2(twice(0x3F7FF8FCu), fma2(xr[q], p[q], nz2));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        uint32_t s0, s1;
+        unpk2(sh[q], s0, s1);
+        p[q] = fma2(p[q], pk2((s0 - 0x4B400000u + 0x7Fu) * 0x00800000u, (s1 - 0x4B400000u + 0x7Fu) * 0x00800000u), nz2);
+    }
+    float pf[16], mg[16];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        uint32_t a, b;
+        unpk2(p[q], a, b);
+        pf[2 * q] = __uint_as_float(a);
+        pf[2 * q + 1] = __uint_as_float(b);
+        unpk2(mag[q], a, b);
+        mg[2 * q] = __uint_as_float(a);
+        mg[2 * q + 1] = __uint_as_float(b);
+    }
+    // p >= 0.5 always (a polynomial near 1 times 2^k, k >= 0); NaNs pass the test and stay NaNs either way
+    float big = pf[0];
+#pragma unroll
+    for (int u = 1; u + 1 < 16; u += 2) big = max3(big, pf[u], pf[u + 1]);
+    big = fmaxf(big, pf[15]);
+    if (big < kRcpFastBelow) {
+        // rcp_fast for two values at once: r = rcp.approx(p); e = 1 - p r; r += r e; e = 1 - p r; r += r e (fused steps)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            float r0, r1;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(pf[2 * q]));
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(pf[2 * q + 1]));
+            const uint64_t np = p[q] ^ twice(0x80000000u);
+            uint64_t r = pk2f(r0, r1);
+            uint64_t e = fma2(np, r, twice(0x3F800000u));
+            r = fma2(r, e, r);
+            e = fma2(np, r, twice(0x3F800000u));
+            r = fma2(r, e, r);
+            uint32_t a, b;
+            unpk2(r, a, b);
+            out[2 * q] = mg[2 * q] > 0.0f ? __uint_as_float(a) : pf[2 * q];
+            out[2 * q + 1] = mg[2 * q + 1] > 0.0f ? __uint_as_float(b) : pf[2 * q + 1];
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) out[u] = mg[u] > 0.0f ? cmath::recip(pf[u]) : pf[u];
+    }
+}
+
 // Optional cycle accounting of the consumers (build with -DCATENA_PF_PROFILE; one lane per consumer warp adds up where
 // its cycles go): [0] whole kernel, [1] pass 1, [2] pass 2, [3] pass 2 waiting for scores, [4] first TMEM load of a
 // tile, [5] waiting for the TMEM stores, [6] waiting for the outputs, [7] set-up before the roles start.
@@ -274,7 +353,7 @@ __device__ unsigned long long g_pf_prof[16];
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, uint32_t S, uint32_t Hq,
-                       uint32_t Hkv, float scale, uint32_t* err) {
+                       uint32_t Hkv, float scale, uint32_t* err, uint64_t neg_zero2) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* q_tile = smem;                                   // 32 KiB
@@ -439,6 +518,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int gI = 1; gI < kGroups; ++gI) m = fmaxf(m, ctl->xch[gI][r]);
         m = cmath::mul(m, scale);
+        const uint64_t scale2 = pk2f(scale, scale), m2 = pk2f(m, m);
         asm volatile("bar.sync 1, %0;" ::"n"(kGroups * kConsumers) : "memory");   // all parts read before xch is reused for the sums
         // ---- pass 2: probabilities into TMEM, row sum ----
         PF_T(pf_p2);
@@ -471,9 +551,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tmem_ld_wait();
                     PF_T(pf_l1);
                     if (c == 0) PF_ADD(4, pf_l1 - pf_l0);
+                    if (MASKED || kExpW != 16) {
 #pragma unroll
-                    for (uint32_t e = 0; e < 16; ++e) sc[e] = __uint_as_float(v[e]);
-                    if (c + 1 < (uint32_t)kKeys / kGroups / 16) tmem_ld16(base + (c + 1) * 16, v);
+                        for (uint32_t e = 0; e < 16; ++e) sc[e] = __uint_as_float(v[e]);
+                        if (c + 1 < (uint32_t)kKeys / kGroups / 16) tmem_ld16(base + (c + 1) * 16, v);
+                    }
+                    if constexpr (!MASKED && kExpW == 16) {
+                        // a whole trip of 16 unmasked keys, two per instruction
+                        float ps[16];
+                        exp_scores_packed(v, scale2, m2, neg_zero2, ps);
+                        if (c + 1 < (uint32_t)kKeys / kGroups / 16) tmem_ld16(base + (c + 1) * 16, v);
+#pragma unroll
+                        for (uint32_t u = 0; u < 16; ++u) l = cmath::add(l, ps[u]);                // ascending key order
+#pragma unroll
+                        for (uint32_t u = 0; u < 16; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[u >> 1], lo[u >> 1]);
+                    } else {
 #pragma unroll
                     for (uint32_t e = 0; e < 16; e += kExpW) {       // kExpW keys side by side
                         float xs[kExpW], ps[kExpW];
@@ -490,6 +582,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         }
 #pragma unroll
                         for (uint32_t u = 0; u < (uint32_t)kExpW; u += 2) split_hi_lo(ps[u], ps[u + 1], hi[(e + u) >> 1], lo[(e + u) >> 1]);
+                    }
                     }
                     // in place: the 16 score columns just read become 8 columns of hi parts and 8 of lo parts
                     tmem_st8(base + c * 16, hi);
@@ -642,7 +735,7 @@ catena_status_t enqueue_attn_prefill_tc(const void* q, const void* k_cache, cons
     dim3 grid((unsigned)ceil_div_u64(seq, attn3::kTile), (unsigned)hq, (unsigned)batch);
     attn3::attn_prefill_tc_kernel<<<grid, attn3::kThreads, smem, tls().stream>>>(map_q, map_k, map_v, (__nv_bfloat16*)out, (uint32_t)seq,
                                                                                 (uint32_t)hq, (uint32_t)hkv, 1.0f / sqrtf(128.0f),
-                                                                                g_attn3_err_dev[dev]);
+                                                                                g_attn3_err_dev[dev], 0x8000000080000000ull);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail_cuda(e, "attn_prefill_tc launch");
