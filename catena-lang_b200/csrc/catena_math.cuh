@@ -189,30 +189,95 @@ __device__ __forceinline__ bool all_within_64(const float (&x)[W]) {
     if (W % 2 == 0) big = fmaxf(big, fabsf(x[W - 1]));
     return big <= 64.0f;
 }
-// exp~(x) for a batch that passed all_within_64
+// ---- packed f32x2 arithmetic (sm_100): one instruction, two separately rounded IEEE operations ---------------------------
+// A PRODUCT is written as fma(a, b, -0) with the -0 read from constant memory: ptxas merges a packed mul with the packed add or
+// sub that consumes it into one fma — explicit .rn and --fmad=false notwithstanding (measured: the results are those of
+// fma.rn.f32x2) — which would round once.  An fma whose addend the assembler cannot see stays an fma, and a * b + (-0) is
+// exactly the rounded product (a zero product keeps its sign).  Sums, differences and genuine fmas need no such care.
+static __constant__ unsigned long long c_neg_zero2 = 0x8000000080000000ull;
+__device__ __forceinline__ uint64_t pk2f(float lo, float hi) { uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi)); return d; }
+__device__ __forceinline__ uint64_t pk2u(uint32_t lo, uint32_t hi) { uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi)); return d; }
+__device__ __forceinline__ void unpk2f(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ void unpk2u(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) { uint64_t d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) { return fma2(a, b, c_neg_zero2); }
+__host__ __device__ constexpr uint64_t twice(uint32_t bits) { return ((uint64_t)bits << 32) | bits; }
+// rcp_fast for two values: the same approximation and the same four fused steps per value
+__device__ __forceinline__ uint64_t rcp_fast2(uint64_t p) {
+    float p0, p1, r0, r1;
+    unpk2f(p, p0, p1);
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(p0));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(p1));
+    const uint64_t np = p ^ twice(0x80000000u);
+    uint64_t r = pk2f(r0, r1);
+    uint64_t e = fma2(np, r, twice(0x3F800000u));
+    r = fma2(r, e, r);
+    e = fma2(np, r, twice(0x3F800000u));
+    return fma2(r, e, r);
+}
+
+// exp~(x) for a batch that passed all_within_64: two values per instruction when W is even (same operations, same order,
+// same roundings as the scalar stages)
 template <int W>
 __device__ __forceinline__ void exp_fast_n(const float (&x)[W], float (&out)[W]) {
-    float mag[W], sh[W], kf[W], xr[W], p[W];
+    if constexpr (W % 2 == 0) {
+        constexpr int H = W / 2;
+        uint64_t mag[H], sh[H], xr[H], p[H];
 #pragma unroll
-    for (int u = 0; u < W; ++u) mag[u] = fabsf(x[u]);
+        for (int q = 0; q < H; ++q) mag[q] = pk2f(fabsf(x[2 * q]), fabsf(x[2 * q + 1]));
 #pragma unroll
-    for (int u = 0; u < W; ++u) sh[u] = add(mul(mag[u], from_bits(0x3FB8AA3Bu)), 12582912.0f);
+        for (int q = 0; q < H; ++q) sh[q] = add2(mul2(mag[q], twice(0x3FB8AA3Bu)), twice(0x4B400000u));     // + 12582912
 #pragma unroll
-    for (int u = 0; u < W; ++u) kf[u] = sub(sh[u], 12582912.0f);
+        for (int q = 0; q < H; ++q) p[q] = sub2(sh[q], twice(0x4B400000u));                                   // kf
 #pragma unroll
-    for (int u = 0; u < W; ++u) xr[u] = sub(mag[u], mul(kf[u], from_bits(0x3F317200u)));
+        for (int q = 0; q < H; ++q) xr[q] = sub2(mag[q], mul2(p[q], twice(0x3F317200u)));
 #pragma unroll
-    for (int u = 0; u < W; ++u) xr[u] = sub(xr[u], mul(kf[u], from_bits(0x35BFBE8Eu)));
+        for (int q = 0; q < H; ++q) xr[q] = sub2(xr[q], mul2(p[q], twice(0x35BFBE8Eu)));
 #pragma unroll
-    for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3EEF1187u), mul(xr[u], from_bits(0x3E738A8Bu)));
+        for (int q = 0; q < H; ++q) p[q] = add2(twice(0x3EEF1187u), mul2(xr[q], twice(0x3E738A8Bu)));
 #pragma unroll
-    for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3F809C7Eu), mul(xr[u], p[u]));
+        for (int q = 0; q < H; ++q) p[q] = add2(twice(0x3F809C7Eu), mul2(xr[q], p[q]));
 #pragma unroll
-    for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3F7FF8FCu), mul(xr[u], p[u]));
+        for (int q = 0; q < H; ++q) p[q] = add2(twice(0x3F7FF8FCu), mul2(xr[q], p[q]));
 #pragma unroll
-    for (int u = 0; u < W; ++u) p[u] = mul(p[u], from_bits((to_bits(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
+        for (int q = 0; q < H; ++q) {
+            uint32_t s0, s1;
+            unpk2u(sh[q], s0, s1);
+            p[q] = mul2(p[q], pk2u((s0 - 0x4B400000u + 0x7Fu) * 0x00800000u, (s1 - 0x4B400000u + 0x7Fu) * 0x00800000u));
+        }
 #pragma unroll
-    for (int u = 0; u < W; ++u) out[u] = x[u] < 0.0f ? rcp_fast(p[u]) : p[u];
+        for (int q = 0; q < H; ++q) {
+            float a, b, ra, rb;
+            unpk2f(p[q], a, b);
+            unpk2f(rcp_fast2(p[q]), ra, rb);
+            out[2 * q] = x[2 * q] < 0.0f ? ra : a;
+            out[2 * q + 1] = x[2 * q + 1] < 0.0f ? rb : b;
+        }
+    } else {
+        float mag[W], sh[W], kf[W], xr[W], p[W];
+#pragma unroll
+        for (int u = 0; u < W; ++u) mag[u] = fabsf(x[u]);
+#pragma unroll
+        for (int u = 0; u < W; ++u) sh[u] = add(mul(mag[u], from_bits(0x3FB8AA3Bu)), 12582912.0f);
+#pragma unroll
+        for (int u = 0; u < W; ++u) kf[u] = sub(sh[u], 12582912.0f);
+#pragma unroll
+        for (int u = 0; u < W; ++u) xr[u] = sub(mag[u], mul(kf[u], from_bits(0x3F317200u)));
+#pragma unroll
+        for (int u = 0; u < W; ++u) xr[u] = sub(xr[u], mul(kf[u], from_bits(0x35BFBE8Eu)));
+#pragma unroll
+        for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3EEF1187u), mul(xr[u], from_bits(0x3E738A8Bu)));
+#pragma unroll
+        for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3F809C7Eu), mul(xr[u], p[u]));
+#pragma unroll
+        for (int u = 0; u < W; ++u) p[u] = add(from_bits(0x3F7FF8FCu), mul(xr[u], p[u]));
+#pragma unroll
+        for (int u = 0; u < W; ++u) p[u] = mul(p[u], from_bits((to_bits(sh[u]) - 0x4B400000u + 0x7Fu) * 0x00800000u));
+#pragma unroll
+        for (int u = 0; u < W; ++u) out[u] = x[u] < 0.0f ? rcp_fast(p[u]) : p[u];
+    }
 }
 template <int W>
 __device__ __forceinline__ void exp_approx_n(const float (&x)[W], float (&out)[W]) {
@@ -230,8 +295,14 @@ __device__ __forceinline__ void sigmoid_n(const float (&x)[W], float (&out)[W]) 
 #pragma unroll
         for (int u = 0; u < W; ++u) nx[u] = -x[u];
         exp_fast_n(nx, e);
+        if constexpr (W % 2 == 0) {
 #pragma unroll
-        for (int u = 0; u < W; ++u) out[u] = rcp_fast(add(1.0f, e[u]));
+            for (int q = 0; q < W / 2; ++q)
+                unpk2f(rcp_fast2(add2(twice(0x3F800000u), pk2f(e[2 * q], e[2 * q + 1]))), out[2 * q], out[2 * q + 1]);
+        } else {
+#pragma unroll
+            for (int u = 0; u < W; ++u) out[u] = rcp_fast(add(1.0f, e[u]));
+        }
     } else {
 #pragma unroll
         for (int u = 0; u < W; ++u) out[u] = sigmoid(x[u]);
