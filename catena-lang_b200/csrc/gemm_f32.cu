@@ -30,6 +30,7 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     // columns of this thread's register tile: TN consecutive ones, or — for the 8-wide tile — 4 + 4 half a tile apart, so that
     // a warp's 16-byte reads of a Bs row are contiguous (conflict-free) instead of 32 bytes apart (4-way conflicts)
     constexpr bool SPLIT = TN == 8;
+    constexpr bool PACKED = TN % 2 == 0;      // pairs of neighbouring columns: packed f32x2 arithmetic
     auto col_of = [&](int j) { return SPLIT ? (j / 4) * (BN / 2) + tx * 4 + (j % 4) : tx * TN + j; };
 
     float acc[TM][TN];
@@ -37,14 +38,14 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     for (int i = 0; i < TM; ++i)
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;  // bit pattern 0x00000000 (matrix.hex:249)
-    // The 8 x 8 tile keeps its accumulators as PAIRS of neighbouring columns and works on them with the packed f32x2
-    // arithmetic of sm_100: each half is the same separately rounded IEEE product and sum, so the bits do not change, but a
-    // k step is 64 arithmetic instructions instead of 128.
-    uint64_t acc2[SPLIT ? TM : 1][SPLIT ? TN / 2 : 1];
+    // A register tile of even width keeps its accumulators as PAIRS of neighbouring columns and works on them with the packed
+    // f32x2 arithmetic of sm_100: each half is the same separately rounded IEEE product and sum, so the bits do not change,
+    // but a k step of the 8 x 8 tile is 64 arithmetic instructions instead of 128.
+    uint64_t acc2[PACKED ? TM : 1][PACKED ? TN / 2 : 1];
 #pragma unroll
-    for (int i = 0; i < (SPLIT ? TM : 1); ++i)
+    for (int i = 0; i < (PACKED ? TM : 1); ++i)
 #pragma unroll
-        for (int j = 0; j < (SPLIT ? TN / 2 : 1); ++j) acc2[i][j] = 0ull;
+        for (int j = 0; j < (PACKED ? TN / 2 : 1); ++j) acc2[i][j] = 0ull;
 
     // The next k-slab travels from global memory into registers while the current one is multiplied out of shared
     // memory (small products are latency bound: eight exposed slab loads were most of a 256^3 launch).
@@ -83,13 +84,22 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         stage();
         if (k0 + BK < k) fetch(k0 + BK);
         __syncthreads();
-        if constexpr (SPLIT) {
-            // one k step: four 16-byte loads for the 8 + 8 operands, then 32 packed products and 32 packed sums
+        if constexpr (PACKED) {
+            // one k step: the operands (for the 8 x 8 tile four 16-byte loads), then TM x TN / 2 packed products and sums
             auto step = [&](int kk) {
-                const ulonglong2 b0 = *reinterpret_cast<const ulonglong2*>(&Bs[kk][tx * 4]), b1 = *reinterpret_cast<const ulonglong2*>(&Bs[kk][BN / 2 + tx * 4]);
-                const float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * TM]), a1 = *reinterpret_cast<const float4*>(&As[kk][ty * TM + 4]);
-                const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const uint64_t bv[4] = {b0.x, b0.y, b1.x, b1.y};      // columns (0,1) (2,3) | (4,5) (6,7) of the register tile
+                float av[TM];
+                uint64_t bv[TN / 2];          // column pairs of the register tile
+                if constexpr (SPLIT) {
+                    const ulonglong2 b0 = *reinterpret_cast<const ulonglong2*>(&Bs[kk][tx * 4]), b1 = *reinterpret_cast<const ulonglong2*>(&Bs[kk][BN / 2 + tx * 4]);
+                    const float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * TM]), a1 = *reinterpret_cast<const float4*>(&As[kk][ty * TM + 4]);
+                    av[0] = a0.x; av[1] = a0.y; av[2] = a0.z; av[3] = a0.w; av[4] = a1.x; av[5] = a1.y; av[6] = a1.z; av[7] = a1.w;
+                    bv[0] = b0.x; bv[1] = b0.y; bv[2] = b1.x; bv[3] = b1.y;     // columns (0,1) (2,3) | (4,5) (6,7)
+                } else {
+#pragma unroll
+                    for (int i = 0; i < TM; ++i) av[i] = As[kk][ty * TM + i];
+#pragma unroll
+                    for (int j = 0; j < TN / 2; ++j) bv[j] = *reinterpret_cast<const uint64_t*>(&Bs[kk][tx * TN + 2 * j]);
+                }
 #pragma unroll
                 for (int i = 0; i < TM; ++i) {
                     uint64_t aa;
@@ -108,7 +118,7 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
                 }
             };
             if (kb == BK) {
-#pragma unroll 4
+#pragma unroll(TM * TN >= 64 ? 4 : 16)
                 for (int kk = 0; kk < BK; ++kk) step(kk);
             } else {
                 for (int kk = 0; kk < kb; ++kk) step(kk);
@@ -137,7 +147,7 @@ matmul_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         }
         __syncthreads();
     }
-    if constexpr (SPLIT) {
+    if constexpr (PACKED) {
 #pragma unroll
         for (int i = 0; i < TM; ++i)
 #pragma unroll
@@ -185,18 +195,24 @@ catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint
     uint64_t big_tiles = ceil_div_u64(n, 64) * ceil_div_u64(m, 64);
     const uint64_t huge_tiles = ceil_div_u64(n, 128) * ceil_div_u64(m, 128);
     // row tiles ride on grid.y (at most 65535): 4 194 240 rows with the 64-row tiles; taller products are refused, not mis-launched
-    if (ceil_div_u64(n, big_tiles >= (uint64_t)sms ? 64 : 16) > 65535)
+    if (ceil_div_u64(n, 3 * big_tiles >= 2 * (uint64_t)sms ? 64 : 16) > 65535)
         return fail(CATENA_E_TOO_LARGE, "matmul f32: more than 65535 row tiles (4194240 rows)");
     if (huge_tiles >= 2 * (uint64_t)sms) {
         // large products are bound by instruction issue (two FP instructions per multiply-add, by contract): an 8 x 8 register
         // tile spends 4 shared-memory loads per 128 of them where the 4 x 4 tile spends 2 per 32
         dim3 grid((unsigned)ceil_div_u64(m, 128), (unsigned)ceil_div_u64(n, 128));
         matmul_f32_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
-    } else if (big_tiles >= (uint64_t)sms) {
+    } else if (3 * big_tiles >= 2 * (uint64_t)sms) {          // from two thirds of a wave of 64 x 64 tiles on (768^3: 144 tiles)
         dim3 grid((unsigned)ceil_div_u64(m, 64), (unsigned)ceil_div_u64(n, 64));
         matmul_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
+    } else if (ceil_div_u64(m, 32) * ceil_div_u64(n, 16) >= 64) {
+        // small products are latency bound: more, smaller tiles to cover the SMs.  One element per thread reads two
+        // shared-memory words per multiply-add, which made shared memory the limit (8192 wavefronts per SM at 256^3); a 2 x 2
+        // register tile reads two 8-byte words per four (256^3: 8.1 against 10.3 us, 512^3: 28.7 against 45.3 us).
+        dim3 grid((unsigned)ceil_div_u64(m, 32), (unsigned)ceil_div_u64(n, 16));
+        matmul_f32_kernel<16, 32, 128, 2, 2><<<grid, 128, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
     } else {
-        // small products are latency bound: more, smaller tiles to cover the SMs
+        // tiny products: one element per thread, as many CTAs as there are 16 x 16 tiles
         dim3 grid((unsigned)ceil_div_u64(m, 16), (unsigned)ceil_div_u64(n, 16));
         matmul_f32_kernel<16, 16, 128, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
     }

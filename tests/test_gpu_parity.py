@@ -52,11 +52,13 @@ def test_matmul_reference_vectors(rt):
     assert r.v.to_f32_vec().tolist() == a
 
 
-@pytest.mark.parametrize("n,m,k", [(256, 256, 256), (1, 1, 1), (37, 53, 29), (130, 70, 257), (64, 64, 1),
-                                   (640, 1280, 96), (1000, 900, 515), (2200, 2250, 67)])
+@pytest.mark.parametrize("n,m,k", [(256, 256, 256), (1, 1, 1), (37, 53, 29), (130, 70, 257), (64, 64, 1), (300, 270, 131),
+                                   (513, 511, 40), (640, 1280, 96), (1000, 900, 515), (2200, 2250, 67)])
 def test_matmul_bit_exact(rt, orc, n, m, k):
-    """Every tile shape gives the oracle's bits: 16 x 16 tiles (small products), 64 x 64 with a 4 x 4 register tile, and — from
-    296 tiles of 128 x 128 on — an 8 x 8 register tile (the last case, with ragged edges and a partial k slab)."""
+    """Every tile shape gives the oracle's bits: 16 x 16 tiles of one element per thread (tiny products), 16 x 32 with a 2 x 2
+    register tile (small ones: 256^3, and 300 x 270 x 131 / 513 x 511 x 40 with ragged edges and a partial k slab), 64 x 64 with
+    a 4 x 4 register tile, and — from 296 tiles of 128 x 128 on — an 8 x 8 register tile (the last case, ragged too).  All but
+    the first work on pairs of columns with packed f32x2 arithmetic."""
     rng = np.random.default_rng(0)
     a = rng.uniform(-1, 1, (n, k)).astype(np.float32)
     b = rng.uniform(-1, 1, (k, m)).astype(np.float32)
