@@ -24,6 +24,7 @@ By default a launch runs the program COMPILED: the library writes PTX for it and
 """
 import ctypes as C
 import os
+import threading
 
 import numpy as np
 
@@ -79,6 +80,9 @@ class _Buffer:
         self.slot, self.lowered = slot, lowered
 
 
+_COMPILE_LOCK = threading.Lock()
+
+
 class MapProgram:
     """A compiled producer.  `env_kinds` lists the runtime environment values the launch must supply, in order: 'f32',
     'u32', 'u64', 'bool' (scalars) or 'buffer'."""
@@ -130,14 +134,18 @@ class MapProgram:
         """Handle of the kernel compiled for the current device (built on first use, kept for the program's lifetime)."""
         from . import check, lib
         device = int(lib().catena_b200_current_device())
-        if not hasattr(self, "_kernels"):
-            self._kernels = {}
-        if device not in self._kernels:
-            init = [what[1] if what[0] == "const" else 0 for what in self.presets]
-            handle = C.c_void_p()
-            check(lib().catena_b200_map_compile_s(*self._spec(init), C.byref(handle)))
-            self._kernels[device] = handle
-        return self._kernels[device]
+        if device < 0:                       # no call has bound a device yet: the library's lazy default, device 0
+            check(lib().catena_b200_init(0))
+            device = 0
+        with _COMPILE_LOCK:                 # two host threads launching a new program compile it once
+            if not hasattr(self, "_kernels"):
+                self._kernels = {}
+            if device not in self._kernels:
+                init = [what[1] if what[0] == "const" else 0 for what in self.presets]
+                handle = C.c_void_p()
+                check(lib().catena_b200_map_compile_s(*self._spec(init), C.byref(handle)))
+                self._kernels[device] = handle
+            return self._kernels[device]
 
     def __del__(self):
         for handle in getattr(self, "_kernels", {}).values():
