@@ -145,6 +145,58 @@ struct Emitter {
         fault("!%p1", ERR_RANGE);
     }
 
+    // f32 arithmetic of elements v and v + 1 as ONE packed f32x2 instruction (sm_100): each half is the scalar instruction's
+    // separately rounded IEEE operation.  A product is fma(a, b, -0) with the -0 from a kernel parameter: ptxas merges a packed mul
+    // with the packed add or sub that consumes it into one fma, explicit .rn notwithstanding (measured: csrc/gemm_f32.cu), and an
+    // fma whose addend it cannot see stays an fma; a * b + (-0) is exactly the rounded product.  Returns false for other opcodes.
+    bool packed_pair(uint32_t k, uint32_t v) {
+        const catena_b200_map_insn_t& in = s.code[k];
+        auto pair = [&](const char* rd, uint32_t reg) { line("mov.b64 %s, {%s, %s};", rd, lo(v, reg).c_str(), lo(v + 1, reg).c_str()); };
+        auto result = [&](const char* rd) { line("mov.b64 {%s, %s}, %s;", lo(v, in.dst).c_str(), lo(v + 1, in.dst).c_str(), rd); };
+        switch (in.op) {
+        case CATENA_MAP_F32_ADD:
+        case CATENA_MAP_F32_SUB:
+            pair("%rd0", in.a);
+            pair("%rd1", in.b);
+            line("%s.rn.f32x2 %%rd2, %%rd0, %%rd1;", in.op == CATENA_MAP_F32_ADD ? "add" : "sub");
+            result("%rd2");
+            return true;
+        case CATENA_MAP_F32_MUL:
+            pair("%rd0", in.a);
+            pair("%rd1", in.b);
+            line("fma.rn.f32x2 %%rd2, %%rd0, %%rd1, %%nz2;");
+            result("%rd2");
+            return true;
+        case CATENA_MAP_F32_FMA:
+            pair("%rd0", in.a);
+            pair("%rd1", in.b);
+            pair("%rd2", in.c);
+            line("fma.rn.f32x2 %%rd3, %%rd0, %%rd1, %%rd2;");
+            result("%rd3");
+            return true;
+        case CATENA_MAP_F32_MULADD:
+        case CATENA_MAP_F32_MULSUB:
+        case CATENA_MAP_F32_SUBMUL:
+            pair("%rd0", in.a);
+            pair("%rd1", in.b);
+            pair("%rd2", in.c);
+            line("fma.rn.f32x2 %%rd3, %%rd0, %%rd1, %%nz2;");
+            if (in.op == CATENA_MAP_F32_MULADD) line("add.rn.f32x2 %%rd3, %%rd3, %%rd2;");
+            else if (in.op == CATENA_MAP_F32_MULSUB) line("sub.rn.f32x2 %%rd3, %%rd3, %%rd2;");
+            else line("sub.rn.f32x2 %%rd3, %%rd2, %%rd3;");
+            result("%rd3");
+            return true;
+        default: return false;
+        }
+    }
+    // instruction k for all elements of the thread
+    void instruction_all(uint32_t k) {
+        for (uint32_t v = 0; v < lanes; ++v) {
+            if (v + 1 < lanes && packed_pair(k, v)) ++v;
+            else instruction(k, v);
+        }
+    }
+
     // one program instruction for element v; `k` is its index (jump bookkeeping)
     void instruction(uint32_t k, uint32_t v) {
         const catena_b200_map_insn_t& in = s.code[k];
@@ -281,7 +333,8 @@ struct Emitter {
         line(".param .u64 p_out,");
         line(".param .u64 p_index0,");
         line(".param .u64 p_len,");
-        line(".param .u64 p_err)");
+        line(".param .u64 p_err,");
+        line(".param .u64 p_nz2)");
         out += ".reqntid " + std::to_string(kThreads) + ", 1, 1\n{\n";
         if (s.n_init) line(".reg .b32 %%lc_<%u>, %%hc_<%u>;", s.n_init, s.n_init);
         for (uint32_t v = 0; v < lanes; ++v) {
@@ -290,7 +343,7 @@ struct Emitter {
             line(".reg .pred %%ok%u;", v);
         }
         if (nb) line(".reg .b64 %%bb_<%u>, %%bn8_<%u>, %%bn4_<%u>;", nb, nb, nb);
-        line(".reg .b64 %%rd<4>, %%out, %%index0, %%len, %%err, %%tile, %%tiles, %%step, %%tid64;");
+        line(".reg .b64 %%rd<4>, %%out, %%index0, %%len, %%err, %%tile, %%tiles, %%step, %%tid64, %%nz2;");
         line(".reg .b32 %%r<4>, %%fault, %%back, %%gave;");
         line(".reg .pred %%p<4>;");
         out += "\n";
@@ -299,6 +352,7 @@ struct Emitter {
         line("ld.param.u64 %%err, [p_err];");
         line("cvta.to.global.u64 %%err, %%err;");
         line("ld.param.u64 %%index0, [p_index0];");
+        line("ld.param.u64 %%nz2, [p_nz2];");
         line("ld.param.u64 %%len, [p_len];");
         for (uint32_t j = 0; j < nb; ++j) {
             line("ld.param.u64 %%bb_%u, [p_bufs+%u];", j, 16 * j);
@@ -356,7 +410,7 @@ struct Emitter {
                 unpack(v, s.index_reg, v ? "%rd1" : "%rd0");
             }
             for (uint32_t k = 0; k < s.n_insn && s.code[k].op != CATENA_MAP_HALT; ++k)
-                for (uint32_t v = 0; v < lanes; ++v) instruction(k, v);
+                instruction_all(k);
             for (uint32_t v = 0; v < lanes; ++v) {
                 if (s.elem_bytes == 8) {
                     line("mov.b64 %%rd1, {%s, %s};", lo(v, s.result_reg).c_str(), hi(v, s.result_reg).c_str());
@@ -393,7 +447,7 @@ struct Emitter {
         for (uint32_t k = 0; k < s.n_insn; ++k) {
             if (target[k]) out += "L_" + std::to_string(k) + ":\n";
             if (lanes > 1 && s.code[k].op == CATENA_MAP_HALT) break;       // straight line: the first HALT ends the element
-            for (uint32_t v = 0; v < lanes; ++v) instruction(k, v);
+            instruction_all(k);
         }
         line("bra STORE;");
         out += "GIVE_UP:\n";
@@ -559,7 +613,8 @@ catena_status_t catena_b200_map_kernel_launch_s(const catena_b200_map_kernel_t* 
     uint64_t blocks = ceil_div_u64(len, (uint64_t)mapjit::kThreads * kernel->lanes);
     if (blocks > (uint64_t)sms * kernel->ctas_per_sm) blocks = (uint64_t)sms * kernel->ctas_per_sm;
     uint64_t out_ptr = (uint64_t)(uintptr_t)result, err_ptr = (uint64_t)(uintptr_t)err;
-    void* params[6] = {dyn.data(), bufs, &out_ptr, &index0, &len, &err_ptr};
+    uint64_t neg_zero2 = 0x8000000080000000ull;        // two packed -0.0f: the addend that makes a packed fma a rounded product
+    void* params[7] = {dyn.data(), bufs, &out_ptr, &index0, &len, &err_ptr, &neg_zero2};
     const CUresult r = mapjit::driver().launch(kernel->function, (unsigned)blocks, 1, 1, mapjit::kThreads, 1, 1, 0, (CUstream)tls().stream, params, nullptr);
     count_launch();
     catena_status_t s = CATENA_OK;

@@ -83,7 +83,11 @@ def test_f32_arithmetic_is_explicitly_rounded_and_constants_are_immediates():
         m = re.match(r"(@!?%\w+ )?(add|sub|mul|div|fma|rcp)\.(\S+)", l)
         if m and m.group(3).endswith("f32"):
             assert ".rn." in l, l                      # an explicitly rounded operation is never contracted
-    assert not any(l.startswith("fma") for l in body)  # nn.silu has no f32.fma: products and sums round separately
+    # nn.silu has no f32.fma: products and sums round separately.  The only fmas are the PRODUCTS of two elements at once,
+    # a * b + (-0) with the -0 from a kernel parameter (a packed mul would be merged with the add behind it by ptxas)
+    fmas = [l for l in body if l.startswith("fma")]
+    assert fmas and all(l.startswith("fma.rn.f32x2") and l.endswith("%nz2;") for l in fmas)
+    assert any(l.startswith("add.rn.f32x2") for l in body) and not any(l.startswith("mul.rn.f32x2") for l in body)
     # 1 / x is the correctly rounded reciprocal (both divisions of nn.sigmoid are 1 / x)
     assert any(l.startswith("rcp.rn.f32") for l in body) and not any(l.startswith("div.") for l in body)
     # the polynomial's coefficients are immediates; the only kernel-parameter preset would be an environment scalar (none here)

@@ -342,3 +342,33 @@ def test_one_compiled_kernel_serves_every_environment():
         cb.free(raw)
         cb.free(m)
     assert prog.compiled().value == handle
+
+
+def test_compiled_reciprocal_is_the_ieee_reciprocal_for_every_class_of_operand():
+    """`1 / x` in a compiled kernel is `rcp.rn`, in the interpreter an IEEE division: the same bits for zeros, subnormals,
+    infinities, negative and huge values (NaN results compared as NaNs), and numpy's quotient."""
+    from catena_lang_b200.map_program import MapProgram
+    rng = np.random.default_rng(77)
+    bits = np.concatenate([
+        rng.integers(0, 2 ** 32, 200_000, dtype=np.uint64).astype(np.uint32),                      # every class, NaNs included
+        rng.uniform(0.5, 4.0, 100_000).astype(np.float32).view(np.uint32),
+        np.array([0x3F000000, 0x3EFFFFFF, 0x717FFFFF, 0x71800000, 0x00000000, 0x80000000, 0x00000001, 0x007FFFFF, 0x00800000,
+                  0x7F800000, 0xFF800000, 0x7F7FFFFF, 0x3F800000, 0x3F7FFFFF, 0x3F800001, 0x7E800000, 0x7F000000], np.uint32)])
+    x = bits.view(np.float32)
+    # registers: 0 = 1.0f (constant), 1 = index, 2 = x[i], 3 = 1 / x[i]
+    code = [Insn(OP["LOAD_F32"], 2, 1, 0, 0, 0, 0), Insn(OP["F32_DIV"], 3, 0, 2, 0, 0, 0), Insn(OP["HALT"], 0, 0, 0, 0, 0, 0)]
+    prog = MapProgram("reciprocal", code, [("const", 0x3F800000)], 4, 1, 3, ["buffer"], 4)
+    m = cb.upload(x)
+    outs = []
+    for compiled in (True, False):
+        raw = prog.launch(x.size, [(m.data, m.len)], compiled=compiled)
+        outs.append(cb.download(raw, np.uint32))
+        cb.free(raw)
+    cb.free(m)
+    got, want = outs[0].view(np.float32), outs[1].view(np.float32)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(outs[0][ok], outs[1][ok])
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore", under="ignore"):
+        host = (np.float32(1.0) / x).astype(np.float32)
+    assert np.array_equal(outs[1][ok], host.view(np.uint32)[ok])          # and both are numpy's IEEE quotient
