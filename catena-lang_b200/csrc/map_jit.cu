@@ -14,7 +14,8 @@
 // V = 1 for programs with `bool.ifc` branches or `reducec` loops.  Register k of the program is a pair of 32-bit PTX
 // registers (low, high half) per element, exactly the interpreter's split: 32-bit instructions write the low half only.
 // Preset registers are shared by the four elements; constants of the program are immediates, environment values are kernel
-// parameters.
+// parameters.  With four elements per thread the f32 sums, differences, products and fmas of elements (0, 1) and (2, 3) are one
+// packed f32x2 instruction each (packed_pair below): half the arithmetic instructions of a kernel that is bound by issue.
 //
 // Nothing a compiled program does can fault or hang the GPU, for the same reasons as in the interpreter: the program is
 // validated first; loads are predicated on the bounds check; taken backward jumps are counted against the same budget; the
