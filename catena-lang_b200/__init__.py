@@ -170,6 +170,7 @@ def lib():
     proto("catena_b200_debug_set_prefill_tc", None, [C.c_int])
     proto("catena_b200_debug_set_decode_fused", None, [C.c_int])
     proto("catena_b200_debug_rcp_check", C.c_int, [C.POINTER(C.c_uint64)])
+    proto("catena_b200_debug_packed_f32x2_check", C.c_int, [C.POINTER(C.c_uint64)])
     proto("catena_b200_debug_set_wait_limit_ns", None, [u64])
     proto("catena_b200_debug_stall_next", None, [C.c_int, C.c_uint32])
     _lib = L

@@ -68,6 +68,7 @@ static inline uint64_t ceil_div_u64(uint64_t a, uint64_t b) { return (a + b - 1)
 catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint64_t n, uint64_t m,
                                   uint64_t k);
 catena_status_t launch_identity_matmul_f32(const float* a, float* c, uint64_t n, int identity_on_left);
+catena_status_t packed_f32x2_check(uint64_t out[3]);
 // gemm_tc.cu
 catena_status_t launch_gemm_tc(const void* a, const void* b, void* c, uint64_t m, uint64_t n, uint64_t k,
                                uint64_t ldc, int is_i8);

@@ -183,6 +183,40 @@ __global__ void identity_matmul_kernel(const float* __restrict__ A, float* __res
     C[idx] = acc;
 }
 
+// Check of the packed forms the kernels above (and catena_math.cuh, map_jit.cu) rely on, over `n` pseudo-random operand
+// triples per thread: counts[0] = pairs compared; counts[1] = pairs where fma.rn.f32x2(a, b, z) followed by add.rn.f32x2
+// (z = -0 from a kernel argument) differs from __fadd_rn(c, __fmul_rn(a, b)) — must be 0; counts[2] = pairs where
+// mul.rn.f32x2 followed by add.rn.f32x2 differs — NOT 0 with CUDA 12.9: the assembler merges the two into one fma.
+__global__ void packed_f32x2_check_kernel(unsigned long long* counts, uint32_t n, uint64_t neg_zero2) {
+    uint32_t state = (blockIdx.x * blockDim.x + threadIdx.x) * 2654435761u + 12345u;
+    auto next = [&]() {             // xorshift; floats in [-2, 2) with every mantissa pattern, a few exact zeros and tiny values
+        state ^= state << 13; state ^= state >> 17; state ^= state << 5;
+        const uint32_t pick = state & 63u;
+        if (pick == 0) return (state & 0x80000000u);                               // +0 / -0
+        if (pick == 1) return (state & 0x807FFFFFu) | 0x00800000u;                 // tiny normal
+        return (state & 0x807FFFFFu) | (0x3F000000u + ((state >> 8) & 0x01000000u));
+    };
+    unsigned long long compared = 0, bad_fma_form = 0, bad_mul_form = 0;
+    for (uint32_t k = 0; k < n; ++k) {
+        const uint32_t a0 = next(), a1 = next(), b0 = next(), b1 = next(), c0 = next(), c1 = next();
+        const uint64_t a = ((uint64_t)a1 << 32) | a0, b = ((uint64_t)b1 << 32) | b0, c = ((uint64_t)c1 << 32) | c0;
+        uint64_t p, viaFma, viaMul;
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(a), "l"(b), "l"(neg_zero2));
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(viaFma) : "l"(c), "l"(p));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(p) : "l"(a), "l"(b));
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(viaMul) : "l"(c), "l"(p));
+        const uint32_t w0 = __float_as_uint(__fadd_rn(__uint_as_float(c0), __fmul_rn(__uint_as_float(a0), __uint_as_float(b0))));
+        const uint32_t w1 = __float_as_uint(__fadd_rn(__uint_as_float(c1), __fmul_rn(__uint_as_float(a1), __uint_as_float(b1))));
+        const uint64_t want = ((uint64_t)w1 << 32) | w0;
+        ++compared;
+        bad_fma_form += viaFma != want;
+        bad_mul_form += viaMul != want;
+    }
+    atomicAdd(&counts[0], compared);
+    atomicAdd(&counts[1], bad_fma_form);
+    atomicAdd(&counts[2], bad_mul_form);
+}
+
 // two packed -0.0f: the addend that makes a packed fma a rounded product (passed as an argument: see the kernel)
 static const uint64_t kNegZero2 = 0x8000000080000000ull;
 
@@ -217,6 +251,21 @@ catena_status_t launch_matmul_f32(const float* a, const float* b, float* c, uint
         matmul_f32_kernel<16, 16, 128, 1, 1><<<grid, 256, 0, st>>>(a, b, c, (int)n, (int)m, (int)k, kNegZero2);
     }
     count_launch();
+    return CATENA_OK;
+}
+
+catena_status_t packed_f32x2_check(uint64_t out[3]) {
+    unsigned long long* dev = nullptr;
+    CATENA_CUDA(cudaMalloc(&dev, 3 * sizeof(unsigned long long)));
+    cudaMemsetAsync(dev, 0, 3 * sizeof(unsigned long long), tls().stream);
+    packed_f32x2_check_kernel<<<148 * 4, 256, 0, tls().stream>>>(dev, 256, kNegZero2);
+    count_launch();
+    unsigned long long host[3] = {0, 0, 0};
+    cudaError_t e = cudaMemcpyAsync(host, dev, sizeof(host), cudaMemcpyDeviceToHost, tls().stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(tls().stream);
+    cudaFree(dev);
+    if (e != cudaSuccess) return fail_cuda(e, "packed f32x2 check");
+    for (int i = 0; i < 3; ++i) out[i] = host[i];
     return CATENA_OK;
 }
 

@@ -319,6 +319,12 @@ catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]) {
     return attn_prefill_rcp_check(out);
 }
 
+catena_status_t catena_b200_debug_packed_f32x2_check(uint64_t out[3]) {
+    if (!out) return fail(CATENA_E_BAD_ARG, "packed f32x2 check: null argument");
+    CATENA_TRY(ensure_device());
+    return packed_f32x2_check(out);
+}
+
 catena_status_t catena_b200_check_device_errors(void) {
     CATENA_TRY(gemm_tc_check_errors());
     CATENA_TRY(decode_fused_check_errors());

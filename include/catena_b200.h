@@ -428,6 +428,13 @@ void catena_b200_debug_attn_last_launch(uint32_t out[4]);
  * [0.5, 2^100); this compares that sequence with the IEEE reciprocal for EVERY float of the range on the device:
  * out[0] = values compared, out[1] = mismatches (must be 0).  No counterpart in the reference. */
 catena_status_t catena_b200_debug_rcp_check(uint64_t out[2]);
+/* test hook: the kernels that use sm_100's packed f32x2 arithmetic write a product as fma.rn.f32x2(a, b, -0) with the -0 hidden
+ * from the assembler, because a packed mul is merged with the packed add behind it into one fma (which rounds once, against
+ * the contract of catena-lang/src/runtime/artifact.rs:59-80).  Over pseudo-random operands on the device: out[0] = pairs
+ * compared, out[1] = pairs where the fma form followed by a packed add differs from __fadd_rn(c, __fmul_rn(a, b)) (must be
+ * 0), out[2] = pairs where a packed mul followed by a packed add differs (not 0 while the assembler merges them).  No
+ * counterpart in the reference. */
+catena_status_t catena_b200_debug_packed_f32x2_check(uint64_t out[3]);
 /* test hooks for the give-up path of the bounded device-side waits (catena-lang/src/codegen/prelude.rs:38-55 traps
  * instead; here a wait that runs out makes the kernel drain its copies, free its tensor memory and return, and the host
  * reports CATENA_E_TIMEOUT).  set_wait_limit_ns: limit of every wait in the tcgen05 GEMM (CTA-pair kernel) and the
