@@ -469,7 +469,7 @@ def kernel_suite(cb, L, torch, dev, stream, peaks, sm_max_mhz):
             roof["note"] = ("the same register program on the library's interpreter (the cross-check of the compiled kernel): bound by "
                             "the interpreter's instruction issue, not by HBM; same bits")
         if which in ("sum_u64", "dot_u64"):
-            roof["note"] = "each step is a whole program call: two kernels, an 8-byte copy back and a stream synchronisation"
+            roof["note"] = "each step is a whole program call: one kernel whose last CTA writes the total to pinned host memory, and a stream synchronisation"
         out[name] = {"case": desc, "us_per_launch": ms * 1e3, "value": value, "unit": unit, "steps": steps, "sm_mhz": sampled_mhz, "roofline": roof}
     cb.check(L.catena_b200_check_device_errors())
     return out

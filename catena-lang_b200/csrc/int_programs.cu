@@ -29,10 +29,13 @@ __device__ __forceinline__ uint64_t block_sum(uint64_t v, uint64_t* smem) {
     return t;      // valid in thread 0
 }
 
-// partial[b] = sum over this block's grid-stride share of x[i] (* y[i] when DOT)
+// One launch folds the whole buffer: every CTA adds the sum of its grid-stride share of x[i] (* y[i] when DOT) to work[0]
+// with one 64-bit atomic (addition modulo 2^64 is associative and commutative: any order gives the same bits), then takes a
+// ticket from work[1]; the CTA that draws the last ticket reads the total, writes it to `result` — a word of pinned host
+// memory, so that no copy follows the kernel — and puts both words back to zero for the next call.
 template <bool DOT>
 __global__ void __launch_bounds__(kThreads) fold_u64_kernel(const uint64_t* __restrict__ x, const uint64_t* __restrict__ y, uint64_t n,
-                                                            uint64_t* __restrict__ partial) {
+                                                            unsigned long long* work, unsigned long long* result) {
     __shared__ uint64_t smem[kThreads / 32];
     uint64_t acc = 0;
     const uint64_t stride = (uint64_t)gridDim.x * kThreads * 2;
@@ -56,15 +59,35 @@ __global__ void __launch_bounds__(kThreads) fold_u64_kernel(const uint64_t* __re
         }
     }
     const uint64_t t = block_sum(acc, smem);
-    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+    if (threadIdx.x == 0) {
+        atomicAdd(&work[0], (unsigned long long)t);
+        __threadfence();                                          // the sum is visible before the ticket is
+        if (atomicAdd(&work[1], 1ull) == (unsigned long long)gridDim.x - 1) {
+            __threadfence();
+            *result = atomicExch(&work[0], 0ull);                 // every CTA's sum is in: read the total and clear it
+            work[1] = 0;
+        }
+    }
 }
 
-__global__ void __launch_bounds__(kThreads) fold_u64_finish_kernel(const uint64_t* __restrict__ partial, uint32_t count, uint64_t* __restrict__ out) {
-    __shared__ uint64_t smem[kThreads / 32];
-    uint64_t acc = 0;
-    for (uint32_t i = threadIdx.x; i < count; i += kThreads) acc += partial[i];
-    const uint64_t t = block_sum(acc, smem);
-    if (threadIdx.x == 0) *out = t;
+// Per host thread and device: the two device words of the kernel above (zero between calls) and the pinned host word
+// the last CTA writes the total to.
+struct FoldState {
+    unsigned long long* work = nullptr;
+    unsigned long long* result = nullptr;      // cudaHostAlloc: the same address on host and device
+};
+static thread_local FoldState g_fold_state[kMaxDevices];
+
+static catena_status_t fold_state(FoldState** out) {
+    FoldState& st = g_fold_state[tls().device];
+    if (!st.work) {
+        CATENA_CUDA(cudaMalloc(&st.work, 2 * sizeof(unsigned long long)));
+        CATENA_CUDA(cudaMemset(st.work, 0, 2 * sizeof(unsigned long long)));
+        CATENA_CUDA(cudaHostAlloc(&st.result, sizeof(unsigned long long), cudaHostAllocPortable | cudaHostAllocMapped));
+        *st.result = 0;
+    }
+    *out = &st;
+    return CATENA_OK;
 }
 
 catena_status_t fold_u64(const uint64_t* x, const uint64_t* y, uint64_t n, uint64_t* host_out) {
@@ -75,21 +98,21 @@ catena_status_t fold_u64(const uint64_t* x, const uint64_t* y, uint64_t n, uint6
     const int sms = tls().sm_count > 0 ? tls().sm_count : 148;
     uint64_t blocks = ceil_div_u64(n, (uint64_t)kThreads * kPerThread);
     if (blocks > (uint64_t)sms * 8) blocks = (uint64_t)sms * 8;            // grid: at most 8 CTAs per SM, grid-stride beyond
-    void* scratch = nullptr;
-    CATENA_TRY(pool_alloc((blocks + 1) * sizeof(uint64_t), &scratch));
-    uint64_t* partial = static_cast<uint64_t*>(scratch);
+    FoldState* fs = nullptr;
+    CATENA_TRY(fold_state(&fs));
     cudaStream_t st = tls().stream;
-    if (y) fold_u64_kernel<true><<<(unsigned)blocks, kThreads, 0, st>>>(x, y, n, partial);
-    else fold_u64_kernel<false><<<(unsigned)blocks, kThreads, 0, st>>>(x, nullptr, n, partial);
-    fold_u64_finish_kernel<<<1, kThreads, 0, st>>>(partial, (uint32_t)blocks, partial + blocks);
-    count_launch(2);
-    catena_status_t s = CATENA_OK;
+    if (y) fold_u64_kernel<true><<<(unsigned)blocks, kThreads, 0, st>>>(x, y, n, fs->work, fs->result);
+    else fold_u64_kernel<false><<<(unsigned)blocks, kThreads, 0, st>>>(x, nullptr, n, fs->work, fs->result);
+    count_launch();
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaMemcpyAsync(host_out, partial + blocks, sizeof(uint64_t), cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) s = fail_cuda(e, "u64 fold");
-    pool_free(scratch);
-    return s;
+    if (e != cudaSuccess) {
+        // a launch that did not complete may have left the words half way: clear them before the next call
+        (void)cudaMemset(fs->work, 0, 2 * sizeof(unsigned long long));
+        return fail_cuda(e, "u64 fold");
+    }
+    *host_out = *fs->result;
+    return CATENA_OK;
 }
 
 inline catena_status_t check_u64_mem(catena_mem_t m, const char* what) {
