@@ -125,7 +125,7 @@ catena_status_t decode_fused_check_errors();
 // map_program.cu
 catena_status_t map_program_check_errors();
 catena_status_t map_program_validate(const catena_b200_map_insn_t* code, uint32_t n_insn, uint32_t n_init, uint32_t n_regs, uint32_t index_reg,
-                                     uint32_t result_reg, uint32_t n_buffers);
+                                     uint32_t result_reg, uint32_t n_buffers, uint32_t max_regs);
 catena_status_t map_program_error_word(uint32_t** err);     // the device error word the interpreter and the compiled kernels share
 // map_reduce.cu
 enum ReduceKind { RED_SUM = 0, RED_MAX = 1, RED_SUMSQ = 2 };

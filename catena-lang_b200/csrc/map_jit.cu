@@ -34,6 +34,9 @@ namespace catena {
 namespace mapjit {
 
 constexpr uint32_t kThreads = 256;
+// A compiled program's registers are PTX virtual registers (the assembler allocates the real ones), so the file may be larger
+// than the interpreter's 256, which sit in shared memory: programs with branches get no register reuse from the host compilers.
+constexpr uint32_t kMaxRegs = 4096;
 constexpr uint32_t kBackJumpBudget = 1u << 22;      // as map_program.cu
 enum Err : uint32_t { ERR_ASSERT = 1, ERR_RANGE = 2, ERR_UNDEFINED = 3, ERR_BUDGET = 4 };
 
@@ -482,7 +485,11 @@ struct Emitter {
 static catena_status_t check_spec(const Spec& s) {
     if (s.elem_bytes != 4 && s.elem_bytes != 8) return fail(CATENA_E_BAD_ARG, "map kernel: elements of 4 or 8 bytes");
     if (s.n_init && !s.init) return fail(CATENA_E_BAD_ARG, "map kernel: null argument");
-    return map_program_validate(s.code, s.n_insn, s.n_init, s.n_regs, s.index_reg, s.result_reg, s.n_buffers);
+    CATENA_TRY(map_program_validate(s.code, s.n_insn, s.n_init, s.n_regs, s.index_reg, s.result_reg, s.n_buffers, kMaxRegs));
+    uint32_t dynamic = 0;
+    for (uint32_t k = 0; k < s.n_init; ++k) dynamic += !(s.is_const && s.is_const[k]);
+    if (dynamic > 256) return fail(CATENA_E_TOO_LARGE, "map kernel: more than 256 environment presets (they travel as kernel parameters)");
+    return CATENA_OK;
 }
 
 // ---- driver entry points (looked up through the runtime: the library does not link libcuda) -------------------------

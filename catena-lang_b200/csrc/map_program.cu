@@ -312,9 +312,10 @@ static uint32_t operand_mask(uint32_t op) {
 }
 
 static catena_status_t validate(const catena_b200_map_insn_t* code, uint32_t n_insn, uint32_t n_init, uint32_t n_regs, uint32_t index_reg,
-                                uint32_t result_reg, uint32_t n_buffers) {
+                                uint32_t result_reg, uint32_t n_buffers, uint32_t max_regs = kMaxRegs) {
     if (!code || n_insn == 0 || n_insn > kMaxInsns) return fail(CATENA_E_BAD_ARG, "map program: between 1 and 2048 instructions");
-    if (n_regs == 0 || n_regs > kMaxRegs || n_init > n_regs) return fail(CATENA_E_BAD_ARG, "map program: at most 256 registers, preset ones included");
+    if (n_regs == 0 || n_regs > max_regs || n_init > n_regs)
+        return fail(CATENA_E_BAD_ARG, "map program: too many registers (interpreted: 256, compiled: 4096; preset ones included)");
     if (index_reg < n_init || index_reg >= n_regs || result_reg >= n_regs) return fail(CATENA_E_BAD_ARG, "map program: index or result register out of range");
     if (n_buffers > kMaxBuffers) return fail(CATENA_E_BAD_ARG, "map program: more than 16 buffers");
     if (code[n_insn - 1].op != CATENA_MAP_HALT) return fail(CATENA_E_BAD_ARG, "map program: the last instruction must be HALT");
@@ -336,8 +337,8 @@ static catena_status_t validate(const catena_b200_map_insn_t* code, uint32_t n_i
 }  // namespace mapvm
 
 catena_status_t map_program_validate(const catena_b200_map_insn_t* code, uint32_t n_insn, uint32_t n_init, uint32_t n_regs, uint32_t index_reg,
-                                     uint32_t result_reg, uint32_t n_buffers) {
-    return mapvm::validate(code, n_insn, n_init, n_regs, index_reg, result_reg, n_buffers);
+                                     uint32_t result_reg, uint32_t n_buffers, uint32_t max_regs) {
+    return mapvm::validate(code, n_insn, n_init, n_regs, index_reg, result_reg, n_buffers, max_regs);
 }
 
 catena_status_t map_program_error_word(uint32_t** err) {

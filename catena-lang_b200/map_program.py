@@ -58,7 +58,8 @@ _ALIASES = {"bool.id", ":.forget", "u64.name", "ix.to-u64", "u32.bitcast-f32", "
 _PRESETS = {"bool.t": 1, "bool.f": 0, "u64.zero": 0, "u64.one": 1, "u32.one": 1, "f32.one": 0x3F800000}
 _ELEM = {"ptr<f32>": ("LOAD_F32", 4), "ptr<u64>": ("LOAD_U64", 8)}
 
-MAX_REGS, MAX_INSNS, MAX_BUFFERS = 256, 2048, 16
+MAX_REGS, MAX_INSNS, MAX_BUFFERS = 256, 2048, 16       # what the interpreter takes
+MAX_REGS_COMPILED = 4096                                # a compiled kernel's registers are PTX virtual registers
 
 
 def _mov(lowered):
@@ -203,8 +204,8 @@ class _Builder:
     def fresh(self):
         r = self.next_reg
         self.next_reg += 1
-        if self.fixed_presets is not None and self.next_reg > MAX_REGS:
-            raise Unsupported("the producer needs more than 256 registers")
+        if self.fixed_presets is not None and self.next_reg > MAX_REGS_COMPILED:
+            raise Unsupported("the producer needs more than 4096 registers")
         return r
 
     def const_value(self, reg):
@@ -559,8 +560,8 @@ def _compile(modules, name, env_vars, elem_lowered, body):
     second.fixed_presets = {what: k for k, what in enumerate(presets)}
     second.presets = presets
     second.next_reg = len(presets)
-    if second.next_reg >= MAX_REGS:
-        raise Unsupported("the producer needs more than 256 registers")
+    if second.next_reg >= MAX_REGS_COMPILED:
+        raise Unsupported("the producer needs more than 4096 registers")
     index, result = run(second)
     code, n_regs = second.code, max(second.next_reg, 1)
     if not any(c.op in (OP["JMP"], OP["JZ"]) for c in code):

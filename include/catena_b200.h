@@ -256,7 +256,8 @@ catena_status_t catena_b200_map_program_range_s(const catena_b200_map_insn_t* co
  * and the driver compiles it for the device (cuModuleLoadDataEx).  The compiled kernel gives the bits of the interpreter
  * above and reports the same faults through the same status, at the speed of a prebuilt map kernel.
  * `init_is_const[k] != 0` marks preset register k as a constant of the program (its value is taken from `init` now and
- * baked in); the other presets are environment values, read from the `init` of every launch.  NULL = none is constant.
+ * baked in); the other presets are environment values (at most 256), read from the `init` of every launch.  NULL = none is
+ * constant.  A compiled program may use up to 4096 registers (the interpreter: 256).
  * catena_b200_map_ptx_s only writes the PTX text (`length` receives its size with the terminator; `text` may be NULL to
  * ask for the size) and needs no GPU.  A kernel belongs to the device that was current when it was compiled and may be
  * launched from any host thread bound to that device; releasing it waits for the device to be idle first. */

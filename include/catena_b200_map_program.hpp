@@ -160,7 +160,8 @@ struct Program {
 
 namespace detail {
 
-constexpr uint32_t kMaxRegs = 256, kMaxInsns = 2048, kMaxBuffers = 16;
+// kMaxRegs: what the interpreter takes; a compiled kernel's registers are PTX virtual registers, up to kMaxRegsCompiled
+constexpr uint32_t kMaxRegs = 256, kMaxRegsCompiled = 4096, kMaxInsns = 2048, kMaxBuffers = 16;
 
 // a value while the program is built: a register, or a buffer of the launch's table (typed once cast)
 struct Sym {
@@ -228,7 +229,7 @@ public:
     uint32_t constant(uint64_t v) { Preset p; p.kind = Preset::Const; p.value = v; return preset(p); }
     uint32_t fresh() {
         const uint32_t r = next_reg_++;
-        if (fixed_ && next_reg_ > kMaxRegs) throw Unsupported("the producer needs more than 256 registers");
+        if (fixed_ && next_reg_ > kMaxRegsCompiled) throw Unsupported("the producer needs more than 4096 registers");
         return r;
     }
     size_t emit(int op, uint32_t dst = 0, uint32_t a = 0, uint32_t b = 0, uint32_t c = 0, uint32_t target = 0) {
@@ -622,7 +623,7 @@ inline Program compile(const std::vector<GpuModule>& modules, const std::string&
     std::vector<Preset> presets = first.presets();
     std::map<Preset, uint32_t> fixed;
     for (size_t k = 0; k < presets.size(); ++k) fixed[presets[k]] = (uint32_t)k;
-    if (presets.size() >= kMaxRegs) throw Unsupported("the producer needs more than 256 registers");
+    if (presets.size() >= kMaxRegsCompiled) throw Unsupported("the producer needs more than 4096 registers");
     Builder second(ev, &fixed, presets, (uint32_t)presets.size());
     run(second);
     prog.code = second.code;

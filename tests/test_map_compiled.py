@@ -132,3 +132,23 @@ def test_malformed_programs_get_no_text():
     init = (C.c_uint64 * 4)()
     assert L.catena_b200_map_ptx_s(arr, 1, init, None, 0, 4, 0, 0, 0, 8, text, 64, None) == cb.E_TOO_LARGE
     assert len(text.value) == 63
+
+
+def test_a_long_branching_producer_compiles_beyond_the_interpreters_register_file(tmp_path):
+    """Programs with branches get no register reuse from the host compiler, so a long one needs more than the interpreter's
+    256 registers; a compiled kernel's registers are PTX virtual registers (up to 4096) and the assembler allocates the real ones."""
+    from catena_lang_b200.map_program import MAX_REGS
+    mods, name = rp.generate(1124, n_ops=130, result="u64", control=True)
+    mm = lo.module_map(mods)
+    [launch] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+    prog = lo.map_program_for(launch, mm)
+    assert prog.n_regs > MAX_REGS
+    info = assemble(prog.ptx(), tmp_path)
+    assert "0 bytes spill stores" in info
+    # the interpreter's entry point refuses the same program before any launch
+    code = (Insn * len(prog.code))(*prog.code)
+    init = (C.c_uint64 * len(prog.presets))()
+    bufs = (cb.CatenaMem * 2)()
+    out = cb.CatenaMem()
+    assert cb.lib().catena_b200_map_program_s(code, len(prog.code), init, len(prog.presets), prog.n_regs, prog.index_reg, prog.result_reg,
+                                              bufs, 2, prog.elem_bytes, 4, C.byref(out)) == cb.E_BAD_ARG

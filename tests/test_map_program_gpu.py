@@ -372,3 +372,33 @@ def test_compiled_reciprocal_is_the_ieee_reciprocal_for_every_class_of_operand()
     with np.errstate(divide="ignore", invalid="ignore", over="ignore", under="ignore"):
         host = (np.float32(1.0) / x).astype(np.float32)
     assert np.array_equal(outs[1][ok], host.view(np.uint32)[ok])          # and both are numpy's IEEE quotient
+
+
+def test_a_producer_beyond_256_registers_runs_compiled():
+    """A long producer with a conditional and a fold (no register reuse across branches: more than the interpreter's 256
+    registers) runs as a compiled kernel and gives the bits of the CPU interpreter; the interpreter's entry point refuses it."""
+    import random_programs as rp
+    from catena_lang_b200.map_program import MAX_REGS
+    mods, name = rp.generate(1124, n_ops=130, result="u64", control=True)
+    mm = lo.module_map(mods)
+    [launch] = [a for a in mm[name].entry.assignments if a.op == "materializec"]
+    prog = lo.map_program_for(launch, mm)
+    assert prog.n_regs > MAX_REGS
+    table, xs = rp.tables(1124)
+    mt, mx = cb.upload(table), cb.upload(xs)
+    env = [0x0123456789ABCDEF, np.float32(1.5), (mt.data, mt.len), (mx.data, mx.len)]
+    n = 2000
+    raw = prog.launch(n, env, compiled=True)
+    got = cb.download(raw, np.uint64)
+    cb.free(raw)
+    want = map_vm.run(prog, [env[0], env[1], (0, table.nbytes), (0, xs.nbytes)], n, [table.view(np.uint8), xs.view(np.uint8)])
+    assert np.array_equal(got, want.astype(np.uint64))
+    with pytest.raises(cb.CatenaError) as err:
+        prog.launch(n, env, compiled=False)
+    assert err.value.status == cb.E_BAD_ARG
+    cb.free(mt)
+    cb.free(mx)
+    # through the runtime (compiled by default)
+    rt = cb.Runtime.from_modules(mods)
+    [out] = rt.exec(name, [env[0], env[1], rt.mem_u64(table), rt.mem_f32(xs), n])
+    assert np.array_equal(out.v.to_u64_vec(), got)
