@@ -193,8 +193,37 @@ struct Emitter {
         default: return false;
         }
     }
+    // In a whole tile the elements of a thread are index0 + e0 + v * 256: a load of buffer[index] needs ONE address (the others are
+    // constant offsets from it) and ONE bounds test (the last element's, indices ascend).  When that test fails the elements
+    // are tested one by one, as everywhere else.  %idx0 holds index0 + e0.
+    bool whole_tile = false;
+    uint32_t tile_loads = 0;
+    bool tile_load(uint32_t k) {
+        const catena_b200_map_insn_t& in = s.code[k];
+        const bool wide = in.op == CATENA_MAP_LOAD_U64;
+        if (!whole_tile || (!wide && in.op != CATENA_MAP_LOAD_F32) || in.a != s.index_reg) return false;
+        const uint32_t bytes = wide ? 8 : 4, id = tile_loads++;
+        line("add.u64 %%rd0, %%idx0, %u;", (lanes - 1) * kThreads);
+        line("setp.lt.u64 %%p1, %%rd0, %%bn%u_%u;", bytes, in.b);
+        line("@!%%p1 bra TL_EACH_%u;", id);
+        line("mad.lo.u64 %%rd1, %%idx0, %u, %%bb_%u;", bytes, in.b);
+        for (uint32_t v = 0; v < lanes; ++v) {
+            if (wide) {
+                line("ld.global.nc.b64 %%rd2, [%%rd1+%u];", v * kThreads * bytes);
+                unpack(v, in.dst, "%rd2");
+            } else {
+                line("ld.global.nc.b32 %s, [%%rd1+%u];", lo(v, in.dst).c_str(), v * kThreads * bytes);
+            }
+        }
+        line("bra TL_DONE_%u;", id);
+        out += "TL_EACH_" + std::to_string(id) + ":\n";
+        for (uint32_t v = 0; v < lanes; ++v) load(wide, v, in);
+        out += "TL_DONE_" + std::to_string(id) + ":\n";
+        return true;
+    }
     // instruction k for all elements of the thread
     void instruction_all(uint32_t k) {
+        if (tile_load(k)) return;
         for (uint32_t v = 0; v < lanes; ++v) {
             if (v + 1 < lanes && packed_pair(k, v)) ++v;
             else instruction(k, v);
@@ -347,7 +376,7 @@ struct Emitter {
             line(".reg .pred %%ok%u;", v);
         }
         if (nb) line(".reg .b64 %%bb_<%u>, %%bn8_<%u>, %%bn4_<%u>;", nb, nb, nb);
-        line(".reg .b64 %%rd<4>, %%out, %%index0, %%len, %%err, %%tile, %%tiles, %%step, %%tid64, %%nz2;");
+        line(".reg .b64 %%rd<4>, %%out, %%index0, %%len, %%err, %%tile, %%tiles, %%step, %%tid64, %%nz2, %%idx0;");
         line(".reg .b32 %%r<4>, %%fault, %%back, %%gave;");
         line(".reg .pred %%p<4>;");
         out += "\n";
@@ -405,24 +434,22 @@ struct Emitter {
             line("mul.lo.u64 %%rd0, %%rd0, %u;", per_tile);
             line("setp.gt.u64 %%p0, %%rd0, %%len;");
             line("@%%p0 bra RAGGED;");
-            line("add.u64 %%rd0, %%e0, %%index0;");
+            line("add.u64 %%idx0, %%e0, %%index0;");
             for (uint32_t v = 0; v < lanes; ++v) {
-                if (v) {
-                    line("add.u64 %%e%u, %%e0, %u;", v, v * kThreads);
-                    line("add.u64 %%rd1, %%rd0, %u;", v * kThreads);
-                }
-                unpack(v, s.index_reg, v ? "%rd1" : "%rd0");
+                if (v) line("add.u64 %%rd1, %%idx0, %u;", v * kThreads);
+                unpack(v, s.index_reg, v ? "%rd1" : "%idx0");
             }
+            whole_tile = true;
             for (uint32_t k = 0; k < s.n_insn && s.code[k].op != CATENA_MAP_HALT; ++k)
                 instruction_all(k);
+            whole_tile = false;
+            line("mad.lo.u64 %%rd0, %%e0, %u, %%out;", s.elem_bytes);        // one address, constant offsets
             for (uint32_t v = 0; v < lanes; ++v) {
                 if (s.elem_bytes == 8) {
                     line("mov.b64 %%rd1, {%s, %s};", lo(v, s.result_reg).c_str(), hi(v, s.result_reg).c_str());
-                    line("mad.lo.u64 %%rd0, %%e%u, 8, %%out;", v);
-                    line("st.global.b64 [%%rd0], %%rd1;");
+                    line("st.global.b64 [%%rd0+%u], %%rd1;", v * kThreads * 8);
                 } else {
-                    line("mad.lo.u64 %%rd0, %%e%u, 4, %%out;", v);
-                    line("st.global.b32 [%%rd0], %s;", lo(v, s.result_reg).c_str());
+                    line("st.global.b32 [%%rd0+%u], %s;", v * kThreads * 4, lo(v, s.result_reg).c_str());
                 }
             }
             line("bra NEXT;");
